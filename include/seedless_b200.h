@@ -1,0 +1,184 @@
+/* seedless_b200.h -- C ABI of libseedless_b200.so
+ *
+ * A B200 (sm_100a) implementation of the Seedless decode core of penta2himajin/qwisp: the
+ * per-token forward of a Qwen3-hybrid MoE model with 4-bit MLX-affine group-64 weights.
+ * The reference exposes this path as a Swift struct of closures that its Tell runtime calls
+ * (`Tell.SpecBackend`, swift/Sources/QwispCore/TellRuntime.swift:83-111) plus the batched
+ * engine protocol `BatchSlots` (swift/Sources/QwispCore/ContinuousBatch.swift:38-66); each
+ * entry point below names the closure / method it replaces.
+ *
+ * Conventions: every function returns an int32 status, 0 = ok, < 0 = error.  After any
+ * device-side or injected failure the engine is poisoned: every later call on it returns
+ * SL_ERR_POISONED and sl_last_fault() returns the first fault's text (the reference's GPU
+ * fault firewall, swift/Sources/QwispCore/SeedlessFusedVerify.swift:376-416).
+ * One thread at a time per engine (the reference serialises decode the same way,
+ * swift/Sources/QwispCore/LLMBackend.swift:121-142).  All pointers are plain host pointers
+ * unless a parameter says "device".  fp16 values are passed as uint16_t bit patterns.
+ * There is no CPU fallback: every entry point fails with SL_ERR_NO_DEVICE without a GPU.
+ */
+#ifndef SEEDLESS_B200_H
+#define SEEDLESS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    SL_OK = 0,
+    SL_ERR_INVALID = -1,      /* bad argument / shape */
+    SL_ERR_NO_DEVICE = -2,    /* no usable CUDA device */
+    SL_ERR_CUDA = -3,         /* a CUDA call failed (engine poisoned) */
+    SL_ERR_POISONED = -4,     /* engine already poisoned by an earlier fault */
+    SL_ERR_CAPACITY = -5,     /* rows > max_rows, sequence > max_seq_len, out of KV pages ... */
+    SL_ERR_NOT_FOUND = -6,    /* unknown tensor name */
+    SL_ERR_FORMAT = -7        /* malformed state blob */
+};
+
+/* Model geometry (swift/Sources/QwispCore/QwispModel.swift:83-120; the reference hard-codes
+ * these, swift/Sources/QwispCore/SeedlessEngine.swift:13-16) and engine sizing
+ * (maxM / maxSeqLen of SeedlessFusedForward.init, SeedlessFusedVerify.swift:3368-3374).
+ * Fixed by the kernels: GDN head dim 128, conv kernel 4, attention head dim 256, rope dim 64,
+ * group size 64, 4 bit.  hidden and moe_inter must be multiples of 256. */
+typedef struct sl_config {
+    int32_t hidden;          /* 2048 */
+    int32_t n_layers;        /* 40 */
+    int32_t attn_every;      /* 4: layer i is full attention iff (i+1) % attn_every == 0 */
+    int32_t vocab;           /* 151936 (multiple of 16) */
+    int32_t n_experts;       /* 256 (<= 256) */
+    int32_t top_k;           /* 8 */
+    int32_t moe_inter;       /* 512 */
+    int32_t gdn_k_heads;     /* 16 */
+    int32_t gdn_v_heads;     /* 32 */
+    int32_t attn_heads;      /* 16 */
+    int32_t attn_kv_heads;   /* 2 */
+    float rope_theta;        /* 1e7 */
+    float rms_eps;           /* 1e-6 */
+    int32_t max_rows;        /* rows (tokens) per call, all streams together */
+    int32_t max_streams;     /* stream slots (each holds GDN state + a KV page table) */
+    int32_t kv_page_size;    /* positions per KV page (multiple of 32) */
+    int32_t kv_pages;        /* pages in the engine's KV arena, shared by all streams */
+} sl_config;
+
+/* One named tensor handed to sl_engine_create.  Names: "embed", "final_norm", "lm_head.w/.s/.b",
+ * "L<i>.in_norm", "L<i>.post_norm", "L<i>.gdn.in_proj_qkv.w/.s/.b" (also _z,_b,_a),
+ * "L<i>.gdn.conv_w" (f32 [convDim,4]), "L<i>.gdn.A_log", "L<i>.gdn.dt_bias" (f32),
+ * "L<i>.gdn.norm", "L<i>.gdn.out_proj.*", "L<i>.attn.q_proj.*" (k_,v_,o_), "L<i>.attn.q_norm",
+ * "L<i>.attn.k_norm", "L<i>.moe.router" (fp16 [E,H]), "L<i>.moe.shared_gate" (fp16 [H]),
+ * "L<i>.moe.gate_proj.*" ([E*I,H]), "L<i>.moe.up_proj.*", "L<i>.moe.down_proj.*" ([E*H,I]),
+ * "L<i>.moe.shared_gate_proj.*", "L<i>.moe.shared_up_proj.*", "L<i>.moe.shared_down_proj.*".
+ * 4-bit tensors are in the MLX affine layout: .w uint32 [N,K/8] (8 nibbles per word, low
+ * first), .s/.b fp16 [N,K/64] (SeedlessMetalForward.swift:219-221).  The data is copied. */
+typedef struct sl_weight_desc {
+    const char* name;
+    const void* data;
+    uint64_t nbytes;
+    int32_t on_device;       /* 0 = host pointer, 1 = device pointer */
+} sl_weight_desc;
+
+/* Seeded synthetic weights generated on the device (integer hash -> Irwin-Hall normal ->
+ * fp16 -> 4-bit affine quantiser), bit-identical to the CPU oracle's generator. */
+typedef struct sl_synth_spec {
+    uint64_t seed;
+    float norm_jitter;       /* RMSNorm weights = 1 + N(0, norm_jitter); 0 => exactly 1 */
+    float conv_std;          /* std of the depthwise conv weights */
+} sl_synth_spec;
+
+typedef struct sl_engine sl_engine;
+typedef struct sl_stream sl_stream;
+typedef struct sl_fullsnap sl_fullsnap;
+typedef struct sl_snap { int32_t kv_len; int32_t parity; int32_t valid; } sl_snap;
+
+/* ---- engine (SeedlessEngine.build + makeFused, SeedlessEngine.swift:33-144) ---- */
+int32_t sl_engine_create(const sl_config* cfg, const sl_weight_desc* weights, int32_t n_weights, sl_engine** out);
+int32_t sl_engine_create_synthetic(const sl_config* cfg, const sl_synth_spec* synth, sl_engine** out);
+int32_t sl_engine_destroy(sl_engine* e);
+/* Run all work of this engine on the given CUDA stream (a cudaStream_t); NULL = the engine's own. */
+int32_t sl_engine_set_cuda_stream(sl_engine* e, void* cuda_stream);
+/* Copy a named tensor back to the host (parity checks of the loader / generator). */
+int32_t sl_engine_read_tensor(sl_engine* e, const char* name, void* host_buf, uint64_t nbytes);
+int32_t sl_engine_tensor_bytes(sl_engine* e, const char* name, uint64_t* nbytes);
+/* Sticky fault text or NULL (SpecBackend.gpuFault, TellRuntime.swift:107-110). */
+const char* sl_last_fault(sl_engine* e);
+/* Host-side test hook: the next device-touching call reports failure and poisons the engine
+ * (mirrors `injectCBFailure`, SeedlessFusedVerify.swift:403-404).  Never faults the GPU. */
+int32_t sl_inject_fault(sl_engine* e, int32_t on);
+/* Kernels this engine has launched so far (bench bookkeeping). */
+int64_t sl_engine_launch_count(sl_engine* e);
+
+/* ---- stream = one sequence's caches: KV page table + GDN state ("backend instance" /
+ *      "lane", SeedlessFusedVerify.swift:3368-3452, LaneServe.swift:256) ---- */
+int32_t sl_stream_create(sl_engine* e, int32_t max_seq_len, sl_stream** out);
+int32_t sl_stream_destroy(sl_stream* s);
+int32_t sl_stream_len(sl_stream* s);
+int32_t sl_stream_reset(sl_stream* s);
+
+/* SpecBackend.forward (TellRuntime.swift:84; SeedlessFusedVerify.swift:3641): embed + all
+ * layers + final norm for M tokens appended at the current position; out_normed_f16 [M,H]
+ * (may be NULL). */
+int32_t sl_forward(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_normed_f16);
+/* SpecBackend.stepArgmax (SeedlessFusedVerify.swift:3832-3912): forward + lm_head + per-row
+ * greedy argmax (first maximum wins); only int32[M] is read back. */
+int32_t sl_step_argmax(sl_stream* s, const int32_t* tokens, int32_t M, int32_t* out_tokens);
+/* SpecBackend.chainedStepArgmax (SeedlessFusedVerify.swift:4405-4513): K greedy steps with
+ * the token fed back on the device; identical to K calls of sl_step_argmax with M = 1. */
+int32_t sl_chained_step_argmax(sl_stream* s, int32_t first, int32_t K, int32_t* out_tokens);
+/* The same split in two so a caller can time the device work alone: enqueue K chained steps
+ * (first < 0: continue from the token the previous step produced, already on the device),
+ * then collect the K tokens (synchronises). */
+int32_t sl_chained_enqueue(sl_stream* s, int32_t first, int32_t K);
+int32_t sl_chained_collect(sl_stream* s, int32_t K, int32_t* out_tokens);
+/* SpecBackend.stepLogitsRows (TellRuntime.swift:115-121): full fp16 logits [M,V] read back. */
+int32_t sl_step_logits(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_logits_f16);
+
+/* SpecBackend.snapshot / rollback (SeedlessFusedVerify.swift:4039-4047): undo exactly one
+ * following forward/step: KV length rewind + GDN ping-pong swap. */
+int32_t sl_snapshot(sl_stream* s, sl_snap* out);
+int32_t sl_rollback_one_step(sl_stream* s, const sl_snap* snap);
+/* fullSnapshot / fullRestore (SeedlessFusedVerify.swift:4053-4068): arbitrary rewind inside
+ * the same stream: KV length + deep copy of the GDN state. */
+int32_t sl_full_snapshot(sl_stream* s, sl_fullsnap** out);
+int32_t sl_full_restore(sl_stream* s, const sl_fullsnap* snap);
+int32_t sl_fullsnap_free(sl_fullsnap* snap);
+/* persistentStateData / restorePersistentState (SeedlessFusedVerify.swift:4077-4154): the
+ * self-describing "QWS1" blob; restorable into a stream of a different max_seq_len.
+ * sl_state_restore returns SL_ERR_FORMAT on any mismatch; the stream must then be reset. */
+int32_t sl_state_size(sl_stream* s, uint64_t* nbytes);
+int32_t sl_state_save(sl_stream* s, void* buf, uint64_t nbytes);
+int32_t sl_state_restore(sl_stream* s, const void* buf, uint64_t nbytes);
+
+/* BatchSlots.step / SeedlessLaneBatch.stepArgmaxBatch (SeedlessLaneBatch.swift:876): one
+ * greedy step over B streams, one token each; row b is bit-identical to a solo step. */
+int32_t sl_batch_step_argmax(sl_engine* e, sl_stream* const* streams, const int32_t* tokens, int32_t B, int32_t* out_tokens);
+
+/* ---- single operators (the reference's per-op wrappers used by its kernel tests:
+ *      SeedlessMetalForward.qmm SeedlessMetalForward.swift:222, routeTop8Rows
+ *      SeedlessFusedVerify.swift:174, moeBlockRows / gdnLayerRows / attnLayerRows
+ *      SeedlessVerifyForward.swift:37-248) ---- */
+/* y[M,N] = x[M,K] . dequant4(W[N,K])^T; host buffers; N % 16 == 0, K % 256 == 0. */
+int32_t sl_op_qmm4(const uint16_t* x_f16, const uint32_t* w, const uint16_t* scales_f16, const uint16_t* biases_f16,
+                   int32_t M, int32_t K, int32_t N, uint16_t* y_f16);
+/* Same on device buffers, enqueued on cuda_stream without synchronising (micro-benchmarks). */
+int32_t sl_op_qmm4_device(const void* x_dev, const void* w_dev, const void* s_dev, const void* b_dev,
+                          int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream);
+/* 4-bit affine quantiser on the device: w fp16 [N,K] -> packed/scales/biases (host buffers). */
+int32_t sl_op_quantize_q4(const uint16_t* w_f16, int64_t N, int64_t K, uint32_t* packed, uint16_t* scales_f16, uint16_t* biases_f16);
+/* MoE block of `layer` on already-normed rows x [M,H]: out [M,H], inds [M,top_k], scores fp16. */
+int32_t sl_op_moe_block(sl_engine* e, int32_t layer, const uint16_t* x_f16, int32_t M,
+                        uint16_t* out_f16, int32_t* inds, uint16_t* scores_f16);
+/* Mixer (GDN or attention) of `layer` on already-normed rows x [M,H] placed at positions
+ * pos0..pos0+M-1 of the stream; advances only that layer's cache, not the stream length. */
+int32_t sl_op_mixer(sl_stream* s, int32_t layer, const uint16_t* x_f16, int32_t M, int32_t pos0, uint16_t* out_f16);
+/* final-norm'ed rows -> logits (may be NULL) and greedy tokens (may be NULL). */
+int32_t sl_op_lm_head(sl_engine* e, const uint16_t* normed_f16, int32_t M, uint16_t* out_logits_f16, int32_t* out_tokens);
+
+/* ---- synthetic data helpers (same generator as the engine's weights) ---- */
+int32_t sl_synth_tokens(uint64_t seed, const char* name, int64_t n, int32_t vocab, int32_t* out);
+int32_t sl_synth_f16(uint64_t seed, const char* name, int64_t n, float mean, float std, uint16_t* out_f16);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

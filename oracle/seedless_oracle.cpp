@@ -1,0 +1,789 @@
+// seedless_oracle.cpp -- CPU restatement of the Seedless decode core of penta2himajin/qwisp.
+//
+// TEST INFRASTRUCTURE ONLY.  Nothing in the product (the CUDA library, the Python package)
+// may import, link or call this file; only tests/, the smoke check and the CPU-baseline /
+// reference legs of bench.py use it, as the checker and as the timed host baseline.
+//
+// PARITY UNPINNED: the reference ships no golden vectors for this path (all of its
+// comparisons are computed at run time against MLX on an Apple GPU) and neither Swift/Metal
+// nor MLX exists on this machine, so this restatement cannot be checked against outputs of
+// the reference itself.  It follows the reference's Metal kernel bodies op for op, with fp16
+// rounding at exactly the points those kernels round.  Where Apple's `simd_sum` leaves the
+// order unspecified, a fixed xor-butterfly over the 32 lanes is used and thereby defined as
+// canonical.  The one stored CPU reference the project has (a float64 attention reference
+// inside its test 96) is restated in tests/ and used to pin the attention op.
+//
+// File:line citations are paths inside the reference project:
+//   SMF = swift/Sources/QwispCore/SeedlessMetalForward.swift
+//   SFV = swift/Sources/QwispCore/SeedlessFusedVerify.swift
+//   SVF = swift/Sources/QwispCore/SeedlessVerifyForward.swift
+//   GD  = swift/Sources/QwispCore/GatedDelta.swift
+//
+// Third-party arithmetic that is NOT in the reference tree: the 4-bit affine quantiser
+// `MLX.quantized(w, groupSize:64, bits:4, mode:.affine)` of mlx-swift 0.31.4 (python mlx
+// 0.31.2).  Its published algorithm (per group: scale from (max-min)/15 signed towards the
+// larger-magnitude edge, edge snapped onto the grid, bias = edge) is restated in
+// quantize_group(); the dequant contract w = scale*q + bias with 8 nibbles per uint32,
+// low nibble first, fp16 scale/bias per 64 inputs is the reference's own (SMF:82-87,219-221).
+//
+// Build: see oracle/Makefile (g++ -O2 -ffp-contract=off -fopenmp, x86-64-v3).
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+#include <algorithm>
+
+typedef _Float16 h16;
+
+// ---------------------------------------------------------------- fp16 helpers
+// Every fp16 operation is done as: widen to float, one float op, round to fp16.  For + - * /
+// this equals a correctly rounded fp16 operation (float carries >= 2*11+2 bits).
+static inline float h2f(h16 a) { return (float)a; }
+static inline h16 f2h(float a) { return (h16)a; }
+static inline h16 hadd(h16 a, h16 b) { return f2h(h2f(a) + h2f(b)); }
+static inline h16 hsub(h16 a, h16 b) { return f2h(h2f(a) - h2f(b)); }
+static inline h16 hmul(h16 a, h16 b) { return f2h(h2f(a) * h2f(b)); }
+static inline h16 hdiv(h16 a, h16 b) { return f2h(h2f(a) / h2f(b)); }
+static inline h16 hexp(h16 a) { return f2h(expf(h2f(a))); }
+static inline h16 habs(h16 a) { return f2h(fabsf(h2f(a))); }
+static inline float rsqrt_rn(float v) { return (float)(1.0 / sqrt((double)v)); }
+
+// "MLX stable sigmoid" in fp16 arithmetic (SMF:986-988): y = 1/(1+exp(|x|)); x<0 ? y : 1-y
+static inline h16 sigmoid_h(h16 x) {
+    h16 one = f2h(1.0f);
+    h16 y = hdiv(one, hadd(one, hexp(habs(x))));
+    return (h2f(x) < 0.0f) ? y : hsub(one, y);
+}
+// same in f32 (SMF:1599-1602, SFV:808-812)
+static inline float sigmoid_f(float x) {
+    float y = 1.0f / (1.0f + expf(fabsf(x)));
+    return (x < 0.0f) ? y : (1.0f - y);
+}
+
+// Canonical stand-in for Metal's simd_sum over 32 lanes: xor butterfly, offsets 16,8,4,2,1.
+static inline float bfly_sum32(const float* v) {
+    float a[32], b[32];
+    for (int i = 0; i < 32; ++i) a[i] = v[i];
+    for (int off = 16; off >= 1; off >>= 1) {
+        for (int i = 0; i < 32; ++i) b[i] = a[i] + a[i ^ off];
+        for (int i = 0; i < 32; ++i) a[i] = b[i];
+    }
+    return a[0];
+}
+static inline float bfly_max32(const float* v) {
+    float m = v[0];
+    for (int i = 1; i < 32; ++i) m = fmaxf(m, v[i]);
+    return m;
+}
+
+// ---------------------------------------------------------------- synthetic data
+// Counter-based generator using integer arithmetic only, so that the CUDA library can
+// produce bit-identical tensors on the device: value = (sum of eight 16-bit uniforms,
+// centred) * C * std, an Irwin-Hall approximation of N(0, std) with support +-4.9 sigma.
+static inline uint64_t mix64(uint64_t z) {
+    z ^= z >> 30; z *= 0xbf58476d1ce4e5b9ULL;
+    z ^= z >> 27; z *= 0x94d049bb133111ebULL;
+    z ^= z >> 31; return z;
+}
+static const uint64_t GOLD = 0x9E3779B97F4A7C15ULL;
+static const float UNIT_C = 0x1.3988e2p-16f;   // 1/sqrt(8*(2^32-1)/12)
+
+static inline uint64_t tensor_seed(uint64_t base_seed, const char* name) {
+    uint64_t h = 0xcbf29ce484222325ULL;
+    for (const char* p = name; *p; ++p) { h ^= (uint8_t)*p; h *= 0x100000001b3ULL; }
+    return mix64(h ^ mix64(base_seed));
+}
+static inline float synth_unit(uint64_t tseed, uint64_t idx) {
+    uint64_t r1 = mix64(tseed + GOLD * (2 * idx + 1));
+    uint64_t r2 = mix64(r1 ^ 0xD1B54A32D192ED03ULL);
+    int32_t s = (int32_t)(r1 & 0xffff) + (int32_t)((r1 >> 16) & 0xffff) +
+                (int32_t)((r1 >> 32) & 0xffff) + (int32_t)(r1 >> 48) +
+                (int32_t)(r2 & 0xffff) + (int32_t)((r2 >> 16) & 0xffff) +
+                (int32_t)((r2 >> 32) & 0xffff) + (int32_t)(r2 >> 48);
+    s -= 4 * 65535;
+    return (float)s * UNIT_C;
+}
+
+extern "C" uint64_t orc_tensor_seed(uint64_t base_seed, const char* name) { return tensor_seed(base_seed, name); }
+
+// out[i] = fp16(mean + unit(i)*std)   (mean 0 for weights, 1 for jittered norm weights)
+extern "C" void orc_synth_f16(uint64_t tseed, uint64_t n, float mean, float std, h16* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i) {
+        float v = synth_unit(tseed, (uint64_t)i) * std;
+        out[i] = f2h(mean + v);
+    }
+}
+extern "C" void orc_synth_f32(uint64_t tseed, uint64_t n, float mean, float std, float* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)n; ++i) out[i] = mean + synth_unit(tseed, (uint64_t)i) * std;
+}
+extern "C" void orc_synth_tokens(uint64_t tseed, uint64_t n, int32_t vocab, int32_t* out) {
+    for (uint64_t i = 0; i < n; ++i) out[i] = (int32_t)(mix64(tseed + GOLD * (2 * i + 1)) % (uint64_t)vocab);
+}
+
+// ---------------------------------------------------------------- 4-bit affine quantiser
+// Published MLX affine quantisation (mlx 0.31.x `quantize`, mode affine), group of 64, 4 bit.
+static inline void quantize_group(const h16* w, uint32_t* packed8, h16* scale_out, h16* bias_out) {
+    float wmin = h2f(w[0]), wmax = h2f(w[0]);
+    for (int j = 1; j < 64; ++j) { float v = h2f(w[j]); wmin = fminf(wmin, v); wmax = fmaxf(wmax, v); }
+    const float n_bins = 15.0f, eps = 1e-7f;
+    float scale = fmaxf((wmax - wmin) / n_bins, eps);
+    bool side = fabsf(wmin) > fabsf(wmax);
+    scale = side ? scale : -scale;
+    float edge = side ? wmin : wmax;
+    float q0 = roundf(edge / scale);
+    bool at_zero = (q0 == 0.0f);
+    scale = at_zero ? scale : edge / q0;
+    float bias = at_zero ? 0.0f : edge;
+    *scale_out = f2h(scale);
+    *bias_out = f2h(bias);
+    for (int p = 0; p < 8; ++p) {
+        uint32_t word = 0;
+        for (int j = 0; j < 8; ++j) {
+            float q = roundf((h2f(w[p * 8 + j]) - bias) / scale);
+            q = fminf(fmaxf(q, 0.0f), n_bins);
+            word |= ((uint32_t)q & 0xfu) << (4 * j);
+        }
+        packed8[p] = word;
+    }
+}
+// w [N,K] fp16 -> packed [N,K/8] u32, scales/biases [N,K/64] fp16
+extern "C" void orc_quantize_q4(const h16* w, int64_t N, int64_t K, uint32_t* packed, h16* scales, h16* biases) {
+    int64_t G = K / 64;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t g = 0; g < G; ++g)
+            quantize_group(w + n * K + g * 64, packed + n * (K / 8) + g * 8, scales + n * G + g, biases + n * G + g);
+}
+// generate fp16 ~N(0,std) from the tensor seed and quantise, without materialising w
+static void synth_quantized(uint64_t tseed, int64_t N, int64_t K, float std, uint32_t* packed, h16* scales, h16* biases) {
+    int64_t G = K / 64;
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        h16 buf[64];
+        for (int64_t g = 0; g < G; ++g) {
+            uint64_t base = (uint64_t)(n * K + g * 64);
+            for (int j = 0; j < 64; ++j) buf[j] = f2h(0.0f + synth_unit(tseed, base + j) * std);
+            quantize_group(buf, packed + n * (K / 8) + g * 8, scales + n * G + g, biases + n * G + g);
+        }
+    }
+}
+extern "C" void orc_synth_q4(uint64_t tseed, int64_t N, int64_t K, float std, uint32_t* packed, h16* scales, h16* biases) {
+    synth_quantized(tseed, N, K, std, packed, scales, biases);
+}
+extern "C" void orc_dequant_q4(const uint32_t* packed, const h16* scales, const h16* biases, int64_t N, int64_t K, float* out) {
+    int64_t G = K / 64;
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t k = 0; k < K; ++k) {
+            uint32_t q = (packed[n * (K / 8) + k / 8] >> (4 * (k % 8))) & 0xf;
+            out[n * K + k] = h2f(scales[n * G + k / 64]) * (float)q + h2f(biases[n * G + k / 64]);
+        }
+}
+
+// ---------------------------------------------------------------- q4 GEMV (SMF:238-310)
+// One output element.  32 lanes; per 512-wide block lane l owns 16 consecutive inputs
+// (2 packs); per lane-block: sum of x (4-element partial sums in fp16, SMF:241), products
+// x*q (exact), four-term sums left to right, then scale*accum + sum*bias; lanes are
+// combined by the canonical butterfly; result rounded to fp16.
+static inline float qdot_row(const h16* x, const uint32_t* wrow, const h16* srow, const h16* brow, int K) {
+    float lane[32];
+    for (int l = 0; l < 32; ++l) lane[l] = 0.0f;
+    for (int kb = 0; kb < K; kb += 512) {
+        for (int l = 0; l < 32; ++l) {
+            const h16* xp = x + kb + l * 16;
+            float sum = 0.0f, xv[16];
+            for (int i = 0; i < 16; i += 4) {
+                h16 hs = hadd(hadd(hadd(xp[i], xp[i + 1]), xp[i + 2]), xp[i + 3]);
+                sum += h2f(hs);
+                xv[i] = h2f(xp[i]); xv[i + 1] = h2f(xp[i + 1]); xv[i + 2] = h2f(xp[i + 2]); xv[i + 3] = h2f(xp[i + 3]);
+            }
+            const uint32_t* wp = wrow + (kb + l * 16) / 8;
+            float accum = 0.0f;
+            for (int i = 0; i < 4; ++i) {
+                uint32_t ws = (i & 1) ? (wp[i >> 1] >> 16) : (wp[i >> 1] & 0xffffu);
+                // x/16^j * (nibble<<4j) == x*nibble exactly (SMF:243-245,253-256)
+                float t = xv[4 * i] * (float)(ws & 0xf) + xv[4 * i + 1] * (float)((ws >> 4) & 0xf);
+                t = t + xv[4 * i + 2] * (float)((ws >> 8) & 0xf);
+                t = t + xv[4 * i + 3] * (float)((ws >> 12) & 0xf);
+                accum += t;
+            }
+            int g = (kb + l * 16) / 64;
+            float sc = h2f(srow[g]), bi = h2f(brow[g]);
+            lane[l] += sc * accum + sum * bi;
+        }
+    }
+    return bfly_sum32(lane);
+}
+// y[M,N] = x[M,K] . dequant(W[N,K])^T, fp16 out
+extern "C" void orc_qmm4(const h16* x, const uint32_t* packed, const h16* scales, const h16* biases,
+                         int M, int K, int N, h16* y) {
+    int G = K / 64;
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int m = 0; m < M; ++m)
+            y[(int64_t)m * N + n] = f2h(qdot_row(x + (int64_t)m * K, packed + (int64_t)n * (K / 8), scales + (int64_t)n * G, biases + (int64_t)n * G, K));
+}
+
+// fp16-weight GEMV used for the router [E,H] and the shared-expert gate [1,H].  The reference
+// stores both 8-bit (SMF:384-434); the benchmark configuration names them fp16, so the lane
+// structure of that kernel is kept (lane l owns 8 consecutive inputs per 256-wide block,
+// sequential f32 accumulate, butterfly) with the fp16 weight in place of the dequantised one.
+static inline float fdot_row(const h16* x, const h16* wrow, int K) {
+    float lane[32];
+    for (int l = 0; l < 32; ++l) lane[l] = 0.0f;
+    for (int kb = 0; kb < K; kb += 256)
+        for (int l = 0; l < 32; ++l) {
+            const h16* xp = x + kb + l * 8; const h16* wp = wrow + kb + l * 8;
+            float acc = lane[l];
+            for (int i = 0; i < 8; ++i) acc += h2f(xp[i]) * h2f(wp[i]);
+            lane[l] = acc;
+        }
+    return bfly_sum32(lane);
+}
+extern "C" void orc_fmm(const h16* x, const h16* w, int M, int K, int N, h16* y) {
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int m = 0; m < M; ++m) y[(int64_t)m * N + n] = f2h(fdot_row(x + (int64_t)m * K, w + (int64_t)n * K, K));
+}
+
+// ---------------------------------------------------------------- RMSNorm (SMF:788-828)
+// threads of 4 consecutive elements, f32 sum of squares, butterfly per 32-lane group, second
+// butterfly over the (zero padded) 32 group sums, inv = rsqrt(acc/D + eps),
+// out = w * fp16(x*inv) as an fp16 product.  w == nullptr means a weight of ones.
+static float rms_inv(const h16* x, int D, float eps) {
+    int nthreads = (D + 3) / 4;
+    int ngroups = (nthreads + 31) / 32;
+    float gsum[32];
+    for (int i = 0; i < 32; ++i) gsum[i] = 0.0f;
+    for (int g = 0; g < ngroups; ++g) {
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            int t = g * 32 + l; float acc = 0.0f;
+            for (int i = 0; i < 4; ++i) { int d = t * 4 + i; if (t < nthreads && d < D) { float xi = h2f(x[d]); acc += xi * xi; } }
+            lane[l] = acc;
+        }
+        gsum[g] = bfly_sum32(lane);
+    }
+    float acc = bfly_sum32(gsum);
+    return rsqrt_rn(acc / (float)D + eps);
+}
+static void rmsnorm_row(const h16* x, const h16* w, int D, float eps, h16* out) {
+    float inv = rms_inv(x, D, eps);
+    for (int d = 0; d < D; ++d) {
+        h16 nv = f2h(h2f(x[d]) * inv);
+        out[d] = w ? hmul(w[d], nv) : nv;
+    }
+}
+extern "C" void orc_rmsnorm(const h16* x, const h16* w, int M, int D, float eps, h16* out) {
+    for (int m = 0; m < M; ++m) rmsnorm_row(x + (int64_t)m * D, w, D, eps, out + (int64_t)m * D);
+}
+
+// ---------------------------------------------------------------- router top-k (SFV:180-214)
+// logits fp16 [E]: max; e=exp(l-max); Z by halving tree over 256 slots; gates=fp16(e/Z);
+// k rounds of arg-max on the raw logits (strict > in the tree => lowest index wins ties);
+// scores = gates of the chosen; fp16 sequential sum; fp16 divide.
+static void route_row(const h16* logits, int E, int topk, int32_t* inds, h16* scores) {
+    const int TG = 256;
+    float lg[TG], red[TG], gates[TG], work[TG];
+    int redi[TG];
+    for (int i = 0; i < TG; ++i) lg[i] = (i < E) ? h2f(logits[i]) : -INFINITY;
+    float m = lg[0];
+    for (int i = 1; i < TG; ++i) m = fmaxf(m, lg[i]);
+    for (int i = 0; i < TG; ++i) red[i] = (i < E) ? expf(lg[i] - m) : 0.0f;
+    float e[TG];
+    for (int i = 0; i < TG; ++i) e[i] = red[i];
+    for (int s = TG / 2; s > 0; s >>= 1) for (int i = 0; i < s; ++i) red[i] += red[i + s];
+    float Z = red[0];
+    for (int i = 0; i < TG; ++i) { gates[i] = (i < E) ? h2f(f2h(e[i] / Z)) : 0.0f; work[i] = lg[i]; }
+    for (int k = 0; k < topk; ++k) {
+        for (int i = 0; i < TG; ++i) { red[i] = work[i]; redi[i] = i; }
+        for (int s = TG / 2; s > 0; s >>= 1)
+            for (int i = 0; i < s; ++i) if (red[i + s] > red[i]) { red[i] = red[i + s]; redi[i] = redi[i + s]; }
+        int bi = redi[0];
+        inds[k] = bi; scores[k] = f2h(gates[bi]); work[bi] = -INFINITY;
+    }
+    h16 ss = f2h(0.0f);
+    for (int k = 0; k < topk; ++k) ss = hadd(ss, scores[k]);
+    for (int k = 0; k < topk; ++k) scores[k] = hdiv(scores[k], ss);
+}
+extern "C" void orc_route_topk(const h16* logits, int M, int E, int topk, int32_t* inds, h16* scores) {
+    for (int m = 0; m < M; ++m) route_row(logits + (int64_t)m * E, E, topk, inds + m * topk, scores + m * topk);
+}
+
+// ---------------------------------------------------------------- model
+struct OrcConfig {
+    int32_t hidden, n_layers, attn_every, vocab;
+    int32_t n_experts, top_k, moe_inter;
+    int32_t gdn_k_heads, gdn_v_heads;        // head dim 128, conv kernel 4
+    int32_t attn_heads, attn_kv_heads;       // head dim 256, rope dim 64
+    float rope_theta, rms_eps;
+    float norm_jitter;                        // 0 => norm weights are exactly 1
+    float conv_std;                           // std of the depthwise conv weights
+};
+static const int DK = 128, DV = 128, CONVK = 4, HD = 256, ROPE = 64;
+
+struct Q4 { std::vector<uint32_t> w; std::vector<h16> s, b; int64_t N = 0, K = 0;
+    const uint32_t* row_w(int64_t n) const { return w.data() + n * (K / 8); }
+    const h16* row_s(int64_t n) const { return s.data() + n * (K / 64); }
+    const h16* row_b(int64_t n) const { return b.data() + n * (K / 64); } };
+
+struct Layer {
+    bool is_attn;
+    std::vector<h16> in_norm, post_norm;
+    // GDN
+    Q4 in_qkv, in_z, in_b, in_a, gdn_out;
+    std::vector<float> conv_w, A_log, dt_bias;
+    std::vector<h16> gdn_norm;
+    // attention
+    Q4 q_proj, k_proj, v_proj, o_proj;
+    std::vector<h16> q_norm, k_norm;
+    // MoE
+    std::vector<h16> router, shared_gate;
+    Q4 gate_proj, up_proj, down_proj;             // [E*I,H], [E*I,H], [E*H,I]
+    Q4 sh_gate, sh_up, sh_down;
+};
+struct Model {
+    OrcConfig c; uint64_t seed;
+    std::vector<h16> embed, final_norm; Q4 lm_head;
+    std::vector<Layer> layers;
+    std::map<std::string, std::pair<const void*, size_t>> index;
+};
+struct LayerState {
+    std::vector<h16> kc, vc;          // attention: [kvh][cap][256]
+    std::vector<h16> conv;            // GDN: [3][convDim]
+    std::vector<float> S;             // GDN: [Hv][Dv][Dk]
+};
+struct Stream { Model* m; int cap; int len; std::vector<LayerState> L; };
+
+static void make_q4(Model* M, Q4& q, const std::string& name, int64_t N, int64_t K) {
+    q.N = N; q.K = K; q.w.resize(N * K / 8); q.s.resize(N * K / 64); q.b.resize(N * K / 64);
+    synth_quantized(tensor_seed(M->seed, name.c_str()), N, K, 0.02f, q.w.data(), q.s.data(), q.b.data());
+    M->index[name + ".w"] = {q.w.data(), q.w.size() * 4};
+    M->index[name + ".s"] = {q.s.data(), q.s.size() * 2};
+    M->index[name + ".b"] = {q.b.data(), q.b.size() * 2};
+}
+static void make_f16(Model* M, std::vector<h16>& v, const std::string& name, int64_t n, float mean, float std) {
+    v.resize(n); orc_synth_f16(tensor_seed(M->seed, name.c_str()), n, mean, std, v.data());
+    M->index[name] = {v.data(), v.size() * 2};
+}
+static void make_f32(Model* M, std::vector<float>& v, const std::string& name, int64_t n, float mean, float std) {
+    v.resize(n); orc_synth_f32(tensor_seed(M->seed, name.c_str()), n, mean, std, v.data());
+    M->index[name] = {v.data(), v.size() * 4};
+}
+
+extern "C" void* orc_model_create(const OrcConfig* cfg, uint64_t seed) {
+    Model* M = new Model(); M->c = *cfg; M->seed = seed;
+    const OrcConfig& c = M->c;
+    int H = c.hidden, E = c.n_experts, I = c.moe_inter;
+    int keyDim = c.gdn_k_heads * DK, valDim = c.gdn_v_heads * DV, convDim = 2 * keyDim + valDim;
+    make_f16(M, M->embed, "embed", (int64_t)c.vocab * H, 0.0f, 0.02f);
+    make_f16(M, M->final_norm, "final_norm", H, 1.0f, c.norm_jitter);
+    make_q4(M, M->lm_head, "lm_head", c.vocab, H);
+    M->layers.resize(c.n_layers);
+    for (int i = 0; i < c.n_layers; ++i) {
+        Layer& L = M->layers[i];
+        std::string p = "L" + std::to_string(i) + ".";
+        L.is_attn = ((i + 1) % c.attn_every) == 0;
+        make_f16(M, L.in_norm, p + "in_norm", H, 1.0f, c.norm_jitter);
+        make_f16(M, L.post_norm, p + "post_norm", H, 1.0f, c.norm_jitter);
+        if (!L.is_attn) {
+            make_q4(M, L.in_qkv, p + "gdn.in_proj_qkv", convDim, H);
+            make_q4(M, L.in_z, p + "gdn.in_proj_z", valDim, H);
+            make_q4(M, L.in_b, p + "gdn.in_proj_b", c.gdn_v_heads, H);
+            make_q4(M, L.in_a, p + "gdn.in_proj_a", c.gdn_v_heads, H);
+            make_f32(M, L.conv_w, p + "gdn.conv_w", (int64_t)convDim * CONVK, 0.0f, c.conv_std);
+            make_f32(M, L.A_log, p + "gdn.A_log", c.gdn_v_heads, 0.0f, 1.0f);
+            make_f32(M, L.dt_bias, p + "gdn.dt_bias", c.gdn_v_heads, 0.0f, 1.0f);
+            make_f16(M, L.gdn_norm, p + "gdn.norm", DV, 1.0f, c.norm_jitter);
+            make_q4(M, L.gdn_out, p + "gdn.out_proj", H, valDim);
+        } else {
+            make_q4(M, L.q_proj, p + "attn.q_proj", (int64_t)c.attn_heads * 2 * HD, H);
+            make_q4(M, L.k_proj, p + "attn.k_proj", (int64_t)c.attn_kv_heads * HD, H);
+            make_q4(M, L.v_proj, p + "attn.v_proj", (int64_t)c.attn_kv_heads * HD, H);
+            make_q4(M, L.o_proj, p + "attn.o_proj", H, (int64_t)c.attn_heads * HD);
+            make_f16(M, L.q_norm, p + "attn.q_norm", HD, 1.0f, c.norm_jitter);
+            make_f16(M, L.k_norm, p + "attn.k_norm", HD, 1.0f, c.norm_jitter);
+        }
+        make_f16(M, L.router, p + "moe.router", (int64_t)E * H, 0.0f, 0.02f);
+        make_f16(M, L.shared_gate, p + "moe.shared_gate", H, 0.0f, 0.02f);
+        make_q4(M, L.gate_proj, p + "moe.gate_proj", (int64_t)E * I, H);
+        make_q4(M, L.up_proj, p + "moe.up_proj", (int64_t)E * I, H);
+        make_q4(M, L.down_proj, p + "moe.down_proj", (int64_t)E * H, I);
+        make_q4(M, L.sh_gate, p + "moe.shared_gate_proj", I, H);
+        make_q4(M, L.sh_up, p + "moe.shared_up_proj", I, H);
+        make_q4(M, L.sh_down, p + "moe.shared_down_proj", H, I);
+    }
+    return M;
+}
+extern "C" void orc_model_destroy(void* m) { delete (Model*)m; }
+extern "C" int orc_model_tensor(void* m, const char* name, const void** ptr, uint64_t* nbytes) {
+    Model* M = (Model*)m; auto it = M->index.find(name);
+    if (it == M->index.end()) return -1;
+    *ptr = it->second.first; *nbytes = it->second.second; return 0;
+}
+extern "C" int orc_model_tensor_count(void* m) { return (int)((Model*)m)->index.size(); }
+extern "C" const char* orc_model_tensor_name(void* m, int i) {
+    Model* M = (Model*)m; auto it = M->index.begin(); std::advance(it, i); return it->first.c_str();
+}
+
+extern "C" void* orc_stream_create(void* m, int max_seq_len) {
+    Model* M = (Model*)m; Stream* s = new Stream(); s->m = M; s->cap = max_seq_len; s->len = 0;
+    const OrcConfig& c = M->c;
+    int convDim = 2 * c.gdn_k_heads * DK + c.gdn_v_heads * DV;
+    s->L.resize(c.n_layers);
+    for (int i = 0; i < c.n_layers; ++i) {
+        if (M->layers[i].is_attn) {
+            s->L[i].kc.assign((size_t)c.attn_kv_heads * max_seq_len * HD, f2h(0.0f));
+            s->L[i].vc.assign((size_t)c.attn_kv_heads * max_seq_len * HD, f2h(0.0f));
+        } else {
+            s->L[i].conv.assign((size_t)(CONVK - 1) * convDim, f2h(0.0f));
+            s->L[i].S.assign((size_t)c.gdn_v_heads * DV * DK, 0.0f);
+        }
+    }
+    return s;
+}
+extern "C" void orc_stream_destroy(void* s) { delete (Stream*)s; }
+extern "C" int orc_stream_len(void* s) { return ((Stream*)s)->len; }
+// operator tests drive single layers through orc_mixer_rows, which leaves the length alone
+extern "C" int orc_stream_set_len(void* s, int len) { Stream* st = (Stream*)s; if (len < 0 || len > st->cap) return -1; st->len = len; return 0; }
+
+// ---------------------------------------------------------------- MoE block (SVF:205-248)
+static void swiglu_h(const h16* g, const h16* u, int n, h16* h) {           // SMF:982-990
+    for (int i = 0; i < n; ++i) h[i] = hmul(hmul(g[i], sigmoid_h(g[i])), u[i]);
+}
+static void qmm_rows(const h16* x, const Q4& q, int64_t row0, int N, h16* y) {   // one input row
+    int K = (int)q.K;
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n) y[n] = f2h(qdot_row(x, q.row_w(row0 + n), q.row_s(row0 + n), q.row_b(row0 + n), K));
+}
+static void moe_block_row(const Model* M, const Layer& L, const h16* x, h16* out, int32_t* inds_out, h16* scores_out) {
+    const OrcConfig& c = M->c; int H = c.hidden, E = c.n_experts, I = c.moe_inter, T = c.top_k;
+    std::vector<h16> logits(E), g(I), u(I), h(I), d((size_t)T * H), y(H), sg(I), su(I), sh(I), sy(H);
+    orc_fmm(x, L.router.data(), 1, H, E, logits.data());
+    std::vector<int32_t> inds(T); std::vector<h16> scores(T);
+    route_row(logits.data(), E, T, inds.data(), scores.data());
+    for (int k = 0; k < T; ++k) {
+        int e = inds[k];
+        qmm_rows(x, L.gate_proj, (int64_t)e * I, I, g.data());
+        qmm_rows(x, L.up_proj, (int64_t)e * I, I, u.data());
+        swiglu_h(g.data(), u.data(), I, h.data());
+        qmm_rows(h.data(), L.down_proj, (int64_t)e * H, H, d.data() + (size_t)k * H);
+    }
+    for (int n = 0; n < H; ++n) {                                        // SFV:462-471
+        h16 acc = f2h(0.0f);
+        for (int k = 0; k < T; ++k) acc = hadd(acc, hmul(d[(size_t)k * H + n], scores[k]));
+        y[n] = acc;
+    }
+    qmm_rows(x, L.sh_gate, 0, I, sg.data());
+    qmm_rows(x, L.sh_up, 0, I, su.data());
+    swiglu_h(sg.data(), su.data(), I, sh.data());
+    qmm_rows(sh.data(), L.sh_down, 0, H, sy.data());
+    h16 sgl = f2h(fdot_row(x, L.shared_gate.data(), H));
+    h16 s = sigmoid_h(sgl);                                              // SFV:480-483
+    for (int n = 0; n < H; ++n) out[n] = hadd(y[n], hmul(s, sy[n]));
+    if (inds_out) for (int k = 0; k < T; ++k) inds_out[k] = inds[k];
+    if (scores_out) for (int k = 0; k < T; ++k) scores_out[k] = scores[k];
+}
+extern "C" void orc_moe_block(void* m, int layer, const h16* x, int Mrows, h16* out, int32_t* inds, h16* scores) {
+    Model* M = (Model*)m; int H = M->c.hidden, T = M->c.top_k;
+    for (int r = 0; r < Mrows; ++r)
+        moe_block_row(M, M->layers[layer], x + (int64_t)r * H, out + (int64_t)r * H,
+                      inds ? inds + r * T : nullptr, scores ? scores + r * T : nullptr);
+}
+
+// ---------------------------------------------------------------- GDN layer, one token (SVF:115-169)
+static void gdn_row(const Model* M, const Layer& L, LayerState& st, const h16* x, h16* out) {
+    const OrcConfig& c = M->c; int H = c.hidden, Hk = c.gdn_k_heads, Hv = c.gdn_v_heads;
+    int keyDim = Hk * DK, valDim = Hv * DV, convDim = 2 * keyDim + valDim;
+    std::vector<h16> qkv(convDim), z(valDim), bP(Hv), aP(Hv), conv(convDim), qn(keyDim), kn(keyDim), y(valDim), gated(valDim);
+    qmm_rows(x, L.in_qkv, 0, convDim, qkv.data());
+    qmm_rows(x, L.in_z, 0, valDim, z.data());
+    qmm_rows(x, L.in_b, 0, Hv, bP.data());
+    qmm_rows(x, L.in_a, 0, Hv, aP.data());
+    // causal depthwise conv over [hist(3) | new], f32 accumulate with f32 weights, silu (SFV:644-655)
+    for (int ch = 0; ch < convDim; ++ch) {
+        float acc = 0.0f;
+        for (int k = 0; k < CONVK; ++k) {
+            float xv = (k < CONVK - 1) ? h2f(st.conv[(size_t)k * convDim + ch]) : h2f(qkv[ch]);
+            acc += xv * L.conv_w[(size_t)ch * CONVK + k];
+        }
+        conv[ch] = f2h(acc * sigmoid_f(acc));
+    }
+    // history <- last three rows of [hist | new] (SFV:657-661)
+    for (int ch = 0; ch < convDim; ++ch) {
+        st.conv[0 * (size_t)convDim + ch] = st.conv[1 * (size_t)convDim + ch];
+        st.conv[1 * (size_t)convDim + ch] = st.conv[2 * (size_t)convDim + ch];
+        st.conv[2 * (size_t)convDim + ch] = qkv[ch];
+    }
+    // q,k: weightless rmsnorm then fp16 scale (SFV:873-909); scales SFV:3001-3008
+    float invScale = (float)pow((double)DK, -0.5);
+    h16 qs = f2h(invScale * invScale), ks = f2h(invScale);
+    for (int hh = 0; hh < Hk; ++hh) {
+        const h16* qp = conv.data() + hh * DK; const h16* kp = conv.data() + keyDim + hh * DK;
+        float iq = rms_inv(qp, DK, c.rms_eps), ik = rms_inv(kp, DK, c.rms_eps);
+        for (int d = 0; d < DK; ++d) {
+            qn[hh * DK + d] = hmul(qs, f2h(h2f(qp[d]) * iq));
+            kn[hh * DK + d] = hmul(ks, f2h(h2f(kp[d]) * ik));
+        }
+    }
+    const h16* v = conv.data() + 2 * keyDim;
+    // beta, g (SFV:927-936); recurrence (GD:63-124): lane l owns dk 4l..4l+3
+    for (int hv = 0; hv < Hv; ++hv) {
+        float beta = h2f(sigmoid_h(bP[hv]));
+        float xa = h2f(aP[hv]) + L.dt_bias[hv];
+        float sp = fmaxf(xa, 0.0f) + logf(1.0f + expf(-fabsf(xa)));
+        float g = expf(-expf(L.A_log[hv]) * sp);
+        int hk = hv / (Hv / Hk);
+        const h16* qh = qn.data() + hk * DK; const h16* kh = kn.data() + hk * DK;
+        for (int dv = 0; dv < DV; ++dv) {
+            float* S = st.S.data() + ((size_t)hv * DV + dv) * DK;
+            float lane[32];
+            for (int l = 0; l < 32; ++l) {
+                float kv = 0.0f;
+                for (int i = 0; i < 4; ++i) { int s = 4 * l + i; S[s] = S[s] * g; kv += S[s] * h2f(kh[s]); }
+                lane[l] = kv;
+            }
+            float kv_mem = bfly_sum32(lane);
+            float delta = (h2f(v[hv * DV + dv]) - kv_mem) * beta;
+            for (int l = 0; l < 32; ++l) {
+                float o = 0.0f;
+                for (int i = 0; i < 4; ++i) { int s = 4 * l + i; S[s] = S[s] + h2f(kh[s]) * delta; o += S[s] * h2f(qh[s]); }
+                lane[l] = o;
+            }
+            y[hv * DV + dv] = f2h(bfly_sum32(lane));
+        }
+    }
+    // gated RMSNorm: normed = w*fp16(y*inv); out = fp16(silu_f32(z) * normed) (SFV:803-813)
+    for (int hv = 0; hv < Hv; ++hv) {
+        const h16* yp = y.data() + hv * DV;
+        float inv = rms_inv(yp, DV, c.rms_eps);
+        for (int d = 0; d < DV; ++d) {
+            float nrm = h2f(hmul(L.gdn_norm[d], f2h(h2f(yp[d]) * inv)));
+            float zf = h2f(z[hv * DV + d]);
+            gated[hv * DV + d] = f2h((zf * sigmoid_f(zf)) * nrm);
+        }
+    }
+    qmm_rows(gated.data(), L.gdn_out, 0, H, out);
+}
+
+// ---------------------------------------------------------------- attention layer, one token (SVF:37-85)
+static void rope_head(const h16* normed, int pos, float theta, h16* out) {      // SFV:1235-1248
+    int hd2 = ROPE / 2; float fpos = (float)pos;
+    for (int d = 0; d < HD; ++d) {
+        if (d >= ROPE) { out[d] = normed[d]; continue; }
+        int ii = (d < hd2) ? d : (d - hd2);
+        float freq = expf(-2.0f * (float)ii / (float)ROPE * logf(theta));
+        float ang = fpos * freq;
+        float cs = cosf(ang), sn = sinf(ang);
+        float x0 = h2f(normed[ii]), x1 = h2f(normed[ii + hd2]);
+        out[d] = f2h(d < hd2 ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs));
+    }
+}
+// one query head over N keys: 32 groups stride the keys, online softmax in f32 per group,
+// groups merged at the end (SMF:4957-4988).  keys/values: [N][256] for this kv head.
+static void sdpa_head(const h16* q, const h16* keys, const h16* values, int N, float scale, h16* out) {
+    static thread_local std::vector<float> O; O.assign(32 * HD, 0.0f);
+    float maxs[32], sums[32], qs[HD];
+    for (int d = 0; d < HD; ++d) qs[d] = scale * h2f(q[d]);
+    for (int g = 0; g < 32; ++g) {
+        float mx = -INFINITY, se = 0.0f; float* o = O.data() + g * HD;
+        for (int i = g; i < N; i += 32) {
+            const h16* kp = keys + (size_t)i * HD; const h16* vp = values + (size_t)i * HD;
+            float lane[32];
+            for (int l = 0; l < 32; ++l) { float s = 0.0f; for (int j = 0; j < 8; ++j) s += qs[l * 8 + j] * h2f(kp[l * 8 + j]); lane[l] = s; }
+            float score = bfly_sum32(lane);
+            float nm = fmaxf(mx, score);
+            float factor = expf(mx - nm), es = expf(score - nm);
+            mx = nm; se = se * factor + es;
+            for (int d = 0; d < HD; ++d) o[d] = o[d] * factor + es * h2f(vp[d]);
+        }
+        maxs[g] = mx; sums[g] = se;
+    }
+    float nm = bfly_max32(maxs);
+    float fac[32], ws[32];
+    for (int g = 0; g < 32; ++g) { fac[g] = expf(maxs[g] - nm); ws[g] = sums[g] * fac[g]; }
+    float total = bfly_sum32(ws);
+    for (int d = 0; d < HD; ++d) {
+        float lane[32];
+        for (int g = 0; g < 32; ++g) lane[g] = O[g * HD + d] * fac[g];
+        float o = bfly_sum32(lane);
+        out[d] = f2h(total == 0.0f ? o : (o / total));
+    }
+}
+static void attn_row(const Model* M, const Layer& L, LayerState& st, int cap, int pos, const h16* x, h16* out) {
+    const OrcConfig& c = M->c; int H = c.hidden, NH = c.attn_heads, KV = c.attn_kv_heads;
+    std::vector<h16> qo((size_t)NH * 2 * HD), ko((size_t)KV * HD), vo((size_t)KV * HD), nrm(HD), qrot((size_t)NH * HD), attn((size_t)NH * HD), gated((size_t)NH * HD);
+    qmm_rows(x, L.q_proj, 0, NH * 2 * HD, qo.data());
+    qmm_rows(x, L.k_proj, 0, KV * HD, ko.data());
+    qmm_rows(x, L.v_proj, 0, KV * HD, vo.data());
+    for (int h = 0; h < NH; ++h) {
+        rmsnorm_row(qo.data() + (size_t)h * 2 * HD, L.q_norm.data(), HD, c.rms_eps, nrm.data());
+        rope_head(nrm.data(), pos, c.rope_theta, qrot.data() + (size_t)h * HD);
+    }
+    for (int h = 0; h < KV; ++h) {
+        rmsnorm_row(ko.data() + (size_t)h * HD, L.k_norm.data(), HD, c.rms_eps, nrm.data());
+        rope_head(nrm.data(), pos, c.rope_theta, st.kc.data() + ((size_t)h * cap + pos) * HD);
+        memcpy(st.vc.data() + ((size_t)h * cap + pos) * HD, vo.data() + (size_t)h * HD, HD * sizeof(h16));
+    }
+    float scale = (float)pow((double)HD, -0.5);
+    int gqa = NH / KV;
+#pragma omp parallel for schedule(static)
+    for (int h = 0; h < NH; ++h) {
+        int kvh = h / gqa;
+        sdpa_head(qrot.data() + (size_t)h * HD, st.kc.data() + (size_t)kvh * cap * HD, st.vc.data() + (size_t)kvh * cap * HD,
+                  pos + 1, scale, attn.data() + (size_t)h * HD);
+    }
+    for (int h = 0; h < NH; ++h)                                                   // SMF:1012-1022
+        for (int d = 0; d < HD; ++d) {
+            h16 gv = qo[(size_t)h * 2 * HD + HD + d];
+            gated[(size_t)h * HD + d] = hmul(attn[(size_t)h * HD + d], sigmoid_h(gv));
+        }
+    qmm_rows(gated.data(), L.o_proj, 0, H, out);
+}
+
+// mixer of one layer applied to already-normed rows, advancing that layer's cache only
+extern "C" int orc_mixer_rows(void* sp, int layer, const h16* x, int Mrows, int pos0, h16* out) {
+    Stream* s = (Stream*)sp; Model* M = s->m; int H = M->c.hidden;
+    if (pos0 + Mrows > s->cap) return -1;
+    for (int r = 0; r < Mrows; ++r) {
+        if (M->layers[layer].is_attn) attn_row(M, M->layers[layer], s->L[layer], s->cap, pos0 + r, x + (int64_t)r * H, out + (int64_t)r * H);
+        else gdn_row(M, M->layers[layer], s->L[layer], x + (int64_t)r * H, out + (int64_t)r * H);
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------- whole forward (SVF:284-309)
+// rows are processed one token at a time: the reference's M-row forward is defined to be
+// bit-identical to M sequential single-row steps (SVF:6-10).
+static void forward_token(Stream* s, int32_t tok, h16* normed_out) {
+    Model* M = s->m; const OrcConfig& c = M->c; int H = c.hidden;
+    std::vector<h16> h(H), n(H), r(H);
+    memcpy(h.data(), M->embed.data() + (size_t)tok * H, H * sizeof(h16));
+    for (int i = 0; i < c.n_layers; ++i) {
+        Layer& L = M->layers[i];
+        rmsnorm_row(h.data(), L.in_norm.data(), H, c.rms_eps, n.data());
+        if (L.is_attn) attn_row(M, L, s->L[i], s->cap, s->len, n.data(), r.data());
+        else gdn_row(M, L, s->L[i], n.data(), r.data());
+        for (int d = 0; d < H; ++d) h[d] = hadd(h[d], r[d]);                        // SFV:969
+        rmsnorm_row(h.data(), L.post_norm.data(), H, c.rms_eps, n.data());
+        moe_block_row(M, L, n.data(), r.data(), nullptr, nullptr);
+        for (int d = 0; d < H; ++d) h[d] = hadd(h[d], r[d]);
+    }
+    rmsnorm_row(h.data(), M->final_norm.data(), H, c.rms_eps, normed_out);
+    s->len += 1;
+}
+extern "C" int orc_forward(void* sp, const int32_t* tokens, int Mrows, h16* out_normed) {
+    Stream* s = (Stream*)sp; int H = s->m->c.hidden;
+    if (s->len + Mrows > s->cap) return -1;
+    std::vector<h16> tmp(H);
+    for (int r = 0; r < Mrows; ++r) {
+        if (tokens[r] < 0 || tokens[r] >= s->m->c.vocab) return -2;
+        forward_token(s, tokens[r], out_normed ? out_normed + (int64_t)r * H : tmp.data());
+    }
+    return 0;
+}
+static int argmax_first(const h16* v, int n) {                                       // SFV:580-591
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int i = 0; i < n; ++i) { float lv = h2f(v[i]); if (lv > best) { best = lv; bi = i; } }
+    return bi;
+}
+// logits fp16 [M,V] (may be null) and greedy tokens [M] (may be null)
+extern "C" int orc_step(void* sp, const int32_t* tokens, int Mrows, h16* out_logits, int32_t* out_tokens) {
+    Stream* s = (Stream*)sp; Model* M = s->m; int H = M->c.hidden, V = M->c.vocab;
+    if (s->len + Mrows > s->cap) return -1;
+    std::vector<h16> normed(H), logits(V);
+    for (int r = 0; r < Mrows; ++r) {
+        if (tokens[r] < 0 || tokens[r] >= V) return -2;
+        forward_token(s, tokens[r], normed.data());
+        h16* lp = out_logits ? out_logits + (int64_t)r * V : logits.data();
+        qmm_rows(normed.data(), M->lm_head, 0, V, lp);
+        if (out_tokens) out_tokens[r] = argmax_first(lp, V);
+    }
+    return 0;
+}
+extern "C" void orc_lm_head(void* m, const h16* normed, int Mrows, h16* out_logits, int32_t* out_tokens) {
+    Model* M = (Model*)m; int H = M->c.hidden, V = M->c.vocab;
+    std::vector<h16> logits(V);
+    for (int r = 0; r < Mrows; ++r) {
+        h16* lp = out_logits ? out_logits + (int64_t)r * V : logits.data();
+        qmm_rows(normed + (int64_t)r * H, M->lm_head, 0, V, lp);
+        if (out_tokens) out_tokens[r] = argmax_first(lp, V);
+    }
+}
+
+// ---------------------------------------------------------------- "QWS1" state blob (SFV:4077-4154)
+extern "C" uint64_t orc_state_size(void* sp) {
+    Stream* s = (Stream*)sp; Model* M = s->m; const OrcConfig& c = M->c;
+    int convDim = 2 * c.gdn_k_heads * DK + c.gdn_v_heads * DV;
+    uint64_t n = 12;
+    for (int i = 0; i < c.n_layers; ++i) {
+        n += 4;
+        if (M->layers[i].is_attn) n += 12 + 2ull * c.attn_kv_heads * s->len * HD * 2;
+        else n += 8 + (uint64_t)(CONVK - 1) * convDim * 2 + (uint64_t)c.gdn_v_heads * DV * DK * 4;
+    }
+    return n;
+}
+extern "C" int orc_state_save(void* sp, uint8_t* buf, uint64_t cap) {
+    Stream* s = (Stream*)sp; Model* M = s->m; const OrcConfig& c = M->c;
+    if (cap < orc_state_size(sp)) return -1;
+    int convDim = 2 * c.gdn_k_heads * DK + c.gdn_v_heads * DV;
+    uint8_t* p = buf;
+    auto u32 = [&](uint32_t v) { memcpy(p, &v, 4); p += 4; };
+    u32(0x31535751u); u32(1); u32((uint32_t)c.n_layers);
+    for (int i = 0; i < c.n_layers; ++i) {
+        LayerState& st = s->L[i];
+        if (M->layers[i].is_attn) {
+            u32(1); u32(c.attn_kv_heads); u32(HD); u32(s->len);
+            for (int which = 0; which < 2; ++which)
+                for (int h = 0; h < c.attn_kv_heads; ++h) {
+                    const h16* src = (which ? st.vc.data() : st.kc.data()) + (size_t)h * s->cap * HD;
+                    memcpy(p, src, (size_t)s->len * HD * 2); p += (size_t)s->len * HD * 2;
+                }
+        } else {
+            u32(2); u32((CONVK - 1) * convDim); u32(c.gdn_v_heads * DV * DK);
+            memcpy(p, st.conv.data(), st.conv.size() * 2); p += st.conv.size() * 2;
+            memcpy(p, st.S.data(), st.S.size() * 4); p += st.S.size() * 4;
+        }
+    }
+    return 0;
+}
+extern "C" int orc_state_restore(void* sp, const uint8_t* buf, uint64_t n) {
+    Stream* s = (Stream*)sp; Model* M = s->m; const OrcConfig& c = M->c;
+    int convDim = 2 * c.gdn_k_heads * DK + c.gdn_v_heads * DV;
+    uint64_t off = 0; bool ok = true;
+    auto u32 = [&]() -> uint32_t { if (off + 4 > n) { ok = false; return 0; } uint32_t v; memcpy(&v, buf + off, 4); off += 4; return v; };
+    if (u32() != 0x31535751u || u32() != 1 || u32() != (uint32_t)c.n_layers || !ok) return -1;
+    int newlen = s->len; bool have_len = false;
+    for (int i = 0; i < c.n_layers; ++i) {
+        LayerState& st = s->L[i];
+        uint32_t flags = u32(); if (!ok) return -1;
+        if (flags != (M->layers[i].is_attn ? 1u : 2u)) return -1;
+        if (flags == 1) {
+            uint32_t kv = u32(), d = u32(), len = u32(); if (!ok) return -1;
+            if (kv != (uint32_t)c.attn_kv_heads || d != (uint32_t)HD || (int)len > s->cap) return -1;
+            if (have_len && (int)len != newlen) return -1;
+            newlen = (int)len; have_len = true;
+            for (int which = 0; which < 2; ++which)
+                for (int h = 0; h < c.attn_kv_heads; ++h) {
+                    size_t bytes = (size_t)len * HD * 2; if (off + bytes > n) return -1;
+                    h16* dst = (which ? st.vc.data() : st.kc.data()) + (size_t)h * s->cap * HD;
+                    memcpy(dst, buf + off, bytes); off += bytes;
+                }
+        } else {
+            uint32_t cc = u32(), sc = u32(); if (!ok) return -1;
+            if (cc != (uint32_t)((CONVK - 1) * convDim) || sc != (uint32_t)(c.gdn_v_heads * DV * DK)) return -1;
+            if (off + (size_t)cc * 2 + (size_t)sc * 4 > n) return -1;
+            memcpy(st.conv.data(), buf + off, (size_t)cc * 2); off += (size_t)cc * 2;
+            memcpy(st.S.data(), buf + off, (size_t)sc * 4); off += (size_t)sc * 4;
+        }
+    }
+    if (off != n) return -1;
+    s->len = newlen;
+    return 0;
+}

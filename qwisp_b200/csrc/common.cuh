@@ -1,0 +1,103 @@
+// common.cuh -- shared device helpers for the Seedless B200 kernels (sm_100a).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sl {
+
+// fixed by the model family (swift/Sources/QwispCore/QwispModel.swift:83-120)
+constexpr int GDN_DK = 128;      // gated-delta key head dim
+constexpr int GDN_DV = 128;      // gated-delta value head dim
+constexpr int CONV_K = 4;        // causal depthwise conv taps
+constexpr int ATT_D = 256;       // attention head dim
+constexpr int ROPE_D = 64;       // rotated dims (NeoX pairs d, d+32)
+constexpr int QGROUP = 64;       // quantisation group
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+    return v;
+}
+// sum over aligned groups of 16 lanes
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+    for (int off = 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+__device__ __forceinline__ float h2f(__half h) { return __half2float(h); }
+__device__ __forceinline__ __half f2h(float f) { return __float2half_rn(f); }
+
+// correctly rounded fp16 arithmetic done through one f32 operation (f32 carries >= 2*11+2 bits)
+__device__ __forceinline__ __half hadd_rn(__half a, __half b) { return f2h(__fadd_rn(h2f(a), h2f(b))); }
+__device__ __forceinline__ __half hsub_rn(__half a, __half b) { return f2h(__fsub_rn(h2f(a), h2f(b))); }
+__device__ __forceinline__ __half hmul_rn(__half a, __half b) { return f2h(__fmul_rn(h2f(a), h2f(b))); }
+__device__ __forceinline__ __half hdiv_rn(__half a, __half b) { return f2h(__fdiv_rn(h2f(a), h2f(b))); }
+
+// "stable sigmoid" in fp16 arithmetic: y = 1/(1+exp(|x|)); x<0 ? y : 1-y
+// (swift/Sources/QwispCore/SeedlessMetalForward.swift:986-988)
+__device__ __forceinline__ __half sigmoid_h(__half x) {
+    const __half one = f2h(1.0f);
+    __half ex = f2h(expf(fabsf(h2f(x))));
+    __half y = hdiv_rn(one, hadd_rn(one, ex));
+    return (h2f(x) < 0.0f) ? y : hsub_rn(one, y);
+}
+// same in f32 (SeedlessMetalForward.swift:1599-1602)
+__device__ __forceinline__ float sigmoid_f(float x) {
+    float y = __fdiv_rn(1.0f, 1.0f + expf(fabsf(x)));
+    return (x < 0.0f) ? y : (1.0f - y);
+}
+// SwiGLU in fp16: (g*sigmoid(g))*u (SeedlessMetalForward.swift:982-990)
+__device__ __forceinline__ __half swiglu_h(__half g, __half u) { return hmul_rn(hmul_rn(g, sigmoid_h(g)), u); }
+
+// mma.sync m16n8k16, fp16 x fp16 -> fp32
+__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Programmatic dependent launch: wait for the kernels this one depends on / let dependents start.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// L2 prefetch of [p, p+bytes): bytes a multiple of 16, p 16-byte aligned
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// per-stream device-resident bookkeeping, indexed by stream slot
+struct StreamTable {
+    int* kv_len;            // [max_streams] positions already in the cache
+    int* parity;            // [max_streams] which GDN ping-pong side is current
+    int* page_table;        // [max_streams][max_pages]
+    int max_pages;
+    float* gdn_state;       // [max_streams][2][n_gdn][Hv][128][128]
+    __half* conv_hist;      // [max_streams][2][n_gdn][3][convDim]
+    size_t state_stride_layer, state_stride_side, state_stride_stream;   // in floats
+    size_t hist_stride_layer, hist_stride_side, hist_stride_stream;      // in halfs
+};
+
+// rows of one call: segment = contiguous rows of one stream, in sequence order
+struct SegDesc { int slot; int row0; int nrows; int pad; };
+
+}  // namespace sl

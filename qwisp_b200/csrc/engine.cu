@@ -1,0 +1,1006 @@
+// engine.cu -- engine / stream objects and the C ABI of libseedless_b200.so.
+//
+// Host-side orchestration of one step (the op order of the reference's fused step,
+// swift/Sources/QwispCore/SeedlessFusedVerify.swift:3455-3549 and :3832-3912):
+//   embed -> per layer [ rmsnorm -> mixer (GDN | attention) -> +resid -> rmsnorm -> MoE -> +resid ]
+//         -> rmsnorm -> lm_head -> argmax
+// All state stays on the device; a decode step reads back only int32 token ids.
+#include "../../include/seedless_b200.h"
+#include "gemv.cuh"
+#include "kernels.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+using namespace sl;
+
+namespace {
+
+constexpr int NSPLIT = 64;          // KV splits of the decode attention
+
+struct Tensor { void* ptr; size_t bytes; };
+
+struct LayerW {
+    bool is_attn = false;
+    int type_index = 0;             // index among layers of the same kind
+    const __half *in_norm = nullptr, *post_norm = nullptr;
+    Q4W in_proj;                    // GDN: qkv|z|b|a rows; attention: q|k|v rows
+    const float *conv_w = nullptr, *A_log = nullptr, *dt_bias = nullptr;
+    const __half* gdn_norm = nullptr;
+    Q4W out_proj;                   // GDN out_proj / attention o_proj
+    const __half *q_norm = nullptr, *k_norm = nullptr;
+    const __half *router = nullptr, *shared_gate = nullptr;
+    Q4W gate, up, down, sh_gate, sh_up, sh_down;
+};
+
+}  // namespace
+
+struct sl_engine {
+    sl_config cfg{};
+    int H = 0, E = 0, I = 0, topk = 0, V = 0;
+    int keyDim = 0, valDim = 0, convDim = 0, gdn_in = 0, attn_in = 0, attn_out = 0;
+    int n_gdn = 0, n_attn = 0;
+    bool exact = true;
+    cudaStream_t own_stream = nullptr, stream = nullptr;
+    std::map<std::string, Tensor> tensors;
+    std::vector<void*> allocs;
+    std::vector<LayerW> layers;
+    const __half *embed = nullptr, *final_norm = nullptr;
+    Q4W lm_head;
+    // scratch (sized by max_rows)
+    __half *h = nullptr, *p = nullptr, *inproj = nullptr, *mix = nullptr, *rlogits = nullptr, *sgl = nullptr, *scores = nullptr;
+    __half *hbuf = nullptr, *dbuf = nullptr, *normed = nullptr, *qrot = nullptr, *opx = nullptr, *opy = nullptr;
+    __half* logits = nullptr; int logits_rows = 0;
+    int* inds = nullptr; MoeLists lists{};
+    float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
+    int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
+    int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
+    unsigned* counters = nullptr;
+    SegDesc* segs = nullptr;
+    int hist_cap = 0;
+    // pinned staging
+    int* pin_i = nullptr; size_t pin_ints = 0;
+    // streams
+    StreamTable tab{};
+    __half* kv_pool = nullptr;
+    std::vector<int> free_pages;
+    std::vector<int> free_slots;
+    // decode graphs keyed by rows (each segment one row)
+    std::map<int, cudaGraphExec_t> graphs;
+    std::map<int, int> eager_runs;
+    bool use_graph = true;
+    bool poisoned = false, inject = false;
+    std::string fault;
+};
+
+struct sl_stream {
+    sl_engine* e;
+    int slot;
+    int max_seq_len;
+    int kv_len;
+    int parity;
+    std::vector<int> pages;
+};
+
+struct sl_fullsnap {
+    int kv_len;
+    float* state;      // [n_gdn][Hv*128*128]
+    __half* hist;      // [n_gdn][3*convDim]
+};
+
+namespace {
+
+int32_t poison(sl_engine* e, const char* what, cudaError_t err) {
+    if (!e->poisoned) {
+        e->poisoned = true;
+        e->fault = std::string(what) + ": " + cudaGetErrorString(err);
+    }
+    return SL_ERR_CUDA;
+}
+#define CU(e, call)                                         \
+    do {                                                    \
+        cudaError_t _err = (call);                          \
+        if (_err != cudaSuccess) return poison((e), #call, _err); \
+    } while (0)
+
+int32_t guard(sl_engine* e) {
+    if (!e) return SL_ERR_INVALID;
+    if (e->poisoned) return SL_ERR_POISONED;
+    if (e->inject) {
+        e->poisoned = true;
+        e->fault = "injected failure (test hook)";
+        e->inject = false;
+        return SL_ERR_CUDA;
+    }
+    return SL_OK;
+}
+
+bool device_ok() {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); return false; }
+    return true;
+}
+
+template <typename T>
+int32_t dalloc(sl_engine* e, T** out, size_t count) {
+    void* p = nullptr;
+    size_t bytes = count * sizeof(T);
+    if (bytes == 0) bytes = 16;
+    CU(e, cudaMalloc(&p, bytes));
+    e->allocs.push_back(p);
+    *out = reinterpret_cast<T*>(p);
+    return SL_OK;
+}
+
+int32_t reg_tensor(sl_engine* e, const std::string& name, void* ptr, size_t bytes) {
+    e->tensors[name] = Tensor{ptr, bytes};
+    return SL_OK;
+}
+
+// one q4 tensor with rows possibly shared by several named sub-tensors (row ranges)
+int32_t alloc_q4(sl_engine* e, Q4W& q, int64_t N, int K, const std::vector<std::pair<std::string, int64_t>>& parts) {
+    uint32_t* w; __half *s, *b;
+    int32_t rc;
+    if ((rc = dalloc(e, &w, (size_t)N * K / 8))) return rc;
+    if ((rc = dalloc(e, &s, (size_t)N * K / 64))) return rc;
+    if ((rc = dalloc(e, &b, (size_t)N * K / 64))) return rc;
+    q.w = w; q.s = s; q.b = b; q.N = N; q.K = K;
+    int64_t row = 0;
+    for (auto& pr : parts) {
+        reg_tensor(e, pr.first + ".w", w + row * (K / 8), (size_t)pr.second * K / 8 * 4);
+        reg_tensor(e, pr.first + ".s", s + row * (K / 64), (size_t)pr.second * K / 64 * 2);
+        reg_tensor(e, pr.first + ".b", b + row * (K / 64), (size_t)pr.second * K / 64 * 2);
+        row += pr.second;
+    }
+    return SL_OK;
+}
+template <typename T>
+int32_t alloc_plain(sl_engine* e, const T** out, const std::string& name, size_t count) {
+    T* p; int32_t rc;
+    if ((rc = dalloc(e, &p, count))) return rc;
+    *out = p;
+    return reg_tensor(e, name, p, count * sizeof(T));
+}
+
+bool config_ok(const sl_config& c) {
+    if (c.hidden <= 0 || c.hidden % 256 || c.hidden > 4096) return false;
+    if (c.moe_inter <= 0 || c.moe_inter % 256 || c.moe_inter > 4096) return false;
+    if (c.n_layers <= 0 || c.attn_every <= 0) return false;
+    if (c.vocab <= 0 || c.vocab % 16) return false;
+    if (c.n_experts <= 0 || c.n_experts > 256 || c.n_experts % 8) return false;
+    if (c.top_k <= 0 || c.top_k > c.n_experts || c.top_k > 16) return false;
+    if (c.gdn_k_heads <= 0 || c.gdn_v_heads % c.gdn_k_heads) return false;
+    if ((c.gdn_v_heads * GDN_DV) % 256 || (c.gdn_v_heads * GDN_DV) > 4096) return false;
+    if (c.gdn_v_heads % 16) return false;           // b / a rows form whole 16-row tiles
+    if (c.attn_kv_heads <= 0 || c.attn_heads != 8 * c.attn_kv_heads) return false;
+    if ((c.attn_heads * ATT_D) > 4096) return false;
+    if (c.max_rows <= 0 || c.max_rows > 1024) return false;
+    if (c.max_streams <= 0 || c.max_streams > 1024) return false;
+    if (c.kv_page_size <= 0 || c.kv_page_size % 32) return false;
+    if (c.kv_pages <= 0) return false;
+    return true;
+}
+
+int32_t build_layout(sl_engine* e) {
+    const sl_config& c = e->cfg;
+    e->H = c.hidden; e->E = c.n_experts; e->I = c.moe_inter; e->topk = c.top_k; e->V = c.vocab;
+    e->keyDim = c.gdn_k_heads * GDN_DK; e->valDim = c.gdn_v_heads * GDN_DV; e->convDim = 2 * e->keyDim + e->valDim;
+    e->gdn_in = e->convDim + e->valDim + 2 * c.gdn_v_heads;
+    e->attn_in = c.attn_heads * 2 * ATT_D + 2 * c.attn_kv_heads * ATT_D;
+    e->attn_out = c.attn_heads * ATT_D;
+    const int H = e->H, E = e->E, I = e->I;
+    int32_t rc;
+    if ((rc = alloc_plain(e, &e->embed, "embed", (size_t)c.vocab * H))) return rc;
+    if ((rc = alloc_plain(e, &e->final_norm, "final_norm", (size_t)H))) return rc;
+    if ((rc = alloc_q4(e, e->lm_head, c.vocab, H, {{"lm_head", c.vocab}}))) return rc;
+    e->layers.resize(c.n_layers);
+    for (int i = 0; i < c.n_layers; ++i) {
+        LayerW& L = e->layers[i];
+        std::string p = "L" + std::to_string(i) + ".";
+        L.is_attn = ((i + 1) % c.attn_every) == 0;
+        L.type_index = L.is_attn ? e->n_attn++ : e->n_gdn++;
+        if ((rc = alloc_plain(e, &L.in_norm, p + "in_norm", (size_t)H))) return rc;
+        if ((rc = alloc_plain(e, &L.post_norm, p + "post_norm", (size_t)H))) return rc;
+        if (!L.is_attn) {
+            if ((rc = alloc_q4(e, L.in_proj, e->gdn_in, H,
+                               {{p + "gdn.in_proj_qkv", e->convDim}, {p + "gdn.in_proj_z", e->valDim},
+                                {p + "gdn.in_proj_b", c.gdn_v_heads}, {p + "gdn.in_proj_a", c.gdn_v_heads}}))) return rc;
+            if ((rc = alloc_plain(e, &L.conv_w, p + "gdn.conv_w", (size_t)e->convDim * CONV_K))) return rc;
+            if ((rc = alloc_plain(e, &L.A_log, p + "gdn.A_log", (size_t)c.gdn_v_heads))) return rc;
+            if ((rc = alloc_plain(e, &L.dt_bias, p + "gdn.dt_bias", (size_t)c.gdn_v_heads))) return rc;
+            if ((rc = alloc_plain(e, &L.gdn_norm, p + "gdn.norm", (size_t)GDN_DV))) return rc;
+            if ((rc = alloc_q4(e, L.out_proj, H, e->valDim, {{p + "gdn.out_proj", H}}))) return rc;
+        } else {
+            if ((rc = alloc_q4(e, L.in_proj, e->attn_in, H,
+                               {{p + "attn.q_proj", c.attn_heads * 2 * ATT_D}, {p + "attn.k_proj", c.attn_kv_heads * ATT_D},
+                                {p + "attn.v_proj", c.attn_kv_heads * ATT_D}}))) return rc;
+            if ((rc = alloc_q4(e, L.out_proj, H, e->attn_out, {{p + "attn.o_proj", H}}))) return rc;
+            if ((rc = alloc_plain(e, &L.q_norm, p + "attn.q_norm", (size_t)ATT_D))) return rc;
+            if ((rc = alloc_plain(e, &L.k_norm, p + "attn.k_norm", (size_t)ATT_D))) return rc;
+        }
+        if ((rc = alloc_plain(e, &L.router, p + "moe.router", (size_t)E * H))) return rc;
+        if ((rc = alloc_plain(e, &L.shared_gate, p + "moe.shared_gate", (size_t)H))) return rc;
+        if ((rc = alloc_q4(e, L.gate, (int64_t)E * I, H, {{p + "moe.gate_proj", (int64_t)E * I}}))) return rc;
+        if ((rc = alloc_q4(e, L.up, (int64_t)E * I, H, {{p + "moe.up_proj", (int64_t)E * I}}))) return rc;
+        if ((rc = alloc_q4(e, L.down, (int64_t)E * H, I, {{p + "moe.down_proj", (int64_t)E * H}}))) return rc;
+        if ((rc = alloc_q4(e, L.sh_gate, I, H, {{p + "moe.shared_gate_proj", I}}))) return rc;
+        if ((rc = alloc_q4(e, L.sh_up, I, H, {{p + "moe.shared_up_proj", I}}))) return rc;
+        if ((rc = alloc_q4(e, L.sh_down, H, I, {{p + "moe.shared_down_proj", H}}))) return rc;
+    }
+    return SL_OK;
+}
+
+int32_t build_runtime(sl_engine* e) {
+    const sl_config& c = e->cfg;
+    const int R = c.max_rows, H = e->H;
+    int32_t rc;
+    CU(e, cudaStreamCreateWithFlags(&e->own_stream, cudaStreamNonBlocking));
+    e->stream = e->own_stream;
+    size_t in_w = (size_t)(e->gdn_in > e->attn_in ? e->gdn_in : e->attn_in);
+    size_t mix_w = (size_t)(e->valDim > e->attn_out ? e->valDim : e->attn_out);
+    size_t prow = (size_t)R * e->topk + R;
+    if ((rc = dalloc(e, &e->h, (size_t)R * H))) return rc;
+    if ((rc = dalloc(e, &e->p, (size_t)R * H))) return rc;
+    if ((rc = dalloc(e, &e->normed, (size_t)R * H))) return rc;
+    if ((rc = dalloc(e, &e->opx, (size_t)R * H))) return rc;
+    if ((rc = dalloc(e, &e->opy, (size_t)R * H))) return rc;
+    if ((rc = dalloc(e, &e->inproj, (size_t)R * in_w))) return rc;
+    if ((rc = dalloc(e, &e->mix, (size_t)R * mix_w))) return rc;
+    if ((rc = dalloc(e, &e->rlogits, (size_t)R * e->E))) return rc;
+    if ((rc = dalloc(e, &e->sgl, (size_t)R))) return rc;
+    if ((rc = dalloc(e, &e->scores, (size_t)R * e->topk))) return rc;
+    if ((rc = dalloc(e, &e->inds, (size_t)R * e->topk))) return rc;
+    if ((rc = dalloc(e, &e->hbuf, prow * e->I))) return rc;
+    if ((rc = dalloc(e, &e->dbuf, prow * H))) return rc;
+    if ((rc = dalloc(e, &e->qrot, (size_t)R * c.attn_heads * ATT_D))) return rc;
+    if ((rc = dalloc(e, &e->part_o, (size_t)R * c.attn_heads * NSPLIT * ATT_D))) return rc;
+    if ((rc = dalloc(e, &e->part_ml, (size_t)R * c.attn_heads * NSPLIT * 2))) return rc;
+    if ((rc = dalloc(e, &e->pval, (size_t)R * (e->V / 16)))) return rc;
+    if ((rc = dalloc(e, &e->pidx, (size_t)R * (e->V / 16)))) return rc;
+    if ((rc = dalloc(e, &e->out_tok, (size_t)R))) return rc;
+    if ((rc = dalloc(e, &e->tok_in, (size_t)R))) return rc;
+    e->hist_cap = 1 << 16;
+    if ((rc = dalloc(e, &e->hist, (size_t)e->hist_cap))) return rc;
+    if ((rc = dalloc(e, &e->hist_pos, (size_t)1))) return rc;
+    if ((rc = dalloc(e, &e->row_seg, (size_t)R))) return rc;
+    if ((rc = dalloc(e, &e->row_off, (size_t)R))) return rc;
+    if ((rc = dalloc(e, &e->row_pos, (size_t)R))) return rc;
+    if ((rc = dalloc(e, &e->counters, (size_t)8))) return rc;
+    if ((rc = dalloc(e, &e->segs, (size_t)R))) return rc;
+    if ((rc = dalloc(e, &e->lists.n_active, (size_t)1))) return rc;
+    if ((rc = dalloc(e, &e->lists.slot_expert, (size_t)256))) return rc;
+    if ((rc = dalloc(e, &e->lists.slot_off, (size_t)256))) return rc;
+    if ((rc = dalloc(e, &e->lists.slot_cnt, (size_t)256))) return rc;
+    if ((rc = dalloc(e, &e->lists.pairs, (size_t)R * e->topk))) return rc;
+    CU(e, cudaMemset(e->counters, 0, 8 * sizeof(unsigned)));
+    CU(e, cudaMemset(e->hist_pos, 0, sizeof(int)));
+    e->pin_ints = (size_t)R * 8 + 64;
+    CU(e, cudaMallocHost(&e->pin_i, e->pin_ints * sizeof(int)));
+    // stream tables
+    const int S = c.max_streams;
+    StreamTable& t = e->tab;
+    t.max_pages = c.kv_pages;
+    if ((rc = dalloc(e, &t.kv_len, (size_t)S))) return rc;
+    if ((rc = dalloc(e, &t.parity, (size_t)S))) return rc;
+    if ((rc = dalloc(e, &t.page_table, (size_t)S * t.max_pages))) return rc;
+    CU(e, cudaMemset(t.kv_len, 0, S * sizeof(int)));
+    CU(e, cudaMemset(t.parity, 0, S * sizeof(int)));
+    CU(e, cudaMemset(t.page_table, 0, (size_t)S * t.max_pages * sizeof(int)));
+    t.state_stride_layer = (size_t)c.gdn_v_heads * GDN_DV * GDN_DK;
+    t.state_stride_side = t.state_stride_layer * (e->n_gdn > 0 ? e->n_gdn : 1);
+    t.state_stride_stream = 2 * t.state_stride_side;
+    t.hist_stride_layer = (size_t)(CONV_K - 1) * e->convDim;
+    t.hist_stride_side = t.hist_stride_layer * (e->n_gdn > 0 ? e->n_gdn : 1);
+    t.hist_stride_stream = 2 * t.hist_stride_side;
+    if ((rc = dalloc(e, &t.gdn_state, (size_t)S * t.state_stride_stream))) return rc;
+    if ((rc = dalloc(e, &t.conv_hist, (size_t)S * t.hist_stride_stream))) return rc;
+    size_t page_elems = (size_t)(e->n_attn > 0 ? e->n_attn : 1) * 2 * c.attn_kv_heads * c.kv_page_size * ATT_D;
+    if ((rc = dalloc(e, &e->kv_pool, (size_t)c.kv_pages * page_elems))) return rc;
+    for (int i = c.kv_pages - 1; i >= 0; --i) e->free_pages.push_back(i);
+    for (int i = S - 1; i >= 0; --i) e->free_slots.push_back(i);
+    const char* ng = getenv("SEEDLESS_NO_GRAPH");
+    if (ng && ng[0] == '1') e->use_graph = false;
+    return SL_OK;
+}
+
+// ---- numeric mode of the GEMV family: can the tensor cores take fp16 subnormal operands? ----
+int g_gemv_mode = -1;   // -1 unknown, 0 subnormal operands, 1 exact-integer operands
+int32_t detect_gemv_mode() {
+    if (g_gemv_mode >= 0) return SL_OK;
+    const char* force = getenv("SEEDLESS_GEMV_EXACT");
+    if (force && (force[0] == '0' || force[0] == '1')) { g_gemv_mode = force[0] - '0'; return SL_OK; }
+    const int N = 64, K = 512, M = 8;
+    uint32_t* w; __half *s, *b, *x, *y0, *y1;
+    if (cudaMalloc(&w, (size_t)N * K / 2) != cudaSuccess) return SL_ERR_CUDA;
+    cudaMalloc(&s, (size_t)N * K / 64 * 2); cudaMalloc(&b, (size_t)N * K / 64 * 2);
+    cudaMalloc(&x, (size_t)M * K * 2); cudaMalloc(&y0, (size_t)M * N * 2); cudaMalloc(&y1, (size_t)M * N * 2);
+    launch_synth_q4(tensor_seed(7, "selftest.w"), N, K, 0.02f, w, s, b, 0);
+    launch_synth_f16(tensor_seed(7, "selftest.x"), (int64_t)M * K, 0.f, 1.f, x, 0);
+    DenseArgs a{}; a.w = w; a.s = s; a.b = b; a.N = N; a.K = K; a.M = M; a.x = x; a.ldx = K; a.ldy = N;
+    a.y = y0; launch_dense(PRO_PLAIN, EPI_STORE, false, a, 0, false);
+    a.y = y1; launch_dense(PRO_PLAIN, EPI_STORE, true, a, 0, false);
+    std::vector<__half> h0((size_t)M * N), h1((size_t)M * N);
+    cudaError_t err = cudaDeviceSynchronize();
+    cudaMemcpy(h0.data(), y0, h0.size() * 2, cudaMemcpyDeviceToHost);
+    cudaMemcpy(h1.data(), y1, h1.size() * 2, cudaMemcpyDeviceToHost);
+    cudaFree(w); cudaFree(s); cudaFree(b); cudaFree(x); cudaFree(y0); cudaFree(y1);
+    if (err != cudaSuccess) return SL_ERR_CUDA;
+    float maxd = 0.f, maxv = 0.f;
+    for (size_t i = 0; i < h0.size(); ++i) {
+        float a0 = __half2float(h0[i]), a1 = __half2float(h1[i]);
+        maxd = fmaxf(maxd, fabsf(a0 - a1)); maxv = fmaxf(maxv, fabsf(a1));
+    }
+    g_gemv_mode = (maxv > 0.f && maxd <= 4e-3f * fmaxf(1.f, maxv)) ? 0 : 1;
+    return SL_OK;
+}
+
+int32_t finish_create(sl_engine* e) {
+    if (detect_gemv_mode() != SL_OK) return poison(e, "gemv self-test", cudaGetLastError());
+    e->exact = (g_gemv_mode == 1);
+    return SL_OK;
+}
+
+// ---------------------------------------------------------------- the forward pass
+enum HeadMode { HEAD_NONE = 0, HEAD_NORMED = 1, HEAD_ARGMAX = 2, HEAD_LOGITS = 3 };
+
+void enqueue_moe(sl_engine* e, const LayerW& L, const __half* rows, int ld, bool apply_norm, int M, __half* resid, __half* plain_out) {
+    cudaStream_t st = e->stream;
+    RouterArgs ra{}; ra.h = rows; ra.ldh = ld; ra.norm_w = apply_norm ? L.post_norm : nullptr; ra.eps = e->cfg.rms_eps;
+    ra.router = L.router; ra.shared_gate = L.shared_gate; ra.M = M; ra.H = e->H; ra.E = e->E;
+    ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
+    launch_router(ra, st);
+    RouteArgs ro{}; ro.logits = e->rlogits; ro.M = M; ro.E = e->E; ro.topk = e->topk; ro.inds = e->inds; ro.scores = e->scores;
+    ro.lists = e->lists; ro.counter = e->counters + 1;
+    launch_route(ro, st);
+    ExpertArgs ea{}; ea.gate = L.gate; ea.up = L.up; ea.down = L.down; ea.sh_gate = L.sh_gate; ea.sh_up = L.sh_up; ea.sh_down = L.sh_down;
+    ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = M; ea.H = e->H; ea.I = e->I; ea.topk = e->topk;
+    int nslots = M * e->topk < e->E ? M * e->topk : e->E;
+    launch_expert_gateup(e->exact, ea, nslots, st);
+    launch_expert_down(e->exact, ea, nslots, st);
+    CombineArgs ca{}; ca.dbuf = e->dbuf; ca.scores = e->scores; ca.sgl = e->sgl; ca.h = resid; ca.out = plain_out; ca.M = M; ca.H = e->H; ca.topk = e->topk;
+    launch_combine(ca, st);
+}
+
+// mixer of one layer: input rows are normed inside (norm_w != nullptr) or already normed
+void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __half* norm_w, int M, int nsegs,
+                   __half* resid, __half* plain_out, const int* row_pos_override) {
+    cudaStream_t st = e->stream;
+    const sl_config& c = e->cfg;
+    DenseArgs d{}; d.w = L.in_proj.w; d.s = L.in_proj.s; d.b = L.in_proj.b; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
+    d.x = rows; d.ldx = e->H; d.nw = norm_w; d.eps = c.rms_eps; d.y = e->inproj; d.ldy = (int)L.in_proj.N;
+    launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, e->exact, d, st, false);
+    DenseArgs o{}; o.w = L.out_proj.w; o.s = L.out_proj.s; o.b = L.out_proj.b; o.N = e->H; o.K = L.out_proj.K; o.M = M;
+    o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H;
+    if (!L.is_attn) {
+        GdnArgs g{}; g.inproj = e->inproj; g.ld = e->gdn_in; g.conv_w = L.conv_w; g.A_log = L.A_log; g.dt_bias = L.dt_bias;
+        g.Hk = c.gdn_k_heads; g.Hv = c.gdn_v_heads; g.eps = c.rms_eps; g.tab = e->tab; g.gdn_index = L.type_index; g.segs = e->segs; g.y = e->mix;
+        launch_gdn_core(g, nsegs, st);
+        o.x = e->mix; o.ldx = e->valDim; o.nw = L.gdn_norm; o.z = e->inproj + e->convDim; o.ldz = e->gdn_in;
+        launch_dense(PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, false);
+    } else {
+        AttnArgs a{}; a.inproj = e->inproj; a.ld = e->attn_in; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.NH = c.attn_heads; a.KV = c.attn_kv_heads;
+        a.eps = c.rms_eps; a.theta = c.rope_theta; a.tab = e->tab; a.attn_index = L.type_index; a.n_attn_layers = e->n_attn > 0 ? e->n_attn : 1;
+        a.page_size = c.kv_page_size; a.kv_pool = e->kv_pool; a.segs = e->segs; a.row_seg = e->row_seg; a.row_off = e->row_off;
+        a.row_pos_override = row_pos_override; a.qrot = e->qrot; a.part_o = e->part_o; a.part_ml = e->part_ml; a.nsplit = NSPLIT; a.gated = e->mix; a.M = M;
+        launch_attn_prep(a, st);
+        launch_attn_decode(a, st);
+        launch_attn_combine(a, st);
+        o.x = e->mix; o.ldx = e->attn_out;
+        launch_dense(PRO_PLAIN, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, false);
+    }
+}
+
+// all kernels of one call; descriptors / tokens are already on the device
+void enqueue_step(sl_engine* e, int M, int nsegs, HeadMode head, bool want_logits) {
+    cudaStream_t st = e->stream;
+    launch_embed(e->embed, e->tok_in, M, e->H, e->V, e->h, st);
+    for (const LayerW& L : e->layers) {
+        enqueue_mixer(e, L, e->h, L.in_norm, M, nsegs, e->h, nullptr, nullptr);
+        enqueue_moe(e, L, e->h, e->H, true, M, e->h, nullptr);
+    }
+    if (head == HEAD_NORMED) {
+        launch_final_norm(e->h, e->final_norm, e->cfg.rms_eps, M, e->H, e->normed, st);
+    } else if (head == HEAD_ARGMAX || head == HEAD_LOGITS) {
+        DenseArgs d{}; d.w = e->lm_head.w; d.s = e->lm_head.s; d.b = e->lm_head.b; d.N = e->V; d.K = e->H; d.M = M;
+        d.x = e->h; d.ldx = e->H; d.nw = e->final_norm; d.eps = e->cfg.rms_eps;
+        d.logits = want_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
+        launch_dense(PRO_RMSNORM, EPI_ARGMAX, e->exact, d, st, false);
+    }
+    StepEndArgs se{}; se.tab = e->tab; se.segs = e->segs; se.nsegs = nsegs; se.M = M;
+    se.out_tok = (head == HEAD_ARGMAX || head == HEAD_LOGITS) ? e->out_tok : nullptr;
+    se.tok_in = e->tok_in; se.hist = e->hist; se.hist_pos = e->hist_pos; se.hist_cap = e->hist_cap;
+    launch_step_end(se, st);
+}
+
+// make sure `s` has KV pages for `new_len` positions; uploads new page-table entries
+int32_t ensure_pages(sl_stream* s, int new_len) {
+    sl_engine* e = s->e;
+    if (new_len > s->max_seq_len) return SL_ERR_CAPACITY;
+    int need = (new_len + e->cfg.kv_page_size - 1) / e->cfg.kv_page_size;
+    int have = (int)s->pages.size();
+    if (need <= have) return SL_OK;
+    if ((int)e->free_pages.size() < need - have) return SL_ERR_CAPACITY;
+    for (int i = have; i < need; ++i) { s->pages.push_back(e->free_pages.back()); e->free_pages.pop_back(); }
+    CU(e, cudaMemcpyAsync(e->tab.page_table + (size_t)s->slot * e->tab.max_pages + have, s->pages.data() + have,
+                          (size_t)(need - have) * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    // the source is pageable host memory owned by the stream object: make the copy complete before it can change
+    CU(e, cudaStreamSynchronize(e->stream));
+    return SL_OK;
+}
+
+// upload tokens (optional) and row / segment descriptors for a call
+int32_t upload_descs(sl_engine* e, const std::vector<SegDesc>& segs, const int32_t* tokens, int M) {
+    CU(e, cudaStreamSynchronize(e->stream));    // the pinned staging area may still feed an earlier copy
+    int* pin = e->pin_i;
+    size_t off = 0;
+    int* p_tok = pin + off; off += M;
+    int* p_seg = pin + off; off += M;
+    int* p_off = pin + off; off += M;
+    SegDesc* p_sd = reinterpret_cast<SegDesc*>(pin + off);
+    for (size_t si = 0; si < segs.size(); ++si) {
+        p_sd[si] = segs[si];
+        for (int r = 0; r < segs[si].nrows; ++r) { p_seg[segs[si].row0 + r] = (int)si; p_off[segs[si].row0 + r] = r; }
+    }
+    if (tokens) {
+        memcpy(p_tok, tokens, (size_t)M * sizeof(int));
+        CU(e, cudaMemcpyAsync(e->tok_in, p_tok, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    }
+    CU(e, cudaMemcpyAsync(e->row_seg, p_seg, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaMemcpyAsync(e->row_off, p_off, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaMemcpyAsync(e->segs, p_sd, segs.size() * sizeof(SegDesc), cudaMemcpyHostToDevice, e->stream));
+    return SL_OK;
+}
+
+// decode-shaped steps (every segment one row) replay a CUDA graph after the first eager run
+int32_t enqueue_decode_step(sl_engine* e, int rows) {
+    if (!e->use_graph) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return SL_OK; }
+    auto it = e->graphs.find(rows);
+    if (it == e->graphs.end()) {
+        if (e->eager_runs[rows]++ == 0) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return SL_OK; }
+        cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
+        CU(e, cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+        enqueue_step(e, rows, rows, HEAD_ARGMAX, false);
+        CU(e, cudaStreamEndCapture(e->stream, &graph));
+        CU(e, cudaGraphInstantiate(&exec, graph, 0));
+        cudaGraphDestroy(graph);
+        it = e->graphs.emplace(rows, exec).first;
+    }
+    CU(e, cudaGraphLaunch(it->second, e->stream));
+    return SL_OK;
+}
+
+int32_t sync_check(sl_engine* e) {
+    CU(e, cudaStreamSynchronize(e->stream));
+    CU(e, cudaGetLastError());
+    return SL_OK;
+}
+
+int32_t run_single(sl_stream* s, const int32_t* tokens, int M, HeadMode head, bool want_logits) {
+    sl_engine* e = s->e;
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!tokens || M <= 0) return SL_ERR_INVALID;
+    if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
+    for (int i = 0; i < M; ++i) if (tokens[i] < 0 || tokens[i] >= e->V) return SL_ERR_INVALID;
+    if ((rc = ensure_pages(s, s->kv_len + M))) return rc;
+    if (want_logits && e->logits_rows < M) {
+        __half* lg; if ((rc = dalloc(e, &lg, (size_t)e->cfg.max_rows * e->V))) return rc;
+        e->logits = lg; e->logits_rows = e->cfg.max_rows;
+    }
+    std::vector<SegDesc> segs{SegDesc{s->slot, 0, M, 0}};
+    if ((rc = upload_descs(e, segs, tokens, M))) return rc;
+    if (M == 1 && head == HEAD_ARGMAX && !want_logits) { if ((rc = enqueue_decode_step(e, 1))) return rc; }
+    else enqueue_step(e, M, 1, head, want_logits);
+    s->kv_len += M; s->parity ^= 1;
+    return SL_OK;
+}
+
+}  // namespace
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+extern "C" {
+
+int32_t sl_engine_destroy(sl_engine* e) {
+    if (!e) return SL_ERR_INVALID;
+    cudaDeviceSynchronize();
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
+    for (void* p : e->allocs) cudaFree(p);
+    if (e->pin_i) cudaFreeHost(e->pin_i);
+    if (e->own_stream) cudaStreamDestroy(e->own_stream);
+    cudaGetLastError();
+    delete e;
+    return SL_OK;
+}
+
+static int32_t create_common(const sl_config* cfg, sl_engine** out, sl_engine** made) {
+    if (!cfg || !out) return SL_ERR_INVALID;
+    *out = nullptr;
+    if (!config_ok(*cfg)) return SL_ERR_INVALID;
+    if (!device_ok()) return SL_ERR_NO_DEVICE;
+    sl_engine* e = new sl_engine();
+    e->cfg = *cfg;
+    int32_t rc = build_layout(e);
+    if (!rc) rc = build_runtime(e);
+    if (!rc) rc = finish_create(e);
+    if (rc) { sl_engine_destroy(e); return rc; }
+    *made = e;
+    return SL_OK;
+}
+
+int32_t sl_engine_create(const sl_config* cfg, const sl_weight_desc* weights, int32_t n_weights, sl_engine** out) {
+    sl_engine* e = nullptr;
+    if (!weights || n_weights <= 0) return SL_ERR_INVALID;
+    int32_t rc = create_common(cfg, out, &e);
+    if (rc) return rc;
+    std::map<std::string, bool> seen;
+    for (int i = 0; i < n_weights; ++i) {
+        const sl_weight_desc& d = weights[i];
+        auto it = d.name ? e->tensors.find(d.name) : e->tensors.end();
+        if (it == e->tensors.end()) { sl_engine_destroy(e); return SL_ERR_NOT_FOUND; }
+        if (!d.data || d.nbytes != it->second.bytes) { sl_engine_destroy(e); return SL_ERR_INVALID; }
+        if (cudaMemcpy(it->second.ptr, d.data, d.nbytes, d.on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice) != cudaSuccess) {
+            sl_engine_destroy(e); return SL_ERR_CUDA;
+        }
+        seen[d.name] = true;
+    }
+    if (seen.size() != e->tensors.size()) { sl_engine_destroy(e); return SL_ERR_INVALID; }   // every tensor must be given
+    *out = e;
+    return SL_OK;
+}
+
+int32_t sl_engine_create_synthetic(const sl_config* cfg, const sl_synth_spec* synth, sl_engine** out) {
+    sl_engine* e = nullptr;
+    if (!synth) return SL_ERR_INVALID;
+    int32_t rc = create_common(cfg, out, &e);
+    if (rc) return rc;
+    const uint64_t seed = synth->seed;
+    cudaStream_t st = e->stream;
+    auto has_suffix = [](const std::string& s, const char* suf) { size_t n = strlen(suf); return s.size() >= n && s.compare(s.size() - n, n, suf) == 0; };
+    for (auto& kv : e->tensors) {
+        const std::string& name = kv.first;
+        Tensor& t = kv.second;
+        if (has_suffix(name, ".s") || has_suffix(name, ".b")) continue;          // produced together with ".w"
+        if (has_suffix(name, ".w")) {
+            std::string base = name.substr(0, name.size() - 2);
+            Tensor& ts = e->tensors[base + ".s"]; Tensor& tb = e->tensors[base + ".b"];
+            int64_t groups = (int64_t)(ts.bytes / 2);
+            // the generator indexes groups linearly, so only the total matters: N*K = groups*64
+            launch_synth_q4(tensor_seed(seed, base.c_str()), groups, 64, 0.02f, (uint32_t*)t.ptr, (__half*)ts.ptr, (__half*)tb.ptr, st);
+        } else if (has_suffix(name, "norm")) {
+            launch_synth_f16(tensor_seed(seed, name.c_str()), (int64_t)(t.bytes / 2), 1.0f, synth->norm_jitter, (__half*)t.ptr, st);
+        } else if (has_suffix(name, "gdn.conv_w")) {
+            launch_synth_f32(tensor_seed(seed, name.c_str()), (int64_t)(t.bytes / 4), 0.0f, synth->conv_std, (float*)t.ptr, st);
+        } else if (has_suffix(name, "gdn.A_log") || has_suffix(name, "gdn.dt_bias")) {
+            launch_synth_f32(tensor_seed(seed, name.c_str()), (int64_t)(t.bytes / 4), 0.0f, 1.0f, (float*)t.ptr, st);
+        } else {   // embed, router, shared_gate: fp16 ~N(0, 0.02)
+            launch_synth_f16(tensor_seed(seed, name.c_str()), (int64_t)(t.bytes / 2), 0.0f, 0.02f, (__half*)t.ptr, st);
+        }
+    }
+    if (cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess) { sl_engine_destroy(e); return SL_ERR_CUDA; }
+    *out = e;
+    return SL_OK;
+}
+
+int32_t sl_engine_set_cuda_stream(sl_engine* e, void* cuda_stream) {
+    if (!e) return SL_ERR_INVALID;
+    cudaStreamSynchronize(e->stream);
+    for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);    // graphs are tied to the stream they were captured on
+    e->graphs.clear(); e->eager_runs.clear();
+    e->stream = cuda_stream ? (cudaStream_t)cuda_stream : e->own_stream;
+    return SL_OK;
+}
+
+int32_t sl_engine_tensor_bytes(sl_engine* e, const char* name, uint64_t* nbytes) {
+    if (!e || !name || !nbytes) return SL_ERR_INVALID;
+    auto it = e->tensors.find(name);
+    if (it == e->tensors.end()) return SL_ERR_NOT_FOUND;
+    *nbytes = it->second.bytes;
+    return SL_OK;
+}
+int32_t sl_engine_read_tensor(sl_engine* e, const char* name, void* host_buf, uint64_t nbytes) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!name || !host_buf) return SL_ERR_INVALID;
+    auto it = e->tensors.find(name);
+    if (it == e->tensors.end()) return SL_ERR_NOT_FOUND;
+    if (nbytes != it->second.bytes) return SL_ERR_INVALID;
+    CU(e, cudaMemcpy(host_buf, it->second.ptr, nbytes, cudaMemcpyDeviceToHost));
+    return SL_OK;
+}
+const char* sl_last_fault(sl_engine* e) { return (e && e->poisoned) ? e->fault.c_str() : nullptr; }
+int32_t sl_inject_fault(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->inject = on != 0; return SL_OK; }
+int64_t sl_engine_launch_count(sl_engine* e) { (void)e; return kernel_launch_count(); }
+
+// ---- streams ----
+int32_t sl_stream_create(sl_engine* e, int32_t max_seq_len, sl_stream** out) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!out || max_seq_len <= 0) return SL_ERR_INVALID;
+    if (e->free_slots.empty()) return SL_ERR_CAPACITY;
+    sl_stream* s = new sl_stream{e, e->free_slots.back(), max_seq_len, 0, 0, {}};
+    e->free_slots.pop_back();
+    *out = s;
+    return sl_stream_reset(s);
+}
+int32_t sl_stream_destroy(sl_stream* s) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    cudaStreamSynchronize(e->stream);
+    for (int pg : s->pages) e->free_pages.push_back(pg);
+    e->free_slots.push_back(s->slot);
+    delete s;
+    return SL_OK;
+}
+int32_t sl_stream_len(sl_stream* s) { return s ? s->kv_len : SL_ERR_INVALID; }
+int32_t sl_stream_reset(sl_stream* s) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = guard(e); if (rc) return rc;
+    s->kv_len = 0; s->parity = 0;
+    for (int pg : s->pages) e->free_pages.push_back(pg);
+    s->pages.clear();
+    CU(e, cudaMemsetAsync(e->tab.kv_len + s->slot, 0, sizeof(int), e->stream));
+    CU(e, cudaMemsetAsync(e->tab.parity + s->slot, 0, sizeof(int), e->stream));
+    CU(e, cudaMemsetAsync(e->tab.gdn_state + (size_t)s->slot * e->tab.state_stride_stream, 0, e->tab.state_stride_stream * sizeof(float), e->stream));
+    CU(e, cudaMemsetAsync(e->tab.conv_hist + (size_t)s->slot * e->tab.hist_stride_stream, 0, e->tab.hist_stride_stream * sizeof(__half), e->stream));
+    return sync_check(e);
+}
+
+// ---- forward / step ----
+int32_t sl_forward(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_normed_f16) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = run_single(s, tokens, M, HEAD_NORMED, false); if (rc) return rc;
+    if (out_normed_f16) CU(e, cudaMemcpyAsync(out_normed_f16, e->normed, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_step_argmax(sl_stream* s, const int32_t* tokens, int32_t M, int32_t* out_tokens) {
+    if (!s || !out_tokens) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = run_single(s, tokens, M, HEAD_ARGMAX, false); if (rc) return rc;
+    CU(e, cudaMemcpyAsync(out_tokens, e->out_tok, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_step_logits(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_logits_f16) {
+    if (!s || !out_logits_f16) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = run_single(s, tokens, M, HEAD_LOGITS, true); if (rc) return rc;
+    CU(e, cudaMemcpyAsync(out_logits_f16, e->logits, (size_t)M * e->V * 2, cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_chained_enqueue(sl_stream* s, int32_t first, int32_t K) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = guard(e); if (rc) return rc;
+    if (K <= 0 || K > e->hist_cap) return SL_ERR_INVALID;
+    if (first >= e->V) return SL_ERR_INVALID;
+    if ((rc = ensure_pages(s, s->kv_len + K))) return rc;
+    std::vector<SegDesc> segs{SegDesc{s->slot, 0, 1, 0}};
+    int32_t tok = first;
+    if ((rc = upload_descs(e, segs, first >= 0 ? &tok : nullptr, 1))) return rc;
+    CU(e, cudaMemsetAsync(e->hist_pos, 0, sizeof(int), e->stream));
+    for (int k = 0; k < K; ++k) {
+        if ((rc = enqueue_decode_step(e, 1))) return rc;
+        s->kv_len += 1; s->parity ^= 1;
+    }
+    return SL_OK;
+}
+int32_t sl_chained_collect(sl_stream* s, int32_t K, int32_t* out_tokens) {
+    if (!s || !out_tokens || K <= 0) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = guard(e); if (rc) return rc;
+    if (K > e->hist_cap) return SL_ERR_INVALID;
+    CU(e, cudaMemcpyAsync(out_tokens, e->hist, (size_t)K * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_chained_step_argmax(sl_stream* s, int32_t first, int32_t K, int32_t* out_tokens) {
+    if (first < 0) return SL_ERR_INVALID;
+    int32_t rc = sl_chained_enqueue(s, first, K); if (rc) return rc;
+    return sl_chained_collect(s, K, out_tokens);
+}
+
+int32_t sl_batch_step_argmax(sl_engine* e, sl_stream* const* streams, const int32_t* tokens, int32_t B, int32_t* out_tokens) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!streams || !tokens || !out_tokens || B <= 0) return SL_ERR_INVALID;
+    if (B > e->cfg.max_rows) return SL_ERR_CAPACITY;
+    std::vector<SegDesc> segs;
+    for (int b = 0; b < B; ++b) {
+        if (!streams[b] || streams[b]->e != e) return SL_ERR_INVALID;
+        for (int j = 0; j < b; ++j) if (streams[j] == streams[b]) return SL_ERR_INVALID;
+        if (tokens[b] < 0 || tokens[b] >= e->V) return SL_ERR_INVALID;
+        if ((rc = ensure_pages(streams[b], streams[b]->kv_len + 1))) return rc;
+        segs.push_back(SegDesc{streams[b]->slot, b, 1, 0});
+    }
+    if ((rc = upload_descs(e, segs, tokens, B))) return rc;
+    if ((rc = enqueue_decode_step(e, B))) return rc;
+    for (int b = 0; b < B; ++b) { streams[b]->kv_len += 1; streams[b]->parity ^= 1; }
+    CU(e, cudaMemcpyAsync(out_tokens, e->out_tok, (size_t)B * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+
+// ---- snapshot / rollback ----
+static int32_t push_len_parity(sl_stream* s) {
+    sl_engine* e = s->e;
+    int v[2] = {s->kv_len, s->parity};
+    CU(e, cudaMemcpyAsync(e->tab.kv_len + s->slot, &v[0], sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaMemcpyAsync(e->tab.parity + s->slot, &v[1], sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    return sync_check(e);
+}
+int32_t sl_snapshot(sl_stream* s, sl_snap* out) {
+    if (!s || !out) return SL_ERR_INVALID;
+    out->kv_len = s->kv_len; out->parity = s->parity; out->valid = 1;
+    return SL_OK;
+}
+int32_t sl_rollback_one_step(sl_stream* s, const sl_snap* snap) {
+    if (!s || !snap || !snap->valid) return SL_ERR_INVALID;
+    int32_t rc = guard(s->e); if (rc) return rc;
+    if (snap->kv_len > s->kv_len) return SL_ERR_INVALID;
+    if (snap->kv_len == s->kv_len) return SL_OK;           // nothing ran since the snapshot
+    if (s->parity == snap->parity) return SL_ERR_INVALID;  // more than one step ran: the other side no longer holds the old state
+    s->kv_len = snap->kv_len; s->parity = snap->parity;
+    return push_len_parity(s);
+}
+static float* cur_state(sl_stream* s) { return s->e->tab.gdn_state + (size_t)s->slot * s->e->tab.state_stride_stream + (size_t)s->parity * s->e->tab.state_stride_side; }
+static __half* cur_hist(sl_stream* s) { return s->e->tab.conv_hist + (size_t)s->slot * s->e->tab.hist_stride_stream + (size_t)s->parity * s->e->tab.hist_stride_side; }
+
+int32_t sl_full_snapshot(sl_stream* s, sl_fullsnap** out) {
+    if (!s || !out) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = guard(e); if (rc) return rc;
+    sl_fullsnap* f = new sl_fullsnap{s->kv_len, nullptr, nullptr};
+    size_t sb = e->tab.state_stride_side * sizeof(float), hb = e->tab.hist_stride_side * sizeof(__half);
+    if (cudaMalloc(&f->state, sb) != cudaSuccess || cudaMalloc(&f->hist, hb) != cudaSuccess) {
+        cudaGetLastError(); if (f->state) cudaFree(f->state); delete f; return SL_ERR_CAPACITY;
+    }
+    CU(e, cudaMemcpyAsync(f->state, cur_state(s), sb, cudaMemcpyDeviceToDevice, e->stream));
+    CU(e, cudaMemcpyAsync(f->hist, cur_hist(s), hb, cudaMemcpyDeviceToDevice, e->stream));
+    rc = sync_check(e);
+    if (rc) { cudaFree(f->state); cudaFree(f->hist); delete f; return rc; }
+    *out = f;
+    return SL_OK;
+}
+int32_t sl_full_restore(sl_stream* s, const sl_fullsnap* f) {
+    if (!s || !f) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = guard(e); if (rc) return rc;
+    if (f->kv_len > s->kv_len) return SL_ERR_INVALID;      // KV is append-only: only rewinds are possible
+    size_t sb = e->tab.state_stride_side * sizeof(float), hb = e->tab.hist_stride_side * sizeof(__half);
+    CU(e, cudaMemcpyAsync(cur_state(s), f->state, sb, cudaMemcpyDeviceToDevice, e->stream));
+    CU(e, cudaMemcpyAsync(cur_hist(s), f->hist, hb, cudaMemcpyDeviceToDevice, e->stream));
+    s->kv_len = f->kv_len;
+    return push_len_parity(s);
+}
+int32_t sl_fullsnap_free(sl_fullsnap* f) {
+    if (!f) return SL_ERR_INVALID;
+    cudaFree(f->state); cudaFree(f->hist); delete f;
+    return SL_OK;
+}
+
+// ---- "QWS1" blob ----
+int32_t sl_state_size(sl_stream* s, uint64_t* nbytes) {
+    if (!s || !nbytes) return SL_ERR_INVALID;
+    sl_engine* e = s->e; const sl_config& c = e->cfg;
+    uint64_t n = 12;
+    for (const LayerW& L : e->layers) {
+        n += 4;
+        if (L.is_attn) n += 12 + 2ull * c.attn_kv_heads * s->kv_len * ATT_D * 2;
+        else n += 8 + (uint64_t)(CONV_K - 1) * e->convDim * 2 + (uint64_t)c.gdn_v_heads * GDN_DV * GDN_DK * 4;
+    }
+    *nbytes = n;
+    return SL_OK;
+}
+// copy positions [0,len) of (layer, K|V, head) between the paged arena and a contiguous host run
+static int32_t kv_copy(sl_stream* s, int attn_index, int which, int kvh, int len, uint8_t* host, bool to_host) {
+    sl_engine* e = s->e; const sl_config& c = e->cfg;
+    size_t page_elems = (size_t)e->n_attn * 2 * c.attn_kv_heads * c.kv_page_size * ATT_D;
+    for (int p0 = 0; p0 < len; p0 += c.kv_page_size) {
+        int n = len - p0 < c.kv_page_size ? len - p0 : c.kv_page_size;
+        __half* dev = e->kv_pool + (size_t)s->pages[p0 / c.kv_page_size] * page_elems +
+                      (((size_t)attn_index * 2 + which) * c.attn_kv_heads + kvh) * c.kv_page_size * ATT_D;
+        uint8_t* hp = host + (size_t)p0 * ATT_D * 2;
+        if (to_host) CU(e, cudaMemcpyAsync(hp, dev, (size_t)n * ATT_D * 2, cudaMemcpyDeviceToHost, e->stream));
+        else CU(e, cudaMemcpyAsync(dev, hp, (size_t)n * ATT_D * 2, cudaMemcpyHostToDevice, e->stream));
+    }
+    return SL_OK;
+}
+int32_t sl_state_save(sl_stream* s, void* buf, uint64_t nbytes) {
+    if (!s || !buf) return SL_ERR_INVALID;
+    sl_engine* e = s->e; const sl_config& c = e->cfg;
+    int32_t rc = guard(e); if (rc) return rc;
+    uint64_t need; sl_state_size(s, &need);
+    if (nbytes < need) return SL_ERR_CAPACITY;
+    uint8_t* p = (uint8_t*)buf;
+    auto u32 = [&](uint32_t v) { memcpy(p, &v, 4); p += 4; };
+    u32(0x31535751u); u32(1); u32((uint32_t)c.n_layers);
+    for (const LayerW& L : e->layers) {
+        if (L.is_attn) {
+            u32(1); u32(c.attn_kv_heads); u32(ATT_D); u32(s->kv_len);
+            for (int which = 0; which < 2; ++which)
+                for (int hh = 0; hh < c.attn_kv_heads; ++hh) {
+                    if ((rc = kv_copy(s, L.type_index, which, hh, s->kv_len, p, true))) return rc;
+                    p += (size_t)s->kv_len * ATT_D * 2;
+                }
+        } else {
+            size_t cc = e->tab.hist_stride_layer, sc = e->tab.state_stride_layer;
+            u32(2); u32((uint32_t)cc); u32((uint32_t)sc);
+            CU(e, cudaMemcpyAsync(p, cur_hist(s) + (size_t)L.type_index * cc, cc * 2, cudaMemcpyDeviceToHost, e->stream)); p += cc * 2;
+            CU(e, cudaMemcpyAsync(p, cur_state(s) + (size_t)L.type_index * sc, sc * 4, cudaMemcpyDeviceToHost, e->stream)); p += sc * 4;
+        }
+    }
+    return sync_check(e);
+}
+int32_t sl_state_restore(sl_stream* s, const void* buf, uint64_t nbytes) {
+    if (!s || !buf) return SL_ERR_INVALID;
+    sl_engine* e = s->e; const sl_config& c = e->cfg;
+    int32_t rc = guard(e); if (rc) return rc;
+    const uint8_t* b = (const uint8_t*)buf;
+    // pass 1: validate the whole blob before touching the stream
+    uint64_t off = 0; bool ok = true;
+    auto u32 = [&]() -> uint32_t { if (off + 4 > nbytes) { ok = false; return 0; } uint32_t v; memcpy(&v, b + off, 4); off += 4; return v; };
+    if (u32() != 0x31535751u || u32() != 1u || u32() != (uint32_t)c.n_layers || !ok) return SL_ERR_FORMAT;
+    int len = -1;
+    for (const LayerW& L : e->layers) {
+        uint32_t flags = u32(); if (!ok) return SL_ERR_FORMAT;
+        if (flags != (L.is_attn ? 1u : 2u)) return SL_ERR_FORMAT;
+        if (L.is_attn) {
+            uint32_t kv = u32(), d = u32(), l = u32(); if (!ok) return SL_ERR_FORMAT;
+            if (kv != (uint32_t)c.attn_kv_heads || d != (uint32_t)ATT_D || (int)l > s->max_seq_len) return SL_ERR_FORMAT;
+            if (len >= 0 && (int)l != len) return SL_ERR_FORMAT;
+            len = (int)l;
+            off += 2ull * kv * l * d * 2;
+        } else {
+            uint32_t cc = u32(), sc = u32(); if (!ok) return SL_ERR_FORMAT;
+            if (cc != (uint32_t)e->tab.hist_stride_layer || sc != (uint32_t)e->tab.state_stride_layer) return SL_ERR_FORMAT;
+            off += (uint64_t)cc * 2 + (uint64_t)sc * 4;
+        }
+        if (off > nbytes) return SL_ERR_FORMAT;
+    }
+    if (off != nbytes) return SL_ERR_FORMAT;
+    if (len < 0) len = 0;
+    if ((rc = ensure_pages(s, len))) return rc;
+    // pass 2: copy
+    off = 12;
+    for (const LayerW& L : e->layers) {
+        off += 4;
+        if (L.is_attn) {
+            off += 12;
+            for (int which = 0; which < 2; ++which)
+                for (int hh = 0; hh < c.attn_kv_heads; ++hh) {
+                    if ((rc = kv_copy(s, L.type_index, which, hh, len, const_cast<uint8_t*>(b + off), false))) return rc;
+                    off += (size_t)len * ATT_D * 2;
+                }
+        } else {
+            size_t cc = e->tab.hist_stride_layer, sc = e->tab.state_stride_layer;
+            off += 8;
+            CU(e, cudaMemcpyAsync(cur_hist(s) + (size_t)L.type_index * cc, b + off, cc * 2, cudaMemcpyHostToDevice, e->stream)); off += cc * 2;
+            CU(e, cudaMemcpyAsync(cur_state(s) + (size_t)L.type_index * sc, b + off, sc * 4, cudaMemcpyHostToDevice, e->stream)); off += sc * 4;
+        }
+    }
+    s->kv_len = len;
+    return push_len_parity(s);
+}
+
+// ---- single operators ----
+int32_t sl_op_qmm4_device(const void* x_dev, const void* w_dev, const void* s_dev, const void* b_dev,
+                          int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream) {
+    if (!x_dev || !w_dev || !s_dev || !b_dev || !y_dev) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (!device_ok()) return SL_ERR_NO_DEVICE;
+    if (detect_gemv_mode() != SL_OK) return SL_ERR_CUDA;
+    DenseArgs a{}; a.w = (const uint32_t*)w_dev; a.s = (const __half*)s_dev; a.b = (const __half*)b_dev; a.N = N; a.K = K; a.M = M;
+    a.x = (const __half*)x_dev; a.ldx = K; a.y = (__half*)y_dev; a.ldy = N;
+    launch_dense(PRO_PLAIN, EPI_STORE, g_gemv_mode == 1, a, (cudaStream_t)cuda_stream, false);
+    return cudaGetLastError() == cudaSuccess ? SL_OK : SL_ERR_CUDA;
+}
+int32_t sl_op_qmm4(const uint16_t* x, const uint32_t* w, const uint16_t* sc, const uint16_t* bi, int32_t M, int32_t K, int32_t N, uint16_t* y) {
+    if (!x || !w || !sc || !bi || !y) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (!device_ok()) return SL_ERR_NO_DEVICE;
+    void *dx = nullptr, *dw = nullptr, *ds = nullptr, *db = nullptr, *dy = nullptr;
+    size_t bx = (size_t)M * K * 2, bw = (size_t)N * K / 2, bs = (size_t)N * K / 64 * 2, by = (size_t)M * N * 2;
+    int32_t rc = SL_ERR_CUDA;
+    if (cudaMalloc(&dx, bx) == cudaSuccess && cudaMalloc(&dw, bw) == cudaSuccess && cudaMalloc(&ds, bs) == cudaSuccess &&
+        cudaMalloc(&db, bs) == cudaSuccess && cudaMalloc(&dy, by) == cudaSuccess) {
+        cudaMemcpy(dx, x, bx, cudaMemcpyHostToDevice); cudaMemcpy(dw, w, bw, cudaMemcpyHostToDevice);
+        cudaMemcpy(ds, sc, bs, cudaMemcpyHostToDevice); cudaMemcpy(db, bi, bs, cudaMemcpyHostToDevice);
+        rc = sl_op_qmm4_device(dx, dw, ds, db, M, K, N, dy, nullptr);
+        if (rc == SL_OK && cudaMemcpy(y, dy, by, cudaMemcpyDeviceToHost) != cudaSuccess) rc = SL_ERR_CUDA;
+    }
+    cudaFree(dx); cudaFree(dw); cudaFree(ds); cudaFree(db); cudaFree(dy);
+    cudaGetLastError();
+    return rc;
+}
+int32_t sl_op_quantize_q4(const uint16_t* w, int64_t N, int64_t K, uint32_t* packed, uint16_t* sc, uint16_t* bi) {
+    if (!w || !packed || !sc || !bi || N <= 0 || K <= 0 || K % 64) return SL_ERR_INVALID;
+    if (!device_ok()) return SL_ERR_NO_DEVICE;
+    void *dw = nullptr, *dp = nullptr, *ds = nullptr, *db = nullptr;
+    size_t bw = (size_t)N * K * 2, bp = (size_t)N * K / 2, bs = (size_t)N * K / 64 * 2;
+    int32_t rc = SL_ERR_CUDA;
+    if (cudaMalloc(&dw, bw) == cudaSuccess && cudaMalloc(&dp, bp) == cudaSuccess && cudaMalloc(&ds, bs) == cudaSuccess && cudaMalloc(&db, bs) == cudaSuccess) {
+        cudaMemcpy(dw, w, bw, cudaMemcpyHostToDevice);
+        launch_quantize_q4((const __half*)dw, N, K, (uint32_t*)dp, (__half*)ds, (__half*)db, 0);
+        if (cudaMemcpy(packed, dp, bp, cudaMemcpyDeviceToHost) == cudaSuccess && cudaMemcpy(sc, ds, bs, cudaMemcpyDeviceToHost) == cudaSuccess &&
+            cudaMemcpy(bi, db, bs, cudaMemcpyDeviceToHost) == cudaSuccess) rc = SL_OK;
+    }
+    cudaFree(dw); cudaFree(dp); cudaFree(ds); cudaFree(db);
+    cudaGetLastError();
+    return rc;
+}
+int32_t sl_op_moe_block(sl_engine* e, int32_t layer, const uint16_t* x, int32_t M, uint16_t* out, int32_t* inds, uint16_t* scores) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!x || !out || layer < 0 || layer >= e->cfg.n_layers || M <= 0) return SL_ERR_INVALID;
+    if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
+    CU(e, cudaMemcpyAsync(e->opx, x, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
+    enqueue_moe(e, e->layers[layer], e->opx, e->H, false, M, nullptr, e->opy);
+    CU(e, cudaMemcpyAsync(out, e->opy, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
+    if (inds) CU(e, cudaMemcpyAsync(inds, e->inds, (size_t)M * e->topk * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (scores) CU(e, cudaMemcpyAsync(scores, e->scores, (size_t)M * e->topk * 2, cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_op_mixer(sl_stream* s, int32_t layer, const uint16_t* x, int32_t M, int32_t pos0, uint16_t* out) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!x || !out || layer < 0 || layer >= e->cfg.n_layers || M <= 0 || pos0 < 0) return SL_ERR_INVALID;
+    if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
+    if ((rc = ensure_pages(s, pos0 + M))) return rc;
+    std::vector<SegDesc> segs{SegDesc{s->slot, 0, M, 0}};
+    if ((rc = upload_descs(e, segs, nullptr, M))) return rc;
+    std::vector<int> pos(M);
+    for (int i = 0; i < M; ++i) pos[i] = pos0 + i;
+    CU(e, cudaMemcpyAsync(e->row_pos, pos.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaMemcpyAsync(e->opx, x, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaStreamSynchronize(e->stream));
+    const LayerW& L = e->layers[layer];
+    enqueue_mixer(e, L, e->opx, nullptr, M, 1, nullptr, e->opy, e->row_pos);
+    if (!L.is_attn) {
+        // the GDN core wrote the other ping-pong side; this operator advances only this layer, so copy it back
+        size_t sc = e->tab.state_stride_layer, cc = e->tab.hist_stride_layer;
+        float* cur = cur_state(s) + (size_t)L.type_index * sc;
+        float* oth = e->tab.gdn_state + (size_t)s->slot * e->tab.state_stride_stream + (size_t)(s->parity ^ 1) * e->tab.state_stride_side + (size_t)L.type_index * sc;
+        __half* curh = cur_hist(s) + (size_t)L.type_index * cc;
+        __half* othh = e->tab.conv_hist + (size_t)s->slot * e->tab.hist_stride_stream + (size_t)(s->parity ^ 1) * e->tab.hist_stride_side + (size_t)L.type_index * cc;
+        CU(e, cudaMemcpyAsync(cur, oth, sc * 4, cudaMemcpyDeviceToDevice, e->stream));
+        CU(e, cudaMemcpyAsync(curh, othh, cc * 2, cudaMemcpyDeviceToDevice, e->stream));
+    }
+    CU(e, cudaMemcpyAsync(out, e->opy, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_op_lm_head(sl_engine* e, const uint16_t* normed, int32_t M, uint16_t* out_logits, int32_t* out_tokens) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!normed || M <= 0) return SL_ERR_INVALID;
+    if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
+    if (out_logits && e->logits_rows < M) {
+        __half* lg; if ((rc = dalloc(e, &lg, (size_t)e->cfg.max_rows * e->V))) return rc;
+        e->logits = lg; e->logits_rows = e->cfg.max_rows;
+    }
+    CU(e, cudaMemcpyAsync(e->opx, normed, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
+    DenseArgs d{}; d.w = e->lm_head.w; d.s = e->lm_head.s; d.b = e->lm_head.b; d.N = e->V; d.K = e->H; d.M = M;
+    d.x = e->opx; d.ldx = e->H; d.logits = out_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
+    launch_dense(PRO_PLAIN, EPI_ARGMAX, e->exact, d, e->stream, false);
+    if (out_logits) CU(e, cudaMemcpyAsync(out_logits, e->logits, (size_t)M * e->V * 2, cudaMemcpyDeviceToHost, e->stream));
+    if (out_tokens) CU(e, cudaMemcpyAsync(out_tokens, e->out_tok, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+
+// ---- synthetic data helpers ----
+int32_t sl_synth_tokens(uint64_t seed, const char* name, int64_t n, int32_t vocab, int32_t* out) {
+    if (!name || !out || n < 0 || vocab <= 0) return SL_ERR_INVALID;
+    host_synth_tokens(tensor_seed(seed, name), n, vocab, out);
+    return SL_OK;
+}
+int32_t sl_synth_f16(uint64_t seed, const char* name, int64_t n, float mean, float std, uint16_t* out) {
+    if (!name || !out || n <= 0) return SL_ERR_INVALID;
+    if (!device_ok()) return SL_ERR_NO_DEVICE;
+    void* d = nullptr;
+    if (cudaMalloc(&d, (size_t)n * 2) != cudaSuccess) { cudaGetLastError(); return SL_ERR_CUDA; }
+    launch_synth_f16(tensor_seed(seed, name), n, mean, std, (__half*)d, 0);
+    int32_t rc = cudaMemcpy(out, d, (size_t)n * 2, cudaMemcpyDeviceToHost) == cudaSuccess ? SL_OK : SL_ERR_CUDA;
+    cudaFree(d); cudaGetLastError();
+    return rc;
+}
+
+}  // extern "C"

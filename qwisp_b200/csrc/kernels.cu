@@ -1,0 +1,807 @@
+// kernels.cu -- the Seedless decode kernels for sm_100a and their launchers.
+#include "gemv.cuh"
+#include "kernels.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+
+namespace sl {
+
+static std::atomic<int64_t> g_launches{0};
+int64_t kernel_launch_count() { return g_launches.load(); }
+#define COUNT_LAUNCH() g_launches.fetch_add(1, std::memory_order_relaxed)
+
+// ============================================================================================
+// Dense q4 GEMV: one CTA = 16 weight rows x all K (slices across warps) x up to 8 activation rows.
+// grid (N/16 [N/8 tiles of 8+8 for the SwiGLU pairing], ceil(M/8)).
+// ============================================================================================
+template <int PRO, int EPI, bool EXACT>
+__global__ void __launch_bounds__(512) k_dense(DenseArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.y * 8;
+    const int mr = min(8, a.M - row0);
+    XStage st; float* red; float* fin; int* misc;
+    GemvSmem::carve(smem, min(a.M, 8), a.K, nw, st, red, fin, misc);
+
+    const int tile = blockIdx.x;
+    const int K8 = a.K >> 3, KG = a.K >> 6, slices = a.K >> 8;
+    const uint32_t *wA, *wB; const __half *sA, *bA, *sB, *bB;
+    if (EPI == EPI_SWIGLU) {
+        int64_t row = (int64_t)tile * 8 + r;
+        wA = a.w + row * K8; sA = a.s + row * KG; bA = a.b + row * KG;
+        wB = a.w2 + row * K8; sB = a.s2 + row * KG; bB = a.b2 + row * KG;
+    } else {
+        int64_t row = (int64_t)tile * 16 + r;
+        wA = a.w + row * K8; sA = a.s + row * KG; bA = a.b + row * KG;
+        wB = wA + 8 * (int64_t)K8; sB = sA + 8 * KG; bB = bA + 8 * KG;
+    }
+    // weights do not depend on the activations: get them in flight before staging
+    SliceRegs regs;
+    int sl_i = warp;
+    bool have = sl_i < slices;
+    if (have) load_slice(regs, wA, wB, sA, bA, sB, bB, sl_i, t);
+
+    if (PRO == PRO_PLAIN) stage_plain(st, a.x, a.ldx, row0, mr, a.K);
+    else if (PRO == PRO_RMSNORM) stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K);
+    else stage_normgate(st, a.x, a.ldx, a.z, a.ldz, a.nw, a.eps, row0, mr, a.K);
+    __syncthreads();
+
+    float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
+    while (have) {
+        compute_slice<EXACT>(regs, st, sl_i, r, t, r < mr, accS, accB);
+        sl_i += nw; have = sl_i < slices;
+        if (have) load_slice(regs, wA, wB, sA, bA, sB, bB, sl_i, t);
+    }
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = finish_acc<EXACT>(accS[i], accB[i]);
+    reduce_tile(red, fin, v, nw);
+
+    if (EPI == EPI_STORE || EPI == EPI_RESID) {
+        if (threadIdx.x < 128) {
+            int col = threadIdx.x >> 4, row = threadIdx.x & 15;
+            if (col < mr) {
+                size_t idx = (size_t)(row0 + col) * a.ldy + tile * 16 + row;
+                __half val = f2h(fin[row * 8 + col]);
+                if (EPI == EPI_RESID) val = hadd_rn(a.y[idx], val);
+                a.y[idx] = val;
+            }
+        }
+    } else if (EPI == EPI_SWIGLU) {
+        if (threadIdx.x < 64) {
+            int col = threadIdx.x >> 3, i = threadIdx.x & 7;
+            if (col < mr) {
+                __half g = f2h(fin[i * 8 + col]), u = f2h(fin[(i + 8) * 8 + col]);
+                a.y[(size_t)(row0 + col) * a.ldy + tile * 8 + i] = swiglu_h(g, u);
+            }
+        }
+    } else {  // EPI_ARGMAX: fp16 logits, per-tile first-index maximum, last block reduces all tiles
+        const int tiles = gridDim.x;
+        if (a.logits && threadIdx.x < 128) {
+            int col = threadIdx.x >> 4, row = threadIdx.x & 15;
+            if (col < mr) a.logits[(size_t)(row0 + col) * a.N + tile * 16 + row] = f2h(fin[row * 8 + col]);
+        }
+        if (threadIdx.x < 8 && (int)threadIdx.x < mr) {
+            int col = threadIdx.x;
+            float best = -INFINITY; int bi = 0x7fffffff;
+            for (int row = 0; row < 16; ++row) {
+                float lv = h2f(f2h(fin[row * 8 + col]));
+                if (lv > best) { best = lv; bi = tile * 16 + row; }
+            }
+            a.pval[(size_t)(row0 + col) * tiles + tile] = best;
+            a.pidx[(size_t)(row0 + col) * tiles + tile] = bi;
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned total = gridDim.x * gridDim.y;
+            unsigned ticket = atomicAdd(a.counter, 1u);
+            misc[0] = (ticket == total - 1) ? 1 : 0;
+        }
+        __syncthreads();
+        if (misc[0]) {
+            __threadfence();
+            float* rv = red; int* ri = reinterpret_cast<int*>(fin);   // red has >= 128 floats per warp
+            for (int m = 0; m < a.M; ++m) {
+                float best = -INFINITY; int bi = 0x7fffffff;
+                for (int tl = threadIdx.x; tl < tiles; tl += blockDim.x) {
+                    float lv = __ldcg(a.pval + (size_t)m * tiles + tl); int li = __ldcg(a.pidx + (size_t)m * tiles + tl);
+                    if (lv > best || (lv == best && li < bi)) { best = lv; bi = li; }
+                }
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) {
+                    float ov = __shfl_xor_sync(0xffffffffu, best, off); int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+                    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+                }
+                __syncthreads();
+                if (lane == 0) { rv[warp] = best; ri[warp] = bi; }
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    for (int w = 1; w < nw; ++w) if (rv[w] > best || (rv[w] == best && ri[w] < bi)) { best = rv[w]; bi = ri[w]; }
+                    a.out_tok[m] = bi;
+                }
+            }
+            if (threadIdx.x == 0) *a.counter = 0u;
+        }
+    }
+}
+
+size_t dense_smem_bytes(int M, int K) {
+    int nw = K / 256; if (nw > 16) nw = 16;
+    return GemvSmem::bytes(M < 8 ? M : 8, K, nw);
+}
+
+template <int PRO, int EPI, bool EXACT>
+static void launch_dense_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
+    int nw = a.K / 256; if (nw > 16) nw = 16;
+    size_t smem = GemvSmem::bytes(a.M < 8 ? a.M : 8, a.K, nw);
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaFuncSetAttribute(k_dense<PRO, EPI, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(96 * 1024));
+        configured = 96 * 1024;
+    }
+    dim3 grid((unsigned)(EPI == EPI_SWIGLU ? a.N / 8 : a.N / 16), (unsigned)((a.M + 7) / 8));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(nw * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    DenseArgs copy = a;
+    cudaLaunchKernelEx(&cfg, k_dense<PRO, EPI, EXACT>, copy);
+    COUNT_LAUNCH();
+}
+
+void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl) {
+#define SL_CASE(P, E)                                                                      \
+    if (pro == P && epi == E) {                                                            \
+        if (exact) launch_dense_t<P, E, true>(a, st, pdl); else launch_dense_t<P, E, false>(a, st, pdl); \
+        return;                                                                            \
+    }
+    SL_CASE(PRO_PLAIN, EPI_STORE)
+    SL_CASE(PRO_PLAIN, EPI_RESID)
+    SL_CASE(PRO_RMSNORM, EPI_STORE)
+    SL_CASE(PRO_RMSNORM, EPI_ARGMAX)
+    SL_CASE(PRO_PLAIN, EPI_ARGMAX)
+    SL_CASE(PRO_NORMGATE, EPI_RESID)
+    SL_CASE(PRO_NORMGATE, EPI_STORE)
+    SL_CASE(PRO_PLAIN, EPI_SWIGLU)
+#undef SL_CASE
+    fprintf(stderr, "seedless_b200: no dense kernel for prologue %d / epilogue %d\n", pro, epi);
+    abort();
+}
+
+// ============================================================================================
+// Embedding gather and final norm (rows only)
+// ============================================================================================
+__global__ void k_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h) {
+    int m = blockIdx.x;
+    int tok = tokens[m];
+    if (tok < 0 || tok >= vocab) tok = 0;
+    const uint4* src = reinterpret_cast<const uint4*>(embed + (size_t)tok * H);
+    uint4* dst = reinterpret_cast<uint4*>(h + (size_t)m * H);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st) {
+    k_embed<<<M, 256, 0, st>>>(embed, tokens, M, H, vocab, h);
+    COUNT_LAUNCH();
+}
+
+// block-wide rmsnorm of one row of width H (multiple of 256, <= 4096) with 256 threads
+__device__ __forceinline__ void block_rmsnorm_row(const __half* src, const __half* w, float eps, int H, __half* dst, float* sm8) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float ss = 0.f;
+    for (int k = threadIdx.x * 8; k < H; k += blockDim.x * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(src + k);
+        const __half2* hh = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { float2 f = __half22float2(hh[i]); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); }
+    }
+    ss = warp_sum(ss);
+    __syncthreads();
+    if (lane == 0) sm8[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += sm8[i];
+    float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)H), eps));
+    for (int k = threadIdx.x * 8; k < H; k += blockDim.x * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(src + k);
+        const __half* hv = reinterpret_cast<const __half*>(&v);
+        uint4 o; __half* oh = reinterpret_cast<__half*>(&o);
+        if (w) {
+            uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+            const __half* wh = reinterpret_cast<const __half*>(&wv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) oh[i] = hmul_rn(wh[i], f2h(__fmul_rn(h2f(hv[i]), inv)));
+        } else {
+            o = v;
+        }
+        *reinterpret_cast<uint4*>(dst + k) = o;
+    }
+}
+__global__ void k_final_norm(const __half* h, const __half* w, float eps, int H, __half* out) {
+    __shared__ float sm8[8];
+    block_rmsnorm_row(h + (size_t)blockIdx.x * H, w, eps, H, out + (size_t)blockIdx.x * H, sm8);
+}
+void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st) {
+    k_final_norm<<<M, 256, 0, st>>>(h, w, eps, H, out);
+    COUNT_LAUNCH();
+}
+
+// ============================================================================================
+// MoE router logits.  fp16 router [E][H]; the dot product follows a fixed order (lane l owns 8
+// consecutive inputs of every 256-wide block, sequential f32 accumulate, xor-butterfly over the
+// lanes) so that the fp16 logits, and with them the selected experts, are bit-identical to the
+// CPU restatement.  The reference's router is the same lane layout over an 8-bit weight
+// (swift/Sources/QwispCore/SeedlessMetalForward.swift:384-434).
+// grid: E/8 + 1 CTAs of 256 threads (one warp per expert); the last CTA writes the normed rows
+// and the shared-expert gate logit.
+// ============================================================================================
+__device__ __forceinline__ float canon_dot8(const uint4* wreg, const __half* xrow, int nblk, int lane) {
+    float acc = 0.f;
+    for (int kb = 0; kb < nblk; ++kb) {
+        uint4 xv = *reinterpret_cast<const uint4*>(xrow + kb * 256 + lane * 8);
+        const __half* xh = reinterpret_cast<const __half*>(&xv);
+        const __half* wh = reinterpret_cast<const __half*>(&wreg[kb]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(h2f(xh[i]), h2f(wh[i]), acc);   // product exact in f32
+    }
+    return warp_sum(acc);
+}
+__global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __half* ps = reinterpret_cast<__half*>(smem);            // [8][H]
+    float* sm8 = reinterpret_cast<float*>(ps + 8 * a.H);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nblk = a.H >> 8;                                // <= 16
+    const bool tail = (blockIdx.x == gridDim.x - 1);
+    const int e = blockIdx.x * 8 + warp;
+    uint4 wreg[16];
+    const __half* wrow = tail ? a.shared_gate : (a.router + (size_t)e * a.H);
+    const bool wvalid = tail ? (warp == 0) : (e < a.E);
+#pragma unroll
+    for (int kb = 0; kb < 16; ++kb)
+        wreg[kb] = (wvalid && kb < nblk) ? *reinterpret_cast<const uint4*>(wrow + kb * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+    for (int m0 = 0; m0 < a.M; m0 += 8) {
+        int mr = min(8, a.M - m0);
+        __syncthreads();
+        for (int c = 0; c < mr; ++c) {
+            const __half* src = a.h + (size_t)(m0 + c) * a.ldh;
+            if (a.norm_w) block_rmsnorm_row(src, a.norm_w, a.eps, a.H, ps + c * a.H, sm8);
+            else for (int k = threadIdx.x * 8; k < a.H; k += blockDim.x * 8) *reinterpret_cast<uint4*>(ps + c * a.H + k) = *reinterpret_cast<const uint4*>(src + k);
+        }
+        __syncthreads();
+        if (tail) {
+            for (int i = threadIdx.x; i < mr * a.H / 8; i += blockDim.x) {
+                int c = i / (a.H / 8), k = (i - c * (a.H / 8)) * 8;
+                *reinterpret_cast<uint4*>(a.p + (size_t)(m0 + c) * a.H + k) = *reinterpret_cast<const uint4*>(ps + c * a.H + k);
+            }
+            if (warp == 0)
+                for (int c = 0; c < mr; ++c) {
+                    float d = canon_dot8(wreg, ps + c * a.H, nblk, lane);
+                    if (lane == 0) a.sgl[m0 + c] = f2h(d);
+                }
+        } else if (wvalid) {
+            for (int c = 0; c < mr; ++c) {
+                float d = canon_dot8(wreg, ps + c * a.H, nblk, lane);
+                if (lane == 0) a.logits[(size_t)(m0 + c) * a.E + e] = f2h(d);
+            }
+        }
+    }
+}
+void launch_router(const RouterArgs& a, cudaStream_t st) {
+    size_t smem = (size_t)8 * a.H * 2 + 64;
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_moe_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); configured = true; }
+    k_moe_router<<<(a.E + 7) / 8 + 1, 256, smem, st>>>(a);
+    COUNT_LAUNCH();
+}
+
+// ============================================================================================
+// Top-k selection and renormalisation per row, then (last CTA) grouping of the (row, k) pairs
+// by expert.  Restates swift/Sources/QwispCore/SeedlessFusedVerify.swift:180-214: softmax in
+// f32, gates rounded to fp16, k rounds of arg-max on the raw logits (ties -> lower index),
+// fp16 sequential sum of the chosen gates, fp16 divide.  One CTA of 256 threads per row.
+// ============================================================================================
+__global__ void __launch_bounds__(256) k_moe_route(RouteArgs a) {
+    __shared__ float red[256]; __shared__ int redi[256]; __shared__ float gates[256]; __shared__ float work[256];
+    __shared__ int s_last; __shared__ int s_cnt[256]; __shared__ int s_cur[256]; __shared__ int s_slot[256];
+    const int tid = threadIdx.x, m = blockIdx.x;
+    const __half* lrow = a.logits + (size_t)m * a.E;
+    float lg = (tid < a.E) ? h2f(lrow[tid]) : -INFINITY;
+    red[tid] = lg; __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) { if (tid < s) red[tid] = fmaxf(red[tid], red[tid + s]); __syncthreads(); }
+    float mx = red[0]; __syncthreads();
+    float e = (tid < a.E) ? expf(lg - mx) : 0.0f;
+    red[tid] = e; __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) { if (tid < s) red[tid] = __fadd_rn(red[tid], red[tid + s]); __syncthreads(); }
+    float Z = red[0]; __syncthreads();
+    gates[tid] = (tid < a.E) ? h2f(f2h(__fdiv_rn(e, Z))) : 0.0f;
+    work[tid] = lg;
+    __syncthreads();
+    for (int k = 0; k < a.topk; ++k) {
+        red[tid] = work[tid]; redi[tid] = tid; __syncthreads();
+        for (int s = 128; s > 0; s >>= 1) {
+            if (tid < s) { if (red[tid + s] > red[tid]) { red[tid] = red[tid + s]; redi[tid] = redi[tid + s]; } }
+            __syncthreads();
+        }
+        if (tid == 0) { int bi = redi[0]; a.inds[m * a.topk + k] = bi; a.scores[m * a.topk + k] = f2h(gates[bi]); work[bi] = -INFINITY; }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        __half ss = f2h(0.0f);
+        for (int k = 0; k < a.topk; ++k) ss = hadd_rn(ss, a.scores[m * a.topk + k]);
+        for (int k = 0; k < a.topk; ++k) a.scores[m * a.topk + k] = hdiv_rn(a.scores[m * a.topk + k], ss);
+    }
+    // ---- last CTA: group pairs by expert ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    s_cnt[tid] = 0; s_cur[tid] = 0; s_slot[tid] = -1;
+    __syncthreads();
+    const int npairs = a.M * a.topk;
+    for (int i = tid; i < npairs; i += 256) atomicAdd(&s_cnt[__ldcg(a.inds + i)], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int slot = 0, off = 0;
+        for (int ex = 0; ex < a.E; ++ex)
+            if (s_cnt[ex] > 0) {
+                a.lists.slot_expert[slot] = ex; a.lists.slot_off[slot] = off; a.lists.slot_cnt[slot] = s_cnt[ex];
+                s_slot[ex] = off; off += s_cnt[ex]; ++slot;
+            }
+        *a.lists.n_active = slot;
+        *a.counter = 0u;
+    }
+    __syncthreads();
+    for (int i = tid; i < npairs; i += 256) {
+        int ex = __ldcg(a.inds + i);
+        int pos = atomicAdd(&s_cur[ex], 1);
+        a.lists.pairs[s_slot[ex] + pos] = i;
+    }
+}
+void launch_route(const RouteArgs& a, cudaStream_t st) {
+    k_moe_route<<<a.M, 256, 0, st>>>(a);
+    COUNT_LAUNCH();
+}
+
+// ============================================================================================
+// Routed + shared experts, grouped by expert: every touched expert's weights are read once per
+// call and applied to all rows routed to it (8 rows per MMA pass).
+// gate/up: grid (I/8, nslots + 1); tile = 8 gate rows + 8 up rows, SwiGLU in the epilogue.
+// down:    grid (H/16, nslots + 1).  The last grid.y index is the shared expert (all rows).
+// hbuf / dbuf rows: pair id (row*top_k + k) for routed experts, M*top_k + row for the shared one.
+// ============================================================================================
+template <bool EXACT, bool DOWN>
+__global__ void __launch_bounds__(512) k_expert(ExpertArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, t = lane & 3;
+    const int K = DOWN ? a.I : a.H;
+    const int slot = blockIdx.y;
+    const bool shared = (slot == (int)gridDim.y - 1);
+    if (!shared && slot >= *a.lists.n_active) return;
+    XStage st; float* red; float* fin; int* misc;
+    GemvSmem::carve(smem, min(a.M, 8), K, nw, st, red, fin, misc);
+    const int e = shared ? 0 : a.lists.slot_expert[slot];
+    const int cnt = shared ? a.M : a.lists.slot_cnt[slot];
+    const int off = shared ? 0 : a.lists.slot_off[slot];
+    const int tile = blockIdx.x;
+    const int K8 = K >> 3, KG = K >> 6, slices = K >> 8;
+    const int npair = a.M * a.topk;
+
+    const uint32_t *wA, *wB; const __half *sA, *bA, *sB, *bB;
+    if (DOWN) {
+        const Q4W& q = shared ? a.sh_down : a.down;
+        int64_t row = (int64_t)e * a.H + tile * 16 + r;
+        wA = q.w + row * K8; sA = q.s + row * KG; bA = q.b + row * KG;
+        wB = wA + 8 * (int64_t)K8; sB = sA + 8 * KG; bB = bA + 8 * KG;
+    } else {
+        const Q4W& qg = shared ? a.sh_gate : a.gate;
+        const Q4W& qu = shared ? a.sh_up : a.up;
+        int64_t row = (int64_t)e * a.I + tile * 8 + r;
+        wA = qg.w + row * K8; sA = qg.s + row * KG; bA = qg.b + row * KG;
+        wB = qu.w + row * K8; sB = qu.s + row * KG; bB = qu.b + row * KG;
+    }
+    // K/256 == number of warps here, so each warp keeps its single slice in registers for all rows
+    SliceRegs regs;
+    const bool have = warp < slices;
+    if (have) load_slice(regs, wA, wB, sA, bA, sB, bB, warp, t);
+
+    for (int c0 = 0; c0 < cnt; c0 += 8) {
+        const int mr = min(8, cnt - c0);
+        if (threadIdx.x < 8) {
+            int dst = 0, src = 0;
+            if ((int)threadIdx.x < mr) {
+                if (shared) { dst = npair + c0 + threadIdx.x; src = c0 + threadIdx.x; }
+                else { int pr = a.lists.pairs[off + c0 + threadIdx.x]; dst = pr; src = pr / a.topk; }
+            }
+            misc[threadIdx.x] = DOWN ? dst : src;      // source row of the activations
+            misc[8 + threadIdx.x] = dst;               // destination row
+        }
+        __syncthreads();
+        if (DOWN) stage_gather(st, a.hbuf, a.I, misc, mr, K);
+        else stage_gather(st, a.p, a.H, misc, mr, K);
+        __syncthreads();
+        float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
+        if (have) compute_slice<EXACT>(regs, st, warp, r, t, r < mr, accS, accB);
+        float v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = finish_acc<EXACT>(accS[i], accB[i]);
+        reduce_tile(red, fin, v, nw);
+        if (DOWN) {
+            for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+                int col = i >> 4, row = i & 15;
+                if (col < mr) a.dbuf[(size_t)misc[8 + col] * a.H + tile * 16 + row] = f2h(fin[row * 8 + col]);
+            }
+        } else {
+            if (threadIdx.x < 64) {
+                int col = threadIdx.x >> 3, i = threadIdx.x & 7;
+                if (col < mr) {
+                    __half g = f2h(fin[i * 8 + col]), u = f2h(fin[(i + 8) * 8 + col]);
+                    a.hbuf[(size_t)misc[8 + col] * a.I + tile * 8 + i] = swiglu_h(g, u);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+template <bool EXACT, bool DOWN>
+static void launch_expert_t(const ExpertArgs& a, int nslots, cudaStream_t st) {
+    int K = DOWN ? a.I : a.H;
+    int nw = K / 256;
+    size_t smem = GemvSmem::bytes(a.M < 8 ? a.M : 8, K, nw);
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_expert<EXACT, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); configured = true; }
+    dim3 grid((unsigned)(DOWN ? a.H / 16 : a.I / 8), (unsigned)(nslots + 1));
+    k_expert<EXACT, DOWN><<<grid, nw * 32, smem, st>>>(a);
+    COUNT_LAUNCH();
+}
+void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st) {
+    if (exact) launch_expert_t<true, false>(a, nslots, st); else launch_expert_t<false, false>(a, nslots, st);
+}
+void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st) {
+    if (exact) launch_expert_t<true, true>(a, nslots, st); else launch_expert_t<false, true>(a, nslots, st);
+}
+
+// weighted combine in fp16, ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate
+// logit) * shared (SeedlessFusedVerify.swift:474-484), + residual (SeedlessMetalForward.swift:1024-1028)
+__global__ void __launch_bounds__(256) k_moe_combine(CombineArgs a) {
+    const int m = blockIdx.x;
+    const int npair = a.M * a.topk;
+    const __half s = sigmoid_h(a.sgl[m]);
+    for (int n = threadIdx.x; n < a.H; n += blockDim.x) {
+        __half acc = f2h(0.0f);
+        for (int k = 0; k < a.topk; ++k)
+            acc = hadd_rn(acc, hmul_rn(a.dbuf[(size_t)(m * a.topk + k) * a.H + n], a.scores[m * a.topk + k]));
+        __half res = hadd_rn(acc, hmul_rn(s, a.dbuf[(size_t)(npair + m) * a.H + n]));
+        if (a.h) a.h[(size_t)m * a.H + n] = hadd_rn(a.h[(size_t)m * a.H + n], res);
+        else a.out[(size_t)m * a.H + n] = res;
+    }
+}
+void launch_combine(const CombineArgs& a, cudaStream_t st) {
+    k_moe_combine<<<a.M, 256, 0, st>>>(a);
+    COUNT_LAUNCH();
+}
+
+// ============================================================================================
+// Gated-delta-net core: causal conv1d + SiLU, q/k l2-style norm + scale, beta / decay, the
+// recurrent state update and readout, for all rows of a segment in sequence.
+// (conv: SeedlessFusedVerify.swift:634-663; prep: :839-938; recurrence: GatedDelta.swift:63-124)
+// grid (4 dv-tiles of 32, Hv, nsegs), 128 threads.  The fp32 state tile [32 dv][128 dk] of this
+// CTA lives in registers for the whole call: read once from the current ping-pong side, written
+// once to the other side.  Conv history likewise goes from one side to the other.
+// ============================================================================================
+__global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
+    __shared__ float q_s[128], k_s[128], v_s[32];
+    __shared__ float red_s[8]; __shared__ float gb_s[2];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int dvt = blockIdx.x, hv = blockIdx.y;
+    const SegDesc seg = a.segs[blockIdx.z];
+    const int hk = hv / (a.Hv / a.Hk);
+    const int keyDim = a.Hk * GDN_DK, convDim = 2 * keyDim + a.Hv * GDN_DV;
+    const int side = a.tab.parity[seg.slot];
+    const float* S_in = a.tab.gdn_state + (size_t)seg.slot * a.tab.state_stride_stream + (size_t)side * a.tab.state_stride_side +
+                        (size_t)a.gdn_index * a.tab.state_stride_layer + ((size_t)hv * GDN_DV + dvt * 32) * GDN_DK;
+    float* S_out = a.tab.gdn_state + (size_t)seg.slot * a.tab.state_stride_stream + (size_t)(side ^ 1) * a.tab.state_stride_side +
+                   (size_t)a.gdn_index * a.tab.state_stride_layer + ((size_t)hv * GDN_DV + dvt * 32) * GDN_DK;
+    const __half* hist_in = a.tab.conv_hist + (size_t)seg.slot * a.tab.hist_stride_stream + (size_t)side * a.tab.hist_stride_side +
+                            (size_t)a.gdn_index * a.tab.hist_stride_layer;
+    __half* hist_out = a.tab.conv_hist + (size_t)seg.slot * a.tab.hist_stride_stream + (size_t)(side ^ 1) * a.tab.hist_stride_side +
+                       (size_t)a.gdn_index * a.tab.hist_stride_layer;
+    // state rows of this warp: 8 rows, lane owns dk 4*lane .. 4*lane+3
+    float4 S[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) S[i] = *reinterpret_cast<const float4*>(S_in + (size_t)(warp * 8 + i) * GDN_DK + lane * 4);
+
+    const int ch_q = hk * GDN_DK + tid, ch_k = keyDim + hk * GDN_DK + tid;
+    const int ch_v = 2 * keyDim + hv * GDN_DV + dvt * 32 + (tid & 31);
+    const float4 wq = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_q * 4);
+    const float4 wk = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_k * 4);
+    const float4 wv = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_v * 4);
+    const float invScale = 0.08838834764831845f;             // 128^-0.5
+    const __half qs = f2h(invScale * invScale), ks = f2h(invScale);
+    auto xval = [&](int idx, int ch) -> float {               // row idx of [hist(3) | rows of the segment]
+        return (idx < CONV_K - 1) ? h2f(hist_in[(size_t)idx * convDim + ch])
+                                  : h2f(a.inproj[(size_t)(seg.row0 + idx - (CONV_K - 1)) * a.ld + ch]);
+    };
+    auto conv = [&](int tt, int ch, float4 w) -> float {
+        float acc = 0.f;
+        acc = __fadd_rn(acc, __fmul_rn(xval(tt + 0, ch), w.x));
+        acc = __fadd_rn(acc, __fmul_rn(xval(tt + 1, ch), w.y));
+        acc = __fadd_rn(acc, __fmul_rn(xval(tt + 2, ch), w.z));
+        acc = __fadd_rn(acc, __fmul_rn(xval(tt + 3, ch), w.w));
+        return h2f(f2h(__fmul_rn(acc, sigmoid_f(acc))));
+    };
+    for (int tt = 0; tt < seg.nrows; ++tt) {
+        const int row = seg.row0 + tt;
+        float qc = conv(tt, ch_q, wq), kc = conv(tt, ch_k, wk);
+        if (tid < 32) v_s[tid] = conv(tt, ch_v, wv);
+        float sq = warp_sum(qc * qc), sk = warp_sum(kc * kc);
+        if (lane == 0) { red_s[warp] = sq; red_s[4 + warp] = sk; }
+        if (tid == 0) {
+            __half bh = a.inproj[(size_t)row * a.ld + convDim + a.Hv * GDN_DV + hv];
+            __half ah = a.inproj[(size_t)row * a.ld + convDim + a.Hv * GDN_DV + a.Hv + hv];
+            gb_s[1] = h2f(sigmoid_h(bh));
+            float xa = h2f(ah) + a.dt_bias[hv];
+            float sp = fmaxf(xa, 0.0f) + logf(1.0f + expf(-fabsf(xa)));
+            gb_s[0] = expf(-expf(a.A_log[hv]) * sp);
+        }
+        __syncthreads();
+        float iq = __frsqrt_rn(__fadd_rn(__fdiv_rn(red_s[0] + red_s[1] + red_s[2] + red_s[3], 128.0f), a.eps));
+        float ik = __frsqrt_rn(__fadd_rn(__fdiv_rn(red_s[4] + red_s[5] + red_s[6] + red_s[7], 128.0f), a.eps));
+        q_s[tid] = h2f(hmul_rn(qs, f2h(__fmul_rn(qc, iq))));
+        k_s[tid] = h2f(hmul_rn(ks, f2h(__fmul_rn(kc, ik))));
+        __syncthreads();
+        const float g = gb_s[0], beta = gb_s[1];
+        const float4 kq = *reinterpret_cast<const float4*>(k_s + lane * 4);
+        const float4 qq = *reinterpret_cast<const float4*>(q_s + lane * 4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float4 s = S[i];
+            s.x *= g; s.y *= g; s.z *= g; s.w *= g;
+            float kv = s.x * kq.x + s.y * kq.y + s.z * kq.z + s.w * kq.w;
+            kv = warp_sum(kv);
+            float delta = (v_s[warp * 8 + i] - kv) * beta;
+            s.x = fmaf(kq.x, delta, s.x); s.y = fmaf(kq.y, delta, s.y); s.z = fmaf(kq.z, delta, s.z); s.w = fmaf(kq.w, delta, s.w);
+            float o = s.x * qq.x + s.y * qq.y + s.z * qq.z + s.w * qq.w;
+            o = warp_sum(o);
+            S[i] = s;
+            if (lane == 0) a.y[(size_t)row * (a.Hv * GDN_DV) + hv * GDN_DV + dvt * 32 + warp * 8 + i] = f2h(o);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(S_out + (size_t)(warp * 8 + i) * GDN_DK + lane * 4) = S[i];
+    // new conv history = last three rows of [hist | rows]; q/k channels by one CTA per key head
+    const bool owner_qk = (dvt == 0) && (hv % (a.Hv / a.Hk) == 0);
+    for (int j = 0; j < CONV_K - 1; ++j) {
+        int idx = seg.nrows + j;
+        if (owner_qk) {
+            hist_out[(size_t)j * convDim + ch_q] = f2h(xval(idx, ch_q));
+            hist_out[(size_t)j * convDim + ch_k] = f2h(xval(idx, ch_k));
+        }
+        if (tid < 32) hist_out[(size_t)j * convDim + ch_v] = f2h(xval(idx, ch_v));
+    }
+}
+void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st) {
+    dim3 grid(4, a.Hv, nsegs);
+    k_gdn_core<<<grid, 128, 0, st>>>(a);
+    COUNT_LAUNCH();
+}
+
+// ============================================================================================
+// Attention: q/k RMSNorm + partial NeoX RoPE + KV append; split-KV GQA decode; combine + gate.
+// KV arena: pages [page][attn layer][K|V][kv head][page_size][256] fp16, K stored post-RoPE.
+// (prep: SeedlessFusedVerify.swift:1183-1360; attention: SeedlessMetalForward.swift:4922-4989;
+//  output gate: SeedlessMetalForward.swift:1012-1022)
+// ============================================================================================
+__device__ __forceinline__ int row_position(const AttnArgs& a, int m) {
+    if (a.row_pos_override) return a.row_pos_override[m];
+    const SegDesc seg = a.segs[a.row_seg[m]];
+    return a.tab.kv_len[seg.slot] + a.row_off[m];
+}
+__device__ __forceinline__ __half* kv_ptr(const AttnArgs& a, int slot, int pos, int which, int kvh) {
+    int page = a.tab.page_table[(size_t)slot * a.tab.max_pages + pos / a.page_size];
+    size_t page_elems = (size_t)a.n_attn_layers * 2 * a.KV * a.page_size * ATT_D;
+    return a.kv_pool + (size_t)page * page_elems +
+           ((((size_t)a.attn_index * 2 + which) * a.KV + kvh) * a.page_size + (pos % a.page_size)) * ATT_D;
+}
+// grid (NH + 2*KV, M), 32 threads: one warp per (row, head); lane owns dims 8*lane..8*lane+7
+__global__ void __launch_bounds__(32) k_attn_prep(AttnArgs a) {
+    const int m = blockIdx.y, hidx = blockIdx.x, lane = threadIdx.x;
+    const int slot = a.segs[a.row_seg[m]].slot;
+    const int pos = row_position(a, m);
+    const __half* rowp = a.inproj + (size_t)m * a.ld;
+    if (hidx >= a.NH + a.KV) {                               // V copy
+        int kvh = hidx - a.NH - a.KV;
+        const __half* src = rowp + a.NH * 2 * ATT_D + a.KV * ATT_D + kvh * ATT_D;
+        __half* dst = kv_ptr(a, slot, pos, 1, kvh);
+        reinterpret_cast<uint4*>(dst)[lane] = reinterpret_cast<const uint4*>(src)[lane];
+        return;
+    }
+    const bool isq = hidx < a.NH;
+    const __half* src = isq ? (rowp + (size_t)hidx * 2 * ATT_D) : (rowp + a.NH * 2 * ATT_D + (hidx - a.NH) * ATT_D);
+    const __half* w = isq ? a.q_norm : a.k_norm;
+    uint4 v = reinterpret_cast<const uint4*>(src)[lane];
+    uint4 wv = reinterpret_cast<const uint4*>(w)[lane];
+    const __half* vh = reinterpret_cast<const __half*>(&v);
+    const __half* wh = reinterpret_cast<const __half*>(&wv);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { float f = h2f(vh[i]); ss = fmaf(f, f, ss); }
+    ss = warp_sum(ss);
+    float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), a.eps));
+    float nv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) nv[i] = h2f(hmul_rn(wh[i], f2h(__fmul_rn(h2f(vh[i]), inv))));
+    // rotate dims [0,64): pairs (d, d+32); lanes 0..3 hold d<32, lanes 4..7 hold d+32
+    float other[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, nv[i], 4);
+    uint4 o; __half* oh = reinterpret_cast<__half*>(&o);
+    const float fpos = (float)pos;
+    const float lnb = logf(a.theta);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        int d = lane * 8 + i;
+        if (d >= ROPE_D) { oh[i] = f2h(nv[i]); continue; }
+        int ii = (d < 32) ? d : (d - 32);
+        float freq = expf(-2.0f * (float)ii / (float)ROPE_D * lnb);
+        float ang = fpos * freq;
+        float sn, cs; sincosf(ang, &sn, &cs);
+        float x0 = (d < 32) ? nv[i] : other[i], x1 = (d < 32) ? other[i] : nv[i];
+        oh[i] = f2h((d < 32) ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs));
+    }
+    if (isq) reinterpret_cast<uint4*>(a.qrot + ((size_t)m * a.NH + hidx) * ATT_D)[lane] = o;
+    else reinterpret_cast<uint4*>(kv_ptr(a, slot, pos, 0, hidx - a.NH))[lane] = o;
+}
+void launch_attn_prep(const AttnArgs& a, cudaStream_t st) {
+    dim3 grid(a.NH + 2 * a.KV, a.M);
+    k_attn_prep<<<grid, 32, 0, st>>>(a);
+    COUNT_LAUNCH();
+}
+
+// split-KV decode: grid (nsplit, KV heads, M), 256 threads.  Each warp walks keys of its split
+// (stride 8 warps), lane owns 8 of the 256 dims, the 8 query heads of the kv head share each
+// K/V row.  Online softmax in f32 per warp; warps merged in shared memory; one partial
+// (max, sum, acc[256]) per (row, head, split).  Row m sees positions [0, pos(m)].
+constexpr int ATT_G = 8;     // query heads per kv head handled together (attn_heads / attn_kv_heads must equal it)
+__global__ void __launch_bounds__(256) k_attn_decode(AttnArgs a) {
+    __shared__ float sm_m[8][ATT_G], sm_l[8][ATT_G];
+    __shared__ float sm_o[8][ATT_D];
+    const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = a.segs[a.row_seg[m]].slot;
+    const int N = row_position(a, m) + 1;
+    const int chunk = 32 * ((N + 32 * a.nsplit - 1) / (32 * a.nsplit));
+    const int p0 = split * chunk, p1 = min(N, p0 + chunk);
+    const float scale = 0.0625f;                              // 256^-0.5
+    float q[ATT_G][8];
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g) {
+        uint4 qv = reinterpret_cast<const uint4*>(a.qrot + ((size_t)m * a.NH + kvh * ATT_G + g) * ATT_D)[lane];
+        const __half* qh = reinterpret_cast<const __half*>(&qv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[g][i] = scale * h2f(qh[i]);
+    }
+    float mx[ATT_G], l[ATT_G], acc[ATT_G][8];
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g) { mx[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = 0.f; }
+    for (int pos = p0 + warp; pos < p1; pos += 8) {
+        uint4 kvv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 0, kvh))[lane];
+        uint4 vvv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 1, kvh))[lane];
+        const __half* kh = reinterpret_cast<const __half*>(&kvv);
+        const __half* vh = reinterpret_cast<const __half*>(&vvv);
+        float kf[8], vf[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { kf[i] = h2f(kh[i]); vf[i] = h2f(vh[i]); }
+#pragma unroll
+        for (int g = 0; g < ATT_G; ++g) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s = fmaf(q[g][i], kf[i], s);
+            s = warp_sum(s);
+            float nm = fmaxf(mx[g], s);
+            float factor = __expf(mx[g] - nm), es = __expf(s - nm);
+            mx[g] = nm; l[g] = l[g] * factor + es;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], factor, es * vf[i]);
+        }
+    }
+    // merge the 8 warps, one query head at a time
+    float* po = a.part_o + (((size_t)m * a.NH + kvh * ATT_G) * a.nsplit + split) * ATT_D;
+    float* pml = a.part_ml + (((size_t)m * a.NH + kvh * ATT_G) * a.nsplit + split) * 2;
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g) { if (lane == 0) { sm_m[warp][g] = mx[g]; sm_l[warp][g] = l[g]; } }
+    __syncthreads();
+    for (int g = 0; g < ATT_G; ++g) {
+        float gm = -INFINITY;
+        for (int w = 0; w < 8; ++w) gm = fmaxf(gm, sm_m[w][g]);
+        float f = (mx[g] == -INFINITY) ? 0.f : __expf(mx[g] - gm);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sm_o[warp][lane * 8 + i] = acc[g][i] * f;
+        __syncthreads();
+        {
+            int d = threadIdx.x;                              // 256 threads = 256 dims
+            float o = 0.f;
+            for (int w = 0; w < 8; ++w) o += sm_o[w][d];
+            po[(size_t)g * a.nsplit * ATT_D + d] = o;
+        }
+        if (threadIdx.x == 0) {
+            float ls = 0.f;
+            for (int w = 0; w < 8; ++w) ls += (sm_m[w][g] == -INFINITY) ? 0.f : sm_l[w][g] * __expf(sm_m[w][g] - gm);
+            pml[(size_t)g * a.nsplit * 2 + 0] = gm;
+            pml[(size_t)g * a.nsplit * 2 + 1] = ls;
+        }
+        __syncthreads();
+    }
+}
+void launch_attn_decode(const AttnArgs& a, cudaStream_t st) {
+    dim3 grid(a.nsplit, a.KV, a.M);
+    k_attn_decode<<<grid, 256, 0, st>>>(a);
+    COUNT_LAUNCH();
+}
+// grid (NH, M), 256 threads: merge splits, normalise, round to fp16, multiply by sigmoid(gate) in fp16
+__global__ void __launch_bounds__(256) k_attn_combine(AttnArgs a) {
+    const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
+    const float* po = a.part_o + ((size_t)m * a.NH + h) * a.nsplit * ATT_D;
+    const float* pml = a.part_ml + ((size_t)m * a.NH + h) * a.nsplit * 2;
+    const int N = row_position(a, m) + 1;
+    const int chunk = 32 * ((N + 32 * a.nsplit - 1) / (32 * a.nsplit));
+    const int used = (N + chunk - 1) / chunk;
+    float gm = -INFINITY;
+    for (int s = 0; s < used; ++s) gm = fmaxf(gm, pml[s * 2]);
+    float tot = 0.f, o = 0.f;
+    for (int s = 0; s < used; ++s) {
+        float ms = pml[s * 2];
+        float f = (ms == -INFINITY) ? 0.f : __expf(ms - gm);
+        tot += pml[s * 2 + 1] * f;
+        o += po[(size_t)s * ATT_D + d] * f;
+    }
+    __half out = f2h(tot == 0.f ? o : o / tot);
+    __half gv = a.inproj[(size_t)m * a.ld + (size_t)h * 2 * ATT_D + ATT_D + d];
+    a.gated[((size_t)m * a.NH + h) * ATT_D + d] = hmul_rn(out, sigmoid_h(gv));
+}
+void launch_attn_combine(const AttnArgs& a, cudaStream_t st) {
+    dim3 grid(a.NH, a.M);
+    k_attn_combine<<<grid, 256, 0, st>>>(a);
+    COUNT_LAUNCH();
+}
+
+// ============================================================================================
+// End of a step: advance cache lengths, flip GDN ping-pong sides, feed greedy tokens back as
+// the next step's input and append them to the device-side history (chained steps).
+// ============================================================================================
+__global__ void k_step_end(StepEndArgs a) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < a.nsegs) {
+        SegDesc s = a.segs[i];
+        a.tab.kv_len[s.slot] += s.nrows;
+        a.tab.parity[s.slot] ^= 1;
+    }
+    if (a.out_tok && i < a.M) {
+        int tk = a.out_tok[i];
+        if (a.tok_in) a.tok_in[i] = tk;
+        if (a.hist) a.hist[(*a.hist_pos + i) % a.hist_cap] = tk;
+    }
+    __syncthreads();
+    if (a.hist && a.out_tok && i == 0) *a.hist_pos = (*a.hist_pos + a.M) % a.hist_cap;
+}
+void launch_step_end(const StepEndArgs& a, cudaStream_t st) {
+    int n = a.nsegs > a.M ? a.nsegs : a.M;
+    if (n > 1024) n = 1024;      // one block: history position is updated after every thread has used it
+    k_step_end<<<1, n < 32 ? 32 : n, 0, st>>>(a);
+    COUNT_LAUNCH();
+}
+
+}  // namespace sl

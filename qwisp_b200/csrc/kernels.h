@@ -1,0 +1,118 @@
+// kernels.h -- argument blocks and host launchers of the Seedless B200 kernels.
+#pragma once
+#include "common.cuh"
+
+namespace sl {
+
+struct Q4W { const uint32_t* w = nullptr; const __half* s = nullptr; const __half* b = nullptr; int64_t N = 0; int K = 0; };
+
+struct DenseArgs {
+    const uint32_t* w; const __half* s; const __half* b;        // rows A (and B = A + 8)
+    const uint32_t* w2; const __half* s2; const __half* b2;     // rows B when the epilogue pairs gate/up
+    int N, K, M;
+    const __half* x; int ldx;                                    // activations (plain) / residual stream (rmsnorm) / y (normgate)
+    const __half* nw;                                            // norm weight
+    const __half* z; int ldz;                                    // gate input of the gated norm
+    float eps;
+    __half* y; int ldy;                                          // output rows
+    __half* logits;                                              // optional [M][N] (argmax epilogue)
+    float* pval; int* pidx; int* out_tok; unsigned* counter;     // argmax partials / result / ticket
+};
+
+struct MoeLists {
+    int* n_active;       // [1]
+    int* slot_expert;    // [E]
+    int* slot_off;       // [E]
+    int* slot_cnt;       // [E]
+    int* pairs;          // [M*top_k] pair ids (row*top_k + k) grouped by expert slot
+};
+
+struct RouterArgs {
+    const __half* h; int ldh;            // input rows
+    const __half* norm_w; float eps;     // post-attention norm (nullptr: rows are already normed)
+    const __half* router;                // fp16 [E][H]
+    const __half* shared_gate;           // fp16 [H]
+    int M, H, E;
+    __half* p;                           // normed rows out [M][H]
+    __half* logits;                      // [M][E]
+    __half* sgl;                         // [M] shared-expert gate logit
+};
+
+struct RouteArgs {
+    const __half* logits; int M, E, topk;
+    int* inds; __half* scores;           // [M][topk]
+    MoeLists lists; unsigned* counter;
+};
+
+struct ExpertArgs {
+    Q4W gate, up, down;                  // expert slabs: row (e*I + i) / (e*H + n)
+    Q4W sh_gate, sh_up, sh_down;
+    MoeLists lists;
+    const __half* p;                     // [M][H] normed rows
+    __half* hbuf;                        // [(M*topk + M)][I]
+    __half* dbuf;                        // [(M*topk + M)][H]
+    int M, H, I, topk;
+};
+
+struct CombineArgs {
+    const __half* dbuf; const __half* scores; const __half* sgl;
+    __half* h;                           // residual stream (in place) or nullptr
+    __half* out;                         // plain output when h == nullptr
+    int M, H, topk;
+};
+
+struct GdnArgs {
+    const __half* inproj; int ld;        // [M][ld]: qkv | z | b | a
+    const float* conv_w; const float* A_log; const float* dt_bias;
+    int Hk, Hv; float eps;
+    StreamTable tab; int gdn_index;      // which GDN layer (index among GDN layers)
+    const SegDesc* segs;
+    __half* y;                           // [M][Hv*128]
+};
+
+struct AttnArgs {
+    const __half* inproj; int ld;        // [M][ld]: q(+gate) | k | v
+    const __half* q_norm; const __half* k_norm;
+    int NH, KV; float eps, theta;
+    StreamTable tab; int attn_index;     // index among attention layers
+    int n_attn_layers, page_size;
+    __half* kv_pool;
+    const SegDesc* segs; const int* row_seg; const int* row_off;   // per row: segment, offset inside it
+    const int* row_pos_override;         // optional explicit positions (operator tests) or nullptr
+    __half* qrot;                        // [M][NH][256]
+    float* part_o; float* part_ml;       // split partials
+    int nsplit;
+    __half* gated;                       // [M][NH*256]
+    int M;
+};
+
+struct StepEndArgs {
+    StreamTable tab; const SegDesc* segs; int nsegs;
+    const int* out_tok; int* tok_in; int* hist; int* hist_pos; int hist_cap; int M;
+};
+
+void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl);
+void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st);
+void launch_router(const RouterArgs& a, cudaStream_t st);
+void launch_route(const RouteArgs& a, cudaStream_t st);
+void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st);
+void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st);
+void launch_combine(const CombineArgs& a, cudaStream_t st);
+void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st);
+void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
+void launch_attn_decode(const AttnArgs& a, cudaStream_t st);
+void launch_attn_combine(const AttnArgs& a, cudaStream_t st);
+void launch_step_end(const StepEndArgs& a, cudaStream_t st);
+void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st);
+int64_t kernel_launch_count();
+size_t dense_smem_bytes(int M, int K);
+
+// synthetic data + quantiser (synth.cu)
+uint64_t tensor_seed(uint64_t base_seed, const char* name);
+void launch_synth_f16(uint64_t tseed, int64_t n, float mean, float std, __half* out, cudaStream_t st);
+void launch_synth_f32(uint64_t tseed, int64_t n, float mean, float std, float* out, cudaStream_t st);
+void launch_synth_q4(uint64_t tseed, int64_t N, int64_t K, float std, uint32_t* packed, __half* s, __half* b, cudaStream_t st);
+void launch_quantize_q4(const __half* w, int64_t N, int64_t K, uint32_t* packed, __half* s, __half* b, cudaStream_t st);
+void host_synth_tokens(uint64_t tseed, int64_t n, int32_t vocab, int32_t* out);
+
+}  // namespace sl

@@ -1,0 +1,329 @@
+"""Host-side mirror of the reference's engine interface over the C ABI.
+
+`SpecBackend` carries the same members as the closure struct Tell drives
+(swift/Sources/QwispCore/TellRuntime.swift:83-111): forward, stepArgmax, chainedStepArgmax,
+stepLogitsRows, snapshot / rollback, fullSnapshot / fullRestore, persistentState /
+restorePersistentState, gpuFault.  Failures follow the reference's convention: the call
+returns None and `gpu_fault()` turns non-None (SeedlessFusedVerify.swift:388-416).
+`LaneBatchSlots` mirrors `protocol BatchSlots` (ContinuousBatch.swift:38-66) the way
+`LaneBatchSlots` implements it (LaneServe.swift:296-494): resumable chunked prefill per
+slot, one batched greedy step over the active slots, release.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import SeedlessError, SlSnap, SlWeightDesc, lib
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+class Engine:
+    """Weights + scratch + KV arena on one GPU (SeedlessEngine.build + makeFused)."""
+
+    def __init__(self, cfg, handle):
+        self.cfg = cfg
+        self._h = handle
+
+    @classmethod
+    def synthetic(cls, cfg, seed=0, norm_jitter=0.0, conv_std=0.02):
+        h = C.c_void_p()
+        spec = _lib.synth_spec(seed, norm_jitter, conv_std)
+        rc = lib().sl_engine_create_synthetic(C.byref(cfg), C.byref(spec), C.byref(h))
+        if rc != 0:
+            raise SeedlessError(rc, "sl_engine_create_synthetic")
+        return cls(cfg, h)
+
+    @classmethod
+    def from_tensors(cls, cfg, tensors):
+        """tensors: dict name -> contiguous numpy array in the MLX layout named in the header."""
+        keep = [np.ascontiguousarray(v) for v in tensors.values()]
+        descs = (SlWeightDesc * len(keep))()
+        for i, (name, arr) in enumerate(zip(tensors.keys(), keep)):
+            descs[i] = SlWeightDesc(name.encode(), arr.ctypes.data, arr.nbytes, 0)
+        h = C.c_void_p()
+        rc = lib().sl_engine_create(C.byref(cfg), descs, len(keep), C.byref(h))
+        if rc != 0:
+            raise SeedlessError(rc, "sl_engine_create")
+        return cls(cfg, h)
+
+    def close(self):
+        if self._h:
+            lib().sl_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc, where):
+        if rc != 0:
+            raise SeedlessError(rc, where, self.gpu_fault())
+
+    def gpu_fault(self):
+        f = lib().sl_last_fault(self._h)
+        return f.decode() if f else None
+
+    def inject_fault(self, on=True):
+        lib().sl_inject_fault(self._h, 1 if on else 0)
+
+    def set_cuda_stream(self, cuda_stream_handle):
+        self._check(lib().sl_engine_set_cuda_stream(self._h, C.c_void_p(cuda_stream_handle)), "sl_engine_set_cuda_stream")
+
+    def launch_count(self):
+        return lib().sl_engine_launch_count(self._h)
+
+    def tensor_bytes(self, name):
+        n = C.c_uint64()
+        self._check(lib().sl_engine_tensor_bytes(self._h, name.encode(), C.byref(n)), "sl_engine_tensor_bytes")
+        return n.value
+
+    def read_tensor(self, name):
+        n = self.tensor_bytes(name)
+        buf = np.empty(n, dtype=np.uint8)
+        self._check(lib().sl_engine_read_tensor(self._h, name.encode(), _ptr(buf), n), "sl_engine_read_tensor")
+        return buf
+
+    def stream(self, max_seq_len):
+        h = C.c_void_p()
+        self._check(lib().sl_stream_create(self._h, max_seq_len, C.byref(h)), "sl_stream_create")
+        return Stream(self, h, max_seq_len)
+
+    def batch_step_argmax(self, streams, tokens):
+        B = len(streams)
+        arr = (C.c_void_p * B)(*[s._h for s in streams])
+        toks = _i32(tokens)
+        out = np.empty(B, dtype=np.int32)
+        self._check(lib().sl_batch_step_argmax(self._h, arr, _ptr(toks), B, _ptr(out)), "sl_batch_step_argmax")
+        return out
+
+
+class Stream:
+    """One sequence's caches: KV page table + GDN state."""
+
+    def __init__(self, engine, handle, max_seq_len):
+        self.engine = engine
+        self._h = handle
+        self.max_seq_len = max_seq_len
+
+    def close(self):
+        if self._h and self.engine._h:
+            lib().sl_stream_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def length(self):
+        return lib().sl_stream_len(self._h)
+
+    def reset(self):
+        self.engine._check(lib().sl_stream_reset(self._h), "sl_stream_reset")
+
+    def forward(self, tokens, want_hidden=True):
+        toks = _i32(tokens)
+        out = np.empty((len(toks), self.engine.cfg.hidden), dtype=np.float16) if want_hidden else None
+        self.engine._check(lib().sl_forward(self._h, _ptr(toks), len(toks), _ptr(out)), "sl_forward")
+        return out
+
+    def step_argmax(self, tokens):
+        toks = _i32(tokens)
+        out = np.empty(len(toks), dtype=np.int32)
+        self.engine._check(lib().sl_step_argmax(self._h, _ptr(toks), len(toks), _ptr(out)), "sl_step_argmax")
+        return out
+
+    def chained_step_argmax(self, first, K):
+        out = np.empty(K, dtype=np.int32)
+        self.engine._check(lib().sl_chained_step_argmax(self._h, int(first), K, _ptr(out)), "sl_chained_step_argmax")
+        return out
+
+    def chained_enqueue(self, first, K):
+        self.engine._check(lib().sl_chained_enqueue(self._h, int(first), K), "sl_chained_enqueue")
+
+    def chained_collect(self, K):
+        out = np.empty(K, dtype=np.int32)
+        self.engine._check(lib().sl_chained_collect(self._h, K, _ptr(out)), "sl_chained_collect")
+        return out
+
+    def step_logits(self, tokens):
+        toks = _i32(tokens)
+        out = np.empty((len(toks), self.engine.cfg.vocab), dtype=np.float16)
+        self.engine._check(lib().sl_step_logits(self._h, _ptr(toks), len(toks), _ptr(out)), "sl_step_logits")
+        return out
+
+    def snapshot(self):
+        s = SlSnap()
+        self.engine._check(lib().sl_snapshot(self._h, C.byref(s)), "sl_snapshot")
+        return s
+
+    def rollback(self, snap):
+        self.engine._check(lib().sl_rollback_one_step(self._h, C.byref(snap)), "sl_rollback_one_step")
+
+    def full_snapshot(self):
+        h = C.c_void_p()
+        self.engine._check(lib().sl_full_snapshot(self._h, C.byref(h)), "sl_full_snapshot")
+        return FullSnapshot(h)
+
+    def full_restore(self, snap):
+        self.engine._check(lib().sl_full_restore(self._h, snap._h), "sl_full_restore")
+
+    def state_save(self):
+        n = C.c_uint64()
+        self.engine._check(lib().sl_state_size(self._h, C.byref(n)), "sl_state_size")
+        buf = np.empty(n.value, dtype=np.uint8)
+        self.engine._check(lib().sl_state_save(self._h, _ptr(buf), n.value), "sl_state_save")
+        return buf
+
+    def state_restore(self, blob):
+        """False on a malformed / mismatching blob: the caller must reset and cold-prefill."""
+        blob = np.ascontiguousarray(blob, dtype=np.uint8)
+        rc = lib().sl_state_restore(self._h, _ptr(blob), len(blob))
+        if rc == _lib.SL_ERR_FORMAT:
+            return False
+        self.engine._check(rc, "sl_state_restore")
+        return True
+
+
+class FullSnapshot:
+    def __init__(self, handle):
+        self._h = handle
+
+    def __del__(self):
+        try:
+            if self._h:
+                lib().sl_fullsnap_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+class SpecBackend:
+    """The closure set Tell's speculative loop drives, bound to one stream."""
+
+    def __init__(self, stream, hybrid_chunk=64):
+        self.stream = stream
+        self.hybrid_chunk = min(hybrid_chunk, stream.engine.cfg.max_rows)
+
+    def _guard(self, fn, *a):
+        try:
+            return fn(*a)
+        except SeedlessError:
+            return None
+
+    def forward(self, tokens):
+        return self._guard(self.stream.forward, tokens)
+
+    forward_hybrid = forward
+
+    def step_argmax(self, tokens):
+        r = self._guard(self.stream.step_argmax, tokens)
+        return None if r is None else [int(t) for t in r]
+
+    def chained_step_argmax(self, first, K):
+        r = self._guard(self.stream.chained_step_argmax, first, K)
+        return None if r is None else [int(t) for t in r]
+
+    def step_logits_rows(self, tokens):
+        return self._guard(self.stream.step_logits, tokens)
+
+    def snapshot(self):
+        return self.stream.snapshot()
+
+    def rollback(self, snap):
+        self._guard(self.stream.rollback, snap)
+
+    def full_snapshot(self):
+        return self._guard(self.stream.full_snapshot)
+
+    def full_restore(self, snap):
+        self._guard(self.stream.full_restore, snap)
+
+    def persistent_state(self):
+        return self._guard(self.stream.state_save)
+
+    def restore_persistent_state(self, blob):
+        r = self._guard(self.stream.state_restore, blob)
+        return bool(r)
+
+    def gpu_fault(self):
+        return self.stream.engine.gpu_fault()
+
+
+class LaneBatchSlots:
+    """BatchSlots over engine streams: resumable chunked prefill + batched greedy step."""
+
+    def __init__(self, engine, slot_count, chunk=None, default_seq_budget=4096):
+        self.engine = engine
+        self.slot_count = slot_count
+        self.chunk = chunk or engine.cfg.max_rows
+        self.default_seq_budget = default_seq_budget
+        self._streams = [None] * slot_count
+        self._resume = [0] * slot_count
+
+    def can_admit(self, prompt_len, seq_budget):
+        need = -(-max(seq_budget, prompt_len + 1) // self.engine.cfg.kv_page_size)
+        used = sum(-(-s.max_seq_len // self.engine.cfg.kv_page_size) for s in self._streams if s is not None)
+        return used + need <= self.engine.cfg.kv_pages
+
+    def admit_step(self, prompt, slot, token_budget, seq_budget=0):
+        """-> ("prefilling", consumed) | ("done", first_token, consumed) | ("failed",)"""
+        try:
+            if self._streams[slot] is None:
+                self._streams[slot] = self.engine.stream(seq_budget or self.default_seq_budget)
+                self._resume[slot] = 0
+            st = self._streams[slot]
+            pos = self._resume[slot]
+            consumed = 0
+            first = True
+            while pos < len(prompt):
+                n = min(self.chunk, len(prompt) - pos)
+                if not first and consumed + n > token_budget:
+                    break                                        # forward progress: at least one whole chunk per call
+                last = (pos + n == len(prompt))
+                if last:
+                    tok = int(st.step_argmax(prompt[pos:pos + n])[-1])
+                else:
+                    st.forward(prompt[pos:pos + n], want_hidden=False)
+                pos += n
+                consumed += n
+                first = False
+                if last:
+                    self._resume[slot] = pos
+                    return ("done", tok, consumed)
+            self._resume[slot] = pos
+            return ("prefilling", consumed)
+        except SeedlessError:
+            return ("failed",)
+
+    def admit(self, prompt, slot):
+        r = self.admit_step(prompt, slot, token_budget=1 << 30)
+        return r[1] if r[0] == "done" else None
+
+    def step(self, last):
+        active = [b for b, t in enumerate(last) if t is not None]
+        out = [None] * len(last)
+        if not active:
+            return out
+        toks = self.engine.batch_step_argmax([self._streams[b] for b in active], [last[b] for b in active])
+        for b, t in zip(active, toks):
+            out[b] = int(t)
+        return out
+
+    def release(self, slot):
+        if self._streams[slot] is not None:
+            self._streams[slot].close()
+            self._streams[slot] = None
+        self._resume[slot] = 0

@@ -1,0 +1,81 @@
+"""Single operators over the C ABI -- the counterparts of the reference's per-op wrappers
+its kernel tests call (SeedlessMetalForward.qmm, routeTop8Rows, moeBlockRows, gdnLayerRows,
+attnLayerRows: swift/Sources/QwispCore/SeedlessMetalForward.swift:222,
+SeedlessVerifyForward.swift:37-248)."""
+import ctypes as C
+
+import numpy as np
+
+from ._lib import SeedlessError, lib
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def qmm4(x, packed, scales, biases):
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    packed = np.ascontiguousarray(packed, dtype=np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.float16)
+    biases = np.ascontiguousarray(biases, dtype=np.float16)
+    M, K = x.shape
+    N = packed.shape[0]
+    y = np.empty((M, N), dtype=np.float16)
+    rc = lib().sl_op_qmm4(_p(x), _p(packed), _p(scales), _p(biases), M, K, N, _p(y))
+    if rc != 0:
+        raise SeedlessError(rc, "sl_op_qmm4")
+    return y
+
+
+def quantize_q4(w):
+    w = np.ascontiguousarray(w, dtype=np.float16)
+    N, K = w.shape
+    packed = np.empty((N, K // 8), dtype=np.uint32)
+    s = np.empty((N, K // 64), dtype=np.float16)
+    b = np.empty((N, K // 64), dtype=np.float16)
+    rc = lib().sl_op_quantize_q4(_p(w), N, K, _p(packed), _p(s), _p(b))
+    if rc != 0:
+        raise SeedlessError(rc, "sl_op_quantize_q4")
+    return packed, s, b
+
+
+def moe_block(engine, layer, x):
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    M = x.shape[0]
+    out = np.empty_like(x)
+    inds = np.empty((M, engine.cfg.top_k), dtype=np.int32)
+    scores = np.empty((M, engine.cfg.top_k), dtype=np.float16)
+    engine._check(lib().sl_op_moe_block(engine._h, layer, _p(x), M, _p(out), _p(inds), _p(scores)), "sl_op_moe_block")
+    return out, inds, scores
+
+
+def mixer(stream, layer, x, pos0):
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    out = np.empty_like(x)
+    stream.engine._check(lib().sl_op_mixer(stream._h, layer, _p(x), x.shape[0], pos0, _p(out)), "sl_op_mixer")
+    return out
+
+
+def lm_head(engine, normed, want_logits=True):
+    normed = np.ascontiguousarray(normed, dtype=np.float16)
+    M = normed.shape[0]
+    logits = np.empty((M, engine.cfg.vocab), dtype=np.float16) if want_logits else None
+    toks = np.empty(M, dtype=np.int32)
+    engine._check(lib().sl_op_lm_head(engine._h, _p(normed), M, _p(logits), _p(toks)), "sl_op_lm_head")
+    return logits, toks
+
+
+def synth_tokens(seed, name, n, vocab):
+    out = np.empty(n, dtype=np.int32)
+    rc = lib().sl_synth_tokens(seed, name.encode(), n, vocab, _p(out))
+    if rc != 0:
+        raise SeedlessError(rc, "sl_synth_tokens")
+    return out
+
+
+def synth_f16(seed, name, n, mean=0.0, std=1.0):
+    out = np.empty(n, dtype=np.float16)
+    rc = lib().sl_synth_f16(seed, name.encode(), n, mean, std, _p(out))
+    if rc != 0:
+        raise SeedlessError(rc, "sl_synth_f16")
+    return out

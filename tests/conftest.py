@@ -1,0 +1,91 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def has_gpu():
+    try:
+        import ctypes
+        cuda = ctypes.CDLL("libcuda.so.1")
+        n = ctypes.c_int(0)
+        return cuda.cuInit(0) == 0 and cuda.cuDeviceGetCount(ctypes.byref(n)) == 0 and n.value > 0
+    except OSError:
+        return False
+
+
+def pytest_collection_modifyitems(config, items):
+    if has_gpu():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+# ---- geometries ----
+# "mini": the reference's own multi-layer test geometry (real head / hidden dims, E=16,
+# one GDN + one attention layer, small vocabulary): SeedlessVerifyTests.swift:1071-1132.
+MINI = dict(hidden=2048, n_layers=2, attn_every=2, vocab=1024, n_experts=16, top_k=8, moe_inter=512,
+            gdn_k_heads=16, gdn_v_heads=32, attn_heads=16, attn_kv_heads=2)
+# "tiny": narrow dims so the CPU oracle is quick on multi-step tests
+TINY = dict(hidden=512, n_layers=4, attn_every=2, vocab=512, n_experts=16, top_k=4, moe_inter=512,
+            gdn_k_heads=8, gdn_v_heads=16, attn_heads=8, attn_kv_heads=1)
+SEED = 1
+JITTER = 0.1
+CONV_STD = 0.5
+
+
+def oracle_model(geom, seed=SEED):
+    from oracle import oracle as O
+    cfg = O.config(norm_jitter=JITTER, conv_std=CONV_STD, **geom)
+    return O.Model(cfg, seed)
+
+
+def gpu_engine(geom, seed=SEED, **kw):
+    import qwisp_b200 as Q
+    args = dict(max_rows=64, max_streams=8, kv_page_size=32, kv_pages=64)
+    args.update(kw)
+    cfg = Q.config(**geom, **args)
+    return Q.Engine.synthetic(cfg, seed=seed, norm_jitter=JITTER, conv_std=CONV_STD)
+
+
+@pytest.fixture(scope="session")
+def mini_oracle():
+    return oracle_model(MINI)
+
+
+@pytest.fixture(scope="session")
+def tiny_oracle():
+    return oracle_model(TINY)
+
+
+@pytest.fixture(scope="session")
+def mini_engine():
+    e = gpu_engine(MINI)
+    yield e
+    e.close()
+
+
+@pytest.fixture(scope="session")
+def tiny_engine():
+    e = gpu_engine(TINY)
+    yield e
+    e.close()
+
+
+def f16_report(got, ref):
+    g = np.asarray(got, dtype=np.float64)
+    r = np.asarray(ref, dtype=np.float64)
+    d = np.abs(g - r)
+    return dict(max_abs=float(d.max()), mean_abs=float(d.mean()), ref_max=float(np.abs(r).max()),
+                exact_frac=float((np.asarray(got) == np.asarray(ref)).mean()))

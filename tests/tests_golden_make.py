@@ -1,0 +1,8 @@
+"""Import shim so tests can call tests/golden/make_golden.py:compute()."""
+import importlib.util
+import os
+
+_spec = importlib.util.spec_from_file_location("make_golden", os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "make_golden.py"))
+_mod = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(_mod)
+compute = _mod.compute
