@@ -105,8 +105,16 @@ const char* sl_last_fault(sl_engine* e);
 /* Host-side test hook: the next device-touching call reports failure and poisons the engine
  * (mirrors `injectCBFailure`, SeedlessFusedVerify.swift:403-404).  Never faults the GPU. */
 int32_t sl_inject_fault(sl_engine* e, int32_t on);
-/* Kernels this engine has launched so far (bench bookkeeping). */
+/* Kernels this library has launched so far (bench bookkeeping). */
 int64_t sl_engine_launch_count(sl_engine* e);
+/* Replay decode steps as CUDA graphs (default on) or launch every kernel eagerly. */
+int32_t sl_engine_use_graphs(sl_engine* e, int32_t on);
+/* Per-kernel timing with CUDA events on the launching stream, for eager launches only (the
+ * reference's profiled forward splits its command buffer per stage for the same purpose,
+ * SeedlessFusedVerify.swift:4352-4378).  The report has one line per kernel:
+ * "name launches total_ms algorithmic_bytes". */
+int32_t sl_profile_start(sl_engine* e);
+int32_t sl_profile_report(sl_engine* e, char* buf, uint64_t cap);
 
 /* ---- stream = one sequence's caches: KV page table + GDN state ("backend instance" /
  *      "lane", SeedlessFusedVerify.swift:3368-3452, LaneServe.swift:256) ---- */

@@ -44,6 +44,8 @@ def lib():
         L.orc_tensor_seed.argtypes = [C.c_uint64, C.c_char_p]
         L.orc_model_create.restype = C.c_void_p
         L.orc_model_create.argtypes = [C.POINTER(OrcConfig), C.c_uint64]
+        L.orc_model_create_lazy.restype = C.c_void_p
+        L.orc_model_create_lazy.argtypes = [C.POINTER(OrcConfig), C.c_uint64]
         L.orc_model_destroy.argtypes = [C.c_void_p]
         L.orc_model_tensor.argtypes = [C.c_void_p, C.c_char_p, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64)]
         L.orc_model_tensor_count.argtypes = [C.c_void_p]
@@ -150,10 +152,11 @@ def route_topk(logits, topk=8):
 class Model:
     """Synthetic model generated from (config, seed); tensors are readable by name."""
 
-    def __init__(self, cfg: OrcConfig, seed: int):
+    def __init__(self, cfg: OrcConfig, seed: int, lazy_experts: bool = False):
         self.cfg = cfg
         self.seed = seed
-        self.h = lib().orc_model_create(C.byref(cfg), C.c_uint64(seed))
+        make = lib().orc_model_create_lazy if lazy_experts else lib().orc_model_create
+        self.h = make(C.byref(cfg), C.c_uint64(seed))
 
     def close(self):
         if self.h:

@@ -162,10 +162,10 @@ extern "C" void orc_quantize_q4(const h16* w, int64_t N, int64_t K, uint32_t* pa
             quantize_group(w + n * K + g * 64, packed + n * (K / 8) + g * 8, scales + n * G + g, biases + n * G + g);
 }
 // generate fp16 ~N(0,std) from the tensor seed and quantise, without materialising w
-static void synth_quantized(uint64_t tseed, int64_t N, int64_t K, float std, uint32_t* packed, h16* scales, h16* biases) {
+static void synth_quantized_rows(uint64_t tseed, int64_t row0, int64_t N, int64_t K, float std, uint32_t* packed, h16* scales, h16* biases) {
     int64_t G = K / 64;
 #pragma omp parallel for schedule(static)
-    for (int64_t n = 0; n < N; ++n) {
+    for (int64_t n = row0; n < row0 + N; ++n) {
         h16 buf[64];
         for (int64_t g = 0; g < G; ++g) {
             uint64_t base = (uint64_t)(n * K + g * 64);
@@ -173,6 +173,9 @@ static void synth_quantized(uint64_t tseed, int64_t N, int64_t K, float std, uin
             quantize_group(buf, packed + n * (K / 8) + g * 8, scales + n * G + g, biases + n * G + g);
         }
     }
+}
+static void synth_quantized(uint64_t tseed, int64_t N, int64_t K, float std, uint32_t* packed, h16* scales, h16* biases) {
+    synth_quantized_rows(tseed, 0, N, K, std, packed, scales, biases);
 }
 extern "C" void orc_synth_q4(uint64_t tseed, int64_t N, int64_t K, float std, uint32_t* packed, h16* scales, h16* biases) {
     synth_quantized(tseed, N, K, std, packed, scales, biases);
@@ -328,10 +331,14 @@ struct OrcConfig {
 };
 static const int DK = 128, DV = 128, CONVK = 4, HD = 256, ROPE = 64;
 
-struct Q4 { std::vector<uint32_t> w; std::vector<h16> s, b; int64_t N = 0, K = 0;
-    const uint32_t* row_w(int64_t n) const { return w.data() + n * (K / 8); }
-    const h16* row_s(int64_t n) const { return s.data() + n * (K / 64); }
-    const h16* row_b(int64_t n) const { return b.data() + n * (K / 64); } };
+// storage comes from calloc so that rows which are never generated (lazy experts) cost no memory
+struct Q4 { uint32_t* w = nullptr; h16 *s = nullptr, *b = nullptr; int64_t N = 0, K = 0; uint64_t tseed = 0;
+    void alloc(int64_t n, int64_t k) { N = n; K = k; w = (uint32_t*)calloc((size_t)(n * k / 8), 4); s = (h16*)calloc((size_t)(n * k / 64), 2); b = (h16*)calloc((size_t)(n * k / 64), 2); }
+    ~Q4() { free(w); free(s); free(b); }
+    Q4() = default; Q4(const Q4&) = delete; Q4& operator=(const Q4&) = delete;
+    const uint32_t* row_w(int64_t n) const { return w + n * (K / 8); }
+    const h16* row_s(int64_t n) const { return s + n * (K / 64); }
+    const h16* row_b(int64_t n) const { return b + n * (K / 64); } };
 
 struct Layer {
     bool is_attn;
@@ -347,9 +354,11 @@ struct Layer {
     std::vector<h16> router, shared_gate;
     Q4 gate_proj, up_proj, down_proj;             // [E*I,H], [E*I,H], [E*H,I]
     Q4 sh_gate, sh_up, sh_down;
+    std::vector<uint8_t> expert_ready;            // lazy models: experts generated on first use
+    Layer() = default; Layer(const Layer&) = delete; Layer& operator=(const Layer&) = delete;
 };
 struct Model {
-    OrcConfig c; uint64_t seed;
+    OrcConfig c; uint64_t seed; bool lazy = false;
     std::vector<h16> embed, final_norm; Q4 lm_head;
     std::vector<Layer> layers;
     std::map<std::string, std::pair<const void*, size_t>> index;
@@ -361,12 +370,20 @@ struct LayerState {
 };
 struct Stream { Model* m; int cap; int len; std::vector<LayerState> L; };
 
-static void make_q4(Model* M, Q4& q, const std::string& name, int64_t N, int64_t K) {
-    q.N = N; q.K = K; q.w.resize(N * K / 8); q.s.resize(N * K / 64); q.b.resize(N * K / 64);
-    synth_quantized(tensor_seed(M->seed, name.c_str()), N, K, 0.02f, q.w.data(), q.s.data(), q.b.data());
-    M->index[name + ".w"] = {q.w.data(), q.w.size() * 4};
-    M->index[name + ".s"] = {q.s.data(), q.s.size() * 2};
-    M->index[name + ".b"] = {q.b.data(), q.b.size() * 2};
+static void make_q4(Model* M, Q4& q, const std::string& name, int64_t N, int64_t K, bool defer = false) {
+    q.alloc(N, K); q.tseed = tensor_seed(M->seed, name.c_str());
+    if (!defer) synth_quantized(q.tseed, N, K, 0.02f, q.w, q.s, q.b);
+    M->index[name + ".w"] = {q.w, (size_t)(N * K / 8) * 4};
+    M->index[name + ".s"] = {q.s, (size_t)(N * K / 64) * 2};
+    M->index[name + ".b"] = {q.b, (size_t)(N * K / 64) * 2};
+}
+static void ensure_expert(const Model* M, Layer& L, int e) {
+    if (!M->lazy || L.expert_ready[e]) return;
+    int64_t I = M->c.moe_inter, H = M->c.hidden;
+    synth_quantized_rows(L.gate_proj.tseed, (int64_t)e * I, I, H, 0.02f, L.gate_proj.w, L.gate_proj.s, L.gate_proj.b);
+    synth_quantized_rows(L.up_proj.tseed, (int64_t)e * I, I, H, 0.02f, L.up_proj.w, L.up_proj.s, L.up_proj.b);
+    synth_quantized_rows(L.down_proj.tseed, (int64_t)e * H, H, I, 0.02f, L.down_proj.w, L.down_proj.s, L.down_proj.b);
+    L.expert_ready[e] = 1;
 }
 static void make_f16(Model* M, std::vector<h16>& v, const std::string& name, int64_t n, float mean, float std) {
     v.resize(n); orc_synth_f16(tensor_seed(M->seed, name.c_str()), n, mean, std, v.data());
@@ -377,17 +394,18 @@ static void make_f32(Model* M, std::vector<float>& v, const std::string& name, i
     M->index[name] = {v.data(), v.size() * 4};
 }
 
-extern "C" void* orc_model_create(const OrcConfig* cfg, uint64_t seed) {
-    Model* M = new Model(); M->c = *cfg; M->seed = seed;
+static void* model_create(const OrcConfig* cfg, uint64_t seed, bool lazy) {
+    Model* M = new Model(); M->c = *cfg; M->seed = seed; M->lazy = lazy;
     const OrcConfig& c = M->c;
     int H = c.hidden, E = c.n_experts, I = c.moe_inter;
     int keyDim = c.gdn_k_heads * DK, valDim = c.gdn_v_heads * DV, convDim = 2 * keyDim + valDim;
     make_f16(M, M->embed, "embed", (int64_t)c.vocab * H, 0.0f, 0.02f);
     make_f16(M, M->final_norm, "final_norm", H, 1.0f, c.norm_jitter);
     make_q4(M, M->lm_head, "lm_head", c.vocab, H);
-    M->layers.resize(c.n_layers);
+    M->layers = std::vector<Layer>(c.n_layers);
     for (int i = 0; i < c.n_layers; ++i) {
         Layer& L = M->layers[i];
+        L.expert_ready.assign(E, 0);
         std::string p = "L" + std::to_string(i) + ".";
         L.is_attn = ((i + 1) % c.attn_every) == 0;
         make_f16(M, L.in_norm, p + "in_norm", H, 1.0f, c.norm_jitter);
@@ -412,15 +430,19 @@ extern "C" void* orc_model_create(const OrcConfig* cfg, uint64_t seed) {
         }
         make_f16(M, L.router, p + "moe.router", (int64_t)E * H, 0.0f, 0.02f);
         make_f16(M, L.shared_gate, p + "moe.shared_gate", H, 0.0f, 0.02f);
-        make_q4(M, L.gate_proj, p + "moe.gate_proj", (int64_t)E * I, H);
-        make_q4(M, L.up_proj, p + "moe.up_proj", (int64_t)E * I, H);
-        make_q4(M, L.down_proj, p + "moe.down_proj", (int64_t)E * H, I);
+        make_q4(M, L.gate_proj, p + "moe.gate_proj", (int64_t)E * I, H, lazy);
+        make_q4(M, L.up_proj, p + "moe.up_proj", (int64_t)E * I, H, lazy);
+        make_q4(M, L.down_proj, p + "moe.down_proj", (int64_t)E * H, I, lazy);
         make_q4(M, L.sh_gate, p + "moe.shared_gate_proj", I, H);
         make_q4(M, L.sh_up, p + "moe.shared_up_proj", I, H);
         make_q4(M, L.sh_down, p + "moe.shared_down_proj", H, I);
     }
     return M;
 }
+extern "C" void* orc_model_create(const OrcConfig* cfg, uint64_t seed) { return model_create(cfg, seed, false); }
+// routed experts are generated the first time a token is routed to them (same values as the
+// eager model); used to time a few steps of the full-size model without generating 18 GB first
+extern "C" void* orc_model_create_lazy(const OrcConfig* cfg, uint64_t seed) { return model_create(cfg, seed, true); }
 extern "C" void orc_model_destroy(void* m) { delete (Model*)m; }
 extern "C" int orc_model_tensor(void* m, const char* name, const void** ptr, uint64_t* nbytes) {
     Model* M = (Model*)m; auto it = M->index.find(name);
@@ -462,7 +484,7 @@ static void qmm_rows(const h16* x, const Q4& q, int64_t row0, int N, h16* y) {  
 #pragma omp parallel for schedule(static)
     for (int n = 0; n < N; ++n) y[n] = f2h(qdot_row(x, q.row_w(row0 + n), q.row_s(row0 + n), q.row_b(row0 + n), K));
 }
-static void moe_block_row(const Model* M, const Layer& L, const h16* x, h16* out, int32_t* inds_out, h16* scores_out) {
+static void moe_block_row(const Model* M, Layer& L, const h16* x, h16* out, int32_t* inds_out, h16* scores_out) {
     const OrcConfig& c = M->c; int H = c.hidden, E = c.n_experts, I = c.moe_inter, T = c.top_k;
     std::vector<h16> logits(E), g(I), u(I), h(I), d((size_t)T * H), y(H), sg(I), su(I), sh(I), sy(H);
     orc_fmm(x, L.router.data(), 1, H, E, logits.data());
@@ -470,6 +492,7 @@ static void moe_block_row(const Model* M, const Layer& L, const h16* x, h16* out
     route_row(logits.data(), E, T, inds.data(), scores.data());
     for (int k = 0; k < T; ++k) {
         int e = inds[k];
+        ensure_expert(M, L, e);
         qmm_rows(x, L.gate_proj, (int64_t)e * I, I, g.data());
         qmm_rows(x, L.up_proj, (int64_t)e * I, I, u.data());
         swiglu_h(g.data(), u.data(), I, h.data());

@@ -54,6 +54,9 @@ SYMBOLS = {
     "sl_last_fault": (C.c_char_p, [_VP]),
     "sl_inject_fault": (_I32, [_VP, _I32]),
     "sl_engine_launch_count": (_I64, [_VP]),
+    "sl_engine_use_graphs": (_I32, [_VP, _I32]),
+    "sl_profile_start": (_I32, [_VP]),
+    "sl_profile_report": (_I32, [_VP, C.c_char_p, _U64]),
     "sl_stream_create": (_I32, [_VP, _I32, C.POINTER(_VP)]),
     "sl_stream_destroy": (_I32, [_VP]),
     "sl_stream_len": (_I32, [_VP]),

@@ -614,6 +614,12 @@ int32_t sl_engine_read_tensor(sl_engine* e, const char* name, void* host_buf, ui
 const char* sl_last_fault(sl_engine* e) { return (e && e->poisoned) ? e->fault.c_str() : nullptr; }
 int32_t sl_inject_fault(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->inject = on != 0; return SL_OK; }
 int64_t sl_engine_launch_count(sl_engine* e) { (void)e; return kernel_launch_count(); }
+int32_t sl_engine_use_graphs(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->use_graph = on != 0; return SL_OK; }
+int32_t sl_profile_start(sl_engine* e) { if (!e) return SL_ERR_INVALID; cudaStreamSynchronize(e->stream); profile_start(); return SL_OK; }
+int32_t sl_profile_report(sl_engine* e, char* buf, uint64_t cap) {
+    if (!e || !buf) return SL_ERR_INVALID;
+    return profile_report(buf, (size_t)cap) < 0 ? SL_ERR_CAPACITY : SL_OK;
+}
 
 // ---- streams ----
 int32_t sl_stream_create(sl_engine* e, int32_t max_seq_len, sl_stream** out) {

@@ -5,12 +5,52 @@
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
+#include <array>
+#include <map>
+#include <string>
+#include <vector>
 
 namespace sl {
 
 static std::atomic<int64_t> g_launches{0};
 int64_t kernel_launch_count() { return g_launches.load(); }
 #define COUNT_LAUNCH() g_launches.fetch_add(1, std::memory_order_relaxed)
+
+// ---- optional per-kernel timing with CUDA events on the launching stream (eager launches only) ----
+struct ProfEntry { const char* tag; cudaEvent_t a, b; double bytes; };
+static bool g_prof_on = false;
+static std::vector<ProfEntry> g_prof;
+struct ProfScope {
+    cudaStream_t st; bool on;
+    ProfScope(const char* tag, double bytes, cudaStream_t s) : st(s), on(g_prof_on) {
+        if (!on) return;
+        ProfEntry e{tag, nullptr, nullptr, bytes};
+        cudaEventCreate(&e.a); cudaEventCreate(&e.b);
+        cudaEventRecord(e.a, st);
+        g_prof.push_back(e);
+    }
+    ~ProfScope() { if (on) cudaEventRecord(g_prof.back().b, st); }
+};
+void profile_start() { g_prof_on = true; }
+// one line per kernel: "tag launches total_ms total_bytes"; stops profiling
+int profile_report(char* buf, size_t cap) {
+    g_prof_on = false;
+    cudaDeviceSynchronize();
+    std::map<std::string, std::array<double, 3>> acc;
+    for (auto& e : g_prof) {
+        float ms = 0.f; cudaEventElapsedTime(&ms, e.a, e.b);
+        auto& r = acc[e.tag]; r[0] += 1; r[1] += ms; r[2] += e.bytes;
+        cudaEventDestroy(e.a); cudaEventDestroy(e.b);
+    }
+    g_prof.clear();
+    std::string out;
+    char line[256];
+    for (auto& kv : acc) { snprintf(line, sizeof line, "%s %.0f %.6f %.0f\n", kv.first.c_str(), kv.second[0], kv.second[1], kv.second[2]); out += line; }
+    if (out.size() + 1 > cap) return -1;
+    memcpy(buf, out.c_str(), out.size() + 1);
+    return (int)out.size();
+}
 
 // ============================================================================================
 // Dense q4 GEMV: one CTA = 16 weight rows x all K (slices across warps) x up to 8 activation rows.
@@ -153,6 +193,7 @@ static void launch_dense_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
         cfg.attrs = attr; cfg.numAttrs = 1;
     }
     DenseArgs copy = a;
+    ProfScope ps(EPI == EPI_ARGMAX ? "k_dense_lm_head" : "k_dense", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
     cudaLaunchKernelEx(&cfg, k_dense<PRO, EPI, EXACT>, copy);
     COUNT_LAUNCH();
 }
@@ -188,6 +229,7 @@ __global__ void k_embed(const __half* embed, const int* tokens, int M, int H, in
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
 void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st) {
+    ProfScope ps("k_embed", (double)M * H * 4, st);
     k_embed<<<M, 256, 0, st>>>(embed, tokens, M, H, vocab, h);
     COUNT_LAUNCH();
 }
@@ -229,6 +271,7 @@ __global__ void k_final_norm(const __half* h, const __half* w, float eps, int H,
     block_rmsnorm_row(h + (size_t)blockIdx.x * H, w, eps, H, out + (size_t)blockIdx.x * H, sm8);
 }
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st) {
+    ProfScope ps("k_final_norm", (double)M * H * 4, st);
     k_final_norm<<<M, 256, 0, st>>>(h, w, eps, H, out);
     COUNT_LAUNCH();
 }
@@ -298,6 +341,7 @@ void launch_router(const RouterArgs& a, cudaStream_t st) {
     size_t smem = (size_t)8 * a.H * 2 + 64;
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_moe_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); configured = true; }
+    ProfScope ps("k_moe_router", (double)(a.E + 1) * a.H * 2 + (double)a.M * a.H * 4, st);
     k_moe_router<<<(a.E + 7) / 8 + 1, 256, smem, st>>>(a);
     COUNT_LAUNCH();
 }
@@ -368,6 +412,7 @@ __global__ void __launch_bounds__(256) k_moe_route(RouteArgs a) {
     }
 }
 void launch_route(const RouteArgs& a, cudaStream_t st) {
+    ProfScope ps("k_moe_route", (double)a.M * a.E * 2, st);
     k_moe_route<<<a.M, 256, 0, st>>>(a);
     COUNT_LAUNCH();
 }
@@ -461,6 +506,8 @@ static void launch_expert_t(const ExpertArgs& a, int nslots, cudaStream_t st) {
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_expert<EXACT, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); configured = true; }
     dim3 grid((unsigned)(DOWN ? a.H / 16 : a.I / 8), (unsigned)(nslots + 1));
+    int touched = (a.M * a.topk < nslots ? a.M * a.topk : nslots) + 1;   // distinct experts read: exact for one row, an upper bound otherwise
+    ProfScope ps(DOWN ? "k_expert_down" : "k_expert_gateup", (double)touched * (DOWN ? 1 : 2) * a.I * a.H * 0.5625, st);
     k_expert<EXACT, DOWN><<<grid, nw * 32, smem, st>>>(a);
     COUNT_LAUNCH();
 }
@@ -487,6 +534,7 @@ __global__ void __launch_bounds__(256) k_moe_combine(CombineArgs a) {
     }
 }
 void launch_combine(const CombineArgs& a, cudaStream_t st) {
+    ProfScope ps("k_moe_combine", (double)a.M * (a.topk + 3) * a.H * 2, st);
     k_moe_combine<<<a.M, 256, 0, st>>>(a);
     COUNT_LAUNCH();
 }
@@ -593,6 +641,7 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
 }
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st) {
     dim3 grid(4, a.Hv, nsegs);
+    ProfScope ps("k_gdn_core", (double)nsegs * a.Hv * GDN_DV * GDN_DK * 8, st);
     k_gdn_core<<<grid, 128, 0, st>>>(a);
     COUNT_LAUNCH();
 }
@@ -665,6 +714,7 @@ __global__ void __launch_bounds__(32) k_attn_prep(AttnArgs a) {
 }
 void launch_attn_prep(const AttnArgs& a, cudaStream_t st) {
     dim3 grid(a.NH + 2 * a.KV, a.M);
+    ProfScope ps("k_attn_prep", 0.0, st);
     k_attn_prep<<<grid, 32, 0, st>>>(a);
     COUNT_LAUNCH();
 }
@@ -748,6 +798,7 @@ __global__ void __launch_bounds__(256) k_attn_decode(AttnArgs a) {
 }
 void launch_attn_decode(const AttnArgs& a, cudaStream_t st) {
     dim3 grid(a.nsplit, a.KV, a.M);
+    ProfScope ps("k_attn_decode", 0.0, st);
     k_attn_decode<<<grid, 256, 0, st>>>(a);
     COUNT_LAUNCH();
 }
@@ -774,6 +825,7 @@ __global__ void __launch_bounds__(256) k_attn_combine(AttnArgs a) {
 }
 void launch_attn_combine(const AttnArgs& a, cudaStream_t st) {
     dim3 grid(a.NH, a.M);
+    ProfScope ps("k_attn_combine", 0.0, st);
     k_attn_combine<<<grid, 256, 0, st>>>(a);
     COUNT_LAUNCH();
 }
@@ -800,6 +852,7 @@ __global__ void k_step_end(StepEndArgs a) {
 void launch_step_end(const StepEndArgs& a, cudaStream_t st) {
     int n = a.nsegs > a.M ? a.nsegs : a.M;
     if (n > 1024) n = 1024;      // one block: history position is updated after every thread has used it
+    ProfScope ps("k_step_end", 0.0, st);
     k_step_end<<<1, n < 32 ? 32 : n, 0, st>>>(a);
     COUNT_LAUNCH();
 }

@@ -105,6 +105,8 @@ void launch_attn_combine(const AttnArgs& a, cudaStream_t st);
 void launch_step_end(const StepEndArgs& a, cudaStream_t st);
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st);
 int64_t kernel_launch_count();
+void profile_start();
+int profile_report(char* buf, size_t cap);
 size_t dense_smem_bytes(int M, int K);
 
 // synthetic data + quantiser (synth.cu)

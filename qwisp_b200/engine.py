@@ -82,6 +82,22 @@ class Engine:
     def launch_count(self):
         return lib().sl_engine_launch_count(self._h)
 
+    def use_graphs(self, on):
+        self._check(lib().sl_engine_use_graphs(self._h, 1 if on else 0), "sl_engine_use_graphs")
+
+    def profile_start(self):
+        self._check(lib().sl_profile_start(self._h), "sl_profile_start")
+
+    def profile_report(self):
+        """-> {kernel: (launches, total_ms, algorithmic_bytes)} for the eager launches since profile_start()."""
+        buf = C.create_string_buffer(1 << 16)
+        self._check(lib().sl_profile_report(self._h, buf, len(buf)), "sl_profile_report")
+        out = {}
+        for line in buf.value.decode().splitlines():
+            name, n, ms, by = line.split()
+            out[name] = (int(float(n)), float(ms), float(by))
+        return out
+
     def tensor_bytes(self, name):
         n = C.c_uint64()
         self._check(lib().sl_engine_tensor_bytes(self._h, name.encode(), C.byref(n)), "sl_engine_tensor_bytes")

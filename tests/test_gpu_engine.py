@@ -1,0 +1,275 @@
+"""GPU tests of the engine through the C ABI: token parity with the CPU oracle and the
+reference's invariance suite (M-row == sequential, chained == stepped, one-step rollback ==
+replay, full snapshot / restore, QWS1 across arena sizes, lane batch == solo, fault firewall)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from conftest import MINI, ROOT, SEED, TINY, f16_report, gpu_engine
+
+pytestmark = pytest.mark.gpu
+
+
+def prompt(vocab, n, name="prompt"):
+    from oracle import oracle as O
+    return O.synth_tokens(SEED, name, n, vocab)
+
+
+def test_tiny_greedy_matches_golden_and_oracle(tiny_engine, tiny_oracle):
+    g = json.load(open(os.path.join(ROOT, "tests", "golden", "oracle_golden.json")))
+    V = TINY["vocab"]
+    p = prompt(V, 6, "golden.prompt")
+    so, sg = tiny_oracle.stream(64), tiny_engine.stream(64)
+    # teacher-forced: feed the oracle's tokens, compare per-step argmax and logits
+    feed = list(p)
+    ref_toks = g["tiny_greedy"]
+    lg = sg.step_logits(p)
+    ro, rl = so.step(p, want_logits=True)
+    rep = f16_report(lg, rl)
+    print("tiny prefill logits", rep)
+    assert rep["max_abs"] <= 2e-2, rep
+    agree = 0
+    cur = ref_toks[0]
+    got_first = int(np.argmax(lg[-1].astype(np.float32)))
+    agree += got_first == ref_toks[0]
+    for k in range(1, 10):
+        t = int(sg.step_argmax([cur])[0])
+        agree += t == ref_toks[k]
+        cur = ref_toks[k]
+    print("teacher-forced agreement", agree, "/ 10")
+    assert agree >= 9
+    sg.close()
+
+
+def test_mini_logits_within_tolerance(mini_engine, mini_oracle):
+    V = MINI["vocab"]
+    p = prompt(V, 12)
+    so, sg = mini_oracle.stream(64), mini_engine.stream(64)
+    rt, rl = so.step(p, want_logits=True)
+    lg = sg.step_logits(p)
+    rep = f16_report(lg, rl)
+    print("mini logits", rep)
+    assert rep["max_abs"] <= 2e-2, rep
+    hid_o = mini_oracle.stream(64).forward(p)
+    hid_g = mini_engine.stream(64).forward(p)
+    rep_h = f16_report(hid_g, hid_o)
+    print("mini hidden", rep_h)
+    assert rep_h["max_abs"] <= 5e-2
+    # greedy agreement where the oracle's top-1 / top-2 margin is clear
+    srt = np.sort(rl.astype(np.float32), axis=1)
+    clear = (srt[:, -1] - srt[:, -2]) > 4 * rep["max_abs"]
+    got = np.argmax(lg.astype(np.float32), axis=1)
+    assert np.array_equal(got[clear], rt[clear])
+    sg.close()
+
+
+@pytest.mark.parametrize("plan", [[1], [2], [9], [17], [9, 3]])
+def test_rows_equal_sequential(tiny_engine, plan):
+    """verify_forward_rows_bitexact: an M-row step is bit-identical to M single-row steps,
+    including the caches it leaves (checked through the tokens of two further steps)."""
+    V = TINY["vocab"]
+    toks = prompt(V, sum(plan) + 3, "rows")
+    a, b = tiny_engine.stream(64), tiny_engine.stream(64)
+    pos = 0
+    for m in plan:
+        la = a.step_logits(toks[pos:pos + m])
+        lb = np.concatenate([b.step_logits(toks[pos + i:pos + i + 1]) for i in range(m)])
+        assert np.array_equal(la.view(np.uint16), lb.view(np.uint16)), plan
+        pos += m
+    assert np.array_equal(a.state_save(), b.state_save())
+    ta, tb = a.step_argmax(toks[pos:pos + 3]), b.step_argmax(toks[pos:pos + 3])
+    assert np.array_equal(ta, tb)
+    a.close(); b.close()
+
+
+@pytest.mark.parametrize("K", [2, 3, 8])
+def test_chained_equals_stepped(tiny_engine, K):
+    V = TINY["vocab"]
+    p = prompt(V, 5, "chain")
+    a, b = tiny_engine.stream(64), tiny_engine.stream(64)
+    fa, fb = int(a.step_argmax(p)[-1]), int(b.step_argmax(p)[-1])
+    assert fa == fb
+    chained = a.chained_step_argmax(fa, K)
+    stepped, cur = [], fb
+    for _ in range(K):
+        cur = int(b.step_argmax([cur])[0]); stepped.append(cur)
+    assert list(chained) == stepped
+    # chain -> step -> chain interleave
+    c2 = a.chained_step_argmax(int(chained[-1]), 2)
+    s2, cur = [], stepped[-1]
+    for _ in range(2):
+        cur = int(b.step_argmax([cur])[0]); s2.append(cur)
+    assert list(c2) == s2
+    assert np.array_equal(a.state_save(), b.state_save())
+    a.close(); b.close()
+
+
+def test_reject_rollback_equals_replay(tiny_engine):
+    """a3_reject_rollback_equiv: verify batch, partial reject, one-step rollback, replay of the
+    accepted prefix == never having run the rejected rows."""
+    V = TINY["vocab"]
+    p = prompt(V, 7, "spec")
+    a, b = tiny_engine.stream(64), tiny_engine.stream(64)
+    a.step_argmax(p); b.step_argmax(p)
+    drafts = prompt(V, 6, "drafts")
+    snap = a.snapshot()
+    a.step_argmax(drafts)                       # verify batch of 6 rows
+    a.rollback(snap)                            # reject after 2 accepted
+    a.forward(drafts[:2], want_hidden=False)
+    b.forward(drafts[:2], want_hidden=False)
+    assert a.length == b.length == 9
+    assert np.array_equal(a.state_save(), b.state_save())
+    assert np.array_equal(a.step_argmax([3]), b.step_argmax([3]))
+    # a second rollback of the same snapshot is refused (more than one step ran)
+    import qwisp_b200 as Q
+    with pytest.raises(Q.SeedlessError):
+        a.rollback(snap)
+    a.close(); b.close()
+
+
+def test_full_snapshot_restore(tiny_engine):
+    V = TINY["vocab"]
+    p = prompt(V, 6, "full")
+    a = tiny_engine.stream(64)
+    a.step_argmax(p)
+    snap = a.full_snapshot()
+    ref_blob = a.state_save()
+    t1 = a.step_argmax([1, 2, 3])
+    a.step_argmax([4])
+    a.full_restore(snap)
+    assert a.length == 6
+    assert np.array_equal(a.state_save(), ref_blob)
+    assert np.array_equal(a.step_argmax([1, 2, 3]), t1)
+    a.close()
+
+
+def test_state_blob_cross_arena_and_oracle_interop(tiny_engine, tiny_oracle):
+    """lane_admit_restore_cross_arena_bitexact + blob interop with the oracle's writer."""
+    V = TINY["vocab"]
+    p = prompt(V, 9, "blob")
+    a = tiny_engine.stream(48)
+    a.step_argmax(p)
+    blob = a.state_save()
+    b = tiny_engine.stream(96)                  # different arena size
+    assert b.state_restore(blob)
+    nxt = [7, 11, 13]
+    assert np.array_equal(a.step_argmax(nxt), b.step_argmax(nxt))
+    c = tiny_engine.stream(48)
+    assert not c.state_restore(blob[:-2])       # truncated
+    bad = blob.copy(); bad[0] ^= 0xFF
+    assert not c.state_restore(bad)
+    small = tiny_engine.stream(4)
+    assert not small.state_restore(blob)
+    # the oracle can read a GPU blob and continues with near-identical logits
+    so = tiny_oracle.stream(64)
+    assert so.state_restore(blob)
+    d = tiny_engine.stream(64); assert d.state_restore(blob)
+    _, rl = so.step([5], want_logits=True)
+    gl = d.step_logits([5])
+    assert f16_report(gl, rl)["max_abs"] <= 2e-2
+    for s in (a, b, c, small, d):
+        s.close()
+
+
+def test_lane_batch_equals_solo(tiny_engine):
+    """lane_batch_argmax_bitexact: B=3 lanes with different histories == each lane solo, 4 steps."""
+    V = TINY["vocab"]
+    lens = [3, 8, 5]
+    solo, lane = [], []
+    for i, n in enumerate(lens):
+        p = prompt(V, n, f"lane{i}")
+        s1, s2 = tiny_engine.stream(64), tiny_engine.stream(64)
+        f1, f2 = int(s1.step_argmax(p)[-1]), int(s2.step_argmax(p)[-1])
+        assert f1 == f2
+        solo.append((s1, f1)); lane.append((s2, f2))
+    cur_solo = [f for _, f in solo]
+    cur_lane = [f for _, f in lane]
+    for _ in range(4):
+        cur_solo = [int(s.step_argmax([t])[0]) for (s, _), t in zip(solo, cur_solo)]
+        cur_lane = [int(t) for t in tiny_engine.batch_step_argmax([s for s, _ in lane], cur_lane)]
+        assert cur_solo == cur_lane
+    for (s1, _), (s2, _) in zip(solo, lane):
+        assert np.array_equal(s1.state_save(), s2.state_save())
+        s1.close(); s2.close()
+
+
+def test_lane_batch_slots_protocol(tiny_engine):
+    """BatchSlots: resumable chunked prefill with forward progress, batched step, release."""
+    import qwisp_b200 as Q
+    V = TINY["vocab"]
+    slots = Q.LaneBatchSlots(tiny_engine, slot_count=3, chunk=4, default_seq_budget=64)
+    p0, p1 = list(prompt(V, 10, "slot0")), list(prompt(V, 3, "slot1"))
+    r = slots.admit_step(p0, 0, token_budget=1)           # budget below one chunk: still one whole chunk
+    assert r == ("prefilling", 4)
+    r = slots.admit_step(p0, 0, token_budget=8)
+    assert r[0] == "done" and r[2] == 6
+    first0 = r[1]
+    first1 = slots.admit(p1, 1)
+    ref = tiny_engine.stream(64)
+    assert int(ref.step_argmax(p0)[-1]) == first0
+    out = slots.step([first0, first1, None])
+    assert out[2] is None and out[0] == int(ref.step_argmax([first0])[0])
+    slots.release(0); slots.release(1)
+    ref.close()
+
+
+def test_sizes_and_errors(tiny_engine):
+    import qwisp_b200 as Q
+    s = tiny_engine.stream(8)
+    with pytest.raises(Q.SeedlessError) as ei:
+        s.step_argmax(list(range(9)))                   # beyond max_seq_len
+    assert ei.value.code == -5
+    with pytest.raises(Q.SeedlessError) as ei:
+        s.step_argmax([TINY["vocab"]])                  # token id out of range
+    assert ei.value.code == -1
+    with pytest.raises(Q.SeedlessError) as ei:
+        s.step_argmax(list(range(65)))                  # rows > max_rows
+    assert ei.value.code == -5
+    assert s.length == 0
+    s.step_argmax([1, 2, 3])
+    assert s.length == 3
+    s.reset()
+    assert s.length == 0
+    s.close()
+
+
+def test_fault_firewall():
+    """gpu-failure-firewall: an injected failure poisons that engine only, stickily."""
+    import qwisp_b200 as Q
+    e1, e2 = gpu_engine(TINY, max_streams=2), gpu_engine(TINY, max_streams=2)
+    try:
+        s1, s2 = e1.stream(16), e2.stream(16)
+        assert e1.gpu_fault() is None
+        e1.inject_fault()
+        bk = Q.SpecBackend(s1)
+        assert bk.step_argmax([1]) is None
+        assert "injected" in bk.gpu_fault()
+        assert bk.step_argmax([1]) is None and bk.forward([1]) is None      # sticky
+        with pytest.raises(Q.SeedlessError) as ei:
+            s1.step_argmax([1])
+        assert ei.value.code == -4
+        assert e2.gpu_fault() is None
+        assert len(s2.step_argmax([1, 2])) == 2                              # the other engine is unaffected
+    finally:
+        e1.close(); e2.close()
+
+
+def test_engine_from_host_tensors(tiny_oracle):
+    """The weight-loading boundary: tensors handed over by name in the MLX layout."""
+    import qwisp_b200 as Q
+    from conftest import JITTER, CONV_STD
+    cfg = Q.config(**TINY, max_rows=16, max_streams=2, kv_page_size=32, kv_pages=8)
+    tensors = {n: tiny_oracle.tensor_bytes(n).copy() for n in tiny_oracle.tensor_names()}
+    eng = Q.Engine.from_tensors(cfg, tensors)
+    ref = gpu_engine(TINY, max_rows=16, max_streams=2, kv_pages=8)
+    try:
+        p = prompt(TINY["vocab"], 7, "host")
+        a, b = eng.stream(32), ref.stream(32)
+        assert np.array_equal(a.step_logits(p).view(np.uint16), b.step_logits(p).view(np.uint16))
+        missing = dict(tensors); missing.pop("embed")
+        with pytest.raises(Q.SeedlessError):
+            Q.Engine.from_tensors(cfg, missing)
+    finally:
+        eng.close(); ref.close()
