@@ -179,6 +179,12 @@ int32_t sl_op_moe_block(sl_engine* e, int32_t layer, const uint16_t* x_f16, int3
 /* Mixer (GDN or attention) of `layer` on already-normed rows x [M,H] placed at positions
  * pos0..pos0+M-1 of the stream; advances only that layer's cache, not the stream length. */
 int32_t sl_op_mixer(sl_stream* s, int32_t layer, const uint16_t* x_f16, int32_t M, int32_t pos0, uint16_t* out_f16);
+/* One whole decoder layer (rmsnorm, mixer, +resid, rmsnorm, MoE, +resid; the reference's
+ * decoder-layer test, SeedlessMetalForward.swift:3757) on residual-stream rows h_in [M,H] at
+ * positions pos0..; advances only that layer's cache. */
+int32_t sl_op_layer(sl_stream* s, int32_t layer, const uint16_t* h_in_f16, int32_t M, int32_t pos0, uint16_t* h_out_f16);
+/* Head of the step on residual-stream rows: final norm + lm_head + greedy argmax. */
+int32_t sl_op_head(sl_engine* e, const uint16_t* h_rows_f16, int32_t M, uint16_t* out_logits_f16, int32_t* out_tokens);
 /* final-norm'ed rows -> logits (may be NULL) and greedy tokens (may be NULL). */
 int32_t sl_op_lm_head(sl_engine* e, const uint16_t* normed_f16, int32_t M, uint16_t* out_logits_f16, int32_t* out_tokens);
 

@@ -198,6 +198,20 @@ class Model:
         lib().orc_lm_head(C.c_void_p(self.h), _p(normed), C.c_int(M), _p(logits), _p(toks))
         return logits, toks
 
+    def embed(self, tokens):
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.empty((len(tokens), self.cfg.hidden), dtype=np.float16)
+        lib().orc_embed(C.c_void_p(self.h), _p(tokens), C.c_int(len(tokens)), _p(out))
+        return out
+
+    def head(self, h):
+        h = np.ascontiguousarray(h, dtype=np.float16)
+        M = h.shape[0]
+        logits = np.empty((M, self.cfg.vocab), dtype=np.float16)
+        toks = np.empty(M, dtype=np.int32)
+        lib().orc_head(C.c_void_p(self.h), _p(h), C.c_int(M), _p(logits), _p(toks))
+        return logits, toks
+
     def stream(self, max_seq_len):
         return Stream(self, max_seq_len)
 
@@ -252,6 +266,14 @@ class Stream:
             raise RuntimeError(f"orc_mixer_rows rc={rc}")
         return out
 
+    def layer_rows(self, layer, h_in, pos0):
+        h_in = np.ascontiguousarray(h_in, dtype=np.float16)
+        out = np.empty_like(h_in)
+        rc = lib().orc_layer_rows(C.c_void_p(self.h), C.c_int(layer), _p(h_in), C.c_int(h_in.shape[0]), C.c_int(pos0), _p(out))
+        if rc != 0:
+            raise RuntimeError(f"orc_layer_rows rc={rc}")
+        return out
+
     def state_save(self):
         n = lib().orc_state_size(C.c_void_p(self.h))
         buf = np.empty(n, dtype=np.uint8)
@@ -263,6 +285,11 @@ class Stream:
     def state_restore(self, blob):
         blob = np.ascontiguousarray(blob, dtype=np.uint8)
         return lib().orc_state_restore(C.c_void_p(self.h), _p(blob), C.c_uint64(len(blob))) == 0
+
+
+def set_alt_order(on):
+    """Control experiment only: use another (equally valid) lane-reduction order."""
+    lib().orc_set_alt_order(C.c_int(1 if on else 0))
 
 
 def config(hidden=2048, n_layers=40, attn_every=4, vocab=151936, n_experts=256, top_k=8, moe_inter=512,

@@ -66,10 +66,16 @@ static inline float sigmoid_f(float x) {
 }
 
 // Canonical stand-in for Metal's simd_sum over 32 lanes: xor butterfly, offsets 16,8,4,2,1.
+// g_alt_order = 1 walks the offsets upwards instead (1,2,..,16): an equally valid simd_sum
+// order, used only by the control experiment that measures how far two correct
+// implementations of the random-weight model drift apart.
+static int g_alt_order = 0;
+extern "C" void orc_set_alt_order(int on) { g_alt_order = on; }
 static inline float bfly_sum32(const float* v) {
     float a[32], b[32];
     for (int i = 0; i < 32; ++i) a[i] = v[i];
-    for (int off = 16; off >= 1; off >>= 1) {
+    for (int step = 0; step < 5; ++step) {
+        int off = g_alt_order ? (1 << step) : (16 >> step);
         for (int i = 0; i < 32; ++i) b[i] = a[i] + a[i ^ off];
         for (int i = 0; i < 32; ++i) a[i] = b[i];
     }
@@ -679,6 +685,38 @@ extern "C" int orc_mixer_rows(void* sp, int layer, const h16* x, int Mrows, int 
         else gdn_row(M, M->layers[layer], s->L[layer], x + (int64_t)r * H, out + (int64_t)r * H);
     }
     return 0;
+}
+
+extern "C" void orc_lm_head(void* m, const h16* normed, int Mrows, h16* out_logits, int32_t* out_tokens);
+// one whole decoder layer on given residual-stream rows (SVF:288-305), advancing that layer's cache only
+extern "C" int orc_layer_rows(void* sp, int layer, const h16* h_in, int Mrows, int pos0, h16* h_out) {
+    Stream* s = (Stream*)sp; Model* M = s->m; const OrcConfig& c = M->c; int H = c.hidden;
+    if (pos0 + Mrows > s->cap) return -1;
+    Layer& L = M->layers[layer];
+    std::vector<h16> h(H), n(H), r(H);
+    for (int row = 0; row < Mrows; ++row) {
+        memcpy(h.data(), h_in + (int64_t)row * H, H * sizeof(h16));
+        rmsnorm_row(h.data(), L.in_norm.data(), H, c.rms_eps, n.data());
+        if (L.is_attn) attn_row(M, L, s->L[layer], s->cap, pos0 + row, n.data(), r.data());
+        else gdn_row(M, L, s->L[layer], n.data(), r.data());
+        for (int d = 0; d < H; ++d) h[d] = hadd(h[d], r[d]);
+        rmsnorm_row(h.data(), L.post_norm.data(), H, c.rms_eps, n.data());
+        moe_block_row(M, L, n.data(), r.data(), nullptr, nullptr);
+        for (int d = 0; d < H; ++d) h[d] = hadd(h[d], r[d]);
+        memcpy(h_out + (int64_t)row * H, h.data(), H * sizeof(h16));
+    }
+    return 0;
+}
+extern "C" void orc_embed(void* m, const int32_t* tokens, int Mrows, h16* out) {
+    Model* M = (Model*)m; int H = M->c.hidden;
+    for (int r = 0; r < Mrows; ++r) memcpy(out + (int64_t)r * H, M->embed.data() + (size_t)tokens[r] * H, H * sizeof(h16));
+}
+// final norm + lm_head + argmax on residual-stream rows
+extern "C" void orc_head(void* m, const h16* h, int Mrows, h16* out_logits, int32_t* out_tokens) {
+    Model* M = (Model*)m; int H = M->c.hidden;
+    std::vector<h16> normed((size_t)Mrows * H);
+    for (int r = 0; r < Mrows; ++r) rmsnorm_row(h + (int64_t)r * H, M->final_norm.data(), H, M->c.rms_eps, normed.data() + (int64_t)r * H);
+    orc_lm_head(m, normed.data(), Mrows, out_logits, out_tokens);
 }
 
 // ---------------------------------------------------------------- whole forward (SVF:284-309)

@@ -59,7 +59,7 @@ struct sl_engine {
     float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
-    unsigned* counters = nullptr;
+    unsigned* counters = nullptr; unsigned* tile_counters = nullptr;
     SegDesc* segs = nullptr;
     int hist_cap = 0;
     // pinned staging
@@ -276,6 +276,8 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->lists.slot_off, (size_t)256))) return rc;
     if ((rc = dalloc(e, &e->lists.slot_cnt, (size_t)256))) return rc;
     if ((rc = dalloc(e, &e->lists.pairs, (size_t)R * e->topk))) return rc;
+    if ((rc = dalloc(e, &e->tile_counters, (size_t)(H / 16)))) return rc;
+    CU(e, cudaMemset(e->tile_counters, 0, (size_t)(H / 16) * sizeof(unsigned)));
     CU(e, cudaMemset(e->counters, 0, 8 * sizeof(unsigned)));
     CU(e, cudaMemset(e->hist_pos, 0, sizeof(int)));
     e->pin_ints = (size_t)R * 8 + 64;
@@ -352,17 +354,14 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const __half* rows, int ld, bool
     RouterArgs ra{}; ra.h = rows; ra.ldh = ld; ra.norm_w = apply_norm ? L.post_norm : nullptr; ra.eps = e->cfg.rms_eps;
     ra.router = L.router; ra.shared_gate = L.shared_gate; ra.M = M; ra.H = e->H; ra.E = e->E;
     ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
+    ra.topk = e->topk; ra.inds = e->inds; ra.scores = e->scores; ra.lists = e->lists; ra.counter = e->counters + 1;
     launch_router(ra, st);
-    RouteArgs ro{}; ro.logits = e->rlogits; ro.M = M; ro.E = e->E; ro.topk = e->topk; ro.inds = e->inds; ro.scores = e->scores;
-    ro.lists = e->lists; ro.counter = e->counters + 1;
-    launch_route(ro, st);
     ExpertArgs ea{}; ea.gate = L.gate; ea.up = L.up; ea.down = L.down; ea.sh_gate = L.sh_gate; ea.sh_up = L.sh_up; ea.sh_down = L.sh_down;
     ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = M; ea.H = e->H; ea.I = e->I; ea.topk = e->topk;
+    ea.scores = e->scores; ea.sgl = e->sgl; ea.resid = resid; ea.out = plain_out; ea.tile_counter = e->tile_counters;
     int nslots = M * e->topk < e->E ? M * e->topk : e->E;
     launch_expert_gateup(e->exact, ea, nslots, st);
     launch_expert_down(e->exact, ea, nslots, st);
-    CombineArgs ca{}; ca.dbuf = e->dbuf; ca.scores = e->scores; ca.sgl = e->sgl; ca.h = resid; ca.out = plain_out; ca.M = M; ca.H = e->H; ca.topk = e->topk;
-    launch_combine(ca, st);
 }
 
 // mixer of one layer: input rows are normed inside (norm_w != nullptr) or already normed
@@ -973,6 +972,52 @@ int32_t sl_op_mixer(sl_stream* s, int32_t layer, const uint16_t* x, int32_t M, i
         CU(e, cudaMemcpyAsync(curh, othh, cc * 2, cudaMemcpyDeviceToDevice, e->stream));
     }
     CU(e, cudaMemcpyAsync(out, e->opy, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_op_layer(sl_stream* s, int32_t layer, const uint16_t* h_in, int32_t M, int32_t pos0, uint16_t* h_out) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!h_in || !h_out || layer < 0 || layer >= e->cfg.n_layers || M <= 0 || pos0 < 0) return SL_ERR_INVALID;
+    if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
+    if ((rc = ensure_pages(s, pos0 + M))) return rc;
+    std::vector<SegDesc> segs{SegDesc{s->slot, 0, M, 0}};
+    if ((rc = upload_descs(e, segs, nullptr, M))) return rc;
+    std::vector<int> pos(M);
+    for (int i = 0; i < M; ++i) pos[i] = pos0 + i;
+    CU(e, cudaMemcpyAsync(e->row_pos, pos.data(), (size_t)M * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaMemcpyAsync(e->h, h_in, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
+    CU(e, cudaStreamSynchronize(e->stream));
+    const LayerW& L = e->layers[layer];
+    enqueue_mixer(e, L, e->h, L.in_norm, M, 1, e->h, nullptr, e->row_pos);
+    enqueue_moe(e, L, e->h, e->H, true, M, e->h, nullptr);
+    if (!L.is_attn) {
+        size_t sc = e->tab.state_stride_layer, cc = e->tab.hist_stride_layer;
+        float* cur = cur_state(s) + (size_t)L.type_index * sc;
+        float* oth = e->tab.gdn_state + (size_t)s->slot * e->tab.state_stride_stream + (size_t)(s->parity ^ 1) * e->tab.state_stride_side + (size_t)L.type_index * sc;
+        __half* curh = cur_hist(s) + (size_t)L.type_index * cc;
+        __half* othh = e->tab.conv_hist + (size_t)s->slot * e->tab.hist_stride_stream + (size_t)(s->parity ^ 1) * e->tab.hist_stride_side + (size_t)L.type_index * cc;
+        CU(e, cudaMemcpyAsync(cur, oth, sc * 4, cudaMemcpyDeviceToDevice, e->stream));
+        CU(e, cudaMemcpyAsync(curh, othh, cc * 2, cudaMemcpyDeviceToDevice, e->stream));
+    }
+    CU(e, cudaMemcpyAsync(h_out, e->h, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_op_head(sl_engine* e, const uint16_t* h_rows, int32_t M, uint16_t* out_logits, int32_t* out_tokens) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!h_rows || M <= 0) return SL_ERR_INVALID;
+    if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
+    if (out_logits && e->logits_rows < M) {
+        __half* lg; if ((rc = dalloc(e, &lg, (size_t)e->cfg.max_rows * e->V))) return rc;
+        e->logits = lg; e->logits_rows = e->cfg.max_rows;
+    }
+    CU(e, cudaMemcpyAsync(e->opx, h_rows, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
+    DenseArgs d{}; d.w = e->lm_head.w; d.s = e->lm_head.s; d.b = e->lm_head.b; d.N = e->V; d.K = e->H; d.M = M;
+    d.x = e->opx; d.ldx = e->H; d.nw = e->final_norm; d.eps = e->cfg.rms_eps;
+    d.logits = out_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
+    launch_dense(PRO_RMSNORM, EPI_ARGMAX, e->exact, d, e->stream, false);
+    if (out_logits) CU(e, cudaMemcpyAsync(out_logits, e->logits, (size_t)M * e->V * 2, cudaMemcpyDeviceToHost, e->stream));
+    if (out_tokens) CU(e, cudaMemcpyAsync(out_tokens, e->out_tok, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);
 }
 int32_t sl_op_lm_head(sl_engine* e, const uint16_t* normed, int32_t M, uint16_t* out_logits, int32_t* out_tokens) {

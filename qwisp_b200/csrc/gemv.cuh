@@ -47,12 +47,15 @@ __device__ __forceinline__ uint4 permute_scale8(uint4 v) {
     o.w = *reinterpret_cast<uint32_t*>(&q3);
     return o;
 }
+// Sum of 8 consecutive activations the way the reference's GEMV forms its bias term: groups of
+// four are added in fp16 (each add rounded), the fp16 partial sums are then added in f32
+// (swift/Sources/QwispCore/SeedlessMetalForward.swift:238-247).  Matching this keeps fp16
+// outputs identical to the CPU restatement except at rare rounding boundaries.
 __device__ __forceinline__ float sum8_f32(uint4 v) {
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); s += f.x; s += f.y; }
-    return s;
+    const __half* h = reinterpret_cast<const __half*>(&v);
+    __half a = hadd_rn(hadd_rn(hadd_rn(h[0], h[1]), h[2]), h[3]);
+    __half b = hadd_rn(hadd_rn(hadd_rn(h[4], h[5]), h[6]), h[7]);
+    return h2f(a) + h2f(b);
 }
 // lane holds 8 consecutive activations of column `col` starting at k0 (multiple of 8): write
 // them staged and accumulate the group sum (8 consecutive lanes cover one group of 64)

@@ -101,8 +101,8 @@ __global__ void __launch_bounds__(512) k_dense(DenseArgs a) {
     reduce_tile(red, fin, v, nw);
 
     if (EPI == EPI_STORE || EPI == EPI_RESID) {
-        if (threadIdx.x < 128) {
-            int col = threadIdx.x >> 4, row = threadIdx.x & 15;
+        for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+            int col = i >> 4, row = i & 15;
             if (col < mr) {
                 size_t idx = (size_t)(row0 + col) * a.ldy + tile * 16 + row;
                 __half val = f2h(fin[row * 8 + col]);
@@ -111,8 +111,8 @@ __global__ void __launch_bounds__(512) k_dense(DenseArgs a) {
             }
         }
     } else if (EPI == EPI_SWIGLU) {
-        if (threadIdx.x < 64) {
-            int col = threadIdx.x >> 3, i = threadIdx.x & 7;
+        for (int j = threadIdx.x; j < 64; j += blockDim.x) {
+            int col = j >> 3, i = j & 7;
             if (col < mr) {
                 __half g = f2h(fin[i * 8 + col]), u = f2h(fin[(i + 8) * 8 + col]);
                 a.y[(size_t)(row0 + col) * a.ldy + tile * 8 + i] = swiglu_h(g, u);
@@ -120,10 +120,11 @@ __global__ void __launch_bounds__(512) k_dense(DenseArgs a) {
         }
     } else {  // EPI_ARGMAX: fp16 logits, per-tile first-index maximum, last block reduces all tiles
         const int tiles = gridDim.x;
-        if (a.logits && threadIdx.x < 128) {
-            int col = threadIdx.x >> 4, row = threadIdx.x & 15;
-            if (col < mr) a.logits[(size_t)(row0 + col) * a.N + tile * 16 + row] = f2h(fin[row * 8 + col]);
-        }
+        if (a.logits)
+            for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+                int col = i >> 4, row = i & 15;
+                if (col < mr) a.logits[(size_t)(row0 + col) * a.N + tile * 16 + row] = f2h(fin[row * 8 + col]);
+            }
         if (threadIdx.x < 8 && (int)threadIdx.x < mr) {
             int col = threadIdx.x;
             float best = -INFINITY; int bi = 0x7fffffff;
@@ -296,11 +297,67 @@ __device__ __forceinline__ float canon_dot8(const uint4* wreg, const __half* xro
     }
     return warp_sum(acc);
 }
+// One warp routes one row.  Restates swift/Sources/QwispCore/SeedlessFusedVerify.swift:180-214
+// including the ORDER of its 256-slot halving trees: lane l holds slots l, l+32, .., l+224, so
+// the tree levels 128/64/32 are lane-local and the levels 16..1 are xor-shuffles whose results
+// are meaningful in lanes < s -- the same pairs (i, i+s) the reference combines.  Softmax in f32,
+// gates rounded to fp16, top-k by k rounds of arg-max on the raw logits (strict > keeps the
+// lower slot), fp16 sequential sum of the chosen gates, fp16 divide.
+__device__ __forceinline__ void route_row_warp(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, int lane) {
+    float lg[8], ex[8], gates[8], work[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { int slot = j * 32 + lane; lg[j] = (slot < E) ? h2f(__ldcg(lrow + slot)) : -INFINITY; }
+    float mx = lg[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mx = fmaxf(mx, lg[j]);
+    mx = warp_max(mx);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { int slot = j * 32 + lane; ex[j] = (slot < E) ? expf(lg[j] - mx) : 0.0f; }
+    float r0 = __fadd_rn(ex[0], ex[4]), r1 = __fadd_rn(ex[1], ex[5]), r2 = __fadd_rn(ex[2], ex[6]), r3 = __fadd_rn(ex[3], ex[7]);
+    r0 = __fadd_rn(r0, r2); r1 = __fadd_rn(r1, r3);
+    r0 = __fadd_rn(r0, r1);
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) r0 = __fadd_rn(r0, __shfl_xor_sync(0xffffffffu, r0, s));
+    const float Z = __shfl_sync(0xffffffffu, r0, 0);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { gates[j] = h2f(f2h(__fdiv_rn(ex[j], Z))); work[j] = lg[j]; }
+    __half sc[16];
+    int ids[16];
+#pragma unroll 1
+    for (int k = 0; k < topk; ++k) {
+        float v[8]; int id[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[j] = work[j]; id[j] = j * 32 + lane; }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) if (v[j + 4] > v[j]) { v[j] = v[j + 4]; id[j] = id[j + 4]; }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) if (v[j + 2] > v[j]) { v[j] = v[j + 2]; id[j] = id[j + 2]; }
+        if (v[1] > v[0]) { v[0] = v[1]; id[0] = id[1]; }
+        float bv = v[0]; int bi = id[0];
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, s); int oi = __shfl_xor_sync(0xffffffffu, bi, s);
+            if (ov > bv) { bv = ov; bi = oi; }            // exact for lanes < s, which is all the next level reads
+        }
+        bi = __shfl_sync(0xffffffffu, bi, 0);
+        float gsel = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (j == (bi >> 5)) { gsel = gates[j]; if (lane == (bi & 31)) work[j] = -INFINITY; }
+        gsel = __shfl_sync(0xffffffffu, gsel, bi & 31);
+        ids[k] = bi; sc[k] = f2h(gsel);
+    }
+    __half ss = f2h(0.0f);
+    for (int k = 0; k < topk; ++k) ss = hadd_rn(ss, sc[k]);
+    if (lane == 0)
+        for (int k = 0; k < topk; ++k) { inds_out[k] = ids[k]; scores_out[k] = hdiv_rn(sc[k], ss); }
+}
+
 __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __half* ps = reinterpret_cast<__half*>(smem);            // [8][H]
     float* sm8 = reinterpret_cast<float*>(ps + 8 * a.H);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __shared__ int s_last; __shared__ int s_cnt[256]; __shared__ int s_cur[256]; __shared__ int s_off[256];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int nblk = a.H >> 8;                                // <= 16
     const bool tail = (blockIdx.x == gridDim.x - 1);
     const int e = blockIdx.x * 8 + warp;
@@ -336,6 +393,43 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
             }
         }
     }
+    // ---- the CTA that finishes last routes every row and groups the (row, k) pairs by expert ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int m = warp; m < a.M; m += 8) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, lane);
+    if (tid == 0) *a.counter = 0u;
+    __syncthreads();
+    if (a.M == 1) {                                          // one row: its k experts are distinct, slot k = k-th choice
+        if (tid < a.topk) {
+            a.lists.slot_expert[tid] = a.inds[tid]; a.lists.slot_off[tid] = tid; a.lists.slot_cnt[tid] = 1; a.lists.pairs[tid] = tid;
+        }
+        if (tid == 0) *a.lists.n_active = a.topk;
+        return;
+    }
+    s_cnt[tid] = 0; s_cur[tid] = 0; s_off[tid] = 0;
+    __syncthreads();
+    const int npairs = a.M * a.topk;
+    for (int i = tid; i < npairs; i += 256) atomicAdd(&s_cnt[a.inds[i]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int slot = 0, off = 0;
+        for (int ex = 0; ex < a.E; ++ex)
+            if (s_cnt[ex] > 0) {
+                a.lists.slot_expert[slot] = ex; a.lists.slot_off[slot] = off; a.lists.slot_cnt[slot] = s_cnt[ex];
+                s_off[ex] = off; off += s_cnt[ex]; ++slot;
+            }
+        *a.lists.n_active = slot;
+    }
+    __syncthreads();
+    for (int i = tid; i < npairs; i += 256) {
+        int ex = a.inds[i];
+        int pos = atomicAdd(&s_cur[ex], 1);
+        a.lists.pairs[s_off[ex] + pos] = i;
+    }
 }
 void launch_router(const RouterArgs& a, cudaStream_t st) {
     size_t smem = (size_t)8 * a.H * 2 + 64;
@@ -347,81 +441,11 @@ void launch_router(const RouterArgs& a, cudaStream_t st) {
 }
 
 // ============================================================================================
-// Top-k selection and renormalisation per row, then (last CTA) grouping of the (row, k) pairs
-// by expert.  Restates swift/Sources/QwispCore/SeedlessFusedVerify.swift:180-214: softmax in
-// f32, gates rounded to fp16, k rounds of arg-max on the raw logits (ties -> lower index),
-// fp16 sequential sum of the chosen gates, fp16 divide.  One CTA of 256 threads per row.
-// ============================================================================================
-__global__ void __launch_bounds__(256) k_moe_route(RouteArgs a) {
-    __shared__ float red[256]; __shared__ int redi[256]; __shared__ float gates[256]; __shared__ float work[256];
-    __shared__ int s_last; __shared__ int s_cnt[256]; __shared__ int s_cur[256]; __shared__ int s_slot[256];
-    const int tid = threadIdx.x, m = blockIdx.x;
-    const __half* lrow = a.logits + (size_t)m * a.E;
-    float lg = (tid < a.E) ? h2f(lrow[tid]) : -INFINITY;
-    red[tid] = lg; __syncthreads();
-    for (int s = 128; s > 0; s >>= 1) { if (tid < s) red[tid] = fmaxf(red[tid], red[tid + s]); __syncthreads(); }
-    float mx = red[0]; __syncthreads();
-    float e = (tid < a.E) ? expf(lg - mx) : 0.0f;
-    red[tid] = e; __syncthreads();
-    for (int s = 128; s > 0; s >>= 1) { if (tid < s) red[tid] = __fadd_rn(red[tid], red[tid + s]); __syncthreads(); }
-    float Z = red[0]; __syncthreads();
-    gates[tid] = (tid < a.E) ? h2f(f2h(__fdiv_rn(e, Z))) : 0.0f;
-    work[tid] = lg;
-    __syncthreads();
-    for (int k = 0; k < a.topk; ++k) {
-        red[tid] = work[tid]; redi[tid] = tid; __syncthreads();
-        for (int s = 128; s > 0; s >>= 1) {
-            if (tid < s) { if (red[tid + s] > red[tid]) { red[tid] = red[tid + s]; redi[tid] = redi[tid + s]; } }
-            __syncthreads();
-        }
-        if (tid == 0) { int bi = redi[0]; a.inds[m * a.topk + k] = bi; a.scores[m * a.topk + k] = f2h(gates[bi]); work[bi] = -INFINITY; }
-        __syncthreads();
-    }
-    if (tid == 0) {
-        __half ss = f2h(0.0f);
-        for (int k = 0; k < a.topk; ++k) ss = hadd_rn(ss, a.scores[m * a.topk + k]);
-        for (int k = 0; k < a.topk; ++k) a.scores[m * a.topk + k] = hdiv_rn(a.scores[m * a.topk + k], ss);
-    }
-    // ---- last CTA: group pairs by expert ----
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    s_cnt[tid] = 0; s_cur[tid] = 0; s_slot[tid] = -1;
-    __syncthreads();
-    const int npairs = a.M * a.topk;
-    for (int i = tid; i < npairs; i += 256) atomicAdd(&s_cnt[__ldcg(a.inds + i)], 1);
-    __syncthreads();
-    if (tid == 0) {
-        int slot = 0, off = 0;
-        for (int ex = 0; ex < a.E; ++ex)
-            if (s_cnt[ex] > 0) {
-                a.lists.slot_expert[slot] = ex; a.lists.slot_off[slot] = off; a.lists.slot_cnt[slot] = s_cnt[ex];
-                s_slot[ex] = off; off += s_cnt[ex]; ++slot;
-            }
-        *a.lists.n_active = slot;
-        *a.counter = 0u;
-    }
-    __syncthreads();
-    for (int i = tid; i < npairs; i += 256) {
-        int ex = __ldcg(a.inds + i);
-        int pos = atomicAdd(&s_cur[ex], 1);
-        a.lists.pairs[s_slot[ex] + pos] = i;
-    }
-}
-void launch_route(const RouteArgs& a, cudaStream_t st) {
-    ProfScope ps("k_moe_route", (double)a.M * a.E * 2, st);
-    k_moe_route<<<a.M, 256, 0, st>>>(a);
-    COUNT_LAUNCH();
-}
-
-// ============================================================================================
 // Routed + shared experts, grouped by expert: every touched expert's weights are read once per
 // call and applied to all rows routed to it (8 rows per MMA pass).
 // gate/up: grid (I/8, nslots + 1); tile = 8 gate rows + 8 up rows, SwiGLU in the epilogue.
-// down:    grid (H/16, nslots + 1).  The last grid.y index is the shared expert (all rows).
+// down:    grid (H/16, nslots + 1).  The last grid.y index is the shared expert (all rows).  Its last
+//          CTA per tile also does the weighted combine + shared expert + residual.
 // hbuf / dbuf rows: pair id (row*top_k + k) for routed experts, M*top_k + row for the shared one.
 // ============================================================================================
 template <bool EXACT, bool DOWN>
@@ -487,8 +511,8 @@ __global__ void __launch_bounds__(512) k_expert(ExpertArgs a) {
                 if (col < mr) a.dbuf[(size_t)misc[8 + col] * a.H + tile * 16 + row] = f2h(fin[row * 8 + col]);
             }
         } else {
-            if (threadIdx.x < 64) {
-                int col = threadIdx.x >> 3, i = threadIdx.x & 7;
+            for (int j = threadIdx.x; j < 64; j += blockDim.x) {
+                int col = j >> 3, i = j & 7;
                 if (col < mr) {
                     __half g = f2h(fin[i * 8 + col]), u = f2h(fin[(i + 8) * 8 + col]);
                     a.hbuf[(size_t)misc[8 + col] * a.I + tile * 8 + i] = swiglu_h(g, u);
@@ -496,6 +520,30 @@ __global__ void __launch_bounds__(512) k_expert(ExpertArgs a) {
             }
         }
         __syncthreads();
+    }
+    if (DOWN) {
+        // The CTA that finishes last for this tile of 16 output rows combines them for every row:
+        // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit)
+        // * shared (:474-484), + residual (SeedlessMetalForward.swift:1024-1028).
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned ticket = atomicAdd(a.tile_counter + tile, 1u);
+            misc[0] = (ticket == (unsigned)*a.lists.n_active) ? 1 : 0;     // n_active routed slots + the shared expert
+        }
+        __syncthreads();
+        if (!misc[0]) return;
+        __threadfence();
+        if (threadIdx.x == 0) a.tile_counter[tile] = 0u;
+        for (int i = threadIdx.x; i < a.M * 16; i += blockDim.x) {
+            int m = i >> 4, n = tile * 16 + (i & 15);
+            __half acc = f2h(0.0f);
+            for (int k = 0; k < a.topk; ++k)
+                acc = hadd_rn(acc, hmul_rn(__ldcg(a.dbuf + (size_t)(m * a.topk + k) * a.H + n), a.scores[m * a.topk + k]));
+            __half res = hadd_rn(acc, hmul_rn(sigmoid_h(a.sgl[m]), __ldcg(a.dbuf + (size_t)(npair + m) * a.H + n)));
+            if (a.resid) a.resid[(size_t)m * a.H + n] = hadd_rn(a.resid[(size_t)m * a.H + n], res);
+            else a.out[(size_t)m * a.H + n] = res;
+        }
     }
 }
 template <bool EXACT, bool DOWN>
@@ -516,27 +564,6 @@ void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStrea
 }
 void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st) {
     if (exact) launch_expert_t<true, true>(a, nslots, st); else launch_expert_t<false, true>(a, nslots, st);
-}
-
-// weighted combine in fp16, ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate
-// logit) * shared (SeedlessFusedVerify.swift:474-484), + residual (SeedlessMetalForward.swift:1024-1028)
-__global__ void __launch_bounds__(256) k_moe_combine(CombineArgs a) {
-    const int m = blockIdx.x;
-    const int npair = a.M * a.topk;
-    const __half s = sigmoid_h(a.sgl[m]);
-    for (int n = threadIdx.x; n < a.H; n += blockDim.x) {
-        __half acc = f2h(0.0f);
-        for (int k = 0; k < a.topk; ++k)
-            acc = hadd_rn(acc, hmul_rn(a.dbuf[(size_t)(m * a.topk + k) * a.H + n], a.scores[m * a.topk + k]));
-        __half res = hadd_rn(acc, hmul_rn(s, a.dbuf[(size_t)(npair + m) * a.H + n]));
-        if (a.h) a.h[(size_t)m * a.H + n] = hadd_rn(a.h[(size_t)m * a.H + n], res);
-        else a.out[(size_t)m * a.H + n] = res;
-    }
-}
-void launch_combine(const CombineArgs& a, cudaStream_t st) {
-    ProfScope ps("k_moe_combine", (double)a.M * (a.topk + 3) * a.H * 2, st);
-    k_moe_combine<<<a.M, 256, 0, st>>>(a);
-    COUNT_LAUNCH();
 }
 
 // ============================================================================================

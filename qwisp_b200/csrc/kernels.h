@@ -36,11 +36,7 @@ struct RouterArgs {
     __half* p;                           // normed rows out [M][H]
     __half* logits;                      // [M][E]
     __half* sgl;                         // [M] shared-expert gate logit
-};
-
-struct RouteArgs {
-    const __half* logits; int M, E, topk;
-    int* inds; __half* scores;           // [M][topk]
+    int topk; int* inds; __half* scores; // [M][topk] routing result (written by the last CTA)
     MoeLists lists; unsigned* counter;
 };
 
@@ -52,13 +48,10 @@ struct ExpertArgs {
     __half* hbuf;                        // [(M*topk + M)][I]
     __half* dbuf;                        // [(M*topk + M)][H]
     int M, H, I, topk;
-};
-
-struct CombineArgs {
-    const __half* dbuf; const __half* scores; const __half* sgl;
-    __half* h;                           // residual stream (in place) or nullptr
-    __half* out;                         // plain output when h == nullptr
-    int M, H, topk;
+    const __half* scores; const __half* sgl;   // combine inputs (down kernel)
+    __half* resid;                       // residual stream updated in place, or nullptr ...
+    __half* out;                         // ... then the block output goes here
+    unsigned* tile_counter;              // [H/16] tickets, zero between launches
 };
 
 struct GdnArgs {
@@ -94,10 +87,8 @@ struct StepEndArgs {
 void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl);
 void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st);
 void launch_router(const RouterArgs& a, cudaStream_t st);
-void launch_route(const RouteArgs& a, cudaStream_t st);
 void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st);
 void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st);
-void launch_combine(const CombineArgs& a, cudaStream_t st);
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st);
 void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
 void launch_attn_decode(const AttnArgs& a, cudaStream_t st);

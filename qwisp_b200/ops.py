@@ -56,6 +56,22 @@ def mixer(stream, layer, x, pos0):
     return out
 
 
+def layer(stream, layer_index, h_in, pos0):
+    h_in = np.ascontiguousarray(h_in, dtype=np.float16)
+    out = np.empty_like(h_in)
+    stream.engine._check(lib().sl_op_layer(stream._h, layer_index, _p(h_in), h_in.shape[0], pos0, _p(out)), "sl_op_layer")
+    return out
+
+
+def head(engine, h_rows, want_logits=True):
+    h_rows = np.ascontiguousarray(h_rows, dtype=np.float16)
+    M = h_rows.shape[0]
+    logits = np.empty((M, engine.cfg.vocab), dtype=np.float16) if want_logits else None
+    toks = np.empty(M, dtype=np.int32)
+    engine._check(lib().sl_op_head(engine._h, _p(h_rows), M, _p(logits), _p(toks)), "sl_op_head")
+    return logits, toks
+
+
 def lm_head(engine, normed, want_logits=True):
     normed = np.ascontiguousarray(normed, dtype=np.float16)
     M = normed.shape[0]

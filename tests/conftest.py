@@ -53,7 +53,7 @@ def oracle_model(geom, seed=SEED):
 
 def gpu_engine(geom, seed=SEED, **kw):
     import qwisp_b200 as Q
-    args = dict(max_rows=64, max_streams=8, kv_page_size=32, kv_pages=64)
+    args = dict(max_rows=64, max_streams=48, kv_page_size=32, kv_pages=256)
     args.update(kw)
     cfg = Q.config(**geom, **args)
     return Q.Engine.synthetic(cfg, seed=seed, norm_jitter=JITTER, conv_std=CONV_STD)
