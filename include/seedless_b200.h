@@ -168,8 +168,13 @@ int32_t sl_batch_step_argmax(sl_engine* e, sl_stream* const* streams, const int3
 /* y[M,N] = x[M,K] . dequant4(W[N,K])^T; host buffers; N % 16 == 0, K % 256 == 0. */
 int32_t sl_op_qmm4(const uint16_t* x_f16, const uint32_t* w, const uint16_t* scales_f16, const uint16_t* biases_f16,
                    int32_t M, int32_t K, int32_t N, uint16_t* y_f16);
-/* Same on device buffers, enqueued on cuda_stream without synchronising (micro-benchmarks). */
-int32_t sl_op_qmm4_device(const void* x_dev, const void* w_dev, const void* s_dev, const void* b_dev,
+/* The kernels read weights in a fragment-major layout made once at load time from the MLX layout:
+ * wr holds (N/16) * (K/128) * 1024 bytes, sr holds (N/16) * (K/128) * 128 bytes (device buffers). */
+int32_t sl_op_repack_q4_device(const void* w_dev, const void* s_dev, const void* b_dev, int32_t K, int32_t N,
+                               void* wr_dev, void* sr_dev, void* cuda_stream);
+/* The GEMV on device buffers in that layout, enqueued on cuda_stream without synchronising
+ * (micro-benchmarks). */
+int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
                           int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream);
 /* 4-bit affine quantiser on the device: w fp16 [N,K] -> packed/scales/biases (host buffers). */
 int32_t sl_op_quantize_q4(const uint16_t* w_f16, int64_t N, int64_t K, uint32_t* packed, uint16_t* scales_f16, uint16_t* biases_f16);

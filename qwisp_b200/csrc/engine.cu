@@ -35,6 +35,8 @@ struct LayerW {
     const __half *q_norm = nullptr, *k_norm = nullptr;
     const __half *router = nullptr, *shared_gate = nullptr;
     Q4W gate, up, down, sh_gate, sh_up, sh_down;
+    // fragment-major copies the kernels read (gate/up fused into paired tiles)
+    Q4R r_in, r_out, r_gu, r_down, r_sh_gu, r_sh_down;
 };
 
 }  // namespace
@@ -50,7 +52,7 @@ struct sl_engine {
     std::vector<void*> allocs;
     std::vector<LayerW> layers;
     const __half *embed = nullptr, *final_norm = nullptr;
-    Q4W lm_head;
+    Q4W lm_head; Q4R r_lm_head;
     // scratch (sized by max_rows)
     __half *h = nullptr, *p = nullptr, *inproj = nullptr, *mix = nullptr, *rlogits = nullptr, *sgl = nullptr, *scores = nullptr;
     __half *hbuf = nullptr, *dbuf = nullptr, *normed = nullptr, *qrot = nullptr, *opx = nullptr, *opy = nullptr;
@@ -60,6 +62,7 @@ struct sl_engine {
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
     unsigned* counters = nullptr; unsigned* tile_counters = nullptr;
+    long long* dbg = nullptr;
     SegDesc* segs = nullptr;
     int hist_cap = 0;
     // pinned staging
@@ -73,6 +76,8 @@ struct sl_engine {
     std::map<int, cudaGraphExec_t> graphs;
     std::map<int, int> eager_runs;
     bool use_graph = true;
+    bool use_prefetch = true;       // L2 prefetch of the weights later kernels read
+    bool use_pdl = false;           // programmatic dependent launch between the GEMV-family kernels
     bool poisoned = false, inject = false;
     std::string fault;
 };
@@ -304,8 +309,39 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->kv_pool, (size_t)c.kv_pages * page_elems))) return rc;
     for (int i = c.kv_pages - 1; i >= 0; --i) e->free_pages.push_back(i);
     for (int i = S - 1; i >= 0; --i) e->free_slots.push_back(i);
+    if (getenv("SEEDLESS_DEBUG_TIMELINE")) { if ((rc = dalloc(e, &e->dbg, (size_t)64 * 8))) return rc; CU(e, cudaMemset(e->dbg, 0, 64 * 8 * 8)); }
+    const char* pfe = getenv("SEEDLESS_PREFETCH");
+    if (pfe) e->use_prefetch = (pfe[0] == '1');
+    const char* pd = getenv("SEEDLESS_PDL");
+    if (pd) e->use_pdl = (pd[0] == '1');
     const char* ng = getenv("SEEDLESS_NO_GRAPH");
     if (ng && ng[0] == '1') e->use_graph = false;
+    return SL_OK;
+}
+
+// allocate and fill the fragment-major copy of a (pair of) 4-bit tensor(s)
+int32_t repack(sl_engine* e, const Q4W& a, const Q4W* pair, Q4R& out) {
+    int64_t tiles = pair ? a.N / 8 : a.N / 16;
+    uint4 *wr, *sr; int32_t rc;
+    if ((rc = dalloc(e, &wr, (size_t)tiles * q4r_w_uint4(a.K)))) return rc;
+    if ((rc = dalloc(e, &sr, (size_t)tiles * q4r_s_uint4(a.K)))) return rc;
+    launch_repack_q4(a, pair, wr, sr, e->stream);
+    out.wr = wr; out.sr = sr; out.tiles = (int)tiles; out.K = a.K;
+    return SL_OK;
+}
+int32_t repack_all(sl_engine* e) {
+    int32_t rc;
+    if ((rc = repack(e, e->lm_head, nullptr, e->r_lm_head))) return rc;
+    for (LayerW& L : e->layers) {
+        if ((rc = repack(e, L.in_proj, nullptr, L.r_in))) return rc;
+        if ((rc = repack(e, L.out_proj, nullptr, L.r_out))) return rc;
+        if ((rc = repack(e, L.gate, &L.up, L.r_gu))) return rc;
+        if ((rc = repack(e, L.down, nullptr, L.r_down))) return rc;
+        if ((rc = repack(e, L.sh_gate, &L.sh_up, L.r_sh_gu))) return rc;
+        if ((rc = repack(e, L.sh_down, nullptr, L.r_sh_down))) return rc;
+    }
+    CU(e, cudaStreamSynchronize(e->stream));
+    CU(e, cudaGetLastError());
     return SL_OK;
 }
 
@@ -320,16 +356,20 @@ int32_t detect_gemv_mode() {
     if (cudaMalloc(&w, (size_t)N * K / 2) != cudaSuccess) return SL_ERR_CUDA;
     cudaMalloc(&s, (size_t)N * K / 64 * 2); cudaMalloc(&b, (size_t)N * K / 64 * 2);
     cudaMalloc(&x, (size_t)M * K * 2); cudaMalloc(&y0, (size_t)M * N * 2); cudaMalloc(&y1, (size_t)M * N * 2);
+    uint4 *wr, *sr;
+    cudaMalloc(&wr, (size_t)(N / 16) * q4r_w_uint4(K) * 16); cudaMalloc(&sr, (size_t)(N / 16) * q4r_s_uint4(K) * 16);
     launch_synth_q4(tensor_seed(7, "selftest.w"), N, K, 0.02f, w, s, b, 0);
     launch_synth_f16(tensor_seed(7, "selftest.x"), (int64_t)M * K, 0.f, 1.f, x, 0);
-    DenseArgs a{}; a.w = w; a.s = s; a.b = b; a.N = N; a.K = K; a.M = M; a.x = x; a.ldx = K; a.ldy = N;
+    Q4W qw; qw.w = w; qw.s = s; qw.b = b; qw.N = N; qw.K = K;
+    launch_repack_q4(qw, nullptr, wr, sr, 0);
+    DenseArgs a{}; a.q.wr = wr; a.q.sr = sr; a.q.tiles = N / 16; a.q.K = K; a.N = N; a.K = K; a.M = M; a.x = x; a.ldx = K; a.ldy = N;
     a.y = y0; launch_dense(PRO_PLAIN, EPI_STORE, false, a, 0, false);
     a.y = y1; launch_dense(PRO_PLAIN, EPI_STORE, true, a, 0, false);
     std::vector<__half> h0((size_t)M * N), h1((size_t)M * N);
     cudaError_t err = cudaDeviceSynchronize();
     cudaMemcpy(h0.data(), y0, h0.size() * 2, cudaMemcpyDeviceToHost);
     cudaMemcpy(h1.data(), y1, h1.size() * 2, cudaMemcpyDeviceToHost);
-    cudaFree(w); cudaFree(s); cudaFree(b); cudaFree(x); cudaFree(y0); cudaFree(y1);
+    cudaFree(w); cudaFree(s); cudaFree(b); cudaFree(x); cudaFree(y0); cudaFree(y1); cudaFree(wr); cudaFree(sr);
     if (err != cudaSuccess) return SL_ERR_CUDA;
     float maxd = 0.f, maxv = 0.f;
     for (size_t i = 0; i < h0.size(); ++i) {
@@ -349,19 +389,29 @@ int32_t finish_create(sl_engine* e) {
 // ---------------------------------------------------------------- the forward pass
 enum HeadMode { HEAD_NONE = 0, HEAD_NORMED = 1, HEAD_ARGMAX = 2, HEAD_LOGITS = 3 };
 
-void enqueue_moe(sl_engine* e, const LayerW& L, const __half* rows, int ld, bool apply_norm, int M, __half* resid, __half* plain_out) {
+void pf_q4(PfList& pf, int i, const Q4R& q, size_t max_bytes = (size_t)48 << 20) {
+    size_t wb = (size_t)q.tiles * q4r_w_uint4(q.K) * 16, gb = (size_t)q.tiles * q4r_s_uint4(q.K) * 16;
+    if (wb > max_bytes) { wb = max_bytes; gb = 0; }
+    pf.p[i] = q.wr; pf.bytes[i] = (unsigned)wb;
+    if (i + 1 < 6 && gb) { pf.p[i + 1] = q.sr; pf.bytes[i + 1] = (unsigned)gb; }
+}
+
+// next: the layer after L (nullptr after the last one, where the lm_head follows)
+void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half* rows, int ld, bool apply_norm, int M, __half* resid, __half* plain_out) {
     cudaStream_t st = e->stream;
     RouterArgs ra{}; ra.h = rows; ra.ldh = ld; ra.norm_w = apply_norm ? L.post_norm : nullptr; ra.eps = e->cfg.rms_eps;
     ra.router = L.router; ra.shared_gate = L.shared_gate; ra.M = M; ra.H = e->H; ra.E = e->E;
     ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
     ra.topk = e->topk; ra.inds = e->inds; ra.scores = e->scores; ra.lists = e->lists; ra.counter = e->counters + 1;
-    launch_router(ra, st);
-    ExpertArgs ea{}; ea.gate = L.gate; ea.up = L.up; ea.down = L.down; ea.sh_gate = L.sh_gate; ea.sh_up = L.sh_up; ea.sh_down = L.sh_down;
+    ra.dbg = e->dbg;
+    launch_router(ra, st, e->use_pdl);
+    ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
     ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = M; ea.H = e->H; ea.I = e->I; ea.topk = e->topk;
     ea.scores = e->scores; ea.sgl = e->sgl; ea.resid = resid; ea.out = plain_out; ea.tile_counter = e->tile_counters;
+    if (e->use_prefetch) { if (next) pf_q4(ea.pf, 0, next->r_in); else pf_q4(ea.pf, 0, e->r_lm_head, (size_t)24 << 20); }
     int nslots = M * e->topk < e->E ? M * e->topk : e->E;
-    launch_expert_gateup(e->exact, ea, nslots, st);
-    launch_expert_down(e->exact, ea, nslots, st);
+    launch_expert_gateup(e->exact, ea, nslots, st, e->use_pdl);
+    launch_expert_down(e->exact, ea, nslots, st, e->use_pdl);
 }
 
 // mixer of one layer: input rows are normed inside (norm_w != nullptr) or already normed
@@ -369,17 +419,23 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
                    __half* resid, __half* plain_out, const int* row_pos_override) {
     cudaStream_t st = e->stream;
     const sl_config& c = e->cfg;
-    DenseArgs d{}; d.w = L.in_proj.w; d.s = L.in_proj.s; d.b = L.in_proj.b; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
+    DenseArgs d{}; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
     d.x = rows; d.ldx = e->H; d.nw = norm_w; d.eps = c.rms_eps; d.y = e->inproj; d.ldy = (int)L.in_proj.N;
-    launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, e->exact, d, st, false);
-    DenseArgs o{}; o.w = L.out_proj.w; o.s = L.out_proj.s; o.b = L.out_proj.b; o.N = e->H; o.K = L.out_proj.K; o.M = M;
+    if (e->use_prefetch) pf_q4(d.pf, 0, L.r_out);
+    launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, e->exact, d, st, e->use_pdl);
+    DenseArgs o{}; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
     o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H;
+    if (e->use_prefetch) {
+        o.pf.p[0] = L.router; o.pf.bytes[0] = (unsigned)((size_t)e->E * e->H * 2);
+        pf_q4(o.pf, 1, L.r_sh_gu);
+        pf_q4(o.pf, 3, L.r_sh_down);
+    }
     if (!L.is_attn) {
         GdnArgs g{}; g.inproj = e->inproj; g.ld = e->gdn_in; g.conv_w = L.conv_w; g.A_log = L.A_log; g.dt_bias = L.dt_bias;
         g.Hk = c.gdn_k_heads; g.Hv = c.gdn_v_heads; g.eps = c.rms_eps; g.tab = e->tab; g.gdn_index = L.type_index; g.segs = e->segs; g.y = e->mix;
-        launch_gdn_core(g, nsegs, st);
+        launch_gdn_core(g, nsegs, st, e->use_pdl);
         o.x = e->mix; o.ldx = e->valDim; o.nw = L.gdn_norm; o.z = e->inproj + e->convDim; o.ldz = e->gdn_in;
-        launch_dense(PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, false);
+        launch_dense(PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, e->use_pdl);
     } else {
         AttnArgs a{}; a.inproj = e->inproj; a.ld = e->attn_in; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.NH = c.attn_heads; a.KV = c.attn_kv_heads;
         a.eps = c.rms_eps; a.theta = c.rope_theta; a.tab = e->tab; a.attn_index = L.type_index; a.n_attn_layers = e->n_attn > 0 ? e->n_attn : 1;
@@ -389,7 +445,7 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
         launch_attn_decode(a, st);
         launch_attn_combine(a, st);
         o.x = e->mix; o.ldx = e->attn_out;
-        launch_dense(PRO_PLAIN, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, false);
+        launch_dense(PRO_PLAIN, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, e->use_pdl);
     }
 }
 
@@ -397,17 +453,18 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
 void enqueue_step(sl_engine* e, int M, int nsegs, HeadMode head, bool want_logits) {
     cudaStream_t st = e->stream;
     launch_embed(e->embed, e->tok_in, M, e->H, e->V, e->h, st);
-    for (const LayerW& L : e->layers) {
+    for (size_t li = 0; li < e->layers.size(); ++li) {
+        const LayerW& L = e->layers[li];
         enqueue_mixer(e, L, e->h, L.in_norm, M, nsegs, e->h, nullptr, nullptr);
-        enqueue_moe(e, L, e->h, e->H, true, M, e->h, nullptr);
+        enqueue_moe(e, L, li + 1 < e->layers.size() ? &e->layers[li + 1] : nullptr, e->h, e->H, true, M, e->h, nullptr);
     }
     if (head == HEAD_NORMED) {
         launch_final_norm(e->h, e->final_norm, e->cfg.rms_eps, M, e->H, e->normed, st);
     } else if (head == HEAD_ARGMAX || head == HEAD_LOGITS) {
-        DenseArgs d{}; d.w = e->lm_head.w; d.s = e->lm_head.s; d.b = e->lm_head.b; d.N = e->V; d.K = e->H; d.M = M;
+        DenseArgs d{}; d.q = e->r_lm_head; d.N = e->V; d.K = e->H; d.M = M;
         d.x = e->h; d.ldx = e->H; d.nw = e->final_norm; d.eps = e->cfg.rms_eps;
         d.logits = want_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
-        launch_dense(PRO_RMSNORM, EPI_ARGMAX, e->exact, d, st, false);
+        launch_dense(PRO_RMSNORM, EPI_ARGMAX, e->exact, d, st, e->use_pdl);
     }
     StepEndArgs se{}; se.tab = e->tab; se.segs = e->segs; se.nsegs = nsegs; se.M = M;
     se.out_tok = (head == HEAD_ARGMAX || head == HEAD_LOGITS) ? e->out_tok : nullptr;
@@ -548,6 +605,7 @@ int32_t sl_engine_create(const sl_config* cfg, const sl_weight_desc* weights, in
         seen[d.name] = true;
     }
     if (seen.size() != e->tensors.size()) { sl_engine_destroy(e); return SL_ERR_INVALID; }   // every tensor must be given
+    if ((rc = repack_all(e))) { sl_engine_destroy(e); return rc; }
     *out = e;
     return SL_OK;
 }
@@ -581,6 +639,7 @@ int32_t sl_engine_create_synthetic(const sl_config* cfg, const sl_synth_spec* sy
         }
     }
     if (cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess) { sl_engine_destroy(e); return SL_ERR_CUDA; }
+    if ((rc = repack_all(e))) { sl_engine_destroy(e); return rc; }
     *out = e;
     return SL_OK;
 }
@@ -613,6 +672,11 @@ int32_t sl_engine_read_tensor(sl_engine* e, const char* name, void* host_buf, ui
 const char* sl_last_fault(sl_engine* e) { return (e && e->poisoned) ? e->fault.c_str() : nullptr; }
 int32_t sl_inject_fault(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->inject = on != 0; return SL_OK; }
 int64_t sl_engine_launch_count(sl_engine* e) { (void)e; return kernel_launch_count(); }
+int32_t sl_debug_read(sl_engine* e, long long* out, int32_t n) {
+    if (!e || !e->dbg || !out || n > 64 * 8) return SL_ERR_INVALID;
+    cudaStreamSynchronize(e->stream);
+    return cudaMemcpy(out, e->dbg, (size_t)n * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? SL_OK : SL_ERR_CUDA;
+}
 int32_t sl_engine_use_graphs(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->use_graph = on != 0; return SL_OK; }
 int32_t sl_profile_start(sl_engine* e) { if (!e) return SL_ERR_INVALID; cudaStreamSynchronize(e->stream); profile_start(); return SL_OK; }
 int32_t sl_profile_report(sl_engine* e, char* buf, uint64_t cap) {
@@ -889,13 +953,22 @@ int32_t sl_state_restore(sl_stream* s, const void* buf, uint64_t nbytes) {
 }
 
 // ---- single operators ----
-int32_t sl_op_qmm4_device(const void* x_dev, const void* w_dev, const void* s_dev, const void* b_dev,
+int32_t sl_op_repack_q4_device(const void* w_dev, const void* s_dev, const void* b_dev, int32_t K, int32_t N,
+                               void* wr_dev, void* sr_dev, void* cuda_stream) {
+    if (!w_dev || !s_dev || !b_dev || !wr_dev || !sr_dev) return SL_ERR_INVALID;
+    if (N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (!device_ok()) return SL_ERR_NO_DEVICE;
+    Q4W q; q.w = (const uint32_t*)w_dev; q.s = (const __half*)s_dev; q.b = (const __half*)b_dev; q.N = N; q.K = K;
+    launch_repack_q4(q, nullptr, (uint4*)wr_dev, (uint4*)sr_dev, (cudaStream_t)cuda_stream);
+    return cudaGetLastError() == cudaSuccess ? SL_OK : SL_ERR_CUDA;
+}
+int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
                           int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream) {
-    if (!x_dev || !w_dev || !s_dev || !b_dev || !y_dev) return SL_ERR_INVALID;
+    if (!x_dev || !wr_dev || !sr_dev || !y_dev) return SL_ERR_INVALID;
     if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
     if (!device_ok()) return SL_ERR_NO_DEVICE;
     if (detect_gemv_mode() != SL_OK) return SL_ERR_CUDA;
-    DenseArgs a{}; a.w = (const uint32_t*)w_dev; a.s = (const __half*)s_dev; a.b = (const __half*)b_dev; a.N = N; a.K = K; a.M = M;
+    DenseArgs a{}; a.q.wr = (const uint4*)wr_dev; a.q.sr = (const uint4*)sr_dev; a.q.tiles = N / 16; a.q.K = K; a.N = N; a.K = K; a.M = M;
     a.x = (const __half*)x_dev; a.ldx = K; a.y = (__half*)y_dev; a.ldy = N;
     launch_dense(PRO_PLAIN, EPI_STORE, g_gemv_mode == 1, a, (cudaStream_t)cuda_stream, false);
     return cudaGetLastError() == cudaSuccess ? SL_OK : SL_ERR_CUDA;
@@ -904,17 +977,19 @@ int32_t sl_op_qmm4(const uint16_t* x, const uint32_t* w, const uint16_t* sc, con
     if (!x || !w || !sc || !bi || !y) return SL_ERR_INVALID;
     if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
     if (!device_ok()) return SL_ERR_NO_DEVICE;
-    void *dx = nullptr, *dw = nullptr, *ds = nullptr, *db = nullptr, *dy = nullptr;
+    void *dx = nullptr, *dw = nullptr, *ds = nullptr, *db = nullptr, *dy = nullptr, *dwr = nullptr, *dsr = nullptr;
     size_t bx = (size_t)M * K * 2, bw = (size_t)N * K / 2, bs = (size_t)N * K / 64 * 2, by = (size_t)M * N * 2;
+    size_t bwr = (size_t)(N / 16) * q4r_w_uint4(K) * 16, bsr = (size_t)(N / 16) * q4r_s_uint4(K) * 16;
     int32_t rc = SL_ERR_CUDA;
     if (cudaMalloc(&dx, bx) == cudaSuccess && cudaMalloc(&dw, bw) == cudaSuccess && cudaMalloc(&ds, bs) == cudaSuccess &&
-        cudaMalloc(&db, bs) == cudaSuccess && cudaMalloc(&dy, by) == cudaSuccess) {
+        cudaMalloc(&db, bs) == cudaSuccess && cudaMalloc(&dy, by) == cudaSuccess && cudaMalloc(&dwr, bwr) == cudaSuccess && cudaMalloc(&dsr, bsr) == cudaSuccess) {
         cudaMemcpy(dx, x, bx, cudaMemcpyHostToDevice); cudaMemcpy(dw, w, bw, cudaMemcpyHostToDevice);
         cudaMemcpy(ds, sc, bs, cudaMemcpyHostToDevice); cudaMemcpy(db, bi, bs, cudaMemcpyHostToDevice);
-        rc = sl_op_qmm4_device(dx, dw, ds, db, M, K, N, dy, nullptr);
+        rc = sl_op_repack_q4_device(dw, ds, db, K, N, dwr, dsr, nullptr);
+        if (rc == SL_OK) rc = sl_op_qmm4_device(dx, dwr, dsr, M, K, N, dy, nullptr);
         if (rc == SL_OK && cudaMemcpy(y, dy, by, cudaMemcpyDeviceToHost) != cudaSuccess) rc = SL_ERR_CUDA;
     }
-    cudaFree(dx); cudaFree(dw); cudaFree(ds); cudaFree(db); cudaFree(dy);
+    cudaFree(dx); cudaFree(dw); cudaFree(ds); cudaFree(db); cudaFree(dy); cudaFree(dwr); cudaFree(dsr);
     cudaGetLastError();
     return rc;
 }
@@ -939,7 +1014,7 @@ int32_t sl_op_moe_block(sl_engine* e, int32_t layer, const uint16_t* x, int32_t 
     if (!x || !out || layer < 0 || layer >= e->cfg.n_layers || M <= 0) return SL_ERR_INVALID;
     if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
     CU(e, cudaMemcpyAsync(e->opx, x, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
-    enqueue_moe(e, e->layers[layer], e->opx, e->H, false, M, nullptr, e->opy);
+    enqueue_moe(e, e->layers[layer], nullptr, e->opx, e->H, false, M, nullptr, e->opy);
     CU(e, cudaMemcpyAsync(out, e->opy, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
     if (inds) CU(e, cudaMemcpyAsync(inds, e->inds, (size_t)M * e->topk * 4, cudaMemcpyDeviceToHost, e->stream));
     if (scores) CU(e, cudaMemcpyAsync(scores, e->scores, (size_t)M * e->topk * 2, cudaMemcpyDeviceToHost, e->stream));
@@ -990,7 +1065,7 @@ int32_t sl_op_layer(sl_stream* s, int32_t layer, const uint16_t* h_in, int32_t M
     CU(e, cudaStreamSynchronize(e->stream));
     const LayerW& L = e->layers[layer];
     enqueue_mixer(e, L, e->h, L.in_norm, M, 1, e->h, nullptr, e->row_pos);
-    enqueue_moe(e, L, e->h, e->H, true, M, e->h, nullptr);
+    enqueue_moe(e, L, nullptr, e->h, e->H, true, M, e->h, nullptr);
     if (!L.is_attn) {
         size_t sc = e->tab.state_stride_layer, cc = e->tab.hist_stride_layer;
         float* cur = cur_state(s) + (size_t)L.type_index * sc;
@@ -1012,7 +1087,7 @@ int32_t sl_op_head(sl_engine* e, const uint16_t* h_rows, int32_t M, uint16_t* ou
         e->logits = lg; e->logits_rows = e->cfg.max_rows;
     }
     CU(e, cudaMemcpyAsync(e->opx, h_rows, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
-    DenseArgs d{}; d.w = e->lm_head.w; d.s = e->lm_head.s; d.b = e->lm_head.b; d.N = e->V; d.K = e->H; d.M = M;
+    DenseArgs d{}; d.q = e->r_lm_head; d.N = e->V; d.K = e->H; d.M = M;
     d.x = e->opx; d.ldx = e->H; d.nw = e->final_norm; d.eps = e->cfg.rms_eps;
     d.logits = out_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
     launch_dense(PRO_RMSNORM, EPI_ARGMAX, e->exact, d, e->stream, false);
@@ -1029,7 +1104,7 @@ int32_t sl_op_lm_head(sl_engine* e, const uint16_t* normed, int32_t M, uint16_t*
         e->logits = lg; e->logits_rows = e->cfg.max_rows;
     }
     CU(e, cudaMemcpyAsync(e->opx, normed, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
-    DenseArgs d{}; d.w = e->lm_head.w; d.s = e->lm_head.s; d.b = e->lm_head.b; d.N = e->V; d.K = e->H; d.M = M;
+    DenseArgs d{}; d.q = e->r_lm_head; d.N = e->V; d.K = e->H; d.M = M;
     d.x = e->opx; d.ldx = e->H; d.logits = out_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
     launch_dense(PRO_PLAIN, EPI_ARGMAX, e->exact, d, e->stream, false);
     if (out_logits) CU(e, cudaMemcpyAsync(out_logits, e->logits, (size_t)M * e->V * 2, cudaMemcpyDeviceToHost, e->stream));

@@ -1,5 +1,4 @@
 // kernels.cu -- the Seedless decode kernels for sm_100a and their launchers.
-#include "gemv.cuh"
 #include "kernels.h"
 
 #include <atomic>
@@ -53,166 +52,252 @@ int profile_report(char* buf, size_t cap) {
 }
 
 // ============================================================================================
-// Dense q4 GEMV: one CTA = 16 weight rows x all K (slices across warps) x up to 8 activation rows.
-// grid (N/16 [N/8 tiles of 8+8 for the SwiGLU pairing], ceil(M/8)).
+// Dense q4 GEMV, split flavour: a CTA holds TPC tiles of 16 weight rows, WPT warps share a tile's
+// K/256 slices (see gemv_plan), up to 8 activation rows per pass.  grid (ceil(tiles/TPC), ceil(M/8)).
+// Weights are requested before the grid dependency is awaited, so under programmatic dependent
+// launch their latency overlaps the tail of the previous kernel.
 // ============================================================================================
-template <int PRO, int EPI, bool EXACT>
-__global__ void __launch_bounds__(512) k_dense(DenseArgs a) {
+template <int PRO, int EPI, bool EXACT, int SPW>
+__global__ void __launch_bounds__(SPW == 2 ? 256 : 512, SPW == 2 ? 3 : 1) k_gemv(DenseArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
-    const int row0 = blockIdx.y * 8;
-    const int mr = min(8, a.M - row0);
+    const int slices = a.K >> 8;
+    const int WPT = slices / SPW, TPC = nw / WPT;
+    const int row0 = blockIdx.y * ROWS_PER_PASS;
+    const int mr = min(ROWS_PER_PASS, a.M - row0);
     XStage st; float* red; float* fin; int* misc;
-    GemvSmem::carve(smem, min(a.M, 8), a.K, nw, st, red, fin, misc);
+    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), a.K, TPC * slices, TPC, st, red, fin, misc);
 
-    const int tile = blockIdx.x;
-    const int K8 = a.K >> 3, KG = a.K >> 6, slices = a.K >> 8;
-    const uint32_t *wA, *wB; const __half *sA, *bA, *sB, *bB;
-    if (EPI == EPI_SWIGLU) {
-        int64_t row = (int64_t)tile * 8 + r;
-        wA = a.w + row * K8; sA = a.s + row * KG; bA = a.b + row * KG;
-        wB = a.w2 + row * K8; sB = a.s2 + row * KG; bB = a.b2 + row * KG;
-    } else {
-        int64_t row = (int64_t)tile * 16 + r;
-        wA = a.w + row * K8; sA = a.s + row * KG; bA = a.b + row * KG;
-        wB = wA + 8 * (int64_t)K8; sB = sA + 8 * KG; bB = bA + 8 * KG;
-    }
-    // weights do not depend on the activations: get them in flight before staging
-    SliceRegs regs;
-    int sl_i = warp;
-    bool have = sl_i < slices;
-    if (have) load_slice(regs, wA, wB, sA, bA, sB, bB, sl_i, t);
-
-    if (PRO == PRO_PLAIN) stage_plain(st, a.x, a.ldx, row0, mr, a.K);
-    else if (PRO == PRO_RMSNORM) stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K);
-    else stage_normgate(st, a.x, a.ldx, a.z, a.ldz, a.nw, a.eps, row0, mr, a.K);
-    __syncthreads();
-
-    float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
-    while (have) {
-        compute_slice<EXACT>(regs, st, sl_i, r, t, r < mr, accS, accB);
-        sl_i += nw; have = sl_i < slices;
-        if (have) load_slice(regs, wA, wB, sA, bA, sB, bB, sl_i, t);
-    }
-    float v[4];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tl = warp / WPT, part = warp - tl * WPT;
+    const int tile = blockIdx.x * TPC + tl;
+    const int ntiles = (EPI == EPI_SWIGLU) ? a.N / 8 : a.N / 16;
+    const bool valid = tile < ntiles;
+    // activations first, then the weights, then wait for the activations (see stage_issue)
+    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
+    StageRegs sregs;
+    stage_issue<PRO>(sregs, src, row0, mr, a.K);
+    SliceRegs regs[SPW];
+    if (valid) {
+        const uint4* wt = a.q.wr + (size_t)tile * q4r_w_uint4(a.K);
+        const uint4* stl = a.q.sr + (size_t)tile * q4r_s_uint4(a.K);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = finish_acc<EXACT>(accS[i], accB[i]);
-    reduce_tile(red, fin, v, nw);
-
+        for (int i = 0; i < SPW; ++i) load_slice(regs[i], wt, stl, part * SPW + i, lane);
+    }
+    if (blockIdx.y == 0) prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
+    stage_finish<PRO>(sregs, st, src, mr, a.K);
+    __syncthreads();
+    if (valid) {
+#pragma unroll
+        for (int i = 0; i < SPW; ++i) {
+            float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+            compute_slice(regs[i], st, part * SPW + i, r, t, mr, accS, accB);
+            finish_acc4(accS, accB, t, v);
+            store_partial(red, tl * slices + part * SPW + i, lane, v);
+        }
+    }
+    __syncthreads();
+    reduce_tiles(red, fin, TPC, slices);
+    __syncthreads();
     if (EPI == EPI_STORE || EPI == EPI_RESID) {
-        for (int i = threadIdx.x; i < 128; i += blockDim.x) {
-            int col = i >> 4, row = i & 15;
-            if (col < mr) {
-                size_t idx = (size_t)(row0 + col) * a.ldy + tile * 16 + row;
-                __half val = f2h(fin[row * 8 + col]);
+        for (int i = threadIdx.x; i < TPC * 32; i += blockDim.x) {
+            int tl2 = i >> 5, col = (i >> 4) & 1, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
+            if (tile2 < ntiles && col < mr) {
+                size_t idx = (size_t)(row0 + col) * a.ldy + tile2 * 16 + row;
+                __half val = f2h(tile_value(fin + tl2 * 128, row, col));
                 if (EPI == EPI_RESID) val = hadd_rn(a.y[idx], val);
                 a.y[idx] = val;
             }
         }
-    } else if (EPI == EPI_SWIGLU) {
-        for (int j = threadIdx.x; j < 64; j += blockDim.x) {
-            int col = j >> 3, i = j & 7;
-            if (col < mr) {
-                __half g = f2h(fin[i * 8 + col]), u = f2h(fin[(i + 8) * 8 + col]);
-                a.y[(size_t)(row0 + col) * a.ldy + tile * 8 + i] = swiglu_h(g, u);
+    } else {   // EPI_SWIGLU
+        for (int j = threadIdx.x; j < TPC * 16; j += blockDim.x) {
+            int tl2 = j >> 4, col = (j >> 3) & 1, i = j & 7, tile2 = blockIdx.x * TPC + tl2;
+            if (tile2 < ntiles && col < mr) {
+                __half g = f2h(tile_value(fin + tl2 * 128, i, col)), u = f2h(tile_value(fin + tl2 * 128, i + 8, col));
+                a.y[(size_t)(row0 + col) * a.ldy + tile2 * 8 + i] = swiglu_h(g, u);
             }
         }
-    } else {  // EPI_ARGMAX: fp16 logits, per-tile first-index maximum, last block reduces all tiles
-        const int tiles = gridDim.x;
-        if (a.logits)
-            for (int i = threadIdx.x; i < 128; i += blockDim.x) {
-                int col = i >> 4, row = i & 15;
-                if (col < mr) a.logits[(size_t)(row0 + col) * a.N + tile * 16 + row] = f2h(fin[row * 8 + col]);
-            }
-        if (threadIdx.x < 8 && (int)threadIdx.x < mr) {
-            int col = threadIdx.x;
-            float best = -INFINITY; int bi = 0x7fffffff;
-            for (int row = 0; row < 16; ++row) {
-                float lv = h2f(f2h(fin[row * 8 + col]));
-                if (lv > best) { best = lv; bi = tile * 16 + row; }
-            }
-            a.pval[(size_t)(row0 + col) * tiles + tile] = best;
-            a.pidx[(size_t)(row0 + col) * tiles + tile] = bi;
-        }
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned total = gridDim.x * gridDim.y;
-            unsigned ticket = atomicAdd(a.counter, 1u);
-            misc[0] = (ticket == total - 1) ? 1 : 0;
-        }
-        __syncthreads();
-        if (misc[0]) {
-            __threadfence();
-            float* rv = red; int* ri = reinterpret_cast<int*>(fin);   // red has >= 128 floats per warp
-            for (int m = 0; m < a.M; ++m) {
-                float best = -INFINITY; int bi = 0x7fffffff;
-                for (int tl = threadIdx.x; tl < tiles; tl += blockDim.x) {
-                    float lv = __ldcg(a.pval + (size_t)m * tiles + tl); int li = __ldcg(a.pidx + (size_t)m * tiles + tl);
-                    if (lv > best || (lv == best && li < bi)) { best = lv; bi = li; }
-                }
+    }
+}
+
+// ============================================================================================
+// lm_head + greedy argmax, streaming flavour: a warp owns whole tiles (all K), walks its tiles with
+// the next slice's weights always in flight, and keeps a running first-index maximum per activation
+// row; CTAs are persistent.  Only per-CTA (value, index) partials and, at the end, one int32 per
+// row leave the kernel (logits are written only on request).  grid (<= 148*3, ceil(M/8)), 256 threads.
+// (argmax rule: swift/Sources/QwispCore/SeedlessFusedVerify.swift:572-596)
+// ============================================================================================
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+template <int PRO, bool EXACT>
+__global__ void __launch_bounds__(256) k_head(DenseArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, t = lane & 3;
+    const int slices = a.K >> 8, ntiles = a.N / 16;
+    const int row0 = blockIdx.y * ROWS_PER_PASS;
+    const int mr = min(ROWS_PER_PASS, a.M - row0);
+    XStage st; float* red; float* fin; int* misc;
+    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), a.K, 1, 1, st, red, fin, misc);      // red: [8 warps][2 rows] values, fin: indices
+    const int stride = gridDim.x * nw;
+    int tile = blockIdx.x * nw + warp;
+    bool have = tile < ntiles;
+    SliceRegs cur, nxt;
+    const size_t wstep = q4r_w_uint4(a.K), sstep = q4r_s_uint4(a.K);
+    auto load = [&](SliceRegs& rg, int tl, int sl_i) { load_slice(rg, a.q.wr + (size_t)tl * wstep, a.q.sr + (size_t)tl * sstep, sl_i, lane); };
+    pdl_launch_dependents();
+    pdl_wait();
+    if (PRO == PRO_PLAIN) stage_plain(st, a.x, a.ldx, row0, mr, a.K);
+    else stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K);
+    if (have) load(cur, tile, 0);
+    __syncthreads();
+    float best[2] = {-INFINITY, -INFINITY}; int besti[2] = {0x7fffffff, 0x7fffffff};
+    while (have) {
+        float tot[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int sidx = 0; sidx < slices; ++sidx) {
+            int ns = sidx + 1, ntile = tile;
+            if (ns == slices) { ns = 0; ntile = tile + stride; }
+            if (ntile < ntiles) load(nxt, ntile, ns);
+            float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
+            compute_slice(cur, st, sidx, r, t, mr, accS, accB);
+            float v[4];
+            finish_acc4(accS, accB, t, v);
 #pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) {
-                    float ov = __shfl_xor_sync(0xffffffffu, best, off); int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-                    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-                }
-                __syncthreads();
-                if (lane == 0) { rv[warp] = best; ri[warp] = bi; }
-                __syncthreads();
-                if (threadIdx.x == 0) {
-                    for (int w = 1; w < nw; ++w) if (rv[w] > best || (rv[w] == best && ri[w] < bi)) { best = rv[w]; bi = ri[w]; }
-                    a.out_tok[m] = bi;
+            for (int j = 0; j < 4; ++j) tot[j] += v[j];
+            cur = nxt;
+        }
+        // gather the six term columns of rows A and B from lanes t = 0,1,2 and add them in column order
+        const int base = lane & ~3;
+        float cA[6], cB[6];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+            cA[2 * q] = __shfl_sync(0xffffffffu, tot[0], base + q); cA[2 * q + 1] = __shfl_sync(0xffffffffu, tot[1], base + q);
+            cB[2 * q] = __shfl_sync(0xffffffffu, tot[2], base + q); cB[2 * q + 1] = __shfl_sync(0xffffffffu, tot[3], base + q);
+        }
+        if (t == 0) {
+#pragma unroll
+            for (int j = 0; j < ROWS_PER_PASS; ++j) {
+                if (j < mr) {
+#pragma unroll
+                    for (int hb = 0; hb < 2; ++hb) {
+                        const float* cc = hb ? cB : cA;
+                        int row = tile * 16 + r + 8 * hb;
+                        __half hv = f2h((cc[3 * j] + cc[3 * j + 1]) + cc[3 * j + 2]);
+                        if (a.logits) a.logits[(size_t)(row0 + j) * a.N + row] = hv;
+                        float lv = h2f(hv);
+                        if (better(lv, row, best[j], besti[j])) { best[j] = lv; besti[j] = row; }
+                    }
                 }
             }
-            if (threadIdx.x == 0) *a.counter = 0u;
         }
+        tile += stride; have = tile < ntiles;
     }
+    // lanes with t == 0 hold the running maxima of both pass-rows: merge over r (xor 4, 8, 16), then over warps
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int off = 4; off <= 16; off <<= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best[j], off); int oi = __shfl_xor_sync(0xffffffffu, besti[j], off);
+            if (better(ov, oi, best[j], besti[j])) { best[j] = ov; besti[j] = oi; }
+        }
+    int* fini = reinterpret_cast<int*>(fin);
+    if (lane == 0) { red[warp * 2] = best[0]; red[warp * 2 + 1] = best[1]; fini[warp * 2] = besti[0]; fini[warp * 2 + 1] = besti[1]; }
+    __syncthreads();
+    const int parts = gridDim.x;
+    if ((int)threadIdx.x < mr) {
+        int col = threadIdx.x; float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int w = 0; w < nw; ++w) if (better(red[w * 2 + col], fini[w * 2 + col], bv, bi)) { bv = red[w * 2 + col]; bi = fini[w * 2 + col]; }
+        a.pval[(size_t)(row0 + col) * parts + blockIdx.x] = bv;
+        a.pidx[(size_t)(row0 + col) * parts + blockIdx.x] = bi;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned total = gridDim.x * gridDim.y;
+        unsigned ticket = atomicAdd(a.counter, 1u);
+        misc[0] = (ticket == total - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!misc[0]) return;
+    __threadfence();
+    for (int m = warp; m < a.M; m += nw) {          // one warp per row over the per-CTA partials
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int p = lane; p < parts; p += 32) {
+            float lv = __ldcg(a.pval + (size_t)m * parts + p); int li = __ldcg(a.pidx + (size_t)m * parts + p);
+            if (better(lv, li, bv, bi)) { bv = lv; bi = li; }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, off); int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) a.out_tok[m] = bi;
+    }
+    if (threadIdx.x == 0) *a.counter = 0u;
 }
 
-size_t dense_smem_bytes(int M, int K) {
-    int nw = K / 256; if (nw > 16) nw = 16;
-    return GemvSmem::bytes(M < 8 ? M : 8, K, nw);
+static void set_pdl(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, bool pdl) {
+    if (!pdl) return;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
 }
 
-template <int PRO, int EPI, bool EXACT>
-static void launch_dense_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
-    int nw = a.K / 256; if (nw > 16) nw = 16;
-    size_t smem = GemvSmem::bytes(a.M < 8 ? a.M : 8, a.K, nw);
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaFuncSetAttribute(k_dense<PRO, EPI, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(96 * 1024));
-        configured = 96 * 1024;
-    }
-    dim3 grid((unsigned)(EPI == EPI_SWIGLU ? a.N / 8 : a.N / 16), (unsigned)((a.M + 7) / 8));
+template <int PRO, int EPI, bool EXACT, int SPW>
+static void launch_gemv_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
+    GemvPlan pl = gemv_plan(a.K);
+    int slices = a.K / 256;
+    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, pl.tpc * slices, pl.tpc);
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_gemv<PRO, EPI, EXACT, SPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
+    int ntiles = EPI == EPI_SWIGLU ? a.N / 8 : a.N / 16;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = dim3(nw * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS));
+    cfg.blockDim = dim3(pl.nw * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
-    if (pdl) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
-    }
+    set_pdl(cfg, attr, pdl);
     DenseArgs copy = a;
-    ProfScope ps(EPI == EPI_ARGMAX ? "k_dense_lm_head" : "k_dense", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
-    cudaLaunchKernelEx(&cfg, k_dense<PRO, EPI, EXACT>, copy);
+    ProfScope ps("k_gemv", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
+    cudaLaunchKernelEx(&cfg, k_gemv<PRO, EPI, EXACT, SPW>, copy);
+    COUNT_LAUNCH();
+}
+template <int PRO, bool EXACT>
+static void launch_head_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
+    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 1, 1);
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_head<PRO, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
+    int ntiles = a.N / 16;
+    int gx = (ntiles + 7) / 8; if (gx > 148 * 3) gx = 148 * 3;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)gx, (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS));
+    cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    set_pdl(cfg, attr, pdl);
+    DenseArgs copy = a;
+    ProfScope ps("k_head", (double)a.N * a.K * 0.5625 + (double)a.M * a.K * 2, st);
+    cudaLaunchKernelEx(&cfg, k_head<PRO, EXACT>, copy);
     COUNT_LAUNCH();
 }
 
 void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl) {
-#define SL_CASE(P, E)                                                                      \
-    if (pro == P && epi == E) {                                                            \
-        if (exact) launch_dense_t<P, E, true>(a, st, pdl); else launch_dense_t<P, E, false>(a, st, pdl); \
-        return;                                                                            \
+    const int spw = gemv_plan(a.K).spw;
+    if (epi == EPI_ARGMAX) {
+        if (pro == PRO_RMSNORM) { if (exact) launch_head_t<PRO_RMSNORM, true>(a, st, pdl); else launch_head_t<PRO_RMSNORM, false>(a, st, pdl); return; }
+        if (pro == PRO_PLAIN) { if (exact) launch_head_t<PRO_PLAIN, true>(a, st, pdl); else launch_head_t<PRO_PLAIN, false>(a, st, pdl); return; }
+    }
+#define SL_CASE(P, E)                                                                                       \
+    if (pro == P && epi == E) {                                                                             \
+        if (exact) { if (spw == 2) launch_gemv_t<P, E, true, 2>(a, st, pdl); else launch_gemv_t<P, E, true, 1>(a, st, pdl); }    \
+        else { if (spw == 2) launch_gemv_t<P, E, false, 2>(a, st, pdl); else launch_gemv_t<P, E, false, 1>(a, st, pdl); }        \
+        return;                                                                                             \
     }
     SL_CASE(PRO_PLAIN, EPI_STORE)
     SL_CASE(PRO_PLAIN, EPI_RESID)
     SL_CASE(PRO_RMSNORM, EPI_STORE)
-    SL_CASE(PRO_RMSNORM, EPI_ARGMAX)
-    SL_CASE(PRO_PLAIN, EPI_ARGMAX)
     SL_CASE(PRO_NORMGATE, EPI_RESID)
     SL_CASE(PRO_NORMGATE, EPI_STORE)
-    SL_CASE(PRO_PLAIN, EPI_SWIGLU)
 #undef SL_CASE
     fprintf(stderr, "seedless_b200: no dense kernel for prologue %d / epilogue %d\n", pro, epi);
     abort();
@@ -236,11 +321,18 @@ void launch_embed(const __half* embed, const int* tokens, int M, int H, int voca
 }
 
 // block-wide rmsnorm of one row of width H (multiple of 256, <= 4096) with 256 threads
-__device__ __forceinline__ void block_rmsnorm_row(const __half* src, const __half* w, float eps, int H, __half* dst, float* sm8) {
+__device__ __forceinline__ void block_rmsnorm_row(const __half* src, const __half* w, float eps, int H, __half* dst, float* sm8,
+                                                  bool pre = false, uint4 pv = make_uint4(0, 0, 0, 0), uint4 pw = make_uint4(0, 0, 0, 0)) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the thread's first 8-element chunk and its weights stay in registers across the reduction,
+    // so the common case (H <= 8 * blockDim) touches global memory once
+    const int k0 = threadIdx.x * 8;
+    uint4 v0 = make_uint4(0, 0, 0, 0), w0 = make_uint4(0, 0, 0, 0);
+    if (pre) { v0 = pv; w0 = pw; }
+    else if (k0 < H) { v0 = *reinterpret_cast<const uint4*>(src + k0); if (w) w0 = *reinterpret_cast<const uint4*>(w + k0); }
     float ss = 0.f;
-    for (int k = threadIdx.x * 8; k < H; k += blockDim.x * 8) {
-        uint4 v = *reinterpret_cast<const uint4*>(src + k);
+    for (int k = k0; k < H; k += blockDim.x * 8) {
+        uint4 v = (k == k0) ? v0 : *reinterpret_cast<const uint4*>(src + k);
         const __half2* hh = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) { float2 f = __half22float2(hh[i]); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); }
@@ -252,12 +344,12 @@ __device__ __forceinline__ void block_rmsnorm_row(const __half* src, const __hal
     float tot = 0.f;
     for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += sm8[i];
     float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)H), eps));
-    for (int k = threadIdx.x * 8; k < H; k += blockDim.x * 8) {
-        uint4 v = *reinterpret_cast<const uint4*>(src + k);
+    for (int k = k0; k < H; k += blockDim.x * 8) {
+        uint4 v = (k == k0) ? v0 : *reinterpret_cast<const uint4*>(src + k);
         const __half* hv = reinterpret_cast<const __half*>(&v);
         uint4 o; __half* oh = reinterpret_cast<__half*>(&o);
         if (w) {
-            uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+            uint4 wv = (k == k0) ? w0 : *reinterpret_cast<const uint4*>(w + k);
             const __half* wh = reinterpret_cast<const __half*>(&wv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) oh[i] = hmul_rn(wh[i], f2h(__fmul_rn(h2f(hv[i]), inv)));
@@ -286,70 +378,73 @@ void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H
 // grid: E/8 + 1 CTAs of 256 threads (one warp per expert); the last CTA writes the normed rows
 // and the shared-expert gate logit.
 // ============================================================================================
-__device__ __forceinline__ float canon_dot8(const uint4* wreg, const __half* xrow, int nblk, int lane) {
-    float acc = 0.f;
-    for (int kb = 0; kb < nblk; ++kb) {
-        uint4 xv = *reinterpret_cast<const uint4*>(xrow + kb * 256 + lane * 8);
-        const __half* xh = reinterpret_cast<const __half*>(&xv);
-        const __half* wh = reinterpret_cast<const __half*>(&wreg[kb]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc = fmaf(h2f(xh[i]), h2f(wh[i]), acc);   // product exact in f32
-    }
-    return warp_sum(acc);
-}
 // One warp routes one row.  Restates swift/Sources/QwispCore/SeedlessFusedVerify.swift:180-214
-// including the ORDER of its 256-slot halving trees: lane l holds slots l, l+32, .., l+224, so
+// including the ORDER of its 256-slot halving trees: lane l looks at slots l, l+32, .., l+224, so
 // the tree levels 128/64/32 are lane-local and the levels 16..1 are xor-shuffles whose results
 // are meaningful in lanes < s -- the same pairs (i, i+s) the reference combines.  Softmax in f32,
 // gates rounded to fp16, top-k by k rounds of arg-max on the raw logits (strict > keeps the
 // lower slot), fp16 sequential sum of the chosen gates, fp16 divide.
-__device__ __forceinline__ void route_row_warp(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, int lane) {
-    float lg[8], ex[8], gates[8], work[8];
+// buf: 2*256 floats + 32 ints of shared memory owned by this warp.  Loops are kept rolled: this
+// code runs in one warp of one CTA, so a small instruction footprint matters more than ILP.
+// Order of the reference's selection tree (256 slots halved to 128, 64, ... 1, the lower slot of
+// each compared pair winning ties): larger logit first, then smaller bit-reversed slot number (the
+// last level compares slots 0 and 1, so bit 0 of the slot decides first).  A 24-bit key
+// (order-preserving fp16 bits, then 255 - bitreverse8(slot)) has the same order, so k hardware
+// warp-max reductions select the same experts in the same sequence.
+__device__ __noinline__ void route_row_warp(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, float* buf, int lane) {
+    float* lg = buf;
+    {   // one 16-byte load per lane covers the 256 slots; shared memory turns it into the slot = j*32+lane order
+        uint4 raw = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);      // -inf pairs
+        const bool vec = ((E & 7) == 0) && lane * 8 + 8 <= E;     // rows of E halves stay 16-byte aligned only then
+        if (vec) raw = __ldcg(reinterpret_cast<const uint4*>(lrow) + lane);
+        const __half* rh = reinterpret_cast<const __half*>(&raw);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { int slot = j * 32 + lane; lg[j] = (slot < E) ? h2f(__ldcg(lrow + slot)) : -INFINITY; }
-    float mx = lg[0];
+        for (int i = 0; i < 8; ++i) lg[lane * 8 + i] = (lane * 8 + i < E) ? h2f(rh[i]) : -INFINITY;
+        if (!vec && lane * 8 < E)
+            for (int i = 0; i < 8 && lane * 8 + i < E; ++i) lg[lane * 8 + i] = h2f(__ldcg(lrow + lane * 8 + i));
+    }
+    __syncwarp();
+    float v0[8];
+    unsigned key[8];
+    float mx = -INFINITY;
 #pragma unroll
-    for (int j = 1; j < 8; ++j) mx = fmaxf(mx, lg[j]);
+    for (int j = 0; j < 8; ++j) {
+        v0[j] = lg[j * 32 + lane]; mx = fmaxf(mx, v0[j]);
+        unsigned hb = __half_as_ushort(f2h(v0[j]));                       // exact: the value came from fp16
+        if (hb == 0x8000u) hb = 0u;                                       // -0 compares equal to +0
+        hb = (hb & 0x8000u) ? (~hb & 0xffffu) : (hb | 0x8000u);
+        key[j] = (j * 32 + lane < E) ? ((hb << 8) | (255u - (__brev((unsigned)(j * 32 + lane)) >> 24))) : 0u;
+    }
     mx = warp_max(mx);
+    float ex[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { int slot = j * 32 + lane; ex[j] = (slot < E) ? expf(lg[j] - mx) : 0.0f; }
+    for (int j = 0; j < 8; ++j) { int slot = j * 32 + lane; ex[j] = (slot < E) ? expf(v0[j] - mx) : 0.0f; }
     float r0 = __fadd_rn(ex[0], ex[4]), r1 = __fadd_rn(ex[1], ex[5]), r2 = __fadd_rn(ex[2], ex[6]), r3 = __fadd_rn(ex[3], ex[7]);
     r0 = __fadd_rn(r0, r2); r1 = __fadd_rn(r1, r3);
     r0 = __fadd_rn(r0, r1);
 #pragma unroll
     for (int s = 16; s >= 1; s >>= 1) r0 = __fadd_rn(r0, __shfl_xor_sync(0xffffffffu, r0, s));
     const float Z = __shfl_sync(0xffffffffu, r0, 0);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { gates[j] = h2f(f2h(__fdiv_rn(ex[j], Z))); work[j] = lg[j]; }
-    __half sc[16];
-    int ids[16];
+    int my_id = 0; float my_ex = 0.f;                                     // lane k ends up holding the k-th choice
 #pragma unroll 1
     for (int k = 0; k < topk; ++k) {
-        float v[8]; int id[8];
+        unsigned best = key[0];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { v[j] = work[j]; id[j] = j * 32 + lane; }
+        for (int j = 1; j < 8; ++j) best = max(best, key[j]);
+        best = __reduce_max_sync(0xffffffffu, best);
+        const int slot = (int)(__brev(255u - (best & 0xffu)) >> 24), ol = slot & 31, oj = slot >> 5;
+        float e_sel = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) if (v[j + 4] > v[j]) { v[j] = v[j + 4]; id[j] = id[j + 4]; }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) if (v[j + 2] > v[j]) { v[j] = v[j + 2]; id[j] = id[j + 2]; }
-        if (v[1] > v[0]) { v[0] = v[1]; id[0] = id[1]; }
-        float bv = v[0]; int bi = id[0];
-#pragma unroll
-        for (int s = 16; s >= 1; s >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, s); int oi = __shfl_xor_sync(0xffffffffu, bi, s);
-            if (ov > bv) { bv = ov; bi = oi; }            // exact for lanes < s, which is all the next level reads
-        }
-        bi = __shfl_sync(0xffffffffu, bi, 0);
-        float gsel = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) if (j == (bi >> 5)) { gsel = gates[j]; if (lane == (bi & 31)) work[j] = -INFINITY; }
-        gsel = __shfl_sync(0xffffffffu, gsel, bi & 31);
-        ids[k] = bi; sc[k] = f2h(gsel);
+        for (int j = 0; j < 8; ++j) if (j == oj) { e_sel = ex[j]; if (lane == ol) key[j] = 0u; }
+        e_sel = __shfl_sync(0xffffffffu, e_sel, ol);
+        if (lane == k) { my_id = oj * 32 + ol; my_ex = e_sel; }
     }
+    // gate of the k-th choice = fp16(exp / Z); the sum runs in fp16 in ascending k, then each is divided by it
+    const __half g = f2h(__fdiv_rn(my_ex, Z));
     __half ss = f2h(0.0f);
-    for (int k = 0; k < topk; ++k) ss = hadd_rn(ss, sc[k]);
-    if (lane == 0)
-        for (int k = 0; k < topk; ++k) { inds_out[k] = ids[k]; scores_out[k] = hdiv_rn(sc[k], ss); }
+    for (int k = 0; k < topk; ++k) ss = hadd_rn(ss, __ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, (unsigned)__half_as_ushort(g), k)));
+    if (lane < topk) { inds_out[lane] = my_id; scores_out[lane] = hdiv_rn(g, ss); }
+    __syncwarp();
 }
 
 __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
@@ -357,52 +452,76 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     __half* ps = reinterpret_cast<__half*>(smem);            // [8][H]
     float* sm8 = reinterpret_cast<float*>(ps + 8 * a.H);
     __shared__ int s_last; __shared__ int s_cnt[256]; __shared__ int s_cur[256]; __shared__ int s_off[256];
+    __shared__ float s_route[8][512 + 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    long long tq0 = clock64(), tq[6] = {0, 0, 0, 0, 0, 0};
     const int nblk = a.H >> 8;                                // <= 16
     const bool tail = (blockIdx.x == gridDim.x - 1);
     const int e = blockIdx.x * 8 + warp;
+    // the first row's activations and norm weights go out ahead of the (much larger) weight loads
+    uint4 pv = make_uint4(0, 0, 0, 0), pw = make_uint4(0, 0, 0, 0);
+    if (a.norm_w && tid * 8 < a.H) { pv = *reinterpret_cast<const uint4*>(a.h + tid * 8); pw = *reinterpret_cast<const uint4*>(a.norm_w + tid * 8); }
     uint4 wreg[16];
     const __half* wrow = tail ? a.shared_gate : (a.router + (size_t)e * a.H);
     const bool wvalid = tail ? (warp == 0) : (e < a.E);
 #pragma unroll
     for (int kb = 0; kb < 16; ++kb)
         wreg[kb] = (wvalid && kb < nblk) ? *reinterpret_cast<const uint4*>(wrow + kb * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+    prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
+    tq[0] = clock64() - tq0;
     for (int m0 = 0; m0 < a.M; m0 += 8) {
         int mr = min(8, a.M - m0);
         __syncthreads();
         for (int c = 0; c < mr; ++c) {
             const __half* src = a.h + (size_t)(m0 + c) * a.ldh;
-            if (a.norm_w) block_rmsnorm_row(src, a.norm_w, a.eps, a.H, ps + c * a.H, sm8);
+            if (a.norm_w) block_rmsnorm_row(src, a.norm_w, a.eps, a.H, ps + c * a.H, sm8, m0 + c == 0, pv, pw);
             else for (int k = threadIdx.x * 8; k < a.H; k += blockDim.x * 8) *reinterpret_cast<uint4*>(ps + c * a.H + k) = *reinterpret_cast<const uint4*>(src + k);
         }
         __syncthreads();
+        tq[1] = clock64() - tq0;
         if (tail) {
             for (int i = threadIdx.x; i < mr * a.H / 8; i += blockDim.x) {
                 int c = i / (a.H / 8), k = (i - c * (a.H / 8)) * 8;
                 *reinterpret_cast<uint4*>(a.p + (size_t)(m0 + c) * a.H + k) = *reinterpret_cast<const uint4*>(ps + c * a.H + k);
             }
-            if (warp == 0)
-                for (int c = 0; c < mr; ++c) {
-                    float d = canon_dot8(wreg, ps + c * a.H, nblk, lane);
-                    if (lane == 0) a.sgl[m0 + c] = f2h(d);
-                }
-        } else if (wvalid) {
+        }
+        if (wvalid) {
             for (int c = 0; c < mr; ++c) {
-                float d = canon_dot8(wreg, ps + c * a.H, nblk, lane);
-                if (lane == 0) a.logits[(size_t)(m0 + c) * a.E + e] = f2h(d);
+                const __half* xrow = ps + c * a.H;
+                float acc = 0.f;
+#pragma unroll
+                for (int kb = 0; kb < 16; ++kb) {
+                    if (kb < nblk) {
+                        uint4 xv = *reinterpret_cast<const uint4*>(xrow + kb * 256 + lane * 8);
+                        const __half* xh = reinterpret_cast<const __half*>(&xv);
+                        const __half* wh = reinterpret_cast<const __half*>(&wreg[kb]);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc = fmaf(h2f(xh[i]), h2f(wh[i]), acc);   // product exact in f32
+                    }
+                }
+                float d = warp_sum(acc);
+                if (lane == 0) { if (tail) a.sgl[m0 + c] = f2h(d); else a.logits[(size_t)(m0 + c) * a.E + e] = f2h(d); }
             }
         }
     }
     // ---- the CTA that finishes last routes every row and groups the (row, k) pairs by expert ----
+    tq[2] = clock64() - tq0;
     __threadfence();
     __syncthreads();
     if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
     __syncthreads();
+    tq[3] = clock64() - tq0;
+    if (a.dbg && tid == 0 && !s_last) { for (int i = 0; i < 4; ++i) a.dbg[blockIdx.x * 8 + i] = tq[i]; }
     if (!s_last) return;
     __threadfence();
-    for (int m = warp; m < a.M; m += 8) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, lane);
+    tq[5] = clock64() - tq0;
+    for (int m = warp; m < a.M; m += 8) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, s_route[warp], lane);
     if (tid == 0) *a.counter = 0u;
     __syncthreads();
+    tq[4] = clock64() - tq0;
+    if (a.dbg && tid == 0) { for (int i = 0; i < 6; ++i) a.dbg[blockIdx.x * 8 + i] = tq[i]; a.dbg[blockIdx.x * 8 + 7] = 1; }
     if (a.M == 1) {                                          // one row: its k experts are distinct, slot k = k-th choice
         if (tid < a.topk) {
             a.lists.slot_expert[tid] = a.inds[tid]; a.lists.slot_off[tid] = tid; a.lists.slot_cnt[tid] = 1; a.lists.pairs[tid] = tid;
@@ -431,151 +550,190 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
         a.lists.pairs[s_off[ex] + pos] = i;
     }
 }
-void launch_router(const RouterArgs& a, cudaStream_t st) {
+void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl) {
     size_t smem = (size_t)8 * a.H * 2 + 64;
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_moe_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); configured = true; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((a.E + 7) / 8 + 1)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    set_pdl(cfg, attr, pdl);
+    RouterArgs copy = a;
     ProfScope ps("k_moe_router", (double)(a.E + 1) * a.H * 2 + (double)a.M * a.H * 4, st);
-    k_moe_router<<<(a.E + 7) / 8 + 1, 256, smem, st>>>(a);
+    cudaLaunchKernelEx(&cfg, k_moe_router, copy);
     COUNT_LAUNCH();
 }
 
 // ============================================================================================
 // Routed + shared experts, grouped by expert: every touched expert's weights are read once per
-// call and applied to all rows routed to it (8 rows per MMA pass).
-// gate/up: grid (I/8, nslots + 1); tile = 8 gate rows + 8 up rows, SwiGLU in the epilogue.
-// down:    grid (H/16, nslots + 1).  The last grid.y index is the shared expert (all rows).  Its last
-//          CTA per tile also does the weighted combine + shared expert + residual.
+// call and applied to all rows routed to it (8 rows per MMA pass).  Same CTA organisation as the
+// split GEMV (TPC tiles per CTA, WPT warps per tile).
+// gate/up: grid (ceil((I/8)/TPC), nslots + 1); tile = 8 gate rows + 8 up rows, SwiGLU in the epilogue.
+// down:    grid (ceil((H/16)/TPC), nslots + 1).  The last grid.y index is the shared expert (all
+//          rows).  The CTA that finishes last for a group of output tiles also does the weighted
+//          combine + shared expert + residual for those outputs.
 // hbuf / dbuf rows: pair id (row*top_k + k) for routed experts, M*top_k + row for the shared one.
 // ============================================================================================
-template <bool EXACT, bool DOWN>
-__global__ void __launch_bounds__(512) k_expert(ExpertArgs a) {
+// tile pointers of expert e (or the shared expert) in the repacked slabs
+template <bool DOWN>
+__device__ __forceinline__ void expert_tile(const ExpertArgs& a, bool shared, int e, int tile, int K, const uint4*& wt, const uint4*& stl) {
+    const Q4R& q = DOWN ? (shared ? a.sh_down : a.down) : (shared ? a.sh_gu : a.gu);
+    const size_t T = (size_t)e * (DOWN ? a.H / 16 : a.I / 8) + tile;
+    wt = q.wr + T * q4r_w_uint4(K); stl = q.sr + T * q4r_s_uint4(K);
+}
+template <bool EXACT, bool DOWN, int SPW>
+__global__ void __launch_bounds__(SPW == 2 ? 256 : 512, SPW == 2 ? 2 : 1) k_expert(ExpertArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
     const int K = DOWN ? a.I : a.H;
+    const int slices = K >> 8, WPT = slices / SPW, TPC = nw / WPT;
     const int slot = blockIdx.y;
     const bool shared = (slot == (int)gridDim.y - 1);
-    if (!shared && slot >= *a.lists.n_active) return;
-    XStage st; float* red; float* fin; int* misc;
-    GemvSmem::carve(smem, min(a.M, 8), K, nw, st, red, fin, misc);
-    const int e = shared ? 0 : a.lists.slot_expert[slot];
-    const int cnt = shared ? a.M : a.lists.slot_cnt[slot];
-    const int off = shared ? 0 : a.lists.slot_off[slot];
-    const int tile = blockIdx.x;
-    const int K8 = K >> 3, KG = K >> 6, slices = K >> 8;
+    const int tl = warp / WPT, part = warp - tl * WPT;
+    const int tile = blockIdx.x * TPC + tl;
+    const int ntiles = DOWN ? a.H / 16 : a.I / 8;
+    const bool valid = tile < ntiles;
     const int npair = a.M * a.topk;
-
-    const uint32_t *wA, *wB; const __half *sA, *bA, *sB, *bB;
-    if (DOWN) {
-        const Q4W& q = shared ? a.sh_down : a.down;
-        int64_t row = (int64_t)e * a.H + tile * 16 + r;
-        wA = q.w + row * K8; sA = q.s + row * KG; bA = q.b + row * KG;
-        wB = wA + 8 * (int64_t)K8; sB = sA + 8 * KG; bB = bA + 8 * KG;
-    } else {
-        const Q4W& qg = shared ? a.sh_gate : a.gate;
-        const Q4W& qu = shared ? a.sh_up : a.up;
-        int64_t row = (int64_t)e * a.I + tile * 8 + r;
-        wA = qg.w + row * K8; sA = qg.s + row * KG; bA = qg.b + row * KG;
-        wB = qu.w + row * K8; sB = qu.s + row * KG; bB = qu.b + row * KG;
-    }
-    // K/256 == number of warps here, so each warp keeps its single slice in registers for all rows
-    SliceRegs regs;
-    const bool have = warp < slices;
-    if (have) load_slice(regs, wA, wB, sA, bA, sB, bB, warp, t);
-
-    for (int c0 = 0; c0 < cnt; c0 += 8) {
-        const int mr = min(8, cnt - c0);
-        if (threadIdx.x < 8) {
-            int dst = 0, src = 0;
-            if ((int)threadIdx.x < mr) {
-                if (shared) { dst = npair + c0 + threadIdx.x; src = c0 + threadIdx.x; }
-                else { int pr = a.lists.pairs[off + c0 + threadIdx.x]; dst = pr; src = pr / a.topk; }
+    SliceRegs regs[SPW];
+    pdl_launch_dependents();
+    pdl_wait();
+    XStage st; float* red; float* fin; int* misc;
+    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), K, TPC * slices, TPC, st, red, fin, misc);
+    const int n_active = *a.lists.n_active;
+    const bool active = shared || slot < n_active;
+    if (active) {
+        const int e = shared ? 0 : a.lists.slot_expert[slot];
+        const int cnt = shared ? a.M : a.lists.slot_cnt[slot];
+        const int off = shared ? 0 : a.lists.slot_off[slot];
+        for (int c0 = 0; c0 < cnt; c0 += ROWS_PER_PASS) {
+            const int mr = min(ROWS_PER_PASS, cnt - c0);
+            if (threadIdx.x < ROWS_PER_PASS) {
+                int dst = 0, srow = 0;
+                if ((int)threadIdx.x < mr) {
+                    if (shared) { dst = npair + c0 + threadIdx.x; srow = c0 + threadIdx.x; }
+                    else { int pr = a.lists.pairs[off + c0 + threadIdx.x]; dst = pr; srow = pr / a.topk; }
+                }
+                misc[threadIdx.x] = DOWN ? dst : srow;     // source row of the activations
+                misc[8 + threadIdx.x] = dst;               // destination row
             }
-            misc[threadIdx.x] = DOWN ? dst : src;      // source row of the activations
-            misc[8 + threadIdx.x] = dst;               // destination row
-        }
-        __syncthreads();
-        if (DOWN) stage_gather(st, a.hbuf, a.I, misc, mr, K);
-        else stage_gather(st, a.p, a.H, misc, mr, K);
-        __syncthreads();
-        float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
-        if (have) compute_slice<EXACT>(regs, st, warp, r, t, r < mr, accS, accB);
-        float v[4];
+            __syncthreads();
+            // activations first, then (first pass) the expert's weights, then wait for the activations
+            StageSrc src{DOWN ? a.hbuf : a.p, DOWN ? a.I : a.H, misc, nullptr, nullptr, 0, 0.f};
+            StageRegs sregs;
+            stage_issue<PRO_PLAIN>(sregs, src, 0, mr, K);
+            if (c0 == 0) {
+                if (valid) {
+                    const uint4 *wt, *stl; expert_tile<DOWN>(a, shared, e, tile, K, wt, stl);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = finish_acc<EXACT>(accS[i], accB[i]);
-        reduce_tile(red, fin, v, nw);
-        if (DOWN) {
-            for (int i = threadIdx.x; i < 128; i += blockDim.x) {
-                int col = i >> 4, row = i & 15;
-                if (col < mr) a.dbuf[(size_t)misc[8 + col] * a.H + tile * 16 + row] = f2h(fin[row * 8 + col]);
-            }
-        } else {
-            for (int j = threadIdx.x; j < 64; j += blockDim.x) {
-                int col = j >> 3, i = j & 7;
-                if (col < mr) {
-                    __half g = f2h(fin[i * 8 + col]), u = f2h(fin[(i + 8) * 8 + col]);
-                    a.hbuf[(size_t)misc[8 + col] * a.I + tile * 8 + i] = swiglu_h(g, u);
+                    for (int i = 0; i < SPW; ++i) load_slice(regs[i], wt, stl, part * SPW + i, lane);
+                }
+                if (!DOWN) {
+                    // pull what the down kernel will read for this expert into L2: this CTA's 1/gridDim.x share
+                    const Q4R& qd = shared ? a.sh_down : a.down;
+                    const size_t wbytes = (size_t)(a.H / 16) * q4r_w_uint4(a.I) * 16, gbytes = (size_t)(a.H / 16) * q4r_s_uint4(a.I) * 16;
+                    PfList pd{};
+                    pd.p[0] = reinterpret_cast<const char*>(qd.wr) + (size_t)e * wbytes; pd.bytes[0] = (unsigned)wbytes;
+                    pd.p[1] = reinterpret_cast<const char*>(qd.sr) + (size_t)e * gbytes; pd.bytes[1] = (unsigned)gbytes;
+                    prefetch_ranges(pd, blockIdx.x, gridDim.x);
+                    prefetch_ranges(a.pf, (shared ? n_active : slot) * gridDim.x + blockIdx.x, gridDim.x * (n_active + 1));
                 }
             }
+            stage_finish<PRO_PLAIN>(sregs, st, src, mr, K);
+            __syncthreads();
+            if (valid) {
+#pragma unroll
+                for (int i = 0; i < SPW; ++i) {
+                    float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+                    compute_slice(regs[i], st, part * SPW + i, r, t, mr, accS, accB);
+                    finish_acc4(accS, accB, t, v);
+                    store_partial(red, tl * slices + part * SPW + i, lane, v);
+                }
+            }
+            __syncthreads();
+            reduce_tiles(red, fin, TPC, slices);
+            __syncthreads();
+            if (DOWN) {
+                for (int i = threadIdx.x; i < TPC * 32; i += blockDim.x) {
+                    int tl2 = i >> 5, col = (i >> 4) & 1, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
+                    if (tile2 < ntiles && col < mr) a.dbuf[(size_t)misc[8 + col] * a.H + tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, col));
+                }
+            } else {
+                for (int j = threadIdx.x; j < TPC * 16; j += blockDim.x) {
+                    int tl2 = j >> 4, col = (j >> 3) & 1, i = j & 7, tile2 = blockIdx.x * TPC + tl2;
+                    if (tile2 < ntiles && col < mr) {
+                        __half g = f2h(tile_value(fin + tl2 * 128, i, col)), u = f2h(tile_value(fin + tl2 * 128, i + 8, col));
+                        a.hbuf[(size_t)misc[8 + col] * a.I + tile2 * 8 + i] = swiglu_h(g, u);
+                    }
+                }
+            }
+            __syncthreads();
         }
-        __syncthreads();
     }
-    if (DOWN) {
-        // The CTA that finishes last for this tile of 16 output rows combines them for every row:
-        // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit)
-        // * shared (:474-484), + residual (SeedlessMetalForward.swift:1024-1028).
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned ticket = atomicAdd(a.tile_counter + tile, 1u);
-            misc[0] = (ticket == (unsigned)*a.lists.n_active) ? 1 : 0;     // n_active routed slots + the shared expert
-        }
-        __syncthreads();
-        if (!misc[0]) return;
-        __threadfence();
-        if (threadIdx.x == 0) a.tile_counter[tile] = 0u;
-        for (int i = threadIdx.x; i < a.M * 16; i += blockDim.x) {
-            int m = i >> 4, n = tile * 16 + (i & 15);
-            __half acc = f2h(0.0f);
-            for (int k = 0; k < a.topk; ++k)
-                acc = hadd_rn(acc, hmul_rn(__ldcg(a.dbuf + (size_t)(m * a.topk + k) * a.H + n), a.scores[m * a.topk + k]));
-            __half res = hadd_rn(acc, hmul_rn(sigmoid_h(a.sgl[m]), __ldcg(a.dbuf + (size_t)(npair + m) * a.H + n)));
-            if (a.resid) a.resid[(size_t)m * a.H + n] = hadd_rn(a.resid[(size_t)m * a.H + n], res);
-            else a.out[(size_t)m * a.H + n] = res;
-        }
+    if (!DOWN || !active) return;
+    // The CTA that finishes last for this group of output tiles combines them for every row:
+    // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit)
+    // * shared (:474-484), + residual (SeedlessMetalForward.swift:1024-1028).
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned ticket = atomicAdd(a.tile_counter + blockIdx.x, 1u);
+        misc[0] = (ticket == (unsigned)n_active) ? 1 : 0;            // n_active routed slots + the shared expert
+    }
+    __syncthreads();
+    if (!misc[0]) return;
+    __threadfence();
+    if (threadIdx.x == 0) a.tile_counter[blockIdx.x] = 0u;
+    const int ncols = min(TPC * 16, a.H - blockIdx.x * TPC * 16);
+    for (int i = threadIdx.x; i < a.M * ncols; i += blockDim.x) {
+        int m = i / ncols, n = blockIdx.x * TPC * 16 + (i - m * ncols);
+        __half acc = f2h(0.0f);
+        for (int k = 0; k < a.topk; ++k)
+            acc = hadd_rn(acc, hmul_rn(__ldcg(a.dbuf + (size_t)(m * a.topk + k) * a.H + n), a.scores[m * a.topk + k]));
+        __half res = hadd_rn(acc, hmul_rn(sigmoid_h(a.sgl[m]), __ldcg(a.dbuf + (size_t)(npair + m) * a.H + n)));
+        if (a.resid) a.resid[(size_t)m * a.H + n] = hadd_rn(a.resid[(size_t)m * a.H + n], res);
+        else a.out[(size_t)m * a.H + n] = res;
     }
 }
-template <bool EXACT, bool DOWN>
-static void launch_expert_t(const ExpertArgs& a, int nslots, cudaStream_t st) {
+template <bool EXACT, bool DOWN, int SPW>
+static void launch_expert_t(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) {
     int K = DOWN ? a.I : a.H;
-    int nw = K / 256;
-    size_t smem = GemvSmem::bytes(a.M < 8 ? a.M : 8, K, nw);
+    GemvPlan pl = gemv_plan(K);
+    int slices = K / 256;
+    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, K, pl.tpc * slices, pl.tpc);
     static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_expert<EXACT, DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); configured = true; }
-    dim3 grid((unsigned)(DOWN ? a.H / 16 : a.I / 8), (unsigned)(nslots + 1));
+    if (!configured) { cudaFuncSetAttribute(k_expert<EXACT, DOWN, SPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
+    int ntiles = DOWN ? a.H / 16 : a.I / 8;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)(nslots + 1));
+    cfg.blockDim = dim3(pl.nw * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    set_pdl(cfg, attr, pdl);
+    ExpertArgs copy = a;
     int touched = (a.M * a.topk < nslots ? a.M * a.topk : nslots) + 1;   // distinct experts read: exact for one row, an upper bound otherwise
     ProfScope ps(DOWN ? "k_expert_down" : "k_expert_gateup", (double)touched * (DOWN ? 1 : 2) * a.I * a.H * 0.5625, st);
-    k_expert<EXACT, DOWN><<<grid, nw * 32, smem, st>>>(a);
+    cudaLaunchKernelEx(&cfg, k_expert<EXACT, DOWN, SPW>, copy);
     COUNT_LAUNCH();
 }
-void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st) {
-    if (exact) launch_expert_t<true, false>(a, nslots, st); else launch_expert_t<false, false>(a, nslots, st);
+template <bool DOWN>
+static void launch_expert_d(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) {
+    int spw = gemv_plan(DOWN ? a.I : a.H).spw;
+    if (exact) { if (spw == 2) launch_expert_t<true, DOWN, 2>(a, nslots, st, pdl); else launch_expert_t<true, DOWN, 1>(a, nslots, st, pdl); }
+    else { if (spw == 2) launch_expert_t<false, DOWN, 2>(a, nslots, st, pdl); else launch_expert_t<false, DOWN, 1>(a, nslots, st, pdl); }
 }
-void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st) {
-    if (exact) launch_expert_t<true, true>(a, nslots, st); else launch_expert_t<false, true>(a, nslots, st);
-}
+void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { launch_expert_d<false>(exact, a, nslots, st, pdl); }
+void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { launch_expert_d<true>(exact, a, nslots, st, pdl); }
 
 // ============================================================================================
 // Gated-delta-net core: causal conv1d + SiLU, q/k l2-style norm + scale, beta / decay, the
 // recurrent state update and readout, for all rows of a segment in sequence.
 // (conv: SeedlessFusedVerify.swift:634-663; prep: :839-938; recurrence: GatedDelta.swift:63-124)
-// grid (4 dv-tiles of 32, Hv, nsegs), 128 threads.  The fp32 state tile [32 dv][128 dk] of this
+// grid (8 dv-tiles of 16, Hv, nsegs), 128 threads.  The fp32 state tile [16 dv][128 dk] of this
 // CTA lives in registers for the whole call: read once from the current ping-pong side, written
 // once to the other side.  Conv history likewise goes from one side to the other.
 // ============================================================================================
 __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
-    __shared__ float q_s[128], k_s[128], v_s[32];
+    __shared__ float q_s[128], k_s[128], v_s[16];
     __shared__ float red_s[8]; __shared__ float gb_s[2];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int dvt = blockIdx.x, hv = blockIdx.y;
@@ -584,20 +742,22 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
     const int keyDim = a.Hk * GDN_DK, convDim = 2 * keyDim + a.Hv * GDN_DV;
     const int side = a.tab.parity[seg.slot];
     const float* S_in = a.tab.gdn_state + (size_t)seg.slot * a.tab.state_stride_stream + (size_t)side * a.tab.state_stride_side +
-                        (size_t)a.gdn_index * a.tab.state_stride_layer + ((size_t)hv * GDN_DV + dvt * 32) * GDN_DK;
+                        (size_t)a.gdn_index * a.tab.state_stride_layer + ((size_t)hv * GDN_DV + dvt * 16) * GDN_DK;
     float* S_out = a.tab.gdn_state + (size_t)seg.slot * a.tab.state_stride_stream + (size_t)(side ^ 1) * a.tab.state_stride_side +
-                   (size_t)a.gdn_index * a.tab.state_stride_layer + ((size_t)hv * GDN_DV + dvt * 32) * GDN_DK;
+                   (size_t)a.gdn_index * a.tab.state_stride_layer + ((size_t)hv * GDN_DV + dvt * 16) * GDN_DK;
     const __half* hist_in = a.tab.conv_hist + (size_t)seg.slot * a.tab.hist_stride_stream + (size_t)side * a.tab.hist_stride_side +
                             (size_t)a.gdn_index * a.tab.hist_stride_layer;
     __half* hist_out = a.tab.conv_hist + (size_t)seg.slot * a.tab.hist_stride_stream + (size_t)(side ^ 1) * a.tab.hist_stride_side +
                        (size_t)a.gdn_index * a.tab.hist_stride_layer;
-    // state rows of this warp: 8 rows, lane owns dk 4*lane .. 4*lane+3
-    float4 S[8];
+    // state rows of this warp: 4 rows, lane owns dk 4*lane .. 4*lane+3
+    pdl_launch_dependents();
+    pdl_wait();
+    float4 S[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) S[i] = *reinterpret_cast<const float4*>(S_in + (size_t)(warp * 8 + i) * GDN_DK + lane * 4);
+    for (int i = 0; i < 4; ++i) S[i] = *reinterpret_cast<const float4*>(S_in + (size_t)(warp * 4 + i) * GDN_DK + lane * 4);
 
     const int ch_q = hk * GDN_DK + tid, ch_k = keyDim + hk * GDN_DK + tid;
-    const int ch_v = 2 * keyDim + hv * GDN_DV + dvt * 32 + (tid & 31);
+    const int ch_v = 2 * keyDim + hv * GDN_DV + dvt * 16 + (tid & 15);
     const float4 wq = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_q * 4);
     const float4 wk = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_k * 4);
     const float4 wv = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_v * 4);
@@ -618,7 +778,7 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
     for (int tt = 0; tt < seg.nrows; ++tt) {
         const int row = seg.row0 + tt;
         float qc = conv(tt, ch_q, wq), kc = conv(tt, ch_k, wk);
-        if (tid < 32) v_s[tid] = conv(tt, ch_v, wv);
+        if (tid < 16) v_s[tid] = conv(tt, ch_v, wv);
         float sq = warp_sum(qc * qc), sk = warp_sum(kc * kc);
         if (lane == 0) { red_s[warp] = sq; red_s[4 + warp] = sk; }
         if (tid == 0) {
@@ -639,22 +799,22 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
         const float4 kq = *reinterpret_cast<const float4*>(k_s + lane * 4);
         const float4 qq = *reinterpret_cast<const float4*>(q_s + lane * 4);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < 4; ++i) {
             float4 s = S[i];
             s.x *= g; s.y *= g; s.z *= g; s.w *= g;
             float kv = s.x * kq.x + s.y * kq.y + s.z * kq.z + s.w * kq.w;
             kv = warp_sum(kv);
-            float delta = (v_s[warp * 8 + i] - kv) * beta;
+            float delta = (v_s[warp * 4 + i] - kv) * beta;
             s.x = fmaf(kq.x, delta, s.x); s.y = fmaf(kq.y, delta, s.y); s.z = fmaf(kq.z, delta, s.z); s.w = fmaf(kq.w, delta, s.w);
             float o = s.x * qq.x + s.y * qq.y + s.z * qq.z + s.w * qq.w;
             o = warp_sum(o);
             S[i] = s;
-            if (lane == 0) a.y[(size_t)row * (a.Hv * GDN_DV) + hv * GDN_DV + dvt * 32 + warp * 8 + i] = f2h(o);
+            if (lane == 0) a.y[(size_t)row * (a.Hv * GDN_DV) + hv * GDN_DV + dvt * 16 + warp * 4 + i] = f2h(o);
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(S_out + (size_t)(warp * 8 + i) * GDN_DK + lane * 4) = S[i];
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(S_out + (size_t)(warp * 4 + i) * GDN_DK + lane * 4) = S[i];
     // new conv history = last three rows of [hist | rows]; q/k channels by one CTA per key head
     const bool owner_qk = (dvt == 0) && (hv % (a.Hv / a.Hk) == 0);
     for (int j = 0; j < CONV_K - 1; ++j) {
@@ -663,13 +823,18 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
             hist_out[(size_t)j * convDim + ch_q] = f2h(xval(idx, ch_q));
             hist_out[(size_t)j * convDim + ch_k] = f2h(xval(idx, ch_k));
         }
-        if (tid < 32) hist_out[(size_t)j * convDim + ch_v] = f2h(xval(idx, ch_v));
+        if (tid < 16) hist_out[(size_t)j * convDim + ch_v] = f2h(xval(idx, ch_v));
     }
 }
-void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st) {
-    dim3 grid(4, a.Hv, nsegs);
+void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl) {
+    dim3 grid(8, a.Hv, nsegs);
     ProfScope ps("k_gdn_core", (double)nsegs * a.Hv * GDN_DV * GDN_DK * 8, st);
-    k_gdn_core<<<grid, 128, 0, st>>>(a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(128); cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    set_pdl(cfg, attr, pdl);
+    GdnArgs copy = a;
+    cudaLaunchKernelEx(&cfg, k_gdn_core, copy);
     COUNT_LAUNCH();
 }
 

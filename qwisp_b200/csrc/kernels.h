@@ -1,15 +1,14 @@
 // kernels.h -- argument blocks and host launchers of the Seedless B200 kernels.
 #pragma once
-#include "common.cuh"
+#include "gemv.cuh"
 
 namespace sl {
 
 struct Q4W { const uint32_t* w = nullptr; const __half* s = nullptr; const __half* b = nullptr; int64_t N = 0; int K = 0; };
 
 struct DenseArgs {
-    const uint32_t* w; const __half* s; const __half* b;        // rows A (and B = A + 8)
-    const uint32_t* w2; const __half* s2; const __half* b2;     // rows B when the epilogue pairs gate/up
-    int N, K, M;
+    Q4R q;                                                       // repacked weights (tiles of 16 rows)
+    int N, K, M;                                                 // N outputs (= 16 * tiles)
     const __half* x; int ldx;                                    // activations (plain) / residual stream (rmsnorm) / y (normgate)
     const __half* nw;                                            // norm weight
     const __half* z; int ldz;                                    // gate input of the gated norm
@@ -17,6 +16,7 @@ struct DenseArgs {
     __half* y; int ldy;                                          // output rows
     __half* logits;                                              // optional [M][N] (argmax epilogue)
     float* pval; int* pidx; int* out_tok; unsigned* counter;     // argmax partials / result / ticket
+    PfList pf;                                                   // weights of later kernels to pull into L2
 };
 
 struct MoeLists {
@@ -38,11 +38,13 @@ struct RouterArgs {
     __half* sgl;                         // [M] shared-expert gate logit
     int topk; int* inds; __half* scores; // [M][topk] routing result (written by the last CTA)
     MoeLists lists; unsigned* counter;
+    PfList pf;                           // static prefetch (every CTA)
+    long long* dbg;                      // optional per-CTA clock stamps (development aid), usually nullptr
 };
 
 struct ExpertArgs {
-    Q4W gate, up, down;                  // expert slabs: row (e*I + i) / (e*H + n)
-    Q4W sh_gate, sh_up, sh_down;
+    Q4R gu, down;                        // expert slabs, repacked: gate/up paired tiles (I/8 per expert), down tiles (H/16 per expert)
+    Q4R sh_gu, sh_down;
     MoeLists lists;
     const __half* p;                     // [M][H] normed rows
     __half* hbuf;                        // [(M*topk + M)][I]
@@ -52,6 +54,7 @@ struct ExpertArgs {
     __half* resid;                       // residual stream updated in place, or nullptr ...
     __half* out;                         // ... then the block output goes here
     unsigned* tile_counter;              // [H/16] tickets, zero between launches
+    PfList pf;                           // static prefetch (gate/up kernel: next layer's in-projection)
 };
 
 struct GdnArgs {
@@ -86,10 +89,10 @@ struct StepEndArgs {
 
 void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl);
 void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st);
-void launch_router(const RouterArgs& a, cudaStream_t st);
-void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st);
-void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st);
-void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st);
+void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl);
+void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
+void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
+void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl);
 void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
 void launch_attn_decode(const AttnArgs& a, cudaStream_t st);
 void launch_attn_combine(const AttnArgs& a, cudaStream_t st);
@@ -98,7 +101,6 @@ void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H
 int64_t kernel_launch_count();
 void profile_start();
 int profile_report(char* buf, size_t cap);
-size_t dense_smem_bytes(int M, int K);
 
 // synthetic data + quantiser (synth.cu)
 uint64_t tensor_seed(uint64_t base_seed, const char* name);
@@ -107,5 +109,7 @@ void launch_synth_f32(uint64_t tseed, int64_t n, float mean, float std, float* o
 void launch_synth_q4(uint64_t tseed, int64_t N, int64_t K, float std, uint32_t* packed, __half* s, __half* b, cudaStream_t st);
 void launch_quantize_q4(const __half* w, int64_t N, int64_t K, uint32_t* packed, __half* s, __half* b, cudaStream_t st);
 void host_synth_tokens(uint64_t tseed, int64_t n, int32_t vocab, int32_t* out);
+// MLX affine layout -> fragment-major layout; pair != 0: tile = 8 rows of A + the same 8 rows of B
+void launch_repack_q4(const Q4W& a, const Q4W* b_pair, uint4* wr, uint4* sr, cudaStream_t st);
 
 }  // namespace sl

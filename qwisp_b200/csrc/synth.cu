@@ -124,6 +124,39 @@ void launch_quantize_q4(const __half* w, int64_t N, int64_t K, uint32_t* packed,
     int64_t ng = N * K / 64;
     k_quantize_q4<<<grid_for(ng, 128), 128, 0, st>>>(w, ng, packed, s, b);
 }
+// ---- MLX affine layout -> fragment-major layout (see gemv.cuh) ----
+__global__ void k_repack_q4(const uint32_t* wA, const __half* sA, const __half* bA, const uint32_t* wB, const __half* sB, const __half* bB,
+                            int pair, int64_t tiles, int K, uint4* wr, uint4* sr) {
+    const int GP = K / 128, K8 = K / 8, KG = K / 64;
+    const int64_t total_w = tiles * GP * 64, total_s = tiles * GP * 8;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (; i < total_w + total_s; i += stride) {
+        if (i < total_w) {
+            int64_t T = i / (GP * 64); int rem = (int)(i - T * (GP * 64));
+            int gp = rem >> 6, gi = (rem >> 5) & 1, lane = rem & 31, r = lane >> 2, t = lane & 3;
+            int word = 8 * (2 * gp + gi) + 2 * t;
+            int64_t rowA = pair ? 8 * T + r : 16 * T + r, rowB = pair ? 8 * T + r : 16 * T + 8 + r;
+            const uint32_t* srcB = pair ? wB : wA;
+            wr[i] = make_uint4(wA[rowA * K8 + word], wA[rowA * K8 + word + 1], srcB[rowB * K8 + word], srcB[rowB * K8 + word + 1]);
+        } else {
+            int64_t j = i - total_w;
+            int64_t T = j / (GP * 8); int rem = (int)(j - T * (GP * 8));
+            int gp = rem >> 3, r = rem & 7;
+            int64_t rowA = pair ? 8 * T + r : 16 * T + r, rowB = pair ? 8 * T + r : 16 * T + 8 + r;
+            const __half* sB2 = pair ? sB : sA; const __half* bB2 = pair ? bB : bA;
+            __half v[8] = {sA[rowA * KG + 2 * gp], bA[rowA * KG + 2 * gp], sB2[rowB * KG + 2 * gp], bB2[rowB * KG + 2 * gp],
+                           sA[rowA * KG + 2 * gp + 1], bA[rowA * KG + 2 * gp + 1], sB2[rowB * KG + 2 * gp + 1], bB2[rowB * KG + 2 * gp + 1]};
+            sr[j] = *reinterpret_cast<uint4*>(v);
+        }
+    }
+}
+void launch_repack_q4(const Q4W& a, const Q4W* b_pair, uint4* wr, uint4* sr, cudaStream_t st) {
+    int64_t tiles = b_pair ? a.N / 8 : a.N / 16;
+    int64_t total = tiles * (a.K / 128) * 72;
+    k_repack_q4<<<grid_for(total, 256), 256, 0, st>>>(a.w, a.s, a.b, b_pair ? b_pair->w : nullptr, b_pair ? b_pair->s : nullptr,
+                                                       b_pair ? b_pair->b : nullptr, b_pair ? 1 : 0, tiles, a.K, wr, sr);
+}
 void host_synth_tokens(uint64_t tseed, int64_t n, int32_t vocab, int32_t* out) {
     for (int64_t i = 0; i < n; ++i) out[i] = (int32_t)(mix64(tseed + SL_GOLD * (2 * (uint64_t)i + 1)) % (uint64_t)vocab);
 }
