@@ -176,6 +176,27 @@ int32_t sl_op_repack_q4_device(const void* w_dev, const void* s_dev, const void*
  * (micro-benchmarks). */
 int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
                           int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream);
+/* NO COUNTERPART IN THE REFERENCE.  Greedy tokens of final-normed rows x [M,K] against lm_head
+ * weights in the fragment-major layout above: out_tokens_dev[m] = argmax_n (x[m] . dequant4(W[n])),
+ * lowest n on ties, the same kernel sl_step_argmax ends with.  All pointers are device pointers;
+ * the work is enqueued on cuda_stream and the call returns without synchronising.
+ *
+ * This entry point allocates nothing, at set-up or per call.  It is for hosts that cannot let a
+ * library allocate: a serving process that has handed the whole of device memory to its own
+ * arena at start-up (so a late allocation can fail, or steal pages the arena counts on), and
+ * callers inside a latency-critical loop, where a device allocation may synchronise the whole
+ * device and stall unrelated streams.  The per-CTA maxima and the completion counter the kernel
+ * needs live in ONE fixed module-scope device array of 28,672 bytes, which bounds a call to
+ * M <= 8 rows; a larger M returns SL_ERR_CAPACITY (with a line on stderr) and launches nothing.
+ *   - The first call on each device looks up the array's address and sets the kernel's shared
+ *     memory attribute; make that first call before starting a stream capture.
+ *   - The array is shared by every caller in the process and keeps its last contents.  Only the
+ *     counter must start at zero: each call clears it on cuda_stream ahead of the kernel, and
+ *     the kernel leaves it at zero.  The maxima are overwritten before they are read.
+ *   - Calls that overlap in time on the same device (two streams, two threads) race on the
+ *     array and give undefined tokens: order them on one stream or with events. */
+int32_t sl_op_lm_head_argmax_static(const void* x_dev, const void* wr_dev, const void* sr_dev,
+                                    int32_t M, int32_t K, int32_t N, int32_t* out_tokens_dev, void* cuda_stream);
 /* 4-bit affine quantiser on the device: w fp16 [N,K] -> packed/scales/biases (host buffers). */
 int32_t sl_op_quantize_q4(const uint16_t* w_f16, int64_t N, int64_t K, uint32_t* packed, uint16_t* scales_f16, uint16_t* biases_f16);
 /* MoE block of `layer` on already-normed rows x [M,H]: out [M,H], inds [M,top_k], scores fp16. */

@@ -83,6 +83,7 @@ SYMBOLS = {
     "sl_op_moe_block": (_I32, [_VP, _I32, _VP, _I32, _VP, _VP, _VP]),
     "sl_op_mixer": (_I32, [_VP, _I32, _VP, _I32, _I32, _VP]),
     "sl_op_lm_head": (_I32, [_VP, _VP, _I32, _VP, _VP]),
+    "sl_op_lm_head_argmax_static": (_I32, [_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP]),
     "sl_op_layer": (_I32, [_VP, _I32, _VP, _I32, _I32, _VP]),
     "sl_op_head": (_I32, [_VP, _VP, _I32, _VP, _VP]),
     "sl_synth_tokens": (_I32, [_U64, C.c_char_p, _I64, _I32, _VP]),

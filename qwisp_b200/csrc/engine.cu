@@ -973,6 +973,25 @@ int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_
     launch_dense(PRO_PLAIN, EPI_STORE, g_gemv_mode == 1, a, (cudaStream_t)cuda_stream, false);
     return cudaGetLastError() == cudaSuccess ? SL_OK : SL_ERR_CUDA;
 }
+int32_t sl_op_lm_head_argmax_static(const void* x_dev, const void* wr_dev, const void* sr_dev,
+                                    int32_t M, int32_t K, int32_t N, int32_t* out_tokens_dev, void* cuda_stream) {
+    if (!x_dev || !wr_dev || !sr_dev || !out_tokens_dev) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (M > head_static_max_rows()) {
+        fprintf(stderr, "sl_op_lm_head_argmax_static: M = %d rows exceed the fixed scratch array's limit of %d rows per call\n",
+                (int)M, head_static_max_rows());
+        return SL_ERR_CAPACITY;
+    }
+    if (!device_ok()) return SL_ERR_NO_DEVICE;
+    DenseArgs a{}; a.q.wr = (const uint4*)wr_dev; a.q.sr = (const uint4*)sr_dev; a.q.tiles = N / 16; a.q.K = K; a.N = N; a.K = K; a.M = M;
+    a.x = (const __half*)x_dev; a.ldx = K; a.out_tok = out_tokens_dev;
+    int err = launch_head_static(a, (cudaStream_t)cuda_stream);
+    if (err != 0) {
+        fprintf(stderr, "sl_op_lm_head_argmax_static: CUDA error %d (%s)\n", err, cudaGetErrorString((cudaError_t)err));
+        return SL_ERR_CUDA;
+    }
+    return SL_OK;
+}
 int32_t sl_op_qmm4(const uint16_t* x, const uint32_t* w, const uint16_t* sc, const uint16_t* bi, int32_t M, int32_t K, int32_t N, uint16_t* y) {
     if (!x || !w || !sc || !bi || !y) return SL_ERR_INVALID;
     if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;

@@ -281,6 +281,46 @@ static void launch_head_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
     COUNT_LAUNCH();
 }
 
+// ---- lm_head + greedy argmax with its scratch in a fixed module-scope array (no allocation) ----
+// Layout of the array: [0,256) the completion counter, then per-CTA maxima as float
+// [HEAD_STATIC_MAX_ROWS][HEAD_STATIC_MAX_PARTS], then their indices as int with the same shape.
+#define HEAD_STATIC_MAX_ROWS 8
+#define HEAD_STATIC_MAX_PARTS (148 * 3)
+#define HEAD_STATIC_BYTES (256 + 2 * HEAD_STATIC_MAX_ROWS * HEAD_STATIC_MAX_PARTS * 4)
+static __device__ __align__(256) unsigned char g_head_static_scratch[HEAD_STATIC_BYTES];
+
+int head_static_max_rows() { return HEAD_STATIC_MAX_ROWS; }
+
+// Returns 0, or the cudaError_t of the failing call.  The array's address is looked up once per
+// device; nothing here allocates.  The counter is cleared on the stream before every launch, the
+// maxima need no clearing because each launch overwrites every entry it later reads.
+int launch_head_static(const DenseArgs& in, cudaStream_t st) {
+    static unsigned char* base[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return (int)err;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!base[dev]) {
+        unsigned char* ptr = nullptr;
+        err = cudaGetSymbolAddress((void**)&ptr, g_head_static_scratch);
+        if (err != cudaSuccess) return (int)err;
+        err = cudaFuncSetAttribute(k_head<PRO_PLAIN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        if (err != cudaSuccess) return (int)err;
+        base[dev] = ptr;
+    }
+    DenseArgs a = in;
+    a.counter = reinterpret_cast<unsigned*>(base[dev]);
+    a.pval = reinterpret_cast<float*>(base[dev] + 256);
+    a.pidx = reinterpret_cast<int*>(base[dev] + 256 + HEAD_STATIC_MAX_ROWS * HEAD_STATIC_MAX_PARTS * 4);
+    const int ntiles = a.N / 16;
+    int gx = (ntiles + 7) / 8; if (gx > HEAD_STATIC_MAX_PARTS) gx = HEAD_STATIC_MAX_PARTS;
+    err = cudaMemsetAsync(a.counter, 0, sizeof(unsigned), st);
+    if (err != cudaSuccess) return (int)err;
+    const size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 1, 1);
+    k_head<PRO_PLAIN, false><<<dim3((unsigned)gx, (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS)), 256, smem, st>>>(a);
+    return (int)cudaGetLastError();
+}
+
 void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl) {
     const int spw = gemv_plan(a.K).spw;
     if (epi == EPI_ARGMAX) {

@@ -88,6 +88,9 @@ struct StepEndArgs {
 };
 
 void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl);
+// lm_head + argmax whose scratch is a fixed module-scope device array; returns 0 or a cudaError_t
+int launch_head_static(const DenseArgs& a, cudaStream_t st);
+int head_static_max_rows();
 void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st);
 void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl);
 void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
