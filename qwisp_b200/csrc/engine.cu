@@ -61,8 +61,8 @@ struct sl_engine {
     float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
-    unsigned* counters = nullptr; unsigned* tile_counters = nullptr;
-    long long* dbg = nullptr;
+    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr;
+    long long* dbg = nullptr; int dbg_sel = 0;
     SegDesc* segs = nullptr;
     int hist_cap = 0;
     // pinned staging
@@ -77,7 +77,7 @@ struct sl_engine {
     std::map<int, int> eager_runs;
     bool use_graph = true;
     bool use_prefetch = true;       // L2 prefetch of the weights later kernels read
-    bool use_pdl = false;           // programmatic dependent launch between the GEMV-family kernels
+    bool use_pdl = true;            // programmatic dependent launch between the kernels of a step (SEEDLESS_PDL=0 turns it off)
     bool poisoned = false, inject = false;
     std::string fault;
 };
@@ -284,6 +284,8 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->tile_counters, (size_t)(H / 16)))) return rc;
     CU(e, cudaMemset(e->tile_counters, 0, (size_t)(H / 16) * sizeof(unsigned)));
     CU(e, cudaMemset(e->counters, 0, 8 * sizeof(unsigned)));
+    if ((rc = dalloc(e, &e->att_counters, (size_t)R * c.attn_kv_heads))) return rc;
+    CU(e, cudaMemset(e->att_counters, 0, (size_t)R * c.attn_kv_heads * sizeof(unsigned)));
     CU(e, cudaMemset(e->hist_pos, 0, sizeof(int)));
     e->pin_ints = (size_t)R * 8 + 64;
     CU(e, cudaMallocHost(&e->pin_i, e->pin_ints * sizeof(int)));
@@ -309,7 +311,7 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->kv_pool, (size_t)c.kv_pages * page_elems))) return rc;
     for (int i = c.kv_pages - 1; i >= 0; --i) e->free_pages.push_back(i);
     for (int i = S - 1; i >= 0; --i) e->free_slots.push_back(i);
-    if (getenv("SEEDLESS_DEBUG_TIMELINE")) { if ((rc = dalloc(e, &e->dbg, (size_t)64 * 8))) return rc; CU(e, cudaMemset(e->dbg, 0, 64 * 8 * 8)); }
+    if (getenv("SEEDLESS_DEBUG_TIMELINE")) { e->dbg_sel = atoi(getenv("SEEDLESS_DEBUG_TIMELINE")); if ((rc = dalloc(e, &e->dbg, (size_t)64 * 8))) return rc; CU(e, cudaMemset(e->dbg, 0, 64 * 8 * 8)); }
     const char* pfe = getenv("SEEDLESS_PREFETCH");
     if (pfe) e->use_prefetch = (pfe[0] == '1');
     const char* pd = getenv("SEEDLESS_PDL");
@@ -403,7 +405,7 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     ra.router = L.router; ra.shared_gate = L.shared_gate; ra.M = M; ra.H = e->H; ra.E = e->E;
     ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
     ra.topk = e->topk; ra.inds = e->inds; ra.scores = e->scores; ra.lists = e->lists; ra.counter = e->counters + 1;
-    ra.dbg = e->dbg;
+    ra.dbg = (e->dbg_sel == 1 && L.type_index == 0) ? e->dbg : nullptr;
     launch_router(ra, st, e->use_pdl);
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
     ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = M; ea.H = e->H; ea.I = e->I; ea.topk = e->topk;
@@ -422,8 +424,10 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
     DenseArgs d{}; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
     d.x = rows; d.ldx = e->H; d.nw = norm_w; d.eps = c.rms_eps; d.y = e->inproj; d.ldy = (int)L.in_proj.N;
     if (e->use_prefetch) pf_q4(d.pf, 0, L.r_out);
+    if (e->dbg_sel == 2 && L.type_index == 0 && !L.is_attn) d.dbg = e->dbg;
     launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, e->exact, d, st, e->use_pdl);
-    DenseArgs o{}; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
+    DenseArgs o{};
+    if (e->dbg_sel == 3 && L.type_index == 0 && !L.is_attn) o.dbg = e->dbg; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
     o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H;
     if (e->use_prefetch) {
         o.pf.p[0] = L.router; o.pf.bytes[0] = (unsigned)((size_t)e->E * e->H * 2);
@@ -441,9 +445,11 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
         a.eps = c.rms_eps; a.theta = c.rope_theta; a.tab = e->tab; a.attn_index = L.type_index; a.n_attn_layers = e->n_attn > 0 ? e->n_attn : 1;
         a.page_size = c.kv_page_size; a.kv_pool = e->kv_pool; a.segs = e->segs; a.row_seg = e->row_seg; a.row_off = e->row_off;
         a.row_pos_override = row_pos_override; a.qrot = e->qrot; a.part_o = e->part_o; a.part_ml = e->part_ml; a.nsplit = NSPLIT; a.gated = e->mix; a.M = M;
-        launch_attn_prep(a, st);
-        launch_attn_decode(a, st);
-        launch_attn_combine(a, st);
+        // a row that is its stream's only row in this call can make its own q/K/V inside the attention kernel;
+        // several rows of one stream need every row's K/V in the arena before any of them attends
+        const bool self_prep = (M == nsegs) && (row_pos_override == nullptr || M == 1);
+        if (!self_prep) launch_attn_prep(a, st);
+        launch_attn_fused(a, self_prep, e->att_counters, st, e->use_pdl && self_prep);
         o.x = e->mix; o.ldx = e->attn_out;
         launch_dense(PRO_PLAIN, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, e->use_pdl);
     }

@@ -95,7 +95,8 @@ __device__ __forceinline__ void store_staged(const XStage& st, int col, int k0, 
 // Split in two so that a kernel can put its few activation loads in flight BEFORE its many weight
 // loads (an SM serves its memory requests in order: activations queued behind 100+ KB of weights
 // would arrive last and nothing could be computed while the weights stream in), and only then
-// wait for them.  A warp owns 256-wide chunks; with two rows there are at most two per warp.
+// wait for them.  A warp owns 256-wide chunks; with two rows of K <= 4096 there are at most two per
+// warp of a 16-warp CTA (four per warp of an 8-warp CTA are not supported: K <= 2048 there).
 struct StageSrc {
     const __half* x; int ldx;        // rows (plain) / residual stream (rmsnorm) / y (normgate)
     const int* rows;                 // optional row list (shared memory), else rows row0, row0+1
@@ -113,7 +114,7 @@ __device__ __forceinline__ void stage_issue(StageRegs& sr, const StageSrc& s, in
     for (int j = 0; j < 2; ++j) {
         int u = warp + j * nw;
         if (u < units) {
-            int col = u / chunks, ch = u - col * chunks, k0 = ch * 256 + lane * 8;
+            int col = (u >= chunks) ? 1 : 0, ch = u - col * chunks, k0 = ch * 256 + lane * 8;
             int row = s.rows ? s.rows[col] : row0 + col;
             sr.a[j] = __ldcg(reinterpret_cast<const uint4*>(s.x + (size_t)row * s.ldx + k0));
             if (PRO == PRO_RMSNORM) sr.b[j] = *reinterpret_cast<const uint4*>(s.nw + k0);
@@ -152,7 +153,7 @@ __device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& 
         for (int j = 0; j < 2; ++j) {
             int u = warp + j * nw;
             if (u < units) {
-                int col = u / chunks, ch = u - col * chunks;
+                int col = (u >= chunks) ? 1 : 0, ch = u - col * chunks;
                 float ss = warp_sum(sumsq8(sr.a[j]));
                 if (lane == 0) st.part[col * 16 + ch] = ss;
             }
@@ -163,7 +164,7 @@ __device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& 
     for (int j = 0; j < 2; ++j) {
         int u = warp + j * nw;
         if (u < units) {
-            int col = u / chunks, ch = u - col * chunks, k0 = ch * 256 + lane * 8;
+            int col = (u >= chunks) ? 1 : 0, ch = u - col * chunks, k0 = ch * 256 + lane * 8;
             uint4 o;
             if (PRO == PRO_PLAIN) {
                 o = sr.a[j];
@@ -338,14 +339,23 @@ __device__ __forceinline__ float tile_value(const float* fin_tile, int row, int 
 // A tile is 16 weight rows; its K/256 slices are shared by WPT warps of SPW slices each, and a CTA
 // holds TPC tiles.  Every slice's value is kept separate and the slices are summed in ascending
 // order whatever the split, so the split is a pure scheduling choice: results do not depend on it.
-struct GemvPlan { int spw, wpt, tpc, nw; };
-__host__ __device__ inline GemvPlan gemv_plan(int K) {
+struct GemvPlan { int upw, tpc, nw, lg_slices; };
+// K/256 must be a power of two (K = 256, 512, ... 4096).  A unit is one slice of one tile; a CTA of
+// 16 warps takes UPW units per warp (unit u = warp + 16*i -> tile u >> lg_slices, slice u & (slices-1)),
+// i.e. TPC = 16*UPW/slices whole tiles.  UPW grows (to at most 3) until `groups` independent
+// problems of `ntiles` tiles fit one wave of 148 CTAs.
+__host__ __device__ inline GemvPlan gemv_plan(int K, int ntiles, int groups) {
     GemvPlan p;
     int slices = K >> 8;
-    p.spw = (slices >= 4 && slices <= 8 && (slices & 1) == 0) ? 2 : 1;
-    p.wpt = slices / p.spw;
-    p.tpc = p.wpt >= 8 ? 1 : 8 / p.wpt;
-    p.nw = p.wpt * p.tpc;
+    p.lg_slices = 0; while ((1 << p.lg_slices) < slices) ++p.lg_slices;
+    p.nw = 16;
+    long long units = (long long)ntiles * slices * groups;
+    int upw = (int)((units + 148 * 16 - 1) / (148 * 16));
+    if (upw < 1) upw = 1;
+    if (upw > 3) upw = 3;
+    while ((p.nw * upw) % slices) ++upw;          // whole tiles per CTA (slices <= 16 divides 16)
+    p.upw = upw;
+    p.tpc = p.nw * upw / slices;
     return p;
 }
 

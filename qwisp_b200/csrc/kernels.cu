@@ -57,50 +57,66 @@ int profile_report(char* buf, size_t cap) {
 // Weights are requested before the grid dependency is awaited, so under programmatic dependent
 // launch their latency overlaps the tail of the previous kernel.
 // ============================================================================================
-template <int PRO, int EPI, bool EXACT, int SPW>
-__global__ void __launch_bounds__(SPW == 2 ? 256 : 512, SPW == 2 ? 3 : 1) k_gemv(DenseArgs a) {
+static void set_pdl(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, bool pdl) {
+    if (!pdl) return;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+}
+__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define DBG_STAMP(i) do { if (a.dbg && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 60) a.dbg[blockIdx.x * 8 + (i)] = ((i) == 0 || (i) == 7) ? gtimer() : (clock64() - dbg_t0); } while (0)
+template <int PRO, int EPI, int UPW>
+__global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
+    long long dbg_t0 = clock64();
+    DBG_STAMP(0);
     extern __shared__ __align__(16) unsigned char smem[];
-    const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
-    const int slices = a.K >> 8;
-    const int WPT = slices / SPW, TPC = nw / WPT;
+    const int slices = a.K >> 8, lg = a.lg_slices;
+    const int TPC = (16 * UPW) >> lg;
     const int row0 = blockIdx.y * ROWS_PER_PASS;
     const int mr = min(ROWS_PER_PASS, a.M - row0);
     XStage st; float* red; float* fin; int* misc;
-    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), a.K, TPC * slices, TPC, st, red, fin, misc);
-
-    pdl_launch_dependents();
-    pdl_wait();
-    const int tl = warp / WPT, part = warp - tl * WPT;
-    const int tile = blockIdx.x * TPC + tl;
+    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), a.K, 16 * UPW, TPC, st, red, fin, misc);
     const int ntiles = (EPI == EPI_SWIGLU) ? a.N / 8 : a.N / 16;
-    const bool valid = tile < ntiles;
-    // activations first, then the weights, then wait for the activations (see stage_issue)
+    // The weights do not depend on the kernel before this one: their loads go out before the
+    // programmatic-launch wait, so they are in flight while that kernel finishes.  Dependents are
+    // released only after the wait, so whatever a dependent reads ahead of its own wait was written
+    // by a kernel that is complete.
+    SliceRegs regs[UPW];
+    const size_t wstep = q4r_w_uint4(a.K), sstep = q4r_s_uint4(a.K);
+#pragma unroll
+    for (int i = 0; i < UPW; ++i) {
+        const int u = warp + 16 * i, tile = blockIdx.x * TPC + (u >> lg);
+        if (tile < ntiles) load_slice(regs[i], a.q.wr + (size_t)tile * wstep, a.q.sr + (size_t)tile * sstep, u & (slices - 1), lane);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    DBG_STAMP(1);
     StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
     StageRegs sregs;
     stage_issue<PRO>(sregs, src, row0, mr, a.K);
-    SliceRegs regs[SPW];
-    if (valid) {
-        const uint4* wt = a.q.wr + (size_t)tile * q4r_w_uint4(a.K);
-        const uint4* stl = a.q.sr + (size_t)tile * q4r_s_uint4(a.K);
-#pragma unroll
-        for (int i = 0; i < SPW; ++i) load_slice(regs[i], wt, stl, part * SPW + i, lane);
-    }
     if (blockIdx.y == 0) prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
+    DBG_STAMP(2);
     stage_finish<PRO>(sregs, st, src, mr, a.K);
     __syncthreads();
-    if (valid) {
+    DBG_STAMP(3);
 #pragma unroll
-        for (int i = 0; i < SPW; ++i) {
+    for (int i = 0; i < UPW; ++i) {
+        const int u = warp + 16 * i, tile = blockIdx.x * TPC + (u >> lg);
+        if (tile < ntiles) {
             float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
-            compute_slice(regs[i], st, part * SPW + i, r, t, mr, accS, accB);
+            compute_slice(regs[i], st, u & (slices - 1), r, t, mr, accS, accB);
             finish_acc4(accS, accB, t, v);
-            store_partial(red, tl * slices + part * SPW + i, lane, v);
+            store_partial(red, u, lane, v);
         }
     }
+    DBG_STAMP(4);
     __syncthreads();
-    reduce_tiles(red, fin, TPC, slices);
+    DBG_STAMP(5);
+    reduce_tiles(red, fin, min(TPC, ntiles - (int)blockIdx.x * TPC), slices);
     __syncthreads();
+    DBG_STAMP(6);
     if (EPI == EPI_STORE || EPI == EPI_RESID) {
         for (int i = threadIdx.x; i < TPC * 32; i += blockDim.x) {
             int tl2 = i >> 5, col = (i >> 4) & 1, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
@@ -120,17 +136,26 @@ __global__ void __launch_bounds__(SPW == 2 ? 256 : 512, SPW == 2 ? 3 : 1) k_gemv
             }
         }
     }
+    DBG_STAMP(7);
+}
+template <int PRO, int EPI, int UPW>
+static void launch_gemv_t(const DenseArgs& a, const GemvPlan& pl, cudaStream_t st, bool pdl) {
+    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 16 * UPW, pl.tpc);
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_gemv<PRO, EPI, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
+    int ntiles = EPI == EPI_SWIGLU ? a.N / 8 : a.N / 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS));
+    cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    set_pdl(cfg, attr, pdl);
+    DenseArgs copy = a; copy.lg_slices = pl.lg_slices;
+    ProfScope ps("k_gemv", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
+    cudaLaunchKernelEx(&cfg, k_gemv<PRO, EPI, UPW>, copy);
+    COUNT_LAUNCH();
 }
 
-// ============================================================================================
-// lm_head + greedy argmax, streaming flavour: a warp owns whole tiles (all K), walks its tiles with
-// the next slice's weights always in flight, and keeps a running first-index maximum per activation
-// row; CTAs are persistent.  Only per-CTA (value, index) partials and, at the end, one int32 per
-// row leave the kernel (logits are written only on request).  grid (<= 148*3, ceil(M/8)), 256 threads.
-// (argmax rule: swift/Sources/QwispCore/SeedlessFusedVerify.swift:572-596)
-// ============================================================================================
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
-
 template <int PRO, bool EXACT>
 __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -147,11 +172,11 @@ __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
     SliceRegs cur, nxt;
     const size_t wstep = q4r_w_uint4(a.K), sstep = q4r_s_uint4(a.K);
     auto load = [&](SliceRegs& rg, int tl, int sl_i) { load_slice(rg, a.q.wr + (size_t)tl * wstep, a.q.sr + (size_t)tl * sstep, sl_i, lane); };
-    pdl_launch_dependents();
+    if (have) load(cur, tile, 0);                 // weights: ahead of the programmatic-launch wait
     pdl_wait();
+    pdl_launch_dependents();
     if (PRO == PRO_PLAIN) stage_plain(st, a.x, a.ldx, row0, mr, a.K);
     else stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K);
-    if (have) load(cur, tile, 0);
     __syncthreads();
     float best[2] = {-INFINITY, -INFINITY}; int besti[2] = {0x7fffffff, 0x7fffffff};
     while (have) {
@@ -238,31 +263,6 @@ __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
     if (threadIdx.x == 0) *a.counter = 0u;
 }
 
-static void set_pdl(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, bool pdl) {
-    if (!pdl) return;
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-}
-
-template <int PRO, int EPI, bool EXACT, int SPW>
-static void launch_gemv_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
-    GemvPlan pl = gemv_plan(a.K);
-    int slices = a.K / 256;
-    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, pl.tpc * slices, pl.tpc);
-    static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_gemv<PRO, EPI, EXACT, SPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
-    int ntiles = EPI == EPI_SWIGLU ? a.N / 8 : a.N / 16;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS));
-    cfg.blockDim = dim3(pl.nw * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    set_pdl(cfg, attr, pdl);
-    DenseArgs copy = a;
-    ProfScope ps("k_gemv", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
-    cudaLaunchKernelEx(&cfg, k_gemv<PRO, EPI, EXACT, SPW>, copy);
-    COUNT_LAUNCH();
-}
 template <int PRO, bool EXACT>
 static void launch_head_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
     size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 1, 1);
@@ -322,15 +322,16 @@ int launch_head_static(const DenseArgs& in, cudaStream_t st) {
 }
 
 void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl) {
-    const int spw = gemv_plan(a.K).spw;
     if (epi == EPI_ARGMAX) {
         if (pro == PRO_RMSNORM) { if (exact) launch_head_t<PRO_RMSNORM, true>(a, st, pdl); else launch_head_t<PRO_RMSNORM, false>(a, st, pdl); return; }
         if (pro == PRO_PLAIN) { if (exact) launch_head_t<PRO_PLAIN, true>(a, st, pdl); else launch_head_t<PRO_PLAIN, false>(a, st, pdl); return; }
     }
+    const GemvPlan pl = gemv_plan(a.K, epi == EPI_SWIGLU ? a.N / 8 : a.N / 16, 1);
 #define SL_CASE(P, E)                                                                                       \
     if (pro == P && epi == E) {                                                                             \
-        if (exact) { if (spw == 2) launch_gemv_t<P, E, true, 2>(a, st, pdl); else launch_gemv_t<P, E, true, 1>(a, st, pdl); }    \
-        else { if (spw == 2) launch_gemv_t<P, E, false, 2>(a, st, pdl); else launch_gemv_t<P, E, false, 1>(a, st, pdl); }        \
+        if (pl.upw == 1) launch_gemv_t<P, E, 1>(a, pl, st, pdl);                                            \
+        else if (pl.upw == 2) launch_gemv_t<P, E, 2>(a, pl, st, pdl);                                       \
+        else launch_gemv_t<P, E, 3>(a, pl, st, pdl);                                                        \
         return;                                                                                             \
     }
     SL_CASE(PRO_PLAIN, EPI_STORE)
@@ -494,21 +495,22 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     __shared__ int s_last; __shared__ int s_cnt[256]; __shared__ int s_cur[256]; __shared__ int s_off[256];
     __shared__ float s_route[8][512 + 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    pdl_launch_dependents();
-    pdl_wait();
     long long tq0 = clock64(), tq[6] = {0, 0, 0, 0, 0, 0};
     const int nblk = a.H >> 8;                                // <= 16
     const bool tail = (blockIdx.x == gridDim.x - 1);
     const int e = blockIdx.x * 8 + warp;
-    // the first row's activations and norm weights go out ahead of the (much larger) weight loads
+    // router rows and norm weights do not depend on the kernel before: loaded ahead of the wait
     uint4 pv = make_uint4(0, 0, 0, 0), pw = make_uint4(0, 0, 0, 0);
-    if (a.norm_w && tid * 8 < a.H) { pv = *reinterpret_cast<const uint4*>(a.h + tid * 8); pw = *reinterpret_cast<const uint4*>(a.norm_w + tid * 8); }
+    if (a.norm_w && tid * 8 < a.H) pw = *reinterpret_cast<const uint4*>(a.norm_w + tid * 8);
     uint4 wreg[16];
     const __half* wrow = tail ? a.shared_gate : (a.router + (size_t)e * a.H);
     const bool wvalid = tail ? (warp == 0) : (e < a.E);
 #pragma unroll
     for (int kb = 0; kb < 16; ++kb)
         wreg[kb] = (wvalid && kb < nblk) ? *reinterpret_cast<const uint4*>(wrow + kb * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+    pdl_wait();
+    pdl_launch_dependents();
+    if (a.norm_w && tid * 8 < a.H) pv = *reinterpret_cast<const uint4*>(a.h + tid * 8);
     prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
     tq[0] = clock64() - tq0;
     for (int m0 = 0; m0 < a.M; m0 += 8) {
@@ -621,29 +623,42 @@ __device__ __forceinline__ void expert_tile(const ExpertArgs& a, bool shared, in
     const size_t T = (size_t)e * (DOWN ? a.H / 16 : a.I / 8) + tile;
     wt = q.wr + T * q4r_w_uint4(K); stl = q.sr + T * q4r_s_uint4(K);
 }
-template <bool EXACT, bool DOWN, int SPW>
-__global__ void __launch_bounds__(SPW == 2 ? 256 : 512, SPW == 2 ? 2 : 1) k_expert(ExpertArgs a) {
+template <bool DOWN, int UPW>
+__global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
     const int K = DOWN ? a.I : a.H;
-    const int slices = K >> 8, WPT = slices / SPW, TPC = nw / WPT;
+    const int slices = K >> 8, lg = a.lg_slices;
+    const int TPC = (16 * UPW) >> lg;
     const int slot = blockIdx.y;
     const bool shared = (slot == (int)gridDim.y - 1);
-    const int tl = warp / WPT, part = warp - tl * WPT;
-    const int tile = blockIdx.x * TPC + tl;
     const int ntiles = DOWN ? a.H / 16 : a.I / 8;
-    const bool valid = tile < ntiles;
     const int npair = a.M * a.topk;
-    SliceRegs regs[SPW];
-    pdl_launch_dependents();
-    pdl_wait();
+    SliceRegs regs[UPW];
     XStage st; float* red; float* fin; int* misc;
-    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), K, TPC * slices, TPC, st, red, fin, misc);
+    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), K, 16 * UPW, TPC, st, red, fin, misc);
+    // What may be read ahead of the programmatic-launch wait: data written two or more kernels back
+    // (every kernel releases its dependents only after its own wait).  For the down kernel that
+    // covers the router's lists, so its weights are in flight while gate/up still computes; for
+    // gate/up (which follows the router directly) only the shared expert's weights qualify.
+    const bool early = DOWN || shared;
+    if (!early) { pdl_wait(); pdl_launch_dependents(); }
     const int n_active = *a.lists.n_active;
     const bool active = shared || slot < n_active;
+    const int e = (shared || !active) ? 0 : a.lists.slot_expert[slot];
     if (active) {
-        const int e = shared ? 0 : a.lists.slot_expert[slot];
+        const Q4R& q = DOWN ? (shared ? a.sh_down : a.down) : (shared ? a.sh_gu : a.gu);
+        const size_t wstep = q4r_w_uint4(K), sstep = q4r_s_uint4(K);
+        const size_t T0 = (size_t)e * ntiles;
+#pragma unroll
+        for (int i = 0; i < UPW; ++i) {
+            const int u = warp + 16 * i, tile = blockIdx.x * TPC + (u >> lg);
+            if (tile < ntiles) load_slice(regs[i], q.wr + (T0 + tile) * wstep, q.sr + (T0 + tile) * sstep, u & (slices - 1), lane);
+        }
+    }
+    if (early) { pdl_wait(); pdl_launch_dependents(); }
+    if (active) {
         const int cnt = shared ? a.M : a.lists.slot_cnt[slot];
         const int off = shared ? 0 : a.lists.slot_off[slot];
         for (int c0 = 0; c0 < cnt; c0 += ROWS_PER_PASS) {
@@ -658,40 +673,23 @@ __global__ void __launch_bounds__(SPW == 2 ? 256 : 512, SPW == 2 ? 2 : 1) k_expe
                 misc[8 + threadIdx.x] = dst;               // destination row
             }
             __syncthreads();
-            // activations first, then (first pass) the expert's weights, then wait for the activations
             StageSrc src{DOWN ? a.hbuf : a.p, DOWN ? a.I : a.H, misc, nullptr, nullptr, 0, 0.f};
             StageRegs sregs;
             stage_issue<PRO_PLAIN>(sregs, src, 0, mr, K);
-            if (c0 == 0) {
-                if (valid) {
-                    const uint4 *wt, *stl; expert_tile<DOWN>(a, shared, e, tile, K, wt, stl);
-#pragma unroll
-                    for (int i = 0; i < SPW; ++i) load_slice(regs[i], wt, stl, part * SPW + i, lane);
-                }
-                if (!DOWN) {
-                    // pull what the down kernel will read for this expert into L2: this CTA's 1/gridDim.x share
-                    const Q4R& qd = shared ? a.sh_down : a.down;
-                    const size_t wbytes = (size_t)(a.H / 16) * q4r_w_uint4(a.I) * 16, gbytes = (size_t)(a.H / 16) * q4r_s_uint4(a.I) * 16;
-                    PfList pd{};
-                    pd.p[0] = reinterpret_cast<const char*>(qd.wr) + (size_t)e * wbytes; pd.bytes[0] = (unsigned)wbytes;
-                    pd.p[1] = reinterpret_cast<const char*>(qd.sr) + (size_t)e * gbytes; pd.bytes[1] = (unsigned)gbytes;
-                    prefetch_ranges(pd, blockIdx.x, gridDim.x);
-                    prefetch_ranges(a.pf, (shared ? n_active : slot) * gridDim.x + blockIdx.x, gridDim.x * (n_active + 1));
-                }
-            }
             stage_finish<PRO_PLAIN>(sregs, st, src, mr, K);
             __syncthreads();
-            if (valid) {
 #pragma unroll
-                for (int i = 0; i < SPW; ++i) {
+            for (int i = 0; i < UPW; ++i) {
+                const int u = warp + 16 * i, tile = blockIdx.x * TPC + (u >> lg);
+                if (tile < ntiles) {
                     float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
-                    compute_slice(regs[i], st, part * SPW + i, r, t, mr, accS, accB);
+                    compute_slice(regs[i], st, u & (slices - 1), r, t, mr, accS, accB);
                     finish_acc4(accS, accB, t, v);
-                    store_partial(red, tl * slices + part * SPW + i, lane, v);
+                    store_partial(red, u, lane, v);
                 }
             }
             __syncthreads();
-            reduce_tiles(red, fin, TPC, slices);
+            reduce_tiles(red, fin, min(TPC, ntiles - (int)blockIdx.x * TPC), slices);
             __syncthreads();
             if (DOWN) {
                 for (int i = threadIdx.x; i < TPC * 32; i += blockDim.x) {
@@ -735,34 +733,34 @@ __global__ void __launch_bounds__(SPW == 2 ? 256 : 512, SPW == 2 ? 2 : 1) k_expe
         else a.out[(size_t)m * a.H + n] = res;
     }
 }
-template <bool EXACT, bool DOWN, int SPW>
-static void launch_expert_t(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) {
+template <bool DOWN, int UPW>
+static void launch_expert_t(const ExpertArgs& a, const GemvPlan& pl, int nslots, cudaStream_t st, bool pdl) {
     int K = DOWN ? a.I : a.H;
-    GemvPlan pl = gemv_plan(K);
-    int slices = K / 256;
-    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, K, pl.tpc * slices, pl.tpc);
+    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, K, 16 * UPW, pl.tpc);
     static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_expert<EXACT, DOWN, SPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
+    if (!configured) { cudaFuncSetAttribute(k_expert<DOWN, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
     int ntiles = DOWN ? a.H / 16 : a.I / 8;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)(nslots + 1));
-    cfg.blockDim = dim3(pl.nw * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     set_pdl(cfg, attr, pdl);
-    ExpertArgs copy = a;
-    int touched = (a.M * a.topk < nslots ? a.M * a.topk : nslots) + 1;   // distinct experts read: exact for one row, an upper bound otherwise
-    ProfScope ps(DOWN ? "k_expert_down" : "k_expert_gateup", (double)touched * (DOWN ? 1 : 2) * a.I * a.H * 0.5625, st);
-    cudaLaunchKernelEx(&cfg, k_expert<EXACT, DOWN, SPW>, copy);
+    ExpertArgs copy = a; copy.lg_slices = pl.lg_slices;
+    ProfScope ps(DOWN ? "k_expert_down" : "k_expert_gateup", 0.0, st);
+    cudaLaunchKernelEx(&cfg, k_expert<DOWN, UPW>, copy);
     COUNT_LAUNCH();
 }
+// the plan is sized for the batch-1 case (top_k routed experts + the shared one share a wave); the
+// combine in the down kernel works on groups of TPC tiles, so tile_counter needs H/16/TPC entries
 template <bool DOWN>
-static void launch_expert_d(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) {
-    int spw = gemv_plan(DOWN ? a.I : a.H).spw;
-    if (exact) { if (spw == 2) launch_expert_t<true, DOWN, 2>(a, nslots, st, pdl); else launch_expert_t<true, DOWN, 1>(a, nslots, st, pdl); }
-    else { if (spw == 2) launch_expert_t<false, DOWN, 2>(a, nslots, st, pdl); else launch_expert_t<false, DOWN, 1>(a, nslots, st, pdl); }
+static void launch_expert_d(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) {
+    const GemvPlan pl = gemv_plan(DOWN ? a.I : a.H, DOWN ? a.H / 16 : a.I / 8, a.topk + 1);
+    if (pl.upw == 1) launch_expert_t<DOWN, 1>(a, pl, nslots, st, pdl);
+    else if (pl.upw == 2) launch_expert_t<DOWN, 2>(a, pl, nslots, st, pdl);
+    else launch_expert_t<DOWN, 3>(a, pl, nslots, st, pdl);
 }
-void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { launch_expert_d<false>(exact, a, nslots, st, pdl); }
-void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { launch_expert_d<true>(exact, a, nslots, st, pdl); }
+void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { (void)exact; launch_expert_d<false>(a, nslots, st, pdl); }
+void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { (void)exact; launch_expert_d<true>(a, nslots, st, pdl); }
 
 // ============================================================================================
 // Gated-delta-net core: causal conv1d + SiLU, q/k l2-style norm + scale, beta / decay, the
@@ -790,11 +788,12 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
     __half* hist_out = a.tab.conv_hist + (size_t)seg.slot * a.tab.hist_stride_stream + (size_t)(side ^ 1) * a.tab.hist_stride_side +
                        (size_t)a.gdn_index * a.tab.hist_stride_layer;
     // state rows of this warp: 4 rows, lane owns dk 4*lane .. 4*lane+3
-    pdl_launch_dependents();
-    pdl_wait();
+    // the state was written a whole step ago: loaded ahead of the programmatic-launch wait
     float4 S[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) S[i] = *reinterpret_cast<const float4*>(S_in + (size_t)(warp * 4 + i) * GDN_DK + lane * 4);
+    pdl_wait();
+    pdl_launch_dependents();
 
     const int ch_q = hk * GDN_DK + tid, ch_k = keyDim + hk * GDN_DK + tid;
     const int ch_v = 2 * keyDim + hv * GDN_DV + dvt * 16 + (tid & 15);
@@ -1034,6 +1033,222 @@ void launch_attn_decode(const AttnArgs& a, cudaStream_t st) {
     k_attn_decode<<<grid, 256, 0, st>>>(a);
     COUNT_LAUNCH();
 }
+// ---- one-kernel attention: (optional) q/k prep + split-KV decode + merge of the splits ----
+// norm + partial rotation of one 256-wide head held as 8 values per lane; returns the fp16 values
+__device__ __forceinline__ uint4 norm_rope_head(const __half* src, const __half* w, float eps, float theta, int pos, int lane) {
+    uint4 v = reinterpret_cast<const uint4*>(src)[lane];
+    uint4 wv = reinterpret_cast<const uint4*>(w)[lane];
+    const __half* vh = reinterpret_cast<const __half*>(&v);
+    const __half* wh = reinterpret_cast<const __half*>(&wv);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { float f = h2f(vh[i]); ss = fmaf(f, f, ss); }
+    ss = warp_sum(ss);
+    float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), eps));
+    float nv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) nv[i] = h2f(hmul_rn(wh[i], f2h(__fmul_rn(h2f(vh[i]), inv))));
+    float other[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, nv[i], 4);
+    uint4 o; __half* oh = reinterpret_cast<__half*>(&o);
+    const float fpos = (float)pos;
+    const float lnb = logf(theta);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        int d = lane * 8 + i;
+        if (d >= ROPE_D) { oh[i] = f2h(nv[i]); continue; }
+        int ii = (d < 32) ? d : (d - 32);
+        float freq = expf(-2.0f * (float)ii / (float)ROPE_D * lnb);
+        float ang = fpos * freq;
+        float sn, cs; sincosf(ang, &sn, &cs);
+        float x0 = (d < 32) ? nv[i] : other[i], x1 = (d < 32) ? other[i] : nv[i];
+        oh[i] = f2h((d < 32) ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs));
+    }
+    return o;
+}
+// grid (nsplit, KV heads, M), 256 threads, dynamic shared memory 8*8*256 floats.
+// prep != 0 (every row is the only row of its stream in this launch): each CTA norms and rotates its
+// 8 query heads itself, and the CTA whose key range holds the row's own position also makes that
+// position's K and V, stores them in the arena and uses them from shared memory.  prep == 0: q and
+// the arena were written by k_attn_prep.  Either way the CTA that finishes last for a (row, kv head)
+// merges the splits, normalises, rounds to fp16 and applies the sigmoid output gate.
+__global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsigned* counters) {
+    extern __shared__ __align__(16) float sm_acc[];           // [8 warps][8 heads][256]
+    __shared__ float sm_m[8][ATT_G], sm_l[8][ATT_G];
+    __shared__ __align__(16) __half sq[ATT_G][ATT_D];
+    __shared__ __align__(16) __half sk[ATT_D], sv[ATT_D];
+    __shared__ int s_last;
+    const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int slot = a.segs[a.row_seg[m]].slot;
+    const int pos_m = row_position(a, m);
+    const int N = pos_m + 1;
+    const int chunk = 32 * ((N + 32 * a.nsplit - 1) / (32 * a.nsplit));
+    const int used = (N + chunk - 1) / chunk;
+    if (split >= used) return;
+    const int p0 = split * chunk, p1 = min(N, p0 + chunk);
+    const bool own = prep && (pos_m >= p0) && (pos_m < p1);
+    const __half* rowp = a.inproj + (size_t)m * a.ld;
+    if (prep) {
+        uint4 qo = norm_rope_head(rowp + (size_t)(kvh * ATT_G + warp) * 2 * ATT_D, a.q_norm, a.eps, a.theta, pos_m, lane);
+        reinterpret_cast<uint4*>(sq[warp])[lane] = qo;
+        if (own && warp == 0) {
+            uint4 ko = norm_rope_head(rowp + a.NH * 2 * ATT_D + kvh * ATT_D, a.k_norm, a.eps, a.theta, pos_m, lane);
+            reinterpret_cast<uint4*>(sk)[lane] = ko;
+            reinterpret_cast<uint4*>(kv_ptr(a, slot, pos_m, 0, kvh))[lane] = ko;
+        }
+        if (own && warp == 1) {
+            uint4 vo = reinterpret_cast<const uint4*>(rowp + a.NH * 2 * ATT_D + a.KV * ATT_D + kvh * ATT_D)[lane];
+            reinterpret_cast<uint4*>(sv)[lane] = vo;
+            reinterpret_cast<uint4*>(kv_ptr(a, slot, pos_m, 1, kvh))[lane] = vo;
+        }
+    } else {
+        reinterpret_cast<uint4*>(sq[warp])[lane] = reinterpret_cast<const uint4*>(a.qrot + ((size_t)m * a.NH + kvh * ATT_G + warp) * ATT_D)[lane];
+    }
+    __syncthreads();
+    const float scale = 0.0625f;                              // 256^-0.5
+    float q[ATT_G][8];
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g) {
+        uint4 qv = reinterpret_cast<const uint4*>(sq[g])[lane];
+        const __half* qh = reinterpret_cast<const __half*>(&qv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[g][i] = scale * h2f(qh[i]);
+    }
+    float mx[ATT_G], l[ATT_G], acc[ATT_G][8];
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g) { mx[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = 0.f; }
+    for (int pos = p0 + warp; pos < p1; pos += 8) {
+        uint4 kvv, vvv;
+        if (own && pos == pos_m) { kvv = reinterpret_cast<const uint4*>(sk)[lane]; vvv = reinterpret_cast<const uint4*>(sv)[lane]; }
+        else {
+            kvv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 0, kvh))[lane];
+            vvv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 1, kvh))[lane];
+        }
+        const __half* kh = reinterpret_cast<const __half*>(&kvv);
+        const __half* vh = reinterpret_cast<const __half*>(&vvv);
+        float kf[8], vf[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { kf[i] = h2f(kh[i]); vf[i] = h2f(vh[i]); }
+#pragma unroll
+        for (int g = 0; g < ATT_G; ++g) {
+            float sc = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sc = fmaf(q[g][i], kf[i], sc);
+            sc = warp_sum(sc);
+            float nm = fmaxf(mx[g], sc);
+            float factor = __expf(mx[g] - nm), es = __expf(sc - nm);
+            mx[g] = nm; l[g] = l[g] * factor + es;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], factor, es * vf[i]);
+        }
+    }
+    // ---- merge the 8 warps: all heads at once through shared memory ----
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < ATT_G; ++g) { sm_m[warp][g] = mx[g]; sm_l[warp][g] = l[g]; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < ATT_G; ++g) {
+        float gm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) gm = fmaxf(gm, sm_m[w][g]);
+        float f = (mx[g] == -INFINITY) ? 0.f : __expf(mx[g] - gm);
+        float4 lo = make_float4(acc[g][0] * f, acc[g][1] * f, acc[g][2] * f, acc[g][3] * f);
+        float4 hi = make_float4(acc[g][4] * f, acc[g][5] * f, acc[g][6] * f, acc[g][7] * f);
+        float4* dst = reinterpret_cast<float4*>(sm_acc + ((size_t)warp * ATT_G + g) * ATT_D + lane * 8);
+        dst[0] = lo; dst[1] = hi;
+    }
+    __syncthreads();
+    {
+        const int d = threadIdx.x;                            // 256 threads = 256 dims
+        float* po = a.part_o + (((size_t)m * a.NH + kvh * ATT_G) * a.nsplit + split) * ATT_D;
+#pragma unroll
+        for (int g = 0; g < ATT_G; ++g) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) o += sm_acc[((size_t)w * ATT_G + g) * ATT_D + d];
+            po[(size_t)g * a.nsplit * ATT_D + d] = o;
+        }
+        if (d < ATT_G) {
+            const int g = d;
+            float gm = -INFINITY;
+            for (int w = 0; w < 8; ++w) gm = fmaxf(gm, sm_m[w][g]);
+            float ls = 0.f;
+            for (int w = 0; w < 8; ++w) ls += (sm_m[w][g] == -INFINITY) ? 0.f : sm_l[w][g] * __expf(sm_m[w][g] - gm);
+            float* pml = a.part_ml + (((size_t)m * a.NH + kvh * ATT_G + g) * a.nsplit + split) * 2;
+            pml[0] = gm; pml[1] = ls;
+        }
+    }
+    // ---- the CTA that finishes last for this (row, kv head) merges the splits ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned ticket = atomicAdd(counters + m * a.KV + kvh, 1u);
+        s_last = (ticket == (unsigned)used - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    {
+        const int g = warp, h = kvh * ATT_G + g;
+        const float* po = a.part_o + ((size_t)m * a.NH + h) * a.nsplit * ATT_D;
+        const float* pml = a.part_ml + ((size_t)m * a.NH + h) * a.nsplit * 2;
+        float msv[2], lsv[2], fv[2];                          // nsplit <= 64: two splits per lane
+        float gm = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            int sp = j * 32 + lane;
+            msv[j] = -INFINITY; lsv[j] = 0.f;
+            if (sp < used) { float2 ml = __ldcg(reinterpret_cast<const float2*>(pml) + sp); msv[j] = ml.x; lsv[j] = ml.y; }
+            gm = fmaxf(gm, msv[j]);
+        }
+        gm = warp_max(gm);
+        float tot = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) { fv[j] = (msv[j] == -INFINITY) ? 0.f : __expf(msv[j] - gm); tot += lsv[j] * fv[j]; }
+        tot = warp_sum(tot);
+        float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int sp = 0; sp < used; ++sp) {
+            float f = __shfl_sync(0xffffffffu, (sp < 32) ? fv[0] : fv[1], sp & 31);
+            const float4* src = reinterpret_cast<const float4*>(po + (size_t)sp * ATT_D + lane * 8);
+            float4 x0 = __ldcg(src), x1 = __ldcg(src + 1);
+            o[0] = fmaf(x0.x, f, o[0]); o[1] = fmaf(x0.y, f, o[1]); o[2] = fmaf(x0.z, f, o[2]); o[3] = fmaf(x0.w, f, o[3]);
+            o[4] = fmaf(x1.x, f, o[4]); o[5] = fmaf(x1.y, f, o[5]); o[6] = fmaf(x1.z, f, o[6]); o[7] = fmaf(x1.w, f, o[7]);
+        }
+        uint4 gvv = reinterpret_cast<const uint4*>(rowp + (size_t)h * 2 * ATT_D + ATT_D)[lane];
+        const __half* gh = reinterpret_cast<const __half*>(&gvv);
+        uint4 outv; __half* oh = reinterpret_cast<__half*>(&outv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            __half out = f2h(tot == 0.f ? o[i] : o[i] / tot);
+            oh[i] = hmul_rn(out, sigmoid_h(gh[i]));
+        }
+        reinterpret_cast<uint4*>(a.gated + ((size_t)m * a.NH + h) * ATT_D)[lane] = outv;
+    }
+    if (threadIdx.x == 0) counters[m * a.KV + kvh] = 0u;
+}
+void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStream_t st, bool pdl) {
+    static bool configured = false;
+    const size_t smem = (size_t)8 * ATT_G * ATT_D * sizeof(float);
+    if (!configured) { cudaFuncSetAttribute(k_attn_fused, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); configured = true; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)a.nsplit, (unsigned)a.KV, (unsigned)a.M);
+    cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    set_pdl(cfg, attr, pdl);
+    AttnArgs copy = a; int p = prep ? 1 : 0;
+    ProfScope ps("k_attn_fused", 0.0, st);
+    cudaLaunchKernelEx(&cfg, k_attn_fused, copy, p, counters);
+    COUNT_LAUNCH();
+}
+
 // grid (NH, M), 256 threads: merge splits, normalise, round to fp16, multiply by sigmoid(gate) in fp16
 __global__ void __launch_bounds__(256) k_attn_combine(AttnArgs a) {
     const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;

@@ -7,6 +7,8 @@ namespace sl {
 struct Q4W { const uint32_t* w = nullptr; const __half* s = nullptr; const __half* b = nullptr; int64_t N = 0; int K = 0; };
 
 struct DenseArgs {
+    long long* dbg = nullptr;            // optional per-CTA clock stamps (development aid)
+    int lg_slices = 0;                   // log2(K/256), filled by the launcher
     Q4R q;                                                       // repacked weights (tiles of 16 rows)
     int N, K, M;                                                 // N outputs (= 16 * tiles)
     const __half* x; int ldx;                                    // activations (plain) / residual stream (rmsnorm) / y (normgate)
@@ -43,6 +45,8 @@ struct RouterArgs {
 };
 
 struct ExpertArgs {
+    long long* dbg = nullptr;            // optional per-CTA clock stamps (development aid)
+    int lg_slices = 0;                   // log2(K/256), filled by the launcher
     Q4R gu, down;                        // expert slabs, repacked: gate/up paired tiles (I/8 per expert), down tiles (H/16 per expert)
     Q4R sh_gu, sh_down;
     MoeLists lists;
@@ -98,6 +102,8 @@ void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl);
 void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
 void launch_attn_decode(const AttnArgs& a, cudaStream_t st);
+// q/k prep (when every row is its stream's only row) + split-KV decode + merge in one launch; counters: M*KV zeros
+void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStream_t st, bool pdl);
 void launch_attn_combine(const AttnArgs& a, cudaStream_t st);
 void launch_step_end(const StepEndArgs& a, cudaStream_t st);
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st);
