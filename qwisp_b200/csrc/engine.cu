@@ -61,7 +61,7 @@ struct sl_engine {
     float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
-    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr;
+    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr;
     long long* dbg = nullptr; int dbg_sel = 0;
     SegDesc* segs = nullptr;
     int hist_cap = 0;
@@ -284,6 +284,8 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->tile_counters, (size_t)(H / 16)))) return rc;
     CU(e, cudaMemset(e->tile_counters, 0, (size_t)(H / 16) * sizeof(unsigned)));
     CU(e, cudaMemset(e->counters, 0, 8 * sizeof(unsigned)));
+    if ((rc = dalloc(e, &e->err_flag, (size_t)4))) return rc;
+    CU(e, cudaMemset(e->err_flag, 0, 4 * sizeof(unsigned)));
     if ((rc = dalloc(e, &e->att_counters, (size_t)R * c.attn_kv_heads))) return rc;
     CU(e, cudaMemset(e->att_counters, 0, (size_t)R * c.attn_kv_heads * sizeof(unsigned)));
     CU(e, cudaMemset(e->hist_pos, 0, sizeof(int)));
@@ -409,7 +411,7 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     launch_router(ra, st, e->use_pdl);
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
     ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = M; ea.H = e->H; ea.I = e->I; ea.topk = e->topk;
-    ea.scores = e->scores; ea.sgl = e->sgl; ea.resid = resid; ea.out = plain_out; ea.tile_counter = e->tile_counters;
+    ea.scores = e->scores; ea.sgl = e->sgl; ea.resid = resid; ea.out = plain_out; ea.tile_counter = e->tile_counters; ea.err = e->err_flag;
     if (e->use_prefetch) { if (next) pf_q4(ea.pf, 0, next->r_in); else pf_q4(ea.pf, 0, e->r_lm_head, (size_t)24 << 20); }
     int nslots = M * e->topk < e->E ? M * e->topk : e->E;
     launch_expert_gateup(e->exact, ea, nslots, st, e->use_pdl);
@@ -421,13 +423,13 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
                    __half* resid, __half* plain_out, const int* row_pos_override) {
     cudaStream_t st = e->stream;
     const sl_config& c = e->cfg;
-    DenseArgs d{}; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
+    DenseArgs d{}; d.err = e->err_flag; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
     d.x = rows; d.ldx = e->H; d.nw = norm_w; d.eps = c.rms_eps; d.y = e->inproj; d.ldy = (int)L.in_proj.N;
     if (e->use_prefetch) pf_q4(d.pf, 0, L.r_out);
     if (e->dbg_sel == 2 && L.type_index == 0 && !L.is_attn) d.dbg = e->dbg;
     launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, e->exact, d, st, e->use_pdl);
     DenseArgs o{};
-    if (e->dbg_sel == 3 && L.type_index == 0 && !L.is_attn) o.dbg = e->dbg; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
+    if (e->dbg_sel == 3 && L.type_index == 0 && !L.is_attn) o.dbg = e->dbg; o.err = e->err_flag; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
     o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H;
     if (e->use_prefetch) {
         o.pf.p[0] = L.router; o.pf.bytes[0] = (unsigned)((size_t)e->E * e->H * 2);
@@ -675,7 +677,17 @@ int32_t sl_engine_read_tensor(sl_engine* e, const char* name, void* host_buf, ui
     CU(e, cudaMemcpy(host_buf, it->second.ptr, nbytes, cudaMemcpyDeviceToHost));
     return SL_OK;
 }
-const char* sl_last_fault(sl_engine* e) { return (e && e->poisoned) ? e->fault.c_str() : nullptr; }
+const char* sl_last_fault(sl_engine* e) {
+    if (!e) return nullptr;
+    if (!e->poisoned && e->err_flag) {
+        // a kernel whose bounded wait on a bulk copy gave up leaves a mark here instead of hanging
+        unsigned flag = 0;
+        if (cudaStreamSynchronize(e->stream) == cudaSuccess && cudaMemcpy(&flag, e->err_flag, sizeof(flag), cudaMemcpyDeviceToHost) == cudaSuccess && flag) {
+            e->poisoned = true; e->fault = "a kernel gave up waiting for a bulk copy into shared memory";
+        }
+    }
+    return e->poisoned ? e->fault.c_str() : nullptr;
+}
 int32_t sl_inject_fault(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->inject = on != 0; return SL_OK; }
 int64_t sl_engine_launch_count(sl_engine* e) { (void)e; return kernel_launch_count(); }
 int32_t sl_debug_read(sl_engine* e, long long* out, int32_t n) {

@@ -4,24 +4,27 @@
 // word w[n, k/8] (low nibble first) -- the MLX affine layout of the reference
 // (swift/Sources/QwispCore/SeedlessMetalForward.swift:219-221, 238-310).
 //
-// B200 formulation.  HBM-bound, and at one activation row the legacy f16 tensor path would
-// itself become a bottleneck, so the goal is few instructions AND few MMAs per weight nibble:
-//   * a 4-bit value q in the low half of a byte, read as an fp8 e4m3 number, is exactly q * 2^-9
-//     (q < 8 are subnormals, q >= 8 normals with exponent field 1), so nibbles become tensor-core
-//     operands with one AND (and one shift for the odd ones): no conversion, no table;
-//   * mma.sync m16n8k32 e4m3 x e4m3 -> f32 consumes 16 weight rows x 32 inputs per instruction;
-//   * an fp16 activation is split exactly into three e4m3 terms x = x1 + x2/16 + x3/256 (each
-//     term carries 4 significant bits of the residual); the three terms sit in three of the eight
-//     MMA columns, so one instruction yields all three partial products and an MMA pass serves
-//     two activation rows (columns 0-2 and 3-5).  Products are exact, accumulation is f32;
+// B200 formulation.  HBM-bound; the work per weight nibble on the SM must stay small, and it is
+// the integer/logic pipe (half rate) that saturates first:
+//   * nibbles become exact fp16 integers in registers with one logic op per PAIR of weights:
+//     (w & 0x000F000F) | 0x64006400 is the fp16x2 {1024+q0, 1024+q4}, (w & 0x00F000F0) | 0x64006400
+//     is {1024+16*q1, 1024+16*q5}; the same two masks on w >> 8 give q2,q6 and q3,q7.  One fp16x2
+//     subtract (or multiply-add with 1/16, -64) per register removes offset and factor exactly;
+//     that runs on the FMA pipe, which has room.  (An fp8 e4m3 operand path was measured first:
+//     on this part mma.sync with e4m3 operands is executed by converting every operand register
+//     to fp16, 12 conversions per instruction on the logic pipe, so it is slower, not faster.)
+//   * mma.sync m16n8k16 f16 x f16 -> f32: 16 weight rows x 16 inputs per instruction, the eight
+//     columns are eight activation rows, so one pass serves up to 8 rows.  Products are exact
+//     (4-bit integer x fp16), accumulation is f32;
+//   * the pairing (q_i, q_{i+4}) is matched by storing each 8 activations in shared memory in the
+//     order 0,4,1,5,2,6,3,7, so one 128-bit shared load is the B operand of two instructions;
 //   * per group of 64 inputs: acc += scale * C + bias * sum(x): two FMAs per group and output
 //     instead of per element (the algebra the reference uses, SeedlessMetalForward.swift:249-258);
 //   * a warp owns 16 weight rows x 256 inputs (one "slice" = 4 groups); weights are read in the
-//     fragment-major layout below with 128-bit coalesced loads;
+//     fragment-major layout below, which arrives in shared memory by bulk asynchronous copies;
 //   * each row's result is independent of how many rows share the call (columns of an MMA do not
 //     interact) and slices are summed in ascending order whatever the CTA organisation.
 #pragma once
-#include <cuda_fp8.h>
 #include "common.cuh"
 
 namespace sl {
@@ -29,13 +32,13 @@ namespace sl {
 enum { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_NORMGATE = 2 };
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_ARGMAX = 3 };
 
-constexpr int ROWS_PER_PASS = 2;     // activation rows per MMA pass (3 term columns each)
+constexpr int ROWS_PER_PASS = 8;     // activation rows per MMA pass (the 8 columns of m16n8k16)
 
 struct XStage {
-    unsigned char* xs;   // [rows][3 terms][K + 64] e4m3 bytes in fragment order
-    float* sxs;          // [K/64][2] per-group sums of x (bias term)
-    float* part;         // [2][16] scratch for the rmsnorm prologue
-    int stride;          // K + 64 (bytes) between terms
+    __half* xs;          // [rows][stride] fp16, every 8 consecutive inputs stored as 0,4,1,5,2,6,3,7
+    float* sxs;          // [K/64][8] per-group sums of x (bias term)
+    float* part;         // [8][16] scratch for the rmsnorm prologue
+    int stride;          // K + 8 (halves) between rows: 16 bytes of skew keeps the B loads conflict-free
 };
 
 // Sum of 8 consecutive activations the way the reference's GEMV forms its bias term: groups of
@@ -48,78 +51,68 @@ __device__ __forceinline__ float sum8_f32(uint4 v) {
     __half b = hadd_rn(hadd_rn(hadd_rn(h[4], h[5]), h[6]), h[7]);
     return h2f(a) + h2f(b);
 }
-// fp16 pair -> e4m3 pair (round to nearest, saturating) and back
-__device__ __forceinline__ uint32_t to_e4m3x2(__half2 v) {
-    return (uint32_t)__nv_cvt_halfraw2_to_fp8x2(static_cast<__half2_raw>(v), __NV_SATFINITE, __NV_E4M3);
-}
-__device__ __forceinline__ __half2 from_e4m3x2(uint32_t e) {
-    return __half2(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)e, __NV_E4M3));
-}
-// 8 consecutive fp16 values -> three 8-byte e4m3 terms in fragment order (x0,x2,x4,x6, x1,x3,x5,x7);
-// x = t1 + t2/16 + t3/256 exactly (every residual is exactly representable in fp16)
-__device__ __forceinline__ void split_terms8(uint4 v, uint2 out[3]) {
-    const __half2 k16 = __floats2half2_rn(16.f, 16.f);
-    __half2 r[4];
-    const __half2* hv = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) r[i] = hv[i];
-#pragma unroll
-    for (int term = 0; term < 3; ++term) {
-        uint32_t e[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            e[i] = to_e4m3x2(r[i]);
-            if (term < 2) r[i] = __hmul2(__hsub2(r[i], from_e4m3x2(e[i])), k16);
-        }
-        uint32_t A = e[0] | (e[1] << 16), B = e[2] | (e[3] << 16);      // bytes x0,x1,x2,x3 / x4,x5,x6,x7
-        out[term].x = __byte_perm(A, B, 0x6420);
-        out[term].y = __byte_perm(A, B, 0x7531);
-    }
-}
 // lane holds 8 consecutive activations of pass-row `col` starting at k0 (multiple of 8): write
-// the staged terms and accumulate the group sum (8 consecutive lanes cover one group of 64)
+// them in the paired order and accumulate the group sum (8 consecutive lanes cover one group of 64)
 __device__ __forceinline__ void store_staged(const XStage& st, int col, int k0, uint4 v, int lane) {
     float s = sum8_f32(v);
     s += __shfl_xor_sync(0xffffffffu, s, 4);
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     s += __shfl_xor_sync(0xffffffffu, s, 1);
-    if ((lane & 7) == 0) st.sxs[(k0 >> 6) * 2 + col] = s;
-    uint2 tm[3];
-    split_terms8(v, tm);
-#pragma unroll
-    for (int term = 0; term < 3; ++term)
-        *reinterpret_cast<uint2*>(st.xs + (size_t)(col * 3 + term) * st.stride + k0) = tm[term];
+    if ((lane & 7) == 0) st.sxs[(k0 >> 6) * 8 + col] = s;
+    uint4 o;
+    o.x = __byte_perm(v.x, v.z, 0x5410);       // (x0, x4)
+    o.y = __byte_perm(v.x, v.z, 0x7632);       // (x1, x5)
+    o.z = __byte_perm(v.y, v.w, 0x5410);       // (x2, x6)
+    o.w = __byte_perm(v.y, v.w, 0x7632);       // (x3, x7)
+    *reinterpret_cast<uint4*>(st.xs + (size_t)col * st.stride + k0) = o;
 }
 
 // ---- prologues: stage `mr` (<= ROWS_PER_PASS) activation rows of width K ----
-// Split in two so that a kernel can put its few activation loads in flight BEFORE its many weight
-// loads (an SM serves its memory requests in order: activations queued behind 100+ KB of weights
-// would arrive last and nothing could be computed while the weights stream in), and only then
-// wait for them.  A warp owns 256-wide chunks; with two rows of K <= 4096 there are at most two per
-// warp of a 16-warp CTA (four per warp of an 8-warp CTA are not supported: K <= 2048 there).
+// A warp owns 256-wide chunks (unit u = row * chunks + chunk, units u = warp, warp + nw, ...).
+// The first two units of a warp are requested by stage_issue and held in registers, so a kernel
+// can put those loads in flight early and do other set-up before it needs them; further units
+// (more than two rows, or K = 4096 with two) are loaded where they are used.
 struct StageSrc {
     const __half* x; int ldx;        // rows (plain) / residual stream (rmsnorm) / y (normgate)
-    const int* rows;                 // optional row list (shared memory), else rows row0, row0+1
+    const int* rows;                 // optional row list (shared memory), else rows row0, row0+1, ...
     const __half* nw;                // norm weight
     const __half* z; int ldz;        // gate input of the gated norm
     float eps;
 };
-struct StageRegs { uint4 a[2], b[2], c[2]; };
+struct StageRegs { uint4 a[2], b[2], c[2]; };   // activations, norm weights, gate inputs of the first two units
 
+__device__ __forceinline__ uint4 stage_load(const StageSrc& s, int row0, int col, int k0) {
+    int row = s.rows ? s.rows[col] : row0 + col;
+    return __ldcg(reinterpret_cast<const uint4*>(s.x + (size_t)row * s.ldx + k0));
+}
+// norm weights of the warp's first two units: constants, so they may be requested before the
+// programmatic-launch wait (they are cold in L2 once per token, a full DRAM round trip)
 template <int PRO>
-__device__ __forceinline__ void stage_issue(StageRegs& sr, const StageSrc& s, int row0, int mr, int K) {
+__device__ __forceinline__ void stage_issue_const(StageRegs& sr, const StageSrc& s, int mr, int K) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int chunks = K >> 8, units = mr * chunks;
+    const int lgc = 31 - __clz(K >> 8), units = mr << lgc;
+    if (PRO == PRO_PLAIN) return;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
         int u = warp + j * nw;
         if (u < units) {
-            int col = (u >= chunks) ? 1 : 0, ch = u - col * chunks, k0 = ch * 256 + lane * 8;
-            int row = s.rows ? s.rows[col] : row0 + col;
-            sr.a[j] = __ldcg(reinterpret_cast<const uint4*>(s.x + (size_t)row * s.ldx + k0));
-            if (PRO == PRO_RMSNORM) sr.b[j] = *reinterpret_cast<const uint4*>(s.nw + k0);
+            const int k0 = ((u & ((1 << lgc) - 1)) << 8) + lane * 8;
+            sr.b[j] = *reinterpret_cast<const uint4*>(s.nw + (PRO == PRO_NORMGATE ? (k0 & 127) : k0));
+        }
+    }
+}
+template <int PRO>
+__device__ __forceinline__ void stage_issue(StageRegs& sr, const StageSrc& s, int row0, int mr, int K) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int lgc = 31 - __clz(K >> 8), units = mr << lgc;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        int u = warp + j * nw;
+        if (u < units) {
+            const int col = u >> lgc, k0 = ((u & ((1 << lgc) - 1)) << 8) + lane * 8;
+            sr.a[j] = stage_load(s, row0, col, k0);
             if (PRO == PRO_NORMGATE) {
-                sr.b[j] = *reinterpret_cast<const uint4*>(s.nw + (k0 & 127));
+                const int row = s.rows ? s.rows[col] : row0 + col;
                 sr.c[j] = __ldcg(reinterpret_cast<const uint4*>(s.z + (size_t)row * s.ldz + k0));
             }
         }
@@ -145,88 +138,67 @@ __device__ __forceinline__ float sumsq8(uint4 v) {
 // x = fp16(silu_f32(z) * float(w * fp16(y * inv))) (SeedlessFusedVerify.swift:803-813).
 // Contains one __syncthreads() for PRO_RMSNORM; the caller synchronises before reading xs.
 template <int PRO>
-__device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& st, const StageSrc& s, int mr, int K) {
+__device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& st, const StageSrc& s, int row0, int mr, int K, long long* dbgp = nullptr, long long t0 = 0) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int chunks = K >> 8, units = mr * chunks;
+    const int lgc = 31 - __clz(K >> 8), chunks = 1 << lgc, units = mr << lgc;
     if (PRO == PRO_RMSNORM) {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            int u = warp + j * nw;
-            if (u < units) {
-                int col = (u >= chunks) ? 1 : 0, ch = u - col * chunks;
-                float ss = warp_sum(sumsq8(sr.a[j]));
-                if (lane == 0) st.part[col * 16 + ch] = ss;
-            }
+        for (int j = 0, u = warp; u < units; ++j, u += nw) {
+            const int col = u >> lgc, ch = u & (chunks - 1);
+            const uint4 v = (j == 0) ? sr.a[0] : ((j == 1) ? sr.a[1] : stage_load(s, row0, col, (ch << 8) + lane * 8));
+            float ss = warp_sum(sumsq8(v));
+            if (dbgp && threadIdx.x == 0) dbgp[8] = clock64() - t0;
+            if (lane == 0) st.part[col * 16 + ch] = ss;
         }
         __syncthreads();
+        if (dbgp && threadIdx.x == 0) dbgp[9] = clock64() - t0;
     }
+    for (int j = 0, u = warp; u < units; ++j, u += nw) {
+        const int col = u >> lgc, ch = u & (chunks - 1), k0 = (ch << 8) + lane * 8;
+        const uint4 v = (j == 0) ? sr.a[0] : ((j == 1) ? sr.a[1] : stage_load(s, row0, col, k0));
+        uint4 o;
+        if (PRO == PRO_PLAIN) {
+            o = v;
+        } else if (PRO == PRO_RMSNORM) {
+            float tot = 0.f;
+            for (int c = 0; c < chunks; ++c) tot += st.part[col * 16 + c];
+            float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), s.eps));
+            if (dbgp && threadIdx.x == 0) dbgp[10] = clock64() - t0;
+            const uint4 wv = (j == 0) ? sr.b[0] : ((j == 1) ? sr.b[1] : *reinterpret_cast<const uint4*>(s.nw + k0));
+            o = rms_apply8(v, wv, inv);
+            if (dbgp && threadIdx.x == 0) { dbgp[11] = clock64() - t0 + (o.x & 1); }
+        } else {
+            const int row = s.rows ? s.rows[col] : row0 + col;
+            const uint4 zv = (j == 0) ? sr.c[0] : ((j == 1) ? sr.c[1] : __ldcg(reinterpret_cast<const uint4*>(s.z + (size_t)row * s.ldz + k0)));
+            const uint4 wv = (j == 0) ? sr.b[0] : ((j == 1) ? sr.b[1] : *reinterpret_cast<const uint4*>(s.nw + (k0 & 127)));
+            const __half* yh = reinterpret_cast<const __half*>(&v);
+            const __half* zh = reinterpret_cast<const __half*>(&zv);
+            const __half* wh = reinterpret_cast<const __half*>(&wv);
+            float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        int u = warp + j * nw;
-        if (u < units) {
-            int col = (u >= chunks) ? 1 : 0, ch = u - col * chunks, k0 = ch * 256 + lane * 8;
-            uint4 o;
-            if (PRO == PRO_PLAIN) {
-                o = sr.a[j];
-            } else if (PRO == PRO_RMSNORM) {
-                float tot = 0.f;
-                for (int c = 0; c < chunks; ++c) tot += st.part[col * 16 + c];
-                float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), s.eps));
-                o = rms_apply8(sr.a[j], sr.b[j], inv);
-            } else {
-                const __half* yh = reinterpret_cast<const __half*>(&sr.a[j]);
-                const __half* zh = reinterpret_cast<const __half*>(&sr.c[j]);
-                const __half* wh = reinterpret_cast<const __half*>(&sr.b[j]);
-                float ss = 0.f;
+            for (int i = 0; i < 8; ++i) { float f = h2f(yh[i]); ss = fmaf(f, f, ss); }
+            ss = half_warp_sum(ss);                       // 16 lanes per head of 128
+            float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), s.eps));
+            __half* oh = reinterpret_cast<__half*>(&o);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { float f = h2f(yh[i]); ss = fmaf(f, f, ss); }
-                ss = half_warp_sum(ss);                       // 16 lanes per head of 128
-                float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), s.eps));
-                __half* oh = reinterpret_cast<__half*>(&o);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float nrm = h2f(hmul_rn(wh[i], f2h(__fmul_rn(h2f(yh[i]), inv))));
-                    float zf = h2f(zh[i]);
-                    oh[i] = f2h(__fmul_rn(__fmul_rn(zf, sigmoid_f(zf)), nrm));
-                }
+            for (int i = 0; i < 8; ++i) {
+                float nrm = h2f(hmul_rn(wh[i], f2h(__fmul_rn(h2f(yh[i]), inv))));
+                float zf = h2f(zh[i]);
+                oh[i] = f2h(__fmul_rn(__fmul_rn(zf, sigmoid_f(zf)), nrm));
             }
-            store_staged(st, col, k0, o, lane);
         }
+        store_staged(st, col, k0, o, lane);
+        if (dbgp && threadIdx.x == 0) dbgp[12] = clock64() - t0;
     }
 }
-// generic (any number of chunks per warp) versions used by the persistent head kernel
+// whole-prologue forms for kernels that have nothing to overlap with the loads
 __device__ __forceinline__ void stage_plain(const XStage& st, const __half* x, int ldx, int row0, int mr, int K) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int chunks = K >> 8;
-    for (int u = warp; u < mr * chunks; u += nw) {
-        int col = u / chunks, ch = u - col * chunks;
-        int k0 = ch * 256 + lane * 8;
-        uint4 v = __ldcg(reinterpret_cast<const uint4*>(x + (size_t)(row0 + col) * ldx + k0));
-        store_staged(st, col, k0, v, lane);
-    }
+    StageSrc s{x, ldx, nullptr, nullptr, nullptr, 0, 0.f};
+    StageRegs sr; stage_issue<PRO_PLAIN>(sr, s, row0, mr, K); stage_finish<PRO_PLAIN>(sr, st, s, row0, mr, K);
 }
 __device__ __forceinline__ void stage_rmsnorm(const XStage& st, const __half* h, int ldh, const __half* w, float eps,
                                               int row0, int mr, int K) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int chunks = K >> 8, units = mr * chunks;
-    for (int u = warp; u < units; u += nw) {
-        int col = u / chunks, ch = u - col * chunks;
-        int k0 = ch * 256 + lane * 8;
-        uint4 v = __ldcg(reinterpret_cast<const uint4*>(h + (size_t)(row0 + col) * ldh + k0));
-        float ss = warp_sum(sumsq8(v));
-        if (lane == 0) st.part[col * 16 + ch] = ss;
-    }
-    __syncthreads();
-    for (int u = warp; u < units; u += nw) {
-        int col = u / chunks, ch = u - col * chunks;
-        int k0 = ch * 256 + lane * 8;
-        float tot = 0.f;
-        for (int c = 0; c < chunks; ++c) tot += st.part[col * 16 + c];
-        float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), eps));
-        uint4 v = __ldcg(reinterpret_cast<const uint4*>(h + (size_t)(row0 + col) * ldh + k0));
-        uint4 wv = *reinterpret_cast<const uint4*>(w + k0);
-        store_staged(st, col, k0, rms_apply8(v, wv, inv), lane);
-    }
+    StageSrc s{h, ldh, nullptr, w, nullptr, 0, eps};
+    StageRegs sr; stage_issue_const<PRO_RMSNORM>(sr, s, mr, K); stage_issue<PRO_RMSNORM>(sr, s, row0, mr, K); stage_finish<PRO_RMSNORM>(sr, st, s, row0, mr, K);
 }
 
 // ---- L2 prefetch of weights a LATER kernel will read: keeps HBM streaming while this kernel and
@@ -276,64 +248,96 @@ __device__ __forceinline__ void load_slice(SliceRegs& rg, const uint4* wr_tile, 
     rg.sc[0] = ldg_nc_u4(sp); rg.sc[1] = ldg_nc_u4(sp + 8);
 }
 
+// the same fragments from a copy of the unit in shared memory (w: 128 uint4, s: 16 uint4 of the unit)
+__device__ __forceinline__ void load_slice_smem(SliceRegs& rg, const uint4* w_unit, const uint4* s_unit, int lane) {
+    rg.w[0] = w_unit[lane]; rg.w[1] = w_unit[lane + 32]; rg.w[2] = w_unit[lane + 64]; rg.w[3] = w_unit[lane + 96];
+    rg.sc[0] = s_unit[lane >> 2]; rg.sc[1] = s_unit[8 + (lane >> 2)];
+}
+
 // (not volatile: pure functions of their operands, so the compiler may interleave independent groups)
-__device__ __forceinline__ void mma_e4m3(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+__device__ __forceinline__ void mma_f16(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 // first MMA of a group: the accumulator starts from zero without spending registers on it
-__device__ __forceinline__ void mma_e4m3_z(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+__device__ __forceinline__ void mma_f16_z(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
         : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
+// (a & b) | c in one logic instruction (the compiler otherwise spends two when b and c are both constants)
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// one word (8 nibbles q0..q7) -> fp16x2 registers {q0,q4}, {q1,q5}, {q2,q6}, {q3,q7}, exact
+__device__ __forceinline__ void dequant8(uint32_t w, uint32_t d[4]) {
+    const uint32_t w8 = w >> 8;
+    const uint32_t mlo = 0x000F000Fu, mhi = 0x00F000F0u, magic = 0x64006400u;
+    uint32_t l0 = and_or(w, mlo, magic), h0 = and_or(w, mhi, magic);
+    uint32_t l1 = and_or(w8, mlo, magic), h1 = and_or(w8, mhi, magic);
+    const __half2 k1024 = __floats2half2_rn(1024.f, 1024.f), k16th = __floats2half2_rn(0.0625f, 0.0625f), k64 = __floats2half2_rn(-64.f, -64.f);
+    __half2 r0 = __hsub2(*reinterpret_cast<__half2*>(&l0), k1024);
+    __half2 r1 = __hfma2(*reinterpret_cast<__half2*>(&h0), k16th, k64);
+    __half2 r2 = __hsub2(*reinterpret_cast<__half2*>(&l1), k1024);
+    __half2 r3 = __hfma2(*reinterpret_cast<__half2*>(&h1), k16th, k64);
+    d[0] = *reinterpret_cast<uint32_t*>(&r0); d[1] = *reinterpret_cast<uint32_t*>(&r1);
+    d[2] = *reinterpret_cast<uint32_t*>(&r2); d[3] = *reinterpret_cast<uint32_t*>(&r3);
+}
 
-// One slice (4 groups) of a 16-row tile against the staged rows.  MMA column n = lane/4 carries
-// pass-row n/3, term n%3 (columns 6,7 unused).  accS/accB [4]: (row A, col 2t), (row A, col 2t+1),
-// (row B, col 2t), (row B, col 2t+1); the bias term is added once per pass-row, in its term-0 column.
-__device__ __forceinline__ void compute_slice(const SliceRegs& r, const XStage& st, int slice, int n, int t, int mr,
-                                              float accS[4], float accB[4]) {
-    const bool col_active = (n < 3 * mr);
-    const unsigned char* xp = st.xs + (size_t)n * st.stride + slice * 256 + 16 * t;     // n = row*3 + term
+// B operands of one slice for this lane (MMA column n = lane/4 is pass-row n) and the group sums of
+// its two columns: loaded from the activation stage once, reusable for every tile of the same slice
+struct XRegs { uint4 x[8]; float2 sx[4]; };
+__device__ __forceinline__ void load_xregs(XRegs& xr, const XStage& st, int slice, int n, int t, int mr) {
+    const __half* xp = st.xs + (size_t)n * st.stride + slice * 256 + 16 * t;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-        uint4 X = make_uint4(0, 0, 0, 0);
-        if (col_active) X = *reinterpret_cast<const uint4*>(xp + 64 * g);
-        const uint4 wv = r.w[g];
+        xr.x[2 * g] = make_uint4(0, 0, 0, 0); xr.x[2 * g + 1] = make_uint4(0, 0, 0, 0);
+        if (n < mr) { xr.x[2 * g] = *reinterpret_cast<const uint4*>(xp + 64 * g); xr.x[2 * g + 1] = *reinterpret_cast<const uint4*>(xp + 64 * g + 8); }
+        xr.sx[g] = *reinterpret_cast<const float2*>(st.sxs + (slice * 4 + g) * 8 + 2 * t);
+    }
+}
+// One slice (4 groups) of a 16-row tile.
+// accS/accB [4]: (row A, col 2t), (row A, col 2t+1), (row B, col 2t), (row B, col 2t+1).
+__device__ __forceinline__ void compute_slice_x(const SliceRegs& r, const XRegs& xr, float accS[4], float accB[4]) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const uint4 X0 = xr.x[2 * g], X1 = xr.x[2 * g + 1];
+        const uint4 wv = r.w[g];                      // row A words (x, y), row B words (z, w)
+        uint32_t a[4], b[4];
         float c[4];
-        mma_e4m3_z(c, wv.x & 0x0f0f0f0fu, wv.z & 0x0f0f0f0fu, (wv.x >> 4) & 0x0f0f0f0fu, (wv.z >> 4) & 0x0f0f0f0fu, X.x, X.y);
-        mma_e4m3(c, wv.y & 0x0f0f0f0fu, wv.w & 0x0f0f0f0fu, (wv.y >> 4) & 0x0f0f0f0fu, (wv.w >> 4) & 0x0f0f0f0fu, X.z, X.w);
-        const float2 sx2 = *reinterpret_cast<const float2*>(st.sxs + (slice * 4 + g) * 2);
-        const float sx0 = (t == 0) ? sx2.x : 0.f;       // column 0 = row 0 term 0
-        const float sx1 = (t == 1) ? sx2.y : 0.f;       // column 3 = row 1 term 0
+        dequant8(wv.x, a); dequant8(wv.z, b);
+        mma_f16_z(c, a[0], b[0], a[1], b[1], X0.x, X0.y);
+        mma_f16(c, a[2], b[2], a[3], b[3], X0.z, X0.w);
+        dequant8(wv.y, a); dequant8(wv.w, b);
+        mma_f16(c, a[0], b[0], a[1], b[1], X1.x, X1.y);
+        mma_f16(c, a[2], b[2], a[3], b[3], X1.z, X1.w);
+        const float2 sx2 = xr.sx[g];
         const uint4 sv = r.sc[g >> 1];
         const uint32_t sa_ba = (g & 1) ? sv.z : sv.x, sb_bb = (g & 1) ? sv.w : sv.y;
         float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&sa_ba));    // (scale A, bias A)
         float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&sb_bb));    // (scale B, bias B)
         accS[0] = fmaf(fa.x, c[0], accS[0]); accS[1] = fmaf(fa.x, c[1], accS[1]);
         accS[2] = fmaf(fb.x, c[2], accS[2]); accS[3] = fmaf(fb.x, c[3], accS[3]);
-        accB[0] = fmaf(fa.y, sx0, accB[0]); accB[1] = fmaf(fa.y, sx1, accB[1]);
-        accB[2] = fmaf(fb.y, sx0, accB[2]); accB[3] = fmaf(fb.y, sx1, accB[3]);
+        accB[0] = fmaf(fa.y, sx2.x, accB[0]); accB[1] = fmaf(fa.y, sx2.y, accB[1]);
+        accB[2] = fmaf(fb.y, sx2.x, accB[2]); accB[3] = fmaf(fb.y, sx2.y, accB[3]);
     }
 }
-// undo the operand scales: nibbles carry 2^-9, term k of the activation carries 16^k
+__device__ __forceinline__ void compute_slice(const SliceRegs& r, const XStage& st, int slice, int n, int t, int mr,
+                                              float accS[4], float accB[4]) {
+    XRegs xr;
+    load_xregs(xr, st, slice, n, t, mr);
+    compute_slice_x(r, xr, accS, accB);
+}
+// scale part + bias part of the slice
 __device__ __forceinline__ void finish_acc4(const float accS[4], const float accB[4], int t, float v[4]) {
-    const int m0 = (2 * t) % 3, m1 = (2 * t + 1) % 3;
-    const float k0 = (m0 == 0) ? 512.f : ((m0 == 1) ? 32.f : 2.f);
-    const float k1 = (m1 == 0) ? 512.f : ((m1 == 1) ? 32.f : 2.f);
-    v[0] = fmaf(accS[0], k0, accB[0]);
-    v[1] = fmaf(accS[1], k1, accB[1]);
-    v[2] = fmaf(accS[2], k0, accB[2]);
-    v[3] = fmaf(accS[3], k1, accB[3]);
+    (void)t;
+    v[0] = accS[0] + accB[0]; v[1] = accS[1] + accB[1]; v[2] = accS[2] + accB[2]; v[3] = accS[3] + accB[3];
 }
-// value of pass-row j (0/1) of weight row `row` from the reduced 16x8 tile: the three term columns in order
-__device__ __forceinline__ float tile_value(const float* fin_tile, int row, int j) {
-    const float* p = fin_tile + row * 8 + 3 * j;
-    return (p[0] + p[1]) + p[2];
-}
+// value of pass-row j of weight row `row` from the reduced 16x8 tile
+__device__ __forceinline__ float tile_value(const float* fin_tile, int row, int j) { return fin_tile[row * 8 + j]; }
 
 // ---- CTA organisation of the split GEMV ----
 // A tile is 16 weight rows; its K/256 slices are shared by WPT warps of SPW slices each, and a CTA
@@ -376,21 +380,46 @@ __device__ __forceinline__ void reduce_tiles(const float* red, float* fin, int t
 }
 
 // dynamic shared memory carve-up shared by host (size) and device (pointers)
+// Weight stage: the CTA's units (one slice of one tile each: 2048 B of nibbles + 256 B of scales)
+// are contiguous in the fragment-major layout, so each round of 16 units arrives by two bulk copies.
+struct WStage { uint4* w; uint4* s; uint64_t* bar; };
 struct GemvSmem {
+    __host__ __device__ static size_t wstage_bytes(int nunits) { return (size_t)nunits * (2048 + 256) + 64; }
     __host__ __device__ static size_t bytes(int rows, int K, int nred, int tpc) {
-        size_t xs = (size_t)rows * 3 * (K + 64);
-        return xs + (size_t)(K / 64) * 2 * 4 + 2 * 16 * 4 + (size_t)nred * 128 * 4 + (size_t)tpc * 128 * 4 + 128;
+        size_t xs = (size_t)rows * (K + 8) * 2;
+        return xs + (size_t)(K / 64) * 8 * 4 + 8 * 16 * 4 + (size_t)nred * 128 * 4 + (size_t)tpc * 128 * 4 + 128;
+    }
+    // [weight stage (nunits > 0)] [activation stage] ...; every part stays 16-byte aligned
+    __device__ static unsigned char* carve_w(unsigned char* base, int nunits, WStage& ws) {
+        ws.w = reinterpret_cast<uint4*>(base);
+        ws.s = reinterpret_cast<uint4*>(base + (size_t)nunits * 2048);
+        ws.bar = reinterpret_cast<uint64_t*>(base + (size_t)nunits * (2048 + 256));
+        return base + wstage_bytes(nunits);
     }
     __device__ static void carve(unsigned char* base, int rows, int K, int nred, int tpc, XStage& st, float*& red, float*& fin, int*& misc) {
-        size_t xs = (size_t)rows * 3 * (K + 64);
-        st.xs = base;
+        size_t xs = (size_t)rows * (K + 8) * 2;
+        st.xs = reinterpret_cast<__half*>(base);
         st.sxs = reinterpret_cast<float*>(base + xs);
-        st.part = st.sxs + (K / 64) * 2;
-        red = st.part + 2 * 16;
+        st.part = st.sxs + (K / 64) * 8;
+        red = st.part + 8 * 16;
         fin = red + nred * 128;
         misc = reinterpret_cast<int*>(fin + tpc * 128);      // 32 ints
-        st.stride = K + 64;
+        st.stride = K + 8;
     }
 };
+
+// One thread: start the bulk copies of the CTA's `nvu` valid units (global unit index u0), one
+// mbarrier per round of 16 units.  w_all / s_all are the matrix's (or the expert's) arrays.
+__device__ __forceinline__ void wstage_issue(const WStage& ws, const uint4* w_all, const uint4* s_all, size_t u0, int nvu, int rounds) {
+    for (int i = 0; i < rounds; ++i) mbar_init(ws.bar + i, 1);
+    mbar_fence_init();
+    for (int i = 0; i < rounds; ++i) {
+        const int n = min(16, nvu - 16 * i);
+        if (n <= 0) break;
+        mbar_expect_tx(ws.bar + i, (uint32_t)n * (2048 + 256));
+        bulk_g2s(ws.w + (size_t)16 * i * 128, w_all + (u0 + 16 * i) * 128, (uint32_t)n * 2048, ws.bar + i);
+        bulk_g2s(ws.s + (size_t)16 * i * 16, s_all + (u0 + 16 * i) * 16, (uint32_t)n * 256, ws.bar + i);
+    }
+}
 
 }  // namespace sl

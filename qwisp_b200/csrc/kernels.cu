@@ -64,7 +64,7 @@ static void set_pdl(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, bool pdl
     cfg.attrs = attr; cfg.numAttrs = 1;
 }
 __device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define DBG_STAMP(i) do { if (a.dbg && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 60) a.dbg[blockIdx.x * 8 + (i)] = ((i) == 0 || (i) == 7) ? gtimer() : (clock64() - dbg_t0); } while (0)
+#define DBG_STAMP(i) do { if (a.dbg && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 30) a.dbg[blockIdx.x * 16 + (i)] = ((i) == 0 || (i) == 7) ? gtimer() : (clock64() - dbg_t0); } while (0)
 template <int PRO, int EPI, int UPW>
 __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
     long long dbg_t0 = clock64();
@@ -76,37 +76,43 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
     const int TPC = (16 * UPW) >> lg;
     const int row0 = blockIdx.y * ROWS_PER_PASS;
     const int mr = min(ROWS_PER_PASS, a.M - row0);
-    XStage st; float* red; float* fin; int* misc;
-    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), a.K, 16 * UPW, TPC, st, red, fin, misc);
+    WStage ws; XStage st; float* red; float* fin; int* misc;
+    GemvSmem::carve(GemvSmem::carve_w(smem, 16 * UPW, ws), min(a.M, ROWS_PER_PASS), a.K, 16 * UPW, TPC, st, red, fin, misc);
     const int ntiles = (EPI == EPI_SWIGLU) ? a.N / 8 : a.N / 16;
-    // The weights do not depend on the kernel before this one: their loads go out before the
-    // programmatic-launch wait, so they are in flight while that kernel finishes.  Dependents are
-    // released only after the wait, so whatever a dependent reads ahead of its own wait was written
-    // by a kernel that is complete.
-    SliceRegs regs[UPW];
-    const size_t wstep = q4r_w_uint4(a.K), sstep = q4r_s_uint4(a.K);
-#pragma unroll
-    for (int i = 0; i < UPW; ++i) {
-        const int u = warp + 16 * i, tile = blockIdx.x * TPC + (u >> lg);
-        if (tile < ntiles) load_slice(regs[i], a.q.wr + (size_t)tile * wstep, a.q.sr + (size_t)tile * sstep, u & (slices - 1), lane);
+    const int nvu = min(TPC, ntiles - (int)blockIdx.x * TPC) << lg;      // valid units of this CTA
+    // The weights do not depend on the kernel before this one: one thread starts their bulk copies
+    // into shared memory before the programmatic-launch wait, so they stream in while that kernel
+    // finishes and while this CTA stages its activations; they occupy neither registers nor the
+    // load/store queue.  Dependents are released only after the wait, so whatever a dependent
+    // reads ahead of its own wait was written by a kernel that is complete.
+    if (threadIdx.x == 480) {                              // last warp: it stages no activations at batch 1
+        if (a.dbg && blockIdx.x < 30) a.dbg[blockIdx.x * 16 + 14] = clock64() - dbg_t0;
+        wstage_issue(ws, a.q.wr, a.q.sr, (size_t)blockIdx.x * TPC << lg, nvu, UPW);
+        if (a.dbg && blockIdx.x < 30) a.dbg[blockIdx.x * 16 + 15] = clock64() - dbg_t0;
     }
+    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
+    StageRegs sregs;
+    stage_issue_const<PRO>(sregs, src, mr, a.K);
     pdl_wait();
     pdl_launch_dependents();
     DBG_STAMP(1);
-    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
-    StageRegs sregs;
     stage_issue<PRO>(sregs, src, row0, mr, a.K);
     if (blockIdx.y == 0) prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
     DBG_STAMP(2);
-    stage_finish<PRO>(sregs, st, src, mr, a.K);
+    stage_finish<PRO>(sregs, st, src, row0, mr, a.K, (a.dbg && blockIdx.x < 30 && blockIdx.y == 0) ? a.dbg + blockIdx.x * 16 : nullptr, dbg_t0);
     __syncthreads();
     DBG_STAMP(3);
-#pragma unroll
+    XRegs xr;                                     // the warp's slice is the same for all its units (16 % slices == 0)
+    load_xregs(xr, st, warp & (slices - 1), r, t, mr);
+#pragma unroll 1
     for (int i = 0; i < UPW; ++i) {
-        const int u = warp + 16 * i, tile = blockIdx.x * TPC + (u >> lg);
-        if (tile < ntiles) {
+        const int u = warp + 16 * i;
+        if (u < nvu) {
+            if (!mbar_wait_bounded(ws.bar + i, 0) && a.err && lane == 0) atomicOr(a.err, 1u);
+            SliceRegs rg;
+            load_slice_smem(rg, ws.w + (size_t)u * 128, ws.s + (size_t)u * 16, lane);
             float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
-            compute_slice(regs[i], st, u & (slices - 1), r, t, mr, accS, accB);
+            compute_slice_x(rg, xr, accS, accB);
             finish_acc4(accS, accB, t, v);
             store_partial(red, u, lane, v);
         }
@@ -114,12 +120,12 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
     DBG_STAMP(4);
     __syncthreads();
     DBG_STAMP(5);
-    reduce_tiles(red, fin, min(TPC, ntiles - (int)blockIdx.x * TPC), slices);
+    reduce_tiles(red, fin, nvu >> lg, slices);
     __syncthreads();
     DBG_STAMP(6);
     if (EPI == EPI_STORE || EPI == EPI_RESID) {
-        for (int i = threadIdx.x; i < TPC * 32; i += blockDim.x) {
-            int tl2 = i >> 5, col = (i >> 4) & 1, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
+        for (int i = threadIdx.x; i < TPC * 128; i += blockDim.x) {
+            int tl2 = i >> 7, col = (i >> 4) & 7, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
             if (tile2 < ntiles && col < mr) {
                 size_t idx = (size_t)(row0 + col) * a.ldy + tile2 * 16 + row;
                 __half val = f2h(tile_value(fin + tl2 * 128, row, col));
@@ -128,8 +134,8 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
             }
         }
     } else {   // EPI_SWIGLU
-        for (int j = threadIdx.x; j < TPC * 16; j += blockDim.x) {
-            int tl2 = j >> 4, col = (j >> 3) & 1, i = j & 7, tile2 = blockIdx.x * TPC + tl2;
+        for (int j = threadIdx.x; j < TPC * 64; j += blockDim.x) {
+            int tl2 = j >> 6, col = (j >> 3) & 7, i = j & 7, tile2 = blockIdx.x * TPC + tl2;
             if (tile2 < ntiles && col < mr) {
                 __half g = f2h(tile_value(fin + tl2 * 128, i, col)), u = f2h(tile_value(fin + tl2 * 128, i + 8, col));
                 a.y[(size_t)(row0 + col) * a.ldy + tile2 * 8 + i] = swiglu_h(g, u);
@@ -140,9 +146,9 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
 }
 template <int PRO, int EPI, int UPW>
 static void launch_gemv_t(const DenseArgs& a, const GemvPlan& pl, cudaStream_t st, bool pdl) {
-    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 16 * UPW, pl.tpc);
+    size_t smem = GemvSmem::wstage_bytes(16 * UPW) + GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 16 * UPW, pl.tpc);
     static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_gemv<PRO, EPI, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
+    if (!configured) { cudaFuncSetAttribute(k_gemv<PRO, EPI, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
     int ntiles = EPI == EPI_SWIGLU ? a.N / 8 : a.N / 16;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS));
@@ -178,6 +184,7 @@ __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
     if (PRO == PRO_PLAIN) stage_plain(st, a.x, a.ldx, row0, mr, a.K);
     else stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K);
     __syncthreads();
+    // lane (r, t) sees weight rows r and r+8 of each tile for pass-rows (MMA columns) 2t and 2t+1
     float best[2] = {-INFINITY, -INFINITY}; int besti[2] = {0x7fffffff, 0x7fffffff};
     while (have) {
         float tot[4] = {0.f, 0.f, 0.f, 0.f};
@@ -193,33 +200,23 @@ __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
             for (int j = 0; j < 4; ++j) tot[j] += v[j];
             cur = nxt;
         }
-        // gather the six term columns of rows A and B from lanes t = 0,1,2 and add them in column order
-        const int base = lane & ~3;
-        float cA[6], cB[6];
 #pragma unroll
-        for (int q = 0; q < 3; ++q) {
-            cA[2 * q] = __shfl_sync(0xffffffffu, tot[0], base + q); cA[2 * q + 1] = __shfl_sync(0xffffffffu, tot[1], base + q);
-            cB[2 * q] = __shfl_sync(0xffffffffu, tot[2], base + q); cB[2 * q + 1] = __shfl_sync(0xffffffffu, tot[3], base + q);
-        }
-        if (t == 0) {
+        for (int j = 0; j < 2; ++j) {
+            const int col = 2 * t + j;
+            if (col < mr) {
 #pragma unroll
-            for (int j = 0; j < ROWS_PER_PASS; ++j) {
-                if (j < mr) {
-#pragma unroll
-                    for (int hb = 0; hb < 2; ++hb) {
-                        const float* cc = hb ? cB : cA;
-                        int row = tile * 16 + r + 8 * hb;
-                        __half hv = f2h((cc[3 * j] + cc[3 * j + 1]) + cc[3 * j + 2]);
-                        if (a.logits) a.logits[(size_t)(row0 + j) * a.N + row] = hv;
-                        float lv = h2f(hv);
-                        if (better(lv, row, best[j], besti[j])) { best[j] = lv; besti[j] = row; }
-                    }
+                for (int hb = 0; hb < 2; ++hb) {
+                    int row = tile * 16 + r + 8 * hb;
+                    __half hv = f2h(tot[2 * hb + j]);
+                    if (a.logits) a.logits[(size_t)(row0 + col) * a.N + row] = hv;
+                    float lv = h2f(hv);
+                    if (better(lv, row, best[j], besti[j])) { best[j] = lv; besti[j] = row; }
                 }
             }
         }
         tile += stride; have = tile < ntiles;
     }
-    // lanes with t == 0 hold the running maxima of both pass-rows: merge over r (xor 4, 8, 16), then over warps
+    // merge over r (xor 4, 8, 16): lanes 0..3 then hold the warp's maxima of pass-rows 2t, 2t+1
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -228,12 +225,15 @@ __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
             if (better(ov, oi, best[j], besti[j])) { best[j] = ov; besti[j] = oi; }
         }
     int* fini = reinterpret_cast<int*>(fin);
-    if (lane == 0) { red[warp * 2] = best[0]; red[warp * 2 + 1] = best[1]; fini[warp * 2] = besti[0]; fini[warp * 2 + 1] = besti[1]; }
+    if (lane < 4) {
+        red[warp * 8 + 2 * lane] = best[0]; red[warp * 8 + 2 * lane + 1] = best[1];
+        fini[warp * 8 + 2 * lane] = besti[0]; fini[warp * 8 + 2 * lane + 1] = besti[1];
+    }
     __syncthreads();
     const int parts = gridDim.x;
     if ((int)threadIdx.x < mr) {
         int col = threadIdx.x; float bv = -INFINITY; int bi = 0x7fffffff;
-        for (int w = 0; w < nw; ++w) if (better(red[w * 2 + col], fini[w * 2 + col], bv, bi)) { bv = red[w * 2 + col]; bi = fini[w * 2 + col]; }
+        for (int w = 0; w < nw; ++w) if (better(red[w * 8 + col], fini[w * 8 + col], bv, bi)) { bv = red[w * 8 + col]; bi = fini[w * 8 + col]; }
         a.pval[(size_t)(row0 + col) * parts + blockIdx.x] = bv;
         a.pidx[(size_t)(row0 + col) * parts + blockIdx.x] = bi;
     }
@@ -635,27 +635,21 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
     const bool shared = (slot == (int)gridDim.y - 1);
     const int ntiles = DOWN ? a.H / 16 : a.I / 8;
     const int npair = a.M * a.topk;
-    SliceRegs regs[UPW];
-    XStage st; float* red; float* fin; int* misc;
-    GemvSmem::carve(smem, min(a.M, ROWS_PER_PASS), K, 16 * UPW, TPC, st, red, fin, misc);
+    WStage ws; XStage st; float* red; float* fin; int* misc;
+    GemvSmem::carve(GemvSmem::carve_w(smem, 16 * UPW, ws), min(a.M, ROWS_PER_PASS), K, 16 * UPW, TPC, st, red, fin, misc);
+    const int nvu = min(TPC, ntiles - (int)blockIdx.x * TPC) << lg;      // valid units of this CTA
     // What may be read ahead of the programmatic-launch wait: data written two or more kernels back
     // (every kernel releases its dependents only after its own wait).  For the down kernel that
-    // covers the router's lists, so its weights are in flight while gate/up still computes; for
-    // gate/up (which follows the router directly) only the shared expert's weights qualify.
+    // covers the router's lists, so its weights stream into shared memory while gate/up still
+    // computes; for gate/up (which follows the router directly) only the shared expert's do.
     const bool early = DOWN || shared;
     if (!early) { pdl_wait(); pdl_launch_dependents(); }
     const int n_active = *a.lists.n_active;
     const bool active = shared || slot < n_active;
     const int e = (shared || !active) ? 0 : a.lists.slot_expert[slot];
-    if (active) {
+    if (active && threadIdx.x == 480) {                    // last warp: it stages no activations at batch 1
         const Q4R& q = DOWN ? (shared ? a.sh_down : a.down) : (shared ? a.sh_gu : a.gu);
-        const size_t wstep = q4r_w_uint4(K), sstep = q4r_s_uint4(K);
-        const size_t T0 = (size_t)e * ntiles;
-#pragma unroll
-        for (int i = 0; i < UPW; ++i) {
-            const int u = warp + 16 * i, tile = blockIdx.x * TPC + (u >> lg);
-            if (tile < ntiles) load_slice(regs[i], q.wr + (T0 + tile) * wstep, q.sr + (T0 + tile) * sstep, u & (slices - 1), lane);
-        }
+        wstage_issue(ws, q.wr, q.sr, ((size_t)e * ntiles + (size_t)blockIdx.x * TPC) << lg, nvu, UPW);
     }
     if (early) { pdl_wait(); pdl_launch_dependents(); }
     if (active) {
@@ -676,29 +670,34 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
             StageSrc src{DOWN ? a.hbuf : a.p, DOWN ? a.I : a.H, misc, nullptr, nullptr, 0, 0.f};
             StageRegs sregs;
             stage_issue<PRO_PLAIN>(sregs, src, 0, mr, K);
-            stage_finish<PRO_PLAIN>(sregs, st, src, mr, K);
+            stage_finish<PRO_PLAIN>(sregs, st, src, 0, mr, K);
             __syncthreads();
-#pragma unroll
+            XRegs xr;
+            load_xregs(xr, st, warp & (slices - 1), r, t, mr);
+#pragma unroll 1
             for (int i = 0; i < UPW; ++i) {
-                const int u = warp + 16 * i, tile = blockIdx.x * TPC + (u >> lg);
-                if (tile < ntiles) {
+                const int u = warp + 16 * i;
+                if (u < nvu) {
+                    if (c0 == 0 && !mbar_wait_bounded(ws.bar + i, 0) && a.err && lane == 0) atomicOr(a.err, 1u);
+                    SliceRegs rg;
+                    load_slice_smem(rg, ws.w + (size_t)u * 128, ws.s + (size_t)u * 16, lane);
                     float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
-                    compute_slice(regs[i], st, u & (slices - 1), r, t, mr, accS, accB);
+                    compute_slice_x(rg, xr, accS, accB);
                     finish_acc4(accS, accB, t, v);
                     store_partial(red, u, lane, v);
                 }
             }
             __syncthreads();
-            reduce_tiles(red, fin, min(TPC, ntiles - (int)blockIdx.x * TPC), slices);
+            reduce_tiles(red, fin, nvu >> lg, slices);
             __syncthreads();
             if (DOWN) {
-                for (int i = threadIdx.x; i < TPC * 32; i += blockDim.x) {
-                    int tl2 = i >> 5, col = (i >> 4) & 1, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
+                for (int i = threadIdx.x; i < TPC * 128; i += blockDim.x) {
+                    int tl2 = i >> 7, col = (i >> 4) & 7, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
                     if (tile2 < ntiles && col < mr) a.dbuf[(size_t)misc[8 + col] * a.H + tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, col));
                 }
             } else {
-                for (int j = threadIdx.x; j < TPC * 16; j += blockDim.x) {
-                    int tl2 = j >> 4, col = (j >> 3) & 1, i = j & 7, tile2 = blockIdx.x * TPC + tl2;
+                for (int j = threadIdx.x; j < TPC * 64; j += blockDim.x) {
+                    int tl2 = j >> 6, col = (j >> 3) & 7, i = j & 7, tile2 = blockIdx.x * TPC + tl2;
                     if (tile2 < ntiles && col < mr) {
                         __half g = f2h(tile_value(fin + tl2 * 128, i, col)), u = f2h(tile_value(fin + tl2 * 128, i + 8, col));
                         a.hbuf[(size_t)misc[8 + col] * a.I + tile2 * 8 + i] = swiglu_h(g, u);
@@ -736,9 +735,9 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
 template <bool DOWN, int UPW>
 static void launch_expert_t(const ExpertArgs& a, const GemvPlan& pl, int nslots, cudaStream_t st, bool pdl) {
     int K = DOWN ? a.I : a.H;
-    size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, K, 16 * UPW, pl.tpc);
+    size_t smem = GemvSmem::wstage_bytes(16 * UPW) + GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, K, 16 * UPW, pl.tpc);
     static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_expert<DOWN, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
+    if (!configured) { cudaFuncSetAttribute(k_expert<DOWN, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
     int ntiles = DOWN ? a.H / 16 : a.I / 8;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)(nslots + 1));

@@ -9,6 +9,7 @@ struct Q4W { const uint32_t* w = nullptr; const __half* s = nullptr; const __hal
 struct DenseArgs {
     long long* dbg = nullptr;            // optional per-CTA clock stamps (development aid)
     int lg_slices = 0;                   // log2(K/256), filled by the launcher
+    unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
     Q4R q;                                                       // repacked weights (tiles of 16 rows)
     int N, K, M;                                                 // N outputs (= 16 * tiles)
     const __half* x; int ldx;                                    // activations (plain) / residual stream (rmsnorm) / y (normgate)
@@ -47,6 +48,7 @@ struct RouterArgs {
 struct ExpertArgs {
     long long* dbg = nullptr;            // optional per-CTA clock stamps (development aid)
     int lg_slices = 0;                   // log2(K/256), filled by the launcher
+    unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
     Q4R gu, down;                        // expert slabs, repacked: gate/up paired tiles (I/8 per expert), down tiles (H/16 per expert)
     Q4R sh_gu, sh_down;
     MoeLists lists;
