@@ -76,7 +76,8 @@ struct sl_engine {
     std::map<int, cudaGraphExec_t> graphs;
     std::map<int, int> eager_runs;
     bool use_graph = true;
-    bool use_prefetch = true;       // L2 prefetch of the weights later kernels read
+    bool use_prefetch = false;      // L2 prefetch of the weights later kernels read (SEEDLESS_PREFETCH=1); slower now that
+                                    // every kernel starts its own weight copies ahead of the launch wait
     bool use_pdl = true;            // programmatic dependent launch between the kernels of a step (SEEDLESS_PDL=0 turns it off)
     bool poisoned = false, inject = false;
     std::string fault;
