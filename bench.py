@@ -244,9 +244,22 @@ def main():
         shares = {k: {"launches_per_step": v[0] // nprof, "ms_per_step": v[1] / nprof, "share": v[1] / tot} for k, v in rep.items()}
         dom = max((k for k in rep if rep[k][2] > 0), key=lambda k: rep[k][1])
         n, ms, by = rep[dom]
-        ach = (by / n) / (ms / n * 1e-3) / 1e9
+        # Average duration of one launch of the dominant kernel INSIDE the timed region: its share of
+        # the step (per-launch CUDA events of the eager pass; ncu's launch list gives the same shares)
+        # times the step time measured by the events around the timed region.  The eager per-launch
+        # figure itself (event pair around every launch, no graph) is kept beside it.
+        per_step = shares[dom]["launches_per_step"]
+        us_in_step = shares[dom]["share"] * (dev_ms / K) / per_step * 1e3
+        ach = (by / n) / (us_in_step * 1e-6) / 1e9
+        # dram__bytes_read+write per launch from the ncu capture summarised in
+        # profiles/decode_step_kernels_4layer_ncu_full.md (same weight shapes; k_gemv = mix of the
+        # step's 30 GDN in/out projections and 10 attention q-k-v / o projections, the attention
+        # in-projection scaled from the GDN one by its rows)
+        ncu_traffic = {"k_gemv": (30 * 14.27e6 + 10 * 14.27e6 * 9216 / 12288 + 30 * 4.78e6 + 10 * 4.76e6) / 80,
+                       "k_expert_gateup": 10.64e6, "k_expert_down": 5.36e6, "k_moe_router": 1.12e6, "k_gdn_core": 2.32e6 + 2.1e6}
         roofline = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs,
-                    "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": by / n, "us_per_launch": ms / n * 1e3}
+                    "traffic": ncu_traffic.get(dom) if args.layers == 40 else None, "peak_source": peak_src,
+                    "algorithmic_bytes_per_launch": by / n, "us_per_launch": us_in_step, "us_per_launch_eager_events": ms / n * 1e3}
 
     tok_s = world * K / (dev_ms * 1e-3)
     e2e_tok_s = world * K / (e2e_ms * 1e-3)

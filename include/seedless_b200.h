@@ -161,6 +161,19 @@ int32_t sl_state_restore(sl_stream* s, const void* buf, uint64_t nbytes);
  * greedy step over B streams, one token each; row b is bit-identical to a solo step. */
 int32_t sl_batch_step_argmax(sl_engine* e, sl_stream* const* streams, const int32_t* tokens, int32_t B, int32_t* out_tokens);
 
+/* ---- expert-parallel batched decode (NO COUNTERPART IN THE REFERENCE, which runs on one GPU) ----
+ * One process per GPU, each with its own engine holding the full model; rank r of `world` computes
+ * experts [r*E/world, (r+1)*E/world) for the rows of every rank.  After sl_ep_init, a call of
+ * sl_batch_step_argmax with exactly rows_per_rank streams runs the expert-parallel step: per MoE
+ * layer an NCCL all-gather of the normed rows and routing indices, the local experts on all rows
+ * that chose them, and an NCCL reduce-scatter of the pair outputs back to the rows' owners, who
+ * combine them in ascending k.  All ranks must make that call in lockstep with the same row count.
+ * Token streams are bit-identical to the single-GPU engine's.  cfg.max_rows must be at least
+ * world * rows_per_rank.  Every other entry point (prefill, single steps) stays rank-local.
+ * NCCL is resolved at run time from libnccl.so.2 (SL_ERR_NOT_FOUND if absent). */
+int32_t sl_ep_unique_id(uint8_t* out128);                 /* rank 0: make the 128-byte id, share it by any host channel */
+int32_t sl_ep_init(sl_engine* e, int32_t rank, int32_t world, const uint8_t* id128, int32_t rows_per_rank);
+
 /* ---- single operators (the reference's per-op wrappers used by its kernel tests:
  *      SeedlessMetalForward.qmm SeedlessMetalForward.swift:222, routeTop8Rows
  *      SeedlessFusedVerify.swift:174, moeBlockRows / gdnLayerRows / attnLayerRows

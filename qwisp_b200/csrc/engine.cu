@@ -8,6 +8,8 @@
 #include "../../include/seedless_b200.h"
 #include "gemv.cuh"
 #include "kernels.h"
+#include <dlfcn.h>
+#include <nccl.h>
 
 #include <cstdio>
 #include <cstdlib>
@@ -63,6 +65,10 @@ struct sl_engine {
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
     unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr;
     long long* dbg = nullptr; int dbg_sel = 0;
+    // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
+    int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
+    bool ep_step = false, ep_graph = false;
+    void* ep_comm = nullptr;
     SegDesc* segs = nullptr;
     int hist_cap = 0;
     // pinned staging
@@ -105,6 +111,10 @@ int32_t poison(sl_engine* e, const char* what, cudaError_t err) {
         e->poisoned = true;
         e->fault = std::string(what) + ": " + cudaGetErrorString(err);
     }
+    return SL_ERR_CUDA;
+}
+int32_t poison_msg(sl_engine* e, const std::string& what) {
+    if (!e->poisoned) { e->poisoned = true; e->fault = what; }
     return SL_ERR_CUDA;
 }
 #define CU(e, call)                                         \
@@ -391,6 +401,36 @@ int32_t finish_create(sl_engine* e) {
     return SL_OK;
 }
 
+// ---------------------------------------------------------------- NCCL, loaded on demand
+// The library has no link-time dependency on NCCL: expert-parallel mode resolves the few entry
+// points it needs from the process's libnccl.so.2 (the copy the host framework already loaded, if any).
+struct NcclApi {
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*);
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*GroupStart)();
+    ncclResult_t (*GroupEnd)();
+    const char* (*GetErrorString)(ncclResult_t);
+    bool ok = false;
+};
+static NcclApi g_nccl;
+static bool load_nccl() {
+    if (g_nccl.ok) return true;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return false;
+#define SL_NCCL_SYM(field, name) *(void**)(&g_nccl.field) = dlsym(h, name); if (!g_nccl.field) return false;
+    SL_NCCL_SYM(GetUniqueId, "ncclGetUniqueId") SL_NCCL_SYM(CommInitRank, "ncclCommInitRank") SL_NCCL_SYM(CommDestroy, "ncclCommDestroy")
+    SL_NCCL_SYM(AllGather, "ncclAllGather") SL_NCCL_SYM(ReduceScatter, "ncclReduceScatter")
+    SL_NCCL_SYM(GroupStart, "ncclGroupStart") SL_NCCL_SYM(GroupEnd, "ncclGroupEnd") SL_NCCL_SYM(GetErrorString, "ncclGetErrorString")
+#undef SL_NCCL_SYM
+    g_nccl.ok = true;
+    return true;
+}
+#define NC(e, call) do { ncclResult_t _r = (call); if (_r != ncclSuccess) return poison_msg(e, std::string("NCCL: ") + g_nccl.GetErrorString(_r)); } while (0)
+
 // ---------------------------------------------------------------- the forward pass
 enum HeadMode { HEAD_NONE = 0, HEAD_NORMED = 1, HEAD_ARGMAX = 2, HEAD_LOGITS = 3 };
 
@@ -401,6 +441,42 @@ void pf_q4(PfList& pf, int i, const Q4R& q, size_t max_bytes = (size_t)48 << 20)
     if (i + 1 < 6 && gb) { pf.p[i + 1] = q.sr; pf.bytes[i + 1] = (unsigned)gb; }
 }
 
+// Expert-parallel MoE block of a decode step.  Every rank runs the same number M of rows (its own
+// streams).  Rank r owns experts [ep_e0, ep_e1).  Per layer:
+//   router on the local rows  ->  all-gather of the normed rows and of the routing indices
+//   ->  this rank's experts run on the rows of ALL ranks that chose them (pairs grouped locally)
+//   ->  reduce-scatter of the pair outputs: every pair was computed by exactly one rank and is zero
+//       elsewhere, so the sum is exact and the owner receives the same bits a single GPU computes
+//   ->  the owner combines in ascending k, adds the shared expert (computed locally) and the residual.
+// Buffers are the engine's ordinary ones (sized by max_rows >= world * M): rank r's rows live at
+// offset r*M of p / inds, its pairs at offset r*M*top_k of dbuf, so both collectives run in place.
+int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __half* resid, __half* plain_out) {
+    cudaStream_t st = e->stream;
+    const int R = e->ep_world, r = e->ep_rank, T = R * M, topk = e->topk, H = e->H;
+    ncclComm_t comm = (ncclComm_t)e->ep_comm;
+    ra.p = e->p + (size_t)r * M * H;
+    ra.inds = e->inds + (size_t)r * M * topk;
+    launch_router(ra, st, false);                      // its own pair lists are not used in this mode
+    NC(e, g_nccl.GroupStart());
+    NC(e, g_nccl.AllGather(ra.p, e->p, (size_t)M * H, ncclFloat16, comm, st));
+    NC(e, g_nccl.AllGather(ra.inds, e->inds, (size_t)M * topk, ncclInt32, comm, st));
+    NC(e, g_nccl.GroupEnd());
+    launch_build_lists(e->inds, T * topk, e->ep_e0, e->ep_e1, e->lists, st);
+    CU(e, cudaMemsetAsync(e->dbuf, 0, (size_t)T * topk * H * sizeof(__half), st));
+    ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
+    ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = T; ea.H = H; ea.I = e->I; ea.topk = topk;
+    ea.M_shared = M; ea.shared_row0 = r * M;
+    ea.scores = e->scores; ea.sgl = e->sgl; ea.tile_counter = nullptr; ea.err = e->err_flag;
+    const int local_e = e->ep_e1 - e->ep_e0;
+    const int nslots = T * topk < local_e ? T * topk : local_e;
+    launch_expert_gateup(e->exact, ea, nslots, st, false);
+    launch_expert_down(e->exact, ea, nslots, st, false);
+    __half* mine = e->dbuf + (size_t)r * M * topk * H;
+    NC(e, g_nccl.ReduceScatter(e->dbuf, mine, (size_t)M * topk * H, ncclFloat16, ncclSum, comm, st));
+    launch_moe_combine(e->dbuf, r * M * topk, T * topk, e->scores, e->sgl, M, H, topk, resid, plain_out, st);
+    return SL_OK;
+}
+
 // next: the layer after L (nullptr after the last one, where the lm_head follows)
 void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half* rows, int ld, bool apply_norm, int M, __half* resid, __half* plain_out) {
     cudaStream_t st = e->stream;
@@ -409,6 +485,7 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
     ra.topk = e->topk; ra.inds = e->inds; ra.scores = e->scores; ra.lists = e->lists; ra.counter = e->counters + 1;
     ra.dbg = (e->dbg_sel == 1 && L.type_index == 0) ? e->dbg : nullptr;
+    if (e->ep_step) { enqueue_moe_ep(e, L, ra, M, resid, plain_out); return; }
     launch_router(ra, st, e->use_pdl);
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
     ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = M; ea.H = e->H; ea.I = e->I; ea.topk = e->topk;
@@ -522,17 +599,18 @@ int32_t upload_descs(sl_engine* e, const std::vector<SegDesc>& segs, const int32
 
 // decode-shaped steps (every segment one row) replay a CUDA graph after the first eager run
 int32_t enqueue_decode_step(sl_engine* e, int rows) {
-    if (!e->use_graph) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return SL_OK; }
-    auto it = e->graphs.find(rows);
+    if (!e->use_graph || (e->ep_step && !e->ep_graph)) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return e->poisoned ? SL_ERR_CUDA : SL_OK; }
+    const int key = rows | (e->ep_step ? (1 << 24) : 0);
+    auto it = e->graphs.find(key);
     if (it == e->graphs.end()) {
-        if (e->eager_runs[rows]++ == 0) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return SL_OK; }
+        if (e->eager_runs[key]++ == 0) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return SL_OK; }
         cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
         CU(e, cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
         enqueue_step(e, rows, rows, HEAD_ARGMAX, false);
         CU(e, cudaStreamEndCapture(e->stream, &graph));
         CU(e, cudaGraphInstantiate(&exec, graph, 0));
         cudaGraphDestroy(graph);
-        it = e->graphs.emplace(rows, exec).first;
+        it = e->graphs.emplace(key, exec).first;
     }
     CU(e, cudaGraphLaunch(it->second, e->stream));
     return SL_OK;
@@ -572,6 +650,7 @@ extern "C" {
 
 int32_t sl_engine_destroy(sl_engine* e) {
     if (!e) return SL_ERR_INVALID;
+    if (e->ep_comm && g_nccl.ok) { cudaStreamSynchronize(e->stream); g_nccl.CommDestroy((ncclComm_t)e->ep_comm); e->ep_comm = nullptr; }
     cudaDeviceSynchronize();
     for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
     for (void* p : e->allocs) cudaFree(p);
@@ -803,10 +882,40 @@ int32_t sl_batch_step_argmax(sl_engine* e, sl_stream* const* streams, const int3
         segs.push_back(SegDesc{streams[b]->slot, b, 1, 0});
     }
     if ((rc = upload_descs(e, segs, tokens, B))) return rc;
-    if ((rc = enqueue_decode_step(e, B))) return rc;
+    e->ep_step = (e->ep_world > 1 && B == e->ep_rows);    // every rank makes this call with the same B, in lockstep
+    rc = enqueue_decode_step(e, B);
+    e->ep_step = false;
+    if (rc) return rc;
     for (int b = 0; b < B; ++b) { streams[b]->kv_len += 1; streams[b]->parity ^= 1; }
     CU(e, cudaMemcpyAsync(out_tokens, e->out_tok, (size_t)B * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);
+}
+
+// ---- expert-parallel decode (no counterpart in the reference, which runs on one GPU) ----
+int32_t sl_ep_unique_id(uint8_t* out128) {
+    if (!out128) return SL_ERR_INVALID;
+    if (!load_nccl()) return SL_ERR_NOT_FOUND;
+    static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+    ncclUniqueId id;
+    if (g_nccl.GetUniqueId(&id) != ncclSuccess) return SL_ERR_CUDA;
+    memcpy(out128, &id, 128);
+    return SL_OK;
+}
+int32_t sl_ep_init(sl_engine* e, int32_t rank, int32_t world, const uint8_t* id128, int32_t rows_per_rank) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!id128 || world < 1 || rank < 0 || rank >= world || rows_per_rank <= 0) return SL_ERR_INVALID;
+    if (e->E % world) return SL_ERR_INVALID;
+    if ((int64_t)world * rows_per_rank > e->cfg.max_rows) return SL_ERR_CAPACITY;   // gathered rows use the ordinary buffers
+    if (e->ep_comm) return SL_ERR_INVALID;
+    if (!load_nccl()) return SL_ERR_NOT_FOUND;
+    ncclUniqueId id; memcpy(&id, id128, 128);
+    ncclComm_t comm = nullptr;
+    NC(e, g_nccl.CommInitRank(&comm, world, id, rank));
+    e->ep_comm = comm; e->ep_rank = rank; e->ep_world = world; e->ep_rows = rows_per_rank;
+    e->ep_e0 = rank * (e->E / world); e->ep_e1 = e->ep_e0 + e->E / world;
+    const char* g = getenv("SEEDLESS_EP_GRAPH");
+    e->ep_graph = g && g[0] == '1';
+    return SL_OK;
 }
 
 // ---- snapshot / rollback ----

@@ -56,10 +56,12 @@ struct ExpertArgs {
     __half* hbuf;                        // [(M*topk + M)][I]
     __half* dbuf;                        // [(M*topk + M)][H]
     int M, H, I, topk;
+    int M_shared = -1;                   // rows the shared expert runs on (-1: all M) and where they start in p:
+    int shared_row0 = 0;                 // expert-parallel calls see every rank's rows in p but own only some
     const __half* scores; const __half* sgl;   // combine inputs (down kernel)
     __half* resid;                       // residual stream updated in place, or nullptr ...
     __half* out;                         // ... then the block output goes here
-    unsigned* tile_counter;              // [H/16] tickets, zero between launches
+    unsigned* tile_counter;              // [H/16] tickets, zero between launches; nullptr: no fused combine (dbuf only)
     PfList pf;                           // static prefetch (gate/up kernel: next layer's in-projection)
 };
 
@@ -101,6 +103,11 @@ void launch_embed(const __half* embed, const int* tokens, int M, int H, int voca
 void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl);
 void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
 void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
+// expert-parallel helpers: group the (row, k) pairs of `npairs/topk` rows whose expert lies in [e0, e1)
+void launch_build_lists(const int* inds, int npairs, int e0, int e1, MoeLists lists, cudaStream_t st);
+// out/resid[m] (+)= sum_k fp16(d[pair0 + m*topk + k] * score[m,k]) (ascending k) + sigmoid(sgl[m]) * d[shared0 + m]
+void launch_moe_combine(const __half* dbuf, int pair0, int shared0, const __half* scores, const __half* sgl, int M, int H, int topk,
+                        __half* resid, __half* out, cudaStream_t st);
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl);
 void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
 void launch_attn_decode(const AttnArgs& a, cudaStream_t st);

@@ -114,6 +114,23 @@ class Engine:
         self._check(lib().sl_stream_create(self._h, max_seq_len, C.byref(h)), "sl_stream_create")
         return Stream(self, h, max_seq_len)
 
+    # ---- expert-parallel batched decode (one engine per GPU / process) ----
+    @staticmethod
+    def ep_unique_id():
+        """128-byte NCCL id made on one rank; hand it to every rank's ep_init over any host channel."""
+        buf = np.zeros(128, dtype=np.uint8)
+        rc = lib().sl_ep_unique_id(_ptr(buf))
+        if rc != 0:
+            raise SeedlessError(rc, "sl_ep_unique_id", None)
+        return buf
+
+    def ep_init(self, rank, world, unique_id, rows_per_rank):
+        """After this, batch_step_argmax with exactly rows_per_rank streams runs expert-parallel:
+        this rank computes experts [rank*E/world, (rank+1)*E/world) for every rank's rows."""
+        uid = np.ascontiguousarray(unique_id, dtype=np.uint8)
+        assert uid.size == 128
+        self._check(lib().sl_ep_init(self._h, int(rank), int(world), _ptr(uid), int(rows_per_rank)), "sl_ep_init")
+
     def batch_step_argmax(self, streams, tokens):
         B = len(streams)
         arr = (C.c_void_p * B)(*[s._h for s in streams])

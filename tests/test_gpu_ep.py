@@ -1,0 +1,23 @@
+"""Expert-parallel decode on 2 GPUs equals the single-GPU engine token for token.  Needs two
+devices: on a one-GPU box the test is skipped (the host-side partition logic is covered on CPU
+by tests/test_ep_host.py)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+def test_expert_parallel_tokens_match_single_gpu():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(ROOT, "tests", "ep_worker.py")]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "EP_CHECK_OK" in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
