@@ -16,7 +16,11 @@ excluded (swift/Sources/QwispCore/TellRuntime.swift:1267, 1449-1450).
 
 `--impl reference` times the reference's path on the host cores instead (the CPU restatement of
 its kernels: the reference itself is Swift + Metal and cannot run on Linux).
-With N > 1 every rank runs its own batch-1 stream on its own GPU (weak scaling, no collective).
+With N > 1 the workload is the batched one BASELINE.json pairs with multi-GPU: 64 concurrent streams
+decoded with the MoE expert-parallel across the N GPUs (NCCL all-gather dispatch + reduce-scatter
+combine per layer, attention/GDN data-parallel), aggregate tok/s, total work fixed ("strong").
+The N=1 line carries the same 64-stream workload on one GPU as `batch64_1gpu`, so both series
+(batch 1, batch 64) have their one-GPU point.
 """
 import argparse
 import json
@@ -140,6 +144,102 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+BATCH_STREAMS = 64
+WORKLOAD64 = ("cfg5 (decode part): the same model, 64 concurrent streams, seeded random prompts of 128-256 tokens "
+              "(BASELINE.json: 128-2048; shortened to bound prefill time, stated here), batched greedy decode; "
+              "prefill, the shared-prefix cache and the scheduler are outside the timed region")
+
+
+def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
+    """64 streams dealt to the ranks in blocks; every decode step is one sl_batch_step_argmax per rank
+    (expert-parallel when world > 1).  Returns (aggregate tok/s by device events, by wall clock,
+    ms per step, launches per step, tokens of this rank)."""
+    import numpy as np
+    from qwisp_b200 import ep as EP
+    mine = EP.streams_of_rank(rank, world, BATCH_STREAMS)
+    B = len(mine)
+    max_prompt = 256
+    seq = max_prompt + K + W + 8
+    cfg = Q.config(n_layers=layers, max_rows=max(max_prompt, BATCH_STREAMS), max_streams=B + 1, kv_page_size=64,
+                   kv_pages=(B + 1) * (seq // 64 + 2))
+    eng = Q.Engine.synthetic(cfg, seed=0, norm_jitter=0.0, conv_std=0.02)
+    tstream = torch.cuda.Stream()
+    eng.set_cuda_stream(tstream.cuda_stream)
+    if world > 1:
+        uid = torch.from_numpy(Q.Engine.ep_unique_id() if rank == 0 else np.zeros(128, dtype=np.uint8)).cuda()
+        dist.broadcast(uid, 0)
+        eng.ep_init(rank, world, uid.cpu().numpy(), B)
+    streams, last = [], []
+    for g in mine:
+        n = 128 + (g * 37) % 129
+        prompt = Q.ops.synth_tokens(0, f"bench.batch.prompt.{g}", n, cfg.vocab)
+        st = eng.stream(seq)
+        last.append(int(st.step_argmax(prompt)[-1]))
+        streams.append(st)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        last = [int(v) for v in eng.batch_step_argmax(streams, last)]
+    n0 = eng.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0 = time.time()
+    ev0.record(tstream)
+    toks = []
+    for _ in range(K):
+        out = eng.batch_step_argmax(streams, last)       # host tokens in, host tokens out, one synchronisation per step
+        last = [int(v) for v in out]
+        toks.append(out.copy())
+    ev1.record(tstream)
+    barrier()
+    wall = time.time() - t0
+    ms = ev0.elapsed_time(ev1)
+    launches = (eng.launch_count() - n0) / K
+    if dist is not None:
+        t = torch.tensor([ms, wall * 1e3], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, wall = float(t[0]), float(t[1]) / 1e3
+    fault = eng.gpu_fault()
+    for st in streams:
+        st.close()
+    eng.close()
+    if fault:
+        raise SystemExit(f"engine fault during the batched run: {fault}")
+    return {"tok_s": BATCH_STREAMS * K / (ms * 1e-3), "tok_s_wall": BATCH_STREAMS * K / wall, "ms_per_step": ms / K,
+            "launches_per_step": launches, "rows_per_rank": B, "tokens": np.stack(toks)}
+
+
+def run_batch64_line(args, rank, local_rank, world):
+    import torch
+    import qwisp_b200 as Q
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    K, W = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    r = measure_batch64(Q, torch, dist, rank, world, args.layers, K, W)
+    clocks = sampler.stop()
+    if rank == 0:
+        line = {"metric": "decode_tok_per_s_batch64_ep", "value": r["tok_s"], "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f16", "data": "synthetic",
+                "config": {"workload": WORKLOAD64 if args.layers == 40 else f"DEBUG {args.layers}-layer variant of " + WORKLOAD64,
+                           "parallelism": f"ep{world}: experts split {256 // world} per GPU, {r['rows_per_rank']} streams per GPU; "
+                                          "per MoE layer one NCCL all-gather (rows + routing) and one reduce-scatter (pair outputs)",
+                           "l2": "inputs larger than L2: a step streams the touched experts (GBs) plus 1.6 GB of dense weights",
+                           "timing": "K host-driven batched steps between CUDA events on the launching stream, max over ranks"},
+                "clocks": clocks,
+                "e2e": {"value": r["tok_s_wall"], "unit": "tok/s", "h2d_bytes_per_step": 4 * r["rows_per_rank"], "d2h_bytes_per_step": 4 * r["rows_per_rank"]},
+                "gpu_launches": int(r["launches_per_step"] * K), "roofline": None, "cpu_baseline": None}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -147,6 +247,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-batch64", action="store_true", help="skip the 64-stream measurement on the one-GPU line")
     ap.add_argument("--layers", type=int, default=40, help="debug only: fewer layers (the reported line then says so)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -154,6 +255,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         return run_reference(args, rank, world)
+    if world > 1:
+        return run_batch64_line(args, rank, local_rank, world)
 
     import numpy as np
     import torch
@@ -272,6 +375,14 @@ def main():
         cpu = cpu_oracle_sample(max_seconds=float(os.environ.get("SEEDLESS_CPU_SECONDS", "40")))
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
 
+    st.close(); st2.close(); eng.close()
+    batch64 = None
+    if not args.no_batch64:
+        import torch as _t
+        _t.cuda.empty_cache()
+        b = measure_batch64(Q, torch, None, 0, 1, args.layers, min(K, 32), 3)
+        batch64 = {"metric": "decode_tok_per_s_batch64", "value": b["tok_s"], "e2e": b["tok_s_wall"], "ms_per_step": b["ms_per_step"],
+                   "steps": min(K, 32), "workload": WORKLOAD64, "launches_per_step": b["launches_per_step"]}
     if rank == 0:
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -287,12 +398,9 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
             "gpu_launches": int((launches_per_step or 0) * K),
-            "roofline": roofline, "cpu_baseline": cpu,
+            "roofline": roofline, "cpu_baseline": cpu, "batch64_1gpu": batch64,
         }
         print(json.dumps(line), flush=True)
-    st.close(); st2.close(); eng.close()
-    if dist is not None:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
