@@ -513,13 +513,48 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     if (a.norm_w && tid * 8 < a.H) pv = *reinterpret_cast<const uint4*>(a.h + tid * 8);
     prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
     tq[0] = clock64() - tq0;
-    for (int m0 = 0; m0 < a.M; m0 += 8) {
+    {   // rows m0 .. m0+7 of this CTA (grid.y walks the row groups)
+        const int m0 = blockIdx.y * 8;
         int mr = min(8, a.M - m0);
         __syncthreads();
-        for (int c = 0; c < mr; ++c) {
-            const __half* src = a.h + (size_t)(m0 + c) * a.ldh;
-            if (a.norm_w) block_rmsnorm_row(src, a.norm_w, a.eps, a.H, ps + c * a.H, sm8, m0 + c == 0, pv, pw);
-            else for (int k = threadIdx.x * 8; k < a.H; k += blockDim.x * 8) *reinterpret_cast<uint4*>(ps + c * a.H + k) = *reinterpret_cast<const uint4*>(src + k);
+        if (a.M == 1 || !a.norm_w || (a.H & 255)) {
+            for (int c = 0; c < mr; ++c) {
+                const __half* src = a.h + (size_t)(m0 + c) * a.ldh;
+                if (a.norm_w) block_rmsnorm_row(src, a.norm_w, a.eps, a.H, ps + c * a.H, sm8, m0 + c == 0, pv, pw);
+                else for (int k = threadIdx.x * 8; k < a.H; k += blockDim.x * 8) *reinterpret_cast<uint4*>(ps + c * a.H + k) = *reinterpret_cast<const uint4*>(src + k);
+            }
+        } else if (warp < mr) {
+            // several rows: one warp per row, the eight rows of a pass side by side.  Same sums in the same
+            // order as the block-wide form (per thread 8 elements, a butterfly per 256-chunk, chunks added
+            // in ascending order), so the normed rows are identical bit for bit.
+            const __half* src = a.h + (size_t)(m0 + warp) * a.ldh;
+            uint4 xv[16];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) xv[c] = (c < nblk) ? *reinterpret_cast<const uint4*>(src + c * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+            float tot = 0.f;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                if (c < nblk) {
+                    const __half2* hh = reinterpret_cast<const __half2*>(&xv[c]);
+                    float ss = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(hh[i]); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); }
+                    tot += warp_sum(ss);
+                }
+            }
+            const float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)a.H), a.eps));
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                if (c < nblk) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(a.norm_w + c * 256 + lane * 8);
+                    const __half* hv = reinterpret_cast<const __half*>(&xv[c]);
+                    const __half* wh = reinterpret_cast<const __half*>(&wv);
+                    uint4 o; __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) oh[i] = hmul_rn(wh[i], f2h(__fmul_rn(h2f(hv[i]), inv)));
+                    *reinterpret_cast<uint4*>(ps + warp * a.H + c * 256 + lane * 8) = o;
+                }
+            }
         }
         __syncthreads();
         tq[1] = clock64() - tq0;
@@ -552,7 +587,7 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     tq[2] = clock64() - tq0;
     __threadfence();
     __syncthreads();
-    if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
+    if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x * gridDim.y - 1) ? 1 : 0; }
     __syncthreads();
     tq[3] = clock64() - tq0;
     if (a.dbg && tid == 0 && !s_last) { for (int i = 0; i < 4; ++i) a.dbg[blockIdx.x * 8 + i] = tq[i]; }
@@ -597,7 +632,7 @@ void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl) {
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_moe_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); configured = true; }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((a.E + 7) / 8 + 1)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.gridDim = dim3((unsigned)((a.E + 7) / 8 + 1), (unsigned)((a.M + 7) / 8)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     set_pdl(cfg, attr, pdl);
     RouterArgs copy = a;
