@@ -67,7 +67,7 @@ struct sl_engine {
     long long* dbg = nullptr; int dbg_sel = 0;
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
     int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
-    bool ep_step = false, ep_graph = false;
+    bool ep_step = false;
     void* ep_comm = nullptr;
     SegDesc* segs = nullptr;
     int hist_cap = 0;
@@ -599,7 +599,9 @@ int32_t upload_descs(sl_engine* e, const std::vector<SegDesc>& segs, const int32
 
 // decode-shaped steps (every segment one row) replay a CUDA graph after the first eager run
 int32_t enqueue_decode_step(sl_engine* e, int rows) {
-    if (!e->use_graph || (e->ep_step && !e->ep_graph)) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return e->poisoned ? SL_ERR_CUDA : SL_OK; }
+    // expert-parallel steps are enqueued eagerly: capturing the NCCL collectives into the step graph
+    // deadlocked on two ranks when it was tried, so that combination is not offered
+    if (!e->use_graph || e->ep_step) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return e->poisoned ? SL_ERR_CUDA : SL_OK; }
     const int key = rows | (e->ep_step ? (1 << 24) : 0);
     auto it = e->graphs.find(key);
     if (it == e->graphs.end()) {
@@ -913,8 +915,6 @@ int32_t sl_ep_init(sl_engine* e, int32_t rank, int32_t world, const uint8_t* id1
     NC(e, g_nccl.CommInitRank(&comm, world, id, rank));
     e->ep_comm = comm; e->ep_rank = rank; e->ep_world = world; e->ep_rows = rows_per_rank;
     e->ep_e0 = rank * (e->E / world); e->ep_e1 = e->ep_e0 + e->E / world;
-    const char* g = getenv("SEEDLESS_EP_GRAPH");
-    e->ep_graph = g && g[0] == '1';
     return SL_OK;
 }
 
