@@ -161,6 +161,20 @@ int32_t sl_state_restore(sl_stream* s, const void* buf, uint64_t nbytes);
  * greedy step over B streams, one token each; row b is bit-identical to a solo step. */
 int32_t sl_batch_step_argmax(sl_engine* e, sl_stream* const* streams, const int32_t* tokens, int32_t B, int32_t* out_tokens);
 
+/* ---- speculative sampling on the device (stepSampleRows, SeedlessFusedVerify.swift:3954; kernel
+ *      spec_sample_rows, SamplerGPU.swift:39-156) ----
+ * Forward M rows, then per row: out_full = categorical draw by Gumbel-max at temperature 1/inv_temperature
+ * over the top_p nucleus (top_p >= 0.999: whole vocabulary), out_resid = the same draw with
+ * draft_tokens[m] excluded (= out_full when the draft is -1 or draft_tokens is NULL), out_accept = 1 when
+ * coin < p(draft).  inv_temperature <= 0 is greedy: out_full equals sl_step_argmax's token.  The noise is a
+ * counter-based hash of (seed_lo, seed_hi ^ (base_pos + m), token), so a call is reproducible.  Only the
+ * three int32 arrays leave the device. */
+int32_t sl_step_sample_rows(sl_stream* s, const int32_t* tokens, int32_t M, const int32_t* draft_tokens, float inv_temperature, float top_p,
+                            uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept);
+/* The sampling kernel alone on host logits [M, vocab] fp16 (kernel tests). */
+int32_t sl_op_sample_rows(sl_engine* e, const uint16_t* logits_f16, int32_t M, const int32_t* draft_tokens, float inv_temperature, float top_p,
+                          uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept);
+
 /* ---- expert-parallel batched decode (NO COUNTERPART IN THE REFERENCE, which runs on one GPU) ----
  * One process per GPU, each with its own engine holding the full model; rank r of `world` computes
  * experts [r*E/world, (r+1)*E/world) for the rows of every rank.  After sl_ep_init, a call of

@@ -848,3 +848,123 @@ extern "C" int orc_state_restore(void* sp, const uint8_t* buf, uint64_t n) {
     s->len = newlen;
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Speculative sampling rows (swift/Sources/QwispCore/SamplerGPU.swift:39-156): per row the
+// maximum logit, softmax weights at temperature 1/invT with a 1024-bucket fixed-point histogram
+// for top-p, Gumbel-max with hash noise over the nucleus (full and draft-excluded), accept test.
+// The block-wide float sums follow a 1024-thread organisation (thread t owns tokens t, t+1024, ...;
+// xor butterfly inside each group of 32; groups added in ascending order).  exp and log are the
+// deterministic routines the device uses (IEEE +,*,/ only), so every integer output is reproduced.
+static float det_expf_ref(float x) {
+    if (x < -87.0f) return 0.0f;
+    const float n = nearbyintf(x * 1.44269504f);
+    float r = x - n * 0.693145751953125f;
+    r = r - n * 1.42860682e-6f;
+    float p = 1.0f / 720.0f;
+    p = p * r + 1.0f / 120.0f; p = p * r + 1.0f / 24.0f; p = p * r + 1.0f / 6.0f;
+    p = p * r + 0.5f; p = p * r + 1.0f; p = p * r + 1.0f;
+    int32_t b = ((int32_t)n + 127) << 23; float sc; memcpy(&sc, &b, 4);
+    return p * sc;
+}
+static float det_logf_ref(float a) {
+    int32_t bits; memcpy(&bits, &a, 4);
+    int e = ((bits >> 23) & 255) - 127;
+    int32_t mb = (bits & 0x007fffff) | 0x3f800000; float m; memcpy(&m, &mb, 4);
+    if (m > 1.41421354f) { m = m * 0.5f; e += 1; }
+    const float f = m - 1.0f;
+    const float s = f / (2.0f + f);
+    const float z = s * s;
+    float p = 1.0f / 9.0f;
+    p = p * z + 1.0f / 7.0f; p = p * z + 0.2f; p = p * z + 1.0f / 3.0f; p = p * z + 1.0f;
+    const float lm = (2.0f * s) * p;
+    const float fe = (float)e;
+    return fe * 0.693145751953125f + (lm + fe * 1.42860682e-6f);
+}
+static uint32_t qhash_ref(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t h = a * 0x9E3779B1u + 0x165667B1u;
+    h ^= b + 0x9E3779B9u + (h << 6) + (h >> 2);
+    h ^= c + 0x9E3779B9u + (h << 6) + (h >> 2);
+    h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12; h *= 0x297A2D39u; h ^= h >> 15;
+    return h;
+}
+static float u01_ref(uint32_t h) { float v = (float)(h >> 8) * (1.0f / 16777216.0f); return v > 1e-7f ? v : 1e-7f; }
+static float block_sum_ref(const std::vector<float>& part) {      // part[1024]
+    float tot = 0.f;
+    for (int w = 0; w < 32; ++w) {
+        float v[32];
+        for (int l = 0; l < 32; ++l) v[l] = part[w * 32 + l];
+        for (int s = 16; s >= 1; s >>= 1) { float nv[32]; for (int l = 0; l < 32; ++l) nv[l] = v[l] + v[l ^ s]; memcpy(v, nv, sizeof(v)); }
+        tot = tot + v[0];
+    }
+    return tot;
+}
+extern "C" void orc_sample_rows(const h16* logits, int M, int V, const int32_t* draft, float invT, float top_p,
+                                uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept) {
+    const int T = 1024, BINS = 1024;
+    const float SPAN = 40.0f;
+    for (int m = 0; m < M; ++m) {
+        const h16* row = logits + (size_t)m * V;
+        const int d = draft ? draft[m] : -1;
+        const bool greedy = invT <= 0.0f;
+        const uint32_t salt = seed_hi ^ (base_pos + (uint32_t)m);
+        float gmax = -INFINITY;
+        for (int v = 0; v < V; ++v) gmax = std::max(gmax, h2f(row[v]));
+        const bool do_top_p = !greedy && top_p < 0.999f;
+        float lthr = -INFINITY, znuc = 0.f;
+        if (!greedy) {
+            std::vector<uint32_t> hist(BINS, 0u);
+            std::vector<float> part(T, 0.f);
+            const float bin_w = SPAN / (float)BINS;
+            for (int t = 0; t < T; ++t) {
+                float z = 0.f;
+                for (int v = t; v < V; v += T) {
+                    const float g = (gmax - h2f(row[v])) * invT;
+                    const float w = det_expf_ref(-g);
+                    z = z + w;
+                    if (do_top_p) {
+                        const float q = g / bin_w;
+                        const uint32_t b = (q >= (float)(BINS - 1)) ? (uint32_t)(BINS - 1) : (uint32_t)q;
+                        hist[b] += (uint32_t)(w * 8192.0f);
+                    }
+                }
+                part[t] = z;
+            }
+            znuc = block_sum_ref(part);
+            if (do_top_p) {
+                uint32_t total = 0; for (int b = 0; b < BINS; ++b) total += hist[b];
+                const uint32_t target = (uint32_t)(top_p * (float)total);
+                uint32_t cum = 0; int bstar = BINS - 1;
+                for (int b = 0; b < BINS; ++b) { cum += hist[b]; if (cum >= target) { bstar = b; break; } }
+                lthr = gmax - ((float)(bstar + 1) * bin_w) / invT;
+                for (int t = 0; t < T; ++t) {
+                    float zn = 0.f;
+                    for (int v = t; v < V; v += T) { const float L = h2f(row[v]); if (L >= lthr) zn = zn + det_expf_ref((L - gmax) * invT); }
+                    part[t] = zn;
+                }
+                znuc = block_sum_ref(part);
+            }
+        }
+        float fs = -INFINITY, rs = -INFINITY; int fi = 0x7fffffff, ri = 0x7fffffff;
+        for (int v = 0; v < V; ++v) {
+            const float L = h2f(row[v]);
+            if (do_top_p && L < lthr) continue;
+            float score = L;
+            if (!greedy) score = L * invT - det_logf_ref(-det_logf_ref(u01_ref(qhash_ref(seed_lo, salt, (uint32_t)v))));
+            if (score > fs || (score == fs && v < fi)) { fs = score; fi = v; }
+            if (v != d && (score > rs || (score == rs && v < ri))) { rs = score; ri = v; }
+        }
+        out_full[m] = fi;
+        out_resid[m] = (d < 0) ? fi : ri;
+        float p_draft = 0.f;
+        if (d >= 0) {
+            if (greedy) p_draft = (d == fi) ? 1.0f : 0.0f;
+            else {
+                const float Ld = h2f(row[d]);
+                if (!do_top_p || Ld >= lthr) p_draft = det_expf_ref((Ld - gmax) * invT) / znuc;
+            }
+        }
+        const float coin = u01_ref(qhash_ref(seed_lo, salt, 0x9999AAAAu));
+        out_accept[m] = (coin < p_draft) ? 1 : 0;
+    }
+}

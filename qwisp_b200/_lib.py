@@ -77,6 +77,8 @@ SYMBOLS = {
     "sl_state_restore": (_I32, [_VP, _VP, _U64]),
     "sl_batch_step_argmax": (_I32, [_VP, C.POINTER(_VP), _VP, _I32, _VP]),
     "sl_op_qmm4": (_I32, [_VP, _VP, _VP, _VP, _I32, _I32, _I32, _VP]),
+    "sl_step_sample_rows": (_I32, [_VP, _VP, _I32, _VP, _F, _F, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP, _VP]),
+    "sl_op_sample_rows": (_I32, [_VP, _VP, _I32, _VP, _F, _F, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP, _VP]),
     "sl_ep_unique_id": (_I32, [_VP]),
     "sl_ep_init": (_I32, [_VP, _I32, _I32, _VP, _I32]),
     "sl_op_qmm4_device": (_I32, [_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP]),

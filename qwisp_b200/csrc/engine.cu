@@ -63,7 +63,7 @@ struct sl_engine {
     float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
-    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr;
+    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; int* samp_buf = nullptr;
     long long* dbg = nullptr; int dbg_sel = 0;
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
     int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
@@ -295,6 +295,7 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->tile_counters, (size_t)(H / 16)))) return rc;
     CU(e, cudaMemset(e->tile_counters, 0, (size_t)(H / 16) * sizeof(unsigned)));
     CU(e, cudaMemset(e->counters, 0, 8 * sizeof(unsigned)));
+    if ((rc = dalloc(e, &e->samp_buf, (size_t)4 * R))) return rc;
     if ((rc = dalloc(e, &e->err_flag, (size_t)4))) return rc;
     CU(e, cudaMemset(e->err_flag, 0, 4 * sizeof(unsigned)));
     if ((rc = dalloc(e, &e->att_counters, (size_t)R * c.attn_kv_heads))) return rc;
@@ -839,6 +840,37 @@ int32_t sl_step_logits(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t*
     int32_t rc = run_single(s, tokens, M, HEAD_LOGITS, true); if (rc) return rc;
     CU(e, cudaMemcpyAsync(out_logits_f16, e->logits, (size_t)M * e->V * 2, cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);
+}
+// device part shared by the two sampling entry points: logits [M][V] on the device -> three int32 per row on the host
+static int32_t sample_rows_device(sl_engine* e, const __half* logits, int M, const int32_t* draft, float inv_t, float top_p,
+                                  uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept) {
+    int* d = e->samp_buf;                      // [4][max_rows]: draft, full, resid, accept
+    const int R = e->cfg.max_rows;
+    if (draft) CU(e, cudaMemcpyAsync(d, draft, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    launch_sample_rows(logits, draft ? d : nullptr, d + R, d + 2 * R, d + 3 * R, M, e->V, inv_t, top_p, seed_lo, seed_hi, base_pos, e->stream);
+    if (out_full) CU(e, cudaMemcpyAsync(out_full, d + R, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    if (out_resid) CU(e, cudaMemcpyAsync(out_resid, d + 2 * R, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    if (out_accept) CU(e, cudaMemcpyAsync(out_accept, d + 3 * R, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_step_sample_rows(sl_stream* s, const int32_t* tokens, int32_t M, const int32_t* draft_tokens, float inv_temperature, float top_p,
+                            uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    int32_t rc = run_single(s, tokens, M, HEAD_LOGITS, true); if (rc) return rc;
+    return sample_rows_device(e, e->logits, M, draft_tokens, inv_temperature, top_p, seed_lo, seed_hi, base_pos, out_full, out_resid, out_accept);
+}
+int32_t sl_op_sample_rows(sl_engine* e, const uint16_t* logits_f16, int32_t M, const int32_t* draft_tokens, float inv_temperature, float top_p,
+                          uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!logits_f16 || M <= 0) return SL_ERR_INVALID;
+    if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
+    if (e->logits_rows < M) {
+        __half* lg; if ((rc = dalloc(e, &lg, (size_t)e->cfg.max_rows * e->V))) return rc;
+        e->logits = lg; e->logits_rows = e->cfg.max_rows;
+    }
+    CU(e, cudaMemcpyAsync(e->logits, logits_f16, (size_t)M * e->V * 2, cudaMemcpyHostToDevice, e->stream));
+    return sample_rows_device(e, e->logits, M, draft_tokens, inv_temperature, top_p, seed_lo, seed_hi, base_pos, out_full, out_resid, out_accept);
 }
 int32_t sl_chained_enqueue(sl_stream* s, int32_t first, int32_t K) {
     if (!s) return SL_ERR_INVALID;

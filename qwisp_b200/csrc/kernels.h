@@ -96,6 +96,9 @@ struct StepEndArgs {
 };
 
 void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl);
+// speculative-sampling rows on fp16 logits [M][V]: categorical draw, draw without the draft token, accept flag
+void launch_sample_rows(const __half* logits, const int* draft, int* samp_full, int* samp_resid, int* accept, int M, int V,
+                        float invT, float top_p, uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, cudaStream_t st);
 // lm_head + argmax whose scratch is a fixed module-scope device array; returns 0 or a cudaError_t
 int launch_head_static(const DenseArgs& a, cudaStream_t st);
 int head_static_max_rows();

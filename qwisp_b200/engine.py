@@ -191,6 +191,16 @@ class Stream:
         self.engine._check(lib().sl_chained_collect(self._h, K, _ptr(out)), "sl_chained_collect")
         return out
 
+    def step_sample_rows(self, tokens, draft, inv_t, top_p, seed_lo, seed_hi, base_pos):
+        """Forward the rows, then sample on the device: -> (full, resid, accept) int32 [M]."""
+        toks = _i32(tokens)
+        M = len(toks)
+        d = None if draft is None else _i32(draft)
+        full, resid, acc = (np.empty(M, dtype=np.int32) for _ in range(3))
+        self.engine._check(lib().sl_step_sample_rows(self._h, _ptr(toks), M, _ptr(d) if d is not None else None, float(inv_t), float(top_p),
+                                                     int(seed_lo), int(seed_hi), int(base_pos), _ptr(full), _ptr(resid), _ptr(acc)), "sl_step_sample_rows")
+        return full, resid, acc
+
     def step_logits(self, tokens):
         toks = _i32(tokens)
         out = np.empty((len(toks), self.engine.cfg.vocab), dtype=np.float16)

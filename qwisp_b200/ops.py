@@ -95,3 +95,14 @@ def synth_f16(seed, name, n, mean=0.0, std=1.0):
     if rc != 0:
         raise SeedlessError(rc, "sl_synth_f16")
     return out
+
+
+def sample_rows(engine, logits, draft, inv_t, top_p, seed_lo, seed_hi, base_pos):
+    """The sampling kernel on host logits [M, vocab] fp16 -> (full, resid, accept) int32 [M]."""
+    logits = np.ascontiguousarray(logits, dtype=np.float16)
+    M = logits.shape[0]
+    d = None if draft is None else np.ascontiguousarray(draft, dtype=np.int32)
+    full, resid, acc = (np.empty(M, dtype=np.int32) for _ in range(3))
+    engine._check(lib().sl_op_sample_rows(engine._h, _p(logits), M, _p(d) if d is not None else None, float(inv_t), float(top_p),
+                                          int(seed_lo), int(seed_hi), int(base_pos), _p(full), _p(resid), _p(acc)), "sl_op_sample_rows")
+    return full, resid, acc

@@ -273,3 +273,18 @@ def test_engine_from_host_tensors(tiny_oracle):
             Q.Engine.from_tensors(cfg, missing)
     finally:
         eng.close(); ref.close()
+
+
+def test_step_sample_rows_greedy_equals_argmax(mini_engine):
+    """At temperature 0 the sampling step returns the argmax step's tokens (stepSampleRows with
+    invT <= 0, SamplerGPU.swift:13-15) and leaves the caches in the same state."""
+    import qwisp_b200 as Q
+    prompt = Q.ops.synth_tokens(SEED, "sample.prompt", 9, mini_engine.cfg.vocab)
+    a, b = mini_engine.stream(64), mini_engine.stream(64)
+    ta = a.step_argmax(prompt)
+    full, resid, acc = b.step_sample_rows(prompt, None, 0.0, 1.0, 1, 2, 0)
+    assert np.array_equal(ta, full) and np.array_equal(full, resid) and not acc.any()
+    nxt_a = a.step_argmax([int(ta[-1])])
+    nxt_b, _, _ = b.step_sample_rows([int(full[-1])], [int(nxt_a[0])], 0.0, 1.0, 1, 2, 9)
+    assert np.array_equal(nxt_a, nxt_b)
+    a.close(); b.close()

@@ -312,3 +312,29 @@ def test_lm_head_argmax_with_tie(mini_engine, mini_oracle):
     z = np.zeros((2, H), np.float16)
     _, tz = Q.ops.lm_head(mini_engine, z, want_logits=False)
     assert list(tz) == [0, 0]
+
+
+@pytest.mark.parametrize("inv_t,top_p", [(0.0, 1.0), (1.0 / 0.7, 1.0), (1.0, 0.9), (2.0, 0.5)])
+def test_sampler_rows_bit_exact(mini_engine, inv_t, top_p):
+    """Speculative-sampling rows: draws, draft-excluded draws and accept flags equal the CPU
+    restatement exactly (integer outputs); greedy equals first-index argmax."""
+    import qwisp_b200 as Q
+    from oracle import oracle as O
+    V, M = mini_engine.cfg.vocab, 8
+    logits = (O.synth_f16(5, "sampler.logits", M * V, 0.0, 2.5)).reshape(M, V)
+    logits[1, 7] = logits[1].max()                      # a tie for the maximum: the lower index must win
+    draft = np.array([3, -1, int(np.argmax(logits[2].astype(np.float32))), 100, 5, -1, 9, 511], dtype=np.int32)
+    got = Q.ops.sample_rows(mini_engine, logits, draft, inv_t, top_p, 0x1234, 0xABCD, 40)
+    ref = O.sample_rows(logits, draft, inv_t, top_p, 0x1234, 0xABCD, 40)
+    for g, r, name in zip(got, ref, ("full", "resid", "accept")):
+        assert np.array_equal(g, r), (name, g, r)
+    if inv_t <= 0:
+        assert np.array_equal(got[0], np.argmax(logits.astype(np.float32), axis=1))
+        assert got[2][2] == 1 and got[2][0] == (1 if draft[0] == got[0][0] else 0)
+    else:
+        assert all(got[1][i] != draft[i] for i in range(M) if draft[i] >= 0)
+    again = Q.ops.sample_rows(mini_engine, logits, draft, inv_t, top_p, 0x1234, 0xABCD, 40)
+    assert all(np.array_equal(a, b) for a, b in zip(got, again))          # reproducible
+    other = Q.ops.sample_rows(mini_engine, logits, draft, inv_t, top_p, 0x1235, 0xABCD, 40)
+    if inv_t > 0 and top_p >= 0.999:
+        assert not np.array_equal(got[0], other[0])                       # the seed matters

@@ -211,3 +211,19 @@ def test_golden_vectors():
     import tests_golden_make as mk
     cur = mk.compute()
     assert cur == g, "oracle output changed against the committed golden vectors"
+
+
+def test_oracle_sampler_greedy_and_nucleus():
+    from oracle import oracle as O
+    V, M = 2048, 5
+    logits = O.synth_f16(9, "sampler.cpu", M * V, 0.0, 3.0).reshape(M, V)
+    draft = np.array([1, -1, 7, 2047, 3], dtype=np.int32)
+    full, resid, acc = O.sample_rows(logits, draft, 0.0, 1.0, 11, 22, 0)
+    assert np.array_equal(full, np.argmax(logits.astype(np.float32), axis=1))
+    assert all(resid[i] != draft[i] for i in range(M) if draft[i] >= 0)
+    f2, r2, a2 = O.sample_rows(logits, draft, 1.0, 0.2, 11, 22, 0)       # a tight nucleus keeps draws among the largest logits
+    for m in range(M):
+        rank = int((logits[m].astype(np.float32) > float(logits[m, f2[m]])).sum())
+        assert rank < 64, (m, rank)
+    f3, _, _ = O.sample_rows(logits, draft, 1.0, 0.2, 11, 22, 0)
+    assert np.array_equal(f2, f3)
