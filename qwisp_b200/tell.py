@@ -5,8 +5,7 @@ matching prefix, and on a rejection a rollback followed by a replay of the accep
 (swift/Sources/QwispCore/TellRuntime.swift:716-900).  Greedy speculation never changes the
 output: the token stream equals plain one-token-at-a-time greedy decode, which is what the
 tests assert.  The module needs only a backend with `step_argmax(tokens) -> list`,
-`snapshot()` and `rollback(snap)`; `qwisp_b200.engine.SpecBackend` is one, the tests' CPU
-backend over the oracle is another."""
+`snapshot()` and `rollback(snap)`; `qwisp_b200.engine.SpecBackend` is one."""
 
 
 def suffix_draft(seq, max_match=8, draft_k=7, min_match=2, alpha=2):
