@@ -203,6 +203,12 @@ int32_t sl_op_repack_q4_device(const void* w_dev, const void* s_dev, const void*
  * (micro-benchmarks). */
 int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
                           int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream);
+/* The same product for MANY rows on the tcgen05 tensor cores (accumulator in tensor memory): the
+ * GEMM form the reference uses for batched and prefill rows (tiled qmm, SeedlessMetalForward.swift:160-185).
+ * Same buffers as sl_op_qmm4_device; N % 128 == 0.  Results agree with the GEMV form within fp16
+ * rounding (the f32 summation order inside a group of 64 inputs differs). */
+int32_t sl_op_qmm4_tc_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
+                             int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream);
 /* NO COUNTERPART IN THE REFERENCE.  Greedy tokens of final-normed rows x [M,K] against lm_head
  * weights in the fragment-major layout above: out_tokens_dev[m] = argmax_n (x[m] . dequant4(W[n])),
  * lowest n on ties, the same kernel sl_step_argmax ends with.  All pointers are device pointers;

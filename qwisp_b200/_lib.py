@@ -82,6 +82,7 @@ SYMBOLS = {
     "sl_ep_unique_id": (_I32, [_VP]),
     "sl_ep_init": (_I32, [_VP, _I32, _I32, _VP, _I32]),
     "sl_op_qmm4_device": (_I32, [_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP]),
+    "sl_op_qmm4_tc_device": (_I32, [_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP]),
     "sl_op_repack_q4_device": (_I32, [_VP, _VP, _VP, _I32, _I32, _VP, _VP, _VP]),
     "sl_op_quantize_q4": (_I32, [_VP, _I64, _I64, _VP, _VP, _VP]),
     "sl_op_moe_block": (_I32, [_VP, _I32, _VP, _I32, _VP, _VP, _VP]),

@@ -1152,6 +1152,15 @@ int32_t sl_op_lm_head_argmax_static(const void* x_dev, const void* wr_dev, const
     }
     return SL_OK;
 }
+int32_t sl_op_qmm4_tc_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
+                             int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream) {
+    if (!x_dev || !wr_dev || !sr_dev || !y_dev) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 128 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (!device_ok()) return SL_ERR_NO_DEVICE;
+    Q4R q{}; q.wr = (const uint4*)wr_dev; q.sr = (const uint4*)sr_dev; q.tiles = N / 16; q.K = K;
+    int err = launch_gemm_tc(q, N, K, M, (const __half*)x_dev, K, (__half*)y_dev, N, false, nullptr, (cudaStream_t)cuda_stream);
+    return err == 0 ? SL_OK : SL_ERR_CUDA;
+}
 int32_t sl_op_qmm4(const uint16_t* x, const uint32_t* w, const uint16_t* sc, const uint16_t* bi, int32_t M, int32_t K, int32_t N, uint16_t* y) {
     if (!x || !w || !sc || !bi || !y) return SL_ERR_INVALID;
     if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;

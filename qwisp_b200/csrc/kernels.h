@@ -96,6 +96,8 @@ struct StepEndArgs {
 };
 
 void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl);
+// many-row GEMM on tcgen05 tensor cores with the accumulator in tensor memory (N % 128 == 0, K % 256 == 0); 0 or an error code
+int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, __half* y, int ldy, bool add_to_y, unsigned* err, cudaStream_t st);
 // speculative-sampling rows on fp16 logits [M][V]: categorical draw, draw without the draft token, accept flag
 void launch_sample_rows(const __half* logits, const int* draft, int* samp_full, int* samp_resid, int* accept, int M, int V,
                         float invT, float top_p, uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, cudaStream_t st);

@@ -338,3 +338,36 @@ def test_sampler_rows_bit_exact(mini_engine, inv_t, top_p):
     other = Q.ops.sample_rows(mini_engine, logits, draft, inv_t, top_p, 0x1235, 0xABCD, 40)
     if inv_t > 0 and top_p >= 0.999:
         assert not np.array_equal(got[0], other[0])                       # the seed matters
+
+
+@pytest.mark.parametrize("M,K,N", [(32, 2048, 256), (70, 2048, 4096), (5, 512, 128), (64, 4096, 2048)])
+def test_tensor_core_gemm_matches_gemv_and_oracle(M, K, N):
+    """The tcgen05/TMEM GEMM for many rows against the GEMV form on the same device buffers (fp16
+    rounding apart) and against the CPU oracle's qmm4 (tolerance of BASELINE.json)."""
+    import ctypes as C
+    import torch
+    import qwisp_b200 as Q
+    from oracle import oracle as O
+    L = Q.lib()
+    w = O.synth_f16(3, f"tc.w.{N}.{K}", N * K, 0.0, 0.02).reshape(N, K)
+    packed, scales, biases = O.quantize_q4(w)
+    x = O.synth_f16(3, f"tc.x.{M}.{K}", M * K, 0.0, 1.0).reshape(M, K)
+    ref = O.qmm4(x, packed, scales, biases)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(-1)).cuda()
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    dw, ds, db, dx = dev(packed), dev(scales), dev(biases), dev(x)
+    wr = torch.empty((N // 16) * (K // 128) * 1024, dtype=torch.uint8, device="cuda")
+    sr = torch.empty((N // 16) * (K // 128) * 128, dtype=torch.uint8, device="cuda")
+    assert L.sl_op_repack_q4_device(ptr(dw), ptr(ds), ptr(db), K, N, ptr(wr), ptr(sr), None) == 0
+    y1 = torch.zeros(M * N, dtype=torch.float16, device="cuda")
+    y2 = torch.zeros(M * N, dtype=torch.float16, device="cuda")
+    assert L.sl_op_qmm4_device(ptr(dx), ptr(wr), ptr(sr), M, K, N, ptr(y1), None) == 0
+    assert L.sl_op_qmm4_tc_device(ptr(dx), ptr(wr), ptr(sr), M, K, N, ptr(y2), None) == 0
+    torch.cuda.synchronize()
+    g1 = y1.cpu().numpy().reshape(M, N)
+    g2 = y2.cpu().numpy().reshape(M, N)
+    rep_o = f16_report(g2, ref)
+    rep_g = f16_report(g2, g1)
+    print(f"tc gemm M={M} K={K} N={N}: vs oracle {rep_o}  vs gemv {rep_g}")
+    assert np.isfinite(g2.astype(np.float32)).all()
+    assert rep_o["max_abs"] <= TOL and rep_g["max_abs"] <= 4e-3
