@@ -64,7 +64,6 @@ struct sl_engine {
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
     unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; int* samp_buf = nullptr;
-    long long* dbg = nullptr; int dbg_sel = 0;
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
     int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
     bool ep_step = false;
@@ -325,7 +324,6 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->kv_pool, (size_t)c.kv_pages * page_elems))) return rc;
     for (int i = c.kv_pages - 1; i >= 0; --i) e->free_pages.push_back(i);
     for (int i = S - 1; i >= 0; --i) e->free_slots.push_back(i);
-    if (getenv("SEEDLESS_DEBUG_TIMELINE")) { e->dbg_sel = atoi(getenv("SEEDLESS_DEBUG_TIMELINE")); if ((rc = dalloc(e, &e->dbg, (size_t)64 * 8))) return rc; CU(e, cudaMemset(e->dbg, 0, 64 * 8 * 8)); }
     const char* pfe = getenv("SEEDLESS_PREFETCH");
     if (pfe) e->use_prefetch = (pfe[0] == '1');
     const char* pd = getenv("SEEDLESS_PDL");
@@ -485,7 +483,6 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     ra.router = L.router; ra.shared_gate = L.shared_gate; ra.M = M; ra.H = e->H; ra.E = e->E;
     ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
     ra.topk = e->topk; ra.inds = e->inds; ra.scores = e->scores; ra.lists = e->lists; ra.counter = e->counters + 1;
-    ra.dbg = (e->dbg_sel == 1 && L.type_index == 0) ? e->dbg : nullptr;
     if (e->ep_step) { enqueue_moe_ep(e, L, ra, M, resid, plain_out); return; }
     launch_router(ra, st, e->use_pdl);
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
@@ -502,13 +499,12 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
                    __half* resid, __half* plain_out, const int* row_pos_override) {
     cudaStream_t st = e->stream;
     const sl_config& c = e->cfg;
-    DenseArgs d{}; d.err = e->err_flag; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
+    DenseArgs d{}; d.err = e->err_flag; d.norm_scratch = e->normed; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
     d.x = rows; d.ldx = e->H; d.nw = norm_w; d.eps = c.rms_eps; d.y = e->inproj; d.ldy = (int)L.in_proj.N;
     if (e->use_prefetch) pf_q4(d.pf, 0, L.r_out);
-    if (e->dbg_sel == 2 && L.type_index == 0 && !L.is_attn) d.dbg = e->dbg;
     launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, e->exact, d, st, e->use_pdl);
     DenseArgs o{};
-    if (e->dbg_sel == 3 && L.type_index == 0 && !L.is_attn) o.dbg = e->dbg; o.err = e->err_flag; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
+    o.err = e->err_flag; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
     o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H;
     if (e->use_prefetch) {
         o.pf.p[0] = L.router; o.pf.bytes[0] = (unsigned)((size_t)e->E * e->H * 2);
@@ -773,11 +769,6 @@ const char* sl_last_fault(sl_engine* e) {
 }
 int32_t sl_inject_fault(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->inject = on != 0; return SL_OK; }
 int64_t sl_engine_launch_count(sl_engine* e) { (void)e; return kernel_launch_count(); }
-int32_t sl_debug_read(sl_engine* e, long long* out, int32_t n) {
-    if (!e || !e->dbg || !out || n > 64 * 8) return SL_ERR_INVALID;
-    cudaStreamSynchronize(e->stream);
-    return cudaMemcpy(out, e->dbg, (size_t)n * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? SL_OK : SL_ERR_CUDA;
-}
 int32_t sl_engine_use_graphs(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->use_graph = on != 0; return SL_OK; }
 int32_t sl_profile_start(sl_engine* e) { if (!e) return SL_ERR_INVALID; cudaStreamSynchronize(e->stream); profile_start(); return SL_OK; }
 int32_t sl_profile_report(sl_engine* e, char* buf, uint64_t cap) {

@@ -138,7 +138,7 @@ __device__ __forceinline__ float sumsq8(uint4 v) {
 // x = fp16(silu_f32(z) * float(w * fp16(y * inv))) (SeedlessFusedVerify.swift:803-813).
 // Contains one __syncthreads() for PRO_RMSNORM; the caller synchronises before reading xs.
 template <int PRO>
-__device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& st, const StageSrc& s, int row0, int mr, int K, long long* dbgp = nullptr, long long t0 = 0) {
+__device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& st, const StageSrc& s, int row0, int mr, int K) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int lgc = 31 - __clz(K >> 8), chunks = 1 << lgc, units = mr << lgc;
     if (PRO == PRO_RMSNORM) {
@@ -146,11 +146,9 @@ __device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& 
             const int col = u >> lgc, ch = u & (chunks - 1);
             const uint4 v = (j == 0) ? sr.a[0] : ((j == 1) ? sr.a[1] : stage_load(s, row0, col, (ch << 8) + lane * 8));
             float ss = warp_sum(sumsq8(v));
-            if (dbgp && threadIdx.x == 0) dbgp[8] = clock64() - t0;
             if (lane == 0) st.part[col * 16 + ch] = ss;
         }
         __syncthreads();
-        if (dbgp && threadIdx.x == 0) dbgp[9] = clock64() - t0;
     }
     for (int j = 0, u = warp; u < units; ++j, u += nw) {
         const int col = u >> lgc, ch = u & (chunks - 1), k0 = (ch << 8) + lane * 8;
@@ -162,10 +160,8 @@ __device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& 
             float tot = 0.f;
             for (int c = 0; c < chunks; ++c) tot += st.part[col * 16 + c];
             float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), s.eps));
-            if (dbgp && threadIdx.x == 0) dbgp[10] = clock64() - t0;
             const uint4 wv = (j == 0) ? sr.b[0] : ((j == 1) ? sr.b[1] : *reinterpret_cast<const uint4*>(s.nw + k0));
             o = rms_apply8(v, wv, inv);
-            if (dbgp && threadIdx.x == 0) { dbgp[11] = clock64() - t0 + (o.x & 1); }
         } else {
             const int row = s.rows ? s.rows[col] : row0 + col;
             const uint4 zv = (j == 0) ? sr.c[0] : ((j == 1) ? sr.c[1] : __ldcg(reinterpret_cast<const uint4*>(s.z + (size_t)row * s.ldz + k0)));
@@ -187,7 +183,6 @@ __device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& 
             }
         }
         store_staged(st, col, k0, o, lane);
-        if (dbgp && threadIdx.x == 0) dbgp[12] = clock64() - t0;
     }
 }
 // whole-prologue forms for kernels that have nothing to overlap with the loads

@@ -63,12 +63,8 @@ static void set_pdl(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, bool pdl
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
 }
-__device__ __forceinline__ long long gtimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define DBG_STAMP(i) do { if (a.dbg && threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x < 30) a.dbg[blockIdx.x * 16 + (i)] = ((i) == 0 || (i) == 7) ? gtimer() : (clock64() - dbg_t0); } while (0)
 template <int PRO, int EPI, int UPW>
 __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
-    long long dbg_t0 = clock64();
-    DBG_STAMP(0);
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
@@ -85,23 +81,16 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
     // finishes and while this CTA stages its activations; they occupy neither registers nor the
     // load/store queue.  Dependents are released only after the wait, so whatever a dependent
     // reads ahead of its own wait was written by a kernel that is complete.
-    if (threadIdx.x == 480) {                              // last warp: it stages no activations at batch 1
-        if (a.dbg && blockIdx.x < 30) a.dbg[blockIdx.x * 16 + 14] = clock64() - dbg_t0;
-        wstage_issue(ws, a.q.wr, a.q.sr, (size_t)blockIdx.x * TPC << lg, nvu, UPW);
-        if (a.dbg && blockIdx.x < 30) a.dbg[blockIdx.x * 16 + 15] = clock64() - dbg_t0;
-    }
+    if (threadIdx.x == 480) wstage_issue(ws, a.q.wr, a.q.sr, (size_t)blockIdx.x * TPC << lg, nvu, UPW);   // last warp: it stages no activations at batch 1
     StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
     StageRegs sregs;
     stage_issue_const<PRO>(sregs, src, mr, a.K);
     pdl_wait();
     pdl_launch_dependents();
-    DBG_STAMP(1);
     stage_issue<PRO>(sregs, src, row0, mr, a.K);
     if (blockIdx.y == 0) prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
-    DBG_STAMP(2);
-    stage_finish<PRO>(sregs, st, src, row0, mr, a.K, (a.dbg && blockIdx.x < 30 && blockIdx.y == 0) ? a.dbg + blockIdx.x * 16 : nullptr, dbg_t0);
+    stage_finish<PRO>(sregs, st, src, row0, mr, a.K);
     __syncthreads();
-    DBG_STAMP(3);
     XRegs xr;                                     // the warp's slice is the same for all its units (16 % slices == 0)
     load_xregs(xr, st, warp & (slices - 1), r, t, mr);
 #pragma unroll 1
@@ -117,12 +106,9 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
             store_partial(red, u, lane, v);
         }
     }
-    DBG_STAMP(4);
     __syncthreads();
-    DBG_STAMP(5);
     reduce_tiles(red, fin, nvu >> lg, slices);
     __syncthreads();
-    DBG_STAMP(6);
     if (EPI == EPI_STORE || EPI == EPI_RESID) {
         for (int i = threadIdx.x; i < TPC * 128; i += blockDim.x) {
             int tl2 = i >> 7, col = (i >> 4) & 7, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
@@ -142,7 +128,6 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
             }
         }
     }
-    DBG_STAMP(7);
 }
 template <int PRO, int EPI, int UPW>
 static void launch_gemv_t(const DenseArgs& a, const GemvPlan& pl, cudaStream_t st, bool pdl) {
@@ -326,6 +311,27 @@ void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t
         if (pro == PRO_RMSNORM) { if (exact) launch_head_t<PRO_RMSNORM, true>(a, st, pdl); else launch_head_t<PRO_RMSNORM, false>(a, st, pdl); return; }
         if (pro == PRO_PLAIN) { if (exact) launch_head_t<PRO_PLAIN, true>(a, st, pdl); else launch_head_t<PRO_PLAIN, false>(a, st, pdl); return; }
     }
+    // Many rows (prefill chunks, large batches): the tcgen05 tensor-core GEMM, with the RMSNorm done by
+    // a row kernel first.  SEEDLESS_TC_ROWS sets the threshold (0 = never); below it, and for the gated
+    // norm of the GDN out-projection, the GEMV family walks the rows in passes of 8.
+    static int tc_rows = -1;
+    if (tc_rows < 0) { const char* v = getenv("SEEDLESS_TC_ROWS"); tc_rows = v ? atoi(v) : 64; }
+    if (tc_rows > 0 && a.M >= tc_rows && a.N % 128 == 0 && a.K % 256 == 0 && (epi == EPI_STORE || epi == EPI_RESID) &&
+        (pro == PRO_PLAIN || (pro == PRO_RMSNORM && a.norm_scratch))) {
+        const __half* x = a.x; int ldx = a.ldx;
+        if (pro == PRO_RMSNORM) {
+            if (a.ldx != a.K) goto gemv_path;                  // the row kernel reads dense rows
+            launch_final_norm(a.x, a.nw, a.eps, a.M, a.K, a.norm_scratch, st);
+            x = a.norm_scratch; ldx = a.K;
+        }
+        {
+            ProfScope ps("k_gemm_umma", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
+            launch_gemm_tc(a.q, a.N, a.K, a.M, x, ldx, a.y, a.ldy, epi == EPI_RESID, a.err, st);
+            COUNT_LAUNCH();
+        }
+        return;
+    }
+gemv_path:
     const GemvPlan pl = gemv_plan(a.K, epi == EPI_SWIGLU ? a.N / 8 : a.N / 16, 1);
 #define SL_CASE(P, E)                                                                                       \
     if (pro == P && epi == E) {                                                                             \
@@ -495,7 +501,6 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     __shared__ int s_last; __shared__ int s_cnt[256]; __shared__ int s_cur[256]; __shared__ int s_off[256];
     __shared__ float s_route[8][512 + 32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-    long long tq0 = clock64(), tq[6] = {0, 0, 0, 0, 0, 0};
     const int nblk = a.H >> 8;                                // <= 16
     const bool tail = (blockIdx.x == gridDim.x - 1);
     const int e = blockIdx.x * 8 + warp;
@@ -512,7 +517,6 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     pdl_launch_dependents();
     if (a.norm_w && tid * 8 < a.H) pv = *reinterpret_cast<const uint4*>(a.h + tid * 8);
     prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
-    tq[0] = clock64() - tq0;
     {   // rows m0 .. m0+7 of this CTA (grid.y walks the row groups)
         const int m0 = blockIdx.y * 8;
         int mr = min(8, a.M - m0);
@@ -557,7 +561,6 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
             }
         }
         __syncthreads();
-        tq[1] = clock64() - tq0;
         if (tail) {
             for (int i = threadIdx.x; i < mr * a.H / 8; i += blockDim.x) {
                 int c = i / (a.H / 8), k = (i - c * (a.H / 8)) * 8;
@@ -584,21 +587,15 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
         }
     }
     // ---- the CTA that finishes last routes every row and groups the (row, k) pairs by expert ----
-    tq[2] = clock64() - tq0;
     __threadfence();
     __syncthreads();
     if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x * gridDim.y - 1) ? 1 : 0; }
     __syncthreads();
-    tq[3] = clock64() - tq0;
-    if (a.dbg && tid == 0 && !s_last) { for (int i = 0; i < 4; ++i) a.dbg[blockIdx.x * 8 + i] = tq[i]; }
     if (!s_last) return;
     __threadfence();
-    tq[5] = clock64() - tq0;
     for (int m = warp; m < a.M; m += 8) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, s_route[warp], lane);
     if (tid == 0) *a.counter = 0u;
     __syncthreads();
-    tq[4] = clock64() - tq0;
-    if (a.dbg && tid == 0) { for (int i = 0; i < 6; ++i) a.dbg[blockIdx.x * 8 + i] = tq[i]; a.dbg[blockIdx.x * 8 + 7] = 1; }
     if (a.M == 1) {                                          // one row: its k experts are distinct, slot k = k-th choice
         if (tid < a.topk) {
             a.lists.slot_expert[tid] = a.inds[tid]; a.lists.slot_off[tid] = tid; a.lists.slot_cnt[tid] = 1; a.lists.pairs[tid] = tid;

@@ -7,9 +7,9 @@ namespace sl {
 struct Q4W { const uint32_t* w = nullptr; const __half* s = nullptr; const __half* b = nullptr; int64_t N = 0; int K = 0; };
 
 struct DenseArgs {
-    long long* dbg = nullptr;            // optional per-CTA clock stamps (development aid)
     int lg_slices = 0;                   // log2(K/256), filled by the launcher
     unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
+    __half* norm_scratch = nullptr;      // [M][K] scratch for the many-row path (normed rows); nullptr keeps the GEMV path
     Q4R q;                                                       // repacked weights (tiles of 16 rows)
     int N, K, M;                                                 // N outputs (= 16 * tiles)
     const __half* x; int ldx;                                    // activations (plain) / residual stream (rmsnorm) / y (normgate)
@@ -42,11 +42,9 @@ struct RouterArgs {
     int topk; int* inds; __half* scores; // [M][topk] routing result (written by the last CTA)
     MoeLists lists; unsigned* counter;
     PfList pf;                           // static prefetch (every CTA)
-    long long* dbg;                      // optional per-CTA clock stamps (development aid), usually nullptr
 };
 
 struct ExpertArgs {
-    long long* dbg = nullptr;            // optional per-CTA clock stamps (development aid)
     int lg_slices = 0;                   // log2(K/256), filled by the launcher
     unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
     Q4R gu, down;                        // expert slabs, repacked: gate/up paired tiles (I/8 per expert), down tiles (H/16 per expert)
