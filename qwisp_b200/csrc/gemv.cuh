@@ -403,11 +403,15 @@ struct GemvSmem {
     }
 };
 
-// One thread: start the bulk copies of the CTA's `nvu` valid units (global unit index u0), one
-// mbarrier per round of 16 units.  w_all / s_all are the matrix's (or the expert's) arrays.
-__device__ __forceinline__ void wstage_issue(const WStage& ws, const uint4* w_all, const uint4* s_all, size_t u0, int nvu, int rounds) {
+// One thread: (init) the mbarriers of a stage, one per round of 16 units; (copy) start the bulk copies of
+// the CTA's `nvu` valid units (global unit index u0) and arm each round's barrier for this phase.
+// w_all / s_all are the matrix's (or the expert's) arrays.  A stage can be refilled once every
+// warp is done reading it; each refill is one more phase of the same barriers.
+__device__ __forceinline__ void wstage_init(const WStage& ws, int rounds) {
     for (int i = 0; i < rounds; ++i) mbar_init(ws.bar + i, 1);
     mbar_fence_init();
+}
+__device__ __forceinline__ void wstage_copy(const WStage& ws, const uint4* w_all, const uint4* s_all, size_t u0, int nvu, int rounds) {
     for (int i = 0; i < rounds; ++i) {
         const int n = min(16, nvu - 16 * i);
         if (n <= 0) break;
@@ -415,6 +419,10 @@ __device__ __forceinline__ void wstage_issue(const WStage& ws, const uint4* w_al
         bulk_g2s(ws.w + (size_t)16 * i * 128, w_all + (u0 + 16 * i) * 128, (uint32_t)n * 2048, ws.bar + i);
         bulk_g2s(ws.s + (size_t)16 * i * 16, s_all + (u0 + 16 * i) * 16, (uint32_t)n * 256, ws.bar + i);
     }
+}
+__device__ __forceinline__ void wstage_issue(const WStage& ws, const uint4* w_all, const uint4* s_all, size_t u0, int nvu, int rounds) {
+    wstage_init(ws, rounds);
+    wstage_copy(ws, w_all, s_all, u0, nvu, rounds);
 }
 
 }  // namespace sl

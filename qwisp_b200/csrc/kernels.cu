@@ -63,17 +63,21 @@ static void set_pdl(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, bool pdl
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
 }
-template <int PRO, int EPI, int UPW>
-__global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
+// NW warps per CTA (8 or 16), UPW units per warp; the CTA's NW*UPW units arrive in rounds of 16.
+// Eight warps leave room for a second CTA on the SM (registers), so the next kernel's CTAs can
+// become resident, start their weight copies and stage while this one computes.
+template <int PRO, int EPI, int NW, int UPW>
+__global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1) k_gemv(DenseArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
     const int slices = a.K >> 8, lg = a.lg_slices;
-    const int TPC = (16 * UPW) >> lg;
+    constexpr int UNITS = NW * UPW, ROUNDS = UNITS / 16;
+    const int TPC = UNITS >> lg;
     const int row0 = blockIdx.y * ROWS_PER_PASS;
     const int mr = min(ROWS_PER_PASS, a.M - row0);
     WStage ws; XStage st; float* red; float* fin; int* misc;
-    GemvSmem::carve(GemvSmem::carve_w(smem, 16 * UPW, ws), min(a.M, ROWS_PER_PASS), a.K, 16 * UPW, TPC, st, red, fin, misc);
+    GemvSmem::carve(GemvSmem::carve_w(smem, UNITS, ws), min(a.M, ROWS_PER_PASS), a.K, UNITS, TPC, st, red, fin, misc);
     const int ntiles = (EPI == EPI_SWIGLU) ? a.N / 8 : a.N / 16;
     const int nvu = min(TPC, ntiles - (int)blockIdx.x * TPC) << lg;      // valid units of this CTA
     // The weights do not depend on the kernel before this one: one thread starts their bulk copies
@@ -81,7 +85,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
     // finishes and while this CTA stages its activations; they occupy neither registers nor the
     // load/store queue.  Dependents are released only after the wait, so whatever a dependent
     // reads ahead of its own wait was written by a kernel that is complete.
-    if (threadIdx.x == 480) wstage_issue(ws, a.q.wr, a.q.sr, (size_t)blockIdx.x * TPC << lg, nvu, UPW);   // last warp: it stages no activations at batch 1
+    if (threadIdx.x == (NW - 1) * 32) wstage_issue(ws, a.q.wr, a.q.sr, (size_t)blockIdx.x * TPC << lg, nvu, ROUNDS);   // last warp: least staging work
     StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
     StageRegs sregs;
     stage_issue_const<PRO>(sregs, src, mr, a.K);
@@ -91,13 +95,13 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
     if (blockIdx.y == 0) prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
     stage_finish<PRO>(sregs, st, src, row0, mr, a.K);
     __syncthreads();
-    XRegs xr;                                     // the warp's slice is the same for all its units (16 % slices == 0)
+    XRegs xr;                                     // the warp's slice is the same for all its units (NW % slices == 0)
     load_xregs(xr, st, warp & (slices - 1), r, t, mr);
 #pragma unroll 1
     for (int i = 0; i < UPW; ++i) {
-        const int u = warp + 16 * i;
+        const int u = warp + NW * i;
         if (u < nvu) {
-            if (!mbar_wait_bounded(ws.bar + i, 0) && a.err && lane == 0) atomicOr(a.err, 1u);
+            if (!mbar_wait_bounded(ws.bar + (u >> 4), 0) && a.err && lane == 0) atomicOr(a.err, 1u);
             SliceRegs rg;
             load_slice_smem(rg, ws.w + (size_t)u * 128, ws.s + (size_t)u * 16, lane);
             float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
@@ -129,20 +133,20 @@ __global__ void __launch_bounds__(512, 1) k_gemv(DenseArgs a) {
         }
     }
 }
-template <int PRO, int EPI, int UPW>
+template <int PRO, int EPI, int NW, int UPW>
 static void launch_gemv_t(const DenseArgs& a, const GemvPlan& pl, cudaStream_t st, bool pdl) {
-    size_t smem = GemvSmem::wstage_bytes(16 * UPW) + GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 16 * UPW, pl.tpc);
+    size_t smem = GemvSmem::wstage_bytes(NW * UPW) + GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, NW * UPW, pl.tpc);
     static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_gemv<PRO, EPI, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
+    if (!configured) { cudaFuncSetAttribute(k_gemv<PRO, EPI, NW, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
     int ntiles = EPI == EPI_SWIGLU ? a.N / 8 : a.N / 16;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS));
-    cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.blockDim = dim3(NW * 32); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     set_pdl(cfg, attr, pdl);
     DenseArgs copy = a; copy.lg_slices = pl.lg_slices;
     ProfScope ps("k_gemv", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
-    cudaLaunchKernelEx(&cfg, k_gemv<PRO, EPI, UPW>, copy);
+    cudaLaunchKernelEx(&cfg, k_gemv<PRO, EPI, NW, UPW>, copy);
     COUNT_LAUNCH();
 }
 
@@ -315,7 +319,7 @@ void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t
     // a row kernel first.  SEEDLESS_TC_ROWS sets the threshold (0 = never); below it, and for the gated
     // norm of the GDN out-projection, the GEMV family walks the rows in passes of 8.
     static int tc_rows = -1;
-    if (tc_rows < 0) { const char* v = getenv("SEEDLESS_TC_ROWS"); tc_rows = v ? atoi(v) : 64; }
+    if (tc_rows < 0) { const char* v = getenv("SEEDLESS_TC_ROWS"); tc_rows = v ? atoi(v) : 128; }
     if (tc_rows > 0 && a.M >= tc_rows && a.N % 128 == 0 && a.K % 256 == 0 && (epi == EPI_STORE || epi == EPI_RESID) &&
         (pro == PRO_PLAIN || (pro == PRO_RMSNORM && a.norm_scratch))) {
         const __half* x = a.x; int ldx = a.ldx;
@@ -333,11 +337,18 @@ void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t
     }
 gemv_path:
     const GemvPlan pl = gemv_plan(a.K, epi == EPI_SWIGLU ? a.N / 8 : a.N / 16, 1);
+    // eight-warp CTAs (same units per CTA, twice the units per warp) when a warp's slice stays fixed with a stride of 8
+    static int narrow_env = -1;
+    if (narrow_env < 0) { const char* v = getenv("SEEDLESS_GEMV_WARPS"); narrow_env = (v && atoi(v) == 8) ? 1 : 0; }   // measured equal to 16 warps; off unless asked for
+    const bool narrow = narrow_env && (a.K >> 8) <= 8 && a.M <= ROWS_PER_PASS;
 #define SL_CASE(P, E)                                                                                       \
     if (pro == P && epi == E) {                                                                             \
-        if (pl.upw == 1) launch_gemv_t<P, E, 1>(a, pl, st, pdl);                                            \
-        else if (pl.upw == 2) launch_gemv_t<P, E, 2>(a, pl, st, pdl);                                       \
-        else launch_gemv_t<P, E, 3>(a, pl, st, pdl);                                                        \
+        if (narrow && pl.upw == 1) launch_gemv_t<P, E, 8, 2>(a, pl, st, pdl);                               \
+        else if (narrow && pl.upw == 2) launch_gemv_t<P, E, 8, 4>(a, pl, st, pdl);                          \
+        else if (narrow) launch_gemv_t<P, E, 8, 6>(a, pl, st, pdl);                                         \
+        else if (pl.upw == 1) launch_gemv_t<P, E, 16, 1>(a, pl, st, pdl);                                   \
+        else if (pl.upw == 2) launch_gemv_t<P, E, 16, 2>(a, pl, st, pdl);                                   \
+        else launch_gemv_t<P, E, 16, 3>(a, pl, st, pdl);                                                    \
         return;                                                                                             \
     }
     SL_CASE(PRO_PLAIN, EPI_STORE)
@@ -663,30 +674,49 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
     const int K = DOWN ? a.I : a.H;
     const int slices = K >> 8, lg = a.lg_slices;
     const int TPC = (16 * UPW) >> lg;
-    const int slot = blockIdx.y;
-    const bool shared = (slot == (int)gridDim.y - 1);
     const int ntiles = DOWN ? a.H / 16 : a.I / 8;
     const int npair = a.M * a.topk;
-    WStage ws; XStage st; float* red; float* fin; int* misc;
-    GemvSmem::carve(GemvSmem::carve_w(smem, 16 * UPW, ws), min(a.M, ROWS_PER_PASS), K, 16 * UPW, TPC, st, red, fin, misc);
+    // A CTA owns one group of output tiles (blockIdx.x) and walks the expert slots blockIdx.y,
+    // blockIdx.y + gridDim.y, ...; slot n_active stands for the shared expert.  With two weight
+    // stages the next slot's weights stream in while the current slot is computed.
+    XStage st; float* red; float* fin; int* misc;
+    const size_t stage_bytes = GemvSmem::wstage_bytes(16 * UPW);
+    auto stage_at = [&](int s_) { WStage w; GemvSmem::carve_w(smem + (size_t)s_ * stage_bytes, 16 * UPW, w); return w; };
+    GemvSmem::carve(smem + (size_t)a.nstages * stage_bytes, min(a.M, ROWS_PER_PASS), K, 16 * UPW, TPC, st, red, fin, misc);
     const int nvu = min(TPC, ntiles - (int)blockIdx.x * TPC) << lg;      // valid units of this CTA
+    const bool issuer = (threadIdx.x == 480);               // last warp: it stages no activations at batch 1
+    auto issue = [&](int j, int n_active, int stage) {
+        const bool sh = (j == n_active);
+        const int e = sh ? 0 : a.lists.slot_expert[j];
+        const Q4R& q = DOWN ? (sh ? a.sh_down : a.down) : (sh ? a.sh_gu : a.gu);
+        wstage_copy(stage_at(stage), q.wr, q.sr, ((size_t)e * ntiles + (size_t)blockIdx.x * TPC) << lg, nvu, UPW);
+    };
+    if (issuer) { wstage_init(stage_at(0), UPW); if (a.nstages == 2) wstage_init(stage_at(1), UPW); }
     // What may be read ahead of the programmatic-launch wait: data written two or more kernels back
     // (every kernel releases its dependents only after its own wait).  For the down kernel that
-    // covers the router's lists, so its weights stream into shared memory while gate/up still
-    // computes; for gate/up (which follows the router directly) only the shared expert's do.
-    const bool early = DOWN || shared;
-    if (!early) { pdl_wait(); pdl_launch_dependents(); }
+    // covers the router's lists, so its first weights stream into shared memory while gate/up still
+    // computes; gate/up follows the router directly, so only the shared expert's weights qualify,
+    // and which CTA row takes the shared expert is known ahead of the lists only at batch 1.
+    const bool early_shared = !DOWN && a.M == 1 && (int)gridDim.y == a.topk + 1 && blockIdx.y == gridDim.y - 1;
+    if (early_shared && issuer) issue((int)gridDim.y - 1, (int)gridDim.y - 1, 0);
+    if (!DOWN) { pdl_wait(); pdl_launch_dependents(); }
     const int n_active = *a.lists.n_active;
-    const bool active = shared || slot < n_active;
-    const int e = (shared || !active) ? 0 : a.lists.slot_expert[slot];
-    if (active && threadIdx.x == 480) {                    // last warp: it stages no activations at batch 1
-        const Q4R& q = DOWN ? (shared ? a.sh_down : a.down) : (shared ? a.sh_gu : a.gu);
-        wstage_issue(ws, q.wr, q.sr, ((size_t)e * ntiles + (size_t)blockIdx.x * TPC) << lg, nvu, UPW);
-    }
-    if (early) { pdl_wait(); pdl_launch_dependents(); }
-    if (active) {
-        const int cnt = shared ? (a.M_shared >= 0 ? a.M_shared : a.M) : a.lists.slot_cnt[slot];
-        const int off = shared ? 0 : a.lists.slot_off[slot];
+    const int total = n_active + 1;
+    if (!early_shared && (int)blockIdx.y < total && issuer) issue(blockIdx.y, n_active, 0);
+    if (DOWN) { pdl_wait(); pdl_launch_dependents(); }
+    int it = 0;
+    for (int j = blockIdx.y; j < total; j += gridDim.y, ++it) {
+        const int stage = (a.nstages == 2) ? (it & 1) : 0;
+        const uint32_t parity = (a.nstages == 2) ? ((it >> 1) & 1) : (it & 1);
+        if (issuer) {
+            // every warp left the previous iteration through a barrier, so its stage may be refilled
+            if (a.nstages == 2) { if (j + (int)gridDim.y < total) issue(j + gridDim.y, n_active, stage ^ 1); }
+            else if (it > 0) issue(j, n_active, 0);
+        }
+        const WStage wsc = stage_at(stage);
+        const bool shared = (j == n_active);
+        const int cnt = shared ? (a.M_shared >= 0 ? a.M_shared : a.M) : a.lists.slot_cnt[j];
+        const int off = shared ? 0 : a.lists.slot_off[j];
         for (int c0 = 0; c0 < cnt; c0 += ROWS_PER_PASS) {
             const int mr = min(ROWS_PER_PASS, cnt - c0);
             if (threadIdx.x < ROWS_PER_PASS) {
@@ -710,9 +740,9 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
             for (int i = 0; i < UPW; ++i) {
                 const int u = warp + 16 * i;
                 if (u < nvu) {
-                    if (c0 == 0 && !mbar_wait_bounded(ws.bar + i, 0) && a.err && lane == 0) atomicOr(a.err, 1u);
+                    if (c0 == 0 && !mbar_wait_bounded(wsc.bar + i, parity) && a.err && lane == 0) atomicOr(a.err, 1u);
                     SliceRegs rg;
-                    load_slice_smem(rg, ws.w + (size_t)u * 128, ws.s + (size_t)u * 16, lane);
+                    load_slice_smem(rg, wsc.w + (size_t)u * 128, wsc.s + (size_t)u * 16, lane);
                     float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
                     compute_slice_x(rg, xr, accS, accB);
                     finish_acc4(accS, accB, t, v);
@@ -728,8 +758,8 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
                     if (tile2 < ntiles && col < mr) a.dbuf[(size_t)misc[8 + col] * a.H + tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, col));
                 }
             } else {
-                for (int j = threadIdx.x; j < TPC * 64; j += blockDim.x) {
-                    int tl2 = j >> 6, col = (j >> 3) & 7, i = j & 7, tile2 = blockIdx.x * TPC + tl2;
+                for (int j2 = threadIdx.x; j2 < TPC * 64; j2 += blockDim.x) {
+                    int tl2 = j2 >> 6, col = (j2 >> 3) & 7, i = j2 & 7, tile2 = blockIdx.x * TPC + tl2;
                     if (tile2 < ntiles && col < mr) {
                         __half g = f2h(tile_value(fin + tl2 * 128, i, col)), u = f2h(tile_value(fin + tl2 * 128, i + 8, col));
                         a.hbuf[(size_t)misc[8 + col] * a.I + tile2 * 8 + i] = swiglu_h(g, u);
@@ -738,45 +768,49 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
             }
             __syncthreads();
         }
-    }
-    if (!DOWN || !active || a.tile_counter == nullptr) return;
-    // The CTA that finishes last for this group of output tiles combines them for every row:
-    // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit)
-    // * shared (:474-484), + residual (SeedlessMetalForward.swift:1024-1028).
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned ticket = atomicAdd(a.tile_counter + blockIdx.x, 1u);
-        misc[0] = (ticket == (unsigned)n_active) ? 1 : 0;            // n_active routed slots + the shared expert
-    }
-    __syncthreads();
-    if (!misc[0]) return;
-    __threadfence();
-    if (threadIdx.x == 0) a.tile_counter[blockIdx.x] = 0u;
-    const int ncols = min(TPC * 16, a.H - blockIdx.x * TPC * 16);
-    for (int i = threadIdx.x; i < a.M * ncols; i += blockDim.x) {
-        int m = i / ncols, n = blockIdx.x * TPC * 16 + (i - m * ncols);
-        __half acc = f2h(0.0f);
-        for (int k = 0; k < a.topk; ++k)
-            acc = hadd_rn(acc, hmul_rn(__ldcg(a.dbuf + (size_t)(m * a.topk + k) * a.H + n), a.scores[m * a.topk + k]));
-        __half res = hadd_rn(acc, hmul_rn(sigmoid_h(a.sgl[m]), __ldcg(a.dbuf + (size_t)(npair + m) * a.H + n)));
-        if (a.resid) a.resid[(size_t)m * a.H + n] = hadd_rn(a.resid[(size_t)m * a.H + n], res);
-        else a.out[(size_t)m * a.H + n] = res;
+        if (!DOWN || a.tile_counter == nullptr) continue;
+        // The CTA that finishes last for this group of output tiles combines them for every row:
+        // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit)
+        // * shared (:474-484), + residual (SeedlessMetalForward.swift:1024-1028).
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            unsigned ticket = atomicAdd(a.tile_counter + blockIdx.x, 1u);
+            misc[16] = (ticket == (unsigned)n_active) ? 1 : 0;           // n_active routed slots + the shared expert
+        }
+        __syncthreads();
+        if (!misc[16]) continue;
+        __threadfence();
+        if (threadIdx.x == 0) a.tile_counter[blockIdx.x] = 0u;
+        const int ncols = min(TPC * 16, a.H - blockIdx.x * TPC * 16);
+        for (int i = threadIdx.x; i < a.M * ncols; i += blockDim.x) {
+            int m = i / ncols, n = blockIdx.x * TPC * 16 + (i - m * ncols);
+            __half acc = f2h(0.0f);
+            for (int k = 0; k < a.topk; ++k)
+                acc = hadd_rn(acc, hmul_rn(__ldcg(a.dbuf + (size_t)(m * a.topk + k) * a.H + n), a.scores[m * a.topk + k]));
+            __half res = hadd_rn(acc, hmul_rn(sigmoid_h(a.sgl[m]), __ldcg(a.dbuf + (size_t)(npair + m) * a.H + n)));
+            if (a.resid) a.resid[(size_t)m * a.H + n] = hadd_rn(a.resid[(size_t)m * a.H + n], res);
+            else a.out[(size_t)m * a.H + n] = res;
+        }
     }
 }
 template <bool DOWN, int UPW>
 static void launch_expert_t(const ExpertArgs& a, const GemvPlan& pl, int nslots, cudaStream_t st, bool pdl) {
     int K = DOWN ? a.I : a.H;
-    size_t smem = GemvSmem::wstage_bytes(16 * UPW) + GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, K, 16 * UPW, pl.tpc);
-    static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_expert<DOWN, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
     int ntiles = DOWN ? a.H / 16 : a.I / 8;
+    const int gx = (ntiles + pl.tpc - 1) / pl.tpc;
+    int gy = 148 / gx; if (gy < 1) gy = 1;
+    if (gy > nslots + 1) gy = nslots + 1;                   // one CTA row per slot at batch 1; fewer rows than slots: CTAs walk them
+    const int nstages = (gy < nslots + 1) ? 2 : 1;
+    size_t smem = nstages * GemvSmem::wstage_bytes(16 * UPW) + GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, K, 16 * UPW, pl.tpc);
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_expert<DOWN, UPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024); configured = true; }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((ntiles + pl.tpc - 1) / pl.tpc), (unsigned)(nslots + 1));
+    cfg.gridDim = dim3((unsigned)gx, (unsigned)gy);
     cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     set_pdl(cfg, attr, pdl);
-    ExpertArgs copy = a; copy.lg_slices = pl.lg_slices;
+    ExpertArgs copy = a; copy.lg_slices = pl.lg_slices; copy.nstages = nstages;
     ProfScope ps(DOWN ? "k_expert_down" : "k_expert_gateup", 0.0, st);
     cudaLaunchKernelEx(&cfg, k_expert<DOWN, UPW>, copy);
     COUNT_LAUNCH();

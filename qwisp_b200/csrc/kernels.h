@@ -54,6 +54,7 @@ struct ExpertArgs {
     __half* hbuf;                        // [(M*topk + M)][I]
     __half* dbuf;                        // [(M*topk + M)][H]
     int M, H, I, topk;
+    int nstages = 1;                     // weight stages per CTA (2: a CTA walks several expert slots, filled by the launcher)
     int M_shared = -1;                   // rows the shared expert runs on (-1: all M) and where they start in p:
     int shared_row0 = 0;                 // expert-parallel calls see every rank's rows in p but own only some
     const __half* scores; const __half* sgl;   // combine inputs (down kernel)
