@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1) k_gemv(DenseArgs a) 
     // load/store queue.  Dependents are released only after the wait, so whatever a dependent
     // reads ahead of its own wait was written by a kernel that is complete.
     if (threadIdx.x == (NW - 1) * 32) wstage_issue(ws, a.q.wr, a.q.sr, (size_t)blockIdx.x * TPC << lg, nvu, ROUNDS);   // last warp: least staging work
-    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
+    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps, a.cmb};
     StageRegs sregs;
     stage_issue_const<PRO>(sregs, src, mr, a.K);
     pdl_wait();
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
     pdl_wait();
     pdl_launch_dependents();
     if (PRO == PRO_PLAIN) stage_plain(st, a.x, a.ldx, row0, mr, a.K);
-    else stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K);
+    else stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K, a.cmb);
     __syncthreads();
     // lane (r, t) sees weight rows r and r+8 of each tile for pass-rows (MMA columns) 2t and 2t+1
     float best[2] = {-INFINITY, -INFINITY}; int besti[2] = {0x7fffffff, 0x7fffffff};
@@ -768,7 +768,7 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
             }
             __syncthreads();
         }
-        if (!DOWN || a.tile_counter == nullptr) continue;
+        if (!DOWN || a.tile_counter == nullptr || a.defer_combine) continue;
         // The CTA that finishes last for this group of output tiles combines them for every row:
         // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit)
         // * shared (:474-484), + residual (SeedlessMetalForward.swift:1024-1028).
@@ -815,6 +815,170 @@ static void launch_expert_t(const ExpertArgs& a, const GemvPlan& pl, int nslots,
     cudaLaunchKernelEx(&cfg, k_expert<DOWN, UPW>, copy);
     COUNT_LAUNCH();
 }
+// ---- batch-1 decode: gate/up + SwiGLU and down + combine of all slots in one launch ----
+// grid (G, top_k + 1): CTA (x, y) computes output-tile group x of slot y in both phases (the two
+// phases have the same number of tile groups).  Between the phases the 16 CTAs of a slot meet at a
+// counter (all CTAs of the grid are resident: one per SM, and dependents are released only after
+// every CTA has started), so the down phase reads the slot's complete SwiGLU row.  Both phases'
+// weights are requested at the start, so the down weights arrive while gate/up computes.  The wait
+// is bounded: after ~4M polls the CTA records the failure and goes on.
+template <int UG, int UD>
+__global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, t = lane & 3;
+    const int lg1 = a.lg_slices, lg2 = a.lg_slices2;
+    const int sl1 = a.H >> 8, sl2 = a.I >> 8;
+    const int TPC1 = (16 * UG) >> lg1, TPC2 = (16 * UD) >> lg2;
+    const int nt1 = a.I / 8, nt2 = a.H / 16;
+    const int npair = a.topk;                                  // one row
+    WStage ws1, ws2; XStage st; float* red; float* fin; int* misc;
+    unsigned char* p = GemvSmem::carve_w(smem, 16 * UG, ws1);
+    p = GemvSmem::carve_w(p, 16 * UD, ws2);
+    constexpr int UM = UG > UD ? UG : UD;
+    GemvSmem::carve(p, 1, a.H > a.I ? a.H : a.I, 16 * UM, TPC1 > TPC2 ? TPC1 : TPC2, st, red, fin, misc);
+    const int nvu1 = min(TPC1, nt1 - (int)blockIdx.x * TPC1) << lg1, nvu2 = min(TPC2, nt2 - (int)blockIdx.x * TPC2) << lg2;
+    const bool issuer = (threadIdx.x == 480);
+    const int y = blockIdx.y;
+    auto issue = [&](bool sh, int e) {
+        const Q4R& q1 = sh ? a.sh_gu : a.gu; const Q4R& q2 = sh ? a.sh_down : a.down;
+        wstage_copy(ws1, q1.wr, q1.sr, ((size_t)e * nt1 + (size_t)blockIdx.x * TPC1) << lg1, nvu1, UG);
+        wstage_copy(ws2, q2.wr, q2.sr, ((size_t)e * nt2 + (size_t)blockIdx.x * TPC2) << lg2, nvu2, UD);
+    };
+    if (issuer) { wstage_init(ws1, UG); wstage_init(ws2, UD); }
+    const bool shared = (y == (int)gridDim.y - 1);             // one row: its top_k experts are distinct, slot k = k-th choice
+    if (shared && issuer) issue(true, 0);
+    pdl_wait();
+    pdl_launch_dependents();
+    if (!shared && issuer) issue(false, a.lists.slot_expert[y]);
+    const int dst = shared ? npair : y;                        // row of hbuf / dbuf (pair id k, or top_k for the shared expert)
+    // ---- phase 1: gate/up + SwiGLU -> hbuf[dst] ----
+    {
+        if (threadIdx.x == 0) { misc[0] = a.shared_row0; misc[8] = dst; }
+        __syncthreads();
+        StageSrc src{a.p, a.H, misc, nullptr, nullptr, 0, 0.f};
+        StageRegs sregs;
+        stage_issue<PRO_PLAIN>(sregs, src, 0, 1, a.H);
+        stage_finish<PRO_PLAIN>(sregs, st, src, 0, 1, a.H);
+        __syncthreads();
+        XRegs xr;
+        load_xregs(xr, st, warp & (sl1 - 1), r, t, 1);
+#pragma unroll 1
+        for (int i = 0; i < UG; ++i) {
+            const int u = warp + 16 * i;
+            if (u < nvu1) {
+                if (!mbar_wait_bounded(ws1.bar + i, 0) && a.err && lane == 0) atomicOr(a.err, 1u);
+                SliceRegs rg;
+                load_slice_smem(rg, ws1.w + (size_t)u * 128, ws1.s + (size_t)u * 16, lane);
+                float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+                compute_slice_x(rg, xr, accS, accB);
+                finish_acc4(accS, accB, t, v);
+                store_partial(red, u, lane, v);
+            }
+        }
+        __syncthreads();
+        reduce_tiles(red, fin, nvu1 >> lg1, sl1);
+        __syncthreads();
+        for (int j2 = threadIdx.x; j2 < TPC1 * 8; j2 += blockDim.x) {
+            int tl2 = j2 >> 3, i = j2 & 7, tile2 = blockIdx.x * TPC1 + tl2;
+            if (tile2 < nt1) {
+                __half g = f2h(tile_value(fin + tl2 * 128, i, 0)), u = f2h(tile_value(fin + tl2 * 128, i + 8, 0));
+                a.hbuf[(size_t)dst * a.I + tile2 * 8 + i] = swiglu_h(g, u);
+            }
+        }
+    }
+    // ---- the CTAs of this slot meet: every tile group's part of the SwiGLU row is in hbuf ----
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* arrive = a.slot_sync + y;
+        unsigned* leave = a.slot_sync + gridDim.y + y;
+        atomicAdd(arrive, 1u);
+        bool ok = false;
+        for (int spin = 0; spin < (1 << 22); ++spin) {
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(arrive) : "memory");
+            if (v >= gridDim.x) { ok = true; break; }
+        }
+        if (!ok && a.err) atomicOr(a.err, 2u);
+        // the last one to leave puts both counters back to zero for the next launch
+        if (atomicAdd(leave, 1u) == gridDim.x - 1) { *arrive = 0u; *leave = 0u; }
+    }
+    __syncthreads();
+    // ---- phase 2: down -> dbuf[dst], then the last CTA of the tile group combines ----
+    {
+        if (threadIdx.x == 0) { misc[0] = dst; }
+        __syncthreads();
+        StageSrc src{a.hbuf, a.I, misc, nullptr, nullptr, 0, 0.f};
+        StageRegs sregs;
+        stage_issue<PRO_PLAIN>(sregs, src, 0, 1, a.I);
+        stage_finish<PRO_PLAIN>(sregs, st, src, 0, 1, a.I);
+        __syncthreads();
+        XRegs xr;
+        load_xregs(xr, st, warp & (sl2 - 1), r, t, 1);
+#pragma unroll 1
+        for (int i = 0; i < UD; ++i) {
+            const int u = warp + 16 * i;
+            if (u < nvu2) {
+                if (!mbar_wait_bounded(ws2.bar + i, 0) && a.err && lane == 0) atomicOr(a.err, 1u);
+                SliceRegs rg;
+                load_slice_smem(rg, ws2.w + (size_t)u * 128, ws2.s + (size_t)u * 16, lane);
+                float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
+                compute_slice_x(rg, xr, accS, accB);
+                finish_acc4(accS, accB, t, v);
+                store_partial(red, u, lane, v);
+            }
+        }
+        __syncthreads();
+        reduce_tiles(red, fin, nvu2 >> lg2, sl2);
+        __syncthreads();
+        for (int i = threadIdx.x; i < TPC2 * 16; i += blockDim.x) {
+            int tl2 = i >> 4, row = i & 15, tile2 = blockIdx.x * TPC2 + tl2;
+            if (tile2 < nt2) a.dbuf[(size_t)dst * a.H + tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, 0));
+        }
+    }
+    if (a.defer_combine) return;                             // the consumer of the row folds the combine into its prologue
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned ticket = atomicAdd(a.tile_counter + blockIdx.x, 1u);
+        misc[16] = (ticket == gridDim.y - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!misc[16]) return;
+    __threadfence();
+    if (threadIdx.x == 0) a.tile_counter[blockIdx.x] = 0u;
+    const int ncols = min(TPC2 * 16, a.H - (int)blockIdx.x * TPC2 * 16);
+    for (int i = threadIdx.x; i < ncols; i += blockDim.x) {
+        const int n = blockIdx.x * TPC2 * 16 + i;
+        __half acc = f2h(0.0f);
+        for (int k = 0; k < a.topk; ++k) acc = hadd_rn(acc, hmul_rn(__ldcg(a.dbuf + (size_t)k * a.H + n), a.scores[k]));
+        __half res = hadd_rn(acc, hmul_rn(sigmoid_h(a.sgl[0]), __ldcg(a.dbuf + (size_t)npair * a.H + n)));
+        if (a.resid) a.resid[n] = hadd_rn(a.resid[n], res);
+        else a.out[n] = res;
+    }
+}
+bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
+    if (a.M != 1 || a.slot_sync == nullptr || (a.tile_counter == nullptr && !a.defer_combine)) return false;
+    const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1);
+    const int g1 = (a.I / 8 + p1.tpc - 1) / p1.tpc, g2 = (a.H / 16 + p2.tpc - 1) / p2.tpc;
+    if (g1 != g2 || p1.upw != 2 || p2.upw != 1) return false;            // the 2048 -> 512 -> 2048 expert shape
+    if (g1 * (a.topk + 1) > 148) return false;                           // every CTA must be resident at once
+    size_t smem = GemvSmem::wstage_bytes(32) + GemvSmem::wstage_bytes(16) + GemvSmem::bytes(1, a.H > a.I ? a.H : a.I, 32, p1.tpc > p2.tpc ? p1.tpc : p2.tpc);
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_expert_fused<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)g1, (unsigned)(a.topk + 1));
+    cfg.blockDim = dim3(512); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    set_pdl(cfg, attr, pdl);
+    ExpertArgs copy = a; copy.lg_slices = p1.lg_slices; copy.lg_slices2 = p2.lg_slices;
+    ProfScope ps("k_expert_fused", 0.0, st);
+    cudaLaunchKernelEx(&cfg, k_expert_fused<2, 1>, copy);
+    COUNT_LAUNCH();
+    return true;
+}
+
 // the plan is sized for the batch-1 case (top_k routed experts + the shared one share a wave); the
 // combine in the down kernel works on groups of TPC tiles, so tile_counter needs H/16/TPC entries
 template <bool DOWN>

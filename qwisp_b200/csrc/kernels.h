@@ -9,6 +9,7 @@ struct Q4W { const uint32_t* w = nullptr; const __half* s = nullptr; const __hal
 struct DenseArgs {
     int lg_slices = 0;                   // log2(K/256), filled by the launcher
     unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
+    CombineSrc cmb;                      // pending MoE combine to fold into the RMSNorm prologue (one row), or empty
     __half* norm_scratch = nullptr;      // [M][K] scratch for the many-row path (normed rows); nullptr keeps the GEMV path
     Q4R q;                                                       // repacked weights (tiles of 16 rows)
     int N, K, M;                                                 // N outputs (= 16 * tiles)
@@ -54,6 +55,9 @@ struct ExpertArgs {
     __half* hbuf;                        // [(M*topk + M)][I]
     __half* dbuf;                        // [(M*topk + M)][H]
     int M, H, I, topk;
+    int lg_slices2 = 0;                  // fused kernel: log2(I/256) of the down phase
+    unsigned* slot_sync = nullptr;       // fused kernel: [2][top_k + 1] counters, zero between launches
+    int defer_combine = 0;               // 1: leave the weighted combine + residual to the consumer of the row (CombineSrc)
     int nstages = 1;                     // weight stages per CTA (2: a CTA walks several expert slots, filled by the launcher)
     int M_shared = -1;                   // rows the shared expert runs on (-1: all M) and where they start in p:
     int shared_row0 = 0;                 // expert-parallel calls see every rank's rows in p but own only some
@@ -107,6 +111,8 @@ void launch_embed(const __half* embed, const int* tokens, int M, int H, int voca
 void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl);
 void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
 void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
+// batch-1 decode: gate/up and down in ONE launch (a per-slot barrier between the phases); false if the shapes do not fit it
+bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl);
 // expert-parallel helpers: group the (row, k) pairs of `npairs/topk` rows whose expert lies in [e0, e1)
 void launch_build_lists(const int* inds, int npairs, int e0, int e1, MoeLists lists, cudaStream_t st);
 // out/resid[m] (+)= sum_k fp16(d[pair0 + m*topk + k] * score[m,k]) (ascending k) + sigmoid(sgl[m]) * d[shared0 + m]
