@@ -64,9 +64,6 @@ struct sl_engine {
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
     unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; int* samp_buf = nullptr; unsigned* slot_sync = nullptr;
-    bool use_defer = false;         // one-row decode: fold the MoE combine into the next consumer's prologue (SEEDLESS_DEFER_COMBINE=1);
-                                    // measured equal to the combine in the expert kernel's last CTAs, so off by default
-    __half* h2 = nullptr;           // second residual-stream buffer for that
     bool use_fused_experts = true;  // batch-1 decode: gate/up + down in one launch (SEEDLESS_FUSED_EXPERTS=0 turns it off)
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
     int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
@@ -299,7 +296,6 @@ int32_t build_runtime(sl_engine* e) {
     CU(e, cudaMemset(e->tile_counters, 0, (size_t)(H / 16) * sizeof(unsigned)));
     CU(e, cudaMemset(e->counters, 0, 8 * sizeof(unsigned)));
     if ((rc = dalloc(e, &e->samp_buf, (size_t)4 * R))) return rc;
-    if ((rc = dalloc(e, &e->h2, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->slot_sync, (size_t)64))) return rc;
     CU(e, cudaMemset(e->slot_sync, 0, 64 * sizeof(unsigned)));
     if ((rc = dalloc(e, &e->err_flag, (size_t)4))) return rc;
@@ -331,7 +327,6 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->kv_pool, (size_t)c.kv_pages * page_elems))) return rc;
     for (int i = c.kv_pages - 1; i >= 0; --i) e->free_pages.push_back(i);
     for (int i = S - 1; i >= 0; --i) e->free_slots.push_back(i);
-    { const char* de = getenv("SEEDLESS_DEFER_COMBINE"); if (de) e->use_defer = (de[0] == '1'); }
     { const char* fe = getenv("SEEDLESS_FUSED_EXPERTS"); if (fe) e->use_fused_experts = (fe[0] == '1'); }
     const char* pfe = getenv("SEEDLESS_PREFETCH");
     if (pfe) e->use_prefetch = (pfe[0] == '1');
@@ -486,8 +481,7 @@ int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __ha
 }
 
 // next: the layer after L (nullptr after the last one, where the lm_head follows)
-void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half* rows, int ld, bool apply_norm, int M, __half* resid, __half* plain_out,
-                 bool defer_combine = false) {
+void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half* rows, int ld, bool apply_norm, int M, __half* resid, __half* plain_out) {
     cudaStream_t st = e->stream;
     RouterArgs ra{}; ra.h = rows; ra.ldh = ld; ra.norm_w = apply_norm ? L.post_norm : nullptr; ra.eps = e->cfg.rms_eps;
     ra.router = L.router; ra.shared_gate = L.shared_gate; ra.M = M; ra.H = e->H; ra.E = e->E;
@@ -501,7 +495,6 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     if (e->use_prefetch) { if (next) pf_q4(ea.pf, 0, next->r_in); else pf_q4(ea.pf, 0, e->r_lm_head, (size_t)24 << 20); }
     int nslots = M * e->topk < e->E ? M * e->topk : e->E;
     ea.slot_sync = e->slot_sync;
-    ea.defer_combine = defer_combine ? 1 : 0;
     if (e->use_fused_experts && launch_expert_fused(ea, st, e->use_pdl)) return;      // batch-1 decode: one launch
     launch_expert_gateup(e->exact, ea, nslots, st, e->use_pdl);
     launch_expert_down(e->exact, ea, nslots, st, e->use_pdl);
@@ -509,12 +502,11 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
 
 // mixer of one layer: input rows are normed inside (norm_w != nullptr) or already normed
 void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __half* norm_w, int M, int nsegs,
-                   __half* resid, __half* plain_out, const int* row_pos_override, const CombineSrc* cmb = nullptr) {
+                   __half* resid, __half* plain_out, const int* row_pos_override) {
     cudaStream_t st = e->stream;
     const sl_config& c = e->cfg;
     DenseArgs d{}; d.err = e->err_flag; d.norm_scratch = e->normed; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
     d.x = rows; d.ldx = e->H; d.nw = norm_w; d.eps = c.rms_eps; d.y = e->inproj; d.ldy = (int)L.in_proj.N;
-    if (cmb) d.cmb = *cmb;
     if (e->use_prefetch) pf_q4(d.pf, 0, L.r_out);
     launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, e->exact, d, st, e->use_pdl);
     DenseArgs o{};
@@ -550,33 +542,16 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
 void enqueue_step(sl_engine* e, int M, int nsegs, HeadMode head, bool want_logits) {
     cudaStream_t st = e->stream;
     launch_embed(e->embed, e->tok_in, M, e->H, e->V, e->h, st);
-    // One-row decode steps leave each MoE block's weighted combine + residual to the next consumer of the
-    // row (the next layer's in-projection, at the end the lm_head): its last-CTA tail was ~3 us of every
-    // layer's critical path.  The consumer writes the combined row to the OTHER stream buffer (other CTAs
-    // still read the old one), so the residual stream alternates between e->h and e->h2.
-    const bool defer = e->use_defer && M == 1 && head == HEAD_ARGMAX && !e->ep_step && e->use_fused_experts;
-    __half* strm = e->h;
-    bool pending = false;
-    CombineSrc cmb; cmb.dbuf = e->dbuf; cmb.scores = e->scores; cmb.sgl = e->sgl; cmb.topk = e->topk;
     for (size_t li = 0; li < e->layers.size(); ++li) {
         const LayerW& L = e->layers[li];
-        if (pending) {
-            __half* other = (strm == e->h) ? e->h2 : e->h;
-            cmb.h_out = other;
-            enqueue_mixer(e, L, strm, L.in_norm, M, nsegs, other, nullptr, nullptr, &cmb);
-            strm = other;
-        } else {
-            enqueue_mixer(e, L, strm, L.in_norm, M, nsegs, strm, nullptr, nullptr);
-        }
-        enqueue_moe(e, L, li + 1 < e->layers.size() ? &e->layers[li + 1] : nullptr, strm, e->H, true, M, strm, nullptr, defer);
-        pending = defer;
+        enqueue_mixer(e, L, e->h, L.in_norm, M, nsegs, e->h, nullptr, nullptr);
+        enqueue_moe(e, L, li + 1 < e->layers.size() ? &e->layers[li + 1] : nullptr, e->h, e->H, true, M, e->h, nullptr);
     }
     if (head == HEAD_NORMED) {
         launch_final_norm(e->h, e->final_norm, e->cfg.rms_eps, M, e->H, e->normed, st);
     } else if (head == HEAD_ARGMAX || head == HEAD_LOGITS) {
         DenseArgs d{}; d.q = e->r_lm_head; d.N = e->V; d.K = e->H; d.M = M;
-        d.x = strm; d.ldx = e->H; d.nw = e->final_norm; d.eps = e->cfg.rms_eps;
-        if (pending) { cmb.h_out = nullptr; d.cmb = cmb; }
+        d.x = e->h; d.ldx = e->H; d.nw = e->final_norm; d.eps = e->cfg.rms_eps;
         d.logits = want_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
         launch_dense(PRO_RMSNORM, EPI_ARGMAX, e->exact, d, st, e->use_pdl);
     }

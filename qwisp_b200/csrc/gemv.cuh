@@ -72,25 +72,12 @@ __device__ __forceinline__ void store_staged(const XStage& st, int col, int k0, 
 // The first two units of a warp are requested by stage_issue and held in registers, so a kernel
 // can put those loads in flight early and do other set-up before it needs them; further units
 // (more than two rows, or K = 4096 with two) are loaded where they are used.
-// A pending MoE combine folded into the consumer's prologue (one row): the activation row is
-//   h + [ sum_k fp16(d_k * score_k) in ascending k  +  sigmoid(gate logit) * d_shared ]
-// with exactly the fp16 operations the expert kernels' own combine performs
-// (SeedlessFusedVerify.swift:462-484, SeedlessMetalForward.swift:1024-1028), so the row is bit-identical;
-// CTA 0 also stores it to h_out, the residual stream the following kernels read and add to.
-struct CombineSrc {
-    const __half* dbuf = nullptr;    // [top_k + 1][width]: the routed experts' outputs in k order, then the shared expert's
-    const __half* scores = nullptr;  // [top_k]
-    const __half* sgl = nullptr;     // [1] shared-gate logit
-    int topk = 0;
-    __half* h_out = nullptr;
-};
 struct StageSrc {
     const __half* x; int ldx;        // rows (plain) / residual stream (rmsnorm) / y (normgate)
     const int* rows;                 // optional row list (shared memory), else rows row0, row0+1, ...
     const __half* nw;                // norm weight
     const __half* z; int ldz;        // gate input of the gated norm
     float eps;
-    CombineSrc cmb;
 };
 struct StageRegs { uint4 a[2], b[2], c[2]; };   // activations, norm weights, gate inputs of the first two units
 
@@ -114,35 +101,6 @@ __device__ __forceinline__ void stage_issue_const(StageRegs& sr, const StageSrc&
         }
     }
 }
-// fp16 add / multiply of two fp16 numbers through f32 round to the same result as the native half
-// instructions (24 >= 2*11 + 2 bits: the double rounding is innocuous), so half2 arithmetic is used here
-__device__ __forceinline__ uint4 combine_row8(const StageSrc& s, int K, int k0, uint4 hv) {
-    const CombineSrc& c = s.cmb;
-    __half2 acc[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] = __floats2half2_rn(0.f, 0.f);
-    uint4 d[16];
-#pragma unroll
-    for (int k = 0; k < 16; ++k) if (k < c.topk) d[k] = __ldcg(reinterpret_cast<const uint4*>(c.dbuf + (size_t)k * K + k0));
-    const uint4 dsh = __ldcg(reinterpret_cast<const uint4*>(c.dbuf + (size_t)c.topk * K + k0));
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-        if (k < c.topk) {
-            const __half2 sc = __half2half2(c.scores[k]);
-            const __half2* dh = reinterpret_cast<const __half2*>(&d[k]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[i] = __hadd2_rn(acc[i], __hmul2_rn(dh[i], sc));   // _rn: never contracted into an fma
-        }
-    }
-    const __half2 sg = __half2half2(sigmoid_h(c.sgl[0]));
-    const __half2* sh = reinterpret_cast<const __half2*>(&dsh);
-    const __half2* hh = reinterpret_cast<const __half2*>(&hv);
-    uint4 o; __half2* oh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) oh[i] = __hadd2_rn(hh[i], __hadd2_rn(acc[i], __hmul2_rn(sg, sh[i])));
-    if (c.h_out && blockIdx.x == 0 && blockIdx.y == 0) *reinterpret_cast<uint4*>(c.h_out + k0) = o;
-    return o;
-}
 template <int PRO>
 __device__ __forceinline__ void stage_issue(StageRegs& sr, const StageSrc& s, int row0, int mr, int K) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -153,7 +111,6 @@ __device__ __forceinline__ void stage_issue(StageRegs& sr, const StageSrc& s, in
         if (u < units) {
             const int col = u >> lgc, k0 = ((u & ((1 << lgc) - 1)) << 8) + lane * 8;
             sr.a[j] = stage_load(s, row0, col, k0);
-            if (PRO == PRO_RMSNORM && s.cmb.dbuf) sr.a[j] = combine_row8(s, K, k0, sr.a[j]);       // one row only
             if (PRO == PRO_NORMGATE) {
                 const int row = s.rows ? s.rows[col] : row0 + col;
                 sr.c[j] = __ldcg(reinterpret_cast<const uint4*>(s.z + (size_t)row * s.ldz + k0));
@@ -234,8 +191,8 @@ __device__ __forceinline__ void stage_plain(const XStage& st, const __half* x, i
     StageRegs sr; stage_issue<PRO_PLAIN>(sr, s, row0, mr, K); stage_finish<PRO_PLAIN>(sr, st, s, row0, mr, K);
 }
 __device__ __forceinline__ void stage_rmsnorm(const XStage& st, const __half* h, int ldh, const __half* w, float eps,
-                                              int row0, int mr, int K, const CombineSrc& cmb = CombineSrc()) {
-    StageSrc s{h, ldh, nullptr, w, nullptr, 0, eps, cmb};
+                                              int row0, int mr, int K) {
+    StageSrc s{h, ldh, nullptr, w, nullptr, 0, eps};
     StageRegs sr; stage_issue_const<PRO_RMSNORM>(sr, s, mr, K); stage_issue<PRO_RMSNORM>(sr, s, row0, mr, K); stage_finish<PRO_RMSNORM>(sr, st, s, row0, mr, K);
 }
 

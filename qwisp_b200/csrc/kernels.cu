@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1) k_gemv(DenseArgs a) 
     // load/store queue.  Dependents are released only after the wait, so whatever a dependent
     // reads ahead of its own wait was written by a kernel that is complete.
     if (threadIdx.x == (NW - 1) * 32) wstage_issue(ws, a.q.wr, a.q.sr, (size_t)blockIdx.x * TPC << lg, nvu, ROUNDS);   // last warp: least staging work
-    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps, a.cmb};
+    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
     StageRegs sregs;
     stage_issue_const<PRO>(sregs, src, mr, a.K);
     pdl_wait();
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
     pdl_wait();
     pdl_launch_dependents();
     if (PRO == PRO_PLAIN) stage_plain(st, a.x, a.ldx, row0, mr, a.K);
-    else stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K, a.cmb);
+    else stage_rmsnorm(st, a.x, a.ldx, a.nw, a.eps, row0, mr, a.K);
     __syncthreads();
     // lane (r, t) sees weight rows r and r+8 of each tile for pass-rows (MMA columns) 2t and 2t+1
     float best[2] = {-INFINITY, -INFINITY}; int besti[2] = {0x7fffffff, 0x7fffffff};
@@ -258,7 +258,13 @@ static void launch_head_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_head<PRO, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
     int ntiles = a.N / 16;
-    int gx = (ntiles + 7) / 8; if (gx > 148 * 3) gx = 148 * 3;
+    // one wave of persistent CTAs: as many as are resident at once with this kernel's registers and shared memory
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_head<PRO, EXACT>, 256, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+        if (per_sm > 3) per_sm = 3;
+    }
+    int gx = (ntiles + 7) / 8; if (gx > 148 * per_sm) gx = 148 * per_sm;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)gx, (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS));
     cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
@@ -505,6 +511,9 @@ __device__ __noinline__ void route_row_warp(const __half* lrow, int E, int topk,
     __syncwarp();
 }
 
+// MULTI: several rows per call (one warp per row in the norm); the one-row instantiation leaves that code
+// out, so it does not compete for registers with the router rows held across the wait
+template <bool MULTI>
 __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __half* ps = reinterpret_cast<__half*>(smem);            // [8][H]
@@ -532,13 +541,13 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
         const int m0 = blockIdx.y * 8;
         int mr = min(8, a.M - m0);
         __syncthreads();
-        if (a.M == 1 || !a.norm_w || (a.H & 255)) {
+        if (!MULTI || a.M == 1 || !a.norm_w || (a.H & 255)) {
             for (int c = 0; c < mr; ++c) {
                 const __half* src = a.h + (size_t)(m0 + c) * a.ldh;
                 if (a.norm_w) block_rmsnorm_row(src, a.norm_w, a.eps, a.H, ps + c * a.H, sm8, m0 + c == 0, pv, pw);
                 else for (int k = threadIdx.x * 8; k < a.H; k += blockDim.x * 8) *reinterpret_cast<uint4*>(ps + c * a.H + k) = *reinterpret_cast<const uint4*>(src + k);
             }
-        } else if (warp < mr) {
+        } else if (MULTI && warp < mr) {
             // several rows: one warp per row, the eight rows of a pass side by side.  Same sums in the same
             // order as the block-wide form (per thread 8 elements, a butterfly per 256-chunk, chunks added
             // in ascending order), so the normed rows are identical bit for bit.
@@ -638,14 +647,19 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
 void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl) {
     size_t smem = (size_t)8 * a.H * 2 + 64;
     static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_moe_router, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); configured = true; }
+    if (!configured) {
+        cudaFuncSetAttribute(k_moe_router<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_moe_router<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        configured = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((a.E + 7) / 8 + 1), (unsigned)((a.M + 7) / 8)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute attr[1];
     set_pdl(cfg, attr, pdl);
     RouterArgs copy = a;
     ProfScope ps("k_moe_router", (double)(a.E + 1) * a.H * 2 + (double)a.M * a.H * 4, st);
-    cudaLaunchKernelEx(&cfg, k_moe_router, copy);
+    if (a.M == 1) cudaLaunchKernelEx(&cfg, k_moe_router<false>, copy);
+    else cudaLaunchKernelEx(&cfg, k_moe_router<true>, copy);
     COUNT_LAUNCH();
 }
 
@@ -768,7 +782,7 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
             }
             __syncthreads();
         }
-        if (!DOWN || a.tile_counter == nullptr || a.defer_combine) continue;
+        if (!DOWN || a.tile_counter == nullptr) continue;
         // The CTA that finishes last for this group of output tiles combines them for every row:
         // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit)
         // * shared (:474-484), + residual (SeedlessMetalForward.swift:1024-1028).
@@ -937,7 +951,6 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
             if (tile2 < nt2) a.dbuf[(size_t)dst * a.H + tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, 0));
         }
     }
-    if (a.defer_combine) return;                             // the consumer of the row folds the combine into its prologue
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -959,7 +972,7 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
     }
 }
 bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
-    if (a.M != 1 || a.slot_sync == nullptr || (a.tile_counter == nullptr && !a.defer_combine)) return false;
+    if (a.M != 1 || a.slot_sync == nullptr || a.tile_counter == nullptr) return false;
     const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1);
     const int g1 = (a.I / 8 + p1.tpc - 1) / p1.tpc, g2 = (a.H / 16 + p2.tpc - 1) / p2.tpc;
     if (g1 != g2 || p1.upw != 2 || p2.upw != 1) return false;            // the 2048 -> 512 -> 2048 expert shape

@@ -9,7 +9,6 @@ struct Q4W { const uint32_t* w = nullptr; const __half* s = nullptr; const __hal
 struct DenseArgs {
     int lg_slices = 0;                   // log2(K/256), filled by the launcher
     unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
-    CombineSrc cmb;                      // pending MoE combine to fold into the RMSNorm prologue (one row), or empty
     __half* norm_scratch = nullptr;      // [M][K] scratch for the many-row path (normed rows); nullptr keeps the GEMV path
     Q4R q;                                                       // repacked weights (tiles of 16 rows)
     int N, K, M;                                                 // N outputs (= 16 * tiles)
@@ -57,7 +56,6 @@ struct ExpertArgs {
     int M, H, I, topk;
     int lg_slices2 = 0;                  // fused kernel: log2(I/256) of the down phase
     unsigned* slot_sync = nullptr;       // fused kernel: [2][top_k + 1] counters, zero between launches
-    int defer_combine = 0;               // 1: leave the weighted combine + residual to the consumer of the row (CombineSrc)
     int nstages = 1;                     // weight stages per CTA (2: a CTA walks several expert slots, filled by the launcher)
     int M_shared = -1;                   // rows the shared expert runs on (-1: all M) and where they start in p:
     int shared_row0 = 0;                 // expert-parallel calls see every rank's rows in p but own only some
