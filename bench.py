@@ -359,7 +359,7 @@ def main():
         # step's 30 GDN in/out projections and 10 attention q-k-v / o projections, the attention
         # in-projection scaled from the GDN one by its rows)
         ncu_traffic = {"k_gemv": (30 * 14.27e6 + 10 * 14.27e6 * 9216 / 12288 + 30 * 4.78e6 + 10 * 4.76e6) / 80,
-                       "k_expert_gateup": 10.64e6, "k_expert_down": 5.36e6, "k_moe_router": 1.12e6, "k_gdn_core": 2.32e6 + 2.1e6}
+                       "k_expert_gateup": 10.64e6, "k_expert_down": 5.36e6, "k_expert_fused": 10.64e6 + 5.36e6, "k_moe_router": 1.12e6, "k_gdn_core": 2.32e6 + 2.1e6}
         roofline = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs,
                     "traffic": ncu_traffic.get(dom) if args.layers == 40 else None, "peak_source": peak_src,
                     "algorithmic_bytes_per_launch": by / n, "us_per_launch": us_in_step, "us_per_launch_eager_events": ms / n * 1e3}

@@ -986,7 +986,7 @@ bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
     cudaLaunchAttribute attr[1];
     set_pdl(cfg, attr, pdl);
     ExpertArgs copy = a; copy.lg_slices = p1.lg_slices; copy.lg_slices2 = p2.lg_slices;
-    ProfScope ps("k_expert_fused", 0.0, st);
+    ProfScope ps("k_expert_fused", (double)(a.topk + 1) * 3.0 * a.I * a.H * 0.5625 + (double)(a.topk + 2) * (a.H + a.I) * 2, st);
     cudaLaunchKernelEx(&cfg, k_expert_fused<2, 1>, copy);
     COUNT_LAUNCH();
     return true;
@@ -1361,6 +1361,42 @@ __device__ __forceinline__ uint4 norm_rope_head(const __half* src, const __half*
     }
     return o;
 }
+// cos / sin of the 32 rotation angles of one position, the same expressions norm_rope_head evaluates
+__device__ __forceinline__ void rope_table_entry(float theta, int pos, int i, float& cs, float& sn) {
+    const float lnb = logf(theta);
+    const float freq = expf(-2.0f * (float)i / (float)ROPE_D * lnb);
+    const float ang = (float)pos * freq;
+    sincosf(ang, &sn, &cs);
+}
+// norm_rope_head with the angles taken from a table (tab_cs / tab_sn [32]) instead of recomputed per lane
+__device__ __forceinline__ uint4 norm_rope_head_tab(const __half* src, const __half* w, float eps, const float* tab_cs, const float* tab_sn, int lane) {
+    uint4 v = reinterpret_cast<const uint4*>(src)[lane];
+    uint4 wv = reinterpret_cast<const uint4*>(w)[lane];
+    const __half* vh = reinterpret_cast<const __half*>(&v);
+    const __half* wh = reinterpret_cast<const __half*>(&wv);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { float f = h2f(vh[i]); ss = fmaf(f, f, ss); }
+    ss = warp_sum(ss);
+    float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), eps));
+    float nv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) nv[i] = h2f(hmul_rn(wh[i], f2h(__fmul_rn(h2f(vh[i]), inv))));
+    float other[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, nv[i], 4);
+    uint4 o; __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        int d = lane * 8 + i;
+        if (d >= ROPE_D) { oh[i] = f2h(nv[i]); continue; }
+        int ii = (d < 32) ? d : (d - 32);
+        const float cs = tab_cs[ii], sn = tab_sn[ii];
+        float x0 = (d < 32) ? nv[i] : other[i], x1 = (d < 32) ? other[i] : nv[i];
+        oh[i] = f2h((d < 32) ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs));
+    }
+    return o;
+}
 // grid (nsplit, KV heads, M), 256 threads, dynamic shared memory 8*8*256 floats.
 // prep != 0 (every row is the only row of its stream in this launch): each CTA norms and rotates its
 // 8 query heads itself, and the CTA whose key range holds the row's own position also makes that
@@ -1373,28 +1409,41 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
     __shared__ __align__(16) __half sq[ATT_G][ATT_D];
     __shared__ __align__(16) __half sk[ATT_D], sv[ATT_D];
     __shared__ int s_last;
+    __shared__ float s_cs[32], s_sn[32];
     const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    pdl_wait();
-    pdl_launch_dependents();
+    // Ahead of the programmatic-launch wait: everything that does not depend on this step's in-projection.
+    // Stream lengths and page tables were written before the step; with prep != 0 every position below the
+    // row's own was stored in an earlier step, so the warp's first keys and values can already be in flight.
     const int slot = a.segs[a.row_seg[m]].slot;
     const int pos_m = row_position(a, m);
     const int N = pos_m + 1;
     const int chunk = 32 * ((N + 32 * a.nsplit - 1) / (32 * a.nsplit));
     const int used = (N + chunk - 1) / chunk;
-    if (split >= used) return;
+    if (split >= used) { pdl_wait(); pdl_launch_dependents(); return; }
     const int p0 = split * chunk, p1 = min(N, p0 + chunk);
     const bool own = prep && (pos_m >= p0) && (pos_m < p1);
     const __half* rowp = a.inproj + (size_t)m * a.ld;
+    uint4 kcur = make_uint4(0, 0, 0, 0), vcur = make_uint4(0, 0, 0, 0);
+    const int first = p0 + warp;
+    const bool early_kv = prep && first < p1 && first != pos_m;
+    if (early_kv) {
+        kcur = reinterpret_cast<const uint4*>(kv_ptr(a, slot, first, 0, kvh))[lane];
+        vcur = reinterpret_cast<const uint4*>(kv_ptr(a, slot, first, 1, kvh))[lane];
+    }
+    if (prep && threadIdx.x < 32) rope_table_entry(a.theta, pos_m, threadIdx.x, s_cs[threadIdx.x], s_sn[threadIdx.x]);
+    pdl_wait();
+    pdl_launch_dependents();
     if (prep) {
-        uint4 qo = norm_rope_head(rowp + (size_t)(kvh * ATT_G + warp) * 2 * ATT_D, a.q_norm, a.eps, a.theta, pos_m, lane);
+        __syncthreads();                                      // the rotation table
+        uint4 qo = norm_rope_head_tab(rowp + (size_t)(kvh * ATT_G + warp) * 2 * ATT_D, a.q_norm, a.eps, s_cs, s_sn, lane);
         reinterpret_cast<uint4*>(sq[warp])[lane] = qo;
-        if (own && warp == 0) {
-            uint4 ko = norm_rope_head(rowp + a.NH * 2 * ATT_D + kvh * ATT_D, a.k_norm, a.eps, a.theta, pos_m, lane);
+        if (own && warp == 1) {
+            uint4 ko = norm_rope_head_tab(rowp + a.NH * 2 * ATT_D + kvh * ATT_D, a.k_norm, a.eps, s_cs, s_sn, lane);
             reinterpret_cast<uint4*>(sk)[lane] = ko;
             reinterpret_cast<uint4*>(kv_ptr(a, slot, pos_m, 0, kvh))[lane] = ko;
         }
-        if (own && warp == 1) {
+        if (own && warp == 2) {
             uint4 vo = reinterpret_cast<const uint4*>(rowp + a.NH * 2 * ATT_D + a.KV * ATT_D + kvh * ATT_D)[lane];
             reinterpret_cast<uint4*>(sv)[lane] = vo;
             reinterpret_cast<uint4*>(kv_ptr(a, slot, pos_m, 1, kvh))[lane] = vo;
@@ -1417,15 +1466,20 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
     for (int g = 0; g < ATT_G; ++g) { mx[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[g][i] = 0.f; }
-    for (int pos = p0 + warp; pos < p1; pos += 8) {
-        uint4 kvv, vvv;
-        if (own && pos == pos_m) { kvv = reinterpret_cast<const uint4*>(sk)[lane]; vvv = reinterpret_cast<const uint4*>(sv)[lane]; }
+    // keys of this warp: first, first + 8, ...; the next key's K and V are requested before the current one is used
+    auto load_kv = [&](int pos, uint4& kk, uint4& vv) {
+        if (own && pos == pos_m) { kk = reinterpret_cast<const uint4*>(sk)[lane]; vv = reinterpret_cast<const uint4*>(sv)[lane]; }
         else {
-            kvv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 0, kvh))[lane];
-            vvv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 1, kvh))[lane];
+            kk = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 0, kvh))[lane];
+            vv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 1, kvh))[lane];
         }
-        const __half* kh = reinterpret_cast<const __half*>(&kvv);
-        const __half* vh = reinterpret_cast<const __half*>(&vvv);
+    };
+    if (!early_kv && first < p1) load_kv(first, kcur, vcur);
+    for (int pos = first; pos < p1; pos += 8) {
+        uint4 knext = make_uint4(0, 0, 0, 0), vnext = make_uint4(0, 0, 0, 0);
+        if (pos + 8 < p1) load_kv(pos + 8, knext, vnext);
+        const __half* kh = reinterpret_cast<const __half*>(&kcur);
+        const __half* vh = reinterpret_cast<const __half*>(&vcur);
         float kf[8], vf[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) { kf[i] = h2f(kh[i]); vf[i] = h2f(vh[i]); }
@@ -1441,6 +1495,7 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], factor, es * vf[i]);
         }
+        kcur = knext; vcur = vnext;
     }
     // ---- merge the 8 warps: all heads at once through shared memory ----
     if (lane == 0) {
