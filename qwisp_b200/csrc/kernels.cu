@@ -951,6 +951,19 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
             if (tile2 < nt2) a.dbuf[(size_t)dst * a.H + tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, 0));
         }
     }
+    // what the combine needs besides the other CTAs' results is fetched before the ticket, so the CTA that
+    // turns out to be last only waits for the expert outputs (column i of the group per thread; TPC2*16 <= 512)
+    const int ncols = min(TPC2 * 16, a.H - (int)blockIdx.x * TPC2 * 16);
+    const int ncol = blockIdx.x * TPC2 * 16 + threadIdx.x;
+    const bool mine = (int)threadIdx.x < ncols;
+    __half hres = f2h(0.0f), sgate = f2h(0.0f);
+    __half sck[16];
+    if (mine) {
+        if (a.resid) hres = a.resid[ncol];
+        sgate = sigmoid_h(a.sgl[0]);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) if (k < a.topk) sck[k] = a.scores[k];
+    }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -961,14 +974,17 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
     if (!misc[16]) return;
     __threadfence();
     if (threadIdx.x == 0) a.tile_counter[blockIdx.x] = 0u;
-    const int ncols = min(TPC2 * 16, a.H - (int)blockIdx.x * TPC2 * 16);
-    for (int i = threadIdx.x; i < ncols; i += blockDim.x) {
-        const int n = blockIdx.x * TPC2 * 16 + i;
+    if (mine) {
+        __half dk[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) if (k < a.topk) dk[k] = __ldcg(a.dbuf + (size_t)k * a.H + ncol);
+        const __half dsh = __ldcg(a.dbuf + (size_t)npair * a.H + ncol);
         __half acc = f2h(0.0f);
-        for (int k = 0; k < a.topk; ++k) acc = hadd_rn(acc, hmul_rn(__ldcg(a.dbuf + (size_t)k * a.H + n), a.scores[k]));
-        __half res = hadd_rn(acc, hmul_rn(sigmoid_h(a.sgl[0]), __ldcg(a.dbuf + (size_t)npair * a.H + n)));
-        if (a.resid) a.resid[n] = hadd_rn(a.resid[n], res);
-        else a.out[n] = res;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) if (k < a.topk) acc = hadd_rn(acc, hmul_rn(dk[k], sck[k]));
+        const __half res = hadd_rn(acc, hmul_rn(sgate, dsh));
+        if (a.resid) a.resid[ncol] = hadd_rn(hres, res);
+        else a.out[ncol] = res;
     }
 }
 bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
@@ -1086,19 +1102,32 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
     float4 S[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) S[i] = *reinterpret_cast<const float4*>(S_in + (size_t)(warp * 4 + i) * GDN_DK + lane * 4);
-    pdl_wait();
-    pdl_launch_dependents();
-
+    // also ahead of the wait: conv weights, decay parameters (cold in HBM once per token) and the three
+    // history rows of this thread's channels (written a step ago)
     const int ch_q = hk * GDN_DK + tid, ch_k = keyDim + hk * GDN_DK + tid;
     const int ch_v = 2 * keyDim + hv * GDN_DV + dvt * 16 + (tid & 15);
     const float4 wq = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_q * 4);
     const float4 wk = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_k * 4);
     const float4 wv = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch_v * 4);
+    const float A_log_h = a.A_log[hv], dt_bias_h = a.dt_bias[hv];
+    float hq[CONV_K - 1], hkk[CONV_K - 1], hvv[CONV_K - 1];
+#pragma unroll
+    for (int j = 0; j < CONV_K - 1; ++j) {
+        hq[j] = h2f(hist_in[(size_t)j * convDim + ch_q]);
+        hkk[j] = h2f(hist_in[(size_t)j * convDim + ch_k]);
+        hvv[j] = h2f(hist_in[(size_t)j * convDim + ch_v]);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+
     const float invScale = 0.08838834764831845f;             // 128^-0.5
     const __half qs = f2h(invScale * invScale), ks = f2h(invScale);
     auto xval = [&](int idx, int ch) -> float {               // row idx of [hist(3) | rows of the segment]
-        return (idx < CONV_K - 1) ? h2f(hist_in[(size_t)idx * convDim + ch])
-                                  : h2f(a.inproj[(size_t)(seg.row0 + idx - (CONV_K - 1)) * a.ld + ch]);
+        if (idx < CONV_K - 1) {
+            const float* hsel = (ch == ch_q) ? hq : ((ch == ch_k) ? hkk : hvv);
+            return (idx == 0) ? hsel[0] : ((idx == 1) ? hsel[1] : hsel[2]);
+        }
+        return h2f(a.inproj[(size_t)(seg.row0 + idx - (CONV_K - 1)) * a.ld + ch]);
     };
     auto conv = [&](int tt, int ch, float4 w) -> float {
         float acc = 0.f;
@@ -1118,9 +1147,9 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
             __half bh = a.inproj[(size_t)row * a.ld + convDim + a.Hv * GDN_DV + hv];
             __half ah = a.inproj[(size_t)row * a.ld + convDim + a.Hv * GDN_DV + a.Hv + hv];
             gb_s[1] = h2f(sigmoid_h(bh));
-            float xa = h2f(ah) + a.dt_bias[hv];
+            float xa = h2f(ah) + dt_bias_h;
             float sp = fmaxf(xa, 0.0f) + logf(1.0f + expf(-fabsf(xa)));
-            gb_s[0] = expf(-expf(a.A_log[hv]) * sp);
+            gb_s[0] = expf(-expf(A_log_h) * sp);
         }
         __syncthreads();
         float iq = __frsqrt_rn(__fadd_rn(__fdiv_rn(red_s[0] + red_s[1] + red_s[2] + red_s[3], 128.0f), a.eps));
