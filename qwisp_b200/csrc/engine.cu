@@ -64,6 +64,7 @@ struct sl_engine {
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
     unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; int* samp_buf = nullptr; unsigned* slot_sync = nullptr;
+    bool use_route_in_experts = true;   // with the fused kernel: routing done by its CTAs (SEEDLESS_ROUTE_IN_EXPERTS=0: by the router's last CTA)
     bool use_fused_experts = true;  // batch-1 decode: gate/up + down in one launch (SEEDLESS_FUSED_EXPERTS=0 turns it off)
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
     int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
@@ -327,6 +328,7 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->kv_pool, (size_t)c.kv_pages * page_elems))) return rc;
     for (int i = c.kv_pages - 1; i >= 0; --i) e->free_pages.push_back(i);
     for (int i = S - 1; i >= 0; --i) e->free_slots.push_back(i);
+    { const char* re = getenv("SEEDLESS_ROUTE_IN_EXPERTS"); if (re) e->use_route_in_experts = (re[0] == '1'); }
     { const char* fe = getenv("SEEDLESS_FUSED_EXPERTS"); if (fe) e->use_fused_experts = (fe[0] == '1'); }
     const char* pfe = getenv("SEEDLESS_PREFETCH");
     if (pfe) e->use_prefetch = (pfe[0] == '1');
@@ -488,14 +490,19 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
     ra.topk = e->topk; ra.inds = e->inds; ra.scores = e->scores; ra.lists = e->lists; ra.counter = e->counters + 1;
     if (e->ep_step) { enqueue_moe_ep(e, L, ra, M, resid, plain_out); return; }
-    launch_router(ra, st, e->use_pdl);
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
     ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = M; ea.H = e->H; ea.I = e->I; ea.topk = e->topk;
     ea.scores = e->scores; ea.sgl = e->sgl; ea.resid = resid; ea.out = plain_out; ea.tile_counter = e->tile_counters; ea.err = e->err_flag;
     if (e->use_prefetch) { if (next) pf_q4(ea.pf, 0, next->r_in); else pf_q4(ea.pf, 0, e->r_lm_head, (size_t)24 << 20); }
     int nslots = M * e->topk < e->E ? M * e->topk : e->E;
     ea.slot_sync = e->slot_sync;
-    if (e->use_fused_experts && launch_expert_fused(ea, st, e->use_pdl)) return;      // batch-1 decode: one launch
+    ea.rlogits = e->rlogits; ea.E = e->E; ea.inds_out = e->inds; ea.scores_out = e->scores;
+    const bool fused = e->use_fused_experts && expert_fused_applicable(ea);
+    // batch-1 decode: the router stops at the logits and the fused expert kernel's CTAs route the row themselves
+    ra.no_route = (fused && e->use_route_in_experts) ? 1 : 0;
+    ea.route_here = ra.no_route;
+    launch_router(ra, st, e->use_pdl);
+    if (fused && launch_expert_fused(ea, st, e->use_pdl)) return;                      // one launch for gate/up + down
     launch_expert_gateup(e->exact, ea, nslots, st, e->use_pdl);
     launch_expert_down(e->exact, ea, nslots, st, e->use_pdl);
 }

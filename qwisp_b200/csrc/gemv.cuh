@@ -374,6 +374,15 @@ __device__ __forceinline__ void reduce_tiles(const float* red, float* fin, int t
     }
 }
 
+// the same sum taken directly from the partials by the thread that writes the output: value of weight row
+// `row` (0..15), pass-row `col` of tile `tl`, slices added in ascending order (identical to reduce_tiles)
+__device__ __forceinline__ float tile_sum(const float* red, int tl, int slices, int row, int col) {
+    const int j = ((((row & 7) << 2) | (col >> 1)) << 2) | (((row >> 3) << 1) | (col & 1));
+    float acc = 0.f;
+    for (int sidx = 0; sidx < slices; ++sidx) acc += red[(tl * slices + sidx) * 128 + j];
+    return acc;
+}
+
 // dynamic shared memory carve-up shared by host (size) and device (pointers)
 // Weight stage: the CTA's units (one slice of one tile each: 2048 B of nibbles + 256 B of scales)
 // are contiguous in the fragment-major layout, so each round of 16 units arrives by two bulk copies.

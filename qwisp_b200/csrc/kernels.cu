@@ -92,6 +92,13 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1) k_gemv(DenseArgs a) 
     pdl_wait();
     pdl_launch_dependents();
     stage_issue<PRO>(sregs, src, row0, mr, a.K);
+    // the residual value this thread will add in the epilogue (first epilogue iteration) is final already:
+    // request it now instead of at the end of the kernel
+    __half resid0 = f2h(0.0f);
+    if (EPI == EPI_RESID) {
+        const int i = threadIdx.x, tl2 = i >> 7, col = (i >> 4) & 7, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
+        if (i < TPC * 128 && tile2 < ntiles && col < mr) resid0 = a.y[(size_t)(row0 + col) * a.ldy + tile2 * 16 + row];
+    }
     if (blockIdx.y == 0) prefetch_ranges(a.pf, blockIdx.x, gridDim.x);
     stage_finish<PRO>(sregs, st, src, row0, mr, a.K);
     __syncthreads();
@@ -111,15 +118,14 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1) k_gemv(DenseArgs a) 
         }
     }
     __syncthreads();
-    reduce_tiles(red, fin, nvu >> lg, slices);
-    __syncthreads();
+    // each output's thread adds the slices' partials itself (ascending order) and writes the result
     if (EPI == EPI_STORE || EPI == EPI_RESID) {
         for (int i = threadIdx.x; i < TPC * 128; i += blockDim.x) {
             int tl2 = i >> 7, col = (i >> 4) & 7, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
             if (tile2 < ntiles && col < mr) {
                 size_t idx = (size_t)(row0 + col) * a.ldy + tile2 * 16 + row;
-                __half val = f2h(tile_value(fin + tl2 * 128, row, col));
-                if (EPI == EPI_RESID) val = hadd_rn(a.y[idx], val);
+                __half val = f2h(tile_sum(red, tl2, slices, row, col));
+                if (EPI == EPI_RESID) val = hadd_rn(i == (int)threadIdx.x ? resid0 : a.y[idx], val);
                 a.y[idx] = val;
             }
         }
@@ -127,7 +133,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1) k_gemv(DenseArgs a) 
         for (int j = threadIdx.x; j < TPC * 64; j += blockDim.x) {
             int tl2 = j >> 6, col = (j >> 3) & 7, i = j & 7, tile2 = blockIdx.x * TPC + tl2;
             if (tile2 < ntiles && col < mr) {
-                __half g = f2h(tile_value(fin + tl2 * 128, i, col)), u = f2h(tile_value(fin + tl2 * 128, i + 8, col));
+                __half g = f2h(tile_sum(red, tl2, slices, i, col)), u = f2h(tile_sum(red, tl2, slices, i + 8, col));
                 a.y[(size_t)(row0 + col) * a.ldy + tile2 * 8 + i] = swiglu_h(g, u);
             }
         }
@@ -606,6 +612,7 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
             }
         }
     }
+    if (a.no_route) return;                                  // the consumer routes from the logits itself
     // ---- the CTA that finishes last routes every row and groups the (row, k) pairs by expert ----
     __threadfence();
     __syncthreads();
@@ -860,21 +867,36 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
         wstage_copy(ws2, q2.wr, q2.sr, ((size_t)e * nt2 + (size_t)blockIdx.x * TPC2) << lg2, nvu2, UD);
     };
     if (issuer) { wstage_init(ws1, UG); wstage_init(ws2, UD); }
+    __shared__ float s_rbuf[512 + 32];
+    __shared__ int s_inds[16];
+    __shared__ __half s_scores[16];
     const bool shared = (y == (int)gridDim.y - 1);             // one row: its top_k experts are distinct, slot k = k-th choice
     if (shared && issuer) issue(true, 0);
     pdl_wait();
     pdl_launch_dependents();
-    if (!shared && issuer) issue(false, a.lists.slot_expert[y]);
+    if (a.route_here) {
+        // every CTA routes the row itself from the router's logits (one warp, same deterministic procedure in
+        // all CTAs) instead of the router kernel ending in a one-CTA routing tail that all CTAs would wait for.
+        // The last warp does it (it stages no activations) and starts this slot's weight copies straight away,
+        // while the other warps stage the activation row; the barrier after the staging publishes the scores.
+        if (warp == 15) {
+            route_row_warp(a.rlogits, a.E, a.topk, s_inds, s_scores, s_rbuf, lane);
+            __syncwarp();
+            if (!shared && lane == 0) issue(false, s_inds[y]);
+            if (blockIdx.x == 0 && y == 0 && lane < a.topk) { a.inds_out[lane] = s_inds[lane]; a.scores_out[lane] = s_scores[lane]; }
+        }
+    } else {
+        if ((int)threadIdx.x < a.topk) { s_inds[threadIdx.x] = a.lists.slot_expert[threadIdx.x]; s_scores[threadIdx.x] = a.scores[threadIdx.x]; }
+        if (!shared && issuer) issue(false, a.lists.slot_expert[y]);
+    }
     const int dst = shared ? npair : y;                        // row of hbuf / dbuf (pair id k, or top_k for the shared expert)
     // ---- phase 1: gate/up + SwiGLU -> hbuf[dst] ----
     {
-        if (threadIdx.x == 0) { misc[0] = a.shared_row0; misc[8] = dst; }
-        __syncthreads();
-        StageSrc src{a.p, a.H, misc, nullptr, nullptr, 0, 0.f};
+        StageSrc src{a.p, a.H, nullptr, nullptr, nullptr, 0, 0.f};
         StageRegs sregs;
-        stage_issue<PRO_PLAIN>(sregs, src, 0, 1, a.H);
-        stage_finish<PRO_PLAIN>(sregs, st, src, 0, 1, a.H);
-        __syncthreads();
+        stage_issue<PRO_PLAIN>(sregs, src, a.shared_row0, 1, a.H);
+        stage_finish<PRO_PLAIN>(sregs, st, src, a.shared_row0, 1, a.H);
+        __syncthreads();                                       // the staged row, and the routing of the last warp
         XRegs xr;
         load_xregs(xr, st, warp & (sl1 - 1), r, t, 1);
 #pragma unroll 1
@@ -891,12 +913,10 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
             }
         }
         __syncthreads();
-        reduce_tiles(red, fin, nvu1 >> lg1, sl1);
-        __syncthreads();
         for (int j2 = threadIdx.x; j2 < TPC1 * 8; j2 += blockDim.x) {
             int tl2 = j2 >> 3, i = j2 & 7, tile2 = blockIdx.x * TPC1 + tl2;
             if (tile2 < nt1) {
-                __half g = f2h(tile_value(fin + tl2 * 128, i, 0)), u = f2h(tile_value(fin + tl2 * 128, i + 8, 0));
+                __half g = f2h(tile_sum(red, tl2, sl1, i, 0)), u = f2h(tile_sum(red, tl2, sl1, i + 8, 0));
                 a.hbuf[(size_t)dst * a.I + tile2 * 8 + i] = swiglu_h(g, u);
             }
         }
@@ -921,12 +941,10 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
     __syncthreads();
     // ---- phase 2: down -> dbuf[dst], then the last CTA of the tile group combines ----
     {
-        if (threadIdx.x == 0) { misc[0] = dst; }
-        __syncthreads();
-        StageSrc src{a.hbuf, a.I, misc, nullptr, nullptr, 0, 0.f};
+        StageSrc src{a.hbuf, a.I, nullptr, nullptr, nullptr, 0, 0.f};
         StageRegs sregs;
-        stage_issue<PRO_PLAIN>(sregs, src, 0, 1, a.I);
-        stage_finish<PRO_PLAIN>(sregs, st, src, 0, 1, a.I);
+        stage_issue<PRO_PLAIN>(sregs, src, dst, 1, a.I);
+        stage_finish<PRO_PLAIN>(sregs, st, src, dst, 1, a.I);
         __syncthreads();
         XRegs xr;
         load_xregs(xr, st, warp & (sl2 - 1), r, t, 1);
@@ -944,11 +962,9 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
             }
         }
         __syncthreads();
-        reduce_tiles(red, fin, nvu2 >> lg2, sl2);
-        __syncthreads();
         for (int i = threadIdx.x; i < TPC2 * 16; i += blockDim.x) {
             int tl2 = i >> 4, row = i & 15, tile2 = blockIdx.x * TPC2 + tl2;
-            if (tile2 < nt2) a.dbuf[(size_t)dst * a.H + tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, 0));
+            if (tile2 < nt2) a.dbuf[(size_t)dst * a.H + tile2 * 16 + row] = f2h(tile_sum(red, tl2, sl2, row, 0));
         }
     }
     // what the combine needs besides the other CTAs' results is fetched before the ticket, so the CTA that
@@ -962,7 +978,7 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
         if (a.resid) hres = a.resid[ncol];
         sgate = sigmoid_h(a.sgl[0]);
 #pragma unroll
-        for (int k = 0; k < 16; ++k) if (k < a.topk) sck[k] = a.scores[k];
+        for (int k = 0; k < 16; ++k) if (k < a.topk) sck[k] = s_scores[k];
     }
     __threadfence();
     __syncthreads();
@@ -987,12 +1003,18 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
         else a.out[ncol] = res;
     }
 }
-bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
-    if (a.M != 1 || a.slot_sync == nullptr || a.tile_counter == nullptr) return false;
+bool expert_fused_applicable(const ExpertArgs& a) {
+    if (a.M != 1 || a.slot_sync == nullptr || a.tile_counter == nullptr || a.topk > 16) return false;
     const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1);
     const int g1 = (a.I / 8 + p1.tpc - 1) / p1.tpc, g2 = (a.H / 16 + p2.tpc - 1) / p2.tpc;
     if (g1 != g2 || p1.upw != 2 || p2.upw != 1) return false;            // the 2048 -> 512 -> 2048 expert shape
     if (g1 * (a.topk + 1) > 148) return false;                           // every CTA must be resident at once
+    return true;
+}
+bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
+    if (!expert_fused_applicable(a)) return false;
+    const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1);
+    const int g1 = (a.I / 8 + p1.tpc - 1) / p1.tpc;
     size_t smem = GemvSmem::wstage_bytes(32) + GemvSmem::wstage_bytes(16) + GemvSmem::bytes(1, a.H > a.I ? a.H : a.I, 32, p1.tpc > p2.tpc ? p1.tpc : p2.tpc);
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_expert_fused<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
@@ -1565,6 +1587,8 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
         }
     }
     // ---- the CTA that finishes last for this (row, kv head) merges the splits ----
+    // (the output gate of this warp's head does not depend on the other CTAs: fetched before the ticket)
+    const uint4 gvv = reinterpret_cast<const uint4*>(rowp + (size_t)(kvh * ATT_G + warp) * 2 * ATT_D + ATT_D)[lane];
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -1600,7 +1624,6 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
             o[0] = fmaf(x0.x, f, o[0]); o[1] = fmaf(x0.y, f, o[1]); o[2] = fmaf(x0.z, f, o[2]); o[3] = fmaf(x0.w, f, o[3]);
             o[4] = fmaf(x1.x, f, o[4]); o[5] = fmaf(x1.y, f, o[5]); o[6] = fmaf(x1.z, f, o[6]); o[7] = fmaf(x1.w, f, o[7]);
         }
-        uint4 gvv = reinterpret_cast<const uint4*>(rowp + (size_t)h * 2 * ATT_D + ATT_D)[lane];
         const __half* gh = reinterpret_cast<const __half*>(&gvv);
         uint4 outv; __half* oh = reinterpret_cast<__half*>(&outv);
 #pragma unroll

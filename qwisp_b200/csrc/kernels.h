@@ -41,6 +41,7 @@ struct RouterArgs {
     __half* sgl;                         // [M] shared-expert gate logit
     int topk; int* inds; __half* scores; // [M][topk] routing result (written by the last CTA)
     MoeLists lists; unsigned* counter;
+    int no_route = 0;                    // 1: stop after the logits; the consumer (fused expert kernel) routes from them itself
     PfList pf;                           // static prefetch (every CTA)
 };
 
@@ -54,6 +55,9 @@ struct ExpertArgs {
     __half* hbuf;                        // [(M*topk + M)][I]
     __half* dbuf;                        // [(M*topk + M)][H]
     int M, H, I, topk;
+    const __half* rlogits = nullptr;     // fused kernel, route_here: router logits [E] of the row; every CTA routes from them itself
+    int E = 0; int route_here = 0;       //   (deterministic, so all CTAs agree) instead of waiting for a routing tail in the router kernel
+    int* inds_out = nullptr; __half* scores_out = nullptr;   //   CTA (0,0) publishes the result
     int lg_slices2 = 0;                  // fused kernel: log2(I/256) of the down phase
     unsigned* slot_sync = nullptr;       // fused kernel: [2][top_k + 1] counters, zero between launches
     int nstages = 1;                     // weight stages per CTA (2: a CTA walks several expert slots, filled by the launcher)
@@ -111,6 +115,7 @@ void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStrea
 void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
 // batch-1 decode: gate/up and down in ONE launch (a per-slot barrier between the phases); false if the shapes do not fit it
 bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl);
+bool expert_fused_applicable(const ExpertArgs& a);      // the shape test launch_expert_fused applies
 // expert-parallel helpers: group the (row, k) pairs of `npairs/topk` rows whose expert lies in [e0, e1)
 void launch_build_lists(const int* inds, int npairs, int e0, int e1, MoeLists lists, cudaStream_t st);
 // out/resid[m] (+)= sum_k fp16(d[pair0 + m*topk + k] * score[m,k]) (ascending k) + sigmoid(sgl[m]) * d[shared0 + m]
