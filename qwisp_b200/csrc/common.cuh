@@ -56,15 +56,6 @@ __device__ __forceinline__ float sigmoid_f(float x) {
 // SwiGLU in fp16: (g*sigmoid(g))*u (SeedlessMetalForward.swift:982-990)
 __device__ __forceinline__ __half swiglu_h(__half g, __half u) { return hmul_rn(hmul_rn(g, sigmoid_h(g)), u); }
 
-// mma.sync m16n8k16, fp16 x fp16 -> fp32
-__device__ __forceinline__ void mma16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 // Programmatic dependent launch: wait for the kernels this one depends on / let dependents start.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -1463,89 +1463,8 @@ void launch_attn_prep(const AttnArgs& a, cudaStream_t st) {
     COUNT_LAUNCH();
 }
 
-// split-KV decode: grid (nsplit, KV heads, M), 256 threads.  Each warp walks keys of its split
-// (stride 8 warps), lane owns 8 of the 256 dims, the 8 query heads of the kv head share each
-// K/V row.  Online softmax in f32 per warp; warps merged in shared memory; one partial
-// (max, sum, acc[256]) per (row, head, split).  Row m sees positions [0, pos(m)].
 constexpr int ATT_G = 8;     // query heads per kv head handled together (attn_heads / attn_kv_heads must equal it)
-__global__ void __launch_bounds__(256) k_attn_decode(AttnArgs a) {
-    __shared__ float sm_m[8][ATT_G], sm_l[8][ATT_G];
-    __shared__ float sm_o[8][ATT_D];
-    const int split = blockIdx.x, kvh = blockIdx.y, m = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int slot = a.segs[a.row_seg[m]].slot;
-    const int N = row_position(a, m) + 1;
-    const int chunk = 32 * ((N + 32 * a.nsplit - 1) / (32 * a.nsplit));
-    const int p0 = split * chunk, p1 = min(N, p0 + chunk);
-    const float scale = 0.0625f;                              // 256^-0.5
-    float q[ATT_G][8];
-#pragma unroll
-    for (int g = 0; g < ATT_G; ++g) {
-        uint4 qv = reinterpret_cast<const uint4*>(a.qrot + ((size_t)m * a.NH + kvh * ATT_G + g) * ATT_D)[lane];
-        const __half* qh = reinterpret_cast<const __half*>(&qv);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[g][i] = scale * h2f(qh[i]);
-    }
-    float mx[ATT_G], l[ATT_G], acc[ATT_G][8];
-#pragma unroll
-    for (int g = 0; g < ATT_G; ++g) { mx[g] = -INFINITY; l[g] = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[g][i] = 0.f; }
-    for (int pos = p0 + warp; pos < p1; pos += 8) {
-        uint4 kvv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 0, kvh))[lane];
-        uint4 vvv = reinterpret_cast<const uint4*>(kv_ptr(a, slot, pos, 1, kvh))[lane];
-        const __half* kh = reinterpret_cast<const __half*>(&kvv);
-        const __half* vh = reinterpret_cast<const __half*>(&vvv);
-        float kf[8], vf[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { kf[i] = h2f(kh[i]); vf[i] = h2f(vh[i]); }
-#pragma unroll
-        for (int g = 0; g < ATT_G; ++g) {
-            float s = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) s = fmaf(q[g][i], kf[i], s);
-            s = warp_sum(s);
-            float nm = fmaxf(mx[g], s);
-            float factor = __expf(mx[g] - nm), es = __expf(s - nm);
-            mx[g] = nm; l[g] = l[g] * factor + es;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], factor, es * vf[i]);
-        }
-    }
-    // merge the 8 warps, one query head at a time
-    float* po = a.part_o + (((size_t)m * a.NH + kvh * ATT_G) * a.nsplit + split) * ATT_D;
-    float* pml = a.part_ml + (((size_t)m * a.NH + kvh * ATT_G) * a.nsplit + split) * 2;
-#pragma unroll
-    for (int g = 0; g < ATT_G; ++g) { if (lane == 0) { sm_m[warp][g] = mx[g]; sm_l[warp][g] = l[g]; } }
-    __syncthreads();
-    for (int g = 0; g < ATT_G; ++g) {
-        float gm = -INFINITY;
-        for (int w = 0; w < 8; ++w) gm = fmaxf(gm, sm_m[w][g]);
-        float f = (mx[g] == -INFINITY) ? 0.f : __expf(mx[g] - gm);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sm_o[warp][lane * 8 + i] = acc[g][i] * f;
-        __syncthreads();
-        {
-            int d = threadIdx.x;                              // 256 threads = 256 dims
-            float o = 0.f;
-            for (int w = 0; w < 8; ++w) o += sm_o[w][d];
-            po[(size_t)g * a.nsplit * ATT_D + d] = o;
-        }
-        if (threadIdx.x == 0) {
-            float ls = 0.f;
-            for (int w = 0; w < 8; ++w) ls += (sm_m[w][g] == -INFINITY) ? 0.f : sm_l[w][g] * __expf(sm_m[w][g] - gm);
-            pml[(size_t)g * a.nsplit * 2 + 0] = gm;
-            pml[(size_t)g * a.nsplit * 2 + 1] = ls;
-        }
-        __syncthreads();
-    }
-}
-void launch_attn_decode(const AttnArgs& a, cudaStream_t st) {
-    dim3 grid(a.nsplit, a.KV, a.M);
-    ProfScope ps("k_attn_decode", 0.0, st);
-    k_attn_decode<<<grid, 256, 0, st>>>(a);
-    COUNT_LAUNCH();
-}
+
 // ---- one-kernel attention: (optional) q/k prep + split-KV decode + merge of the splits ----
 // norm + partial rotation of one 256-wide head held as 8 values per lane; returns the fp16 values
 __device__ __forceinline__ uint4 norm_rope_head(const __half* src, const __half* w, float eps, float theta, int pos, int lane) {
@@ -1818,33 +1737,6 @@ void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStr
     COUNT_LAUNCH();
 }
 
-// grid (NH, M), 256 threads: merge splits, normalise, round to fp16, multiply by sigmoid(gate) in fp16
-__global__ void __launch_bounds__(256) k_attn_combine(AttnArgs a) {
-    const int h = blockIdx.x, m = blockIdx.y, d = threadIdx.x;
-    const float* po = a.part_o + ((size_t)m * a.NH + h) * a.nsplit * ATT_D;
-    const float* pml = a.part_ml + ((size_t)m * a.NH + h) * a.nsplit * 2;
-    const int N = row_position(a, m) + 1;
-    const int chunk = 32 * ((N + 32 * a.nsplit - 1) / (32 * a.nsplit));
-    const int used = (N + chunk - 1) / chunk;
-    float gm = -INFINITY;
-    for (int s = 0; s < used; ++s) gm = fmaxf(gm, pml[s * 2]);
-    float tot = 0.f, o = 0.f;
-    for (int s = 0; s < used; ++s) {
-        float ms = pml[s * 2];
-        float f = (ms == -INFINITY) ? 0.f : __expf(ms - gm);
-        tot += pml[s * 2 + 1] * f;
-        o += po[(size_t)s * ATT_D + d] * f;
-    }
-    __half out = f2h(tot == 0.f ? o : o / tot);
-    __half gv = a.inproj[(size_t)m * a.ld + (size_t)h * 2 * ATT_D + ATT_D + d];
-    a.gated[((size_t)m * a.NH + h) * ATT_D + d] = hmul_rn(out, sigmoid_h(gv));
-}
-void launch_attn_combine(const AttnArgs& a, cudaStream_t st) {
-    dim3 grid(a.NH, a.M);
-    ProfScope ps("k_attn_combine", 0.0, st);
-    k_attn_combine<<<grid, 256, 0, st>>>(a);
-    COUNT_LAUNCH();
-}
 
 // ============================================================================================
 // End of a step: advance cache lengths, flip GDN ping-pong sides, feed greedy tokens back as

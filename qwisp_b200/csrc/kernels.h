@@ -123,10 +123,8 @@ void launch_moe_combine(const __half* dbuf, int pair0, int shared0, const __half
                         __half* resid, __half* out, cudaStream_t st);
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl);
 void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
-void launch_attn_decode(const AttnArgs& a, cudaStream_t st);
 // q/k prep (when every row is its stream's only row) + split-KV decode + merge in one launch; counters: M*KV zeros
 void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStream_t st, bool pdl);
-void launch_attn_combine(const AttnArgs& a, cudaStream_t st);
 void launch_step_end(const StepEndArgs& a, cudaStream_t st);
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st);
 int64_t kernel_launch_count();
