@@ -50,6 +50,12 @@ def compute():
         toks.append(int(st.step([toks[-1]])[0]))
     out["tiny_greedy"] = toks
     out["tiny_blob_sha"] = sha(st.state_save())
+    # speculative-sampling rows: draws, draft-excluded draws and accept flags at two settings
+    sl = O.synth_f16(5, "sampler.logits", 4 * 2048, 0.0, 2.5).reshape(4, 2048)
+    draft = np.array([3, -1, 100, 5], dtype=np.int32)
+    for name, inv_t, top_p in (("sample_t0p7", 1.0 / 0.7, 1.0), ("sample_nucleus", 1.0, 0.9)):
+        f, r, a = O.sample_rows(sl, draft, inv_t, top_p, 0x1234, 0xABCD, 40)
+        out[name] = [f.tolist(), r.tolist(), a.tolist()]
     return out
 
 
