@@ -373,15 +373,17 @@ def test_tensor_core_gemm_matches_gemv_and_oracle(M, K, N):
     assert rep_o["max_abs"] <= TOL and rep_g["max_abs"] <= 4e-3
 
 
-def test_sampler_matches_golden(mini_engine):
+def test_sampler_matches_golden():
     """The committed golden draws (made by the CPU oracle) reproduced on the device without the oracle."""
     import qwisp_b200 as Q
+    from conftest import gpu_engine
     g = _golden()
-    V = mini_engine.cfg.vocab
-    sl = Q.ops.synth_f16(5, "sampler.logits", 4 * 2048, 0.0, 2.5).reshape(4, 2048)
-    if V != 2048:
-        pytest.skip("the golden rows are 2048 wide")
-    draft = np.array([3, -1, 100, 5], dtype=np.int32)
-    for name, inv_t, top_p in (("sample_t0p7", 1.0 / 0.7, 1.0), ("sample_nucleus", 1.0, 0.9)):
-        f, r, a = Q.ops.sample_rows(mini_engine, sl, draft, inv_t, top_p, 0x1234, 0xABCD, 40)
-        assert [f.tolist(), r.tolist(), a.tolist()] == g[name], name
+    eng = gpu_engine(dict(MINI, vocab=2048), max_streams=2, kv_pages=8)
+    try:
+        sl = Q.ops.synth_f16(5, "sampler.logits", 4 * 2048, 0.0, 2.5).reshape(4, 2048)
+        draft = np.array([3, -1, 100, 5], dtype=np.int32)
+        for name, inv_t, top_p in (("sample_t0p7", 1.0 / 0.7, 1.0), ("sample_nucleus", 1.0, 0.9)):
+            f, r, a = Q.ops.sample_rows(eng, sl, draft, inv_t, top_p, 0x1234, 0xABCD, 40)
+            assert [f.tolist(), r.tolist(), a.tolist()] == g[name], name
+    finally:
+        eng.close()
