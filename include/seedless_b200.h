@@ -192,7 +192,7 @@ int32_t sl_ep_init(sl_engine* e, int32_t rank, int32_t world, const uint8_t* id1
  *      SeedlessMetalForward.qmm SeedlessMetalForward.swift:222, routeTop8Rows
  *      SeedlessFusedVerify.swift:174, moeBlockRows / gdnLayerRows / attnLayerRows
  *      SeedlessVerifyForward.swift:37-248) ---- */
-/* y[M,N] = x[M,K] . dequant4(W[N,K])^T; host buffers; N % 16 == 0, K % 256 == 0. */
+/* y[M,N] = x[M,K] . dequant4(W[N,K])^T; host buffers; N % 16 == 0, K in {256, 512, 1024, 2048, 4096}. */
 int32_t sl_op_qmm4(const uint16_t* x_f16, const uint32_t* w, const uint16_t* scales_f16, const uint16_t* biases_f16,
                    int32_t M, int32_t K, int32_t N, uint16_t* y_f16);
 /* The kernels read weights in a fragment-major layout made once at load time from the MLX layout:

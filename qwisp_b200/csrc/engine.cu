@@ -183,7 +183,11 @@ int32_t alloc_plain(sl_engine* e, const T** out, const std::string& name, size_t
     return reg_tensor(e, name, p, count * sizeof(T));
 }
 
+// the GEMV family needs K/256 to be a power of two (a warp's slice index is taken with a mask)
+static bool k_ok(int64_t K) { return K >= 256 && K <= 4096 && K % 256 == 0 && (((K >> 8) & ((K >> 8) - 1)) == 0); }
+
 bool config_ok(const sl_config& c) {
+    if (!k_ok(c.hidden) || !k_ok(c.moe_inter) || !k_ok((int64_t)c.gdn_v_heads * GDN_DV) || !k_ok((int64_t)c.attn_heads * ATT_D)) return false;
     if (c.hidden <= 0 || c.hidden % 256 || c.hidden > 4096) return false;
     if (c.moe_inter <= 0 || c.moe_inter % 256 || c.moe_inter > 4096) return false;
     if (c.n_layers <= 0 || c.attn_every <= 0) return false;
@@ -1129,7 +1133,7 @@ int32_t sl_op_repack_q4_device(const void* w_dev, const void* s_dev, const void*
 int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
                           int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream) {
     if (!x_dev || !wr_dev || !sr_dev || !y_dev) return SL_ERR_INVALID;
-    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || !k_ok(K)) return SL_ERR_INVALID;
     if (!device_ok()) return SL_ERR_NO_DEVICE;
     if (detect_gemv_mode() != SL_OK) return SL_ERR_CUDA;
     DenseArgs a{}; a.q.wr = (const uint4*)wr_dev; a.q.sr = (const uint4*)sr_dev; a.q.tiles = N / 16; a.q.K = K; a.N = N; a.K = K; a.M = M;
@@ -1140,7 +1144,7 @@ int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_
 int32_t sl_op_lm_head_argmax_static(const void* x_dev, const void* wr_dev, const void* sr_dev,
                                     int32_t M, int32_t K, int32_t N, int32_t* out_tokens_dev, void* cuda_stream) {
     if (!x_dev || !wr_dev || !sr_dev || !out_tokens_dev) return SL_ERR_INVALID;
-    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || !k_ok(K)) return SL_ERR_INVALID;
     if (M > head_static_max_rows()) {
         fprintf(stderr, "sl_op_lm_head_argmax_static: M = %d rows exceed the fixed scratch array's limit of %d rows per call\n",
                 (int)M, head_static_max_rows());
@@ -1159,7 +1163,7 @@ int32_t sl_op_lm_head_argmax_static(const void* x_dev, const void* wr_dev, const
 int32_t sl_op_qmm4_tc_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
                              int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream) {
     if (!x_dev || !wr_dev || !sr_dev || !y_dev) return SL_ERR_INVALID;
-    if (M <= 0 || N <= 0 || K <= 0 || N % 128 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 128 || !k_ok(K)) return SL_ERR_INVALID;
     if (!device_ok()) return SL_ERR_NO_DEVICE;
     Q4R q{}; q.wr = (const uint4*)wr_dev; q.sr = (const uint4*)sr_dev; q.tiles = N / 16; q.K = K;
     int err = launch_gemm_tc(q, N, K, M, (const __half*)x_dev, K, (__half*)y_dev, N, false, nullptr, (cudaStream_t)cuda_stream);
@@ -1167,7 +1171,7 @@ int32_t sl_op_qmm4_tc_device(const void* x_dev, const void* wr_dev, const void* 
 }
 int32_t sl_op_qmm4(const uint16_t* x, const uint32_t* w, const uint16_t* sc, const uint16_t* bi, int32_t M, int32_t K, int32_t N, uint16_t* y) {
     if (!x || !w || !sc || !bi || !y) return SL_ERR_INVALID;
-    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || K % 256 || K > 4096) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || !k_ok(K)) return SL_ERR_INVALID;
     if (!device_ok()) return SL_ERR_NO_DEVICE;
     void *dx = nullptr, *dw = nullptr, *ds = nullptr, *db = nullptr, *dy = nullptr, *dwr = nullptr, *dsr = nullptr;
     size_t bx = (size_t)M * K * 2, bw = (size_t)N * K / 2, bs = (size_t)N * K / 64 * 2, by = (size_t)M * N * 2;

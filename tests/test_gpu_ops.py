@@ -92,6 +92,8 @@ def test_qmm4_rejects_bad_shapes():
     import qwisp_b200 as Q
     with pytest.raises(Q.SeedlessError):
         Q.ops.qmm4(np.zeros((1, 192), np.float16), np.zeros((16, 24), np.uint32), np.zeros((16, 3), np.float16), np.zeros((16, 3), np.float16))
+    with pytest.raises(Q.SeedlessError):              # K/256 must be a power of two
+        Q.ops.qmm4(np.zeros((1, 768), np.float16), np.zeros((16, 96), np.uint32), np.zeros((16, 12), np.float16), np.zeros((16, 12), np.float16))
 
 
 @pytest.mark.parametrize("T", [1, 16])
