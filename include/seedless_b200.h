@@ -70,7 +70,10 @@ typedef struct sl_config {
  * "L<i>.moe.gate_proj.*" ([E*I,H]), "L<i>.moe.up_proj.*", "L<i>.moe.down_proj.*" ([E*H,I]),
  * "L<i>.moe.shared_gate_proj.*", "L<i>.moe.shared_up_proj.*", "L<i>.moe.shared_down_proj.*".
  * 4-bit tensors are in the MLX affine layout: .w uint32 [N,K/8] (8 nibbles per word, low
- * first), .s/.b fp16 [N,K/64] (SeedlessMetalForward.swift:219-221).  The data is copied. */
+ * first), .s/.b fp16 [N,K/64] (SeedlessMetalForward.swift:219-221).  The data is copied.
+ * "embed" may instead be given as the checkpoint's 4-bit table "embed.w/.s/.b" ([vocab,hidden]);
+ * it is expanded once into the fp16 table with the reference's per-row arithmetic
+ * (embed_rows_q4, SeedlessFusedVerify.swift:556-570), so lookups give the same halves. */
 typedef struct sl_weight_desc {
     const char* name;
     const void* data;

@@ -113,6 +113,15 @@ def dequant_q4(packed, s, b):
     return out
 
 
+def dequant_q4_half(packed, s, b):
+    """fp16 rows of a 4-bit table, the reference's embed_rows_q4 arithmetic (SeedlessFusedVerify.swift:556-570)."""
+    N, K8 = packed.shape
+    out = np.empty((N, K8 * 8), dtype=np.float16)
+    lib().orc_dequant_q4_half(_p(np.ascontiguousarray(packed)), _p(np.ascontiguousarray(s)), _p(np.ascontiguousarray(b)),
+                              C.c_int64(N), C.c_int64(K8 * 8), _p(out))
+    return out
+
+
 def qmm4(x, packed, s, b):
     x = np.ascontiguousarray(x, dtype=np.float16)
     M, K = x.shape

@@ -707,6 +707,17 @@ extern "C" int orc_layer_rows(void* sp, int layer, const h16* h_in, int Mrows, i
     }
     return 0;
 }
+// 4-bit embedding rows expanded to half: x = scale * nibble + bias in half arithmetic, one rounding
+// (embed_rows_q4, swift/Sources/QwispCore/SeedlessFusedVerify.swift:556-570; the Metal compiler's
+// default fast-math contracts the multiply-add, which is the single-rounding form restated here).
+extern "C" void orc_dequant_q4_half(const uint32_t* w, const h16* sc, const h16* bi, int64_t N, int64_t K, h16* out) {
+    for (int64_t n = 0; n < N; ++n)
+        for (int64_t k = 0; k < K; ++k) {
+            uint32_t q = (w[n * (K / 8) + k / 8] >> (4 * (k % 8))) & 0xFu;
+            int64_t g = n * (K / 64) + k / 64;
+            out[n * K + k] = (h16)((double)sc[g] * (double)q + (double)bi[g]);
+        }
+}
 extern "C" void orc_embed(void* m, const int32_t* tokens, int Mrows, h16* out) {
     Model* M = (Model*)m; int H = M->c.hidden;
     for (int r = 0; r < Mrows; ++r) memcpy(out + (int64_t)r * H, M->embed.data() + (size_t)tokens[r] * H, H * sizeof(h16));

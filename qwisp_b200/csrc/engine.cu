@@ -698,8 +698,42 @@ int32_t sl_engine_create(const sl_config* cfg, const sl_weight_desc* weights, in
     int32_t rc = create_common(cfg, out, &e);
     if (rc) return rc;
     std::map<std::string, bool> seen;
+    // the checkpoint's 4-bit embedding ("embed.w/.s/.b") is accepted in place of "embed" and
+    // expanded into the fp16 table here
+    const sl_weight_desc* eq[3] = {nullptr, nullptr, nullptr};
+    for (int i = 0; i < n_weights; ++i) {
+        if (!weights[i].name) continue;
+        if (!strcmp(weights[i].name, "embed.w")) eq[0] = &weights[i];
+        if (!strcmp(weights[i].name, "embed.s")) eq[1] = &weights[i];
+        if (!strcmp(weights[i].name, "embed.b")) eq[2] = &weights[i];
+    }
+    if (eq[0] || eq[1] || eq[2]) {
+        const uint64_t V = (uint64_t)e->V, H = (uint64_t)e->H;
+        const uint64_t want[3] = {V * H / 2, V * (H / 64) * 2, V * (H / 64) * 2};
+        void* tmp[3] = {nullptr, nullptr, nullptr};
+        const void* src[3];
+        rc = SL_OK;
+        for (int k = 0; k < 3 && !rc; ++k)
+            if (!eq[k] || !eq[k]->data || eq[k]->nbytes != want[k]) rc = SL_ERR_INVALID;
+        for (int k = 0; k < 3 && !rc; ++k) {
+            if (eq[k]->on_device) { src[k] = eq[k]->data; continue; }
+            if (cudaMalloc(&tmp[k], want[k]) != cudaSuccess) { cudaGetLastError(); rc = SL_ERR_CAPACITY; break; }
+            if (cudaMemcpy(tmp[k], eq[k]->data, want[k], cudaMemcpyHostToDevice) != cudaSuccess) { rc = SL_ERR_CUDA; break; }
+            src[k] = tmp[k];
+        }
+        if (!rc) {
+            launch_embed_dequant_q4((const uint32_t*)src[0], (const __half*)src[1], (const __half*)src[2],
+                                    const_cast<__half*>(e->embed), e->V, e->H, e->stream);
+            if (cudaStreamSynchronize(e->stream) != cudaSuccess || cudaGetLastError() != cudaSuccess) rc = SL_ERR_CUDA;
+        }
+        for (int k = 0; k < 3; ++k) if (tmp[k]) cudaFree(tmp[k]);
+        if (rc) { sl_engine_destroy(e); return rc; }
+        seen["embed"] = true;
+    }
     for (int i = 0; i < n_weights; ++i) {
         const sl_weight_desc& d = weights[i];
+        if (&d == eq[0] || &d == eq[1] || &d == eq[2]) continue;
+        if (d.name && seen.count(d.name) && !strcmp(d.name, "embed")) { sl_engine_destroy(e); return SL_ERR_INVALID; }   // both forms given
         auto it = d.name ? e->tensors.find(d.name) : e->tensors.end();
         if (it == e->tensors.end()) { sl_engine_destroy(e); return SL_ERR_NOT_FOUND; }
         if (!d.data || d.nbytes != it->second.bytes) { sl_engine_destroy(e); return SL_ERR_INVALID; }

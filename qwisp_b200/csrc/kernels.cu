@@ -384,6 +384,29 @@ __global__ void k_embed(const __half* embed, const int* tokens, int M, int H, in
     uint4* dst = reinterpret_cast<uint4*>(h + (size_t)m * H);
     for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
 }
+// 4-bit embedding table -> fp16 table, once at load.  Each element is scale * nibble + bias in
+// half arithmetic with one rounding, which is what the reference computes per looked-up row
+// (embed_rows_q4, SeedlessFusedVerify.swift:556-570); doing it for all rows up front turns
+// the per-token lookup into a plain row copy.  One thread per 8 elements (one packed word).
+__global__ void k_embed_dequant_q4(const uint32_t* __restrict__ w, const __half* __restrict__ sc, const __half* __restrict__ bi,
+                                   __half* __restrict__ out, size_t words, int H) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= words) return;
+    size_t row = i / (size_t)(H / 8);
+    int kw = (int)(i % (size_t)(H / 8));
+    size_t g = row * (size_t)(H / 64) + (size_t)(kw / 8);
+    const __half s = sc[g], b = bi[g];
+    const uint32_t pack = w[i];
+    alignas(16) __half v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __hfma(s, __int2half_rn((int)((pack >> (4 * j)) & 0xFu)), b);
+    reinterpret_cast<uint4*>(out)[i] = *reinterpret_cast<const uint4*>(v);
+}
+void launch_embed_dequant_q4(const uint32_t* w, const __half* s, const __half* b, __half* out, int64_t vocab, int H, cudaStream_t st) {
+    const size_t words = (size_t)vocab * (size_t)(H / 8);
+    const unsigned blocks = (unsigned)((words + 255) / 256);
+    k_embed_dequant_q4<<<blocks, 256, 0, st>>>(w, s, b, out, words, H);
+}
 void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st) {
     ProfScope ps("k_embed", (double)M * H * 4, st);
     k_embed<<<M, 256, 0, st>>>(embed, tokens, M, H, vocab, h);

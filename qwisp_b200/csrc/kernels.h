@@ -110,6 +110,7 @@ void launch_sample_rows(const __half* logits, const int* draft, int* samp_full, 
 int launch_head_static(const DenseArgs& a, cudaStream_t st);
 int head_static_max_rows();
 void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st);
+void launch_embed_dequant_q4(const uint32_t* w, const __half* s, const __half* b, __half* out, int64_t vocab, int H, cudaStream_t st);
 void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl);
 void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
 void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);

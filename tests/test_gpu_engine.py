@@ -275,6 +275,36 @@ def test_engine_from_host_tensors(tiny_oracle):
         eng.close(); ref.close()
 
 
+def test_engine_accepts_q4_embedding(tiny_oracle):
+    """The checkpoint's 4-bit embedding table handed over as embed.w/.s/.b: the table the engine
+    holds equals the reference's per-row dequantisation (embed_rows_q4,
+    SeedlessFusedVerify.swift:556-570) bit for bit, and a step over it equals a step of an engine
+    that was given those fp16 rows directly."""
+    import qwisp_b200 as Q
+    from oracle import oracle as O
+    cfg = Q.config(**TINY, max_rows=16, max_streams=2, kv_page_size=32, kv_pages=8)
+    V, H = TINY["vocab"], TINY["hidden"]
+    w, s, b = O.synth_q4(SEED, "embed.q4", V, H)
+    want = O.dequant_q4_half(w, s, b)
+    tensors = {n: tiny_oracle.tensor_bytes(n).copy() for n in tiny_oracle.tensor_names()}
+    q4 = dict(tensors); q4.pop("embed"); q4.update({"embed.w": w, "embed.s": s, "embed.b": b})
+    f16 = dict(tensors); f16["embed"] = want
+    a, bb = Q.Engine.from_tensors(cfg, q4), Q.Engine.from_tensors(cfg, f16)
+    try:
+        got = a.read_tensor("embed").view(np.uint16).reshape(V, H)
+        assert np.array_equal(got, want.view(np.uint16))
+        p = prompt(V, 7, "q4embed")
+        assert np.array_equal(a.stream(32).step_logits(p).view(np.uint16), bb.stream(32).step_logits(p).view(np.uint16))
+        both = dict(q4); both["embed"] = want
+        with pytest.raises(Q.SeedlessError):
+            Q.Engine.from_tensors(cfg, both)
+        short = dict(q4); short["embed.s"] = s[:-1]
+        with pytest.raises(Q.SeedlessError):
+            Q.Engine.from_tensors(cfg, short)
+    finally:
+        a.close(); bb.close()
+
+
 def test_step_sample_rows_greedy_equals_argmax(mini_engine):
     """At temperature 0 the sampling step returns the argmax step's tokens (stepSampleRows with
     invT <= 0, SamplerGPU.swift:13-15) and leaves the caches in the same state."""

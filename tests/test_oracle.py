@@ -205,6 +205,16 @@ def test_state_blob_roundtrip_and_rejection():
     assert not small.state_restore(blob)                    # does not fit
 
 
+def test_q4_rows_to_half_single_rounding():
+    """embed_rows_q4 arithmetic (SeedlessFusedVerify.swift:556-570): scale * nibble + bias, rounded to half once."""
+    w, s, b = O.synth_q4(5, "emb.q4", 64, 256)
+    got = O.dequant_q4_half(w, s, b)
+    q = ((w[:, :, None] >> (4 * np.arange(8, dtype=np.uint32))) & 0xF).reshape(64, 256).astype(np.float64)
+    ref = (np.repeat(s.astype(np.float64), 64, axis=1) * q + np.repeat(b.astype(np.float64), 64, axis=1)).astype(np.float16)
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16))
+    assert np.abs(got.astype(np.float32) - O.dequant_q4(w, s, b)).max() <= 1e-3   # the f32 dequantiser, one half ulp apart at most
+
+
 def test_golden_vectors():
     path = os.path.join(ROOT, "tests", "golden", "oracle_golden.json")
     g = json.load(open(path))
