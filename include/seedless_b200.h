@@ -73,7 +73,11 @@ typedef struct sl_config {
  * first), .s/.b fp16 [N,K/64] (SeedlessMetalForward.swift:219-221).  The data is copied.
  * "embed" may instead be given as the checkpoint's 4-bit table "embed.w/.s/.b" ([vocab,hidden]);
  * it is expanded once into the fp16 table with the reference's per-row arithmetic
- * (embed_rows_q4, SeedlessFusedVerify.swift:556-570), so lookups give the same halves. */
+ * (embed_rows_q4, SeedlessFusedVerify.swift:556-570), so lookups give the same halves.
+ * "L<i>.moe.router" and "L<i>.moe.shared_gate" may instead be given, per layer, in the checkpoint's
+ * 8-bit group-64 layout: "L<i>.moe.router.w" (bytes [E,H]), ".s/.b" (fp16 [E,H/64]),
+ * "L<i>.moe.shared_gate.w" (bytes [H]), ".s/.b" (fp16 [H/64]) - all six or none; the router kernel then
+ * runs the reference's 8-bit GEMV arithmetic (qmm8, SeedlessMetalForward.swift:384-434). */
 typedef struct sl_weight_desc {
     const char* name;
     const void* data;

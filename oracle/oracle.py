@@ -122,6 +122,30 @@ def dequant_q4_half(packed, s, b):
     return out
 
 
+def qmm8(x, w8, s, b):
+    """8-bit group-64 GEMV (qmm8, SeedlessMetalForward.swift:384-434); w8 uint8 [N,K]."""
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    M, K = x.shape
+    N = w8.shape[0]
+    y = np.empty((M, N), dtype=np.float16)
+    lib().orc_qmm8(_p(x), _p(np.ascontiguousarray(w8)), _p(np.ascontiguousarray(s)), _p(np.ascontiguousarray(b)),
+                   C.c_int(M), C.c_int(K), C.c_int(N), _p(y))
+    return y
+
+
+def quantize_q8(w):
+    """fp16 [N,K] -> (uint8 [N,K], fp16 scales [N,K/64], fp16 biases [N,K/64]): affine 8-bit per group of 64
+    (test input maker; any bytes / scales / biases are valid input to qmm8)."""
+    w = np.asarray(w, dtype=np.float32)
+    N, K = w.shape
+    g = w.reshape(N, K // 64, 64)
+    lo, hi = g.min(axis=2), g.max(axis=2)
+    scale = np.maximum((hi - lo) / 255.0, 1e-7).astype(np.float16)
+    bias = lo.astype(np.float16)
+    q = np.clip(np.rint((g - bias.astype(np.float32)[:, :, None]) / scale.astype(np.float32)[:, :, None]), 0, 255).astype(np.uint8)
+    return q.reshape(N, K), scale, bias
+
+
 def qmm4(x, packed, s, b):
     x = np.ascontiguousarray(x, dtype=np.float16)
     M, K = x.shape
@@ -166,6 +190,12 @@ class Model:
         self.seed = seed
         make = lib().orc_model_create_lazy if lazy_experts else lib().orc_model_create
         self.h = make(C.byref(cfg), C.c_uint64(seed))
+
+    def set_router_q8(self, layer, rw, rs, rb, gw, gs, gb):
+        """Give one layer its router / shared gate in the checkpoint's 8-bit group-64 layout."""
+        keep = [np.ascontiguousarray(a) for a in (rw, rs, rb, gw, gs, gb)]
+        rc = lib().orc_model_set_router_q8(C.c_void_p(self.h), C.c_int(layer), *[_p(a) for a in keep])
+        assert rc == 0
 
     def close(self):
         if self.h:

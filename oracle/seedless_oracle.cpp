@@ -255,6 +255,30 @@ static inline float fdot_row(const h16* x, const h16* wrow, int K) {
         }
     return bfly_sum32(lane);
 }
+// 8-bit group-64 GEMV, one output element (qmm8 / qd8 / ld8, swift/Sources/QwispCore/SeedlessMetalForward.swift:373-434):
+// lane l owns 8 consecutive inputs of each 256-wide block; per block sum = x_0+..+x_7 and
+// accum = sum of x_i * byte_i, both sequential in f32; the lane adds scale*accum + sum*bias;
+// lanes are combined by the butterfly.
+static inline float q8dot_row(const h16* x, const uint8_t* wrow, const h16* srow, const h16* brow, int K) {
+    float lane[32];
+    for (int l = 0; l < 32; ++l) lane[l] = 0.0f;
+    for (int kb = 0; kb < K; kb += 256)
+        for (int l = 0; l < 32; ++l) {
+            const h16* xp = x + kb + l * 8; const uint8_t* wp = wrow + kb + l * 8;
+            float sum = 0.0f, accum = 0.0f;
+            for (int i = 0; i < 8; ++i) { float v = h2f(xp[i]); sum += v; accum += v * (float)wp[i]; }
+            int g = (kb + l * 8) / 64;
+            lane[l] += h2f(srow[g]) * accum + sum * h2f(brow[g]);
+        }
+    return bfly_sum32(lane);
+}
+extern "C" void orc_qmm8(const h16* x, const uint8_t* w, const h16* scales, const h16* biases, int M, int K, int N, h16* y) {
+    int G = K / 64;
+#pragma omp parallel for schedule(static)
+    for (int n = 0; n < N; ++n)
+        for (int m = 0; m < M; ++m)
+            y[(int64_t)m * N + n] = f2h(q8dot_row(x + (int64_t)m * K, w + (int64_t)n * K, scales + (int64_t)n * G, biases + (int64_t)n * G, K));
+}
 extern "C" void orc_fmm(const h16* x, const h16* w, int M, int K, int N, h16* y) {
 #pragma omp parallel for schedule(static)
     for (int n = 0; n < N; ++n)
@@ -358,6 +382,9 @@ struct Layer {
     std::vector<h16> q_norm, k_norm;
     // MoE
     std::vector<h16> router, shared_gate;
+    // 8-bit group-64 form of the two (the checkpoint's layout), used when q8 is set
+    bool q8 = false;
+    std::vector<uint8_t> router_q8, sg_q8; std::vector<h16> router_qs, router_qb, sg_qs, sg_qb;
     Q4 gate_proj, up_proj, down_proj;             // [E*I,H], [E*I,H], [E*H,I]
     Q4 sh_gate, sh_up, sh_down;
     std::vector<uint8_t> expert_ready;            // lazy models: experts generated on first use
@@ -450,6 +477,18 @@ extern "C" void* orc_model_create(const OrcConfig* cfg, uint64_t seed) { return 
 // eager model); used to time a few steps of the full-size model without generating 18 GB first
 extern "C" void* orc_model_create_lazy(const OrcConfig* cfg, uint64_t seed) { return model_create(cfg, seed, true); }
 extern "C" void orc_model_destroy(void* m) { delete (Model*)m; }
+// replace one layer's router and shared gate by their 8-bit group-64 form (bytes [E,H] / [H], fp16 scales and biases per 64 inputs)
+extern "C" int orc_model_set_router_q8(void* m, int layer, const uint8_t* rw, const h16* rs, const h16* rb,
+                                       const uint8_t* gw, const h16* gs, const h16* gb) {
+    Model* M = (Model*)m;
+    if (layer < 0 || layer >= M->c.n_layers) return -1;
+    Layer& L = M->layers[layer];
+    const size_t H = (size_t)M->c.hidden, E = (size_t)M->c.n_experts, G = H / 64;
+    L.router_q8.assign(rw, rw + E * H); L.router_qs.assign(rs, rs + E * G); L.router_qb.assign(rb, rb + E * G);
+    L.sg_q8.assign(gw, gw + H); L.sg_qs.assign(gs, gs + G); L.sg_qb.assign(gb, gb + G);
+    L.q8 = true;
+    return 0;
+}
 extern "C" int orc_model_tensor(void* m, const char* name, const void** ptr, uint64_t* nbytes) {
     Model* M = (Model*)m; auto it = M->index.find(name);
     if (it == M->index.end()) return -1;
@@ -493,7 +532,8 @@ static void qmm_rows(const h16* x, const Q4& q, int64_t row0, int N, h16* y) {  
 static void moe_block_row(const Model* M, Layer& L, const h16* x, h16* out, int32_t* inds_out, h16* scores_out) {
     const OrcConfig& c = M->c; int H = c.hidden, E = c.n_experts, I = c.moe_inter, T = c.top_k;
     std::vector<h16> logits(E), g(I), u(I), h(I), d((size_t)T * H), y(H), sg(I), su(I), sh(I), sy(H);
-    orc_fmm(x, L.router.data(), 1, H, E, logits.data());
+    if (L.q8) orc_qmm8(x, L.router_q8.data(), L.router_qs.data(), L.router_qb.data(), 1, H, E, logits.data());
+    else orc_fmm(x, L.router.data(), 1, H, E, logits.data());
     std::vector<int32_t> inds(T); std::vector<h16> scores(T);
     route_row(logits.data(), E, T, inds.data(), scores.data());
     for (int k = 0; k < T; ++k) {
@@ -513,7 +553,7 @@ static void moe_block_row(const Model* M, Layer& L, const h16* x, h16* out, int3
     qmm_rows(x, L.sh_up, 0, I, su.data());
     swiglu_h(sg.data(), su.data(), I, sh.data());
     qmm_rows(sh.data(), L.sh_down, 0, H, sy.data());
-    h16 sgl = f2h(fdot_row(x, L.shared_gate.data(), H));
+    h16 sgl = L.q8 ? f2h(q8dot_row(x, L.sg_q8.data(), L.sg_qs.data(), L.sg_qb.data(), H)) : f2h(fdot_row(x, L.shared_gate.data(), H));
     h16 s = sigmoid_h(sgl);                                              // SFV:480-483
     for (int n = 0; n < H; ++n) out[n] = hadd(y[n], hmul(s, sy[n]));
     if (inds_out) for (int k = 0; k < T; ++k) inds_out[k] = inds[k];

@@ -36,6 +36,9 @@ struct LayerW {
     Q4W out_proj;                   // GDN out_proj / attention o_proj
     const __half *q_norm = nullptr, *k_norm = nullptr;
     const __half *router = nullptr, *shared_gate = nullptr;
+    // 8-bit group-64 router / shared gate (the checkpoint's layout); when set they are used instead of the fp16 pair
+    const uint8_t *router_q8 = nullptr, *sg_q8 = nullptr;
+    const __half *router_qs = nullptr, *router_qb = nullptr, *sg_qs = nullptr, *sg_qb = nullptr;
     Q4W gate, up, down, sh_gate, sh_up, sh_down;
     // fragment-major copies the kernels read (gate/up fused into paired tiles)
     Q4R r_in, r_out, r_gu, r_down, r_sh_gu, r_sh_down;
@@ -491,6 +494,8 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     cudaStream_t st = e->stream;
     RouterArgs ra{}; ra.h = rows; ra.ldh = ld; ra.norm_w = apply_norm ? L.post_norm : nullptr; ra.eps = e->cfg.rms_eps;
     ra.router = L.router; ra.shared_gate = L.shared_gate; ra.M = M; ra.H = e->H; ra.E = e->E;
+    ra.router_q8 = L.router_q8; ra.router_qs = L.router_qs; ra.router_qb = L.router_qb;
+    ra.sg_q8 = L.sg_q8; ra.sg_qs = L.sg_qs; ra.sg_qb = L.sg_qb;
     ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
     ra.topk = e->topk; ra.inds = e->inds; ra.scores = e->scores; ra.lists = e->lists; ra.counter = e->counters + 1;
     if (e->ep_step) { enqueue_moe_ep(e, L, ra, M, resid, plain_out); return; }
@@ -730,9 +735,41 @@ int32_t sl_engine_create(const sl_config* cfg, const sl_weight_desc* weights, in
         if (rc) { sl_engine_destroy(e); return rc; }
         seen["embed"] = true;
     }
+    // the checkpoint's 8-bit router and shared gate ("L<i>.moe.router.w/.s/.b", "L<i>.moe.shared_gate.w/.s/.b":
+    // bytes [E,H] / [H], fp16 scales and biases per 64 inputs) are accepted, per layer, in place of the fp16 pair
+    std::vector<char> taken((size_t)n_weights, 0);
+    for (int li = 0; li < (int)e->layers.size(); ++li) {
+        LayerW& L = e->layers[li];
+        const std::string base = "L" + std::to_string(li) + ".moe.";
+        const char* suffix[6] = {"router.w", "router.s", "router.b", "shared_gate.w", "shared_gate.s", "shared_gate.b"};
+        const uint64_t H = (uint64_t)e->H, E = (uint64_t)e->E;
+        const uint64_t want[6] = {E * H, E * (H / 64) * 2, E * (H / 64) * 2, H, (H / 64) * 2, (H / 64) * 2};
+        int idx[6]; int found = 0;
+        for (int k = 0; k < 6; ++k) {
+            idx[k] = -1;
+            const std::string nm = base + suffix[k];
+            for (int i = 0; i < n_weights; ++i) if (weights[i].name && nm == weights[i].name) { idx[k] = i; ++found; break; }
+        }
+        if (!found) continue;
+        void* dst[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+        rc = (found == 6) ? SL_OK : SL_ERR_INVALID;
+        for (int k = 0; k < 6 && !rc; ++k) {
+            const sl_weight_desc& d = weights[idx[k]];
+            if (!d.data || d.nbytes != want[k]) { rc = SL_ERR_INVALID; break; }
+            uint8_t* p8 = nullptr;
+            if ((rc = dalloc(e, &p8, (size_t)want[k]))) break;
+            if (cudaMemcpy(p8, d.data, want[k], d.on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice) != cudaSuccess) { rc = SL_ERR_CUDA; break; }
+            dst[k] = p8; taken[(size_t)idx[k]] = 1;
+        }
+        if (rc) { sl_engine_destroy(e); return rc; }
+        L.router_q8 = (const uint8_t*)dst[0]; L.router_qs = (const __half*)dst[1]; L.router_qb = (const __half*)dst[2];
+        L.sg_q8 = (const uint8_t*)dst[3]; L.sg_qs = (const __half*)dst[4]; L.sg_qb = (const __half*)dst[5];
+        seen[base + "router"] = true; seen[base + "shared_gate"] = true;
+    }
     for (int i = 0; i < n_weights; ++i) {
         const sl_weight_desc& d = weights[i];
-        if (&d == eq[0] || &d == eq[1] || &d == eq[2]) continue;
+        if (&d == eq[0] || &d == eq[1] || &d == eq[2] || taken[(size_t)i]) continue;
+        if (d.name && seen.count(d.name) && d.name[0] == 'L') { sl_engine_destroy(e); return SL_ERR_INVALID; }   // both forms given
         if (d.name && seen.count(d.name) && !strcmp(d.name, "embed")) { sl_engine_destroy(e); return SL_ERR_INVALID; }   // both forms given
         auto it = d.name ? e->tensors.find(d.name) : e->tensors.end();
         if (it == e->tensors.end()) { sl_engine_destroy(e); return SL_ERR_NOT_FOUND; }

@@ -542,7 +542,11 @@ __device__ __noinline__ void route_row_warp(const __half* lrow, int E, int topk,
 
 // MULTI: several rows per call (one warp per row in the norm); the one-row instantiation leaves that code
 // out, so it does not compete for registers with the router rows held across the wait
-template <bool MULTI>
+// Q8: the router rows and the shared gate are 8-bit group-64 (the checkpoint's layout).  Lane l owns 8
+// consecutive inputs of every 256-wide block, as in the reference's 8-bit GEMV
+// (SeedlessMetalForward.swift:378-434): per block accum = sum of x_i * byte_i (i ascending), the lane adds
+// scale * accum + (sum of x_i) * bias, lanes are summed by the butterfly.
+template <bool MULTI, bool Q8>
 __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __half* ps = reinterpret_cast<__half*>(smem);            // [8][H]
@@ -556,12 +560,25 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     // router rows and norm weights do not depend on the kernel before: loaded ahead of the wait
     uint4 pv = make_uint4(0, 0, 0, 0), pw = make_uint4(0, 0, 0, 0);
     if (a.norm_w && tid * 8 < a.H) pw = *reinterpret_cast<const uint4*>(a.norm_w + tid * 8);
-    uint4 wreg[16];
-    const __half* wrow = tail ? a.shared_gate : (a.router + (size_t)e * a.H);
+    uint4 wreg[16];                                          // fp16 form: 8 halves per block
+    uint2 qreg[16]; __half2 sbreg[16];                        // 8-bit form: 8 bytes per block, (scale, bias) of the lane's group
     const bool wvalid = tail ? (warp == 0) : (e < a.E);
+    if constexpr (Q8) {
+        const uint8_t* qrow = tail ? a.sg_q8 : (a.router_q8 + (size_t)e * a.H);
+        const __half* srow = tail ? a.sg_qs : (a.router_qs + (size_t)e * (a.H >> 6));
+        const __half* brow = tail ? a.sg_qb : (a.router_qb + (size_t)e * (a.H >> 6));
 #pragma unroll
-    for (int kb = 0; kb < 16; ++kb)
-        wreg[kb] = (wvalid && kb < nblk) ? *reinterpret_cast<const uint4*>(wrow + kb * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+        for (int kb = 0; kb < 16; ++kb) {
+            const bool ok = wvalid && kb < nblk;
+            qreg[kb] = ok ? *reinterpret_cast<const uint2*>(qrow + kb * 256 + lane * 8) : make_uint2(0, 0);
+            sbreg[kb] = ok ? __halves2half2(srow[kb * 4 + (lane >> 3)], brow[kb * 4 + (lane >> 3)]) : __halves2half2(f2h(0.f), f2h(0.f));
+        }
+    } else {
+        const __half* wrow = tail ? a.shared_gate : (a.router + (size_t)e * a.H);
+#pragma unroll
+        for (int kb = 0; kb < 16; ++kb)
+            wreg[kb] = (wvalid && kb < nblk) ? *reinterpret_cast<const uint4*>(wrow + kb * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+    }
     pdl_wait();
     pdl_launch_dependents();
     if (a.norm_w && tid * 8 < a.H) pv = *reinterpret_cast<const uint4*>(a.h + tid * 8);
@@ -625,9 +642,22 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
                     if (kb < nblk) {
                         uint4 xv = *reinterpret_cast<const uint4*>(xrow + kb * 256 + lane * 8);
                         const __half* xh = reinterpret_cast<const __half*>(&xv);
-                        const __half* wh = reinterpret_cast<const __half*>(&wreg[kb]);
+                        if constexpr (Q8) {
+                            float sum = 0.f, accum = 0.f;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) acc = fmaf(h2f(xh[i]), h2f(wh[i]), acc);   // product exact in f32
+                            for (int i = 0; i < 8; ++i) {
+                                const float xf = h2f(xh[i]);
+                                const unsigned q = ((i < 4 ? qreg[kb].x : qreg[kb].y) >> (8 * (i & 3))) & 0xffu;
+                                sum = __fadd_rn(sum, xf);
+                                accum = fmaf(xf, (float)q, accum);                              // product exact in f32
+                            }
+                            const float2 sb = __half22float2(sbreg[kb]);
+                            acc = __fadd_rn(acc, __fadd_rn(__fmul_rn(sb.x, accum), __fmul_rn(sum, sb.y)));
+                        } else {
+                            const __half* wh = reinterpret_cast<const __half*>(&wreg[kb]);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc = fmaf(h2f(xh[i]), h2f(wh[i]), acc);   // product exact in f32
+                        }
                     }
                 }
                 float d = warp_sum(acc);
@@ -678,8 +708,10 @@ void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl) {
     size_t smem = (size_t)8 * a.H * 2 + 64;
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(k_moe_router<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        cudaFuncSetAttribute(k_moe_router<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_moe_router<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_moe_router<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_moe_router<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        cudaFuncSetAttribute(k_moe_router<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -688,8 +720,9 @@ void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl) {
     set_pdl(cfg, attr, pdl);
     RouterArgs copy = a;
     ProfScope ps("k_moe_router", (double)(a.E + 1) * a.H * 2 + (double)a.M * a.H * 4, st);
-    if (a.M == 1) cudaLaunchKernelEx(&cfg, k_moe_router<false>, copy);
-    else cudaLaunchKernelEx(&cfg, k_moe_router<true>, copy);
+    const bool q8 = a.router_q8 != nullptr;
+    if (a.M == 1) { if (q8) cudaLaunchKernelEx(&cfg, k_moe_router<false, true>, copy); else cudaLaunchKernelEx(&cfg, k_moe_router<false, false>, copy); }
+    else { if (q8) cudaLaunchKernelEx(&cfg, k_moe_router<true, true>, copy); else cudaLaunchKernelEx(&cfg, k_moe_router<true, false>, copy); }
     COUNT_LAUNCH();
 }
 

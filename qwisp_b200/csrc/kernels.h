@@ -35,6 +35,9 @@ struct RouterArgs {
     const __half* norm_w; float eps;     // post-attention norm (nullptr: rows are already normed)
     const __half* router;                // fp16 [E][H]
     const __half* shared_gate;           // fp16 [H]
+    // the checkpoint's 8-bit group-64 form of the two (set all six or none; they replace the fp16 pair)
+    const uint8_t* router_q8 = nullptr; const __half *router_qs = nullptr, *router_qb = nullptr;   // [E][H] bytes, [E][H/64] scales / biases
+    const uint8_t* sg_q8 = nullptr; const __half *sg_qs = nullptr, *sg_qb = nullptr;               // [H] bytes, [H/64]
     int M, H, E;
     __half* p;                           // normed rows out [M][H]
     __half* logits;                      // [M][E]

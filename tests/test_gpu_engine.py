@@ -305,6 +305,48 @@ def test_engine_accepts_q4_embedding(tiny_oracle):
         a.close(); bb.close()
 
 
+def test_engine_accepts_q8_router_and_shared_gate(tiny_oracle):
+    """The checkpoint's 8-bit group-64 router / shared gate handed over as L<i>.moe.router.w/.s/.b and
+    L<i>.moe.shared_gate.w/.s/.b (qmm8, SeedlessMetalForward.swift:384-434): routing indices bit-exact
+    against the CPU restatement with the same 8-bit tensors, MoE output and model logits within tolerance."""
+    import qwisp_b200 as Q
+    from oracle import oracle as O
+    from conftest import oracle_model
+    cfg = Q.config(**TINY, max_rows=16, max_streams=2, kv_page_size=32, kv_pages=8)
+    H, E, nl = TINY["hidden"], TINY["n_experts"], TINY["n_layers"]
+    tensors = {n: tiny_oracle.tensor_bytes(n).copy() for n in tiny_oracle.tensor_names()}
+    ref = oracle_model(TINY)                     # own copy: the shared fixture keeps its fp16 router
+    for i in range(nl):
+        r16 = tensors.pop(f"L{i}.moe.router").view(np.float16).reshape(E, H)
+        g16 = tensors.pop(f"L{i}.moe.shared_gate").view(np.float16).reshape(1, H)
+        rw, rs, rb = O.quantize_q8(r16)
+        gw, gs, gb = O.quantize_q8(g16)
+        tensors.update({f"L{i}.moe.router.w": rw, f"L{i}.moe.router.s": rs, f"L{i}.moe.router.b": rb,
+                        f"L{i}.moe.shared_gate.w": gw, f"L{i}.moe.shared_gate.s": gs, f"L{i}.moe.shared_gate.b": gb})
+        ref.set_router_q8(i, rw, rs, rb, gw, gs, gb)
+    eng = Q.Engine.from_tensors(cfg, tensors)
+    try:
+        for T in (1, 9):
+            x = O.synth_f16(SEED, f"q8router.x{T}", T * H, 0.0, 1.0).reshape(T, H)
+            for layer in (0, nl - 1):
+                out, inds, scores = Q.ops.moe_block(eng, layer, x)
+                ro, ri, rs_ = ref.moe_block(layer, x)
+                assert np.array_equal(inds, ri), ("routing indices differ", T, layer)
+                assert f16_report(scores, rs_)["max_abs"] <= 2e-3
+                assert f16_report(out, ro)["max_abs"] <= 2e-2
+        p = prompt(TINY["vocab"], 7, "q8router")
+        lg = eng.stream(32).step_logits(p)
+        _, rl = ref.stream(32).step(p, want_logits=True)
+        rep = f16_report(lg, rl)
+        print("q8 router model logits", rep)
+        assert rep["max_abs"] <= 2e-2, rep
+        part = dict(tensors); part.pop("L0.moe.shared_gate.b")
+        with pytest.raises(Q.SeedlessError):
+            Q.Engine.from_tensors(cfg, part)
+    finally:
+        eng.close(); ref.close()
+
+
 def test_step_sample_rows_greedy_equals_argmax(mini_engine):
     """At temperature 0 the sampling step returns the argmax step's tokens (stepSampleRows with
     invT <= 0, SamplerGPU.swift:13-15) and leaves the caches in the same state."""

@@ -215,6 +215,18 @@ def test_q4_rows_to_half_single_rounding():
     assert np.abs(got.astype(np.float32) - O.dequant_q4(w, s, b)).max() <= 1e-3   # the f32 dequantiser, one half ulp apart at most
 
 
+def test_qmm8_against_float64():
+    """8-bit group-64 GEMV (qmm8, SeedlessMetalForward.swift:384-434) against x . (scale*q+bias)^T in float64."""
+    w16 = O.synth_f16(6, "q8.w", 48 * 512, 0.0, 0.02).reshape(48, 512)
+    q, s, b = O.quantize_q8(w16)
+    x = O.synth_f16(6, "q8.x", 3 * 512, 0.0, 1.0).reshape(3, 512)
+    y = O.qmm8(x, q, s, b)
+    deq = np.repeat(s.astype(np.float64), 64, axis=1) * q.astype(np.float64) + np.repeat(b.astype(np.float64), 64, axis=1)
+    ref = x.astype(np.float64) @ deq.T
+    assert np.abs(y.astype(np.float64) - ref).max() <= 2e-3
+    assert np.abs(deq - w16.astype(np.float64)).max() <= 1e-3          # the quantiser used as the test input maker
+
+
 def test_golden_vectors():
     path = os.path.join(ROOT, "tests", "golden", "oracle_golden.json")
     g = json.load(open(path))
