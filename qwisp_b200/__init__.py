@@ -8,3 +8,4 @@ kernels; there is no CPU path and importing the library without it built fails l
 from ._lib import SeedlessError, config, lib, synth_spec  # noqa: F401
 from .engine import Engine, Stream, SpecBackend, LaneBatchSlots  # noqa: F401
 from . import ops  # noqa: F401
+from . import checkpoint  # noqa: F401

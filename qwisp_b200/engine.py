@@ -54,6 +54,12 @@ class Engine:
             raise SeedlessError(rc, "sl_engine_create")
         return cls(cfg, h)
 
+    @classmethod
+    def from_checkpoint(cls, cfg, paths):
+        """Engine over safetensors shards in the reference's tensor naming (SeedlessEngine.swift:33-143)."""
+        from .checkpoint import load_checkpoint
+        return cls.from_tensors(cfg, load_checkpoint(paths, cfg.n_layers, cfg.attn_every))
+
     def close(self):
         if self._h:
             lib().sl_engine_destroy(self._h)
