@@ -77,7 +77,9 @@ typedef struct sl_config {
  * "L<i>.moe.router" and "L<i>.moe.shared_gate" may instead be given, per layer, in the checkpoint's
  * 8-bit group-64 layout: "L<i>.moe.router.w" (bytes [E,H]), ".s/.b" (fp16 [E,H/64]),
  * "L<i>.moe.shared_gate.w" (bytes [H]), ".s/.b" (fp16 [H/64]) - all six or none; the router kernel then
- * runs the reference's 8-bit GEMV arithmetic (qmm8, SeedlessMetalForward.swift:384-434). */
+ * runs the reference's 8-bit GEMV arithmetic (qmm8, SeedlessMetalForward.swift:384-434).
+ * "L<i>.gdn.norm.f32" (f32 [128]) may replace "L<i>.gdn.norm": that layer's gated norm then keeps the
+ * normed value in f32, the reference's behaviour for an f32 weight (SeedlessFusedVerify.swift:2815-2818). */
 typedef struct sl_weight_desc {
     const char* name;
     const void* data;

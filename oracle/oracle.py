@@ -191,6 +191,11 @@ class Model:
         make = lib().orc_model_create_lazy if lazy_experts else lib().orc_model_create
         self.h = make(C.byref(cfg), C.c_uint64(seed))
 
+    def set_gdn_norm_f32(self, layer, w):
+        """Give one GDN layer an f32 norm weight (the reference then keeps the normed value in f32)."""
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        assert w.size == 128 and lib().orc_model_set_gdn_norm_f32(C.c_void_p(self.h), C.c_int(layer), _p(w)) == 0
+
     def set_router_q8(self, layer, rw, rs, rb, gw, gs, gb):
         """Give one layer its router / shared gate in the checkpoint's 8-bit group-64 layout."""
         keep = [np.ascontiguousarray(a) for a in (rw, rs, rb, gw, gs, gb)]

@@ -377,6 +377,7 @@ struct Layer {
     Q4 in_qkv, in_z, in_b, in_a, gdn_out;
     std::vector<float> conv_w, A_log, dt_bias;
     std::vector<h16> gdn_norm;
+    std::vector<float> gdn_norm32;                // set: the gated norm runs with this f32 weight (the reference's promoted variant)
     // attention
     Q4 q_proj, k_proj, v_proj, o_proj;
     std::vector<h16> q_norm, k_norm;
@@ -477,6 +478,13 @@ extern "C" void* orc_model_create(const OrcConfig* cfg, uint64_t seed) { return 
 // eager model); used to time a few steps of the full-size model without generating 18 GB first
 extern "C" void* orc_model_create_lazy(const OrcConfig* cfg, uint64_t seed) { return model_create(cfg, seed, true); }
 extern "C" void orc_model_destroy(void* m) { delete (Model*)m; }
+// give one GDN layer an f32 norm weight [128]
+extern "C" int orc_model_set_gdn_norm_f32(void* m, int layer, const float* w) {
+    Model* M = (Model*)m;
+    if (layer < 0 || layer >= M->c.n_layers) return -1;
+    M->layers[layer].gdn_norm32.assign(w, w + 128);
+    return 0;
+}
 // replace one layer's router and shared gate by their 8-bit group-64 form (bytes [E,H] / [H], fp16 scales and biases per 64 inputs)
 extern "C" int orc_model_set_router_q8(void* m, int layer, const uint8_t* rw, const h16* rs, const h16* rb,
                                        const uint8_t* gw, const h16* gs, const h16* gb) {
@@ -633,7 +641,8 @@ static void gdn_row(const Model* M, const Layer& L, LayerState& st, const h16* x
         const h16* yp = y.data() + hv * DV;
         float inv = rms_inv(yp, DV, c.rms_eps);
         for (int d = 0; d < DV; ++d) {
-            float nrm = h2f(hmul(L.gdn_norm[d], f2h(h2f(yp[d]) * inv)));
+            // f32 weight: normed = w * (y*inv) kept in f32 (SFV:766-813 with a float weight, SFV:2815-2818)
+            float nrm = L.gdn_norm32.empty() ? h2f(hmul(L.gdn_norm[d], f2h(h2f(yp[d]) * inv))) : L.gdn_norm32[d] * (h2f(yp[d]) * inv);
             float zf = h2f(z[hv * DV + d]);
             gated[hv * DV + d] = f2h((zf * sigmoid_f(zf)) * nrm);
         }

@@ -6,7 +6,8 @@ The reference builds its engine from a `WeightStore` by name
 `.weight/.scales/.biases` triples in the MLX affine layout.  `name_map` restates that table for this
 library's names; nothing is re-quantised: 4-bit tensors, the 4-bit embedding and the 8-bit router /
 shared-expert gate go to the engine in the layout they are stored in.  Only the small plain tensors
-are cast (`conv1d.weight`, `A_log`, `dt_bias` to f32; norm weights to f16).
+are cast (`conv1d.weight`, `A_log`, `dt_bias` to f32; norm weights to f16, except a GDN norm weight
+stored as f32, which is handed over as f32 so that norm runs in f32 as in the reference).
 
 The safetensors container (8-byte little-endian header length, a JSON header with dtype / shape /
 data_offsets per tensor, then the raw bytes) is read here with numpy only.
@@ -131,6 +132,9 @@ def load_checkpoint(paths, n_layers, attn_every):
         if src not in store:
             raise KeyError(src)
         arr, dt = store[src]
+        if dst.endswith(".gdn.norm") and dt == "F32":     # the reference promotes this norm to f32 (SeedlessFusedVerify.swift:2815-2818)
+            out[dst + ".f32"] = np.ascontiguousarray(arr, dtype=np.float32).reshape(-1)
+            continue
         if dst.endswith(_F32):
             arr = _as_f32(arr, dt)                      # conv1d.weight [C,K,1] -> f32 [C,K] (same order)
         elif dst.endswith(_F16):

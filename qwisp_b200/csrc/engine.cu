@@ -33,6 +33,7 @@ struct LayerW {
     Q4W in_proj;                    // GDN: qkv|z|b|a rows; attention: q|k|v rows
     const float *conv_w = nullptr, *A_log = nullptr, *dt_bias = nullptr;
     const __half* gdn_norm = nullptr;
+    const float* gdn_norm32 = nullptr;   // set when the checkpoint stores this weight as f32: the gated norm then runs in f32
     Q4W out_proj;                   // GDN out_proj / attention o_proj
     const __half *q_norm = nullptr, *k_norm = nullptr;
     const __half *router = nullptr, *shared_gate = nullptr;
@@ -537,8 +538,8 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
         GdnArgs g{}; g.inproj = e->inproj; g.ld = e->gdn_in; g.conv_w = L.conv_w; g.A_log = L.A_log; g.dt_bias = L.dt_bias;
         g.Hk = c.gdn_k_heads; g.Hv = c.gdn_v_heads; g.eps = c.rms_eps; g.tab = e->tab; g.gdn_index = L.type_index; g.segs = e->segs; g.y = e->mix;
         launch_gdn_core(g, nsegs, st, e->use_pdl);
-        o.x = e->mix; o.ldx = e->valDim; o.nw = L.gdn_norm; o.z = e->inproj + e->convDim; o.ldz = e->gdn_in;
-        launch_dense(PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, e->use_pdl);
+        o.x = e->mix; o.ldx = e->valDim; o.nw = L.gdn_norm; o.nw32 = L.gdn_norm32; o.z = e->inproj + e->convDim; o.ldz = e->gdn_in;
+        launch_dense(L.gdn_norm32 ? PRO_NORMGATE32 : PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, e->use_pdl);
     } else {
         AttnArgs a{}; a.inproj = e->inproj; a.ld = e->attn_in; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.NH = c.attn_heads; a.KV = c.attn_kv_heads;
         a.eps = c.rms_eps; a.theta = c.rope_theta; a.tab = e->tab; a.attn_index = L.type_index; a.n_attn_layers = e->n_attn > 0 ? e->n_attn : 1;
@@ -765,6 +766,26 @@ int32_t sl_engine_create(const sl_config* cfg, const sl_weight_desc* weights, in
         L.router_q8 = (const uint8_t*)dst[0]; L.router_qs = (const __half*)dst[1]; L.router_qb = (const __half*)dst[2];
         L.sg_q8 = (const uint8_t*)dst[3]; L.sg_qs = (const __half*)dst[4]; L.sg_qb = (const __half*)dst[5];
         seen[base + "router"] = true; seen[base + "shared_gate"] = true;
+    }
+    // "L<i>.gdn.norm.f32" (f32 [128]) in place of "L<i>.gdn.norm": the gated norm of that layer keeps its
+    // normed value in f32, as the reference does for an f32 weight (SeedlessFusedVerify.swift:2815-2818)
+    for (int i = 0; i < n_weights; ++i) {
+        const sl_weight_desc& d = weights[i];
+        const size_t len = d.name ? strlen(d.name) : 0;
+        if (len < 14 || strcmp(d.name + len - 13, ".gdn.norm.f32")) continue;
+        const std::string base(d.name, len - 4);
+        auto it = e->tensors.find(base);
+        if (it == e->tensors.end()) { sl_engine_destroy(e); return SL_ERR_NOT_FOUND; }
+        if (!d.data || d.nbytes != GDN_DV * sizeof(float)) { sl_engine_destroy(e); return SL_ERR_INVALID; }
+        float hostw[GDN_DV]; __half hosth[GDN_DV];
+        if (cudaMemcpy(hostw, d.data, sizeof(hostw), d.on_device ? cudaMemcpyDeviceToHost : cudaMemcpyHostToHost) != cudaSuccess) { sl_engine_destroy(e); return SL_ERR_CUDA; }
+        for (int k = 0; k < GDN_DV; ++k) hosth[k] = __float2half_rn(hostw[k]);
+        float* w32 = nullptr;
+        if ((rc = dalloc(e, &w32, (size_t)GDN_DV))) { sl_engine_destroy(e); return rc; }
+        if (cudaMemcpy(w32, hostw, sizeof(hostw), cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(it->second.ptr, hosth, sizeof(hosth), cudaMemcpyHostToDevice) != cudaSuccess) { sl_engine_destroy(e); return SL_ERR_CUDA; }
+        for (LayerW& L : e->layers) if ((const void*)L.gdn_norm == it->second.ptr) L.gdn_norm32 = w32;
+        taken[(size_t)i] = 1; seen[base] = true;
     }
     for (int i = 0; i < n_weights; ++i) {
         const sl_weight_desc& d = weights[i];

@@ -29,7 +29,8 @@
 
 namespace sl {
 
-enum { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_NORMGATE = 2 };
+enum { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_NORMGATE = 2, PRO_NORMGATE32 = 3 };   // NORMGATE32: gated norm with an f32 weight
+__host__ __device__ constexpr bool pro_is_normgate(int pro) { return pro == PRO_NORMGATE || pro == PRO_NORMGATE32; }
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_ARGMAX = 3 };
 
 constexpr int ROWS_PER_PASS = 8;     // activation rows per MMA pass (the 8 columns of m16n8k16)
@@ -78,6 +79,7 @@ struct StageSrc {
     const __half* nw;                // norm weight
     const __half* z; int ldz;        // gate input of the gated norm
     float eps;
+    const float* nw32 = nullptr;     // gated norm only: f32 norm weight (the norm then runs in f32, see stage_finish)
 };
 struct StageRegs { uint4 a[2], b[2], c[2]; };   // activations, norm weights, gate inputs of the first two units
 
@@ -97,7 +99,7 @@ __device__ __forceinline__ void stage_issue_const(StageRegs& sr, const StageSrc&
         int u = warp + j * nw;
         if (u < units) {
             const int k0 = ((u & ((1 << lgc) - 1)) << 8) + lane * 8;
-            sr.b[j] = *reinterpret_cast<const uint4*>(s.nw + (PRO == PRO_NORMGATE ? (k0 & 127) : k0));
+            sr.b[j] = *reinterpret_cast<const uint4*>(s.nw + (pro_is_normgate(PRO) ? (k0 & 127) : k0));
         }
     }
 }
@@ -111,7 +113,7 @@ __device__ __forceinline__ void stage_issue(StageRegs& sr, const StageSrc& s, in
         if (u < units) {
             const int col = u >> lgc, k0 = ((u & ((1 << lgc) - 1)) << 8) + lane * 8;
             sr.a[j] = stage_load(s, row0, col, k0);
-            if (PRO == PRO_NORMGATE) {
+            if (pro_is_normgate(PRO)) {
                 const int row = s.rows ? s.rows[col] : row0 + col;
                 sr.c[j] = __ldcg(reinterpret_cast<const uint4*>(s.z + (size_t)row * s.ldz + k0));
             }
@@ -177,7 +179,10 @@ __device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& 
             __half* oh = reinterpret_cast<__half*>(&o);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                float nrm = h2f(hmul_rn(wh[i], f2h(__fmul_rn(h2f(yh[i]), inv))));
+                // f32 weight: the normed value stays f32, w * (y * inv) (the reference's promoted variant,
+                // SeedlessFusedVerify.swift:766-813 with a float weight); fp16 weight: w * fp16(y * inv) as halves
+                const float yn = __fmul_rn(h2f(yh[i]), inv);
+                float nrm = (PRO == PRO_NORMGATE32) ? __fmul_rn(s.nw32[(k0 & 127) + i], yn) : h2f(hmul_rn(wh[i], f2h(yn)));
                 float zf = h2f(zh[i]);
                 oh[i] = f2h(__fmul_rn(__fmul_rn(zf, sigmoid_f(zf)), nrm));
             }

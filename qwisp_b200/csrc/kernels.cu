@@ -86,7 +86,7 @@ __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1) k_gemv(DenseArgs a) 
     // load/store queue.  Dependents are released only after the wait, so whatever a dependent
     // reads ahead of its own wait was written by a kernel that is complete.
     if (threadIdx.x == (NW - 1) * 32) wstage_issue(ws, a.q.wr, a.q.sr, (size_t)blockIdx.x * TPC << lg, nvu, ROUNDS);   // last warp: least staging work
-    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps};
+    StageSrc src{a.x, a.ldx, nullptr, a.nw, a.z, a.ldz, a.eps, a.nw32};
     StageRegs sregs;
     stage_issue_const<PRO>(sregs, src, mr, a.K);
     pdl_wait();
@@ -368,6 +368,8 @@ gemv_path:
     SL_CASE(PRO_RMSNORM, EPI_STORE)
     SL_CASE(PRO_NORMGATE, EPI_RESID)
     SL_CASE(PRO_NORMGATE, EPI_STORE)
+    SL_CASE(PRO_NORMGATE32, EPI_RESID)
+    SL_CASE(PRO_NORMGATE32, EPI_STORE)
 #undef SL_CASE
     fprintf(stderr, "seedless_b200: no dense kernel for prologue %d / epilogue %d\n", pro, epi);
     abort();

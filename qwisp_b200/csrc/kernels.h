@@ -14,6 +14,7 @@ struct DenseArgs {
     int N, K, M;                                                 // N outputs (= 16 * tiles)
     const __half* x; int ldx;                                    // activations (plain) / residual stream (rmsnorm) / y (normgate)
     const __half* nw;                                            // norm weight
+    const float* nw32 = nullptr;                                 // gated norm: f32 norm weight (norm in f32); nw keeps its fp16 cast
     const __half* z; int ldz;                                    // gate input of the gated norm
     float eps;
     __half* y; int ldy;                                          // output rows

@@ -10,7 +10,7 @@ from conftest import SEED, TINY, oracle_model
 
 def fake_checkpoint(path, model, geom):
     """Write the oracle model's tensors under the checkpoint's names; the embedding as a 4-bit table, the
-    router / shared gate 8-bit, the GDN norm weight as f32 (the case the reference promotes).  Returns the
+    router / shared gate 8-bit, layer 0's GDN norm weight as f32 (the case the reference promotes).  Returns the
     dict the loader is expected to give back."""
     from oracle import oracle as O
     from qwisp_b200 import checkpoint as CK
@@ -32,8 +32,9 @@ def fake_checkpoint(path, model, geom):
             a = a.view(np.uint8).view(np.float32)
             if dst.endswith("conv_w"):
                 a = a.reshape(-1, 4, 1)
-        elif dst.endswith(".gdn.norm"):
+        elif dst == "L0.gdn.norm":                               # stored f32: handed on as f32 (the promoted norm)
             a = a.view(np.uint8).view(np.float16).astype(np.float32)
+            want.pop(dst); want[dst + ".f32"] = a.copy()
         elif dst.endswith(".w"):
             a = a.view(np.uint8).view(np.uint32)
         else:
@@ -68,7 +69,7 @@ def test_checkpoint_roundtrip(tmp_path):
     assert set(got) == set(want)
     for n in want:
         assert np.array_equal(np.ascontiguousarray(got[n]).view(np.uint8).reshape(-1), np.ascontiguousarray(want[n]).view(np.uint8).reshape(-1)), n
-    assert got["L0.gdn.conv_w"].dtype == np.float32 and got["L0.gdn.norm"].dtype == np.float16
+    assert got["L0.gdn.conv_w"].dtype == np.float32 and got["L0.gdn.norm.f32"].dtype == np.float32 and got["L1.in_norm"].dtype == np.float16
     # a missing tensor is named, like the reference's store.req
     raw = {k: v[0] for k, v in CK.read_safetensors(path).items()}
     raw.pop("language_model.model.norm.weight")

@@ -347,6 +347,49 @@ def test_engine_accepts_q8_router_and_shared_gate(tiny_oracle):
         eng.close(); ref.close()
 
 
+def test_engine_f32_gdn_norm_weight(tiny_oracle):
+    """A GDN norm weight handed over as f32 ("L<i>.gdn.norm.f32"): the gated norm keeps its normed value in
+    f32 (the reference's promoted variant, SeedlessFusedVerify.swift:766-813, 2815-2818).  Weights that fp16
+    cannot hold make the two variants differ; the GDN layer output is compared with the CPU restatement
+    given the same f32 weight."""
+    import qwisp_b200 as Q
+    from oracle import oracle as O
+    from conftest import oracle_model
+    cfg = Q.config(**TINY, max_rows=16, max_streams=4, kv_page_size=32, kv_pages=8)
+    H, nl = TINY["hidden"], TINY["n_layers"]
+    tensors = {n: tiny_oracle.tensor_bytes(n).copy() for n in tiny_oracle.tensor_names()}
+    ref = oracle_model(TINY)
+    gdn_layers = [i for i in range(nl) if (i + 1) % TINY["attn_every"] != 0]
+    for i in gdn_layers:
+        w16 = tensors.pop(f"L{i}.gdn.norm").view(np.float16)
+        w32 = (w16.astype(np.float32) * np.float32(1.0003) + np.float32(1e-4) * np.sin(np.arange(128, dtype=np.float32))).astype(np.float32)
+        assert not np.array_equal(w32.astype(np.float16).astype(np.float32), w32)
+        tensors[f"L{i}.gdn.norm.f32"] = w32
+        ref.set_gdn_norm_f32(i, w32)
+    eng = Q.Engine.from_tensors(cfg, tensors)
+    plain = gpu_engine(TINY, max_rows=16, max_streams=4, kv_pages=8)
+    try:
+        layer = gdn_layers[0]
+        x = O.synth_f16(SEED, "f32norm.x", 5 * H, 0.0, 1.0).reshape(5, H)
+        want = ref.stream(32).mixer_rows(layer, x, 0)
+        got = Q.ops.mixer(eng.stream(32), layer, x, 0)
+        rep = f16_report(got, want)
+        print("f32 gdn norm", rep)
+        assert rep["max_abs"] <= 2e-2, rep
+        assert rep["max_abs"] <= 1e-3, rep                          # fp16 rounding of the out-projection apart
+        other = Q.ops.mixer(plain.stream(32), layer, x, 0)          # fp16 weight variant: measurably different
+        assert not np.array_equal(other.view(np.uint16), got.view(np.uint16))
+        p = prompt(TINY["vocab"], 7, "f32norm")
+        lg = eng.stream(32).step_logits(p)
+        _, rl = ref.stream(32).step(p, want_logits=True)
+        assert f16_report(lg, rl)["max_abs"] <= 2e-2
+        bad = dict(tensors); bad[f"L{layer}.gdn.norm.f32"] = np.zeros(64, np.float32)
+        with pytest.raises(Q.SeedlessError):
+            Q.Engine.from_tensors(cfg, bad)
+    finally:
+        eng.close(); plain.close(); ref.close()
+
+
 def test_step_sample_rows_greedy_equals_argmax(mini_engine):
     """At temperature 0 the sampling step returns the argmax step's tokens (stepSampleRows with
     invT <= 0, SamplerGPU.swift:13-15) and leaves the caches in the same state."""
