@@ -9,3 +9,4 @@ from ._lib import SeedlessError, config, lib, synth_spec  # noqa: F401
 from .engine import Engine, Stream, SpecBackend, LaneBatchSlots  # noqa: F401
 from . import ops  # noqa: F401
 from . import checkpoint  # noqa: F401
+from . import scheduler  # noqa: F401
