@@ -314,11 +314,16 @@ class SpecBackend:
 class LaneBatchSlots:
     """BatchSlots over engine streams: resumable chunked prefill + batched greedy step."""
 
-    def __init__(self, engine, slot_count, chunk=None, default_seq_budget=4096):
+    def __init__(self, engine, slot_count, chunk=None, default_seq_budget=4096, prefix_store=None):
         self.engine = engine
         self.slot_count = slot_count
         self.chunk = chunk or engine.cfg.max_rows
         self.default_seq_budget = default_seq_budget
+        # optional PrefixRAMStore: a new request starts from the longest stored state whose tokens are a
+        # prefix of its prompt (all but the last token, which must run to give the first output), and the
+        # state at the end of its prompt is stored for later requests (LaneServe.swift:362-425)
+        self.prefix_store = prefix_store
+        self.restored_tokens = 0
         self._streams = [None] * slot_count
         self._resume = [0] * slot_count
 
@@ -333,6 +338,14 @@ class LaneBatchSlots:
             if self._streams[slot] is None:
                 self._streams[slot] = self.engine.stream(seq_budget or self.default_seq_budget)
                 self._resume[slot] = 0
+                hit = self.prefix_store.best_match(prompt[:-1]) if self.prefix_store is not None else None
+                if hit is not None:
+                    if self._streams[slot].state_restore(hit[1]):
+                        self._resume[slot] = len(hit[0])         # restored tokens are not charged to the budget
+                        self.restored_tokens += len(hit[0])
+                    else:                                        # unusable blob: start cold on a fresh stream
+                        self._streams[slot].close()
+                        self._streams[slot] = self.engine.stream(seq_budget or self.default_seq_budget)
             st = self._streams[slot]
             pos = self._resume[slot]
             consumed = 0
@@ -351,6 +364,8 @@ class LaneBatchSlots:
                 first = False
                 if last:
                     self._resume[slot] = pos
+                    if self.prefix_store is not None:
+                        self.prefix_store.save(prompt, st.state_save())
                     return ("done", tok, consumed)
             self._resume[slot] = pos
             return ("prefilling", consumed)
