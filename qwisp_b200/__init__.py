@@ -10,4 +10,4 @@ from .engine import Engine, Stream, SpecBackend, LaneBatchSlots  # noqa: F401
 from . import ops  # noqa: F401
 from . import checkpoint  # noqa: F401
 from . import scheduler  # noqa: F401
-from .prefix import PrefixRAMStore  # noqa: F401
+from .prefix import PrefixRAMStore, PrefixDiskStore  # noqa: F401

@@ -60,3 +60,45 @@ def test_admission_restores_the_longest_stored_prefix():
         assert [len(k) for k, _ in store.entries] == [27]       # the longer conversation superseded its prefix
     finally:
         eng.close()
+
+
+def test_qwp1_layout_and_disk_store(tmp_path):
+    """The disk tier's file layout and policy, following the reference's own self-check
+    (PrefixPersist.swift:162-215): round trip, longest prefix, model isolation, LRU caps."""
+    import os
+    import struct
+    import time
+    from qwisp_b200.prefix import PrefixDiskStore, fnv1a64, qwp1_decode, qwp1_encode
+    state = bytes(range(64))
+    blob = qwp1_encode("/m", [1, 2, 3], state)
+    assert blob[:4] == b"QWP1" and struct.unpack_from("<II", blob, 4) == (1, 2)
+    assert blob[12:14] == b"/m" and struct.unpack_from("<I", blob, 14)[0] == 3
+    assert struct.unpack_from("<3i", blob, 18) == (1, 2, 3) and blob[30:] == state
+    assert qwp1_decode(blob) == ("/m", [1, 2, 3], state)
+    assert qwp1_decode(blob[:20]) is None and qwp1_decode(b"XXXX" + blob[4:]) is None
+    assert fnv1a64(b"") == 0xCBF29CE484222325 and fnv1a64(b"a") == 0xAF63DC4C8601EC8C
+    d = str(tmp_path / "prefix")
+    st = PrefixDiskStore(d, "/m", max_slots=4)
+    a, ab = [1, 2, 3, 4], [1, 2, 3, 4, 5, 6]
+    st.save(a, state); st.save(ab, state + state)
+    PrefixDiskStore(d, "/other").save(ab + [7], state)
+    assert st.best_match(ab + [9, 9]) == (ab, state + state)
+    assert st.best_match([1, 2, 3, 4, 99]) == (a, state)
+    assert PrefixDiskStore(d, "/nope").best_match(ab) is None
+    assert st.best_match([8, 8, 8]) is None
+    assert st.has(a) and not st.has([77, 78]) and st.restore_hits == 2
+    with open(os.path.join(d, "prefix-garbage.bin"), "wb") as f:
+        f.write(b"not a prefix file")
+    assert st.best_match(ab) == (ab, state + state)             # a malformed file is skipped
+    os.remove(os.path.join(d, "prefix-garbage.bin"))
+    for i in range(6):
+        st.save([100, i], state)
+        time.sleep(0.002)
+    assert len([n for n in os.listdir(d) if n.endswith(".bin")]) == 4
+    assert st.has([100, 5]) and not st.has(a)                   # the oldest went first
+    one = max(os.path.getsize(os.path.join(d, n)) for n in os.listdir(d))
+    st.evict(budget=one)
+    assert len([n for n in os.listdir(d) if n.endswith(".bin")]) == 1
+    st.save([5], b"x" * 10); big = PrefixDiskStore(d, "/m", max_bytes=4)
+    big.save([6], b"y" * 10)
+    assert not big.has([6])                                     # above the per-entry cap: not written
