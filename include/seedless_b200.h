@@ -98,7 +98,7 @@ typedef struct sl_synth_spec {
 typedef struct sl_engine sl_engine;
 typedef struct sl_stream sl_stream;
 typedef struct sl_fullsnap sl_fullsnap;
-typedef struct sl_snap { int32_t kv_len; int32_t parity; int32_t valid; } sl_snap;
+typedef struct sl_snap { int32_t kv_len; int32_t parity; int32_t valid; int32_t calls; } sl_snap;
 
 /* ---- engine (SeedlessEngine.build + makeFused, SeedlessEngine.swift:33-144) ---- */
 int32_t sl_engine_create(const sl_config* cfg, const sl_weight_desc* weights, int32_t n_weights, sl_engine** out);
@@ -114,6 +114,11 @@ const char* sl_last_fault(sl_engine* e);
 /* Host-side test hook: the next device-touching call reports failure and poisons the engine
  * (mirrors `injectCBFailure`, SeedlessFusedVerify.swift:403-404).  Never faults the GPU. */
 int32_t sl_inject_fault(sl_engine* e, int32_t on);
+/* Test hook for the device-side half of the fault firewall: enqueues a one-CTA kernel whose bounded wait
+ * (the routine the weight stages use, limited to a thousand polls on a barrier nothing arms) runs out and
+ * reports through the engine's error word.  Nothing faults or hangs.  The next call that synchronises
+ * returns SL_ERR_CUDA and poisons the engine, as it does when a real kernel's wait gives up. */
+int32_t sl_debug_wait_timeout(sl_engine* e);
 /* Kernels this library has launched so far (bench bookkeeping). */
 int64_t sl_engine_launch_count(sl_engine* e);
 /* Replay decode steps as CUDA graphs (default on) or launch every kernel eagerly. */
@@ -136,6 +141,14 @@ int32_t sl_stream_reset(sl_stream* s);
  * layers + final norm for M tokens appended at the current position; out_normed_f16 [M,H]
  * (may be NULL). */
 int32_t sl_forward(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_normed_f16);
+/* SpecBackend.forwardHybrid (TellRuntime.swift:96-99; SeedlessFusedVerify.swift:4215-4345): the
+ * prefill-only forward.  Same contract and outputs as sl_forward, but the dense projections run on the
+ * tcgen05 tensor-core GEMM.  As in the reference the result is NOT bit-identical to sl_forward (the f32
+ * summation order inside a group of 64 inputs differs) but it is deterministic and independent of how
+ * a prompt is split into calls.  Which family runs is decided by which entry point is called, never by M. */
+int32_t sl_forward_hybrid(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_normed_f16);
+/* SpecBackend.hybridChunk (TellRuntime.swift:234-238): rows per prefill call = min(1024, max_rows). */
+int32_t sl_hybrid_chunk(sl_engine* e);
 /* SpecBackend.stepArgmax (SeedlessFusedVerify.swift:3832-3912): forward + lm_head + per-row
  * greedy argmax (first maximum wins); only int32[M] is read back. */
 int32_t sl_step_argmax(sl_stream* s, const int32_t* tokens, int32_t M, int32_t* out_tokens);
@@ -151,7 +164,9 @@ int32_t sl_chained_collect(sl_stream* s, int32_t K, int32_t* out_tokens);
 int32_t sl_step_logits(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_logits_f16);
 
 /* SpecBackend.snapshot / rollback (SeedlessFusedVerify.swift:4039-4047): undo exactly one
- * following forward/step: KV length rewind + GDN ping-pong swap. */
+ * following forward/step: KV length rewind + GDN ping-pong swap.  The snapshot remembers the stream's
+ * call count; a rollback after anything but exactly one call (each chained step counts) is refused
+ * with SL_ERR_INVALID. */
 int32_t sl_snapshot(sl_stream* s, sl_snap* out);
 int32_t sl_rollback_one_step(sl_stream* s, const sl_snap* snap);
 /* fullSnapshot / fullRestore (SeedlessFusedVerify.swift:4053-4068): arbitrary rewind inside
@@ -177,11 +192,14 @@ int32_t sl_batch_step_argmax(sl_engine* e, sl_stream* const* streams, const int3
  * draft_tokens[m] excluded (= out_full when the draft is -1 or draft_tokens is NULL), out_accept = 1 when
  * coin < p(draft).  inv_temperature <= 0 is greedy: out_full equals sl_step_argmax's token.  The noise is a
  * counter-based hash of (seed_lo, seed_hi ^ (base_pos + m), token), so a call is reproducible.  Only the
- * three int32 arrays leave the device. */
-int32_t sl_step_sample_rows(sl_stream* s, const int32_t* tokens, int32_t M, const int32_t* draft_tokens, float inv_temperature, float top_p,
+ * three int32 arrays leave the device.
+ * logit_adj: host f32 [vocab] or NULL: penalties + bias added to every row's logits before the maximum,
+ * the nucleus, the draws and p(draft) are taken (the reference's logitAdj / LADJ, SamplerGPU.swift:41,69).
+ * draft_tokens outside [-1, vocab) are refused with SL_ERR_INVALID before anything is launched. */
+int32_t sl_step_sample_rows(sl_stream* s, const int32_t* tokens, int32_t M, const int32_t* draft_tokens, const float* logit_adj, float inv_temperature, float top_p,
                             uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept);
 /* The sampling kernel alone on host logits [M, vocab] fp16 (kernel tests). */
-int32_t sl_op_sample_rows(sl_engine* e, const uint16_t* logits_f16, int32_t M, const int32_t* draft_tokens, float inv_temperature, float top_p,
+int32_t sl_op_sample_rows(sl_engine* e, const uint16_t* logits_f16, int32_t M, const int32_t* draft_tokens, const float* logit_adj, float inv_temperature, float top_p,
                           uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept);
 
 /* ---- expert-parallel batched decode (NO COUNTERPART IN THE REFERENCE, which runs on one GPU) ----
@@ -247,6 +265,10 @@ int32_t sl_op_moe_block(sl_engine* e, int32_t layer, const uint16_t* x_f16, int3
 /* Mixer (GDN or attention) of `layer` on already-normed rows x [M,H] placed at positions
  * pos0..pos0+M-1 of the stream; advances only that layer's cache, not the stream length. */
 int32_t sl_op_mixer(sl_stream* s, int32_t layer, const uint16_t* x_f16, int32_t M, int32_t pos0, uint16_t* out_f16);
+/* Test accessor: cached K (post-RoPE) and V of attention layer `layer` at positions pos0..pos0+n-1, each
+ * as fp16 [kv_heads, n, 256] (either may be NULL); the positions must have been written (by a step or
+ * by sl_op_mixer / sl_op_layer), whatever the stream's length says. */
+int32_t sl_op_read_kv(sl_stream* s, int32_t layer, int32_t pos0, int32_t n, uint16_t* out_k_f16, uint16_t* out_v_f16);
 /* One whole decoder layer (rmsnorm, mixer, +resid, rmsnorm, MoE, +resid; the reference's
  * decoder-layer test, SeedlessMetalForward.swift:3757) on residual-stream rows h_in [M,H] at
  * positions pos0..; advances only that layer's cache. */

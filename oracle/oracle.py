@@ -343,12 +343,14 @@ def config(hidden=2048, n_layers=40, attn_every=4, vocab=151936, n_experts=256, 
                      attn_heads, attn_kv_heads, rope_theta, rms_eps, norm_jitter, conv_std)
 
 
-def sample_rows(logits, draft, inv_t, top_p, seed_lo, seed_hi, base_pos):
-    """CPU restatement of the speculative-sampling rows: -> (full, resid, accept) int32 [M]."""
+def sample_rows(logits, draft, inv_t, top_p, seed_lo, seed_hi, base_pos, logit_adj=None):
+    """CPU restatement of the speculative-sampling rows: -> (full, resid, accept) int32 [M].
+    logit_adj: optional f32 [V] added to every row's logits first."""
     logits = np.ascontiguousarray(logits, dtype=np.float16)
     M, V = logits.shape
     d = None if draft is None else np.ascontiguousarray(draft, dtype=np.int32)
+    adj = None if logit_adj is None else np.ascontiguousarray(logit_adj, dtype=np.float32)
     full, resid, acc = (np.empty(M, dtype=np.int32) for _ in range(3))
-    lib().orc_sample_rows(_p(logits), C.c_int(M), C.c_int(V), _p(d) if d is not None else None, C.c_float(inv_t), C.c_float(top_p),
+    lib().orc_sample_rows(_p(logits), _p(adj) if adj is not None else None, C.c_int(M), C.c_int(V), _p(d) if d is not None else None, C.c_float(inv_t), C.c_float(top_p),
                           C.c_uint32(seed_lo), C.c_uint32(seed_hi), C.c_uint32(base_pos), _p(full), _p(resid), _p(acc))
     return full, resid, acc

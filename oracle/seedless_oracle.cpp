@@ -959,7 +959,8 @@ static float block_sum_ref(const std::vector<float>& part) {      // part[1024]
     }
     return tot;
 }
-extern "C" void orc_sample_rows(const h16* logits, int M, int V, const int32_t* draft, float invT, float top_p,
+// adj: optional [V] f32 added to every row's logits first (LADJ, SamplerGPU.swift:41,69); nullptr = none
+extern "C" void orc_sample_rows(const h16* logits, const float* adj, int M, int V, const int32_t* draft, float invT, float top_p,
                                 uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept) {
     const int T = 1024, BINS = 1024;
     const float SPAN = 40.0f;
@@ -968,8 +969,9 @@ extern "C" void orc_sample_rows(const h16* logits, int M, int V, const int32_t* 
         const int d = draft ? draft[m] : -1;
         const bool greedy = invT <= 0.0f;
         const uint32_t salt = seed_hi ^ (base_pos + (uint32_t)m);
+        auto ladj = [&](int v) -> float { const float L = h2f(row[v]); return adj ? (L + adj[v]) : L; };
         float gmax = -INFINITY;
-        for (int v = 0; v < V; ++v) gmax = std::max(gmax, h2f(row[v]));
+        for (int v = 0; v < V; ++v) gmax = std::max(gmax, ladj(v));
         const bool do_top_p = !greedy && top_p < 0.999f;
         float lthr = -INFINITY, znuc = 0.f;
         if (!greedy) {
@@ -979,7 +981,7 @@ extern "C" void orc_sample_rows(const h16* logits, int M, int V, const int32_t* 
             for (int t = 0; t < T; ++t) {
                 float z = 0.f;
                 for (int v = t; v < V; v += T) {
-                    const float g = (gmax - h2f(row[v])) * invT;
+                    const float g = (gmax - ladj(v)) * invT;
                     const float w = det_expf_ref(-g);
                     z = z + w;
                     if (do_top_p) {
@@ -999,7 +1001,7 @@ extern "C" void orc_sample_rows(const h16* logits, int M, int V, const int32_t* 
                 lthr = gmax - ((float)(bstar + 1) * bin_w) / invT;
                 for (int t = 0; t < T; ++t) {
                     float zn = 0.f;
-                    for (int v = t; v < V; v += T) { const float L = h2f(row[v]); if (L >= lthr) zn = zn + det_expf_ref((L - gmax) * invT); }
+                    for (int v = t; v < V; v += T) { const float L = ladj(v); if (L >= lthr) zn = zn + det_expf_ref((L - gmax) * invT); }
                     part[t] = zn;
                 }
                 znuc = block_sum_ref(part);
@@ -1007,7 +1009,7 @@ extern "C" void orc_sample_rows(const h16* logits, int M, int V, const int32_t* 
         }
         float fs = -INFINITY, rs = -INFINITY; int fi = 0x7fffffff, ri = 0x7fffffff;
         for (int v = 0; v < V; ++v) {
-            const float L = h2f(row[v]);
+            const float L = ladj(v);
             if (do_top_p && L < lthr) continue;
             float score = L;
             if (!greedy) score = L * invT - det_logf_ref(-det_logf_ref(u01_ref(qhash_ref(seed_lo, salt, (uint32_t)v))));
@@ -1020,7 +1022,7 @@ extern "C" void orc_sample_rows(const h16* logits, int M, int V, const int32_t* 
         if (d >= 0) {
             if (greedy) p_draft = (d == fi) ? 1.0f : 0.0f;
             else {
-                const float Ld = h2f(row[d]);
+                const float Ld = ladj(d);
                 if (!do_top_p || Ld >= lthr) p_draft = det_expf_ref((Ld - gmax) * invT) / znuc;
             }
         }

@@ -39,7 +39,7 @@ class SlSynthSpec(C.Structure):
 
 
 class SlSnap(C.Structure):
-    _fields_ = [("kv_len", C.c_int32), ("parity", C.c_int32), ("valid", C.c_int32)]
+    _fields_ = [("kv_len", C.c_int32), ("parity", C.c_int32), ("valid", C.c_int32), ("calls", C.c_int32)]
 
 
 # every symbol include/seedless_b200.h declares: name -> (restype, argtypes)
@@ -62,6 +62,9 @@ SYMBOLS = {
     "sl_stream_len": (_I32, [_VP]),
     "sl_stream_reset": (_I32, [_VP]),
     "sl_forward": (_I32, [_VP, _VP, _I32, _VP]),
+    "sl_forward_hybrid": (_I32, [_VP, _VP, _I32, _VP]),
+    "sl_hybrid_chunk": (_I32, [_VP]),
+    "sl_debug_wait_timeout": (_I32, [_VP]),
     "sl_step_argmax": (_I32, [_VP, _VP, _I32, _VP]),
     "sl_chained_step_argmax": (_I32, [_VP, _I32, _I32, _VP]),
     "sl_chained_enqueue": (_I32, [_VP, _I32, _I32]),
@@ -77,8 +80,8 @@ SYMBOLS = {
     "sl_state_restore": (_I32, [_VP, _VP, _U64]),
     "sl_batch_step_argmax": (_I32, [_VP, C.POINTER(_VP), _VP, _I32, _VP]),
     "sl_op_qmm4": (_I32, [_VP, _VP, _VP, _VP, _I32, _I32, _I32, _VP]),
-    "sl_step_sample_rows": (_I32, [_VP, _VP, _I32, _VP, _F, _F, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP, _VP]),
-    "sl_op_sample_rows": (_I32, [_VP, _VP, _I32, _VP, _F, _F, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP, _VP]),
+    "sl_step_sample_rows": (_I32, [_VP, _VP, _I32, _VP, _VP, _F, _F, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP, _VP]),
+    "sl_op_sample_rows": (_I32, [_VP, _VP, _I32, _VP, _VP, _F, _F, C.c_uint32, C.c_uint32, C.c_uint32, _VP, _VP, _VP]),
     "sl_ep_unique_id": (_I32, [_VP]),
     "sl_ep_init": (_I32, [_VP, _I32, _I32, _VP, _I32]),
     "sl_op_qmm4_device": (_I32, [_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP]),
@@ -89,6 +92,7 @@ SYMBOLS = {
     "sl_op_mixer": (_I32, [_VP, _I32, _VP, _I32, _I32, _VP]),
     "sl_op_lm_head": (_I32, [_VP, _VP, _I32, _VP, _VP]),
     "sl_op_lm_head_argmax_static": (_I32, [_VP, _VP, _VP, _I32, _I32, _I32, _VP, _VP]),
+    "sl_op_read_kv": (_I32, [_VP, _I32, _I32, _I32, _VP, _VP]),
     "sl_op_layer": (_I32, [_VP, _I32, _VP, _I32, _I32, _VP]),
     "sl_op_head": (_I32, [_VP, _VP, _I32, _VP, _VP]),
     "sl_synth_tokens": (_I32, [_U64, C.c_char_p, _I64, _I32, _VP]),

@@ -87,8 +87,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
 }
 // Bounded wait: gives up after ~2^22 polls (seconds) so a copy that never lands cannot hang the GPU;
 // the caller records the failure and carries on with whatever is in shared memory.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* b, uint32_t parity) {
-    for (int i = 0; i < (1 << 22); ++i) if (mbar_try_wait(b, parity)) return true;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* b, uint32_t parity, int limit = 1 << 22) {
+    for (int i = 0; i < limit; ++i) if (mbar_try_wait(b, parity)) return true;
     return false;
 }
 

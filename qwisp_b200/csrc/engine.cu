@@ -52,7 +52,7 @@ struct sl_engine {
     int H = 0, E = 0, I = 0, topk = 0, V = 0;
     int keyDim = 0, valDim = 0, convDim = 0, gdn_in = 0, attn_in = 0, attn_out = 0;
     int n_gdn = 0, n_attn = 0;
-    bool exact = true;
+    bool hybrid = false;            // set for the duration of a prefill-mode call: dense projections on the tensor-core GEMM
     cudaStream_t own_stream = nullptr, stream = nullptr;
     std::map<std::string, Tensor> tensors;
     std::vector<void*> allocs;
@@ -67,7 +67,7 @@ struct sl_engine {
     float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
-    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; int* samp_buf = nullptr; unsigned* slot_sync = nullptr;
+    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; unsigned* err_host = nullptr; float* adj_buf = nullptr; int* samp_buf = nullptr; unsigned* slot_sync = nullptr;
     bool use_route_in_experts = true;   // with the fused kernel: routing done by its CTAs (SEEDLESS_ROUTE_IN_EXPERTS=0: by the router's last CTA)
     bool use_fused_experts = true;  // batch-1 decode: gate/up + down in one launch (SEEDLESS_FUSED_EXPERTS=0 turns it off)
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
@@ -101,6 +101,7 @@ struct sl_stream {
     int kv_len;
     int parity;
     std::vector<int> pages;
+    int calls = 0;                  // forward / step calls (chained steps count one each) since creation: what a snapshot remembers
 };
 
 struct sl_fullsnap {
@@ -307,8 +308,12 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->samp_buf, (size_t)4 * R))) return rc;
     if ((rc = dalloc(e, &e->slot_sync, (size_t)64))) return rc;
     CU(e, cudaMemset(e->slot_sync, 0, 64 * sizeof(unsigned)));
-    if ((rc = dalloc(e, &e->err_flag, (size_t)4))) return rc;
-    CU(e, cudaMemset(e->err_flag, 0, 4 * sizeof(unsigned)));
+    // Kernels whose bounded wait runs out leave a code here.  The word lives in mapped page-locked host
+    // memory, so it costs nothing while all is well and the host sees it after the synchronisation that
+    // ends every call, without a copy.
+    CU(e, cudaHostAlloc((void**)&e->err_host, 4 * sizeof(unsigned), cudaHostAllocMapped));
+    memset(e->err_host, 0, 4 * sizeof(unsigned));
+    CU(e, cudaHostGetDevicePointer((void**)&e->err_flag, e->err_host, 0));
     if ((rc = dalloc(e, &e->att_counters, (size_t)R * c.attn_kv_heads))) return rc;
     CU(e, cudaMemset(e->att_counters, 0, (size_t)R * c.attn_kv_heads * sizeof(unsigned)));
     CU(e, cudaMemset(e->hist_pos, 0, sizeof(int)));
@@ -370,47 +375,6 @@ int32_t repack_all(sl_engine* e) {
     }
     CU(e, cudaStreamSynchronize(e->stream));
     CU(e, cudaGetLastError());
-    return SL_OK;
-}
-
-// ---- numeric mode of the GEMV family: can the tensor cores take fp16 subnormal operands? ----
-int g_gemv_mode = -1;   // -1 unknown, 0 subnormal operands, 1 exact-integer operands
-int32_t detect_gemv_mode() {
-    if (g_gemv_mode >= 0) return SL_OK;
-    const char* force = getenv("SEEDLESS_GEMV_EXACT");
-    if (force && (force[0] == '0' || force[0] == '1')) { g_gemv_mode = force[0] - '0'; return SL_OK; }
-    const int N = 64, K = 512, M = 8;
-    uint32_t* w; __half *s, *b, *x, *y0, *y1;
-    if (cudaMalloc(&w, (size_t)N * K / 2) != cudaSuccess) return SL_ERR_CUDA;
-    cudaMalloc(&s, (size_t)N * K / 64 * 2); cudaMalloc(&b, (size_t)N * K / 64 * 2);
-    cudaMalloc(&x, (size_t)M * K * 2); cudaMalloc(&y0, (size_t)M * N * 2); cudaMalloc(&y1, (size_t)M * N * 2);
-    uint4 *wr, *sr;
-    cudaMalloc(&wr, (size_t)(N / 16) * q4r_w_uint4(K) * 16); cudaMalloc(&sr, (size_t)(N / 16) * q4r_s_uint4(K) * 16);
-    launch_synth_q4(tensor_seed(7, "selftest.w"), N, K, 0.02f, w, s, b, 0);
-    launch_synth_f16(tensor_seed(7, "selftest.x"), (int64_t)M * K, 0.f, 1.f, x, 0);
-    Q4W qw; qw.w = w; qw.s = s; qw.b = b; qw.N = N; qw.K = K;
-    launch_repack_q4(qw, nullptr, wr, sr, 0);
-    DenseArgs a{}; a.q.wr = wr; a.q.sr = sr; a.q.tiles = N / 16; a.q.K = K; a.N = N; a.K = K; a.M = M; a.x = x; a.ldx = K; a.ldy = N;
-    a.y = y0; launch_dense(PRO_PLAIN, EPI_STORE, false, a, 0, false);
-    a.y = y1; launch_dense(PRO_PLAIN, EPI_STORE, true, a, 0, false);
-    std::vector<__half> h0((size_t)M * N), h1((size_t)M * N);
-    cudaError_t err = cudaDeviceSynchronize();
-    cudaMemcpy(h0.data(), y0, h0.size() * 2, cudaMemcpyDeviceToHost);
-    cudaMemcpy(h1.data(), y1, h1.size() * 2, cudaMemcpyDeviceToHost);
-    cudaFree(w); cudaFree(s); cudaFree(b); cudaFree(x); cudaFree(y0); cudaFree(y1); cudaFree(wr); cudaFree(sr);
-    if (err != cudaSuccess) return SL_ERR_CUDA;
-    float maxd = 0.f, maxv = 0.f;
-    for (size_t i = 0; i < h0.size(); ++i) {
-        float a0 = __half2float(h0[i]), a1 = __half2float(h1[i]);
-        maxd = fmaxf(maxd, fabsf(a0 - a1)); maxv = fmaxf(maxv, fabsf(a1));
-    }
-    g_gemv_mode = (maxv > 0.f && maxd <= 4e-3f * fmaxf(1.f, maxv)) ? 0 : 1;
-    return SL_OK;
-}
-
-int32_t finish_create(sl_engine* e) {
-    if (detect_gemv_mode() != SL_OK) return poison(e, "gemv self-test", cudaGetLastError());
-    e->exact = (g_gemv_mode == 1);
     return SL_OK;
 }
 
@@ -482,8 +446,8 @@ int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __ha
     ea.scores = e->scores; ea.sgl = e->sgl; ea.tile_counter = nullptr; ea.err = e->err_flag;
     const int local_e = e->ep_e1 - e->ep_e0;
     const int nslots = T * topk < local_e ? T * topk : local_e;
-    launch_expert_gateup(e->exact, ea, nslots, st, false);
-    launch_expert_down(e->exact, ea, nslots, st, false);
+    launch_expert_gateup(ea, nslots, st, false);
+    launch_expert_down(ea, nslots, st, false);
     __half* mine = e->dbuf + (size_t)r * M * topk * H;
     NC(e, g_nccl.ReduceScatter(e->dbuf, mine, (size_t)M * topk * H, ncclFloat16, ncclSum, comm, st));
     launch_moe_combine(e->dbuf, r * M * topk, T * topk, e->scores, e->sgl, M, H, topk, resid, plain_out, st);
@@ -513,8 +477,8 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     ea.route_here = ra.no_route;
     launch_router(ra, st, e->use_pdl);
     if (fused && launch_expert_fused(ea, st, e->use_pdl)) return;                      // one launch for gate/up + down
-    launch_expert_gateup(e->exact, ea, nslots, st, e->use_pdl);
-    launch_expert_down(e->exact, ea, nslots, st, e->use_pdl);
+    launch_expert_gateup(ea, nslots, st, e->use_pdl);
+    launch_expert_down(ea, nslots, st, e->use_pdl);
 }
 
 // mixer of one layer: input rows are normed inside (norm_w != nullptr) or already normed
@@ -525,10 +489,11 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
     DenseArgs d{}; d.err = e->err_flag; d.norm_scratch = e->normed; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
     d.x = rows; d.ldx = e->H; d.nw = norm_w; d.eps = c.rms_eps; d.y = e->inproj; d.ldy = (int)L.in_proj.N;
     if (e->use_prefetch) pf_q4(d.pf, 0, L.r_out);
-    launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, e->exact, d, st, e->use_pdl);
+    d.tc = e->hybrid;
+    launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, d, st, e->use_pdl);
     DenseArgs o{};
     o.err = e->err_flag; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
-    o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H;
+    o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H; o.tc = e->hybrid;
     if (e->use_prefetch) {
         o.pf.p[0] = L.router; o.pf.bytes[0] = (unsigned)((size_t)e->E * e->H * 2);
         pf_q4(o.pf, 1, L.r_sh_gu);
@@ -539,7 +504,7 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
         g.Hk = c.gdn_k_heads; g.Hv = c.gdn_v_heads; g.eps = c.rms_eps; g.tab = e->tab; g.gdn_index = L.type_index; g.segs = e->segs; g.y = e->mix;
         launch_gdn_core(g, nsegs, st, e->use_pdl);
         o.x = e->mix; o.ldx = e->valDim; o.nw = L.gdn_norm; o.nw32 = L.gdn_norm32; o.z = e->inproj + e->convDim; o.ldz = e->gdn_in;
-        launch_dense(L.gdn_norm32 ? PRO_NORMGATE32 : PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, e->use_pdl);
+        launch_dense(L.gdn_norm32 ? PRO_NORMGATE32 : PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, o, st, e->use_pdl);
     } else {
         AttnArgs a{}; a.inproj = e->inproj; a.ld = e->attn_in; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.NH = c.attn_heads; a.KV = c.attn_kv_heads;
         a.eps = c.rms_eps; a.theta = c.rope_theta; a.tab = e->tab; a.attn_index = L.type_index; a.n_attn_layers = e->n_attn > 0 ? e->n_attn : 1;
@@ -551,7 +516,7 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
         if (!self_prep) launch_attn_prep(a, st);
         launch_attn_fused(a, self_prep, e->att_counters, st, e->use_pdl && self_prep);
         o.x = e->mix; o.ldx = e->attn_out;
-        launch_dense(PRO_PLAIN, resid ? EPI_RESID : EPI_STORE, e->exact, o, st, e->use_pdl);
+        launch_dense(PRO_PLAIN, resid ? EPI_RESID : EPI_STORE, o, st, e->use_pdl);
     }
 }
 
@@ -570,7 +535,7 @@ void enqueue_step(sl_engine* e, int M, int nsegs, HeadMode head, bool want_logit
         DenseArgs d{}; d.q = e->r_lm_head; d.N = e->V; d.K = e->H; d.M = M;
         d.x = e->h; d.ldx = e->H; d.nw = e->final_norm; d.eps = e->cfg.rms_eps;
         d.logits = want_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
-        launch_dense(PRO_RMSNORM, EPI_ARGMAX, e->exact, d, st, e->use_pdl);
+        launch_dense(PRO_RMSNORM, EPI_ARGMAX, d, st, e->use_pdl);
     }
     StepEndArgs se{}; se.tab = e->tab; se.segs = e->segs; se.nsegs = nsegs; se.M = M;
     se.out_tok = (head == HEAD_ARGMAX || head == HEAD_LOGITS) ? e->out_tok : nullptr;
@@ -641,6 +606,12 @@ int32_t enqueue_decode_step(sl_engine* e, int rows) {
 int32_t sync_check(sl_engine* e) {
     CU(e, cudaStreamSynchronize(e->stream));
     CU(e, cudaGetLastError());
+    // a kernel that gave up a bounded wait went on with whatever it had: the results of this call are not to be trusted
+    if (e->err_host && *(volatile unsigned*)e->err_host) {
+        char msg[128];
+        snprintf(msg, sizeof msg, "a kernel gave up a bounded wait (code %u): results discarded", *(volatile unsigned*)e->err_host);
+        return poison_msg(e, msg);
+    }
     return SL_OK;
 }
 
@@ -659,7 +630,7 @@ int32_t run_single(sl_stream* s, const int32_t* tokens, int M, HeadMode head, bo
     if ((rc = upload_descs(e, segs, tokens, M))) return rc;
     if (M == 1 && head == HEAD_ARGMAX && !want_logits) { if ((rc = enqueue_decode_step(e, 1))) return rc; }
     else enqueue_step(e, M, 1, head, want_logits);
-    s->kv_len += M; s->parity ^= 1;
+    s->kv_len += M; s->parity ^= 1; s->calls += 1;
     return SL_OK;
 }
 
@@ -677,6 +648,7 @@ int32_t sl_engine_destroy(sl_engine* e) {
     for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
     for (void* p : e->allocs) cudaFree(p);
     if (e->pin_i) cudaFreeHost(e->pin_i);
+    if (e->err_host) cudaFreeHost(e->err_host);
     if (e->own_stream) cudaStreamDestroy(e->own_stream);
     cudaGetLastError();
     delete e;
@@ -692,7 +664,6 @@ static int32_t create_common(const sl_config* cfg, sl_engine** out, sl_engine** 
     e->cfg = *cfg;
     int32_t rc = build_layout(e);
     if (!rc) rc = build_runtime(e);
-    if (!rc) rc = finish_create(e);
     if (rc) { sl_engine_destroy(e); return rc; }
     *made = e;
     return SL_OK;
@@ -870,11 +841,16 @@ const char* sl_last_fault(sl_engine* e) {
     if (!e->poisoned && e->err_flag) {
         // a kernel whose bounded wait on a bulk copy gave up leaves a mark here instead of hanging
         unsigned flag = 0;
-        if (cudaStreamSynchronize(e->stream) == cudaSuccess && cudaMemcpy(&flag, e->err_flag, sizeof(flag), cudaMemcpyDeviceToHost) == cudaSuccess && flag) {
-            e->poisoned = true; e->fault = "a kernel gave up waiting for a bulk copy into shared memory";
+        if (cudaStreamSynchronize(e->stream) == cudaSuccess && (flag = *(volatile unsigned*)e->err_host) != 0) {
+            e->poisoned = true; e->fault = "a kernel gave up a bounded wait (code " + std::to_string(flag) + ")";
         }
     }
     return e->poisoned ? e->fault.c_str() : nullptr;
+}
+int32_t sl_debug_wait_timeout(sl_engine* e) {
+    int32_t rc = guard(e); if (rc) return rc;
+    launch_wait_probe(e->err_flag, e->stream);
+    return SL_OK;
 }
 int32_t sl_inject_fault(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->inject = on != 0; return SL_OK; }
 int64_t sl_engine_launch_count(sl_engine* e) { (void)e; return kernel_launch_count(); }
@@ -890,7 +866,7 @@ int32_t sl_stream_create(sl_engine* e, int32_t max_seq_len, sl_stream** out) {
     int32_t rc = guard(e); if (rc) return rc;
     if (!out || max_seq_len <= 0) return SL_ERR_INVALID;
     if (e->free_slots.empty()) return SL_ERR_CAPACITY;
-    sl_stream* s = new sl_stream{e, e->free_slots.back(), max_seq_len, 0, 0, {}};
+    sl_stream* s = new sl_stream{e, e->free_slots.back(), max_seq_len, 0, 0, {}, 0};
     e->free_slots.pop_back();
     *out = s;
     return sl_stream_reset(s);
@@ -927,6 +903,20 @@ int32_t sl_forward(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out
     if (out_normed_f16) CU(e, cudaMemcpyAsync(out_normed_f16, e->normed, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);
 }
+int32_t sl_forward_hybrid(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_normed_f16) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e;
+    e->hybrid = true;
+    int32_t rc = run_single(s, tokens, M, HEAD_NORMED, false);
+    e->hybrid = false;
+    if (rc) return rc;
+    if (out_normed_f16) CU(e, cudaMemcpyAsync(out_normed_f16, e->normed, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
+    return sync_check(e);
+}
+int32_t sl_hybrid_chunk(sl_engine* e) {
+    if (!e) return SL_ERR_INVALID;
+    return e->cfg.max_rows < 1024 ? e->cfg.max_rows : 1024;
+}
 int32_t sl_step_argmax(sl_stream* s, const int32_t* tokens, int32_t M, int32_t* out_tokens) {
     if (!s || !out_tokens) return SL_ERR_INVALID;
     sl_engine* e = s->e;
@@ -942,35 +932,47 @@ int32_t sl_step_logits(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t*
     return sync_check(e);
 }
 // device part shared by the two sampling entry points: logits [M][V] on the device -> three int32 per row on the host
-static int32_t sample_rows_device(sl_engine* e, const __half* logits, int M, const int32_t* draft, float inv_t, float top_p,
+static int32_t drafts_ok(const sl_engine* e, const int32_t* draft, int M) {
+    // the kernel reads logits[draft]: anything outside [-1, vocab) would be a read outside the row
+    if (draft) for (int i = 0; i < M; ++i) if (draft[i] < -1 || draft[i] >= e->V) return SL_ERR_INVALID;
+    return SL_OK;
+}
+static int32_t sample_rows_device(sl_engine* e, const __half* logits, int M, const int32_t* draft, const float* logit_adj, float inv_t, float top_p,
                                   uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept) {
     int* d = e->samp_buf;                      // [4][max_rows]: draft, full, resid, accept
     const int R = e->cfg.max_rows;
     if (draft) CU(e, cudaMemcpyAsync(d, draft, (size_t)M * sizeof(int), cudaMemcpyHostToDevice, e->stream));
-    launch_sample_rows(logits, draft ? d : nullptr, d + R, d + 2 * R, d + 3 * R, M, e->V, inv_t, top_p, seed_lo, seed_hi, base_pos, e->stream);
+    if (logit_adj) {
+        int32_t rc;
+        if (!e->adj_buf && (rc = dalloc(e, &e->adj_buf, (size_t)e->V))) return rc;
+        CU(e, cudaMemcpyAsync(e->adj_buf, logit_adj, (size_t)e->V * sizeof(float), cudaMemcpyHostToDevice, e->stream));
+    }
+    launch_sample_rows(logits, logit_adj ? e->adj_buf : nullptr, draft ? d : nullptr, d + R, d + 2 * R, d + 3 * R, M, e->V, inv_t, top_p, seed_lo, seed_hi, base_pos, e->stream);
     if (out_full) CU(e, cudaMemcpyAsync(out_full, d + R, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     if (out_resid) CU(e, cudaMemcpyAsync(out_resid, d + 2 * R, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     if (out_accept) CU(e, cudaMemcpyAsync(out_accept, d + 3 * R, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);
 }
-int32_t sl_step_sample_rows(sl_stream* s, const int32_t* tokens, int32_t M, const int32_t* draft_tokens, float inv_temperature, float top_p,
+int32_t sl_step_sample_rows(sl_stream* s, const int32_t* tokens, int32_t M, const int32_t* draft_tokens, const float* logit_adj, float inv_temperature, float top_p,
                             uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept) {
     if (!s) return SL_ERR_INVALID;
     sl_engine* e = s->e;
-    int32_t rc = run_single(s, tokens, M, HEAD_LOGITS, true); if (rc) return rc;
-    return sample_rows_device(e, e->logits, M, draft_tokens, inv_temperature, top_p, seed_lo, seed_hi, base_pos, out_full, out_resid, out_accept);
+    int32_t rc = drafts_ok(e, draft_tokens, M > 0 ? M : 0); if (rc) return rc;
+    rc = run_single(s, tokens, M, HEAD_LOGITS, true); if (rc) return rc;
+    return sample_rows_device(e, e->logits, M, draft_tokens, logit_adj, inv_temperature, top_p, seed_lo, seed_hi, base_pos, out_full, out_resid, out_accept);
 }
-int32_t sl_op_sample_rows(sl_engine* e, const uint16_t* logits_f16, int32_t M, const int32_t* draft_tokens, float inv_temperature, float top_p,
+int32_t sl_op_sample_rows(sl_engine* e, const uint16_t* logits_f16, int32_t M, const int32_t* draft_tokens, const float* logit_adj, float inv_temperature, float top_p,
                           uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, int32_t* out_full, int32_t* out_resid, int32_t* out_accept) {
     int32_t rc = guard(e); if (rc) return rc;
     if (!logits_f16 || M <= 0) return SL_ERR_INVALID;
+    if ((rc = drafts_ok(e, draft_tokens, M))) return rc;
     if (M > e->cfg.max_rows) return SL_ERR_CAPACITY;
     if (e->logits_rows < M) {
         __half* lg; if ((rc = dalloc(e, &lg, (size_t)e->cfg.max_rows * e->V))) return rc;
         e->logits = lg; e->logits_rows = e->cfg.max_rows;
     }
     CU(e, cudaMemcpyAsync(e->logits, logits_f16, (size_t)M * e->V * 2, cudaMemcpyHostToDevice, e->stream));
-    return sample_rows_device(e, e->logits, M, draft_tokens, inv_temperature, top_p, seed_lo, seed_hi, base_pos, out_full, out_resid, out_accept);
+    return sample_rows_device(e, e->logits, M, draft_tokens, logit_adj, inv_temperature, top_p, seed_lo, seed_hi, base_pos, out_full, out_resid, out_accept);
 }
 int32_t sl_chained_enqueue(sl_stream* s, int32_t first, int32_t K) {
     if (!s) return SL_ERR_INVALID;
@@ -985,7 +987,7 @@ int32_t sl_chained_enqueue(sl_stream* s, int32_t first, int32_t K) {
     CU(e, cudaMemsetAsync(e->hist_pos, 0, sizeof(int), e->stream));
     for (int k = 0; k < K; ++k) {
         if ((rc = enqueue_decode_step(e, 1))) return rc;
-        s->kv_len += 1; s->parity ^= 1;
+        s->kv_len += 1; s->parity ^= 1; s->calls += 1;
     }
     return SL_OK;
 }
@@ -1020,7 +1022,7 @@ int32_t sl_batch_step_argmax(sl_engine* e, sl_stream* const* streams, const int3
     rc = enqueue_decode_step(e, B);
     e->ep_step = false;
     if (rc) return rc;
-    for (int b = 0; b < B; ++b) { streams[b]->kv_len += 1; streams[b]->parity ^= 1; }
+    for (int b = 0; b < B; ++b) { streams[b]->kv_len += 1; streams[b]->parity ^= 1; streams[b]->calls += 1; }
     CU(e, cudaMemcpyAsync(out_tokens, e->out_tok, (size_t)B * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);
 }
@@ -1060,7 +1062,7 @@ static int32_t push_len_parity(sl_stream* s) {
 }
 int32_t sl_snapshot(sl_stream* s, sl_snap* out) {
     if (!s || !out) return SL_ERR_INVALID;
-    out->kv_len = s->kv_len; out->parity = s->parity; out->valid = 1;
+    out->kv_len = s->kv_len; out->parity = s->parity; out->valid = 1; out->calls = s->calls;
     return SL_OK;
 }
 int32_t sl_rollback_one_step(sl_stream* s, const sl_snap* snap) {
@@ -1068,8 +1070,10 @@ int32_t sl_rollback_one_step(sl_stream* s, const sl_snap* snap) {
     int32_t rc = guard(s->e); if (rc) return rc;
     if (snap->kv_len > s->kv_len) return SL_ERR_INVALID;
     if (snap->kv_len == s->kv_len) return SL_OK;           // nothing ran since the snapshot
-    if (s->parity == snap->parity) return SL_ERR_INVALID;  // more than one step ran: the other side no longer holds the old state
-    s->kv_len = snap->kv_len; s->parity = snap->parity;
+    // exactly one call may have run: after two the other ping-pong side no longer holds the old state, and after
+    // any odd number the parity alone would not tell
+    if (s->calls != snap->calls + 1 || s->parity == snap->parity) return SL_ERR_INVALID;
+    s->kv_len = snap->kv_len; s->parity = snap->parity; s->calls = snap->calls;
     return push_len_parity(s);
 }
 static float* cur_state(sl_stream* s) { return s->e->tab.gdn_state + (size_t)s->slot * s->e->tab.state_stride_stream + (size_t)s->parity * s->e->tab.state_stride_side; }
@@ -1227,10 +1231,9 @@ int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_
     if (!x_dev || !wr_dev || !sr_dev || !y_dev) return SL_ERR_INVALID;
     if (M <= 0 || N <= 0 || K <= 0 || N % 16 || !k_ok(K)) return SL_ERR_INVALID;
     if (!device_ok()) return SL_ERR_NO_DEVICE;
-    if (detect_gemv_mode() != SL_OK) return SL_ERR_CUDA;
     DenseArgs a{}; a.q.wr = (const uint4*)wr_dev; a.q.sr = (const uint4*)sr_dev; a.q.tiles = N / 16; a.q.K = K; a.N = N; a.K = K; a.M = M;
     a.x = (const __half*)x_dev; a.ldx = K; a.y = (__half*)y_dev; a.ldy = N;
-    launch_dense(PRO_PLAIN, EPI_STORE, g_gemv_mode == 1, a, (cudaStream_t)cuda_stream, false);
+    launch_dense(PRO_PLAIN, EPI_STORE, a, (cudaStream_t)cuda_stream, false);
     return cudaGetLastError() == cudaSuccess ? SL_OK : SL_ERR_CUDA;
 }
 int32_t sl_op_lm_head_argmax_static(const void* x_dev, const void* wr_dev, const void* sr_dev,
@@ -1337,6 +1340,26 @@ int32_t sl_op_mixer(sl_stream* s, int32_t layer, const uint16_t* x, int32_t M, i
     CU(e, cudaMemcpyAsync(out, e->opy, (size_t)M * e->H * 2, cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);
 }
+int32_t sl_op_read_kv(sl_stream* s, int32_t layer, int32_t pos0, int32_t n, uint16_t* out_k_f16, uint16_t* out_v_f16) {
+    if (!s) return SL_ERR_INVALID;
+    sl_engine* e = s->e; const sl_config& c = e->cfg;
+    int32_t rc = guard(e); if (rc) return rc;
+    if (layer < 0 || layer >= c.n_layers || !e->layers[layer].is_attn || pos0 < 0 || n <= 0) return SL_ERR_INVALID;
+    if ((pos0 + n + c.kv_page_size - 1) / c.kv_page_size > (int)s->pages.size()) return SL_ERR_CAPACITY;
+    const size_t page_elems = (size_t)e->n_attn * 2 * c.attn_kv_heads * c.kv_page_size * ATT_D;
+    for (int which = 0; which < 2; ++which) {
+        uint16_t* out = which ? out_v_f16 : out_k_f16;
+        if (!out) continue;
+        for (int hh = 0; hh < c.attn_kv_heads; ++hh)
+            for (int i = 0; i < n; ++i) {
+                const int pos = pos0 + i;
+                const __half* dev = e->kv_pool + (size_t)s->pages[pos / c.kv_page_size] * page_elems +
+                                    ((((size_t)e->layers[layer].type_index * 2 + which) * c.attn_kv_heads + hh) * c.kv_page_size + pos % c.kv_page_size) * ATT_D;
+                CU(e, cudaMemcpyAsync(out + ((size_t)hh * n + i) * ATT_D, dev, ATT_D * 2, cudaMemcpyDeviceToHost, e->stream));
+            }
+    }
+    return sync_check(e);
+}
 int32_t sl_op_layer(sl_stream* s, int32_t layer, const uint16_t* h_in, int32_t M, int32_t pos0, uint16_t* h_out) {
     if (!s) return SL_ERR_INVALID;
     sl_engine* e = s->e;
@@ -1378,7 +1401,7 @@ int32_t sl_op_head(sl_engine* e, const uint16_t* h_rows, int32_t M, uint16_t* ou
     DenseArgs d{}; d.q = e->r_lm_head; d.N = e->V; d.K = e->H; d.M = M;
     d.x = e->opx; d.ldx = e->H; d.nw = e->final_norm; d.eps = e->cfg.rms_eps;
     d.logits = out_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
-    launch_dense(PRO_RMSNORM, EPI_ARGMAX, e->exact, d, e->stream, false);
+    launch_dense(PRO_RMSNORM, EPI_ARGMAX, d, e->stream, false);
     if (out_logits) CU(e, cudaMemcpyAsync(out_logits, e->logits, (size_t)M * e->V * 2, cudaMemcpyDeviceToHost, e->stream));
     if (out_tokens) CU(e, cudaMemcpyAsync(out_tokens, e->out_tok, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);
@@ -1394,7 +1417,7 @@ int32_t sl_op_lm_head(sl_engine* e, const uint16_t* normed, int32_t M, uint16_t*
     CU(e, cudaMemcpyAsync(e->opx, normed, (size_t)M * e->H * 2, cudaMemcpyHostToDevice, e->stream));
     DenseArgs d{}; d.q = e->r_lm_head; d.N = e->V; d.K = e->H; d.M = M;
     d.x = e->opx; d.ldx = e->H; d.logits = out_logits ? e->logits : nullptr; d.pval = e->pval; d.pidx = e->pidx; d.out_tok = e->out_tok; d.counter = e->counters + 0;
-    launch_dense(PRO_PLAIN, EPI_ARGMAX, e->exact, d, e->stream, false);
+    launch_dense(PRO_PLAIN, EPI_ARGMAX, d, e->stream, false);
     if (out_logits) CU(e, cudaMemcpyAsync(out_logits, e->logits, (size_t)M * e->V * 2, cudaMemcpyDeviceToHost, e->stream));
     if (out_tokens) CU(e, cudaMemcpyAsync(out_tokens, e->out_tok, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     return sync_check(e);

@@ -347,14 +347,15 @@ struct GemvPlan { int upw, tpc, nw, lg_slices; };
 // K/256 must be a power of two (K = 256, 512, ... 4096).  A unit is one slice of one tile; a CTA of
 // 16 warps takes UPW units per warp (unit u = warp + 16*i -> tile u >> lg_slices, slice u & (slices-1)),
 // i.e. TPC = 16*UPW/slices whole tiles.  UPW grows (to at most 3) until `groups` independent
-// problems of `ntiles` tiles fit one wave of 148 CTAs.
-__host__ __device__ inline GemvPlan gemv_plan(int K, int ntiles, int groups) {
+// problems of `ntiles` tiles fit one wave of CTAs (one per multiprocessor).
+// nsm: multiprocessors of the device (a wave is one CTA per multiprocessor)
+__host__ __device__ inline GemvPlan gemv_plan(int K, int ntiles, int groups, int nsm) {
     GemvPlan p;
     int slices = K >> 8;
     p.lg_slices = 0; while ((1 << p.lg_slices) < slices) ++p.lg_slices;
     p.nw = 16;
     long long units = (long long)ntiles * slices * groups;
-    int upw = (int)((units + 148 * 16 - 1) / (148 * 16));
+    int upw = (int)((units + nsm * 16 - 1) / (nsm * 16));
     if (upw < 1) upw = 1;
     if (upw > 3) upw = 3;
     while ((p.nw * upw) % slices) ++upw;          // whole tiles per CTA (slices <= 16 divides 16)

@@ -12,6 +12,19 @@
 
 namespace sl {
 
+// multiprocessors of the current device (queried once per device; the launch shapes below are sized by it)
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 static std::atomic<int64_t> g_launches{0};
 int64_t kernel_launch_count() { return g_launches.load(); }
 #define COUNT_LAUNCH() g_launches.fetch_add(1, std::memory_order_relaxed)
@@ -157,7 +170,7 @@ static void launch_gemv_t(const DenseArgs& a, const GemvPlan& pl, cudaStream_t s
 }
 
 __device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
-template <int PRO, bool EXACT>
+template <int PRO>
 __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -258,19 +271,19 @@ __global__ void __launch_bounds__(256) k_head(DenseArgs a) {
     if (threadIdx.x == 0) *a.counter = 0u;
 }
 
-template <int PRO, bool EXACT>
+template <int PRO>
 static void launch_head_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
     size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 1, 1);
     static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(k_head<PRO, EXACT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
+    if (!configured) { cudaFuncSetAttribute(k_head<PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); configured = true; }
     int ntiles = a.N / 16;
     // one wave of persistent CTAs: as many as are resident at once with this kernel's registers and shared memory
     static int per_sm = 0;
     if (per_sm == 0) {
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_head<PRO, EXACT>, 256, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_head<PRO>, 256, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
         if (per_sm > 3) per_sm = 3;
     }
-    int gx = (ntiles + 7) / 8; if (gx > 148 * per_sm) gx = 148 * per_sm;
+    int gx = (ntiles + 7) / 8; if (gx > sm_count() * per_sm) gx = sm_count() * per_sm;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)gx, (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS));
     cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;
@@ -278,7 +291,7 @@ static void launch_head_t(const DenseArgs& a, cudaStream_t st, bool pdl) {
     set_pdl(cfg, attr, pdl);
     DenseArgs copy = a;
     ProfScope ps("k_head", (double)a.N * a.K * 0.5625 + (double)a.M * a.K * 2, st);
-    cudaLaunchKernelEx(&cfg, k_head<PRO, EXACT>, copy);
+    cudaLaunchKernelEx(&cfg, k_head<PRO>, copy);
     COUNT_LAUNCH();
 }
 
@@ -305,7 +318,7 @@ int launch_head_static(const DenseArgs& in, cudaStream_t st) {
         unsigned char* ptr = nullptr;
         err = cudaGetSymbolAddress((void**)&ptr, g_head_static_scratch);
         if (err != cudaSuccess) return (int)err;
-        err = cudaFuncSetAttribute(k_head<PRO_PLAIN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        err = cudaFuncSetAttribute(k_head<PRO_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
         if (err != cudaSuccess) return (int)err;
         base[dev] = ptr;
     }
@@ -318,21 +331,21 @@ int launch_head_static(const DenseArgs& in, cudaStream_t st) {
     err = cudaMemsetAsync(a.counter, 0, sizeof(unsigned), st);
     if (err != cudaSuccess) return (int)err;
     const size_t smem = GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, a.K, 1, 1);
-    k_head<PRO_PLAIN, false><<<dim3((unsigned)gx, (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS)), 256, smem, st>>>(a);
+    k_head<PRO_PLAIN><<<dim3((unsigned)gx, (unsigned)((a.M + ROWS_PER_PASS - 1) / ROWS_PER_PASS)), 256, smem, st>>>(a);
     return (int)cudaGetLastError();
 }
 
-void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl) {
+void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pdl) {
     if (epi == EPI_ARGMAX) {
-        if (pro == PRO_RMSNORM) { if (exact) launch_head_t<PRO_RMSNORM, true>(a, st, pdl); else launch_head_t<PRO_RMSNORM, false>(a, st, pdl); return; }
-        if (pro == PRO_PLAIN) { if (exact) launch_head_t<PRO_PLAIN, true>(a, st, pdl); else launch_head_t<PRO_PLAIN, false>(a, st, pdl); return; }
+        if (pro == PRO_RMSNORM) { launch_head_t<PRO_RMSNORM>(a, st, pdl); return; }
+        if (pro == PRO_PLAIN) { launch_head_t<PRO_PLAIN>(a, st, pdl); return; }
     }
-    // Many rows (prefill chunks, large batches): the tcgen05 tensor-core GEMM, with the RMSNorm done by
-    // a row kernel first.  SEEDLESS_TC_ROWS sets the threshold (0 = never); below it, and for the gated
-    // norm of the GDN out-projection, the GEMV family walks the rows in passes of 8.
-    static int tc_rows = -1;
-    if (tc_rows < 0) { const char* v = getenv("SEEDLESS_TC_ROWS"); tc_rows = v ? atoi(v) : 128; }
-    if (tc_rows > 0 && a.M >= tc_rows && a.N % 128 == 0 && a.K % 256 == 0 && (epi == EPI_STORE || epi == EPI_RESID) &&
+    // Prefill mode (a.tc, chosen by the caller per CALL, never by the number of rows): the tcgen05
+    // tensor-core GEMM, with the RMSNorm done by a row kernel first.  Every row's result there is
+    // independent of how many rows share the call, so a prompt split into chunks in any way gives the
+    // same bits.  The gated norm of the GDN out-projection, and every call outside prefill mode, use
+    // the GEMV family, which walks the rows in passes of 8.
+    if (a.tc && a.N % 128 == 0 && a.K % 256 == 0 && (epi == EPI_STORE || epi == EPI_RESID) &&
         (pro == PRO_PLAIN || (pro == PRO_RMSNORM && a.norm_scratch))) {
         const __half* x = a.x; int ldx = a.ldx;
         if (pro == PRO_RMSNORM) {
@@ -348,7 +361,7 @@ void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t
         return;
     }
 gemv_path:
-    const GemvPlan pl = gemv_plan(a.K, epi == EPI_SWIGLU ? a.N / 8 : a.N / 16, 1);
+    const GemvPlan pl = gemv_plan(a.K, epi == EPI_SWIGLU ? a.N / 8 : a.N / 16, 1, sm_count());
     // eight-warp CTAs (same units per CTA, twice the units per warp) when a warp's slice stays fixed with a stride of 8
     static int narrow_env = -1;
     if (narrow_env < 0) { const char* v = getenv("SEEDLESS_GEMV_WARPS"); narrow_env = (v && atoi(v) == 8) ? 1 : 0; }   // measured equal to 16 warps; off unless asked for
@@ -878,7 +891,7 @@ static void launch_expert_t(const ExpertArgs& a, const GemvPlan& pl, int nslots,
     int K = DOWN ? a.I : a.H;
     int ntiles = DOWN ? a.H / 16 : a.I / 8;
     const int gx = (ntiles + pl.tpc - 1) / pl.tpc;
-    int gy = 148 / gx; if (gy < 1) gy = 1;
+    int gy = sm_count() / gx; if (gy < 1) gy = 1;
     if (gy > nslots + 1) gy = nslots + 1;                   // one CTA row per slot at batch 1; fewer rows than slots: CTAs walk them
     const int nstages = (gy < nslots + 1) ? 2 : 1;
     size_t smem = nstages * GemvSmem::wstage_bytes(16 * UPW) + GemvSmem::bytes(a.M < ROWS_PER_PASS ? a.M : ROWS_PER_PASS, K, 16 * UPW, pl.tpc);
@@ -1216,15 +1229,15 @@ static bool expert_fused2_ok(const ExpertArgs& a, int g1) {
 
 bool expert_fused_applicable(const ExpertArgs& a) {
     if (a.M != 1 || a.slot_sync == nullptr || a.tile_counter == nullptr || a.topk > 16) return false;
-    const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1);
+    const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1, sm_count()), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1, sm_count());
     const int g1 = (a.I / 8 + p1.tpc - 1) / p1.tpc, g2 = (a.H / 16 + p2.tpc - 1) / p2.tpc;
     if (g1 != g2 || p1.upw != 2 || p2.upw != 1) return false;            // the 2048 -> 512 -> 2048 expert shape
-    if (g1 * (a.topk + 1) > 148) return false;                           // every CTA must be resident at once
+    if (g1 * (a.topk + 1) > sm_count()) return false;                           // every CTA must be resident at once
     return true;
 }
 bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
     if (!expert_fused_applicable(a)) return false;
-    const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1);
+    const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1, sm_count()), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1, sm_count());
     const int g1 = (a.I / 8 + p1.tpc - 1) / p1.tpc;
     size_t smem = GemvSmem::wstage_bytes(32) + GemvSmem::wstage_bytes(16) + GemvSmem::bytes(1, a.H > a.I ? a.H : a.I, 32, p1.tpc > p2.tpc ? p1.tpc : p2.tpc);
     static bool configured = false;
@@ -1260,13 +1273,13 @@ bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
 // combine in the down kernel works on groups of TPC tiles, so tile_counter needs H/16/TPC entries
 template <bool DOWN>
 static void launch_expert_d(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) {
-    const GemvPlan pl = gemv_plan(DOWN ? a.I : a.H, DOWN ? a.H / 16 : a.I / 8, a.topk + 1);
+    const GemvPlan pl = gemv_plan(DOWN ? a.I : a.H, DOWN ? a.H / 16 : a.I / 8, a.topk + 1, sm_count());
     if (pl.upw == 1) launch_expert_t<DOWN, 1>(a, pl, nslots, st, pdl);
     else if (pl.upw == 2) launch_expert_t<DOWN, 2>(a, pl, nslots, st, pdl);
     else launch_expert_t<DOWN, 3>(a, pl, nslots, st, pdl);
 }
-void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { (void)exact; launch_expert_d<false>(a, nslots, st, pdl); }
-void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { (void)exact; launch_expert_d<true>(a, nslots, st, pdl); }
+void launch_expert_gateup(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { launch_expert_d<false>(a, nslots, st, pdl); }
+void launch_expert_down(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { launch_expert_d<true>(a, nslots, st, pdl); }
 
 // ---- expert-parallel helpers ----
 // One CTA: pairs (row, k) whose expert lies in [e0, e1) grouped by expert, in the format the expert
@@ -1795,6 +1808,18 @@ void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStr
     COUNT_LAUNCH();
 }
 
+
+// ---- test hook: a bounded wait that runs out ----
+// One CTA waits, with the same routine the weight stages use but a limit of a thousand polls, on an
+// mbarrier that nothing ever arms, and reports the way the real kernels do: it sets a bit in the error
+// word and returns.  Nothing faults and nothing hangs; the host sees the code at its next synchronisation.
+__global__ void k_wait_probe(unsigned* err) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait_bounded(&bar, 0, 1000)) atomicOr(err, 4u);
+}
+void launch_wait_probe(unsigned* err, cudaStream_t st) { k_wait_probe<<<1, 32, 0, st>>>(err); COUNT_LAUNCH(); }
 
 // ============================================================================================
 // End of a step: advance cache lengths, flip GDN ping-pong sides, feed greedy tokens back as

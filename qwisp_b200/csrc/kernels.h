@@ -9,7 +9,8 @@ struct Q4W { const uint32_t* w = nullptr; const __half* s = nullptr; const __hal
 struct DenseArgs {
     int lg_slices = 0;                   // log2(K/256), filled by the launcher
     unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
-    __half* norm_scratch = nullptr;      // [M][K] scratch for the many-row path (normed rows); nullptr keeps the GEMV path
+    __half* norm_scratch = nullptr;      // [M][K] scratch for the tensor-core path (normed rows); nullptr keeps the GEMV path
+    bool tc = false;                     // prefill mode: dense projections on the tcgen05 GEMM (set per call by the caller)
     Q4R q;                                                       // repacked weights (tiles of 16 rows)
     int N, K, M;                                                 // N outputs (= 16 * tiles)
     const __half* x; int ldx;                                    // activations (plain) / residual stream (rmsnorm) / y (normgate)
@@ -104,11 +105,12 @@ struct StepEndArgs {
     const int* out_tok; int* tok_in; int* hist; int* hist_pos; int hist_cap; int M;
 };
 
-void launch_dense(int pro, int epi, bool exact, const DenseArgs& a, cudaStream_t st, bool pdl);
+int sm_count();
+void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pdl);
 // many-row GEMM on tcgen05 tensor cores with the accumulator in tensor memory (N % 128 == 0, K % 256 == 0); 0 or an error code
 int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, __half* y, int ldy, bool add_to_y, unsigned* err, cudaStream_t st);
 // speculative-sampling rows on fp16 logits [M][V]: categorical draw, draw without the draft token, accept flag
-void launch_sample_rows(const __half* logits, const int* draft, int* samp_full, int* samp_resid, int* accept, int M, int V,
+void launch_sample_rows(const __half* logits, const float* adj /*[V] added to every row, or nullptr*/, const int* draft, int* samp_full, int* samp_resid, int* accept, int M, int V,
                         float invT, float top_p, uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, cudaStream_t st);
 // lm_head + argmax whose scratch is a fixed module-scope device array; returns 0 or a cudaError_t
 int launch_head_static(const DenseArgs& a, cudaStream_t st);
@@ -116,8 +118,8 @@ int head_static_max_rows();
 void launch_embed(const __half* embed, const int* tokens, int M, int H, int vocab, __half* h, cudaStream_t st);
 void launch_embed_dequant_q4(const uint32_t* w, const __half* s, const __half* b, __half* out, int64_t vocab, int H, cudaStream_t st);
 void launch_router(const RouterArgs& a, cudaStream_t st, bool pdl);
-void launch_expert_gateup(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
-void launch_expert_down(bool exact, const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
+void launch_expert_gateup(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
+void launch_expert_down(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl);
 // batch-1 decode: gate/up and down in ONE launch (a per-slot barrier between the phases); false if the shapes do not fit it
 bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl);
 bool expert_fused_applicable(const ExpertArgs& a);      // the shape test launch_expert_fused applies
@@ -132,6 +134,7 @@ void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
 void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStream_t st, bool pdl);
 void launch_step_end(const StepEndArgs& a, cudaStream_t st);
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st);
+void launch_wait_probe(unsigned* err, cudaStream_t st);   // test hook: a bounded wait that runs out sets bit 2 of *err
 int64_t kernel_launch_count();
 void profile_start();
 int profile_report(char* buf, size_t cap);

@@ -71,7 +71,9 @@ __device__ __forceinline__ float block_sum_fixed(float v, float* sm32) {
 }
 __device__ __forceinline__ bool better_si(float s, int i, float bs, int bi) { return s > bs || (s == bs && i < bi); }
 
-__global__ void __launch_bounds__(SAMP_T) k_sample_rows(const __half* logits, const int* draft, int* samp_full, int* samp_resid, int* accept,
+// adj: optional [V] f32 penalties / bias added to every row's logits before anything else looks at them
+// (the reference's LADJ(v) = float(row[v]) + logitAdj[v], SamplerGPU.swift:41,69); nullptr = none.
+__global__ void __launch_bounds__(SAMP_T) k_sample_rows(const __half* logits, const float* adj, const int* draft, int* samp_full, int* samp_resid, int* accept,
                                                         float invT, int V, uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, float top_p) {
     __shared__ float sm32[32];
     __shared__ float s_fs[32], s_rs[32]; __shared__ int s_fi[32], s_ri[32];
@@ -82,9 +84,10 @@ __global__ void __launch_bounds__(SAMP_T) k_sample_rows(const __half* logits, co
     const int d = draft ? draft[m] : -1;
     const bool greedy = invT <= 0.0f;
     const uint32_t salt = seed_hi ^ (base_pos + (uint32_t)m);
-    // pass 1: maximum logit
+    auto ladj = [&](int v) -> float { const float L = h2f(row[v]); return adj ? __fadd_rn(L, adj[v]) : L; };
+    // pass 1: maximum (adjusted) logit
     float mx = -INFINITY;
-    for (int v = tid; v < V; v += SAMP_T) mx = fmaxf(mx, h2f(row[v]));
+    for (int v = tid; v < V; v += SAMP_T) mx = fmaxf(mx, ladj(v));
     mx = warp_max(mx);
     if (lane == 0) sm32[warp] = mx;
     __syncthreads();
@@ -98,7 +101,7 @@ __global__ void __launch_bounds__(SAMP_T) k_sample_rows(const __half* logits, co
         const float bin_w = SAMP_SPAN / (float)SAMP_BINS;
         float z = 0.f;
         for (int v = tid; v < V; v += SAMP_T) {
-            const float g = __fmul_rn(__fsub_rn(gmax, h2f(row[v])), invT);
+            const float g = __fmul_rn(__fsub_rn(gmax, ladj(v)), invT);
             const float w = det_expf(-g);
             z = __fadd_rn(z, w);
             if (do_top_p) {
@@ -119,14 +122,14 @@ __global__ void __launch_bounds__(SAMP_T) k_sample_rows(const __half* logits, co
             __syncthreads();
             lthr = s_lthr;
             float zn = 0.f;
-            for (int v = tid; v < V; v += SAMP_T) { const float L = h2f(row[v]); if (L >= lthr) zn = __fadd_rn(zn, det_expf(__fmul_rn(__fsub_rn(L, gmax), invT))); }
+            for (int v = tid; v < V; v += SAMP_T) { const float L = ladj(v); if (L >= lthr) zn = __fadd_rn(zn, det_expf(__fmul_rn(__fsub_rn(L, gmax), invT))); }
             znuc = block_sum_fixed(zn, sm32);
         }
     }
     // Gumbel-max over the nucleus: full, and excluding the draft token
     float fs = -INFINITY, rs = -INFINITY; int fi = 0x7fffffff, ri = 0x7fffffff;
     for (int v = tid; v < V; v += SAMP_T) {
-        const float L = h2f(row[v]);
+        const float L = ladj(v);
         if (do_top_p && L < lthr) continue;
         float score = L;
         if (!greedy) {
@@ -156,7 +159,7 @@ __global__ void __launch_bounds__(SAMP_T) k_sample_rows(const __half* logits, co
         if (d >= 0) {
             if (greedy) p_draft = (d == fi) ? 1.0f : 0.0f;
             else {
-                const float Ld = h2f(row[d]);
+                const float Ld = ladj(d);
                 if (!do_top_p || Ld >= lthr) p_draft = __fdiv_rn(det_expf(__fmul_rn(__fsub_rn(Ld, gmax), invT)), znuc);
             }
         }
@@ -164,9 +167,9 @@ __global__ void __launch_bounds__(SAMP_T) k_sample_rows(const __half* logits, co
         accept[m] = (coin < p_draft) ? 1 : 0;
     }
 }
-void launch_sample_rows(const __half* logits, const int* draft, int* samp_full, int* samp_resid, int* accept, int M, int V,
+void launch_sample_rows(const __half* logits, const float* adj, const int* draft, int* samp_full, int* samp_resid, int* accept, int M, int V,
                         float invT, float top_p, uint32_t seed_lo, uint32_t seed_hi, uint32_t base_pos, cudaStream_t st) {
-    k_sample_rows<<<M, SAMP_T, 0, st>>>(logits, draft, samp_full, samp_resid, accept, invT, V, seed_lo, seed_hi, base_pos, top_p);
+    k_sample_rows<<<M, SAMP_T, 0, st>>>(logits, adj, draft, samp_full, samp_resid, accept, invT, V, seed_lo, seed_hi, base_pos, top_p);
 }
 
 }  // namespace sl

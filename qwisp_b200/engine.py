@@ -82,6 +82,10 @@ class Engine:
     def inject_fault(self, on=True):
         lib().sl_inject_fault(self._h, 1 if on else 0)
 
+    def debug_wait_timeout(self):
+        """Test hook: enqueue a kernel whose bounded wait runs out (nothing faults); the next call fails."""
+        self._check(lib().sl_debug_wait_timeout(self._h), "sl_debug_wait_timeout")
+
     def set_cuda_stream(self, cuda_stream_handle):
         self._check(lib().sl_engine_set_cuda_stream(self._h, C.c_void_p(cuda_stream_handle)), "sl_engine_set_cuda_stream")
 
@@ -178,6 +182,13 @@ class Stream:
         self.engine._check(lib().sl_forward(self._h, _ptr(toks), len(toks), _ptr(out)), "sl_forward")
         return out
 
+    def forward_hybrid(self, tokens, want_hidden=True):
+        """Prefill-only forward (dense projections on the tensor cores); same outputs as forward()."""
+        toks = _i32(tokens)
+        out = np.empty((len(toks), self.engine.cfg.hidden), dtype=np.float16) if want_hidden else None
+        self.engine._check(lib().sl_forward_hybrid(self._h, _ptr(toks), len(toks), _ptr(out)), "sl_forward_hybrid")
+        return out
+
     def step_argmax(self, tokens):
         toks = _i32(tokens)
         out = np.empty(len(toks), dtype=np.int32)
@@ -197,13 +208,18 @@ class Stream:
         self.engine._check(lib().sl_chained_collect(self._h, K, _ptr(out)), "sl_chained_collect")
         return out
 
-    def step_sample_rows(self, tokens, draft, inv_t, top_p, seed_lo, seed_hi, base_pos):
-        """Forward the rows, then sample on the device: -> (full, resid, accept) int32 [M]."""
+    def step_sample_rows(self, tokens, draft, inv_t, top_p, seed_lo, seed_hi, base_pos, logit_adj=None):
+        """Forward the rows, then sample on the device: -> (full, resid, accept) int32 [M].
+        logit_adj: optional f32 [vocab] added to every row's logits first (penalties + bias)."""
         toks = _i32(tokens)
         M = len(toks)
         d = None if draft is None else _i32(draft)
+        adj = None if logit_adj is None else np.ascontiguousarray(logit_adj, dtype=np.float32)
+        if adj is not None and adj.shape != (self.engine.cfg.vocab,):
+            raise ValueError("logit_adj must have one entry per vocabulary token")
         full, resid, acc = (np.empty(M, dtype=np.int32) for _ in range(3))
-        self.engine._check(lib().sl_step_sample_rows(self._h, _ptr(toks), M, _ptr(d) if d is not None else None, float(inv_t), float(top_p),
+        self.engine._check(lib().sl_step_sample_rows(self._h, _ptr(toks), M, _ptr(d) if d is not None else None,
+                                                     _ptr(adj) if adj is not None else None, float(inv_t), float(top_p),
                                                      int(seed_lo), int(seed_hi), int(base_pos), _ptr(full), _ptr(resid), _ptr(acc)), "sl_step_sample_rows")
         return full, resid, acc
 
@@ -262,9 +278,11 @@ class FullSnapshot:
 class SpecBackend:
     """The closure set Tell's speculative loop drives, bound to one stream."""
 
-    def __init__(self, stream, hybrid_chunk=64):
+    def __init__(self, stream, hybrid_chunk=None):
         self.stream = stream
-        self.hybrid_chunk = min(hybrid_chunk, stream.engine.cfg.max_rows)
+        # rows per prefill call: the library's own figure, min(1024, max_rows) (TellRuntime.swift:234-238), unless given
+        chunk = lib().sl_hybrid_chunk(stream.engine._h)
+        self.hybrid_chunk = min(hybrid_chunk, chunk) if hybrid_chunk else chunk
 
     def _guard(self, fn, *a):
         try:
@@ -275,7 +293,8 @@ class SpecBackend:
     def forward(self, tokens):
         return self._guard(self.stream.forward, tokens)
 
-    forward_hybrid = forward
+    def forward_hybrid(self, tokens):
+        return self._guard(self.stream.forward_hybrid, tokens)
 
     def step_argmax(self, tokens):
         r = self._guard(self.stream.step_argmax, tokens)

@@ -56,6 +56,15 @@ def mixer(stream, layer, x, pos0):
     return out
 
 
+def read_kv(stream, layer_index, pos0, n):
+    """Cached K (post-RoPE) and V of an attention layer at positions pos0..pos0+n-1: two fp16 [kv_heads, n, 256]."""
+    cfg = stream.engine.cfg
+    k = np.empty((cfg.attn_kv_heads, n, 256), dtype=np.float16)
+    v = np.empty_like(k)
+    stream.engine._check(lib().sl_op_read_kv(stream._h, layer_index, pos0, n, _p(k), _p(v)), "sl_op_read_kv")
+    return k, v
+
+
 def layer(stream, layer_index, h_in, pos0):
     h_in = np.ascontiguousarray(h_in, dtype=np.float16)
     out = np.empty_like(h_in)
@@ -97,12 +106,15 @@ def synth_f16(seed, name, n, mean=0.0, std=1.0):
     return out
 
 
-def sample_rows(engine, logits, draft, inv_t, top_p, seed_lo, seed_hi, base_pos):
-    """The sampling kernel on host logits [M, vocab] fp16 -> (full, resid, accept) int32 [M]."""
+def sample_rows(engine, logits, draft, inv_t, top_p, seed_lo, seed_hi, base_pos, logit_adj=None):
+    """The sampling kernel on host logits [M, vocab] fp16 -> (full, resid, accept) int32 [M].
+    logit_adj: optional f32 [vocab] added to every row first (penalties + bias)."""
     logits = np.ascontiguousarray(logits, dtype=np.float16)
     M = logits.shape[0]
     d = None if draft is None else np.ascontiguousarray(draft, dtype=np.int32)
+    adj = None if logit_adj is None else np.ascontiguousarray(logit_adj, dtype=np.float32)
     full, resid, acc = (np.empty(M, dtype=np.int32) for _ in range(3))
-    engine._check(lib().sl_op_sample_rows(engine._h, _p(logits), M, _p(d) if d is not None else None, float(inv_t), float(top_p),
+    engine._check(lib().sl_op_sample_rows(engine._h, _p(logits), M, _p(d) if d is not None else None,
+                                          _p(adj) if adj is not None else None, float(inv_t), float(top_p),
                                           int(seed_lo), int(seed_hi), int(base_pos), _p(full), _p(resid), _p(acc)), "sl_op_sample_rows")
     return full, resid, acc

@@ -31,7 +31,7 @@ def test_struct_layout_matches_header():
     assert C.sizeof(_lib.SlConfig) == 17 * 4
     assert C.sizeof(_lib.SlSynthSpec) == 16
     assert C.sizeof(_lib.SlWeightDesc) == 32
-    assert C.sizeof(_lib.SlSnap) == 12
+    assert C.sizeof(_lib.SlSnap) == 16
 
 
 def test_no_oracle_in_product():

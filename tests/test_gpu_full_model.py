@@ -74,3 +74,97 @@ def test_full_model_end_to_end_drift_report():
         assert gpu_rep["mean_abs"] <= 4.0 * alt_rep["mean_abs"] + 1e-3
     finally:
         eng.close()
+
+
+def test_full_model_256_steps_teacher_forced():
+    """BASELINE's headline check on the full model: a prompt, then 256 greedy decode steps of the oracle's
+    own token stream.
+
+    (1) Layer-wise teacher forcing, every step: each layer and the head get the oracle's input for that
+        step and must reproduce its output (max-abs <= 2e-2 per layer and on the logits); the greedy token
+        from identical final hidden states must agree on >= 99% of the steps.  The flips and the oracle's
+        top-1 / top-2 margin at each flip are printed.
+    (2) Token-level teacher forcing, as information with a bound: the engine decodes the same token stream
+        end to end (its own hidden states and caches); per-step argmax agreement and logits error are
+        printed next to the same figures for the oracle against ITSELF under another lane-reduction order
+        on the first 64 steps.  Two correct implementations drift apart on a random-weight model; the
+        engine's drift must stay within 3x the oracle's own.
+    SEEDLESS_TF_STEPS / SEEDLESS_TF_PROMPT shorten or lengthen the run (defaults 256 / 32; BASELINE's
+    prompt is 512 tokens, shortened here to bound the CPU oracle's time, which this docstring states)."""
+    import os
+    import qwisp_b200 as Q
+    from oracle import oracle as O
+    K = int(os.environ.get("SEEDLESS_TF_STEPS", "256"))
+    P = int(os.environ.get("SEEDLESS_TF_PROMPT", "32"))
+    cfg = Q.config(max_rows=max(P, 16), max_streams=3, kv_page_size=64, kv_pages=3 * ((P + K) // 64 + 2))
+    eng = Q.Engine.synthetic(cfg, seed=0, norm_jitter=0.0, conv_std=0.02)
+    orc = O.Model(O.config(), 0, lazy_experts=True)
+    try:
+        toks = O.synth_tokens(0, "bench.prompt", P, cfg.vocab)
+        so, sg, st = orc.stream(P + K + 8), eng.stream(P + K + 8), eng.stream(P + K + 8)
+        worst = 0.0
+
+        def layerwise(tok_rows, pos0):
+            nonlocal worst
+            h = orc.embed(tok_rows)
+            for layer in range(cfg.n_layers):
+                ref = so.layer_rows(layer, h, pos0)
+                got = Q.ops.layer(sg, layer, h, pos0)
+                e = f16_report(got, ref)["max_abs"]
+                worst = max(worst, e)
+                assert e <= 2e-2, (pos0, layer, e)
+                h = ref
+            rl, rt = orc.head(h[-1:])
+            gl, gt = Q.ops.head(eng, h[-1:])
+            return rl[0].astype(np.float32), int(rt[0]), gl[0].astype(np.float32), int(gt[0])
+
+        rl, cur, gl, gt = layerwise(toks, 0)
+        tl = st.step_logits(toks)[-1].astype(np.float32)
+        fed = [cur]
+        lw_agree, tok_agree, lw_err, tok_err, flips, tok_flips = 0, 0, 0.0, [], [], 0
+        ref_tokens, ref_logits = [], []
+        for i in range(K):
+            rl, nxt, gl, gt = layerwise([cur], P + i)
+            tl = st.step_logits([cur])[0].astype(np.float32)
+            srt = np.sort(rl)
+            margin = float(srt[-1] - srt[-2])
+            lw_err = max(lw_err, float(np.abs(gl - rl).max()))
+            if gt == nxt:
+                lw_agree += 1
+            else:
+                flips.append((i, margin))
+            tok_err.append(float(np.abs(tl - rl).mean()))
+            if int(np.argmax(tl)) == nxt:
+                tok_agree += 1
+            ref_tokens.append(nxt)
+            if i < 64:
+                ref_logits.append(rl)
+            cur = nxt
+            fed.append(cur)
+        print(f"layer-wise teacher forcing, {K} steps after a {P}-token prompt: worst layer max-abs {worst:.5f}, "
+              f"logits max-abs {lw_err:.5f}, greedy agreement {lw_agree}/{K}, flips (step, oracle margin): {flips}")
+        print(f"token-level teacher forcing: greedy agreement {tok_agree}/{K}, logits mean-abs per step "
+              f"median {float(np.median(tok_err)):.4f} max {float(np.max(tok_err)):.4f}")
+        assert lw_err <= 2e-2
+        assert lw_agree >= int(np.ceil(0.99 * K)), (lw_agree, flips)
+        # control: the oracle against itself with another reduction order, token-level, first 64 steps
+        n_ctl = min(64, K)
+        O.set_alt_order(True)
+        try:
+            sa = orc.stream(P + n_ctl + 8)
+            sa.step(toks)
+            ctl_agree, ctl_mean = 0, []
+            for i in range(n_ctl):
+                _, al = sa.step([fed[i]], want_logits=True)
+                al = al[0].astype(np.float32)
+                ctl_agree += int(np.argmax(al)) == ref_tokens[i]
+                ctl_mean.append(float(np.abs(al - ref_logits[i]).mean()))      # the oracle's own logits of that step (its own hidden states)
+        finally:
+            O.set_alt_order(False)
+        print(f"control (oracle, other lane-reduction order, token-level, {n_ctl} steps): greedy agreement {ctl_agree}/{n_ctl}, "
+              f"logits mean-abs median {float(np.median(ctl_mean)):.4f}; engine on the same steps: "
+              f"median {float(np.median(tok_err[:n_ctl])):.4f}")
+        assert float(np.median(tok_err[:n_ctl])) <= 3.0 * float(np.median(ctl_mean)) + 1e-3
+        sg.close(); st.close()
+    finally:
+        eng.close()

@@ -19,7 +19,7 @@ def _ptr(t):
     return C.c_void_p(t.data_ptr())
 
 
-def _make_weights(torch, L, seed):
+def _make_weights(torch, L, seed, N=N):
     g = torch.Generator(device="cuda").manual_seed(seed)
     w = torch.randint(0, 2 ** 31 - 1, (N, K // 8), generator=g, device="cuda", dtype=torch.int64).to(torch.int32)
     s = (torch.rand((N, K // 64), generator=g, device="cuda") * 0.01 + 0.002).to(torch.float16)
@@ -50,6 +50,56 @@ def test_static_scratch_argmax_matches_gemv_twice():
         want = np.argmax(logits, axis=1).astype(np.int32)          # first maximum = lowest index on ties
         got = tok.cpu().numpy()
         assert np.array_equal(got, want), (call, got, want)
+
+
+def test_static_scratch_argmax_full_vocabulary():
+    """The real vocabulary (151,936 rows): the grid is capped at the scratch array's 444 partial slots, so
+    every CTA strides over many tiles and the final reduction reads 444 partials per row.  Two calls in a
+    row (8 rows, then 1) against the argmax of the GEMV entry point's logits."""
+    import torch
+    import qwisp_b200 as Q
+    L = Q.lib()
+    NV = 151936
+    wr, sr = _make_weights(torch, L, 13, N=NV)
+    g = torch.Generator(device="cuda").manual_seed(17)
+    for call, M in enumerate((MAX_ROWS, 1)):
+        x = torch.randn((M, K), generator=g, device="cuda").to(torch.float16)
+        y = torch.empty((M, NV), dtype=torch.float16, device="cuda")
+        tok = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+        assert L.sl_op_qmm4_device(_ptr(x), _ptr(wr), _ptr(sr), M, K, NV, _ptr(y), None) == 0
+        assert L.sl_op_lm_head_argmax_static(_ptr(x), _ptr(wr), _ptr(sr), M, K, NV, _ptr(tok), None) == 0
+        torch.cuda.synchronize()
+        logits = y.cpu().numpy().astype(np.float32)
+        assert np.isfinite(logits).all()
+        want = np.argmax(logits, axis=1).astype(np.int32)
+        got = tok.cpu().numpy()
+        assert np.array_equal(got, want), (call, got, want)
+
+
+def test_static_scratch_argmax_matches_cpu_oracle():
+    """The same entry point against the CPU oracle's 4-bit product on seeded weights: identical tokens on
+    every row whose top-1 / top-2 margin is clear of fp16 rounding."""
+    import torch
+    import qwisp_b200 as Q
+    from oracle import oracle as O
+    L = Q.lib()
+    packed, scales, biases = O.synth_q4(21, "noalloc.w", N, K)
+    x = O.synth_f16(21, "noalloc.x", MAX_ROWS * K).reshape(MAX_ROWS, K)
+    ref = O.qmm4(x, packed, scales, biases).astype(np.float32)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(-1)).cuda()
+    dw, ds, db, dx = dev(packed), dev(scales), dev(biases), dev(x)
+    wr = torch.empty((N // 16) * (K // 128) * 1024, dtype=torch.uint8, device="cuda")
+    sr = torch.empty((N // 16) * (K // 128) * 128, dtype=torch.uint8, device="cuda")
+    assert L.sl_op_repack_q4_device(_ptr(dw), _ptr(ds), _ptr(db), K, N, _ptr(wr), _ptr(sr), None) == 0
+    tok = torch.full((MAX_ROWS,), -1, dtype=torch.int32, device="cuda")
+    assert L.sl_op_lm_head_argmax_static(_ptr(dx), _ptr(wr), _ptr(sr), MAX_ROWS, K, N, _ptr(tok), None) == 0
+    torch.cuda.synchronize()
+    got = tok.cpu().numpy()
+    srt = np.sort(ref, axis=1)
+    clear = (srt[:, -1] - srt[:, -2]) > 8e-3
+    assert clear.any()
+    assert np.array_equal(got[clear], np.argmax(ref, axis=1)[clear])
+    assert ((got >= 0) & (got < N)).all()
 
 
 def test_static_scratch_rejects_rows_beyond_limit():
