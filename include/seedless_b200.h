@@ -123,6 +123,11 @@ int32_t sl_debug_wait_timeout(sl_engine* e);
 int64_t sl_engine_launch_count(sl_engine* e);
 /* Replay decode steps as CUDA graphs (default on) or launch every kernel eagerly. */
 int32_t sl_engine_use_graphs(sl_engine* e, int32_t on);
+/* Single-stream decode steps (sl_step_argmax with one row, chained steps) run as ONE kernel launch per token
+ * when the geometry and the device allow it (the default), or as the kernel-per-phase assembly that serves every
+ * other call.  Both produce the same tokens.  on = 0 / 1 selects; on < 0 only queries.  Returns 1 when the
+ * one-kernel step is available (query: and selected), 0 otherwise. */
+int32_t sl_engine_use_persistent(sl_engine* e, int32_t on);
 /* Per-kernel timing with CUDA events on the launching stream, for eager launches only (the
  * reference's profiled forward splits its command buffer per stage for the same purpose,
  * SeedlessFusedVerify.swift:4352-4378).  The report has one line per kernel:

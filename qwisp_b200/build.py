@@ -6,8 +6,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libseedless_b200.so")
-SOURCES = ["synth.cu", "kernels.cu", "sampler.cu", "gemm_tc.cu", "engine.cu"]
-HEADERS = ["common.cuh", "gemv.cuh", "kernels.h", os.path.join("..", "..", "include", "seedless_b200.h")]
+SOURCES = ["synth.cu", "kernels.cu", "step_persistent.cu", "sampler.cu", "gemm_tc.cu", "engine.cu"]
+HEADERS = ["common.cuh", "gemv.cuh", "mixer_math.cuh", "route.cuh", "kernels.h", os.path.join("..", "..", "include", "seedless_b200.h")]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -90,6 +90,9 @@ struct sl_engine {
     bool use_prefetch = false;      // L2 prefetch of the weights later kernels read (SEEDLESS_PREFETCH=1); slower now that
                                     // every kernel starts its own weight copies ahead of the launch wait
     bool use_pdl = true;            // programmatic dependent launch between the kernels of a step (SEEDLESS_PDL=0 turns it off)
+    // the one-kernel decode step (step_persistent.cu): used for single-stream decode steps when the geometry fits
+    bool ps_ok = false, use_persistent = true;   // SEEDLESS_PERSISTENT=0 / sl_engine_use_persistent(e, 0): kernel-per-phase assembly
+    PStepArgs ps{};
     bool poisoned = false, inject = false;
     std::string fault;
 };
@@ -378,6 +381,65 @@ int32_t repack_all(sl_engine* e) {
     return SL_OK;
 }
 
+// Set up the one-kernel decode step: the layer table on the device, the exchange lines, the sequence word.
+// Leaves ps_ok false (the kernel-per-phase assembly then serves every call) when the geometry or the device does
+// not fit: 8-bit router weights, too few multiprocessors for a phase, no cooperative launch.
+int32_t setup_persistent(sl_engine* e) {
+    const sl_config& c = e->cfg;
+    for (const LayerW& L : e->layers) if (L.router_q8) return SL_OK;
+    PsGeom g{};
+    g.H = e->H; g.I = e->I; g.E = e->E; g.topk = e->topk; g.V = e->V;
+    g.Hk = c.gdn_k_heads; g.Hv = c.gdn_v_heads; g.NH = c.attn_heads; g.KV = c.attn_kv_heads;
+    g.keyDim = e->keyDim; g.valDim = e->valDim; g.convDim = e->convDim; g.gdn_in = e->gdn_in; g.attn_in = e->attn_in; g.attn_out = e->attn_out;
+    if (!ps_plan(g, sm_count())) return SL_OK;
+    std::vector<PLayer> host(e->layers.size());
+    for (size_t i = 0; i < e->layers.size(); ++i) {
+        const LayerW& L = e->layers[i]; PLayer& P = host[i];
+        P.is_attn = L.is_attn ? 1 : 0; P.type_index = L.type_index;
+        P.in_norm = L.in_norm; P.post_norm = L.post_norm; P.r_in = L.r_in; P.r_out = L.r_out;
+        P.conv_w = L.conv_w; P.A_log = L.A_log; P.dt_bias = L.dt_bias; P.gdn_norm = L.gdn_norm; P.gdn_norm32 = L.gdn_norm32;
+        P.q_norm = L.q_norm; P.k_norm = L.k_norm; P.router = L.router; P.shared_gate = L.shared_gate;
+        P.r_gu = L.r_gu; P.r_down = L.r_down; P.r_sh_gu = L.r_sh_gu; P.r_sh_down = L.r_sh_down;
+    }
+    PLayer* dl = nullptr; int32_t rc;
+    if ((rc = dalloc(e, &dl, host.size()))) return rc;
+    CU(e, cudaMemcpy(dl, host.data(), host.size() * sizeof(PLayer), cudaMemcpyHostToDevice));
+    PStepArgs& a = e->ps;
+    a.geom = g; a.layers = dl; a.n_layers = (int)host.size();
+    a.embed = e->embed; a.final_norm = e->final_norm; a.lm_head = e->r_lm_head;
+    a.eps = c.rms_eps; a.theta = c.rope_theta;
+    a.tab = e->tab; a.segs = e->segs; a.kv_pool = e->kv_pool; a.n_attn_layers = e->n_attn > 0 ? e->n_attn : 1; a.page_size = c.kv_page_size; a.nsplit = NSPLIT;
+    a.tok_in = e->tok_in; a.out_tok = e->out_tok; a.hist = e->hist; a.hist_pos = e->hist_pos; a.hist_cap = e->hist_cap;
+    // exchange lines of a layer (16 bytes carry 4 halves): residual stream in, in-projection out, mixer out,
+    // residual stream after the mixer, router logits (one per half line) + shared-gate logit, SwiGLU rows; the
+    // block after the last layer also holds one argmax line per CTA
+    int off = 0;
+    const int in_w = e->gdn_in > e->attn_in ? e->gdn_in : e->attn_in, mix_w = e->valDim > e->attn_out ? e->valDim : e->attn_out;
+    a.x_off_h = off; off += e->H / 4;
+    a.x_off_in = off; off += (in_w + 3) / 4;
+    a.x_off_mix = off; off += mix_w / 4;
+    a.x_off_hm = off; off += e->H / 4;
+    a.x_off_lg = off; off += (e->E + 2) / 2;
+    a.x_off_hb = off; off += (e->topk + 1) * e->I / 4;
+    a.x_off_arg = off; off += g.G;
+    a.x_stride = (size_t)((off + 7) & ~7);
+    const size_t xlines = a.x_stride * (host.size() + 1);
+    if ((rc = dalloc(e, &a.xbuf, xlines))) return rc;
+    CU(e, cudaMemset(a.xbuf, 0, xlines * sizeof(uint4)));
+    a.xatt_stride = (size_t)c.attn_heads * NSPLIT * 129;
+    const size_t alines = a.xatt_stride * (size_t)(e->n_attn > 0 ? e->n_attn : 1);
+    if ((rc = dalloc(e, &a.xatt, alines))) return rc;
+    CU(e, cudaMemset(a.xatt, 0, alines * sizeof(uint4)));
+    unsigned* words = nullptr;
+    if ((rc = dalloc(e, &words, (size_t)4))) return rc;
+    const unsigned init[4] = {1u, 0u, 0u, 0u};
+    CU(e, cudaMemcpy(words, init, sizeof(init), cudaMemcpyHostToDevice));
+    a.step_seq = words; a.abort_flag = words + 1; a.err = e->err_flag;
+    { const char* v = getenv("SEEDLESS_PERSISTENT"); if (v) e->use_persistent = (v[0] == '1'); }
+    e->ps_ok = true;
+    return SL_OK;
+}
+
 // ---------------------------------------------------------------- NCCL, loaded on demand
 // The library has no link-time dependency on NCCL: expert-parallel mode resolves the few entry
 // points it needs from the process's libnccl.so.2 (the copy the host framework already loaded, if any).
@@ -584,6 +646,12 @@ int32_t upload_descs(sl_engine* e, const std::vector<SegDesc>& segs, const int32
 
 // decode-shaped steps (every segment one row) replay a CUDA graph after the first eager run
 int32_t enqueue_decode_step(sl_engine* e, int rows) {
+    // a single stream's decode step: one launch of the step kernel does the whole token
+    if (rows == 1 && !e->ep_step && e->ps_ok && e->use_persistent) {
+        profile_launch("k_step_persistent", e->stream, [&] { return launch_step_persistent(e->ps, e->stream); });
+        CU(e, cudaGetLastError());
+        return SL_OK;
+    }
     // expert-parallel steps are enqueued eagerly: capturing the NCCL collectives into the step graph
     // deadlocked on two ranks when it was tried, so that combination is not offered
     if (!e->use_graph || e->ep_step) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return e->poisoned ? SL_ERR_CUDA : SL_OK; }
@@ -772,7 +840,7 @@ int32_t sl_engine_create(const sl_config* cfg, const sl_weight_desc* weights, in
         seen[d.name] = true;
     }
     if (seen.size() != e->tensors.size()) { sl_engine_destroy(e); return SL_ERR_INVALID; }   // every tensor must be given
-    if ((rc = repack_all(e))) { sl_engine_destroy(e); return rc; }
+    if ((rc = repack_all(e)) || (rc = setup_persistent(e))) { sl_engine_destroy(e); return rc; }
     *out = e;
     return SL_OK;
 }
@@ -806,7 +874,7 @@ int32_t sl_engine_create_synthetic(const sl_config* cfg, const sl_synth_spec* sy
         }
     }
     if (cudaStreamSynchronize(st) != cudaSuccess || cudaGetLastError() != cudaSuccess) { sl_engine_destroy(e); return SL_ERR_CUDA; }
-    if ((rc = repack_all(e))) { sl_engine_destroy(e); return rc; }
+    if ((rc = repack_all(e)) || (rc = setup_persistent(e))) { sl_engine_destroy(e); return rc; }
     *out = e;
     return SL_OK;
 }
@@ -855,6 +923,12 @@ int32_t sl_debug_wait_timeout(sl_engine* e) {
 int32_t sl_inject_fault(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->inject = on != 0; return SL_OK; }
 int64_t sl_engine_launch_count(sl_engine* e) { (void)e; return kernel_launch_count(); }
 int32_t sl_engine_use_graphs(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->use_graph = on != 0; return SL_OK; }
+int32_t sl_engine_use_persistent(sl_engine* e, int32_t on) {
+    if (!e) return SL_ERR_INVALID;
+    if (on < 0) return e->ps_ok ? (e->use_persistent ? 1 : 0) : 0;          // query
+    e->use_persistent = on != 0;
+    return e->ps_ok ? 1 : 0;
+}
 int32_t sl_profile_start(sl_engine* e) { if (!e) return SL_ERR_INVALID; cudaStreamSynchronize(e->stream); profile_start(); return SL_OK; }
 int32_t sl_profile_report(sl_engine* e, char* buf, uint64_t cap) {
     if (!e || !buf) return SL_ERR_INVALID;

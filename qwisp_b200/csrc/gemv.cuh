@@ -135,6 +135,29 @@ __device__ __forceinline__ float sumsq8(uint4 v) {
     for (int i = 0; i < 4; ++i) { float2 f = __half22float2(hh[i]); ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss); }
     return ss;
 }
+// Gated RMSNorm of 8 consecutive values of one 128-wide head (the 16 lanes of a half warp hold the head):
+// fp16(silu_f32(z) * float(w * fp16(y * inv))); with an f32 weight (PRO_NORMGATE32) the normed value stays
+// f32, w * (y * inv) (the reference's promoted variant, SeedlessFusedVerify.swift:766-813).
+template <int PRO>
+__device__ __forceinline__ uint4 normgate8(uint4 v, uint4 zv, uint4 wv, const float* nw32, int k0, float eps) {
+    const __half* yh = reinterpret_cast<const __half*>(&v);
+    const __half* zh = reinterpret_cast<const __half*>(&zv);
+    const __half* wh = reinterpret_cast<const __half*>(&wv);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { float f = h2f(yh[i]); ss = fmaf(f, f, ss); }
+    ss = half_warp_sum(ss);                       // 16 lanes per head of 128
+    float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), eps));
+    uint4 o; __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float yn = __fmul_rn(h2f(yh[i]), inv);
+        float nrm = (PRO == PRO_NORMGATE32) ? __fmul_rn(nw32[(k0 & 127) + i], yn) : h2f(hmul_rn(wh[i], f2h(yn)));
+        float zf = h2f(zh[i]);
+        oh[i] = f2h(__fmul_rn(__fmul_rn(zf, sigmoid_f(zf)), nrm));
+    }
+    return o;
+}
 // RMSNorm: x = w * fp16(h * inv), inv = rsqrt(mean(h^2) + eps) (SeedlessMetalForward.swift:800-827).
 // Gated RMSNorm of the GDN out-projection, per head of 128:
 // x = fp16(silu_f32(z) * float(w * fp16(y * inv))) (SeedlessFusedVerify.swift:803-813).
@@ -168,24 +191,7 @@ __device__ __forceinline__ void stage_finish(const StageRegs& sr, const XStage& 
             const int row = s.rows ? s.rows[col] : row0 + col;
             const uint4 zv = (j == 0) ? sr.c[0] : ((j == 1) ? sr.c[1] : __ldcg(reinterpret_cast<const uint4*>(s.z + (size_t)row * s.ldz + k0)));
             const uint4 wv = (j == 0) ? sr.b[0] : ((j == 1) ? sr.b[1] : *reinterpret_cast<const uint4*>(s.nw + (k0 & 127)));
-            const __half* yh = reinterpret_cast<const __half*>(&v);
-            const __half* zh = reinterpret_cast<const __half*>(&zv);
-            const __half* wh = reinterpret_cast<const __half*>(&wv);
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { float f = h2f(yh[i]); ss = fmaf(f, f, ss); }
-            ss = half_warp_sum(ss);                       // 16 lanes per head of 128
-            float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.0f), s.eps));
-            __half* oh = reinterpret_cast<__half*>(&o);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                // f32 weight: the normed value stays f32, w * (y * inv) (the reference's promoted variant,
-                // SeedlessFusedVerify.swift:766-813 with a float weight); fp16 weight: w * fp16(y * inv) as halves
-                const float yn = __fmul_rn(h2f(yh[i]), inv);
-                float nrm = (PRO == PRO_NORMGATE32) ? __fmul_rn(s.nw32[(k0 & 127) + i], yn) : h2f(hmul_rn(wh[i], f2h(yn)));
-                float zf = h2f(zh[i]);
-                oh[i] = f2h(__fmul_rn(__fmul_rn(zf, sigmoid_f(zf)), nrm));
-            }
+            o = normgate8<PRO>(v, zv, wv, s.nw32, k0, s.eps);
         }
         store_staged(st, col, k0, o, lane);
     }

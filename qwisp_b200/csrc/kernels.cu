@@ -1,5 +1,7 @@
 // kernels.cu -- the Seedless decode kernels for sm_100a and their launchers.
 #include "kernels.h"
+#include "mixer_math.cuh"
+#include "route.cuh"
 
 #include <atomic>
 #include <cstdio>
@@ -45,6 +47,12 @@ struct ProfScope {
     ~ProfScope() { if (on) cudaEventRecord(g_prof.back().b, st); }
 };
 void profile_start() { g_prof_on = true; }
+void count_launch() { COUNT_LAUNCH(); }
+void profile_launch(const char* tag, cudaStream_t st, const std::function<int()>& fn) {
+    ProfScope ps(tag, 0.0, st);
+    fn();
+    COUNT_LAUNCH();
+}
 // one line per kernel: "tag launches total_ms total_bytes"; stops profiling
 int profile_report(char* buf, size_t cap) {
     g_prof_on = false;
@@ -486,75 +494,6 @@ void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H
 // grid: E/8 + 1 CTAs of 256 threads (one warp per expert); the last CTA writes the normed rows
 // and the shared-expert gate logit.
 // ============================================================================================
-// One warp routes one row.  Restates swift/Sources/QwispCore/SeedlessFusedVerify.swift:180-214
-// including the ORDER of its 256-slot halving trees: lane l looks at slots l, l+32, .., l+224, so
-// the tree levels 128/64/32 are lane-local and the levels 16..1 are xor-shuffles whose results
-// are meaningful in lanes < s -- the same pairs (i, i+s) the reference combines.  Softmax in f32,
-// gates rounded to fp16, top-k by k rounds of arg-max on the raw logits (strict > keeps the
-// lower slot), fp16 sequential sum of the chosen gates, fp16 divide.
-// buf: 2*256 floats + 32 ints of shared memory owned by this warp.  Loops are kept rolled: this
-// code runs in one warp of one CTA, so a small instruction footprint matters more than ILP.
-// Order of the reference's selection tree (256 slots halved to 128, 64, ... 1, the lower slot of
-// each compared pair winning ties): larger logit first, then smaller bit-reversed slot number (the
-// last level compares slots 0 and 1, so bit 0 of the slot decides first).  A 24-bit key
-// (order-preserving fp16 bits, then 255 - bitreverse8(slot)) has the same order, so k hardware
-// warp-max reductions select the same experts in the same sequence.
-__device__ __noinline__ void route_row_warp(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, float* buf, int lane) {
-    float* lg = buf;
-    {   // one 16-byte load per lane covers the 256 slots; shared memory turns it into the slot = j*32+lane order
-        uint4 raw = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);      // -inf pairs
-        const bool vec = ((E & 7) == 0) && lane * 8 + 8 <= E;     // rows of E halves stay 16-byte aligned only then
-        if (vec) raw = __ldcg(reinterpret_cast<const uint4*>(lrow) + lane);
-        const __half* rh = reinterpret_cast<const __half*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) lg[lane * 8 + i] = (lane * 8 + i < E) ? h2f(rh[i]) : -INFINITY;
-        if (!vec && lane * 8 < E)
-            for (int i = 0; i < 8 && lane * 8 + i < E; ++i) lg[lane * 8 + i] = h2f(__ldcg(lrow + lane * 8 + i));
-    }
-    __syncwarp();
-    float v0[8];
-    unsigned key[8];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        v0[j] = lg[j * 32 + lane]; mx = fmaxf(mx, v0[j]);
-        unsigned hb = __half_as_ushort(f2h(v0[j]));                       // exact: the value came from fp16
-        if (hb == 0x8000u) hb = 0u;                                       // -0 compares equal to +0
-        hb = (hb & 0x8000u) ? (~hb & 0xffffu) : (hb | 0x8000u);
-        key[j] = (j * 32 + lane < E) ? ((hb << 8) | (255u - (__brev((unsigned)(j * 32 + lane)) >> 24))) : 0u;
-    }
-    mx = warp_max(mx);
-    float ex[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { int slot = j * 32 + lane; ex[j] = (slot < E) ? expf(v0[j] - mx) : 0.0f; }
-    float r0 = __fadd_rn(ex[0], ex[4]), r1 = __fadd_rn(ex[1], ex[5]), r2 = __fadd_rn(ex[2], ex[6]), r3 = __fadd_rn(ex[3], ex[7]);
-    r0 = __fadd_rn(r0, r2); r1 = __fadd_rn(r1, r3);
-    r0 = __fadd_rn(r0, r1);
-#pragma unroll
-    for (int s = 16; s >= 1; s >>= 1) r0 = __fadd_rn(r0, __shfl_xor_sync(0xffffffffu, r0, s));
-    const float Z = __shfl_sync(0xffffffffu, r0, 0);
-    int my_id = 0; float my_ex = 0.f;                                     // lane k ends up holding the k-th choice
-#pragma unroll 1
-    for (int k = 0; k < topk; ++k) {
-        unsigned best = key[0];
-#pragma unroll
-        for (int j = 1; j < 8; ++j) best = max(best, key[j]);
-        best = __reduce_max_sync(0xffffffffu, best);
-        const int slot = (int)(__brev(255u - (best & 0xffu)) >> 24), ol = slot & 31, oj = slot >> 5;
-        float e_sel = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) if (j == oj) { e_sel = ex[j]; if (lane == ol) key[j] = 0u; }
-        e_sel = __shfl_sync(0xffffffffu, e_sel, ol);
-        if (lane == k) { my_id = oj * 32 + ol; my_ex = e_sel; }
-    }
-    // gate of the k-th choice = fp16(exp / Z); the sum runs in fp16 in ascending k, then each is divided by it
-    const __half g = f2h(__fdiv_rn(my_ex, Z));
-    __half ss = f2h(0.0f);
-    for (int k = 0; k < topk; ++k) ss = hadd_rn(ss, __ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, (unsigned)__half_as_ushort(g), k)));
-    if (lane < topk) { inds_out[lane] = my_id; scores_out[lane] = hdiv_rn(g, ss); }
-    __syncwarp();
-}
-
 // MULTI: several rows per call (one warp per row in the norm); the one-row instantiation leaves that code
 // out, so it does not compete for registers with the router rows held across the wait
 // Q8: the router rows and the shared gate are 8-bit group-64 (the checkpoint's layout).  Lane l owns 8
@@ -1381,8 +1320,6 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
     pdl_wait();
     pdl_launch_dependents();
 
-    const float invScale = 0.08838834764831845f;             // 128^-0.5
-    const __half qs = f2h(invScale * invScale), ks = f2h(invScale);
     auto xval = [&](int idx, int ch) -> float {               // row idx of [hist(3) | rows of the segment]
         if (idx < CONV_K - 1) {
             const float* hsel = (ch == ch_q) ? hq : ((ch == ch_k) ? hkk : hvv);
@@ -1391,12 +1328,7 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
         return h2f(a.inproj[(size_t)(seg.row0 + idx - (CONV_K - 1)) * a.ld + ch]);
     };
     auto conv = [&](int tt, int ch, float4 w) -> float {
-        float acc = 0.f;
-        acc = __fadd_rn(acc, __fmul_rn(xval(tt + 0, ch), w.x));
-        acc = __fadd_rn(acc, __fmul_rn(xval(tt + 1, ch), w.y));
-        acc = __fadd_rn(acc, __fmul_rn(xval(tt + 2, ch), w.z));
-        acc = __fadd_rn(acc, __fmul_rn(xval(tt + 3, ch), w.w));
-        return h2f(f2h(__fmul_rn(acc, sigmoid_f(acc))));
+        return gdn_conv_silu(xval(tt + 0, ch), xval(tt + 1, ch), xval(tt + 2, ch), xval(tt + 3, ch), w);
     };
     for (int tt = 0; tt < seg.nrows; ++tt) {
         const int row = seg.row0 + tt;
@@ -1407,16 +1339,13 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
         if (tid == 0) {
             __half bh = a.inproj[(size_t)row * a.ld + convDim + a.Hv * GDN_DV + hv];
             __half ah = a.inproj[(size_t)row * a.ld + convDim + a.Hv * GDN_DV + a.Hv + hv];
-            gb_s[1] = h2f(sigmoid_h(bh));
-            float xa = h2f(ah) + dt_bias_h;
-            float sp = fmaxf(xa, 0.0f) + logf(1.0f + expf(-fabsf(xa)));
-            gb_s[0] = expf(-expf(A_log_h) * sp);
+            gdn_gate(bh, ah, A_log_h, dt_bias_h, gb_s[0], gb_s[1]);
         }
         __syncthreads();
-        float iq = __frsqrt_rn(__fadd_rn(__fdiv_rn(red_s[0] + red_s[1] + red_s[2] + red_s[3], 128.0f), a.eps));
-        float ik = __frsqrt_rn(__fadd_rn(__fdiv_rn(red_s[4] + red_s[5] + red_s[6] + red_s[7], 128.0f), a.eps));
-        q_s[tid] = h2f(hmul_rn(qs, f2h(__fmul_rn(qc, iq))));
-        k_s[tid] = h2f(hmul_rn(ks, f2h(__fmul_rn(kc, ik))));
+        float iq = gdn_head_inv(red_s[0], red_s[1], red_s[2], red_s[3], a.eps);
+        float ik = gdn_head_inv(red_s[4], red_s[5], red_s[6], red_s[7], a.eps);
+        q_s[tid] = gdn_scale_q(qc, iq);
+        k_s[tid] = gdn_scale_k(kc, ik);
         __syncthreads();
         const float g = gb_s[0], beta = gb_s[1];
         const float4 kq = *reinterpret_cast<const float4*>(k_s + lane * 4);
@@ -1424,13 +1353,7 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             float4 s = S[i];
-            s.x *= g; s.y *= g; s.z *= g; s.w *= g;
-            float kv = s.x * kq.x + s.y * kq.y + s.z * kq.z + s.w * kq.w;
-            kv = warp_sum(kv);
-            float delta = (v_s[warp * 4 + i] - kv) * beta;
-            s.x = fmaf(kq.x, delta, s.x); s.y = fmaf(kq.y, delta, s.y); s.z = fmaf(kq.z, delta, s.z); s.w = fmaf(kq.w, delta, s.w);
-            float o = s.x * qq.x + s.y * qq.y + s.z * qq.z + s.w * qq.w;
-            o = warp_sum(o);
+            const float o = gdn_row_step(s, g, kq, qq, v_s[warp * 4 + i], beta);
             S[i] = s;
             if (lane == 0) a.y[(size_t)row * (a.Hv * GDN_DV) + hv * GDN_DV + dvt * 16 + warp * 4 + i] = f2h(o);
         }
@@ -1534,8 +1457,6 @@ void launch_attn_prep(const AttnArgs& a, cudaStream_t st) {
     COUNT_LAUNCH();
 }
 
-constexpr int ATT_G = 8;     // query heads per kv head handled together (attn_heads / attn_kv_heads must equal it)
-
 // ---- one-kernel attention: (optional) q/k prep + split-KV decode + merge of the splits ----
 // norm + partial rotation of one 256-wide head held as 8 values per lane; returns the fp16 values
 __device__ __forceinline__ uint4 norm_rope_head(const __half* src, const __half* w, float eps, float theta, int pos, int lane) {
@@ -1570,42 +1491,6 @@ __device__ __forceinline__ uint4 norm_rope_head(const __half* src, const __half*
     }
     return o;
 }
-// cos / sin of the 32 rotation angles of one position, the same expressions norm_rope_head evaluates
-__device__ __forceinline__ void rope_table_entry(float theta, int pos, int i, float& cs, float& sn) {
-    const float lnb = logf(theta);
-    const float freq = expf(-2.0f * (float)i / (float)ROPE_D * lnb);
-    const float ang = (float)pos * freq;
-    sincosf(ang, &sn, &cs);
-}
-// norm_rope_head with the angles taken from a table (tab_cs / tab_sn [32]) instead of recomputed per lane
-__device__ __forceinline__ uint4 norm_rope_head_tab(const __half* src, const __half* w, float eps, const float* tab_cs, const float* tab_sn, int lane) {
-    uint4 v = reinterpret_cast<const uint4*>(src)[lane];
-    uint4 wv = reinterpret_cast<const uint4*>(w)[lane];
-    const __half* vh = reinterpret_cast<const __half*>(&v);
-    const __half* wh = reinterpret_cast<const __half*>(&wv);
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { float f = h2f(vh[i]); ss = fmaf(f, f, ss); }
-    ss = warp_sum(ss);
-    float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), eps));
-    float nv[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) nv[i] = h2f(hmul_rn(wh[i], f2h(__fmul_rn(h2f(vh[i]), inv))));
-    float other[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, nv[i], 4);
-    uint4 o; __half* oh = reinterpret_cast<__half*>(&o);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        int d = lane * 8 + i;
-        if (d >= ROPE_D) { oh[i] = f2h(nv[i]); continue; }
-        int ii = (d < 32) ? d : (d - 32);
-        const float cs = tab_cs[ii], sn = tab_sn[ii];
-        float x0 = (d < 32) ? nv[i] : other[i], x1 = (d < 32) ? other[i] : nv[i];
-        oh[i] = f2h((d < 32) ? (x0 * cs - x1 * sn) : (x0 * sn + x1 * cs));
-    }
-    return o;
-}
 // grid (nsplit, KV heads, M), 256 threads, dynamic shared memory 8*8*256 floats.
 // prep != 0 (every row is the only row of its stream in this launch): each CTA norms and rotates its
 // 8 query heads itself, and the CTA whose key range holds the row's own position also makes that
@@ -1627,10 +1512,9 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
     const int slot = a.segs[a.row_seg[m]].slot;
     const int pos_m = row_position(a, m);
     const int N = pos_m + 1;
-    const int chunk = 32 * ((N + 32 * a.nsplit - 1) / (32 * a.nsplit));
-    const int used = (N + chunk - 1) / chunk;
+    int chunk, used, p0, p1;
+    attn_split_range(N, a.nsplit, split, chunk, used, p0, p1);
     if (split >= used) { pdl_wait(); pdl_launch_dependents(); return; }
-    const int p0 = split * chunk, p1 = min(N, p0 + chunk);
     const bool own = prep && (pos_m >= p0) && (pos_m < p1);
     const __half* rowp = a.inproj + (size_t)m * a.ld;
     uint4 kcur = make_uint4(0, 0, 0, 0), vcur = make_uint4(0, 0, 0, 0);
@@ -1645,10 +1529,10 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
     pdl_launch_dependents();
     if (prep) {
         __syncthreads();                                      // the rotation table
-        uint4 qo = norm_rope_head_tab(rowp + (size_t)(kvh * ATT_G + warp) * 2 * ATT_D, a.q_norm, a.eps, s_cs, s_sn, lane);
+        uint4 qo = norm_rope_head_tab(reinterpret_cast<const uint4*>(rowp + (size_t)(kvh * ATT_G + warp) * 2 * ATT_D)[lane], a.q_norm, a.eps, s_cs, s_sn, lane);
         reinterpret_cast<uint4*>(sq[warp])[lane] = qo;
         if (own && warp == 1) {
-            uint4 ko = norm_rope_head_tab(rowp + a.NH * 2 * ATT_D + kvh * ATT_D, a.k_norm, a.eps, s_cs, s_sn, lane);
+            uint4 ko = norm_rope_head_tab(reinterpret_cast<const uint4*>(rowp + a.NH * 2 * ATT_D + kvh * ATT_D)[lane], a.k_norm, a.eps, s_cs, s_sn, lane);
             reinterpret_cast<uint4*>(sk)[lane] = ko;
             reinterpret_cast<uint4*>(kv_ptr(a, slot, pos_m, 0, kvh))[lane] = ko;
         }
@@ -1693,17 +1577,7 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
 #pragma unroll
         for (int i = 0; i < 8; ++i) { kf[i] = h2f(kh[i]); vf[i] = h2f(vh[i]); }
 #pragma unroll
-        for (int g = 0; g < ATT_G; ++g) {
-            float sc = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sc = fmaf(q[g][i], kf[i], sc);
-            sc = warp_sum(sc);
-            float nm = fmaxf(mx[g], sc);
-            float factor = __expf(mx[g] - nm), es = __expf(sc - nm);
-            mx[g] = nm; l[g] = l[g] * factor + es;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], factor, es * vf[i]);
-        }
+        for (int g = 0; g < ATT_G; ++g) attn_key_step(q[g], kf, vf, mx[g], l[g], acc[g]);
         kcur = knext; vcur = vnext;
     }
     // ---- merge the 8 warps: all heads at once through shared memory ----
@@ -1714,9 +1588,10 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
     __syncthreads();
 #pragma unroll
     for (int g = 0; g < ATT_G; ++g) {
-        float gm = -INFINITY;
+        float m8[8];
 #pragma unroll
-        for (int w = 0; w < 8; ++w) gm = fmaxf(gm, sm_m[w][g]);
+        for (int w = 0; w < 8; ++w) m8[w] = sm_m[w][g];
+        const float gm = attn_warps_max(m8);
         float f = (mx[g] == -INFINITY) ? 0.f : __expf(mx[g] - gm);
         float4 lo = make_float4(acc[g][0] * f, acc[g][1] * f, acc[g][2] * f, acc[g][3] * f);
         float4 hi = make_float4(acc[g][4] * f, acc[g][5] * f, acc[g][6] * f, acc[g][7] * f);
@@ -1736,10 +1611,10 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
         }
         if (d < ATT_G) {
             const int g = d;
-            float gm = -INFINITY;
-            for (int w = 0; w < 8; ++w) gm = fmaxf(gm, sm_m[w][g]);
-            float ls = 0.f;
-            for (int w = 0; w < 8; ++w) ls += (sm_m[w][g] == -INFINITY) ? 0.f : sm_l[w][g] * __expf(sm_m[w][g] - gm);
+            float m8[8], l8[8];
+            for (int w = 0; w < 8; ++w) { m8[w] = sm_m[w][g]; l8[w] = sm_l[w][g]; }
+            const float gm = attn_warps_max(m8);
+            const float ls = attn_warps_lsum(m8, l8, gm);
             float* pml = a.part_ml + (((size_t)m * a.NH + kvh * ATT_G + g) * a.nsplit + split) * 2;
             pml[0] = gm; pml[1] = ls;
         }
@@ -1760,35 +1635,9 @@ __global__ void __launch_bounds__(256) k_attn_fused(AttnArgs a, int prep, unsign
         const int g = warp, h = kvh * ATT_G + g;
         const float* po = a.part_o + ((size_t)m * a.NH + h) * a.nsplit * ATT_D;
         const float* pml = a.part_ml + ((size_t)m * a.NH + h) * a.nsplit * 2;
-        float msv[2], lsv[2], fv[2];                          // nsplit <= 64: two splits per lane
-        float gm = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            int sp = j * 32 + lane;
-            msv[j] = -INFINITY; lsv[j] = 0.f;
-            if (sp < used) { float2 ml = __ldcg(reinterpret_cast<const float2*>(pml) + sp); msv[j] = ml.x; lsv[j] = ml.y; }
-            gm = fmaxf(gm, msv[j]);
-        }
-        gm = warp_max(gm);
-        float tot = 0.f;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) { fv[j] = (msv[j] == -INFINITY) ? 0.f : __expf(msv[j] - gm); tot += lsv[j] * fv[j]; }
-        tot = warp_sum(tot);
-        float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int sp = 0; sp < used; ++sp) {
-            float f = __shfl_sync(0xffffffffu, (sp < 32) ? fv[0] : fv[1], sp & 31);
-            const float4* src = reinterpret_cast<const float4*>(po + (size_t)sp * ATT_D + lane * 8);
-            float4 x0 = __ldcg(src), x1 = __ldcg(src + 1);
-            o[0] = fmaf(x0.x, f, o[0]); o[1] = fmaf(x0.y, f, o[1]); o[2] = fmaf(x0.z, f, o[2]); o[3] = fmaf(x0.w, f, o[3]);
-            o[4] = fmaf(x1.x, f, o[4]); o[5] = fmaf(x1.y, f, o[5]); o[6] = fmaf(x1.z, f, o[6]); o[7] = fmaf(x1.w, f, o[7]);
-        }
-        const __half* gh = reinterpret_cast<const __half*>(&gvv);
-        uint4 outv; __half* oh = reinterpret_cast<__half*>(&outv);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            __half out = f2h(tot == 0.f ? o[i] : o[i] / tot);
-            oh[i] = hmul_rn(out, sigmoid_h(gh[i]));
-        }
+        const uint4 outv = attn_merge_splits(used, lane, gvv,
+            [&](int sp, float4& x0, float4& x1) { const float4* src = reinterpret_cast<const float4*>(po + (size_t)sp * ATT_D + lane * 8); x0 = __ldcg(src); x1 = __ldcg(src + 1); },
+            [&](int sp) { return __ldcg(reinterpret_cast<const float2*>(pml) + sp); });
         reinterpret_cast<uint4*>(a.gated + ((size_t)m * a.NH + h) * ATT_D)[lane] = outv;
     }
     if (threadIdx.x == 0) counters[m * a.KV + kvh] = 0u;

@@ -1,6 +1,7 @@
 // kernels.h -- argument blocks and host launchers of the Seedless B200 kernels.
 #pragma once
 #include "gemv.cuh"
+#include <functional>
 
 namespace sl {
 
@@ -106,6 +107,43 @@ struct StepEndArgs {
 };
 
 int sm_count();
+// ---- the one-kernel decode step (step_persistent.cu) ----
+struct PsGeom {
+    int G;                                  // CTAs (one per multiprocessor)
+    int H, I, E, topk, V;
+    int Hk, Hv, NH, KV;
+    int keyDim, valDim, convDim, gdn_in, attn_in, attn_out;
+    int S_h, S_i;                           // 256-wide slices of K = H, K = I
+    int gu_spp;                             // CTAs per expert slot in the gate/up phase
+    int rows_per_sm;                        // gdn state rows per CTA (multiple of 4)
+    int router_spr;                         // ring slots per router row
+};
+struct PLayer {                             // one layer's weights as the step kernel reads them (an array of these lives on the device)
+    int is_attn, type_index;
+    const __half *in_norm, *post_norm;
+    Q4R r_in, r_out;
+    const float *conv_w, *A_log, *dt_bias; const __half* gdn_norm; const float* gdn_norm32;
+    const __half *q_norm, *k_norm;
+    const __half *router, *shared_gate;     // fp16 forms only
+    Q4R r_gu, r_down, r_sh_gu, r_sh_down;
+};
+struct PStepArgs {
+    PsGeom geom;
+    const PLayer* layers; int n_layers;
+    const __half* embed; const __half* final_norm; Q4R lm_head;
+    float eps, theta;
+    StreamTable tab; const SegDesc* segs;
+    __half* kv_pool; int n_attn_layers, page_size, nsplit;
+    int *tok_in, *out_tok, *hist, *hist_pos; int hist_cap;
+    unsigned* step_seq;                     // sequence number of the next step (device word, >= 1)
+    // exchange lines (16 B each): per layer a block of x_stride lines, plus one block after the last layer
+    uint4* xbuf; size_t x_stride; int x_off_h, x_off_in, x_off_mix, x_off_hm, x_off_lg, x_off_hb, x_off_arg;
+    uint4* xatt; size_t xatt_stride;        // attention partials, one block per attention layer
+    unsigned* err; unsigned* abort_flag;
+};
+bool ps_plan(PsGeom& g, int n_sm);           // fills the derived fields; false if the step kernel cannot run this geometry here
+int launch_step_persistent(const PStepArgs& a, cudaStream_t st);   // cooperative launch; returns a cudaError_t
+
 void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pdl);
 // many-row GEMM on tcgen05 tensor cores with the accumulator in tensor memory (N % 128 == 0, K % 256 == 0); 0 or an error code
 int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, __half* y, int ldy, bool add_to_y, unsigned* err, cudaStream_t st);
@@ -136,6 +174,9 @@ void launch_step_end(const StepEndArgs& a, cudaStream_t st);
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st);
 void launch_wait_probe(unsigned* err, cudaStream_t st);   // test hook: a bounded wait that runs out sets bit 2 of *err
 int64_t kernel_launch_count();
+void count_launch();
+// run `fn` (one kernel launch) between the profiling events of `tag` when profiling is on, and count it
+void profile_launch(const char* tag, cudaStream_t st, const std::function<int()>& fn);
 void profile_start();
 int profile_report(char* buf, size_t cap);
 

@@ -82,6 +82,14 @@ class Engine:
     def inject_fault(self, on=True):
         lib().sl_inject_fault(self._h, 1 if on else 0)
 
+    def use_persistent(self, on=True):
+        """Select the one-kernel decode step (True, the default where available) or the kernel-per-phase
+        assembly for single-stream decode steps; returns whether the one-kernel step is available."""
+        return lib().sl_engine_use_persistent(self._h, 1 if on else 0) == 1
+
+    def persistent_active(self):
+        return lib().sl_engine_use_persistent(self._h, -1) == 1
+
     def debug_wait_timeout(self):
         """Test hook: enqueue a kernel whose bounded wait runs out (nothing faults); the next call fails."""
         self._check(lib().sl_debug_wait_timeout(self._h), "sl_debug_wait_timeout")
