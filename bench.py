@@ -11,7 +11,11 @@ excluded (swift/Sources/QwispCore/TellRuntime.swift:1267, 1449-1450).
             timed with CUDA events on the launching stream (inputs already resident in HBM)
   e2e    -- the same K steps through the step call a host runtime makes (host token in,
             host token out, a synchronisation every step), wall clock
-  roofline     -- the kernel with the largest share of the step, timed live with CUDA events
+  roofline     -- the dominant kernel, timed live with CUDA events inside the timed region.  With the
+                  one-kernel decode step (the default) that kernel IS the step: one launch per token,
+                  algorithmic bytes = the token's 1.7 GB, duration = the events around the K launches / K.
+                  With the kernel-per-phase assembly (SEEDLESS_PERSISTENT=0) it is the kernel with the
+                  largest share of a separate eager pass.
   cpu_baseline -- the CPU oracle on the host cores, on a bounded sample of the same workload
 
 `--impl reference` times the reference's path on the host cores instead (the CPU restatement of
@@ -52,6 +56,33 @@ def algorithmic_bytes_per_token(ctx_len):
     state = 30 * 32 * 128 * 128 * 4 * 2
     kv = 10 * 2 * 2 * 256 * 2 * ctx_len
     return weights + state + kv
+
+
+def batch_step_bytes_per_rank(streams_per_rank, world, ctx_len):
+    """Algorithmic bytes one rank moves in a 64-stream decode step: the replicated dense weights once, the
+    experts touched on this rank (EXPECTED distinct experts per layer for uniform routing of 64 x 8 picks over
+    256, divided among the ranks -- stated as an expectation, the routing of the run is not read back), the
+    rank's streams' GDN state (read + write) and KV."""
+    H, I, V, E = 2048, 512, 151936, 256
+    q = 0.5625
+    gdn = (8192 + 4096 + 64) * H * q + H * 4096 * q
+    att = (8192 + 512 + 512) * H * q + H * 4096 * q
+    dense = 30 * gdn + 10 * att + 40 * (3 * I * H * q + E * H * 2 + H * 2) + V * H * q
+    distinct = E * (1.0 - (1.0 - 1.0 / E) ** (BATCH_STREAMS * 8))
+    experts = 40 * (distinct / world) * 3 * I * H * q
+    state = streams_per_rank * 30 * 32 * 128 * 128 * 4 * 2
+    kv = streams_per_rank * 10 * 2 * 2 * 256 * 2 * ctx_len
+    return dense + experts + state + kv
+
+
+def measured_traffic(kernel):
+    """dram bytes per launch of `kernel` from the ncu capture summarised under profiles/ (a small JSON the
+    summary's author writes next to it); None when there is no capture of the current kernel."""
+    try:
+        t = json.load(open(os.path.join(ROOT, "profiles", "dram_traffic.json")))
+        return t.get(kernel, {}).get("dram_bytes_per_launch")
+    except (OSError, ValueError):
+        return None
 
 
 class ClockSampler:
@@ -97,7 +128,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_oracle_sample(max_seconds, prompt_tokens=2):
+def cpu_oracle_sample(max_seconds, prompt_tokens=2, min_steps=2, max_steps=16):
     """Time the CPU oracle on a bounded sample: the full-size model with experts generated on
     first use; a short prompt, then as many greedy decode steps as fit the budget.  The sample
     runs twice on the same tokens: the first pass generates the routed experts it touches, the
@@ -108,16 +139,20 @@ def cpu_oracle_sample(max_seconds, prompt_tokens=2):
     model = O.Model(cfg, 0, lazy_experts=True)
     build_s = time.time() - t0
     prompt = O.synth_tokens(0, "bench.prompt", prompt_tokens, cfg.vocab)
-    warm = model.stream(64)
+    warm = model.stream(prompt_tokens + 2 * max_steps + 8)
     t0 = time.time()
     first = int(warm.step(prompt)[-1])
-    per_tok = max((time.time() - t0) / prompt_tokens, 1e-3)
-    steps = int(max(2, min(16, (max_seconds / 2.2) / per_tok - prompt_tokens)))
-    toks, cur = [], first
-    for _ in range(steps):
+    prefill_s = time.time() - t0
+    blob = warm.state_save()                                  # the timed pass starts from the same context without a second prefill
+    t0 = time.time()
+    cur = int(warm.step([first])[0])
+    per_tok = max(time.time() - t0, 1e-3)
+    steps = int(max(min_steps, min(max_steps, (max_seconds / 2.0) / per_tok)))
+    toks = [cur]
+    for _ in range(steps - 1):
         cur = int(warm.step([cur])[0]); toks.append(cur)
-    timed = model.stream(64)
-    timed.step(prompt)
+    timed = model.stream(prompt_tokens + 2 * max_steps + 8)
+    assert timed.state_restore(blob)
     t0 = time.time()
     cur = first
     for k in range(steps):
@@ -126,18 +161,58 @@ def cpu_oracle_sample(max_seconds, prompt_tokens=2):
     dt = time.time() - t0
     return {"value": steps / dt, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
             "sample": f"full 40-layer model, {prompt_tokens}-token prompt then {steps} greedy decode steps (context {prompt_tokens}..{prompt_tokens + steps}), "
-                      f"OpenMP on all host cores; model build {build_s:.1f}s excluded",
+                      f"OpenMP on all host cores; model build {build_s:.1f}s and prefill {prefill_s:.1f}s excluded; the steps run twice on the same tokens "
+                      f"(the first pass generates the routed experts it touches), the second pass is timed",
+            "steps": steps, "seconds": dt}
+
+
+def cpu_oracle_batch_sample(n_streams, prompt_tokens, steps):
+    """The 64-stream batched decode on the CPU oracle, bounded: every stream gets a short seeded prompt, then
+    `steps` rounds in which each stream decodes one token (the oracle has no batched step; a round is the
+    streams one after another, each step using all host cores).  Returns aggregate tok/s of the rounds."""
+    from oracle import oracle as O
+    cfg = O.config()
+    t0 = time.time()
+    model = O.Model(cfg, 0, lazy_experts=True)
+    build_s = time.time() - t0
+    streams, last = [], []
+    for g in range(n_streams):
+        st = model.stream(prompt_tokens + steps + 8)
+        prompt = O.synth_tokens(0, f"bench.batch.prompt.{g}", prompt_tokens, cfg.vocab)
+        last.append(int(st.step(prompt)[-1]))
+        streams.append(st)
+    for i, st in enumerate(streams):                       # one untimed round: generates the experts the timed rounds touch first
+        last[i] = int(st.step([last[i]])[0])
+    t0 = time.time()
+    for _ in range(steps):
+        for i, st in enumerate(streams):
+            last[i] = int(st.step([last[i]])[0])
+    dt = time.time() - t0
+    return {"value": n_streams * steps / dt, "unit": "tok/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"full 40-layer model, {n_streams} streams with {prompt_tokens}-token prompts, {steps} timed rounds of one token per stream "
+                      f"(context {prompt_tokens + 1}..{prompt_tokens + 1 + steps}), OpenMP on all host cores; model build {build_s:.1f}s, prompts and one warm-up round excluded",
             "steps": steps, "seconds": dt}
 
 
 def run_reference(args, rank, world):
+    """The reference's path on the host cores (its CPU restatement: the reference itself is Swift + Metal).
+    N = 1: the batch-1 metric at the GPU arm's context (the 512-token prompt is prefilled on the CPU first).
+    N > 1: the 64-stream batched metric on a bounded sample.  Rank 0 alone runs; under torchrun the other ranks exit."""
     if rank != 0:
         return
-    cb = cpu_oracle_sample(max_seconds=float(os.environ.get("SEEDLESS_REF_SECONDS", "90")))
-    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
-            "steps": cb["steps"], "warmup": args.warmup, "ms_per_step": 1000.0 / cb["value"], "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference's kernels on the host cores (the reference is Swift + Metal)"},
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: this arm is the CPU baseline, it uses every core
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())
+    if world > 1 or args.gpus > 1:
+        cb = cpu_oracle_batch_sample(BATCH_STREAMS, prompt_tokens=int(os.environ.get("SEEDLESS_REF_BATCH_PROMPT", "4")), steps=max(1, min(args.steps, 2)))
+        metric, workload, scaling = "decode_tok_per_s_batch64_ep", WORKLOAD64, "strong"
+    else:
+        cb = cpu_oracle_sample(max_seconds=float(os.environ.get("SEEDLESS_REF_SECONDS", "60")), prompt_tokens=PROMPT_LEN,
+                               min_steps=max(2, min(args.steps, 8)), max_steps=max(2, min(args.steps, 16)))
+        metric, workload, scaling = METRIC, WORKLOAD, "weak"
+    line = {"impl": "reference", "metric": metric, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": cb["steps"], "warmup": args.warmup, "ms_per_step": 1000.0 / cb["value"] * (BATCH_STREAMS if metric.endswith("ep") else 1),
+            "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": workload, "note": "CPU restatement of the reference's kernels on the host cores (the reference is Swift + Metal); " + cb["sample"]},
             "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -169,21 +244,24 @@ def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
         uid = torch.from_numpy(Q.Engine.ep_unique_id() if rank == 0 else np.zeros(128, dtype=np.uint8)).cuda()
         dist.broadcast(uid, 0)
         eng.ep_init(rank, world, uid.cpu().numpy(), B)
-    streams, last = [], []
+    streams, last, plens = [], [], []
     for g in mine:
         n = 128 + (g * 37) % 129
         prompt = Q.ops.synth_tokens(0, f"bench.batch.prompt.{g}", n, cfg.vocab)
         st = eng.stream(seq)
         last.append(int(st.step_argmax(prompt)[-1]))
-        streams.append(st)
+        streams.append(st); plens.append(n)
+    first_tokens = list(last)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    warm_toks = []
     for _ in range(W):
         last = [int(v) for v in eng.batch_step_argmax(streams, last)]
+        warm_toks.append(list(last))
     n0 = eng.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -206,11 +284,31 @@ def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
     fault = eng.gpu_fault()
     for st in streams:
         st.close()
+    # The batched (expert-parallel when world > 1) token streams against plain single-stream decoding of the same
+    # prompts on this rank's engine (every rank holds all weights, and a single-stream step never uses the exchange):
+    # the first two streams of the rank, every warm-up and timed step.
+    identical = True
+    all_toks = np.asarray(warm_toks + [list(t) for t in toks])          # [W + K, B]
+    for j in range(min(2, B)):
+        g = mine[j]
+        solo = eng.stream(seq)
+        cur = int(solo.step_argmax(Q.ops.synth_tokens(0, f"bench.batch.prompt.{g}", plens[j], cfg.vocab))[-1])
+        identical = identical and (cur == first_tokens[j])
+        for k in range(all_toks.shape[0]):
+            cur = int(solo.step_argmax([cur])[0])
+            identical = identical and (cur == int(all_toks[k, j]))
+        solo.close()
+    if dist is not None:
+        t = torch.tensor([1 if identical else 0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        identical = bool(int(t[0]))
+    fault = fault or eng.gpu_fault()
     eng.close()
     if fault:
         raise SystemExit(f"engine fault during the batched run: {fault}")
     return {"tok_s": BATCH_STREAMS * K / (ms * 1e-3), "tok_s_wall": BATCH_STREAMS * K / wall, "ms_per_step": ms / K,
-            "launches_per_step": launches, "rows_per_rank": B, "tokens": np.stack(toks)}
+            "launches_per_step": launches, "rows_per_rank": B, "tokens": np.stack(toks), "tokens_identical_to_solo": identical,
+            "ctx": float(np.mean(plens)) + W + K / 2.0}
 
 
 def run_batch64_line(args, rank, local_rank, world):
@@ -229,7 +327,20 @@ def run_batch64_line(args, rank, local_rank, world):
     sampler.start()
     r = measure_batch64(Q, torch, dist, rank, world, args.layers, K, W)
     clocks = sampler.stop()
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline and args.layers == 40:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())          # torchrun exports 1; this leg is the CPU baseline
+        cb = cpu_oracle_batch_sample(BATCH_STREAMS, prompt_tokens=2, steps=1)
+        cpu = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if rank == 0:
+        rank_bytes = batch_step_bytes_per_rank(r["rows_per_rank"], world, r["ctx"]) * (args.layers / 40.0 if args.layers != 40 else 1.0)
+        rank_gbs = rank_bytes / (r["ms_per_step"] * 1e-3) / 1e9
         line = {"metric": "decode_tok_per_s_batch64_ep", "value": r["tok_s"], "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f16", "data": "synthetic",
@@ -240,7 +351,13 @@ def run_batch64_line(args, rank, local_rank, world):
                            "timing": "K host-driven batched steps between CUDA events on the launching stream, max over ranks"},
                 "clocks": clocks,
                 "e2e": {"value": r["tok_s_wall"], "unit": "tok/s", "h2d_bytes_per_step": 4 * r["rows_per_rank"], "d2h_bytes_per_step": 4 * r["rows_per_rank"]},
-                "gpu_launches": int(r["launches_per_step"] * K), "roofline": None, "cpu_baseline": None}
+                "gpu_launches": int(r["launches_per_step"] * K),
+                "ep_tokens_identical": r["tokens_identical_to_solo"],
+                "roofline": {"bound": "hbm", "kernel": "whole expert-parallel step (per rank)", "achieved": rank_gbs, "peak": peak_gbs, "unit": "GB/s",
+                             "frac": rank_gbs / peak_gbs, "traffic": None, "algorithmic_bytes_per_step_per_rank": rank_bytes,
+                             "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s",
+                             "note": "per-rank bytes: replicated dense weights + expected distinct experts / ranks + the rank's streams' state and KV"},
+                "cpu_baseline": cpu}
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     dist.destroy_process_group()
@@ -339,7 +456,20 @@ def main():
         pass
     peak_gbs = float(peaks.get("hbm_gbs", 6650.0))
     peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback 6650 GB/s"
-    if rank == 0:
+    ctx = PROMPT_LEN + W + K // 2
+    step_bytes = algorithmic_bytes_per_token(ctx) * (args.layers / 40.0 if args.layers != 40 else 1.0)
+    persistent = eng.persistent_active()
+    if rank == 0 and persistent:
+        # the step is ONE launch of the step kernel: its duration is the timed region / K, measured by the events above
+        us = dev_ms / K * 1e3
+        ach = step_bytes / (us * 1e-6) / 1e9
+        launches_per_step = 1
+        shares = {"k_step_persistent": {"launches_per_step": 1, "ms_per_step": dev_ms / K, "share": 1.0}}
+        roofline = {"bound": "hbm", "kernel": "k_step_persistent", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs,
+                    "traffic": measured_traffic("k_step_persistent") if args.layers == 40 else None, "peak_source": peak_src,
+                    "algorithmic_bytes_per_launch": step_bytes, "us_per_launch": us,
+                    "note": "one cooperative launch per token; duration = CUDA events around the K launches of the timed region / K"}
+    elif rank == 0:
         eng.use_graphs(False)
         cur2 = int(st.step_argmax([int(toks_dev[-1])])[0])
         n_before = eng.launch_count()
@@ -354,27 +484,18 @@ def main():
         shares = {k: {"launches_per_step": v[0] // nprof, "ms_per_step": v[1] / nprof, "share": v[1] / tot} for k, v in rep.items()}
         dom = max((k for k in rep if rep[k][2] > 0), key=lambda k: rep[k][1])
         n, ms, by = rep[dom]
-        # Average duration of one launch of the dominant kernel INSIDE the timed region: its share of
-        # the step (per-launch CUDA events of the eager pass; ncu's launch list gives the same shares)
-        # times the step time measured by the events around the timed region.  The eager per-launch
-        # figure itself (event pair around every launch, no graph) is kept beside it.
+        # kernel-per-phase assembly: the dominant kernel's average duration inside the timed region = its share of
+        # a step (per-launch CUDA events of an eager pass) times the step time measured by the events around the
+        # timed region; the eager per-launch figure is kept beside it
         per_step = shares[dom]["launches_per_step"]
         us_in_step = shares[dom]["share"] * (dev_ms / K) / per_step * 1e3
         ach = (by / n) / (us_in_step * 1e-6) / 1e9
-        # dram__bytes_read+write per launch from the ncu capture summarised in
-        # profiles/decode_step_kernels_4layer_ncu_full.md (same weight shapes; k_gemv = mix of the
-        # step's 30 GDN in/out projections and 10 attention q-k-v / o projections, the attention
-        # in-projection scaled from the GDN one by its rows)
-        ncu_traffic = {"k_gemv": (30 * 14.27e6 + 10 * 14.27e6 * 9216 / 12288 + 30 * 4.78e6 + 10 * 4.76e6) / 80,
-                       "k_expert_gateup": 10.64e6, "k_expert_down": 5.36e6, "k_expert_fused": 10.64e6 + 5.36e6, "k_moe_router": 1.12e6, "k_gdn_core": 2.32e6 + 2.1e6}
         roofline = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs,
-                    "traffic": ncu_traffic.get(dom) if args.layers == 40 else None, "peak_source": peak_src,
+                    "traffic": measured_traffic(dom) if args.layers == 40 else None, "peak_source": peak_src,
                     "algorithmic_bytes_per_launch": by / n, "us_per_launch": us_in_step, "us_per_launch_eager_events": ms / n * 1e3}
 
     tok_s = world * K / (dev_ms * 1e-3)
     e2e_tok_s = world * K / (e2e_ms * 1e-3)
-    ctx = PROMPT_LEN + W + K // 2
-    step_bytes = algorithmic_bytes_per_token(ctx) * (args.layers / 40.0 if args.layers != 40 else 1.0)
     step_gbs = step_bytes / (dev_ms / K * 1e-3) / 1e9
 
     cpu = None
@@ -388,8 +509,12 @@ def main():
         import torch as _t
         _t.cuda.empty_cache()
         b = measure_batch64(Q, torch, None, 0, 1, args.layers, min(K, 32), 3)
+        bb = batch_step_bytes_per_rank(BATCH_STREAMS, 1, b["ctx"])
+        bg = bb / (b["ms_per_step"] * 1e-3) / 1e9
         batch64 = {"metric": "decode_tok_per_s_batch64", "value": b["tok_s"], "e2e": b["tok_s_wall"], "ms_per_step": b["ms_per_step"],
-                   "steps": min(K, 32), "workload": WORKLOAD64, "launches_per_step": b["launches_per_step"]}
+                   "steps": min(K, 32), "workload": WORKLOAD64, "launches_per_step": b["launches_per_step"],
+                   "roofline": {"bound": "hbm", "achieved": bg, "peak": peak_gbs, "unit": "GB/s", "frac": bg / peak_gbs, "traffic": None,
+                                "algorithmic_bytes_per_step": bb, "note": "whole step; expert bytes are the expectation for uniform routing"}}
     if rank == 0:
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -401,6 +526,7 @@ def main():
                        "prompt_len": PROMPT_LEN, "context_during_timing": [PROMPT_LEN + W, PROMPT_LEN + W + K],
                        "step_algorithmic_bytes": step_bytes, "step_achieved_gbs": step_gbs,
                        "step_frac_of_measured_hbm": step_gbs / peak_gbs, "step_frac_of_nominal_8tbs": step_gbs / 8000.0,
+                       "assembly": "one-kernel decode step (cooperative launch, weight ring, flag-in-data exchange)" if persistent else "kernel-per-phase (CUDA graph + programmatic dependent launch)",
                        "device_vs_e2e_tokens_identical": identical, "kernel_shares": shares},
             "clocks": clocks,
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},

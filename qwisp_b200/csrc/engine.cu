@@ -85,6 +85,7 @@ struct sl_engine {
     std::vector<int> free_slots;
     // decode graphs keyed by rows (each segment one row)
     std::map<int, cudaGraphExec_t> graphs;
+    std::map<int, int> graph_kernels;   // kernels inside each captured step (so replays are counted too)
     std::map<int, int> eager_runs;
     bool use_graph = true;
     bool use_prefetch = false;      // L2 prefetch of the weights later kernels read (SEEDLESS_PREFETCH=1); slower now that
@@ -661,13 +662,17 @@ int32_t enqueue_decode_step(sl_engine* e, int rows) {
         if (e->eager_runs[key]++ == 0) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return SL_OK; }
         cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
         CU(e, cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+        const int64_t before = kernel_launch_count();
         enqueue_step(e, rows, rows, HEAD_ARGMAX, false);
+        e->graph_kernels[key] = (int)(kernel_launch_count() - before);
+        count_launches(-(int64_t)e->graph_kernels[key]);          // the capture itself launched nothing
         CU(e, cudaStreamEndCapture(e->stream, &graph));
         CU(e, cudaGraphInstantiate(&exec, graph, 0));
         cudaGraphDestroy(graph);
         it = e->graphs.emplace(key, exec).first;
     }
     CU(e, cudaGraphLaunch(it->second, e->stream));
+    count_launches(e->graph_kernels[key]);
     return SL_OK;
 }
 

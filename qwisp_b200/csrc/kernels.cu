@@ -48,6 +48,7 @@ struct ProfScope {
 };
 void profile_start() { g_prof_on = true; }
 void count_launch() { COUNT_LAUNCH(); }
+void count_launches(int64_t n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 void profile_launch(const char* tag, cudaStream_t st, const std::function<int()>& fn) {
     ProfScope ps(tag, 0.0, st);
     fn();

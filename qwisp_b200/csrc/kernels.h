@@ -175,6 +175,7 @@ void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H
 void launch_wait_probe(unsigned* err, cudaStream_t st);   // test hook: a bounded wait that runs out sets bit 2 of *err
 int64_t kernel_launch_count();
 void count_launch();
+void count_launches(int64_t n);
 // run `fn` (one kernel launch) between the profiling events of `tag` when profiling is on, and count it
 void profile_launch(const char* tag, cudaStream_t st, const std::function<int()>& fn);
 void profile_start();
