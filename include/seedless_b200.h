@@ -128,6 +128,10 @@ int32_t sl_engine_use_graphs(sl_engine* e, int32_t on);
  * other call.  Both produce the same tokens.  on = 0 / 1 selects; on < 0 only queries.  Returns 1 when the
  * one-kernel step is available (query: and selected), 0 otherwise. */
 int32_t sl_engine_use_persistent(sl_engine* e, int32_t on);
+/* Profiling of the one-kernel step: on = 1 arms a timeline (returns the number of CTAs); every following step
+ * overwrites it with nanosecond stamps of each CTA's phase boundaries, [CTA][layer + 1][24] uint32 relative to the
+ * CTA's start; on = 0 disarms it and, when out is given, copies the last step's stamps to the host. */
+int32_t sl_debug_step_timeline(sl_engine* e, int32_t on, uint32_t* out, uint64_t cap_words);
 /* Per-kernel timing with CUDA events on the launching stream, for eager launches only (the
  * reference's profiled forward splits its command buffer per stage for the same purpose,
  * SeedlessFusedVerify.swift:4352-4378).  The report has one line per kernel:

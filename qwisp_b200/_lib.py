@@ -66,6 +66,7 @@ SYMBOLS = {
     "sl_hybrid_chunk": (_I32, [_VP]),
     "sl_debug_wait_timeout": (_I32, [_VP]),
     "sl_engine_use_persistent": (_I32, [_VP, _I32]),
+    "sl_debug_step_timeline": (_I32, [_VP, _I32, _VP, _U64]),
     "sl_step_argmax": (_I32, [_VP, _VP, _I32, _VP]),
     "sl_chained_step_argmax": (_I32, [_VP, _I32, _I32, _VP]),
     "sl_chained_enqueue": (_I32, [_VP, _I32, _I32]),

@@ -94,6 +94,7 @@ struct sl_engine {
     // the one-kernel decode step (step_persistent.cu): used for single-stream decode steps when the geometry fits
     bool ps_ok = false, use_persistent = true;   // SEEDLESS_PERSISTENT=0 / sl_engine_use_persistent(e, 0): kernel-per-phase assembly
     PStepArgs ps{};
+    uint32_t* ps_timeline = nullptr;
     bool poisoned = false, inject = false;
     std::string fault;
 };
@@ -424,7 +425,9 @@ int32_t setup_persistent(sl_engine* e) {
     a.x_off_hb = off; off += (e->topk + 1) * e->I / 4;
     a.x_off_arg = off; off += g.G;
     a.x_stride = (size_t)((off + 7) & ~7);
-    const size_t xlines = a.x_stride * (host.size() + 1);
+    a.x_reps = 8;
+    a.x_rep_stride = a.x_stride * (host.size() + 1);
+    const size_t xlines = a.x_rep_stride * (size_t)a.x_reps;
     if ((rc = dalloc(e, &a.xbuf, xlines))) return rc;
     CU(e, cudaMemset(a.xbuf, 0, xlines * sizeof(uint4)));
     a.xatt_stride = (size_t)c.attn_heads * NSPLIT * 129;
@@ -928,6 +931,24 @@ int32_t sl_debug_wait_timeout(sl_engine* e) {
 int32_t sl_inject_fault(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->inject = on != 0; return SL_OK; }
 int64_t sl_engine_launch_count(sl_engine* e) { (void)e; return kernel_launch_count(); }
 int32_t sl_engine_use_graphs(sl_engine* e, int32_t on) { if (!e) return SL_ERR_INVALID; e->use_graph = on != 0; return SL_OK; }
+int32_t sl_debug_step_timeline(sl_engine* e, int32_t on, uint32_t* out, uint64_t cap_words) {
+    int32_t rc = guard(e); if (rc) return rc;
+    if (!e->ps_ok) return SL_ERR_NOT_FOUND;
+    const size_t words = (size_t)e->ps.geom.G * (e->ps.n_layers + 1) * 24;
+    if (on) {
+        if (!e->ps_timeline && (rc = dalloc(e, &e->ps_timeline, words))) return rc;
+        CU(e, cudaMemsetAsync(e->ps_timeline, 0, words * 4, e->stream));
+        e->ps.timeline = e->ps_timeline;
+        return (int32_t)e->ps.geom.G;
+    }
+    e->ps.timeline = nullptr;
+    if (out) {
+        if (!e->ps_timeline || cap_words < words) return SL_ERR_CAPACITY;
+        CU(e, cudaMemcpyAsync(out, e->ps_timeline, words * 4, cudaMemcpyDeviceToHost, e->stream));
+        return sync_check(e);
+    }
+    return SL_OK;
+}
 int32_t sl_engine_use_persistent(sl_engine* e, int32_t on) {
     if (!e) return SL_ERR_INVALID;
     if (on < 0) return e->ps_ok ? (e->use_persistent ? 1 : 0) : 0;          // query

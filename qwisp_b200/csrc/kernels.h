@@ -137,9 +137,11 @@ struct PStepArgs {
     int *tok_in, *out_tok, *hist, *hist_pos; int hist_cap;
     unsigned* step_seq;                     // sequence number of the next step (device word, >= 1)
     // exchange lines (16 B each): per layer a block of x_stride lines, plus one block after the last layer
+    int x_reps; size_t x_rep_stride;        // every exchange line exists in x_reps copies, x_rep_stride lines apart
     uint4* xbuf; size_t x_stride; int x_off_h, x_off_in, x_off_mix, x_off_hm, x_off_lg, x_off_hb, x_off_arg;
     uint4* xatt; size_t xatt_stride;        // attention partials, one block per attention layer
     unsigned* err; unsigned* abort_flag;
+    uint32_t* timeline;                     // profiling: [CTA][layer + 1][24] nanosecond stamps, or nullptr
 };
 bool ps_plan(PsGeom& g, int n_sm);           // fills the derived fields; false if the step kernel cannot run this geometry here
 int launch_step_persistent(const PStepArgs& a, cudaStream_t st);   // cooperative launch; returns a cudaError_t

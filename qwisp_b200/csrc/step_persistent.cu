@@ -38,7 +38,10 @@ constexpr int PS_THREADS = (PS_CW + 2) * 32;       // + static producer warp + r
 constexpr int PS_SLOT = 2304;                      // bytes per ring slot: 2048 B of nibbles (or raw data) + 256 B of scales
 constexpr int PS_NS = 80;                          // ring slots
 constexpr long long PS_TIMEOUT = 1ll << 28;        // cycles a single wait may take (~0.14 s) before the step is abandoned
-constexpr int PS_RED_UNITS = 64;                   // partial sums held at once: units of one phase on one SM
+constexpr int PS_RED_UNITS = 64;
+#ifndef PS_FAKE
+#define PS_FAKE 0
+#endif                   // partial sums held at once: units of one phase on one SM
 
 // ---- shared memory carve-up (bytes) ----
 constexpr int PS_OFF_RING = 0;
@@ -52,7 +55,7 @@ constexpr int PS_OFF_HRAW = PS_OFF_HMID + 4096;                // residual strea
 constexpr int PS_OFF_RED = PS_OFF_HRAW + 4096;                 // [units][16] partial sums
 constexpr int PS_OFF_ROUTE = PS_OFF_RED + PS_RED_UNITS * 64;   // routing scratch: 544 floats + inds + scores
 constexpr int PS_OFF_MISC = PS_OFF_ROUTE + 2304;               // part[16], flags, small per-phase arrays; 1536 B
-constexpr int PS_SMEM_BYTES = PS_OFF_MISC + 2560;
+constexpr int PS_SMEM_BYTES = PS_OFF_MISC + 3072;
 // the mixer phases use [PS_OFF_XS, PS_OFF_HRAW) = 20 KB as scratch (the stage and the MoE rows are dead then)
 constexpr int PS_MIX_BYTES = PS_OFF_HRAW - PS_OFF_XS;
 
@@ -70,16 +73,28 @@ struct PsMisc {                 // lives at PS_OFF_MISC
     float sm_m[8][8], sm_l[8][8];
     __align__(16) __half sk[ATT_D];   // attention: this position's key (rotated) and value
     __align__(16) __half sv[ATT_D];
+    __align__(16) PLayer layer[2];    // the consumer warps' copy of the current layer's table entry (and the next one's, loaded ahead)
 };
-static_assert(sizeof(PsMisc) <= 2560, "misc area");
+static_assert(sizeof(PsMisc) <= 3072, "misc area");
+static_assert(sizeof(PLayer) % 4 == 0, "copied word by word");
 
 // ---- the exchange protocol: 16-byte lines {d0, seq, d1, seq} ----
 __device__ __forceinline__ void ll_store(uint4* line, uint32_t d0, uint32_t d1, uint32_t seq) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(line), "r"(d0), "r"(seq), "r"(d1), "r"(seq) : "memory");
+    asm volatile("st.relaxed.gpu.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(line), "r"(d0), "r"(seq), "r"(d1), "r"(seq) : "memory");
 }
 // one half of a line: {d, seq} (values produced one at a time by different warps)
 __device__ __forceinline__ void ll_store_half(uint2* half_line, uint32_t d, uint32_t seq) {
-    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(half_line), "r"(d), "r"(seq) : "memory");
+    asm volatile("st.relaxed.gpu.global.v2.u32 [%0], {%1,%2};" ::"l"(half_line), "r"(d), "r"(seq) : "memory");
+}
+// The exchange lines exist in `reps` copies `stride` lines apart; a producer writes every copy, a consumer CTA
+// polls only copy (CTA index mod reps): a line polled by every CTA of the grid at once is served by its L2
+// slice one request after the other, and the producers' stores queue behind the polls.
+struct PsRep { size_t stride; int reps; };
+__device__ __forceinline__ void ll_store_rep(uint4* line0, const PsRep& rp, uint32_t d0, uint32_t d1, uint32_t seq) {
+    for (int i = 0; i < rp.reps; ++i) ll_store(line0 + (size_t)i * rp.stride, d0, d1, seq);
+}
+__device__ __forceinline__ void ll_store_half_rep(uint2* half0, const PsRep& rp, uint32_t d, uint32_t seq) {
+    for (int i = 0; i < rp.reps; ++i) ll_store_half(half0 + (size_t)i * rp.stride * 2, d, seq);
 }
 struct PsWait { volatile int* s_abort; unsigned* g_abort; unsigned* err; };
 __device__ __forceinline__ void ps_give_up(const PsWait& w, unsigned code) {
@@ -92,8 +107,9 @@ __device__ __forceinline__ bool ll_load(const uint4* line, uint32_t seq, uint32_
     uint32_t a, f0, b, f1;
     long long t0 = 0;
     for (int it = 0;; ++it) {
-        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(f0), "=r"(b), "=r"(f1) : "l"(line) : "memory");
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(f0), "=r"(b), "=r"(f1) : "l"(line) : "memory");
         if (f0 == seq && f1 == seq) { d0 = a; d1 = b; return true; }
+        __nanosleep(40);
         if ((it & 15) == 15) {
             if (*w.s_abort) break;
             if (t0 == 0) t0 = clock64();
@@ -104,12 +120,45 @@ __device__ __forceinline__ bool ll_load(const uint4* line, uint32_t seq, uint32_
     d0 = 0; d1 = 0;
     return false;
 }
+// N lines at once: all loads are issued before any flag is looked at, so the N round trips overlap; lines
+// whose flags are not there yet are asked for again together.  d receives 2 words per line.
+template <int N>
+__device__ __forceinline__ bool ll_load_n(const uint4* const (&line)[N], uint32_t seq, uint32_t (&d)[2 * N], const PsWait& w) {
+    long long t0 = 0;
+    for (int it = 0;; ++it) {
+        uint32_t f0[N], f1[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+            asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d[2 * i]), "=r"(f0[i]), "=r"(d[2 * i + 1]), "=r"(f1[i]) : "l"(line[i]) : "memory");
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < N; ++i) ok = ok && (f0[i] == seq) && (f1[i] == seq);
+        if (ok) return true;
+        __nanosleep(40);
+        if ((it & 15) == 15) {
+            if (*w.s_abort) break;
+            if (t0 == 0) t0 = clock64();
+            else if (clock64() - t0 > PS_TIMEOUT) { ps_give_up(w, 8u); break; }
+            if ((it & 255) == 255 && *(volatile unsigned*)w.g_abort) { *w.s_abort = 1; break; }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2 * N; ++i) d[i] = 0;
+    return false;
+}
 // 8 consecutive halves (two lines) as a uint4
 __device__ __forceinline__ uint4 ll_load8(const uint4* lines, int first_half, uint32_t seq, const PsWait& w) {
-    uint4 v;
-    ll_load(lines + (first_half >> 2), seq, v.x, v.y, w);
-    ll_load(lines + (first_half >> 2) + 1, seq, v.z, v.w, w);
-    return v;
+    const uint4* const ln[2] = {lines + (first_half >> 2), lines + (first_half >> 2) + 1};
+    uint32_t d[4];
+    ll_load_n<2>(ln, seq, d, w);
+    return make_uint4(d[0], d[1], d[2], d[3]);
+}
+// two runs of 8 consecutive halves, polled together
+__device__ __forceinline__ void ll_load8x2(const uint4* lines_a, int first_a, const uint4* lines_b, int first_b, uint32_t seq, const PsWait& w, uint4& va, uint4& vb) {
+    const uint4* const ln[4] = {lines_a + (first_a >> 2), lines_a + (first_a >> 2) + 1, lines_b + (first_b >> 2), lines_b + (first_b >> 2) + 1};
+    uint32_t d[8];
+    ll_load_n<4>(ln, seq, d, w);
+    va = make_uint4(d[0], d[1], d[2], d[3]); vb = make_uint4(d[4], d[5], d[6], d[7]);
 }
 __device__ __forceinline__ __half ll_load_half(const uint4* lines, int idx, uint32_t seq, const PsWait& w) {
     uint32_t d0, d1;
@@ -133,6 +182,14 @@ struct PsRing {
     unsigned char* slots; uint64_t* full; uint64_t* empty;
     __device__ __forceinline__ unsigned char* slot(uint32_t pos) const { return slots + (size_t)(pos % PS_NS) * PS_SLOT; }
 };
+// try_wait that lets the hardware park the warp (up to `ns` nanoseconds) instead of spinning: a spinning warp
+// takes issue slots from the warps of its scheduler that have work (the routing warp, the producers)
+__device__ __forceinline__ bool mbar_try_wait_park(uint64_t* b, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 // consumer: wait until the copy into position `pos` has landed
 __device__ __forceinline__ bool ring_wait(const PsRing& r, uint32_t pos, const PsWait& w) {
     uint64_t* b = r.full + (pos % PS_NS);
@@ -140,7 +197,7 @@ __device__ __forceinline__ bool ring_wait(const PsRing& r, uint32_t pos, const P
     if (mbar_try_wait(b, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        for (int i = 0; i < 32; ++i) if (mbar_try_wait(b, parity)) return true;
+        if (mbar_try_wait_park(b, parity, 20000u)) return true;
         if (*w.s_abort) return false;
         if (clock64() - t0 > PS_TIMEOUT) { ps_give_up(w, 16u); return false; }
     }
@@ -162,7 +219,7 @@ __device__ __forceinline__ void ring_issue(const PsRing& r, uint32_t base, int n
         for (int it = 0;; ++it) {
             if (!done && (use == 0 || mbar_test_wait(r.empty + sl, (use - 1) & 1))) {
                 const void* s0; const void* s1; uint32_t b0, b1;
-                desc(i, s0, b0, s1, b1);
+                desc(PS_FAKE ? 0 : i, s0, b0, s1, b1);
                 unsigned char* dst = r.slots + (size_t)sl * PS_SLOT;
                 mbar_expect_tx(r.full + sl, b0 + b1);
                 bulk_g2s(dst, s0, b0, r.full + sl);
@@ -170,14 +227,19 @@ __device__ __forceinline__ void ring_issue(const PsRing& r, uint32_t base, int n
                 done = true;
             }
             if (__all_sync(0xffffffffu, done)) break;
+            __nanosleep(60);
             if ((it & 7) == 7) {
-                __nanosleep(40);
                 if (*w.s_abort) return;
                 if (t0 == 0) t0 = clock64();
                 else if (clock64() - t0 > PS_TIMEOUT) { ps_give_up(w, 32u); return; }
             }
         }
     }
+}
+__device__ __forceinline__ uint32_t ps_now() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return (uint32_t)t;
 }
 __device__ __forceinline__ void cbar() { asm volatile("bar.sync 1, %0;" ::"n"(PS_CT) : "memory"); }
 
@@ -240,7 +302,8 @@ struct PsSm {
 };
 
 // RMSNorm prologue from 8-value registers: v holds this lane's values of chunk `warp` (warps < K/256)
-__device__ __forceinline__ void ps_stage_rmsnorm(const PsSm& sm, uint4 v, const __half* nw, float eps, int K, int warp, int lane, __half* plain_out) {
+// and wv the norm weights of the same 8 positions (fetched by the caller BEFORE it polls for v)
+__device__ __forceinline__ void ps_stage_rmsnorm(const PsSm& sm, uint4 v, uint4 wv, float eps, int K, int warp, int lane, __half* plain_out) {
     const int chunks = K >> 8;
     const bool active = warp < chunks;
     if (active) {
@@ -253,7 +316,6 @@ __device__ __forceinline__ void ps_stage_rmsnorm(const PsSm& sm, uint4 v, const 
         float tot = 0.f;
         for (int c = 0; c < chunks; ++c) tot += sm.misc->part[c];
         const float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)K), eps));
-        const uint4 wv = *reinterpret_cast<const uint4*>(nw + k0);
         const uint4 o = rms_apply8(v, wv, inv);
         if (plain_out) *reinterpret_cast<uint4*>(plain_out + k0) = o;
         store_staged(sm.st, 0, k0, o, lane);
@@ -289,6 +351,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
     __syncthreads();
     const PsGeom g = a.geom;
     const PsWait w{&sm.misc->abort, a.abort_flag, a.err};
+    const PsRep rp{a.x_rep_stride, a.x_reps};
     const uint32_t seq = *(volatile unsigned*)a.step_seq;
     const int slot_id = a.segs[0].slot;
 
@@ -296,10 +359,55 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
     if (warp == PS_CW) {
         uint32_t base = 0;
         const int side = a.tab.parity[slot_id];
+        const int kv_len0 = a.tab.kv_len[slot_id];
         for (int L = 0; L < a.n_layers; ++L) {
             const PLayer& P = a.layers[L];
             const PsCounts k = ps_counts(g, P.is_attn != 0, c);
             int t0, t1;
+            {   // Pull into L2, well ahead of their use, the small per-layer constants (norm weights, conv taps, conv
+                // history, decay parameters) and, for an attention layer, the cached keys / values of this CTA's split:
+                // each would otherwise cost a full DRAM round trip on the critical path.  One range per lane.
+                const void* pp = nullptr; uint32_t pb = 0;
+                auto rng = [&](int idx, const void* p0_, size_t bytes) {
+                    if (lane != idx) return;
+                    const uintptr_t lo = (uintptr_t)p0_ & ~(uintptr_t)15, hi = ((uintptr_t)p0_ + bytes + 15) & ~(uintptr_t)15;
+                    pp = (const void*)lo; pb = (uint32_t)(hi - lo);
+                };
+                rng(0, P.in_norm, (size_t)g.H * 2); rng(1, P.post_norm, (size_t)g.H * 2);
+                if (!P.is_attn) {
+                    const int total = g.Hv * GDN_DV, r0 = c * g.rows_per_sm, r1 = min(total, r0 + g.rows_per_sm);
+                    if (r1 > r0) {
+                        const int rep_ = g.Hv / g.Hk, hk0 = (r0 / GDN_DV) / rep_, hk1 = ((r1 - 1) / GDN_DV) / rep_;
+                        const __half* hist_in = a.tab.conv_hist + (size_t)slot_id * a.tab.hist_stride_stream + (size_t)side * a.tab.hist_stride_side +
+                                                (size_t)P.type_index * a.tab.hist_stride_layer;
+                        rng(2, P.gdn_norm, 256); rng(3, P.A_log, (size_t)g.Hv * 4); rng(4, P.dt_bias, (size_t)g.Hv * 4);
+                        rng(5, P.conv_w + (size_t)(hk0 * GDN_DK) * 4, 2048); rng(6, P.conv_w + (size_t)(g.keyDim + hk0 * GDN_DK) * 4, 2048);
+                        rng(7, P.conv_w + (size_t)(hk1 * GDN_DK) * 4, 2048); rng(8, P.conv_w + (size_t)(g.keyDim + hk1 * GDN_DK) * 4, 2048);
+                        rng(9, P.conv_w + (size_t)(2 * g.keyDim + r0) * 4, (size_t)(r1 - r0) * 16);
+                        for (int j = 0; j < 3; ++j) {
+                            rng(10 + 5 * j, hist_in + (size_t)j * g.convDim + hk0 * GDN_DK, 256); rng(11 + 5 * j, hist_in + (size_t)j * g.convDim + g.keyDim + hk0 * GDN_DK, 256);
+                            rng(12 + 5 * j, hist_in + (size_t)j * g.convDim + hk1 * GDN_DK, 256); rng(13 + 5 * j, hist_in + (size_t)j * g.convDim + g.keyDim + hk1 * GDN_DK, 256);
+                            rng(14 + 5 * j, hist_in + (size_t)j * g.convDim + 2 * g.keyDim + r0, (size_t)(r1 - r0) * 2);
+                        }
+                    }
+                } else {
+                    rng(2, P.q_norm, ATT_D * 2); rng(3, P.k_norm, ATT_D * 2);
+                    const int N = kv_len0 + 1;
+                    int chunk, used, p0, p1;
+                    attn_split_range(N, a.nsplit, 0, chunk, used, p0, p1);
+                    if (c < g.KV * used) {
+                        const int kvh = c / used, split = c - kvh * used;
+                        attn_split_range(N, a.nsplit, split, chunk, used, p0, p1);
+                        const size_t page_elems = (size_t)a.n_attn_layers * 2 * g.KV * a.page_size * ATT_D;
+                        for (int p = p0 + lane; p < p1 && p < kv_len0; p += 32) {
+                            const int page = a.tab.page_table[(size_t)slot_id * a.tab.max_pages + p / a.page_size];
+                            for (int which = 0; which < 2; ++which)
+                                prefetch_l2_bulk(a.kv_pool + (size_t)page * page_elems + ((((size_t)P.type_index * 2 + which) * g.KV + kvh) * a.page_size + (p % a.page_size)) * ATT_D, ATT_D * 2);
+                        }
+                    }
+                }
+                if (pb) prefetch_l2_bulk(pp, pb);
+            }
             ps_range((P.is_attn ? g.attn_in : g.gdn_in) / 16, g.G, c, t0, t1);
             {   // in-projection units: contiguous in the fragment-major layout
                 const uint4* wr = P.r_in.wr + (size_t)t0 * g.S_h * 128; const uint4* sr = P.r_in.sr + (size_t)t0 * g.S_h * 16;
@@ -405,27 +513,55 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
     const int kv_len0 = a.tab.kv_len[slot_id];
     const int side = a.tab.parity[slot_id];
     uint32_t base = 0;                                       // ring position of the current phase's first piece
+    if (tid < 32) rope_table_entry(a.theta, kv_len0, tid, sm.misc->cs[tid], sm.misc->sn[tid]);   // every attention layer rotates by the same position
     int tok = a.tok_in[0];
     if (tok < 0 || tok >= g.V) tok = 0;
 
+    // optional timeline (profiling): nanosecond stamps of this CTA's phase boundaries, [CTA][layer + 1][24]
+    uint32_t* tl_cta = a.timeline ? a.timeline + (size_t)c * (a.n_layers + 1) * 24 : nullptr;
+    const uint32_t t_start = ps_now();
+#define PS_MARK(L_, i_) do { if (tl_cta && tid == 0) tl_cta[(L_) * 24 + (i_)] = ps_now() - t_start; } while (0)
+    {   // layer 0's table entry; every later entry is copied in during the layer before it
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(a.layers);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.misc->layer[0]);
+        for (int i = tid; i < (int)(sizeof(PLayer) / 4); i += PS_CT) dst[i] = src[i];
+        cbar();
+    }
     for (int L = 0; L < a.n_layers; ++L) {
-        const PLayer& P = a.layers[L];
+        const PLayer& P = sm.misc->layer[L & 1];
         const bool is_attn = P.is_attn != 0;
         const PsCounts k = ps_counts(g, is_attn, c);
-        uint4* X = a.xbuf + (size_t)L * a.x_stride;          // this layer's exchange lines
+        if (L + 1 < a.n_layers && warp == PS_CW - 2) {       // visible to all after the barriers that follow in this layer
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(a.layers + L + 1);
+            uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.misc->layer[(L + 1) & 1]);
+            for (int i = lane; i < (int)(sizeof(PLayer) / 4); i += 32) dst[i] = src[i];
+        }
+        PS_MARK(L, 0);
+        if (tl_cta && tid == 0 && L == 2) {       // profiling only: round-trip time of a polled line (8 dependent loads), and of a store followed by a load of it
+            uint32_t a0 = 0, f0, b0, f1;
+            const uint4* ln = a.xbuf + (size_t)(c % a.x_reps) * a.x_rep_stride;
+            const uint32_t t0 = ps_now();
+            for (int i = 0; i < 8; ++i)
+                asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(f0), "=r"(b0), "=r"(f1) : "l"(ln + (a0 & 1)) : "memory");
+            tl_cta[L * 24 + 17] = ps_now() - t0 + (a0 & 1);
+        }
+        uint4* Xw = a.xbuf + (size_t)L * a.x_stride;                                  // this layer's exchange lines, copy 0 (stores go to every copy)
+        const uint4* X = Xw + (size_t)(c % a.x_reps) * a.x_rep_stride;                // the copy this CTA reads
         uint4* Xnext = a.xbuf + (size_t)(L + 1) * a.x_stride;
         // ---------------------------------------------------------------- in-projection
         {
             const int chunks = g.S_h;
-            uint4 v = make_uint4(0, 0, 0, 0);
+            uint4 v = make_uint4(0, 0, 0, 0), nwv = make_uint4(0, 0, 0, 0);
             if (warp < chunks) {
                 const int k0 = (warp << 8) + lane * 8;
+                nwv = *reinterpret_cast<const uint4*>(P.in_norm + k0);
                 if (L == 0) v = __ldg(reinterpret_cast<const uint4*>(a.embed + (size_t)tok * g.H + k0));
                 else v = ll_load8(X + a.x_off_h, k0, seq, w);
                 *reinterpret_cast<uint4*>(sm.hraw + k0) = v;
             }
-            ps_stage_rmsnorm(sm, v, P.in_norm, a.eps, g.H, warp, lane, nullptr);
+            ps_stage_rmsnorm(sm, v, nwv, a.eps, g.H, warp, lane, nullptr);
             cbar();
+            PS_MARK(L, 1);
             int t0, t1; ps_range((is_attn ? g.attn_in : g.gdn_in) / 16, g.G, c, t0, t1);
             XRegs xr;
             load_xregs(xr, sm.st, warp & (g.S_h - 1), r, t, 1);
@@ -433,6 +569,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                 ps_unit(sm.ring, base + u, w, xr, sm.red + u * 16, lane);
             }
             cbar();
+            PS_MARK(L, 2);
             const int n_out = (t1 - t0) * 16;
             for (int i0 = 0; i0 < n_out; i0 += PS_CT) {
                 const int i = i0 + tid;
@@ -440,10 +577,11 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                 if (i < n_out) val = f2h(ps_tile_sum(sm.red, i >> 4, g.S_h, i & 15));
                 const uint32_t me = __half_as_ushort(val);
                 const uint32_t h1 = __shfl_down_sync(0xffffffffu, me, 1), h2 = __shfl_down_sync(0xffffffffu, me, 2), h3 = __shfl_down_sync(0xffffffffu, me, 3);
-                if (i < n_out && (i & 3) == 0) ll_store(X + a.x_off_in + ((t0 * 16 + i) >> 2), me | (h1 << 16), h2 | (h3 << 16), seq);
+                if (i < n_out && (i & 3) == 0) ll_store_rep(Xw + a.x_off_in + ((t0 * 16 + i) >> 2), rp, me | (h1 << 16), h2 | (h3 << 16), seq);
             }
             base += k.n_in;
         }
+        PS_MARK(L, 3);
         // ---------------------------------------------------------------- mixer core
         if (!is_attn) {
             // --- gated delta net: this CTA owns state rows [r0, r1) (whole groups of 4, inside at most two value heads)
@@ -522,7 +660,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                         o[i] = f2h(gdn_row_step(S[i], gg, kq, qq, sm.misc->v_s[4 * q + i], beta));
                         *reinterpret_cast<float4*>(S_out + (size_t)(row0 + i) * GDN_DK + lane * 4) = S[i];
                     }
-                    if (lane == 0) ll_store(X + a.x_off_mix + (row0 >> 2), pack_h2(o[0], o[1]), pack_h2(o[2], o[3]), seq);
+                    if (lane == 0) ll_store_rep(Xw + a.x_off_mix + (row0 >> 2), rp, pack_h2(o[0], o[1]), pack_h2(o[2], o[3]), seq);
                 }
             }
             base += k.n_state;
@@ -546,8 +684,6 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                 const int kvh = wi / used, split = wi - kvh * used;
                 attn_split_range(N, a.nsplit, split, chunk, used, p0, p1);
                 const bool own = pos >= p0 && pos < p1;
-                if (tid < 32) rope_table_entry(a.theta, pos, tid, sm.misc->cs[tid], sm.misc->sn[tid]);
-                cbar();
                 if (warp < ATT_G) {
                     const uint4 v = ll_load8(XI, (kvh * ATT_G + warp) * 2 * ATT_D + lane * 8, seq, w);
                     reinterpret_cast<uint4*>(sq + warp * ATT_D)[lane] = norm_rope_head_tab(v, P.q_norm, a.eps, sm.misc->cs, sm.misc->sn, lane);
@@ -641,19 +777,20 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     const uint4 outv = attn_merge_splits(used, lane, gvv,
                         [&](int sp, float4& x0, float4& x1) {
                             uint32_t d[8];
-                            const uint4* ln = src + (size_t)sp * 129 + lane * 4;
-#pragma unroll
-                            for (int x = 0; x < 4; ++x) ll_load(ln + x, seq, d[2 * x], d[2 * x + 1], w);
+                            const uint4* l0 = src + (size_t)sp * 129 + lane * 4;
+                            const uint4* const ln[4] = {l0, l0 + 1, l0 + 2, l0 + 3};
+                            ll_load_n<4>(ln, seq, d, w);
                             x0 = make_float4(__uint_as_float(d[0]), __uint_as_float(d[1]), __uint_as_float(d[2]), __uint_as_float(d[3]));
                             x1 = make_float4(__uint_as_float(d[4]), __uint_as_float(d[5]), __uint_as_float(d[6]), __uint_as_float(d[7])); },
                         [&](int sp) { uint32_t d0, d1; ll_load(src + (size_t)sp * 129 + 128, seq, d0, d1, w); return make_float2(__uint_as_float(d0), __uint_as_float(d1)); });
-                    uint4* dst = X + a.x_off_mix + ((hd * ATT_D + lane * 8) >> 2);
-                    ll_store(dst, outv.x, outv.y, seq);
-                    ll_store(dst + 1, outv.z, outv.w, seq);
+                    uint4* dst = Xw + a.x_off_mix + ((hd * ATT_D + lane * 8) >> 2);
+                    ll_store_rep(dst, rp, outv.x, outv.y, seq);
+                    ll_store_rep(dst + 1, rp, outv.z, outv.w, seq);
                 }
             }
             cbar();
         }
+        PS_MARK(L, 4);
         // ---------------------------------------------------------------- out-projection (+ residual)
         {
             int t0, t1; ps_range(g.H / 16, g.G, c, t0, t1);
@@ -661,16 +798,18 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
             if (t1 > t0) {
                 for (int ch = warp; ch < S_o; ch += PS_CW) {
                     const int k0 = (ch << 8) + lane * 8;
-                    const uint4 v = ll_load8(X + a.x_off_mix, k0, seq, w);
-                    uint4 o = v;
-                    if (!is_attn) {
-                        const uint4 zv = ll_load8(X + a.x_off_in, g.convDim + k0, seq, w);
+                    uint4 v, o;
+                    if (is_attn) { v = ll_load8(X + a.x_off_mix, k0, seq, w); o = v; }
+                    else {
                         const uint4 wv = *reinterpret_cast<const uint4*>(P.gdn_norm + (k0 & 127));
+                        uint4 zv;
+                        ll_load8x2(X + a.x_off_mix, k0, X + a.x_off_in, g.convDim + k0, seq, w, v, zv);
                         o = P.gdn_norm32 ? normgate8<PRO_NORMGATE32>(v, zv, wv, P.gdn_norm32, k0, a.eps) : normgate8<PRO_NORMGATE>(v, zv, wv, nullptr, k0, a.eps);
                     }
                     store_staged(sm.st, 0, k0, o, lane);
                 }
                 cbar();
+                PS_MARK(L, 5);
                 XRegs xr;
                 load_xregs(xr, sm.st, warp & (S_o - 1), r, t, 1);
                 for (int u = warp; u < k.n_out; u += PS_CW) {
@@ -684,22 +823,24 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     if (i < n_out) val = hadd_rn(sm.hraw[t0 * 16 + i], f2h(ps_tile_sum(sm.red, i >> 4, S_o, i & 15)));
                     const uint32_t me = __half_as_ushort(val);
                     const uint32_t h1 = __shfl_down_sync(0xffffffffu, me, 1), h2 = __shfl_down_sync(0xffffffffu, me, 2), h3 = __shfl_down_sync(0xffffffffu, me, 3);
-                    if (i < n_out && (i & 3) == 0) ll_store(X + a.x_off_hm + ((t0 * 16 + i) >> 2), me | (h1 << 16), h2 | (h3 << 16), seq);
+                    if (i < n_out && (i & 3) == 0) ll_store_rep(Xw + a.x_off_hm + ((t0 * 16 + i) >> 2), rp, me | (h1 << 16), h2 | (h3 << 16), seq);
                 }
             }
             base += k.n_out;
         }
+        PS_MARK(L, 6);
         // ---------------------------------------------------------------- post-attention norm, router logits, shared gate logit
         {
-            uint4 v = make_uint4(0, 0, 0, 0);
+            uint4 v = make_uint4(0, 0, 0, 0), nwv = make_uint4(0, 0, 0, 0);
             if (warp < g.S_h) {
                 const int k0 = (warp << 8) + lane * 8;
+                nwv = *reinterpret_cast<const uint4*>(P.post_norm + k0);
                 v = ll_load8(X + a.x_off_hm, k0, seq, w);
                 *reinterpret_cast<uint4*>(sm.hmid + k0) = v;
             }
-            cbar();                                                   // the out-projection's readers of the stage are done
-            ps_stage_rmsnorm(sm, v, P.post_norm, a.eps, g.H, warp, lane, sm.pplain);
+            ps_stage_rmsnorm(sm, v, nwv, a.eps, g.H, warp, lane, sm.pplain);
             cbar();
+            PS_MARK(L, 7);
             const int spr = g.router_spr, njobs = k.n_router / spr;
             for (int jl = 0; jl < njobs; ++jl) {
                 if (warp != ((8 + jl) & 15)) continue;
@@ -721,31 +862,38 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     ring_release(sm.ring, pz, lane);
                 }
                 const float d = warp_sum(acc);
+                if (tl_cta && lane == 0 && jl == 0) tl_cta[L * 24 + 16] = ps_now() - t_start;
                 if (lane == 0) {
                     const uint32_t bits = (uint32_t)__half_as_ushort(f2h(d));
-                    if (j == g.E) ll_store(X + a.x_off_lg + (j >> 1), bits, 0u, seq);      // the shared-gate logit has its line to itself (E is even)
-                    else ll_store_half(reinterpret_cast<uint2*>(X + a.x_off_lg) + j, bits, seq);
+                    if (j == g.E) ll_store_rep(Xw + a.x_off_lg + (j >> 1), rp, bits, 0u, seq);      // the shared-gate logit has its line to itself (E is even)
+                    else ll_store_half_rep(reinterpret_cast<uint2*>(Xw + a.x_off_lg) + j, rp, bits, seq);
                 }
             }
             base += k.n_router;
         }
+        PS_MARK(L, 8);
         // ---------------------------------------------------------------- routing, gate/up of this CTA's expert slot
         {
             const bool in_moe = (k.gu_slot >= 0 && k.n_gu > 0) || k.n_down_s > 0;
             if (in_moe && warp == PS_CW - 1) {
                 // every CTA routes the row itself from the logits (deterministic, so all agree)
                 __half* lrow = reinterpret_cast<__half*>(sm.rbuf + 256);          // E <= 256 halves behind the 256 floats the routing itself uses
-                for (int e0 = lane * 4; e0 < g.E; e0 += 128) {
-                    uint32_t d0, d1, d2, d3;
-                    const uint4* ln = X + a.x_off_lg + (e0 >> 1);
-                    ll_load(ln, seq, d0, d1, w); ll_load(ln + 1, seq, d2, d3, w);
-                    lrow[e0] = __ushort_as_half((unsigned short)d0); lrow[e0 + 1] = __ushort_as_half((unsigned short)d1);
-                    lrow[e0 + 2] = __ushort_as_half((unsigned short)d2); lrow[e0 + 3] = __ushort_as_half((unsigned short)d3);
+                {   // lane l takes logits 8l .. 8l+7 (four lines), polled together
+                    const int e0 = lane * 8;
+                    if (e0 < g.E) {
+                        const uint4* base_l = X + a.x_off_lg + (e0 >> 1);
+                        const uint4* const ln[4] = {base_l, base_l + 1, base_l + 2, base_l + 3};
+                        uint32_t d[8];
+                        ll_load_n<4>(ln, seq, d, w);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) lrow[e0 + i] = __ushort_as_half((unsigned short)d[i]);
+                    }
                 }
                 __syncwarp();
+                if (tl_cta && lane == 0) tl_cta[L * 24 + 15] = ps_now() - t_start;
                 route_row_smem(lrow, g.E, g.topk, sm.misc->inds, sm.misc->scores, sm.rbuf, lane);
                 __syncwarp();
-                if (lane == 0) { __threadfence_block(); *(volatile int*)&sm.misc->route_layer = L + 1; }
+                if (lane == 0) { __threadfence_block(); *(volatile int*)&sm.misc->route_layer = L + 1; if (tl_cta) tl_cta[L * 24 + 9] = ps_now() - t_start; }
             }
             if (k.gu_slot >= 0 && k.n_gu > 0) {
                 int x0, x1; ps_range(g.I / 8, g.gu_spp, c % g.gu_spp, x0, x1);
@@ -755,6 +903,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     ps_unit(sm.ring, base + u, w, xr, sm.red + u * 16, lane);
                 }
                 cbar();
+                PS_MARK(L, 10);
                 const int n_out = (x1 - x0) * 8;                            // SwiGLU outputs of this CTA
                 for (int i0 = 0; i0 < n_out; i0 += PS_CT) {
                     const int i = i0 + tid;
@@ -765,11 +914,12 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     }
                     const uint32_t me = __half_as_ushort(val);
                     const uint32_t h1 = __shfl_down_sync(0xffffffffu, me, 1), h2 = __shfl_down_sync(0xffffffffu, me, 2), h3 = __shfl_down_sync(0xffffffffu, me, 3);
-                    if (i < n_out && (i & 3) == 0) ll_store(X + a.x_off_hb + ((k.gu_slot * g.I + x0 * 8 + i) >> 2), me | (h1 << 16), h2 | (h3 << 16), seq);
+                    if (i < n_out && (i & 3) == 0) ll_store_rep(Xw + a.x_off_hb + ((k.gu_slot * g.I + x0 * 8 + i) >> 2), rp, me | (h1 << 16), h2 | (h3 << 16), seq);
                 }
             }
             base += k.n_gu;
         }
+        PS_MARK(L, 11);
         // ---------------------------------------------------------------- down projections of this CTA's output tiles + combine
         {
             int t0, t1; ps_range(g.H / 16, g.G, c, t0, t1);
@@ -787,6 +937,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     store_staged(ss, 0, k0, v, lane);
                 }
                 cbar();
+                PS_MARK(L, 12);
                 const int nunits = ntl * nsl * g.S_i;
                 for (int u = warp; u < nunits; u += PS_CW) {
                     const int tl = u / (nsl * g.S_i), q = u - tl * nsl * g.S_i, kk = q / g.S_i, s = q - kk * g.S_i;
@@ -797,6 +948,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     ps_unit(sm.ring, pz, w, xr, sm.red + u * 16, lane);
                 }
                 cbar();
+                PS_MARK(L, 13);
                 // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit) * shared
                 // (:474-484), + residual (SeedlessMetalForward.swift:1024-1028); each slot's value is rounded to fp16 first
                 const int n_out = ntl * 16;
@@ -814,20 +966,27 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     }
                     const uint32_t me = __half_as_ushort(val);
                     const uint32_t h1 = __shfl_down_sync(0xffffffffu, me, 1), h2 = __shfl_down_sync(0xffffffffu, me, 2), h3 = __shfl_down_sync(0xffffffffu, me, 3);
-                    if (i < n_out && (i & 3) == 0) ll_store(Xnext + a.x_off_h + ((t0 * 16 + i) >> 2), me | (h1 << 16), h2 | (h3 << 16), seq);
+                    if (i < n_out && (i & 3) == 0) ll_store_rep(Xnext + a.x_off_h + ((t0 * 16 + i) >> 2), rp, me | (h1 << 16), h2 | (h3 << 16), seq);
                 }
             }
             base += k.n_down_r + k.n_down_s;
             cbar();
+            PS_MARK(L, 14);
         }
     }
     // ======================================================================= final norm, lm_head, argmax
     {
-        uint4* X = a.xbuf + (size_t)a.n_layers * a.x_stride;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (warp < g.S_h) v = ll_load8(X + a.x_off_h, (warp << 8) + lane * 8, seq, w);
-        ps_stage_rmsnorm(sm, v, a.final_norm, a.eps, g.H, warp, lane, nullptr);
+        uint4* Xw = a.xbuf + (size_t)a.n_layers * a.x_stride;
+        const uint4* X = Xw + (size_t)(c % a.x_reps) * a.x_rep_stride;
+        uint4 v = make_uint4(0, 0, 0, 0), nwv = make_uint4(0, 0, 0, 0);
+        if (warp < g.S_h) {
+            nwv = *reinterpret_cast<const uint4*>(a.final_norm + (warp << 8) + lane * 8);
+            v = ll_load8(X + a.x_off_h, (warp << 8) + lane * 8, seq, w);
+        }
+        PS_MARK(a.n_layers, 0);
+        ps_stage_rmsnorm(sm, v, nwv, a.eps, g.H, warp, lane, nullptr);
         cbar();
+        PS_MARK(a.n_layers, 1);
         int t0, t1; ps_range(g.V / 16, g.G, c, t0, t1);
         const int ntl = t1 - t0, S = g.S_h, full = ntl / 16, rem = ntl - full * 16;
         float best[2] = {-INFINITY, -INFINITY}; int besti[2] = {0x7fffffff, 0x7fffffff};
@@ -865,6 +1024,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
         }
         if (lane == 0) { sm.misc->red16[warp] = bv; sm.misc->redi16[warp] = bi; }
         cbar();
+        PS_MARK(a.n_layers, 2);
         if (warp == 0) {
             bv = (lane < PS_CW) ? sm.misc->red16[lane] : -INFINITY; bi = (lane < PS_CW) ? sm.misc->redi16[lane] : 0x7fffffff;
 #pragma unroll
@@ -872,7 +1032,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                 const float ov = __shfl_xor_sync(0xffffffffu, bv, off); const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
                 if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
             }
-            if (lane == 0) ll_store(X + a.x_off_arg + c, __float_as_uint(bv), (uint32_t)bi, seq);
+            if (lane == 0) ll_store(Xw + a.x_off_arg + c, __float_as_uint(bv), (uint32_t)bi, seq);      // read by CTA 0 alone: copy 0 only
             if (c == 0) {
                 bv = -INFINITY; bi = 0x7fffffff;
                 for (int p = lane; p < g.G; p += 32) {
@@ -895,6 +1055,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                     a.tab.kv_len[slot_id] = kv_len0 + 1;
                     a.tab.parity[slot_id] = side ^ 1;
                     *a.step_seq = seq + 1u;
+                    if (tl_cta) tl_cta[a.n_layers * 24 + 3] = ps_now() - t_start;
                 }
             }
         }

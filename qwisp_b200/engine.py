@@ -87,6 +87,17 @@ class Engine:
         assembly for single-stream decode steps; returns whether the one-kernel step is available."""
         return lib().sl_engine_use_persistent(self._h, 1 if on else 0) == 1
 
+    def step_timeline(self, run):
+        """Profile one or more one-kernel steps: arms the timeline, calls run(), returns the last step's stamps as
+        uint32 [CTAs, layers + 1, 24] (nanoseconds since each CTA's start; 0 = not reached)."""
+        G = lib().sl_debug_step_timeline(self._h, 1, None, 0)
+        if G <= 0:
+            raise SeedlessError(G, "sl_debug_step_timeline")
+        run()
+        out = np.zeros((G, self.cfg.n_layers + 1, 24), dtype=np.uint32)
+        self._check(lib().sl_debug_step_timeline(self._h, 0, _ptr(out), out.size), "sl_debug_step_timeline")
+        return out
+
     def persistent_active(self):
         return lib().sl_engine_use_persistent(self._h, -1) == 1
 
