@@ -123,10 +123,11 @@ int32_t sl_debug_wait_timeout(sl_engine* e);
 int64_t sl_engine_launch_count(sl_engine* e);
 /* Replay decode steps as CUDA graphs (default on) or launch every kernel eagerly. */
 int32_t sl_engine_use_graphs(sl_engine* e, int32_t on);
-/* Single-stream decode steps (sl_step_argmax with one row, chained steps) run as ONE kernel launch per token
- * when the geometry and the device allow it (the default), or as the kernel-per-phase assembly that serves every
- * other call.  Both produce the same tokens.  on = 0 / 1 selects; on < 0 only queries.  Returns 1 when the
- * one-kernel step is available (query: and selected), 0 otherwise. */
+/* Single-stream decode steps (sl_step_argmax with one row, chained steps) run as the kernel-per-phase assembly
+ * that serves every other call (the default: it is the faster one on B200 as measured), or as ONE cooperative
+ * kernel launch per token when the geometry and the device allow it.  Both produce the same tokens and leave the
+ * same caches.  on = 0 / 1 selects; on < 0 only queries.  Returns 1 when the one-kernel step is available
+ * (query: and selected), 0 otherwise.  The environment variable SEEDLESS_PERSISTENT=1 selects it at creation. */
 int32_t sl_engine_use_persistent(sl_engine* e, int32_t on);
 /* Profiling of the one-kernel step: on = 1 arms a timeline (returns the number of CTAs); every following step
  * overwrites it with nanosecond stamps of each CTA's phase boundaries, [CTA][layer + 1][24] uint32 relative to the

@@ -92,7 +92,9 @@ struct sl_engine {
                                     // every kernel starts its own weight copies ahead of the launch wait
     bool use_pdl = true;            // programmatic dependent launch between the kernels of a step (SEEDLESS_PDL=0 turns it off)
     // the one-kernel decode step (step_persistent.cu): used for single-stream decode steps when the geometry fits
-    bool ps_ok = false, use_persistent = true;   // SEEDLESS_PERSISTENT=0 / sl_engine_use_persistent(e, 0): kernel-per-phase assembly
+    // Off by default: measured on B200 it is the slower of the two assemblies (its six all-to-all activation exchanges
+    // per layer cost more than the kernel boundaries they replace); SEEDLESS_PERSISTENT=1 / sl_engine_use_persistent(e, 1) selects it
+    bool ps_ok = false, use_persistent = false;
     PStepArgs ps{};
     uint32_t* ps_timeline = nullptr;
     bool poisoned = false, inject = false;

@@ -20,7 +20,9 @@ namespace sl {
 // SMEM: lrow points to shared memory (plain loads); otherwise to global memory written by other CTAs of a
 // running kernel or by an earlier kernel (L1-bypassing loads).
 template <bool SMEM>
-__device__ __noinline__ void route_row_impl(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, float* buf, int lane) {
+// early_flag (shared memory, may be null): set to early_value as soon as inds_out is complete, before the gates.
+__device__ __noinline__ void route_row_impl(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, float* buf, int lane,
+                                            volatile int* early_flag = nullptr, int early_value = 0) {
     float* lg = buf;
     {   // one 16-byte load per lane covers the 256 slots; shared memory turns it into the slot = j*32+lane order
         uint4 raw = make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);      // -inf pairs
@@ -44,6 +46,24 @@ __device__ __noinline__ void route_row_impl(const __half* lrow, int E, int topk,
         hb = (hb & 0x8000u) ? (~hb & 0xffffu) : (hb | 0x8000u);
         key[j] = (j * 32 + lane < E) ? ((hb << 8) | (255u - (__brev((unsigned)(j * 32 + lane)) >> 24))) : 0u;
     }
+    // Selection first: it needs only the keys, and the chosen experts are what the weight fetch is waiting for.
+    int my_id = 0;                                                         // lane k ends up holding the k-th choice
+#pragma unroll 1
+    for (int k = 0; k < topk; ++k) {
+        unsigned best = key[0];
+#pragma unroll
+        for (int j = 1; j < 8; ++j) best = max(best, key[j]);
+        best = __reduce_max_sync(0xffffffffu, best);
+        const int slot = (int)(__brev(255u - (best & 0xffu)) >> 24), ol = slot & 31, oj = slot >> 5;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (j == oj && lane == ol) key[j] = 0u;
+        if (lane == k) my_id = slot;
+    }
+    if (lane < topk) inds_out[lane] = my_id;
+    if (early_flag) {                                                      // publish the choices before the gate arithmetic
+        __syncwarp();
+        if (lane == 0) { __threadfence_block(); *early_flag = early_value; }
+    }
     mx = warp_max(mx);
     float ex[8];
 #pragma unroll
@@ -54,33 +74,30 @@ __device__ __noinline__ void route_row_impl(const __half* lrow, int E, int topk,
 #pragma unroll
     for (int s = 16; s >= 1; s >>= 1) r0 = __fadd_rn(r0, __shfl_xor_sync(0xffffffffu, r0, s));
     const float Z = __shfl_sync(0xffffffffu, r0, 0);
-    int my_id = 0; float my_ex = 0.f;                                     // lane k ends up holding the k-th choice
+    float my_ex = 0.f;                                                     // exp of the lane's own choice, fetched from the lane that holds it
 #pragma unroll 1
     for (int k = 0; k < topk; ++k) {
-        unsigned best = key[0];
-#pragma unroll
-        for (int j = 1; j < 8; ++j) best = max(best, key[j]);
-        best = __reduce_max_sync(0xffffffffu, best);
-        const int slot = (int)(__brev(255u - (best & 0xffu)) >> 24), ol = slot & 31, oj = slot >> 5;
+        const int id = __shfl_sync(0xffffffffu, my_id, k), ol = id & 31, oj = id >> 5;
         float e_sel = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) if (j == oj) { e_sel = ex[j]; if (lane == ol) key[j] = 0u; }
+        for (int j = 0; j < 8; ++j) if (j == oj) e_sel = ex[j];
         e_sel = __shfl_sync(0xffffffffu, e_sel, ol);
-        if (lane == k) { my_id = oj * 32 + ol; my_ex = e_sel; }
+        if (lane == k) my_ex = e_sel;
     }
     // gate of the k-th choice = fp16(exp / Z); the sum runs in fp16 in ascending k, then each is divided by it
     const __half g = f2h(__fdiv_rn(my_ex, Z));
     __half ss = f2h(0.0f);
     for (int k = 0; k < topk; ++k) ss = hadd_rn(ss, __ushort_as_half((unsigned short)__shfl_sync(0xffffffffu, (unsigned)__half_as_ushort(g), k)));
-    if (lane < topk) { inds_out[lane] = my_id; scores_out[lane] = hdiv_rn(g, ss); }
+    if (lane < topk) scores_out[lane] = hdiv_rn(g, ss);
     __syncwarp();
 }
 
 __device__ __forceinline__ void route_row_warp(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, float* buf, int lane) {
     route_row_impl<false>(lrow, E, topk, inds_out, scores_out, buf, lane);
 }
-__device__ __forceinline__ void route_row_smem(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, float* buf, int lane) {
-    route_row_impl<true>(lrow, E, topk, inds_out, scores_out, buf, lane);
+__device__ __forceinline__ void route_row_smem(const __half* lrow, int E, int topk, int* inds_out, __half* scores_out, float* buf, int lane,
+                                               volatile int* early_flag = nullptr, int early_value = 0) {
+    route_row_impl<true>(lrow, E, topk, inds_out, scores_out, buf, lane, early_flag, early_value);
 }
 
 }  // namespace sl

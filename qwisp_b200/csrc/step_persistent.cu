@@ -41,7 +41,8 @@ constexpr long long PS_TIMEOUT = 1ll << 28;        // cycles a single wait may t
 constexpr int PS_RED_UNITS = 64;
 #ifndef PS_FAKE
 #define PS_FAKE 0
-#endif                   // partial sums held at once: units of one phase on one SM
+#endif
+                   // partial sums held at once: units of one phase on one SM
 
 // ---- shared memory carve-up (bytes) ----
 constexpr int PS_OFF_RING = 0;
@@ -102,39 +103,32 @@ __device__ __forceinline__ void ps_give_up(const PsWait& w, unsigned code) {
     atomicOr(w.g_abort, 1u);
     atomicOr(w.err, code);
 }
-// poll a line until both flags carry this step's sequence number; false once the step is abandoned
-__device__ __forceinline__ bool ll_load(const uint4* line, uint32_t seq, uint32_t& d0, uint32_t& d1, const PsWait& w) {
-    uint32_t a, f0, b, f1;
-    long long t0 = 0;
-    for (int it = 0;; ++it) {
-        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(f0), "=r"(b), "=r"(f1) : "l"(line) : "memory");
-        if (f0 == seq && f1 == seq) { d0 = a; d1 = b; return true; }
-        __nanosleep(40);
-        if ((it & 15) == 15) {
-            if (*w.s_abort) break;
-            if (t0 == 0) t0 = clock64();
-            else if (clock64() - t0 > PS_TIMEOUT) { ps_give_up(w, 8u); break; }
-            if ((it & 255) == 255 && *(volatile unsigned*)w.g_abort) { *w.s_abort = 1; break; }
-        }
-    }
-    d0 = 0; d1 = 0;
-    return false;
+// A plain (relaxed, gpu scope) load of a line that another multiprocessor wrote a moment ago can be served for
+// microseconds from a stale copy near the reader (measured: median 4.6 us from the store to a successful plain
+// poll, 1.2 us with the read below).  So: one plain attempt for all N lines -- enough when the data has been
+// there for a while -- and for every line whose flags are not in yet, a 16-byte compare-and-swap that can never
+// match, which reads the line where it lives in L2 and writes nothing.
+__device__ __forceinline__ void ll_read_home(const uint4* line, uint32_t& d0, uint32_t& f0, uint32_t& d1, uint32_t& f1) {
+    unsigned long long lo, hi;
+    asm volatile("{\n\t.reg .b128 c, n, q;\n\tmov.b128 c, {%2, %2};\n\tmov.b128 n, {%2, %2};\n\tatom.global.relaxed.gpu.cas.b128 q, [%3], c, n;\n\tmov.b128 {%0, %1}, q;\n\t}"
+                 : "=l"(lo), "=l"(hi) : "l"(0xFFFFFFFFFFFFFFFFull), "l"(line) : "memory");
+    d0 = (uint32_t)lo; f0 = (uint32_t)(lo >> 32); d1 = (uint32_t)hi; f1 = (uint32_t)(hi >> 32);
 }
-// N lines at once: all loads are issued before any flag is looked at, so the N round trips overlap; lines
-// whose flags are not there yet are asked for again together.  d receives 2 words per line.
 template <int N>
 __device__ __forceinline__ bool ll_load_n(const uint4* const (&line)[N], uint32_t seq, uint32_t (&d)[2 * N], const PsWait& w) {
+    uint32_t f0[N], f1[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+        asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d[2 * i]), "=r"(f0[i]), "=r"(d[2 * i + 1]), "=r"(f1[i]) : "l"(line[i]) : "memory");
     long long t0 = 0;
     for (int it = 0;; ++it) {
-        uint32_t f0[N], f1[N];
-#pragma unroll
-        for (int i = 0; i < N; ++i)
-            asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d[2 * i]), "=r"(f0[i]), "=r"(d[2 * i + 1]), "=r"(f1[i]) : "l"(line[i]) : "memory");
         bool ok = true;
 #pragma unroll
         for (int i = 0; i < N; ++i) ok = ok && (f0[i] == seq) && (f1[i] == seq);
         if (ok) return true;
-        __nanosleep(40);
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+            if (f0[i] != seq || f1[i] != seq) ll_read_home(line[i], d[2 * i], f0[i], d[2 * i + 1], f1[i]);
         if ((it & 15) == 15) {
             if (*w.s_abort) break;
             if (t0 == 0) t0 = clock64();
@@ -145,6 +139,14 @@ __device__ __forceinline__ bool ll_load_n(const uint4* const (&line)[N], uint32_
 #pragma unroll
     for (int i = 0; i < 2 * N; ++i) d[i] = 0;
     return false;
+}
+// one line
+__device__ __forceinline__ bool ll_load(const uint4* line, uint32_t seq, uint32_t& d0, uint32_t& d1, const PsWait& w) {
+    const uint4* const ln[1] = {line};
+    uint32_t d[2];
+    const bool ok = ll_load_n<1>(ln, seq, d, w);
+    d0 = d[0]; d1 = d[1];
+    return ok;
 }
 // 8 consecutive halves (two lines) as a uint4
 __device__ __forceinline__ uint4 ll_load8(const uint4* lines, int first_half, uint32_t seq, const PsWait& w) {
@@ -519,7 +521,7 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
 
     // optional timeline (profiling): nanosecond stamps of this CTA's phase boundaries, [CTA][layer + 1][24]
     uint32_t* tl_cta = a.timeline ? a.timeline + (size_t)c * (a.n_layers + 1) * 24 : nullptr;
-    const uint32_t t_start = ps_now();
+    const uint32_t t_start = 0;        // stamps are absolute (low 32 bits of the global nanosecond timer): comparable across CTAs
 #define PS_MARK(L_, i_) do { if (tl_cta && tid == 0) tl_cta[(L_) * 24 + (i_)] = ps_now() - t_start; } while (0)
     {   // layer 0's table entry; every later entry is copied in during the layer before it
         const uint32_t* src = reinterpret_cast<const uint32_t*>(a.layers);
@@ -614,15 +616,6 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                             hist_out[ch] = h1; hist_out[(size_t)g.convDim + ch] = h2; hist_out[(size_t)2 * g.convDim + ch] = x;
                         }
                     }
-                    const float ss = warp_sum(qc * qc);
-                    if (lane == 0) sm.misc->red16[warp] = ss;
-                    cbar();
-                    if (need) {
-                        const int w0 = (tid >> 7) * 4;
-                        const float inv = gdn_head_inv(sm.misc->red16[w0], sm.misc->red16[w0 + 1], sm.misc->red16[w0 + 2], sm.misc->red16[w0 + 3], a.eps);
-                        if (isk) k_s[j * 128 + cl] = gdn_scale_k(qc, inv);
-                        else q_s[j * 128 + cl] = gdn_scale_q(qc, inv);
-                    }
                     // v channels of this CTA's rows, decay / beta of its value heads
                     if (tid < r1 - r0) {
                         const int ch = 2 * g.keyDim + r0 + tid;
@@ -637,6 +630,15 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                         const __half bh = ll_load_half(XI, g.convDim + g.valDim + hv, seq, w);
                         const __half ah = ll_load_half(XI, g.convDim + g.valDim + g.Hv + hv, seq, w);
                         gdn_gate(bh, ah, P.A_log[hv], P.dt_bias[hv], sm.misc->gb[tid - 64][0], sm.misc->gb[tid - 64][1]);
+                    }
+                    const float ss = warp_sum(qc * qc);
+                    if (lane == 0) sm.misc->red16[warp] = ss;
+                    cbar();
+                    if (need) {
+                        const int w0 = (tid >> 7) * 4;
+                        const float inv = gdn_head_inv(sm.misc->red16[w0], sm.misc->red16[w0 + 1], sm.misc->red16[w0 + 2], sm.misc->red16[w0 + 3], a.eps);
+                        if (isk) k_s[j * 128 + cl] = gdn_scale_k(qc, inv);
+                        else q_s[j * 128 + cl] = gdn_scale_q(qc, inv);
                     }
                     cbar();
                 }
@@ -891,9 +893,10 @@ __global__ void __launch_bounds__(PS_THREADS, 1) k_step_persistent(PStepArgs a) 
                 }
                 __syncwarp();
                 if (tl_cta && lane == 0) tl_cta[L * 24 + 15] = ps_now() - t_start;
-                route_row_smem(lrow, g.E, g.topk, sm.misc->inds, sm.misc->scores, sm.rbuf, lane);
-                __syncwarp();
-                if (lane == 0) { __threadfence_block(); *(volatile int*)&sm.misc->route_layer = L + 1; if (tl_cta) tl_cta[L * 24 + 9] = ps_now() - t_start; }
+                // the chosen experts are published (route_layer = L + 1) as soon as they are known: the producer warp starts the
+                // weight copies while this warp goes on with the gates
+                route_row_smem(lrow, g.E, g.topk, sm.misc->inds, sm.misc->scores, sm.rbuf, lane, &sm.misc->route_layer, L + 1);
+                if (lane == 0 && tl_cta) tl_cta[L * 24 + 9] = ps_now() - t_start;
             }
             if (k.gu_slot >= 0 && k.n_gu > 0) {
                 int x0, x1; ps_range(g.I / 8, g.gu_spp, c % g.gu_spp, x0, x1);

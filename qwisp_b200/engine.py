@@ -83,8 +83,8 @@ class Engine:
         lib().sl_inject_fault(self._h, 1 if on else 0)
 
     def use_persistent(self, on=True):
-        """Select the one-kernel decode step (True, the default where available) or the kernel-per-phase
-        assembly for single-stream decode steps; returns whether the one-kernel step is available."""
+        """Select the one-kernel decode step (True) or the kernel-per-phase assembly (the default) for
+        single-stream decode steps; returns whether the one-kernel step is available."""
         return lib().sl_engine_use_persistent(self._h, 1 if on else 0) == 1
 
     def step_timeline(self, run):

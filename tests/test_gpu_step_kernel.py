@@ -55,7 +55,7 @@ def test_step_kernel_equals_kernel_per_phase(geom_name, tiny_engine, mini_engine
         assert np.array_equal(a.state_save(), b.state_save())
         a.close(); b.close()
     finally:
-        eng.use_persistent(True)
+        eng.use_persistent(False)
 
 
 def test_step_kernel_two_streams_interleaved(tiny_engine):
@@ -77,7 +77,7 @@ def test_step_kernel_two_streams_interleaved(tiny_engine):
         for s in (s1, s2, r1, r2):
             s.close()
     finally:
-        eng.use_persistent(True)
+        eng.use_persistent(False)
 
 
 def test_step_kernel_full_model_tokens_identical():
