@@ -74,6 +74,10 @@ struct sl_engine {
     int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
     bool ep_step = false;
     void* ep_comm = nullptr;
+    EpPeers ep_peers{};               // peer-memory exchange buffers (own + mapped peers'), see ep_exchange.cu
+    void* ep_region = nullptr;        // this rank's exchange region (shared with the peers through CUDA IPC)
+    void* ep_mapped[8] = {};          // peers' regions as mapped here
+    int ep_layer_seq = 0;             // MoE layers enqueued so far in the step being built
     SegDesc* segs = nullptr;
     int hist_cap = 0;
     // pinned staging
@@ -486,39 +490,36 @@ void pf_q4(PfList& pf, int i, const Q4R& q, size_t max_bytes = (size_t)48 << 20)
     if (i + 1 < 6 && gb) { pf.p[i + 1] = q.sr; pf.bytes[i + 1] = (unsigned)gb; }
 }
 
-// Expert-parallel MoE block of a decode step.  Every rank runs the same number M of rows (its own
-// streams).  Rank r owns experts [ep_e0, ep_e1).  Per layer:
-//   router on the local rows  ->  all-gather of the normed rows and of the routing indices
-//   ->  this rank's experts run on the rows of ALL ranks that chose them (pairs grouped locally)
-//   ->  reduce-scatter of the pair outputs: every pair was computed by exactly one rank and is zero
-//       elsewhere, so the sum is exact and the owner receives the same bits a single GPU computes
-//   ->  the owner combines in ascending k, adds the shared expert (computed locally) and the residual.
-// Buffers are the engine's ordinary ones (sized by max_rows >= world * M): rank r's rows live at
-// offset r*M of p / inds, its pairs at offset r*M*top_k of dbuf, so both collectives run in place.
+// Expert-parallel MoE block of a decode step.  Every rank runs the same number M of rows (its own streams);
+// rank r owns experts [ep_e0, ep_e1).  Per layer (kernels of ep_exchange.cu, no collective):
+//   router on the local rows -> k_ep_dispatch stores the normed rows and routing indices into every rank's
+//   gather buffers over peer memory -> k_ep_lists waits for all ranks' rows, groups the pairs that chose a local
+//   expert -> the expert kernels run on them, the down projection storing each pair's output row straight into
+//   the pair owner's buffer -> k_ep_signal -> k_ep_combine waits for all ranks' outputs and combines in ascending k
+//   with the shared expert (computed locally on the local rows) and the residual.
+// Each pair row is computed by exactly one rank and arrives unreduced: the owner sees a single GPU's bits.
 int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __half* resid, __half* plain_out) {
     cudaStream_t st = e->stream;
     const int R = e->ep_world, r = e->ep_rank, T = R * M, topk = e->topk, H = e->H;
-    ncclComm_t comm = (ncclComm_t)e->ep_comm;
+    const int layer = e->ep_layer_seq++;
+    const EpPeers& P = e->ep_peers;
     ra.p = e->p + (size_t)r * M * H;
     ra.inds = e->inds + (size_t)r * M * topk;
     launch_router(ra, st, false);                      // its own pair lists are not used in this mode
-    NC(e, g_nccl.GroupStart());
-    NC(e, g_nccl.AllGather(ra.p, e->p, (size_t)M * H, ncclFloat16, comm, st));
-    NC(e, g_nccl.AllGather(ra.inds, e->inds, (size_t)M * topk, ncclInt32, comm, st));
-    NC(e, g_nccl.GroupEnd());
-    launch_build_lists(e->inds, T * topk, e->ep_e0, e->ep_e1, e->lists, st);
-    CU(e, cudaMemsetAsync(e->dbuf, 0, (size_t)T * topk * H * sizeof(__half), st));
+    launch_ep_dispatch(P, ra.p, ra.inds, M, H, topk, layer, st);
+    launch_ep_lists(P, T * topk, e->ep_e0, e->ep_e1, e->lists, layer, e->err_flag, st);
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
-    ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = T; ea.H = H; ea.I = e->I; ea.topk = topk;
+    ea.lists = e->lists; ea.p = P.pbuf[r]; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = T; ea.H = H; ea.I = e->I; ea.topk = topk;
     ea.M_shared = M; ea.shared_row0 = r * M;
     ea.scores = e->scores; ea.sgl = e->sgl; ea.tile_counter = nullptr; ea.err = e->err_flag;
+    for (int d = 0; d < R; ++d) ea.peer_dbuf[d] = P.dbuf[d];
+    ea.ep_pairs_per_rank = M * topk;
     const int local_e = e->ep_e1 - e->ep_e0;
     const int nslots = T * topk < local_e ? T * topk : local_e;
     launch_expert_gateup(ea, nslots, st, false);
     launch_expert_down(ea, nslots, st, false);
-    __half* mine = e->dbuf + (size_t)r * M * topk * H;
-    NC(e, g_nccl.ReduceScatter(e->dbuf, mine, (size_t)M * topk * H, ncclFloat16, ncclSum, comm, st));
-    launch_moe_combine(e->dbuf, r * M * topk, T * topk, e->scores, e->sgl, M, H, topk, resid, plain_out, st);
+    launch_ep_signal(P, layer, st);
+    launch_ep_combine(P, e->dbuf + (size_t)T * topk * H, e->scores, e->sgl, M, H, topk, resid, plain_out, layer, e->err_flag, st);
     return SL_OK;
 }
 
@@ -591,6 +592,7 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
 // all kernels of one call; descriptors / tokens are already on the device
 void enqueue_step(sl_engine* e, int M, int nsegs, HeadMode head, bool want_logits) {
     cudaStream_t st = e->stream;
+    e->ep_layer_seq = 0;
     launch_embed(e->embed, e->tok_in, M, e->H, e->V, e->h, st);
     for (size_t li = 0; li < e->layers.size(); ++li) {
         const LayerW& L = e->layers[li];
@@ -609,6 +611,7 @@ void enqueue_step(sl_engine* e, int M, int nsegs, HeadMode head, bool want_logit
     se.out_tok = (head == HEAD_ARGMAX || head == HEAD_LOGITS) ? e->out_tok : nullptr;
     se.tok_in = e->tok_in; se.hist = e->hist; se.hist_pos = e->hist_pos; se.hist_cap = e->hist_cap;
     launch_step_end(se, st);
+    if (e->ep_step) launch_ep_step_end(e->ep_peers.ctr, st);       // every rank advances its exchange counter once per step
 }
 
 // make sure `s` has KV pages for `new_len` positions; uploads new page-table entries
@@ -658,9 +661,9 @@ int32_t enqueue_decode_step(sl_engine* e, int rows) {
         CU(e, cudaGetLastError());
         return SL_OK;
     }
-    // expert-parallel steps are enqueued eagerly: capturing the NCCL collectives into the step graph
-    // deadlocked on two ranks when it was tried, so that combination is not offered
-    if (!e->use_graph || e->ep_step) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return e->poisoned ? SL_ERR_CUDA : SL_OK; }
+    // (expert-parallel steps contain no collective -- the exchange is this library's own kernels over peer memory --
+    // so they are captured like any other step)
+    if (!e->use_graph) { enqueue_step(e, rows, rows, HEAD_ARGMAX, false); return e->poisoned ? SL_ERR_CUDA : SL_OK; }
     const int key = rows | (e->ep_step ? (1 << 24) : 0);
     auto it = e->graphs.find(key);
     if (it == e->graphs.end()) {
@@ -722,6 +725,7 @@ extern "C" {
 int32_t sl_engine_destroy(sl_engine* e) {
     if (!e) return SL_ERR_INVALID;
     if (e->ep_comm && g_nccl.ok) { cudaStreamSynchronize(e->stream); g_nccl.CommDestroy((ncclComm_t)e->ep_comm); e->ep_comm = nullptr; }
+    for (int d = 0; d < 8; ++d) if (e->ep_mapped[d]) { cudaIpcCloseMemHandle(e->ep_mapped[d]); e->ep_mapped[d] = nullptr; }
     cudaDeviceSynchronize();
     for (auto& g : e->graphs) cudaGraphExecDestroy(g.second);
     for (void* p : e->allocs) cudaFree(p);
@@ -1141,7 +1145,7 @@ int32_t sl_ep_unique_id(uint8_t* out128) {
 }
 int32_t sl_ep_init(sl_engine* e, int32_t rank, int32_t world, const uint8_t* id128, int32_t rows_per_rank) {
     int32_t rc = guard(e); if (rc) return rc;
-    if (!id128 || world < 1 || rank < 0 || rank >= world || rows_per_rank <= 0) return SL_ERR_INVALID;
+    if (!id128 || world < 1 || world > 8 || rank < 0 || rank >= world || rows_per_rank <= 0) return SL_ERR_INVALID;
     if (e->E % world) return SL_ERR_INVALID;
     if ((int64_t)world * rows_per_rank > e->cfg.max_rows) return SL_ERR_CAPACITY;   // gathered rows use the ordinary buffers
     if (e->ep_comm) return SL_ERR_INVALID;
@@ -1151,6 +1155,39 @@ int32_t sl_ep_init(sl_engine* e, int32_t rank, int32_t world, const uint8_t* id1
     NC(e, g_nccl.CommInitRank(&comm, world, id, rank));
     e->ep_comm = comm; e->ep_rank = rank; e->ep_world = world; e->ep_rows = rows_per_rank;
     e->ep_e0 = rank * (e->E / world); e->ep_e1 = e->ep_e0 + e->E / world;
+    // The exchange region of this rank: [gathered rows][gathered indices][pair outputs of the local rows][flags, counter].
+    // Its CUDA IPC handle goes to every rank through one all-gather on the new communicator (the only collective this
+    // mode ever runs); each rank maps every peer's region and from then on talks to it with plain loads and stores.
+    const int M = rows_per_rank, T = world * M;
+    const size_t b_p = ((size_t)T * e->H * 2 + 255) & ~(size_t)255, b_i = ((size_t)T * e->topk * 4 + 255) & ~(size_t)255;
+    const size_t b_d = ((size_t)M * e->topk * e->H * 2 + 255) & ~(size_t)255, b_f = 256;
+    unsigned char* region = nullptr;
+    if ((rc = dalloc(e, &region, b_p + b_i + b_d + b_f))) return rc;
+    CU(e, cudaMemsetAsync(region, 0, b_p + b_i + b_d + b_f, e->stream));
+    e->ep_region = region;
+    cudaIpcMemHandle_t mine;
+    CU(e, cudaIpcGetMemHandle(&mine, region));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    unsigned char* hbuf = nullptr;
+    if ((rc = dalloc(e, &hbuf, (size_t)64 * world))) return rc;
+    CU(e, cudaMemcpyAsync(hbuf + 64 * rank, &mine, 64, cudaMemcpyHostToDevice, e->stream));
+    NC(e, g_nccl.AllGather(hbuf + 64 * rank, hbuf, 64, ncclUint8, comm, e->stream));
+    std::vector<cudaIpcMemHandle_t> all((size_t)world);
+    CU(e, cudaMemcpyAsync(all.data(), hbuf, (size_t)64 * world, cudaMemcpyDeviceToHost, e->stream));
+    CU(e, cudaStreamSynchronize(e->stream));
+    EpPeers& P = e->ep_peers;
+    P.world = world; P.rank = rank;
+    for (int d = 0; d < world; ++d) {
+        unsigned char* base = region;
+        if (d != rank) {
+            void* mapped = nullptr;
+            CU(e, cudaIpcOpenMemHandle(&mapped, all[(size_t)d], cudaIpcMemLazyEnablePeerAccess));
+            e->ep_mapped[d] = mapped; base = (unsigned char*)mapped;
+        }
+        P.pbuf[d] = (__half*)base; P.ibuf[d] = (int*)(base + b_p); P.dbuf[d] = (__half*)(base + b_p + b_i);
+        P.flags[d] = (unsigned*)(base + b_p + b_i + b_d);
+    }
+    P.ctr = (unsigned*)(region + b_p + b_i + b_d) + 32;
     return SL_OK;
 }
 

@@ -787,7 +787,15 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
             if (DOWN) {
                 for (int i = threadIdx.x; i < TPC * 128; i += blockDim.x) {
                     int tl2 = i >> 7, col = (i >> 4) & 7, row = i & 15, tile2 = blockIdx.x * TPC + tl2;
-                    if (tile2 < ntiles && col < mr) a.dbuf[(size_t)misc[8 + col] * a.H + tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, col));
+                    if (tile2 < ntiles && col < mr) {
+                        const int dst = misc[8 + col];
+                        __half* rowp = a.dbuf + (size_t)dst * a.H;
+                        if (a.ep_pairs_per_rank > 0 && dst < npair) {       // routed pair in expert-parallel mode: the owner's buffer
+                            const int own = dst / a.ep_pairs_per_rank;
+                            rowp = a.peer_dbuf[own] + (size_t)(dst - own * a.ep_pairs_per_rank) * a.H;
+                        }
+                        rowp[tile2 * 16 + row] = f2h(tile_value(fin + tl2 * 128, row, col));
+                    }
                 }
             } else {
                 for (int j2 = threadIdx.x; j2 < TPC * 64; j2 += blockDim.x) {

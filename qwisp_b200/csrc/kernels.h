@@ -51,6 +51,15 @@ struct RouterArgs {
     PfList pf;                           // static prefetch (every CTA)
 };
 
+// Peer pointers of the expert-parallel exchange (ep_exchange.cu): entry d is rank d's buffer as mapped into this
+// process (entry `rank` is the local one).  pbuf: gathered normed rows [world*M][H]; ibuf: gathered routing indices
+// [world*M][top_k]; dbuf: the pair outputs of the OWNER's rows [M*top_k][H]; flags: [0,8) dispatch, [8,16) combine.
+struct EpPeers {
+    __half* pbuf[8]; int* ibuf[8]; __half* dbuf[8]; unsigned* flags[8];
+    unsigned* ctr;                       // local step counter (all ranks advance it in lockstep)
+    int world, rank;
+};
+
 struct ExpertArgs {
     int lg_slices = 0;                   // log2(K/256), filled by the launcher
     unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
@@ -73,6 +82,10 @@ struct ExpertArgs {
     __half* resid;                       // residual stream updated in place, or nullptr ...
     __half* out;                         // ... then the block output goes here
     unsigned* tile_counter;              // [H/16] tickets, zero between launches; nullptr: no fused combine (dbuf only)
+    // expert-parallel down projection: a routed pair's output row goes to the pair owner's buffer over peer memory
+    // (rank = pair / ep_pairs_per_rank, row inside it = pair % ep_pairs_per_rank); nullptr entries: everything local
+    __half* peer_dbuf[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int ep_pairs_per_rank = 0;
     PfList pf;                           // static prefetch (gate/up kernel: next layer's in-projection)
 };
 
@@ -168,6 +181,12 @@ void launch_build_lists(const int* inds, int npairs, int e0, int e1, MoeLists li
 // out/resid[m] (+)= sum_k fp16(d[pair0 + m*topk + k] * score[m,k]) (ascending k) + sigmoid(sgl[m]) * d[shared0 + m]
 void launch_moe_combine(const __half* dbuf, int pair0, int shared0, const __half* scores, const __half* sgl, int M, int H, int topk,
                         __half* resid, __half* out, cudaStream_t st);
+void launch_ep_dispatch(const EpPeers& P, const __half* p_local, const int* inds_local, int M, int H, int topk, int layer, cudaStream_t st);
+void launch_ep_lists(const EpPeers& P, int npairs, int e0, int e1, const MoeLists& lists, int layer, unsigned* err, cudaStream_t st);
+void launch_ep_signal(const EpPeers& P, int layer, cudaStream_t st);
+void launch_ep_combine(const EpPeers& P, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,
+                       __half* resid, __half* out, int layer, unsigned* err, cudaStream_t st);
+void launch_ep_step_end(unsigned* ctr, cudaStream_t st);
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl);
 void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
 // q/k prep (when every row is its stream's only row) + split-KV decode + merge in one launch; counters: M*KV zeros
