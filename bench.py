@@ -21,8 +21,8 @@ excluded (swift/Sources/QwispCore/TellRuntime.swift:1267, 1449-1450).
 `--impl reference` times the reference's path on the host cores instead (the CPU restatement of
 its kernels: the reference itself is Swift + Metal and cannot run on Linux).
 With N > 1 the workload is the batched one BASELINE.json pairs with multi-GPU: 64 concurrent streams
-decoded with the MoE expert-parallel across the N GPUs (NCCL all-gather dispatch + reduce-scatter
-combine per layer, attention/GDN data-parallel), aggregate tok/s, total work fixed ("strong").
+decoded with the MoE expert-parallel across the N GPUs (dispatch and combine per layer by the library's own
+kernels over NVLink peer memory, attention/GDN data-parallel), aggregate tok/s, total work fixed ("strong").
 The N=1 line carries the same 64-stream workload on one GPU as `batch64_1gpu`, so both series
 (batch 1, batch 64) have their one-GPU point.
 """
@@ -281,6 +281,17 @@ def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
         t = torch.tensor([ms, wall * 1e3], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, wall = float(t[0]), float(t[1]) / 1e3
+    # per-kernel CUDA-event shares of a step (a few eager steps after the timed region; every rank runs them in lockstep)
+    eng.use_graphs(False)
+    prof_last = [int(v) for v in eng.batch_step_argmax(streams, last)]
+    eng.profile_start()
+    nprof = 3
+    for _ in range(nprof):
+        prof_last = [int(v) for v in eng.batch_step_argmax(streams, prof_last)]
+    prep = eng.profile_report()
+    eng.use_graphs(True)
+    ptot = sum(v[1] for v in prep.values()) or 1.0
+    kernel_shares = {k: {"launches_per_step": v[0] / nprof, "ms_per_step": v[1] / nprof, "share": v[1] / ptot} for k, v in prep.items()}
     fault = eng.gpu_fault()
     for st in streams:
         st.close()
@@ -308,6 +319,7 @@ def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
         raise SystemExit(f"engine fault during the batched run: {fault}")
     return {"tok_s": BATCH_STREAMS * K / (ms * 1e-3), "tok_s_wall": BATCH_STREAMS * K / wall, "ms_per_step": ms / K,
             "launches_per_step": launches, "rows_per_rank": B, "tokens": np.stack(toks), "tokens_identical_to_solo": identical,
+            "kernel_shares": kernel_shares,
             "ctx": float(np.mean(plens)) + W + K / 2.0}
 
 
@@ -345,8 +357,10 @@ def run_batch64_line(args, rank, local_rank, world):
                 "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD64 if args.layers == 40 else f"DEBUG {args.layers}-layer variant of " + WORKLOAD64,
-                           "parallelism": f"ep{world}: experts split {256 // world} per GPU, {r['rows_per_rank']} streams per GPU; "
-                                          "per MoE layer one NCCL all-gather (rows + routing) and one reduce-scatter (pair outputs)",
+                           "parallelism": f"ep{world}: experts split {256 // world} per GPU, {r['rows_per_rank']} streams per GPU; per MoE layer the normed rows "
+                                          "and routing indices go to every rank and each pair's expert output goes back to its owner by this library's own "
+                                          "kernels over NVLink peer memory (no collective inside a step; steps replay as CUDA graphs)",
+                           "kernel_shares_rank0": r["kernel_shares"],
                            "l2": "inputs larger than L2: a step streams the touched experts (GBs) plus 1.6 GB of dense weights",
                            "timing": "K host-driven batched steps between CUDA events on the launching stream, max over ranks"},
                 "clocks": clocks,
@@ -512,7 +526,7 @@ def main():
         bb = batch_step_bytes_per_rank(BATCH_STREAMS, 1, b["ctx"])
         bg = bb / (b["ms_per_step"] * 1e-3) / 1e9
         batch64 = {"metric": "decode_tok_per_s_batch64", "value": b["tok_s"], "e2e": b["tok_s_wall"], "ms_per_step": b["ms_per_step"],
-                   "steps": min(K, 32), "workload": WORKLOAD64, "launches_per_step": b["launches_per_step"],
+                   "steps": min(K, 32), "workload": WORKLOAD64, "launches_per_step": b["launches_per_step"], "kernel_shares": b["kernel_shares"],
                    "roofline": {"bound": "hbm", "achieved": bg, "peak": peak_gbs, "unit": "GB/s", "frac": bg / peak_gbs, "traffic": None,
                                 "algorithmic_bytes_per_step": bb, "note": "whole step; expert bytes are the expectation for uniform routing"}}
     if rank == 0:
