@@ -103,6 +103,18 @@ __device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
     return v;
 }
 
+// ---- cross-GPU flags of the expert-parallel exchange (system scope: the other side is a peer GPU) ----
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// sequence number of (step counter, MoE layer of the step, phase 0 = dispatch / 1 = combine): monotonic, never 0
+__device__ __forceinline__ unsigned ep_seq(const unsigned* ctr, int layer, int phase) { return (*ctr) * 256u + (unsigned)layer * 2u + (unsigned)phase + 1u; }
+
 // per-stream device-resident bookkeeping, indexed by stream slot
 struct StreamTable {
     int* kv_len;            // [max_streams] positions already in the cache

@@ -67,7 +67,7 @@ struct sl_engine {
     float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
-    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; unsigned* err_host = nullptr; float* adj_buf = nullptr; int* samp_buf = nullptr; unsigned* slot_sync = nullptr;
+    unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; unsigned* err_host = nullptr; float* adj_buf = nullptr; int* samp_buf = nullptr; unsigned* slot_sync = nullptr; unsigned* router_groups = nullptr;
     bool use_route_in_experts = true;   // with the fused kernel: routing done by its CTAs (SEEDLESS_ROUTE_IN_EXPERTS=0: by the router's last CTA)
     bool use_fused_experts = true;  // batch-1 decode: gate/up + down in one launch (SEEDLESS_FUSED_EXPERTS=0 turns it off)
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
@@ -317,6 +317,8 @@ int32_t build_runtime(sl_engine* e) {
     CU(e, cudaMemset(e->tile_counters, 0, (size_t)(H / 16) * sizeof(unsigned)));
     CU(e, cudaMemset(e->counters, 0, 8 * sizeof(unsigned)));
     if ((rc = dalloc(e, &e->samp_buf, (size_t)4 * R))) return rc;
+    if ((rc = dalloc(e, &e->router_groups, (size_t)(R / 8 + 2)))) return rc;
+    CU(e, cudaMemset(e->router_groups, 0, (size_t)(R / 8 + 2) * sizeof(unsigned)));
     if ((rc = dalloc(e, &e->slot_sync, (size_t)64))) return rc;
     CU(e, cudaMemset(e->slot_sync, 0, 64 * sizeof(unsigned)));
     // Kernels whose bounded wait runs out leave a code here.  The word lives in mapped page-locked host
@@ -492,10 +494,10 @@ void pf_q4(PfList& pf, int i, const Q4R& q, size_t max_bytes = (size_t)48 << 20)
 
 // Expert-parallel MoE block of a decode step.  Every rank runs the same number M of rows (its own streams);
 // rank r owns experts [ep_e0, ep_e1).  Per layer (kernels of ep_exchange.cu, no collective):
-//   router on the local rows -> k_ep_dispatch stores the normed rows and routing indices into every rank's
-//   gather buffers over peer memory -> k_ep_lists waits for all ranks' rows, groups the pairs that chose a local
-//   expert -> the expert kernels run on them, the down projection storing each pair's output row straight into
-//   the pair owner's buffer -> k_ep_signal -> k_ep_combine waits for all ranks' outputs and combines in ascending k
+//   router on the local rows, its last CTA storing the normed rows and routing indices into every rank's gather
+//   buffers over peer memory -> k_ep_lists waits for all ranks' rows, groups the pairs that chose a local expert
+//   -> the expert kernels run on them, the down projection storing each pair's output row straight into the pair
+//   owner's buffer and raising the combine flags -> k_ep_combine waits for all ranks' outputs, combines in ascending k
 //   with the shared expert (computed locally on the local rows) and the residual.
 // Each pair row is computed by exactly one rank and arrives unreduced: the owner sees a single GPU's bits.
 int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __half* resid, __half* plain_out) {
@@ -505,8 +507,9 @@ int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __ha
     const EpPeers& P = e->ep_peers;
     ra.p = e->p + (size_t)r * M * H;
     ra.inds = e->inds + (size_t)r * M * topk;
-    launch_router(ra, st, false);                      // its own pair lists are not used in this mode
-    launch_ep_dispatch(P, ra.p, ra.inds, M, H, topk, layer, st);
+    for (int d = 0; d < R; ++d) { ra.epd.pbuf[d] = P.pbuf[d]; ra.epd.ibuf[d] = P.ibuf[d]; ra.epd.sig.flags[d] = P.flags[d]; }
+    ra.epd.sig.ctr = P.ctr; ra.epd.sig.world = R; ra.epd.sig.rank = r; ra.epd.sig.layer = layer;
+    launch_router(ra, st, false);                      // its last CTA sends the rows and indices to every rank
     launch_ep_lists(P, T * topk, e->ep_e0, e->ep_e1, e->lists, layer, e->err_flag, st);
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
     ea.lists = e->lists; ea.p = P.pbuf[r]; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = T; ea.H = H; ea.I = e->I; ea.topk = topk;
@@ -514,11 +517,11 @@ int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __ha
     ea.scores = e->scores; ea.sgl = e->sgl; ea.tile_counter = nullptr; ea.err = e->err_flag;
     for (int d = 0; d < R; ++d) ea.peer_dbuf[d] = P.dbuf[d];
     ea.ep_pairs_per_rank = M * topk;
+    ea.ep_sig = ra.epd.sig; ea.ep_sig.ticket = e->counters + 2;
     const int local_e = e->ep_e1 - e->ep_e0;
     const int nslots = T * topk < local_e ? T * topk : local_e;
     launch_expert_gateup(ea, nslots, st, false);
-    launch_expert_down(ea, nslots, st, false);
-    launch_ep_signal(P, layer, st);
+    launch_expert_down(ea, nslots, st, false);       // its last CTA raises the combine flags
     launch_ep_combine(P, e->dbuf + (size_t)T * topk * H, e->scores, e->sgl, M, H, topk, resid, plain_out, layer, e->err_flag, st);
     return SL_OK;
 }
@@ -532,6 +535,7 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     ra.sg_q8 = L.sg_q8; ra.sg_qs = L.sg_qs; ra.sg_qb = L.sg_qb;
     ra.p = e->p; ra.logits = e->rlogits; ra.sgl = e->sgl;
     ra.topk = e->topk; ra.inds = e->inds; ra.scores = e->scores; ra.lists = e->lists; ra.counter = e->counters + 1;
+    ra.group_counter = e->router_groups;
     if (e->ep_step) { enqueue_moe_ep(e, L, ra, M, resid, plain_out); return; }
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
     ea.lists = e->lists; ea.p = e->p; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = M; ea.H = e->H; ea.I = e->I; ea.topk = e->topk;

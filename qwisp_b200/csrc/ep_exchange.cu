@@ -4,12 +4,13 @@
 // normed rows and routing choices of ALL ranks (dispatch), and afterwards gets back, for each of its own (row, k)
 // pairs, the one expert output that some rank computed (combine).  Both are tiny (a few hundred KB per layer) and
 // latency-bound, so they are done with plain peer stores from this library's own kernels instead of collectives:
-//   dispatch  k_ep_dispatch: each rank stores its M rows and M*top_k indices straight into every peer's gather
-//             buffers, then (after a system fence) a sequence number into that peer's flag word for this rank;
+//   dispatch  the router kernel's last CTA (k_moe_router, RouterArgs::epd) stores the rank's M normed rows and
+//             M*top_k indices straight into every peer's gather buffers, then (after a system fence) a sequence
+//             number into that peer's flag word for this rank;
 //   wait      k_ep_lists: one CTA waits for all ranks' flags, then groups the pairs that chose a local expert;
 //   combine   the down-projection kernel stores each pair's output row directly into the pair OWNER's buffer
-//             (ExpertArgs::peer_dbuf), k_ep_signal then raises the owner's flag, and k_ep_combine waits for all
-//             flags before it forms the weighted sum in ascending k.
+//             (ExpertArgs::peer_dbuf); its last CTA raises this rank's flag at every peer, and k_ep_combine waits
+//             for all flags before it forms the weighted sum in ascending k.
 // Every pair row is written by exactly one rank and arrives unreduced, so the owner sees the bits a single GPU
 // computes.  No multicast, no collective inside a step (so a step can be captured in a CUDA graph); every wait is
 // bounded and reports through the engine's error word.  There is no counterpart in the reference (one GPU).
@@ -19,16 +20,6 @@ namespace sl {
 
 constexpr long long EP_TIMEOUT = 1ll << 30;        // cycles (~0.5 s) a flag wait may take
 
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// sequence number of (step counter, layer, phase): monotonic, never 0
-__device__ __forceinline__ unsigned ep_seq(const unsigned* ctr, int layer, int phase) { return (*ctr) * 256u + (unsigned)layer * 2u + (unsigned)phase + 1u; }
 // wait until flag >= seq (sequence numbers only grow); false after the budget
 __device__ __forceinline__ bool ep_wait_flag(const unsigned* flag, unsigned seq) {
     const long long t0 = clock64();
@@ -36,23 +27,6 @@ __device__ __forceinline__ bool ep_wait_flag(const unsigned* flag, unsigned seq)
         for (int i = 0; i < 64; ++i) if ((int)(ld_acquire_sys(flag) - seq) >= 0) return true;
         if (clock64() - t0 > EP_TIMEOUT) return false;
     }
-}
-
-// grid (R), 256 threads: block d stores this rank's rows / indices into peer d's gather buffers and raises its flag
-__global__ void __launch_bounds__(256) k_ep_dispatch(EpPeers P, const __half* p_local, const int* inds_local, int M, int H, int topk, int layer) {
-    const int d = blockIdx.x, r = P.rank;
-    const unsigned seq = ep_seq(P.ctr, layer, 0);
-    uint4* dst = reinterpret_cast<uint4*>(P.pbuf[d] + (size_t)r * M * H);
-    const uint4* src = reinterpret_cast<const uint4*>(p_local);
-    for (int i = threadIdx.x; i < M * H / 8; i += blockDim.x) dst[i] = src[i];
-    int* di = P.ibuf[d] + (size_t)r * M * topk;
-    for (int i = threadIdx.x; i < M * topk; i += blockDim.x) di[i] = inds_local[i];
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) st_release_sys(P.flags[d] + r, seq);
-}
-void launch_ep_dispatch(const EpPeers& P, const __half* p_local, const int* inds_local, int M, int H, int topk, int layer, cudaStream_t st) {
-    profile_launch("k_ep_dispatch", st, [&] { k_ep_dispatch<<<P.world, 256, 0, st>>>(P, p_local, inds_local, M, H, topk, layer); return 0; });
 }
 
 // One CTA: wait for every rank's dispatch flag, then group the pairs (row, k) whose expert lies in [e0, e1) by
@@ -85,16 +59,6 @@ __global__ void __launch_bounds__(256) k_ep_lists(EpPeers P, int npairs, int e0,
 }
 void launch_ep_lists(const EpPeers& P, int npairs, int e0, int e1, const MoeLists& lists, int layer, unsigned* err, cudaStream_t st) {
     profile_launch("k_ep_lists", st, [&] { k_ep_lists<<<1, 256, (size_t)npairs * sizeof(int), st>>>(P, npairs, e0, e1, lists, layer, err); return 0; });
-}
-
-// after the down projection: raise this rank's combine flag at every peer (the kernel boundary before this launch
-// completed the down kernel's peer stores)
-__global__ void k_ep_signal(EpPeers P, int layer) {
-    const int d = threadIdx.x;
-    if (d < P.world) { __threadfence_system(); st_release_sys(P.flags[d] + 8 + P.rank, ep_seq(P.ctr, layer, 1)); }
-}
-void launch_ep_signal(const EpPeers& P, int layer, cudaStream_t st) {
-    profile_launch("k_ep_signal", st, [&] { k_ep_signal<<<1, 32, 0, st>>>(P, layer); return 0; });
 }
 
 // grid (M), 256 threads: wait for every rank's combine flag, then

@@ -621,19 +621,48 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
         }
     }
     if (a.no_route) return;                                  // the consumer routes from the logits itself
-    // ---- the CTA that finishes last routes every row and groups the (row, k) pairs by expert ----
+    // ---- the CTA that finishes last for a group of 8 rows routes those rows (one warp per row), so the groups are
+    //      routed side by side; the last of THOSE CTAs then groups the (row, k) pairs of all rows by expert ----
     __threadfence();
     __syncthreads();
-    if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x * gridDim.y - 1) ? 1 : 0; }
+    if (tid == 0) { unsigned ticket = atomicAdd(a.group_counter + blockIdx.y, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int m = warp; m < a.M; m += 8) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, s_route[warp], lane);
+    {
+        const int m = blockIdx.y * 8 + warp;
+        if (m < a.M) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, s_route[warp], lane);
+    }
+    if (tid == 0) a.group_counter[blockIdx.y] = 0u;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) { unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.y - 1) ? 1 : 0; }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
     if (tid == 0) *a.counter = 0u;
     __syncthreads();
+    if (a.epd.sig.world > 0) {
+        // expert-parallel: this CTA sends the rank's normed rows (written by the tail CTAs, complete once the last
+        // ticket was drawn) and routing indices into every rank's gather buffers over peer memory, then raises this
+        // rank's dispatch flag there; the pair lists are built from the gathered indices by a later kernel
+        const EpSignal& sg = a.epd.sig;
+        const int nv = a.M * a.H / 8, ni = a.M * a.topk;
+        for (int d = 0; d < sg.world; ++d) {
+            uint4* dst = reinterpret_cast<uint4*>(a.epd.pbuf[d] + (size_t)sg.rank * a.M * a.H);
+            const uint4* src = reinterpret_cast<const uint4*>(a.p);
+            for (int i = tid; i < nv; i += 256) dst[i] = __ldcg(src + i);
+            int* di = a.epd.ibuf[d] + (size_t)sg.rank * ni;
+            for (int i = tid; i < ni; i += 256) di[i] = __ldcg(a.inds + i);
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid < sg.world) st_release_sys(sg.flags[tid] + sg.rank, ep_seq(sg.ctr, sg.layer, 0));
+        return;
+    }
     if (a.M == 1) {                                          // one row: its k experts are distinct, slot k = k-th choice
         if (tid < a.topk) {
-            a.lists.slot_expert[tid] = a.inds[tid]; a.lists.slot_off[tid] = tid; a.lists.slot_cnt[tid] = 1; a.lists.pairs[tid] = tid;
+            a.lists.slot_expert[tid] = __ldcg(a.inds + tid); a.lists.slot_off[tid] = tid; a.lists.slot_cnt[tid] = 1; a.lists.pairs[tid] = tid;
         }
         if (tid == 0) *a.lists.n_active = a.topk;
         return;
@@ -641,7 +670,7 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     s_cnt[tid] = 0; s_cur[tid] = 0; s_off[tid] = 0;
     __syncthreads();
     const int npairs = a.M * a.topk;
-    for (int i = tid; i < npairs; i += 256) atomicAdd(&s_cnt[a.inds[i]], 1);
+    for (int i = tid; i < npairs; i += 256) atomicAdd(&s_cnt[__ldcg(a.inds + i)], 1);
     __syncthreads();
     if (tid == 0) {
         int slot = 0, off = 0;
@@ -654,7 +683,7 @@ __global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
     }
     __syncthreads();
     for (int i = tid; i < npairs; i += 256) {
-        int ex = a.inds[i];
+        int ex = __ldcg(a.inds + i);
         int pos = atomicAdd(&s_cur[ex], 1);
         a.lists.pairs[s_off[ex] + pos] = i;
     }
@@ -832,6 +861,20 @@ __global__ void __launch_bounds__(512, 1) k_expert(ExpertArgs a) {
             if (a.resid) a.resid[(size_t)m * a.H + n] = hadd_rn(a.resid[(size_t)m * a.H + n], res);
             else a.out[(size_t)m * a.H + n] = res;
         }
+    }
+    if (DOWN && a.ep_sig.world > 0) {
+        // expert-parallel: every CTA makes its peer stores visible system-wide and draws a ticket; the last one
+        // raises this rank's combine flag at every peer
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned ticket = atomicAdd(a.ep_sig.ticket, 1u);
+            misc[17] = (ticket == gridDim.x * gridDim.y - 1) ? 1 : 0;
+            if (misc[17]) *a.ep_sig.ticket = 0u;
+        }
+        __syncthreads();
+        if (misc[17] && (int)threadIdx.x < a.ep_sig.world)
+            st_release_sys(a.ep_sig.flags[threadIdx.x] + 8 + a.ep_sig.rank, ep_seq(a.ep_sig.ctr, a.ep_sig.layer, 1));
     }
 }
 template <bool DOWN, int UPW>

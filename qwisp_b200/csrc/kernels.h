@@ -25,6 +25,11 @@ struct DenseArgs {
     PfList pf;                                                   // weights of later kernels to pull into L2
 };
 
+// what a kernel needs to raise this rank's flags at its peers (world == 0: not expert-parallel)
+struct EpSignal { unsigned* flags[8]; unsigned* ctr; unsigned* ticket; int world = 0, rank = 0, layer = 0; };
+// the router's dispatch: peer gather buffers + flags
+struct EpDispatch { __half* pbuf[8]; int* ibuf[8]; EpSignal sig; };
+
 struct MoeLists {
     int* n_active;       // [1]
     int* slot_expert;    // [E]
@@ -47,7 +52,9 @@ struct RouterArgs {
     __half* sgl;                         // [M] shared-expert gate logit
     int topk; int* inds; __half* scores; // [M][topk] routing result (written by the last CTA)
     MoeLists lists; unsigned* counter;
+    unsigned* group_counter;             // [ceil(M/8)] tickets of the row groups, zero between launches
     int no_route = 0;                    // 1: stop after the logits; the consumer (fused expert kernel) routes from them itself
+    EpDispatch epd;                      // expert-parallel: the last CTA sends the rows and indices to every rank instead of building lists
     PfList pf;                           // static prefetch (every CTA)
 };
 
@@ -86,6 +93,7 @@ struct ExpertArgs {
     // (rank = pair / ep_pairs_per_rank, row inside it = pair % ep_pairs_per_rank); nullptr entries: everything local
     __half* peer_dbuf[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     int ep_pairs_per_rank = 0;
+    EpSignal ep_sig;                     // down kernel: its last CTA raises the combine flags
     PfList pf;                           // static prefetch (gate/up kernel: next layer's in-projection)
 };
 
@@ -181,9 +189,7 @@ void launch_build_lists(const int* inds, int npairs, int e0, int e1, MoeLists li
 // out/resid[m] (+)= sum_k fp16(d[pair0 + m*topk + k] * score[m,k]) (ascending k) + sigmoid(sgl[m]) * d[shared0 + m]
 void launch_moe_combine(const __half* dbuf, int pair0, int shared0, const __half* scores, const __half* sgl, int M, int H, int topk,
                         __half* resid, __half* out, cudaStream_t st);
-void launch_ep_dispatch(const EpPeers& P, const __half* p_local, const int* inds_local, int M, int H, int topk, int layer, cudaStream_t st);
 void launch_ep_lists(const EpPeers& P, int npairs, int e0, int e1, const MoeLists& lists, int layer, unsigned* err, cudaStream_t st);
-void launch_ep_signal(const EpPeers& P, int layer, cudaStream_t st);
 void launch_ep_combine(const EpPeers& P, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,
                        __half* resid, __half* out, int layer, unsigned* err, cudaStream_t st);
 void launch_ep_step_end(unsigned* ctr, cudaStream_t st);
