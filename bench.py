@@ -12,9 +12,9 @@ excluded (swift/Sources/QwispCore/TellRuntime.swift:1267, 1449-1450).
   e2e    -- the same K steps through the step call a host runtime makes (host token in,
             host token out, a synchronisation every step), wall clock
   roofline     -- the dominant kernel, timed live with CUDA events inside the timed region.  With the
-                  one-kernel decode step (the default) that kernel IS the step: one launch per token,
+                  one-kernel decode step (--step-kernel) that kernel IS the step: one launch per token,
                   algorithmic bytes = the token's 1.7 GB, duration = the events around the K launches / K.
-                  With the kernel-per-phase assembly (SEEDLESS_PERSISTENT=0) it is the kernel with the
+                  With the kernel-per-phase assembly (the default) it is the kernel with the
                   largest share of a separate eager pass.
   cpu_baseline -- the CPU oracle on the host cores, on a bounded sample of the same workload
 
@@ -225,6 +225,45 @@ WORKLOAD64 = ("cfg5 (decode part): the same model, 64 concurrent streams, seeded
               "prefill, the shared-prefix cache and the scheduler are outside the timed region")
 
 
+PREFILL_TOKENS = 4096
+
+
+def measure_prefill(Q, torch, layers, n_tokens=PREFILL_TOKENS, reps=3):
+    """Prefill-mode forward (tensor-core GEMM for the dense projections) of one n_tokens prompt given as HOST
+    tokens, one call; CUDA events on the engine's stream around each of `reps` calls after one warm-up call, the
+    stream reset between calls.  Also the per-kernel CUDA-event shares of one eager call."""
+    cfg = Q.config(n_layers=layers, max_rows=n_tokens, max_streams=1, kv_page_size=64, kv_pages=n_tokens // 64 + 4)
+    eng = Q.Engine.synthetic(cfg, seed=0, norm_jitter=0.0, conv_std=0.02)
+    tstream = torch.cuda.Stream()
+    eng.set_cuda_stream(tstream.cuda_stream)
+    prompt = Q.ops.synth_tokens(0, "bench.prefill.prompt", n_tokens, cfg.vocab)
+    st = eng.stream(n_tokens + 64)
+    st.forward_hybrid(prompt, want_hidden=False)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(reps):
+        st.reset()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record(tstream)
+        st.forward_hybrid(prompt, want_hidden=False)
+        ev1.record(tstream)
+        torch.cuda.synchronize()
+        times.append(ev0.elapsed_time(ev1))
+    st.reset()
+    eng.profile_start()
+    st.forward_hybrid(prompt, want_hidden=False)
+    rep = eng.profile_report()
+    tot = sum(v[1] for v in rep.values()) or 1.0
+    shares = {k: {"launches": v[0], "ms": v[1], "share": v[1] / tot} for k, v in rep.items()}
+    fault = eng.gpu_fault()
+    st.close(); eng.close()
+    ms = sorted(times)[len(times) // 2]
+    return {"metric": "prefill_tok_per_s", "value": n_tokens / (ms * 1e-3), "unit": "tok/s", "ms": ms, "tokens": n_tokens, "calls": 1,
+            "mode": "prefill mode (sl_forward_hybrid): dense projections on the tcgen05 GEMM, experts and mixers on the row kernels",
+            "kernel_shares": shares, "gpu_fault": fault}
+
+
 def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
     """64 streams dealt to the ranks in blocks; every decode step is one sl_batch_step_argmax per rank
     (expert-parallel when world > 1).  Returns (aggregate tok/s by device events, by wall clock,
@@ -386,6 +425,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-batch64", action="store_true", help="skip the 64-stream measurement on the one-GPU line")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill-mode measurement on the one-GPU line")
+    ap.add_argument("--step-kernel", action="store_true", help="batch-1 arm: decode with the one-kernel step instead of the kernel-per-phase assembly")
+    ap.add_argument("--timeline", action="store_true", help="with --step-kernel: add the per-phase timeline of one step (median over CTAs, microseconds) to the line")
     ap.add_argument("--layers", type=int, default=40, help="debug only: fewer layers (the reported line then says so)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -410,7 +452,8 @@ def main():
 
     K, W = args.steps, max(args.warmup, 3)
     max_seq = PROMPT_LEN + 2 * (K + W) + 64
-    cfg = Q.config(n_layers=args.layers, max_rows=PROMPT_LEN, max_streams=2, kv_page_size=64, kv_pages=2 * (max_seq // 64 + 2))
+    cfg = Q.config(n_layers=args.layers, max_rows=PROMPT_LEN, max_streams=2, kv_page_size=64, kv_pages=2 * (max_seq // 64 + 2),
+                   flags=Q._lib.SL_FLAG_STEP_KERNEL if args.step_kernel else 0)
     eng = Q.Engine.synthetic(cfg, seed=0, norm_jitter=0.0, conv_std=0.02)
     tstream = torch.cuda.Stream()
     eng.set_cuda_stream(tstream.cuda_stream)
@@ -508,6 +551,34 @@ def main():
                     "traffic": measured_traffic(dom) if args.layers == 40 else None, "peak_source": peak_src,
                     "algorithmic_bytes_per_launch": by / n, "us_per_launch": us_in_step, "us_per_launch_eager_events": ms / n * 1e3}
 
+    timeline = None
+    if rank == 0 and persistent and args.timeline:
+        # phase boundaries of the one-kernel step, stamped by every CTA with the global nanosecond timer: per layer
+        # kind, the median over CTAs of each boundary relative to the median layer start, averaged over the layers
+        names = ["start", "staged", "inproj_units", "inproj_stored", "mixer_end", "out_staged", "out_stored", "router_staged", "router_jobs_issued",
+                 "routed", "gu_units", "gu_stored", "down_staged", "down_units", "layer_end", "logits_polled", "router_job_done"]
+        cur3 = [int(toks_dev[-1])]
+
+        def run3():
+            for _ in range(3):
+                cur3[0] = int(st.step_argmax([cur3[0]])[0])
+        tl = eng.step_timeline(run3).astype(np.int64)
+        tl = np.where(tl > 0, tl, -1).astype(np.float64)
+        tl[tl < 0] = np.nan
+        timeline = {"unit": "us, median over CTAs relative to the median layer start, mean over layers of the kind", "names": names}
+        for kind, layers_of in (("gdn_layer", [L for L in range(args.layers) if (L + 1) % 4]), ("attention_layer", [L for L in range(args.layers) if (L + 1) % 4 == 0])):
+            rows = []
+            for L in layers_of[1:]:
+                med = np.nanmedian(tl[:, L, :17], axis=0)
+                rows.append((med - med[0]) / 1000.0)
+            if rows:
+                timeline[kind] = [round(float(x), 2) for x in np.nanmean(np.stack(rows), axis=0)]
+        starts = np.nanmedian(tl[:, :, 0], axis=0)
+        timeline["layer_us"] = {"gdn": round(float(np.mean([starts[L + 1] - starts[L] for L in range(args.layers - 1) if (L + 1) % 4])) / 1000.0, 2),
+                                "attention": round(float(np.mean([starts[L + 1] - starts[L] for L in range(args.layers - 1) if (L + 1) % 4 == 0])) / 1000.0, 2) if args.layers >= 5 else None}
+        head = np.nanmedian(tl[:, args.layers, :3], axis=0)
+        timeline["lm_head_us"] = round(float(head[2] - head[0]) / 1000.0, 2)
+
     tok_s = world * K / (dev_ms * 1e-3)
     e2e_tok_s = world * K / (e2e_ms * 1e-3)
     step_gbs = step_bytes / (dev_ms / K * 1e-3) / 1e9
@@ -529,6 +600,10 @@ def main():
                    "steps": min(K, 32), "workload": WORKLOAD64, "launches_per_step": b["launches_per_step"], "kernel_shares": b["kernel_shares"],
                    "roofline": {"bound": "hbm", "achieved": bg, "peak": peak_gbs, "unit": "GB/s", "frac": bg / peak_gbs, "traffic": None,
                                 "algorithmic_bytes_per_step": bb, "note": "whole step; expert bytes are the expectation for uniform routing"}}
+    prefill = None
+    if not args.no_prefill and args.layers == 40:
+        torch.cuda.empty_cache()
+        prefill = measure_prefill(Q, torch, args.layers)
     if rank == 0:
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -541,11 +616,11 @@ def main():
                        "step_algorithmic_bytes": step_bytes, "step_achieved_gbs": step_gbs,
                        "step_frac_of_measured_hbm": step_gbs / peak_gbs, "step_frac_of_nominal_8tbs": step_gbs / 8000.0,
                        "assembly": "one-kernel decode step (cooperative launch, weight ring, flag-in-data exchange)" if persistent else "kernel-per-phase (CUDA graph + programmatic dependent launch)",
-                       "device_vs_e2e_tokens_identical": identical, "kernel_shares": shares},
+                       "device_vs_e2e_tokens_identical": identical, "kernel_shares": shares, "step_timeline": timeline},
             "clocks": clocks,
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
             "gpu_launches": int((launches_per_step or 0) * K),
-            "roofline": roofline, "cpu_baseline": cpu, "batch64_1gpu": batch64,
+            "roofline": roofline, "cpu_baseline": cpu, "batch64_1gpu": batch64, "prefill": prefill,
         }
         print(json.dumps(line), flush=True)
 

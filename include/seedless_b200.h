@@ -60,7 +60,18 @@ typedef struct sl_config {
     int32_t max_streams;     /* stream slots (each holds GDN state + a KV page table) */
     int32_t kv_page_size;    /* positions per KV page (multiple of 32) */
     int32_t kv_pages;        /* pages in the engine's KV arena, shared by all streams */
+    int32_t flags;           /* SL_FLAG_* bits, 0 = defaults (how the step is assembled; results do not depend on them) */
 } sl_config;
+
+/* sl_config.flags: assembly switches for measurements and debugging.  Every combination gives the same tokens. */
+enum {
+    SL_FLAG_NO_GRAPH = 1,          /* launch every kernel of a decode step eagerly instead of replaying a CUDA graph */
+    SL_FLAG_NO_PDL = 2,            /* no programmatic dependent launch between the kernels of a step */
+    SL_FLAG_STEP_KERNEL = 4,       /* single-stream decode steps as ONE cooperative kernel launch (see sl_engine_use_persistent) */
+    SL_FLAG_SPLIT_EXPERTS = 8,     /* batch-1 decode: gate/up and down as two launches instead of the fused expert kernel */
+    SL_FLAG_ROUTE_IN_ROUTER = 16,  /* batch-1 decode: the router kernel's last CTA routes (instead of every CTA of the expert kernel) */
+    SL_FLAG_L2_PREFETCH = 32       /* kernels prefetch the weights of later kernels into L2 (slower as measured; kept for comparison) */
+};
 
 /* One named tensor handed to sl_engine_create.  Names: "embed", "final_norm", "lm_head.w/.s/.b",
  * "L<i>.in_norm", "L<i>.post_norm", "L<i>.gdn.in_proj_qkv.w/.s/.b" (also _z,_b,_a),
@@ -127,7 +138,7 @@ int32_t sl_engine_use_graphs(sl_engine* e, int32_t on);
  * that serves every other call (the default: it is the faster one on B200 as measured), or as ONE cooperative
  * kernel launch per token when the geometry and the device allow it.  Both produce the same tokens and leave the
  * same caches.  on = 0 / 1 selects; on < 0 only queries.  Returns 1 when the one-kernel step is available
- * (query: and selected), 0 otherwise.  The environment variable SEEDLESS_PERSISTENT=1 selects it at creation. */
+ * (query: and selected), 0 otherwise.  SL_FLAG_STEP_KERNEL in sl_config.flags selects it at creation. */
 int32_t sl_engine_use_persistent(sl_engine* e, int32_t on);
 /* Profiling of the one-kernel step: on = 1 arms a timeline (returns the number of CTAs); every following step
  * overwrites it with nanosecond stamps of each CTA's phase boundaries, [CTA][layer + 1][24] uint32 relative to the

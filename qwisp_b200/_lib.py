@@ -19,6 +19,9 @@ class SeedlessError(RuntimeError):
         super().__init__(msg)
 
 
+SL_FLAG_NO_GRAPH, SL_FLAG_NO_PDL, SL_FLAG_STEP_KERNEL, SL_FLAG_SPLIT_EXPERTS, SL_FLAG_ROUTE_IN_ROUTER, SL_FLAG_L2_PREFETCH = 1, 2, 4, 8, 16, 32
+
+
 class SlConfig(C.Structure):
     _fields_ = [
         ("hidden", C.c_int32), ("n_layers", C.c_int32), ("attn_every", C.c_int32), ("vocab", C.c_int32),
@@ -27,6 +30,7 @@ class SlConfig(C.Structure):
         ("attn_heads", C.c_int32), ("attn_kv_heads", C.c_int32),
         ("rope_theta", C.c_float), ("rms_eps", C.c_float),
         ("max_rows", C.c_int32), ("max_streams", C.c_int32), ("kv_page_size", C.c_int32), ("kv_pages", C.c_int32),
+        ("flags", C.c_int32),
     ]
 
 
@@ -123,10 +127,10 @@ def lib():
 
 def config(hidden=2048, n_layers=40, attn_every=4, vocab=151936, n_experts=256, top_k=8, moe_inter=512,
            gdn_k_heads=16, gdn_v_heads=32, attn_heads=16, attn_kv_heads=2, rope_theta=1e7, rms_eps=1e-6,
-           max_rows=64, max_streams=4, kv_page_size=64, kv_pages=256):
+           max_rows=64, max_streams=4, kv_page_size=64, kv_pages=256, flags=0):
     """Geometry of the synthetic 35B-A3B-shaped model by default."""
     return SlConfig(hidden, n_layers, attn_every, vocab, n_experts, top_k, moe_inter, gdn_k_heads, gdn_v_heads,
-                    attn_heads, attn_kv_heads, rope_theta, rms_eps, max_rows, max_streams, kv_page_size, kv_pages)
+                    attn_heads, attn_kv_heads, rope_theta, rms_eps, max_rows, max_streams, kv_page_size, kv_pages, flags)
 
 
 def synth_spec(seed=0, norm_jitter=0.0, conv_std=0.02):

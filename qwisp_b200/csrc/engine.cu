@@ -68,8 +68,8 @@ struct sl_engine {
     int *pidx = nullptr, *out_tok = nullptr, *tok_in = nullptr, *hist = nullptr, *hist_pos = nullptr;
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
     unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; unsigned* err_host = nullptr; float* adj_buf = nullptr; int* samp_buf = nullptr; unsigned* slot_sync = nullptr; unsigned* router_groups = nullptr;
-    bool use_route_in_experts = true;   // with the fused kernel: routing done by its CTAs (SEEDLESS_ROUTE_IN_EXPERTS=0: by the router's last CTA)
-    bool use_fused_experts = true;  // batch-1 decode: gate/up + down in one launch (SEEDLESS_FUSED_EXPERTS=0 turns it off)
+    bool use_route_in_experts = true;   // with the fused kernel: routing done by its CTAs (SL_FLAG_ROUTE_IN_ROUTER: by the router's last CTA)
+    bool use_fused_experts = true;  // batch-1 decode: gate/up + down in one launch (SL_FLAG_SPLIT_EXPERTS turns it off)
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
     int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
     bool ep_step = false;
@@ -92,12 +92,12 @@ struct sl_engine {
     std::map<int, int> graph_kernels;   // kernels inside each captured step (so replays are counted too)
     std::map<int, int> eager_runs;
     bool use_graph = true;
-    bool use_prefetch = false;      // L2 prefetch of the weights later kernels read (SEEDLESS_PREFETCH=1); slower now that
+    bool use_prefetch = false;      // L2 prefetch of the weights later kernels read (SL_FLAG_L2_PREFETCH); slower now that
                                     // every kernel starts its own weight copies ahead of the launch wait
-    bool use_pdl = true;            // programmatic dependent launch between the kernels of a step (SEEDLESS_PDL=0 turns it off)
+    bool use_pdl = true;            // programmatic dependent launch between the kernels of a step (SL_FLAG_NO_PDL turns it off)
     // the one-kernel decode step (step_persistent.cu): used for single-stream decode steps when the geometry fits
     // Off by default: measured on B200 it is the slower of the two assemblies (its six all-to-all activation exchanges
-    // per layer cost more than the kernel boundaries they replace); SEEDLESS_PERSISTENT=1 / sl_engine_use_persistent(e, 1) selects it
+    // per layer cost more than the kernel boundaries they replace); SL_FLAG_STEP_KERNEL / sl_engine_use_persistent(e, 1) selects it
     bool ps_ok = false, use_persistent = false;
     PStepArgs ps{};
     uint32_t* ps_timeline = nullptr;
@@ -282,7 +282,7 @@ int32_t build_runtime(sl_engine* e) {
     size_t prow = (size_t)R * e->topk + R;
     if ((rc = dalloc(e, &e->h, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->p, (size_t)R * H))) return rc;
-    if ((rc = dalloc(e, &e->normed, (size_t)R * H))) return rc;
+    if ((rc = dalloc(e, &e->normed, (size_t)R * (e->valDim > H ? e->valDim : H)))) return rc;   // also the gated-norm rows of prefill mode
     if ((rc = dalloc(e, &e->opx, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->opy, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->inproj, (size_t)R * in_w))) return rc;
@@ -354,14 +354,12 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->kv_pool, (size_t)c.kv_pages * page_elems))) return rc;
     for (int i = c.kv_pages - 1; i >= 0; --i) e->free_pages.push_back(i);
     for (int i = S - 1; i >= 0; --i) e->free_slots.push_back(i);
-    { const char* re = getenv("SEEDLESS_ROUTE_IN_EXPERTS"); if (re) e->use_route_in_experts = (re[0] == '1'); }
-    { const char* fe = getenv("SEEDLESS_FUSED_EXPERTS"); if (fe) e->use_fused_experts = (fe[0] == '1'); }
-    const char* pfe = getenv("SEEDLESS_PREFETCH");
-    if (pfe) e->use_prefetch = (pfe[0] == '1');
-    const char* pd = getenv("SEEDLESS_PDL");
-    if (pd) e->use_pdl = (pd[0] == '1');
-    const char* ng = getenv("SEEDLESS_NO_GRAPH");
-    if (ng && ng[0] == '1') e->use_graph = false;
+    // assembly switches come with the configuration (sl_config.flags), not from the environment
+    e->use_route_in_experts = !(c.flags & SL_FLAG_ROUTE_IN_ROUTER);
+    e->use_fused_experts = !(c.flags & SL_FLAG_SPLIT_EXPERTS);
+    e->use_prefetch = (c.flags & SL_FLAG_L2_PREFETCH) != 0;
+    e->use_pdl = !(c.flags & SL_FLAG_NO_PDL);
+    e->use_graph = !(c.flags & SL_FLAG_NO_GRAPH);
     return SL_OK;
 }
 
@@ -447,7 +445,7 @@ int32_t setup_persistent(sl_engine* e) {
     const unsigned init[4] = {1u, 0u, 0u, 0u};
     CU(e, cudaMemcpy(words, init, sizeof(init), cudaMemcpyHostToDevice));
     a.step_seq = words; a.abort_flag = words + 1; a.err = e->err_flag;
-    { const char* v = getenv("SEEDLESS_PERSISTENT"); if (v) e->use_persistent = (v[0] == '1'); }
+    e->use_persistent = (c.flags & SL_FLAG_STEP_KERNEL) != 0;
     e->ps_ok = true;
     return SL_OK;
 }
@@ -566,7 +564,7 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
     launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, d, st, e->use_pdl);
     DenseArgs o{};
     o.err = e->err_flag; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
-    o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H; o.tc = e->hybrid;
+    o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H; o.tc = e->hybrid; o.norm_scratch = e->normed;
     if (e->use_prefetch) {
         o.pf.p[0] = L.router; o.pf.bytes[0] = (unsigned)((size_t)e->E * e->H * 2);
         pf_q4(o.pf, 1, L.r_sh_gu);
@@ -1401,7 +1399,7 @@ int32_t sl_op_lm_head_argmax_static(const void* x_dev, const void* wr_dev, const
 int32_t sl_op_qmm4_tc_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
                              int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream) {
     if (!x_dev || !wr_dev || !sr_dev || !y_dev) return SL_ERR_INVALID;
-    if (M <= 0 || N <= 0 || K <= 0 || N % 128 || !k_ok(K)) return SL_ERR_INVALID;
+    if (M <= 0 || N <= 0 || K <= 0 || N % 16 || !k_ok(K)) return SL_ERR_INVALID;
     if (!device_ok()) return SL_ERR_NO_DEVICE;
     Q4R q{}; q.wr = (const uint4*)wr_dev; q.sr = (const uint4*)sr_dev; q.tiles = N / 16; q.K = K;
     int err = launch_gemm_tc(q, N, K, M, (const __half*)x_dev, K, (__half*)y_dev, N, false, nullptr, (cudaStream_t)cuda_stream);

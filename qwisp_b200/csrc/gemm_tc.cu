@@ -1,33 +1,31 @@
-// gemm_tc.cu -- 4-bit group-64 GEMM for many activation rows ("F2": prefill chunks, large batches)
-// on the 5th-generation tensor cores: tcgen05.mma (kind::f16) issued by one thread, operands in
-// shared memory described by matrix descriptors, the accumulator in tensor memory (TMEM), read
-// back with tcgen05.ld for the per-group scale/bias epilogue.
+// gemm_tc.cu -- 4-bit group-64 GEMM for many activation rows ("F2": prefill chunks) on the 5th-generation
+// tensor cores: tcgen05.mma (kind::f16) issued by one thread, operands in shared memory described by matrix
+// descriptors, the accumulator in tensor memory (TMEM), read back once with tcgen05.ld.
 //
-//   y[t, n] (+)= sum_g ( scale[n,g] * sum_{k in g} q[n,k] x[t,k]  +  bias[n,g] * sum_{k in g} x[t,k] )
+//   y[t, n] (+)= sum_k x[t, k] * fp16(scale[n, k/64] * q[n, k] + bias[n, k/64])
 //
-// the same algebra as the GEMV family (gemv.cuh; reference SeedlessMetalForward.swift:249-258):
-// the tensor core multiplies the exact 4-bit integers q (as fp16) with the fp16 activations and
-// accumulates one group of 64 inputs in f32; the group's scale and bias are applied on CUDA cores.
+// Prefill-mode numerics: every weight is dequantised to fp16 with one rounding (the dequantised-weight GEMM of the
+// reference's batched / prefill path, swift/Sources/QwispCore/SeedlessMetalForward.swift:160-185), so the whole K
+// range accumulates in ONE f32 accumulator in TMEM and the epilogue runs once.  Like the reference's hybrid prefill
+// this is not bit-identical to the GEMV family, but every token column is independent of the others and K is walked in
+// a fixed order, so results do not depend on how many rows share a call or on how a prompt is cut into calls.
 //
-// A CTA of 128 threads owns 128 weight rows (8 tiles of the fragment-major layout) and a pass of
-// 32 activation rows.  Per group of 64 inputs:
-//   1. every thread dequantises two fragment registers (16 nibbles of two weight rows) into the
-//      A stage: K-major, no swizzle, core matrices of 8 rows x 16 bytes; 8 halves of a 16-byte
-//      chunk keep the pair order (0,4,1,5,2,6,3,7) the one-logic-op dequantiser produces, and the
-//      B stage stores the activations of each chunk in the same order, so no permutation is spent;
-//   2. fence.proxy.async + barrier; one thread issues four MMAs (M=128, N=32, K=16 each) into
-//      32 TMEM columns and commits them to an mbarrier;
-//   3. all threads wait (bounded), load their row of the accumulator (tcgen05.ld 32x32b.x32:
-//      thread i of the CTA <-> TMEM lane i <-> weight row i) and fold it into f32 registers.
-// Nothing overlaps inside a CTA; several CTAs per SM (20 KB of shared memory, 32 TMEM columns
-// each) overlap one another's phases.
+// A CTA of 128 threads owns 128 weight rows (8 tiles of the fragment-major layout) and NT activation rows (64 or 256).
+// Two shared-memory stages alternate over the K groups of 64 inputs:
+//   fill   every thread dequantises two fragment registers (16 nibbles of two weight rows, scale and bias applied with
+//          one fp16x2 multiply-add per pair) into the A stage -- K-major, no swizzle, core matrices of 8 rows x 16 bytes,
+//          the 8 halves of a chunk in the pair order (0,4,1,5,2,6,3,7) the one-logic-op dequantiser produces -- and
+//          copies NT x 64 activations into the B stage in the same order, so no permutation is spent;
+//   issue  fence.proxy.async + barrier; one thread issues four MMAs (M=128, N=NT, K=16) that accumulate into the NT
+//          TMEM columns and commits them to the stage's mbarrier; the CTA goes straight on to fill the other stage,
+//          waiting (bounded) on a stage's mbarrier only before it overwrites it.
+// Two CTAs fit a multiprocessor (96 KB of shared memory, 256 TMEM columns each), so one CTA's fill overlaps the other's MMAs.
 #include "kernels.h"
 #include "gemv.cuh"
 
 namespace sl {
 
 constexpr int TC_ROWS = 128;      // weight rows per CTA (UMMA M)
-constexpr int TC_NT = 32;         // activation rows per pass (UMMA N)
 
 __device__ __forceinline__ uint64_t umma_desc_kmajor(const void* smem_ptr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     // shared-memory matrix descriptor: start address, leading (K-chunk) and stride (8-row group)
@@ -64,118 +62,143 @@ struct GemmTcArgs {
     unsigned* err;
 };
 
+template <int NT>
 __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
-    __shared__ __align__(128) unsigned char sA[8 * TC_ROWS * 16];      // [k-chunk][row][16 B]
-    __shared__ __align__(128) unsigned char sB[8 * TC_NT * 16];        // [k-chunk][token][16 B]
-    __shared__ float s_part[TC_NT][8];                                  // per token, per chunk: sum of 8 activations
-    __shared__ float s_sx[TC_NT];
-    __shared__ __align__(8) uint64_t s_bar;
+    extern __shared__ __align__(128) unsigned char smem[];              // 2 stages x [A: 8 chunks x 128 rows x 16 B][B: 8 chunks x NT tokens x 16 B]
+    constexpr int A_BYTES = 8 * TC_ROWS * 16, B_BYTES = 8 * NT * 16, STAGE = A_BYTES + B_BYTES;
+    __shared__ __align__(8) uint64_t s_bar[2];
     __shared__ uint32_t s_tmem;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row0 = blockIdx.x * TC_ROWS, t0 = blockIdx.y * TC_NT;
-    const int nt = min(TC_NT, a.M - t0);
+    const int row0 = blockIdx.x * TC_ROWS, t0 = blockIdx.y * NT;
+    const int nt = min(NT, a.M - t0);
     const int G = a.K >> 6, GP = G >> 1;
-    if (tid == 0) { mbar_init(&s_bar, 1); mbar_fence_init(); }
+    const int ntiles = a.N >> 4;
+    if (tid == 0) { mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1); mbar_fence_init(); }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"(32u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"((uint32_t)NT) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = s_tmem;
-    const uint32_t idesc = (1u << 4) | ((uint32_t)(TC_NT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);   // f32 accumulate, f16 x f16, K-major both
-    // this thread's weight row for the epilogue: row i of the CTA = tile i/16, fragment row (i%16)%8, B half (i%16)/8
-    const int etile = (row0 >> 4) + (tid >> 4), er = tid & 7, eb = (tid >> 3) & 1;
-    const __half* srow = reinterpret_cast<const __half*>(a.q.sr) + ((size_t)etile * GP * 8 + er) * 8 + eb * 2;   // + (g/2)*64 + (g&1)*4
-    float accS[TC_NT], accB[TC_NT];
-#pragma unroll
-    for (int n = 0; n < TC_NT; ++n) { accS[n] = 0.f; accB[n] = 0.f; }
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);   // f32 accumulate, f16 x f16, K-major both
     bool failed = false;
     for (int g = 0; g < G; ++g) {
-        // ---- 1. A stage: two fragment registers per thread (tiles warp and warp+4 of the CTA's 8) ----
+        const int s = g & 1, use = g >> 1;
+        unsigned char* sA = smem + (size_t)s * STAGE;
+        unsigned char* sB = sA + A_BYTES;
+        // the MMAs that read this stage two groups ago must be done before it is overwritten
+        if (use > 0 && !mbar_wait_bounded(&s_bar[s], (uint32_t)((use - 1) & 1))) failed = true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // ---- A stage: two fragment registers per thread (tiles warp and warp+4 of the CTA's 8), dequantised to fp16 weights ----
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int tl = warp + 4 * h;                                   // tile inside the CTA
-            const size_t T = (size_t)(row0 >> 4) + tl;
-            const uint4 wv = ldg_nc_u4(a.q.wr + (T * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
+            const int T = (row0 >> 4) + tl;
             const int r = lane >> 2, t = lane & 3;
-            uint32_t d[4];
             unsigned char* pa = sA + (size_t)(2 * t) * (TC_ROWS * 16) + (size_t)(tl * 16 + r) * 16;
-            dequant8(wv.x, d); *reinterpret_cast<uint4*>(pa) = make_uint4(d[0], d[1], d[2], d[3]);
-            dequant8(wv.y, d); *reinterpret_cast<uint4*>(pa + TC_ROWS * 16) = make_uint4(d[0], d[1], d[2], d[3]);
-            dequant8(wv.z, d); *reinterpret_cast<uint4*>(pa + 8 * 16) = make_uint4(d[0], d[1], d[2], d[3]);
-            dequant8(wv.w, d); *reinterpret_cast<uint4*>(pa + TC_ROWS * 16 + 8 * 16) = make_uint4(d[0], d[1], d[2], d[3]);
-        }
-        // ---- B stage: 32 tokens x 8 chunks, two chunks per thread; chunk sums for the bias term ----
+            uint4 o[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            if (T < ntiles) {                                              // (the last CTA of a matrix whose rows are not a multiple of 128)
+                const uint4 wv = ldg_nc_u4(a.q.wr + ((size_t)T * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
+                const uint4 sv = ldg_nc_u4(a.q.sr + ((size_t)T * GP + (g >> 1)) * 8 + r);
+                const uint32_t sa = (g & 1) ? sv.z : sv.x, sb = (g & 1) ? sv.w : sv.y;         // (scale, bias) of rows A_r and B_r
+                const __half2 hA = *reinterpret_cast<const __half2*>(&sa), hB = *reinterpret_cast<const __half2*>(&sb);
+                const __half2 sA2 = __half2half2(__low2half(hA)), bA2 = __half2half2(__high2half(hA));
+                const __half2 sB2 = __half2half2(__low2half(hB)), bB2 = __half2half2(__high2half(hB));
+                const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+                for (int wi = 0; wi < 4; ++wi) {
+                    uint32_t d[4];
+                    dequant8(words[wi], d);
+                    const __half2 sc = (wi < 2) ? sA2 : sB2, bi = (wi < 2) ? bA2 : bB2;
+                    uint32_t* ow = reinterpret_cast<uint32_t*>(&o[wi]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const __half2 wq = __hfma2(*reinterpret_cast<const __half2*>(&d[j]), sc, bi);
+                        ow[j] = *reinterpret_cast<const uint32_t*>(&wq);
+                    }
+                }
+            }
+            *reinterpret_cast<uint4*>(pa) = o[0];
+            *reinterpret_cast<uint4*>(pa + TC_ROWS * 16) = o[1];
+            *reinterpret_cast<uint4*>(pa + 8 * 16) = o[2];
+            *reinterpret_cast<uint4*>(pa + TC_ROWS * 16 + 8 * 16) = o[3];
+        }
+        // ---- B stage: NT tokens x 8 chunks of 8 activations ----
+#pragma unroll 4
+        for (int h = 0; h < NT * 8 / 128; ++h) {
             const int idx = tid + 128 * h, n = idx >> 3, c = idx & 7;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (n < nt) v = __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + n) * a.ldx + g * 64 + c * 8));
-            s_part[n][c] = sum8_f32(v);
             uint4 o;
             o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
             o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
-            *reinterpret_cast<uint4*>(sB + (size_t)c * (TC_NT * 16) + (size_t)n * 16) = o;
+            *reinterpret_cast<uint4*>(sB + (size_t)c * (NT * 16) + (size_t)n * 16) = o;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        // ---- 2. four MMAs of K = 16 (two 16-byte chunks each) into the 32 accumulator columns ----
+        // ---- four MMAs of K = 16 (two 16-byte chunks each) accumulating into the NT columns ----
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
                 const uint64_t da = umma_desc_kmajor(sA + (size_t)ks * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128);
-                const uint64_t db = umma_desc_kmajor(sB + (size_t)ks * 2 * (TC_NT * 16), TC_NT * 16, 128);
-                umma_f16(tmem_base, da, db, idesc, ks > 0 ? 1u : 0u);
+                const uint64_t db = umma_desc_kmajor(sB + (size_t)ks * 2 * (NT * 16), NT * 16, 128);
+                umma_f16(tmem_base, da, db, idesc, (g > 0 || ks > 0) ? 1u : 0u);
             }
-            umma_commit(&s_bar);
+            umma_commit(&s_bar[s]);
         }
-        if (tid < TC_NT) {      // the group sum of token tid, in the order the GEMV path adds its eight chunk sums
-            const float* p = s_part[tid];
-            s_sx[tid] = ((p[0] + p[4]) + (p[2] + p[6])) + ((p[1] + p[5]) + (p[3] + p[7]));
-        }
-        // ---- 3. accumulator row of this thread ----
-        if (!mbar_wait_bounded(&s_bar, (uint32_t)(g & 1))) failed = true;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        failed = __syncthreads_or(failed ? 1 : 0) != 0;                    // s_sx visible; everyone past the wait; one verdict for the CTA
-        if (failed) break;
-        uint32_t dreg[32];
-        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16), dreg);
-        const __half2 sb = *reinterpret_cast<const __half2*>(srow + (size_t)(g >> 1) * 64 + (g & 1) * 4);
-        const float2 f = __half22float2(sb);                               // (scale, bias) of this row and group
-#pragma unroll
-        for (int n = 0; n < TC_NT; ++n) {
-            accS[n] = fmaf(f.x, __uint_as_float(dreg[n]), accS[n]);
-            accB[n] = fmaf(f.y, s_sx[n], accB[n]);
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();                                                   // the stages and the accumulator may be overwritten
     }
+    // the last commit covers every MMA issued before it
+    if (!mbar_wait_bounded(&s_bar[(G - 1) & 1], (uint32_t)(((G - 1) >> 1) & 1))) failed = true;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    failed = __syncthreads_or(failed ? 1 : 0) != 0;
     if (failed && a.err && tid == 0) atomicOr(a.err, 1u);
     if (!failed) {
         const int row = row0 + tid;
+        for (int c0 = 0; c0 < NT; c0 += 32) {
+            if (c0 >= nt) break;
+            uint32_t dreg[32];
+            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, dreg);
+            if (row < a.N) {
 #pragma unroll
-        for (int n = 0; n < TC_NT; ++n) {
-            if (n < nt) {
-                const size_t idx = (size_t)(t0 + n) * a.ldy + row;
-                __half val = f2h(accS[n] + accB[n]);
-                if (a.add_to_y) val = hadd_rn(a.y[idx], val);
-                a.y[idx] = val;
+                for (int n = 0; n < 32; ++n) {
+                    if (c0 + n < nt) {
+                        const size_t idx = (size_t)(t0 + c0 + n) * a.ldy + row;
+                        __half val = f2h(__uint_as_float(dreg[n]));
+                        if (a.add_to_y) val = hadd_rn(a.y[idx], val);
+                        a.y[idx] = val;
+                    }
+                }
             }
         }
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(32u) : "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)NT) : "memory");
+}
+
+template <int NT>
+static int launch_gemm_tc_t(const GemmTcArgs& a, cudaStream_t st) {
+    constexpr size_t smem = 2 * (8 * TC_ROWS * 16 + 8 * NT * 16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t err = cudaFuncSetAttribute(k_gemm_umma<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return (int)err;
+        configured = true;
+    }
+    dim3 grid((unsigned)((a.N + TC_ROWS - 1) / TC_ROWS), (unsigned)((a.M + NT - 1) / NT));
+    k_gemm_umma<NT><<<grid, 128, smem, st>>>(a);
+    return (int)cudaGetLastError();
 }
 
 int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, __half* y, int ldy, bool add_to_y, unsigned* err, cudaStream_t st) {
-    if (N % TC_ROWS || K % 256) return -1;
+    if (N % 16 || K % 256) return -1;
     GemmTcArgs a{q, N, K, M, x, ldx, y, ldy, add_to_y ? 1 : 0, err};
-    dim3 grid((unsigned)(N / TC_ROWS), (unsigned)((M + TC_NT - 1) / TC_NT));
-    k_gemm_umma<<<grid, 128, 0, st>>>(a);
-    return (int)cudaGetLastError();
+    // the token tile is a scheduling choice only: a token's column never interacts with another's
+    return M <= 64 ? launch_gemm_tc_t<64>(a, st) : launch_gemm_tc_t<256>(a, st);
 }
 
 }  // namespace sl

@@ -85,9 +85,7 @@ static void set_pdl(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, bool pdl
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
 }
-// NW warps per CTA (8 or 16), UPW units per warp; the CTA's NW*UPW units arrive in rounds of 16.
-// Eight warps leave room for a second CTA on the SM (registers), so the next kernel's CTAs can
-// become resident, start their weight copies and stage while this one computes.
+// NW warps per CTA, UPW units per warp; the CTA's NW*UPW units arrive in rounds of 16.
 template <int PRO, int EPI, int NW, int UPW>
 __global__ void __launch_bounds__(NW * 32, NW == 8 ? 2 : 1) k_gemv(DenseArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -173,7 +171,8 @@ static void launch_gemv_t(const DenseArgs& a, const GemvPlan& pl, cudaStream_t s
     cudaLaunchAttribute attr[1];
     set_pdl(cfg, attr, pdl);
     DenseArgs copy = a; copy.lg_slices = pl.lg_slices;
-    ProfScope ps("k_gemv", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
+    // profiling tag by role: the in-projection form stores its rows, the out-projection form adds the residual
+    ProfScope ps(EPI == EPI_RESID ? "k_gemv_outproj" : "k_gemv_inproj", (double)a.N * a.K * 0.5625 + (double)a.M * (a.K + a.N) * 2, st);
     cudaLaunchKernelEx(&cfg, k_gemv<PRO, EPI, NW, UPW>, copy);
     COUNT_LAUNCH();
 }
@@ -344,6 +343,28 @@ int launch_head_static(const DenseArgs& in, cudaStream_t st) {
     return (int)cudaGetLastError();
 }
 
+// Gated RMSNorm of the GDN out-projection as a row kernel (prefill mode): one warp per 256 inputs (two heads of
+// 128) of one row, the arithmetic of the GEMV prologue (normgate8); out is dense [M][K].
+template <int PRO>
+__global__ void __launch_bounds__(256) k_normgate_rows(const __half* y, int ldy, const __half* z, int ldz, const __half* nw, const float* nw32,
+                                                       float eps, int M, int K, __half* out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, chunks = K >> 8;
+    const long u = (long)blockIdx.x * 8 + warp;
+    if (u >= (long)M * chunks) return;
+    const int row = (int)(u / chunks), k0 = ((int)(u % chunks) << 8) + lane * 8;
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(y + (size_t)row * ldy + k0));
+    const uint4 zv = __ldcg(reinterpret_cast<const uint4*>(z + (size_t)row * ldz + k0));
+    const uint4 wv = *reinterpret_cast<const uint4*>(nw + (k0 & 127));
+    *reinterpret_cast<uint4*>(out + (size_t)row * K + k0) = normgate8<PRO>(v, zv, wv, nw32, k0, eps);
+}
+static void launch_normgate_rows(int pro, const DenseArgs& a, cudaStream_t st) {
+    ProfScope ps("k_normgate_rows", (double)a.M * a.K * 6, st);
+    const unsigned grid = (unsigned)(((long)a.M * (a.K >> 8) + 7) / 8);
+    if (pro == PRO_NORMGATE32) k_normgate_rows<PRO_NORMGATE32><<<grid, 256, 0, st>>>(a.x, a.ldx, a.z, a.ldz, a.nw, a.nw32, a.eps, a.M, a.K, a.norm_scratch);
+    else k_normgate_rows<PRO_NORMGATE><<<grid, 256, 0, st>>>(a.x, a.ldx, a.z, a.ldz, a.nw, a.nw32, a.eps, a.M, a.K, a.norm_scratch);
+    COUNT_LAUNCH();
+}
+
 void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pdl) {
     if (epi == EPI_ARGMAX) {
         if (pro == PRO_RMSNORM) { launch_head_t<PRO_RMSNORM>(a, st, pdl); return; }
@@ -352,14 +373,17 @@ void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pd
     // Prefill mode (a.tc, chosen by the caller per CALL, never by the number of rows): the tcgen05
     // tensor-core GEMM, with the RMSNorm done by a row kernel first.  Every row's result there is
     // independent of how many rows share the call, so a prompt split into chunks in any way gives the
-    // same bits.  The gated norm of the GDN out-projection, and every call outside prefill mode, use
-    // the GEMV family, which walks the rows in passes of 8.
-    if (a.tc && a.N % 128 == 0 && a.K % 256 == 0 && (epi == EPI_STORE || epi == EPI_RESID) &&
-        (pro == PRO_PLAIN || (pro == PRO_RMSNORM && a.norm_scratch))) {
+    // same bits; the gated norm of the GDN out-projection runs as a row kernel too.  Every call outside
+    // prefill mode uses the GEMV family, which walks the rows in passes of 8.
+    if (a.tc && a.N % 16 == 0 && a.K % 256 == 0 && (epi == EPI_STORE || epi == EPI_RESID) &&
+        (pro == PRO_PLAIN || a.norm_scratch)) {
         const __half* x = a.x; int ldx = a.ldx;
         if (pro == PRO_RMSNORM) {
             if (a.ldx != a.K) goto gemv_path;                  // the row kernel reads dense rows
             launch_final_norm(a.x, a.nw, a.eps, a.M, a.K, a.norm_scratch, st);
+            x = a.norm_scratch; ldx = a.K;
+        } else if (pro_is_normgate(pro)) {
+            launch_normgate_rows(pro, a, st);
             x = a.norm_scratch; ldx = a.K;
         }
         {
@@ -371,16 +395,9 @@ void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pd
     }
 gemv_path:
     const GemvPlan pl = gemv_plan(a.K, epi == EPI_SWIGLU ? a.N / 8 : a.N / 16, 1, sm_count());
-    // eight-warp CTAs (same units per CTA, twice the units per warp) when a warp's slice stays fixed with a stride of 8
-    static int narrow_env = -1;
-    if (narrow_env < 0) { const char* v = getenv("SEEDLESS_GEMV_WARPS"); narrow_env = (v && atoi(v) == 8) ? 1 : 0; }   // measured equal to 16 warps; off unless asked for
-    const bool narrow = narrow_env && (a.K >> 8) <= 8 && a.M <= ROWS_PER_PASS;
 #define SL_CASE(P, E)                                                                                       \
     if (pro == P && epi == E) {                                                                             \
-        if (narrow && pl.upw == 1) launch_gemv_t<P, E, 8, 2>(a, pl, st, pdl);                               \
-        else if (narrow && pl.upw == 2) launch_gemv_t<P, E, 8, 4>(a, pl, st, pdl);                          \
-        else if (narrow) launch_gemv_t<P, E, 8, 6>(a, pl, st, pdl);                                         \
-        else if (pl.upw == 1) launch_gemv_t<P, E, 16, 1>(a, pl, st, pdl);                                   \
+        if (pl.upw == 1) launch_gemv_t<P, E, 16, 1>(a, pl, st, pdl);                                        \
         else if (pl.upw == 2) launch_gemv_t<P, E, 16, 2>(a, pl, st, pdl);                                   \
         else launch_gemv_t<P, E, 16, 3>(a, pl, st, pdl);                                                    \
         return;                                                                                             \
@@ -1065,159 +1082,6 @@ __global__ void __launch_bounds__(512, 1) k_expert_fused(ExpertArgs a) {
         else a.out[ncol] = res;
     }
 }
-// ---- variant: the down phase gives every CTA whole output tiles ----
-// After the gate/up phase ALL CTAs meet (one counter), then CTA c < H/16 computes output tile c of the
-// down projection for every slot (the routed experts and the shared one: top_k + 1 small weight pieces,
-// requested by the routing warp at the start) and combines them itself: no per-slot output buffer, no
-// completion ticket, no last-CTA tail.  Needs the routing inside the kernel (route_here).
-template <int UG>
-__global__ void __launch_bounds__(512, 1) k_expert_fused2(ExpertArgs a) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = lane >> 2, t = lane & 3;
-    const int lg1 = a.lg_slices;
-    const int sl1 = a.H >> 8, sl2 = a.I >> 8;
-    const int TPC1 = (16 * UG) >> lg1;
-    const int nt1 = a.I / 8, nt2 = a.H / 16;
-    const int nslots = a.topk + 1, U2 = nslots * sl2;            // down-phase units of a CTA: (slot, slice), <= 32
-    WStage ws1, ws2; XStage st; float* red; float* fin; int* misc;
-    unsigned char* p = GemvSmem::carve_w(smem, 16 * UG, ws1);
-    p = GemvSmem::carve_w(p, 32, ws2);
-    GemvSmem::carve(p, 1, a.H, 32, TPC1, st, red, fin, misc);
-    __half* xs2 = reinterpret_cast<__half*>(misc + 32);          // [nslots][I + 8]
-    float* sxs2 = reinterpret_cast<float*>(xs2 + (size_t)nslots * (a.I + 8));   // [nslots][I/64][8]
-    const int nvu1 = min(TPC1, nt1 - (int)blockIdx.x * TPC1) << lg1;
-    const int y = blockIdx.y;
-    const int c = y * gridDim.x + blockIdx.x;                    // linear CTA id = output tile of the down phase
-    const bool own = c < nt2;
-    __shared__ float s_rbuf[512 + 32];
-    __shared__ int s_inds[16];
-    __shared__ __half s_scores[16];
-    const bool shared = (y == (int)gridDim.y - 1);
-    if (threadIdx.x == 480) {
-        wstage_init(ws1, UG); wstage_init(ws2, 2);
-        if (shared) wstage_copy(ws1, a.sh_gu.wr, a.sh_gu.sr, ((size_t)blockIdx.x * TPC1) << lg1, nvu1, UG);
-    }
-    pdl_wait();
-    pdl_launch_dependents();
-    if (warp == 15) {
-        route_row_warp(a.rlogits, a.E, a.topk, s_inds, s_scores, s_rbuf, lane);
-        __syncwarp();
-        if (lane == 0) {
-            if (!shared) wstage_copy(ws1, a.gu.wr, a.gu.sr, ((size_t)s_inds[y] * nt1 + (size_t)blockIdx.x * TPC1) << lg1, nvu1, UG);
-            if (own) {
-                for (int rd = 0; rd < 2; ++rd) {
-                    const int n = min(16, U2 - 16 * rd);
-                    if (n > 0) mbar_expect_tx(ws2.bar + rd, (uint32_t)n * (2048 + 256));
-                }
-                for (int sidx = 0; sidx < nslots; ++sidx) {
-                    const bool sh = (sidx == a.topk);
-                    const Q4R& q2 = sh ? a.sh_down : a.down;
-                    const size_t T = (size_t)(sh ? 0 : s_inds[sidx]) * nt2 + c;
-                    const int u0 = sidx * sl2;
-                    bulk_g2s(ws2.w + (size_t)u0 * 128, q2.wr + T * sl2 * 128, (uint32_t)sl2 * 2048, ws2.bar + (u0 >> 4));
-                    bulk_g2s(ws2.s + (size_t)u0 * 16, q2.sr + T * sl2 * 16, (uint32_t)sl2 * 256, ws2.bar + (u0 >> 4));
-                }
-            }
-        }
-        if (blockIdx.x == 0 && y == 0 && lane < a.topk) { a.inds_out[lane] = s_inds[lane]; a.scores_out[lane] = s_scores[lane]; }
-    }
-    const int dst = shared ? a.topk : y;                       // row of hbuf
-    // ---- phase 1: gate/up + SwiGLU -> hbuf[dst] ----
-    {
-        StageSrc src{a.p, a.H, nullptr, nullptr, nullptr, 0, 0.f};
-        StageRegs sregs;
-        stage_issue<PRO_PLAIN>(sregs, src, a.shared_row0, 1, a.H);
-        stage_finish<PRO_PLAIN>(sregs, st, src, a.shared_row0, 1, a.H);
-        __syncthreads();                                       // the staged row, and the routing of the last warp
-        XRegs xr;
-        load_xregs(xr, st, warp & (sl1 - 1), r, t, 1);
-#pragma unroll 1
-        for (int i = 0; i < UG; ++i) {
-            const int u = warp + 16 * i;
-            if (u < nvu1) {
-                if (!mbar_wait_bounded(ws1.bar + i, 0) && a.err && lane == 0) atomicOr(a.err, 1u);
-                SliceRegs rg;
-                load_slice_smem(rg, ws1.w + (size_t)u * 128, ws1.s + (size_t)u * 16, lane);
-                float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
-                compute_slice_x(rg, xr, accS, accB);
-                finish_acc4(accS, accB, t, v);
-                store_partial(red, u, lane, v);
-            }
-        }
-        __syncthreads();
-        for (int j2 = threadIdx.x; j2 < TPC1 * 8; j2 += blockDim.x) {
-            int tl2 = j2 >> 3, i = j2 & 7, tile2 = blockIdx.x * TPC1 + tl2;
-            if (tile2 < nt1) {
-                __half g = f2h(tile_sum(red, tl2, sl1, i, 0)), u = f2h(tile_sum(red, tl2, sl1, i + 8, 0));
-                a.hbuf[(size_t)dst * a.I + tile2 * 8 + i] = swiglu_h(g, u);
-            }
-        }
-    }
-    // what the combine needs besides the SwiGLU rows: fetched before the meeting point
-    __half hres = f2h(0.0f), sgate = f2h(0.0f);
-    if (own && threadIdx.x < 16) {
-        if (a.resid) hres = a.resid[c * 16 + threadIdx.x];
-        sgate = sigmoid_h(a.sgl[0]);
-    }
-    // ---- all CTAs meet: every slot's SwiGLU row is complete in hbuf ----
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned* arrive = a.slot_sync;
-        unsigned* leave = a.slot_sync + 1;
-        const unsigned total = gridDim.x * gridDim.y;
-        atomicAdd(arrive, 1u);
-        bool ok = false;
-        for (int spin = 0; spin < (1 << 22); ++spin) {
-            unsigned v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(arrive) : "memory");
-            if (v >= total) { ok = true; break; }
-        }
-        if (!ok && a.err) atomicOr(a.err, 2u);
-        if (atomicAdd(leave, 1u) == total - 1) { *arrive = 0u; *leave = 0u; }   // the last one to leave resets both
-    }
-    __syncthreads();
-    if (!own) return;
-    // ---- phase 2: output tile c of the down projection for every slot, combined here ----
-    for (int u = warp; u < U2; u += 16) {                      // staging unit = (slot, 256-wide chunk)
-        const int sidx = u / sl2, ch = u - sidx * sl2, k0 = ch * 256 + lane * 8;
-        XStage ss; ss.xs = xs2 + (size_t)sidx * (a.I + 8); ss.sxs = sxs2 + (size_t)sidx * (a.I >> 6) * 8; ss.part = nullptr; ss.stride = a.I + 8;
-        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(a.hbuf + (size_t)sidx * a.I + k0));
-        store_staged(ss, 0, k0, v, lane);
-    }
-    __syncthreads();
-    for (int u = warp; u < U2; u += 16) {
-        const int sidx = u / sl2, slc = u - sidx * sl2;
-        XStage ss; ss.xs = xs2 + (size_t)sidx * (a.I + 8); ss.sxs = sxs2 + (size_t)sidx * (a.I >> 6) * 8; ss.part = nullptr; ss.stride = a.I + 8;
-        if (!mbar_wait_bounded(ws2.bar + (u >> 4), 0) && a.err && lane == 0) atomicOr(a.err, 1u);
-        SliceRegs rg;
-        load_slice_smem(rg, ws2.w + (size_t)u * 128, ws2.s + (size_t)u * 16, lane);
-        XRegs xr;
-        load_xregs(xr, ss, slc, r, t, 1);
-        float accS[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f}, v[4];
-        compute_slice_x(rg, xr, accS, accB);
-        finish_acc4(accS, accB, t, v);
-        store_partial(red, u, lane, v);
-    }
-    __syncthreads();
-    if (threadIdx.x < 16) {
-        // fp16 weighted sum in ascending k (SeedlessFusedVerify.swift:462-471), + sigmoid(gate logit) * shared
-        // (:474-484), + residual (SeedlessMetalForward.swift:1024-1028); the per-slot value is rounded to fp16
-        // first, as when it went through the output buffer
-        const int row = threadIdx.x;
-        __half acc = f2h(0.0f);
-        for (int k = 0; k < a.topk; ++k) acc = hadd_rn(acc, hmul_rn(f2h(tile_sum(red, k, sl2, row, 0)), s_scores[k]));
-        const __half res = hadd_rn(acc, hmul_rn(sgate, f2h(tile_sum(red, a.topk, sl2, row, 0))));
-        if (a.resid) a.resid[c * 16 + row] = hadd_rn(hres, res);
-        else a.out[c * 16 + row] = res;
-    }
-}
-static bool expert_fused2_ok(const ExpertArgs& a, int g1) {
-    const int sl2 = a.I >> 8;
-    return a.route_here && (a.topk + 1) * sl2 <= 32 && a.H / 16 <= g1 * (a.topk + 1);
-}
-
 bool expert_fused_applicable(const ExpertArgs& a) {
     if (a.M != 1 || a.slot_sync == nullptr || a.tile_counter == nullptr || a.topk > 16) return false;
     const GemvPlan p1 = gemv_plan(a.H, a.I / 8, a.topk + 1, sm_count()), p2 = gemv_plan(a.I, a.H / 16, a.topk + 1, sm_count());
@@ -1239,21 +1103,6 @@ bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl) {
     cudaLaunchAttribute attr[1];
     set_pdl(cfg, attr, pdl);
     ExpertArgs copy = a; copy.lg_slices = p1.lg_slices; copy.lg_slices2 = p2.lg_slices;
-    static int own_tiles = -1;
-    if (own_tiles < 0) { const char* v = getenv("SEEDLESS_EXPERT_OWN_TILES"); own_tiles = (v && v[0] == '1') ? 1 : 0; }   // measured 2% slower than the ticket form: opt-in
-    if (own_tiles && expert_fused2_ok(a, g1)) {
-        const size_t smem2 = GemvSmem::wstage_bytes(32) + GemvSmem::wstage_bytes(32) + GemvSmem::bytes(1, a.H, 32, p1.tpc) +
-                             (size_t)(a.topk + 1) * ((a.I + 8) * 2 + (a.I >> 6) * 8 * 4) + 256;
-        static bool configured2 = false;
-        if (!configured2) { cudaFuncSetAttribute(k_expert_fused2<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 215 * 1024); configured2 = true; }
-        if (smem2 <= 215 * 1024) {
-            cfg.dynamicSmemBytes = smem2;
-            ProfScope ps2("k_expert_fused", (double)(a.topk + 1) * 3.0 * a.I * a.H * 0.5625 + (double)(a.topk + 2) * (a.H + a.I) * 2, st);
-            cudaLaunchKernelEx(&cfg, k_expert_fused2<2>, copy);
-            COUNT_LAUNCH();
-            return true;
-        }
-    }
     ProfScope ps("k_expert_fused", (double)(a.topk + 1) * 3.0 * a.I * a.H * 0.5625 + (double)(a.topk + 2) * (a.H + a.I) * 2, st);
     cudaLaunchKernelEx(&cfg, k_expert_fused<2, 1>, copy);
     COUNT_LAUNCH();

@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_layout_matches_header():
     from qwisp_b200 import _lib
-    assert C.sizeof(_lib.SlConfig) == 17 * 4
+    assert C.sizeof(_lib.SlConfig) == 18 * 4
     assert C.sizeof(_lib.SlSynthSpec) == 16
     assert C.sizeof(_lib.SlWeightDesc) == 32
     assert C.sizeof(_lib.SlSnap) == 16
