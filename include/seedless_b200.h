@@ -70,7 +70,8 @@ enum {
     SL_FLAG_STEP_KERNEL = 4,       /* single-stream decode steps as ONE cooperative kernel launch (see sl_engine_use_persistent) */
     SL_FLAG_SPLIT_EXPERTS = 8,     /* batch-1 decode: gate/up and down as two launches instead of the fused expert kernel */
     SL_FLAG_ROUTE_IN_ROUTER = 16,  /* batch-1 decode: the router kernel's last CTA routes (instead of every CTA of the expert kernel) */
-    SL_FLAG_L2_PREFETCH = 32       /* kernels prefetch the weights of later kernels into L2 (slower as measured; kept for comparison) */
+    SL_FLAG_L2_PREFETCH = 32,      /* kernels prefetch the weights of later kernels into L2 (slower as measured; kept for comparison) */
+    SL_FLAG_PASS_KERNELS = 64      /* calls with more than 8 rows walk them in passes of 8 with the one-to-eight-row kernels instead of the many-row kernels (same bits) */
 };
 
 /* One named tensor handed to sl_engine_create.  Names: "embed", "final_norm", "lm_head.w/.s/.b",

@@ -62,6 +62,8 @@ struct sl_engine {
     // scratch (sized by max_rows)
     __half *h = nullptr, *p = nullptr, *inproj = nullptr, *mix = nullptr, *rlogits = nullptr, *sgl = nullptr, *scores = nullptr;
     __half *hbuf = nullptr, *dbuf = nullptr, *normed = nullptr, *qrot = nullptr, *opx = nullptr, *opy = nullptr;
+    // many-row kernels: prepared rows of a dense projection / of the experts' input, their group sums, chunk sums of the SwiGLU rows
+    __half *xq = nullptr, *xq_p = nullptr; float *sxq = nullptr, *sx_p = nullptr, *csum = nullptr;
     __half* logits = nullptr; int logits_rows = 0;
     int* inds = nullptr; MoeLists lists{};
     float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
@@ -69,6 +71,7 @@ struct sl_engine {
     int *row_seg = nullptr, *row_off = nullptr, *row_pos = nullptr;
     unsigned* counters = nullptr; unsigned* tile_counters = nullptr; unsigned* att_counters = nullptr; unsigned* err_flag = nullptr; unsigned* err_host = nullptr; float* adj_buf = nullptr; int* samp_buf = nullptr; unsigned* slot_sync = nullptr; unsigned* router_groups = nullptr;
     bool use_route_in_experts = true;   // with the fused kernel: routing done by its CTAs (SL_FLAG_ROUTE_IN_ROUTER: by the router's last CTA)
+    bool use_rows = true;           // calls with more than 8 rows use the many-row kernels (SL_FLAG_PASS_KERNELS turns it off)
     bool use_fused_experts = true;  // batch-1 decode: gate/up + down in one launch (SL_FLAG_SPLIT_EXPERTS turns it off)
     // expert-parallel decode (experts [ep_e0, ep_e1) are this rank's; see sl_ep_init)
     int ep_rank = 0, ep_world = 1, ep_rows = 0, ep_e0 = 0, ep_e1 = 0;
@@ -283,6 +286,14 @@ int32_t build_runtime(sl_engine* e) {
     if ((rc = dalloc(e, &e->h, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->p, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->normed, (size_t)R * (e->valDim > H ? e->valDim : H)))) return rc;   // also the gated-norm rows of prefill mode
+    {
+        const size_t wmax = (size_t)(mix_w > (size_t)H ? mix_w : (size_t)H);
+        if ((rc = dalloc(e, &e->xq, (size_t)R * wmax))) return rc;
+        if ((rc = dalloc(e, &e->sxq, (size_t)R * (wmax / 64)))) return rc;
+        if ((rc = dalloc(e, &e->xq_p, (size_t)R * H))) return rc;
+        if ((rc = dalloc(e, &e->sx_p, (size_t)R * (H / 64)))) return rc;
+        if ((rc = dalloc(e, &e->csum, prow * (size_t)(e->I / 8)))) return rc;
+    }
     if ((rc = dalloc(e, &e->opx, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->opy, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->inproj, (size_t)R * in_w))) return rc;
@@ -357,6 +368,7 @@ int32_t build_runtime(sl_engine* e) {
     // assembly switches come with the configuration (sl_config.flags), not from the environment
     e->use_route_in_experts = !(c.flags & SL_FLAG_ROUTE_IN_ROUTER);
     e->use_fused_experts = !(c.flags & SL_FLAG_SPLIT_EXPERTS);
+    e->use_rows = !(c.flags & SL_FLAG_PASS_KERNELS);
     e->use_prefetch = (c.flags & SL_FLAG_L2_PREFETCH) != 0;
     e->use_pdl = !(c.flags & SL_FLAG_NO_PDL);
     e->use_graph = !(c.flags & SL_FLAG_NO_GRAPH);
@@ -518,8 +530,16 @@ int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __ha
     ea.ep_sig = ra.epd.sig; ea.ep_sig.ticket = e->counters + 2;
     const int local_e = e->ep_e1 - e->ep_e0;
     const int nslots = T * topk < local_e ? T * topk : local_e;
-    launch_expert_gateup(ea, nslots, st, false);
-    launch_expert_down(ea, nslots, st, false);       // its last CTA raises the combine flags
+    bool rows_done = false;
+    if (T > 8 && local_e <= 256 && e->use_rows && T <= e->cfg.max_rows) {
+        launch_rows_prep_plain(P.pbuf[r], H, T, H, e->xq_p, e->sx_p, st);
+        ea.xq = e->xq_p; ea.sxq = e->sx_p; ea.csum = e->csum;
+        rows_done = launch_expert_rows_gateup(ea, st) && launch_expert_rows_down(ea, st);
+    }
+    if (!rows_done) {
+        launch_expert_gateup(ea, nslots, st, false);
+        launch_expert_down(ea, nslots, st, false);       // its last CTA raises the combine flags
+    }
     launch_ep_combine(P, e->dbuf + (size_t)T * topk * H, e->scores, e->sgl, M, H, topk, resid, plain_out, layer, e->err_flag, st);
     return SL_OK;
 }
@@ -548,6 +568,16 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     ea.route_here = ra.no_route;
     launch_router(ra, st, e->use_pdl);
     if (fused && launch_expert_fused(ea, st, e->use_pdl)) return;                      // one launch for gate/up + down
+    if (M > 8 && e->E <= 256 && e->use_rows) {
+        // many rows: the normed rows are prepared once, the experts run without CTA-wide barriers, the combine is its own kernel
+        launch_rows_prep_plain(e->p, e->H, M, e->H, e->xq_p, e->sx_p, st);
+        ea.xq = e->xq_p; ea.sxq = e->sx_p; ea.csum = e->csum; ea.tile_counter = nullptr;
+        if (launch_expert_rows_gateup(ea, st) && launch_expert_rows_down(ea, st)) {
+            launch_moe_combine(e->dbuf, e->dbuf + (size_t)M * e->topk * e->H, e->scores, e->sgl, M, e->H, e->topk, resid, plain_out, st);
+            return;
+        }
+        ea.tile_counter = e->tile_counters;
+    }
     launch_expert_gateup(ea, nslots, st, e->use_pdl);
     launch_expert_down(ea, nslots, st, e->use_pdl);
 }
@@ -557,14 +587,14 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
                    __half* resid, __half* plain_out, const int* row_pos_override) {
     cudaStream_t st = e->stream;
     const sl_config& c = e->cfg;
-    DenseArgs d{}; d.err = e->err_flag; d.norm_scratch = e->normed; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
+    DenseArgs d{}; d.err = e->err_flag; d.norm_scratch = e->normed; d.xq = e->use_rows ? e->xq : nullptr; d.sxq = e->sxq; d.q = L.r_in; d.N = (int)L.in_proj.N; d.K = e->H; d.M = M;
     d.x = rows; d.ldx = e->H; d.nw = norm_w; d.eps = c.rms_eps; d.y = e->inproj; d.ldy = (int)L.in_proj.N;
     if (e->use_prefetch) pf_q4(d.pf, 0, L.r_out);
     d.tc = e->hybrid;
     launch_dense(norm_w ? PRO_RMSNORM : PRO_PLAIN, EPI_STORE, d, st, e->use_pdl);
     DenseArgs o{};
     o.err = e->err_flag; o.q = L.r_out; o.N = e->H; o.K = L.out_proj.K; o.M = M;
-    o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H; o.tc = e->hybrid; o.norm_scratch = e->normed;
+    o.eps = c.rms_eps; o.y = resid ? resid : plain_out; o.ldy = e->H; o.tc = e->hybrid; o.norm_scratch = e->normed; o.xq = e->use_rows ? e->xq : nullptr; o.sxq = e->sxq;
     if (e->use_prefetch) {
         o.pf.p[0] = L.router; o.pf.bytes[0] = (unsigned)((size_t)e->E * e->H * 2);
         pf_q4(o.pf, 1, L.r_sh_gu);

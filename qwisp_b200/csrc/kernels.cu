@@ -394,6 +394,7 @@ void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pd
         return;
     }
 gemv_path:
+    if (a.M > ROWS_PER_PASS && launch_dense_rows(pro, epi, a, st)) return;
     const GemvPlan pl = gemv_plan(a.K, epi == EPI_SWIGLU ? a.N / 8 : a.N / 16, 1, sm_count());
 #define SL_CASE(P, E)                                                                                       \
     if (pro == P && epi == E) {                                                                             \

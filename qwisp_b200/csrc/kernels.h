@@ -12,6 +12,7 @@ struct DenseArgs {
     unsigned* err = nullptr;             // set to 1 if a bounded wait on a bulk copy gave up
     __half* norm_scratch = nullptr;      // [M][K] scratch for the tensor-core path (normed rows); nullptr keeps the GEMV path
     bool tc = false;                     // prefill mode: dense projections on the tcgen05 GEMM (set per call by the caller)
+    __half* xq = nullptr; float* sxq = nullptr;   // [M][K] / [M][K/64] scratch of the many-row kernels (calls with more than 8 rows); nullptr: pass kernels
     Q4R q;                                                       // repacked weights (tiles of 16 rows)
     int N, K, M;                                                 // N outputs (= 16 * tiles)
     const __half* x; int ldx;                                    // activations (plain) / residual stream (rmsnorm) / y (normgate)
@@ -95,6 +96,9 @@ struct ExpertArgs {
     int ep_pairs_per_rank = 0;
     EpSignal ep_sig;                     // down kernel: its last CTA raises the combine flags
     PfList pf;                           // static prefetch (gate/up kernel: next layer's in-projection)
+    // many-row kernels: the normed rows in paired order + their group sums (gate/up input), and the chunk sums of the
+    // SwiGLU rows ([(M*topk + M)][I/8], written by gate/up, read by down; hbuf is then in paired order too)
+    const __half* xq = nullptr; const float* sxq = nullptr; float* csum = nullptr;
 };
 
 struct GdnArgs {
@@ -168,6 +172,13 @@ bool ps_plan(PsGeom& g, int n_sm);           // fills the derived fields; false 
 int launch_step_persistent(const PStepArgs& a, cudaStream_t st);   // cooperative launch; returns a cudaError_t
 
 void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pdl);
+// many-row forms (more than 8 rows per call); the bool launchers return false when the shape is not covered
+bool launch_dense_rows(int pro, int epi, const DenseArgs& a, cudaStream_t st);
+void launch_rows_prep_plain(const __half* x, int ldx, int M, int K, __half* xq, float* sxq, cudaStream_t st);
+bool launch_expert_rows_gateup(const ExpertArgs& a, cudaStream_t st);
+bool launch_expert_rows_down(const ExpertArgs& a, cudaStream_t st);
+void launch_moe_combine(const __half* dbuf, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,
+                        __half* resid, __half* out, cudaStream_t st);
 // many-row GEMM on tcgen05 tensor cores with the accumulator in tensor memory (N % 128 == 0, K % 256 == 0); 0 or an error code
 int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, __half* y, int ldy, bool add_to_y, unsigned* err, cudaStream_t st);
 // speculative-sampling rows on fp16 logits [M][V]: categorical draw, draw without the draft token, accept flag

@@ -1,0 +1,495 @@
+// rows_kernels.cu -- the many-row forms of the 4-bit group-64 GEMV family: calls with more than 8 activation rows
+// (batched decode, long verify rows, strict-mode prompt chunks).
+//
+// The one-to-eight-row kernels (kernels.cu) walk the rows in passes of 8 and pay one grid wave, one weight fetch and
+// one dequantisation per pass.  Here the weights of a tile are fetched and dequantised ONCE per 8*RG rows and a row's
+// arithmetic is kept exactly as in the pass kernels, so every output is bit-identical to what the same row gives
+// alone (the batch-invariance rule of the reference, swift/Sources/QwispCore/SeedlessMetalForward.swift:160-185):
+//   - per group of 64 inputs the same chain of four m16n8k16 MMAs (an MMA column never mixes with another column);
+//   - scale * sum and bias * (sum of the group's activations) accumulated over the 4 groups of a 256-input slice;
+//   - slice values added in ascending order starting from 0.
+//
+//   k_rows_prep      the prologue (plain / RMSNorm / gated RMSNorm) of every row, written once per call: activations in the
+//                    paired order the dequantiser produces (0,4,1,5,2,6,3,7 inside every 8) + the per-group sums.
+//   k_gemv_rows      dense projection: a CTA of 8 warps = 8 tiles x (8*RG rows); the rows' slice of 256 inputs is staged in
+//                    shared memory (cp.async, two buffers) and shared by the warps; each warp streams its tile's slices
+//                    from global memory one slice ahead.
+//   k_expert_rows    routed + shared experts grouped by expert: persistent CTAs of 16 consumer warps + 1 producer warp.
+//                    The producer gathers the rows of the next (expert, row block) into a ring of shared-memory stages with
+//                    bulk copies (mbarrier full / empty), the consumers each own one tile over the whole K -- no CTA-wide
+//                    barrier between experts, which is what bounded the pass kernels when every expert has one or two rows.
+//   k_moe_combine    weighted sum of a row's top-k expert rows in ascending k + shared expert + residual.
+#include "kernels.h"
+#include "gemv.cuh"
+
+namespace sl {
+
+// ================================================================================ prologue rows
+// lane holds the 8 prologue'd activations (row, k0 .. k0+7): paired-order store + group sum (8 lanes = one group),
+// the arithmetic of store_staged()
+__device__ __forceinline__ void rows_store(__half* xq_row, float* sx_row, int k0, uint4 v, int lane) {
+    float s = sum8_f32(v);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    if ((lane & 7) == 0) sx_row[k0 >> 6] = s;
+    uint4 o;
+    o.x = __byte_perm(v.x, v.z, 0x5410);
+    o.y = __byte_perm(v.x, v.z, 0x7632);
+    o.z = __byte_perm(v.y, v.w, 0x5410);
+    o.w = __byte_perm(v.y, v.w, 0x7632);
+    *reinterpret_cast<uint4*>(xq_row + k0) = o;
+}
+struct RowsPrepArgs {
+    const __half* x; int ldx;            // rows (plain) / residual stream (rmsnorm) / mixer output (gated norm)
+    const __half* nw; const float* nw32; // norm weight
+    const __half* z; int ldz;            // gate input of the gated norm
+    float eps; int K;
+    __half* xq; float* sxq;              // out: [M][K] paired order, [M][K/64]
+};
+// grid (M), K/256 warps: warp = one 256-input chunk of the row (the unit of stage_finish())
+template <int PRO>
+__global__ void __launch_bounds__(512) k_rows_prep(RowsPrepArgs a) {
+    __shared__ float part[16];
+    const int row = blockIdx.x, ch = threadIdx.x >> 5, lane = threadIdx.x & 31, chunks = a.K >> 8;
+    const int k0 = (ch << 8) + lane * 8;
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)row * a.ldx + k0));
+    uint4 o;
+    if (PRO == PRO_PLAIN) {
+        o = v;
+    } else if (PRO == PRO_RMSNORM) {
+        const float ss = warp_sum(sumsq8(v));
+        if (lane == 0) part[ch] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int c = 0; c < chunks; ++c) tot += part[c];
+        const float inv = __frsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)a.K), a.eps));
+        o = rms_apply8(v, *reinterpret_cast<const uint4*>(a.nw + k0), inv);
+    } else {
+        const uint4 zv = __ldcg(reinterpret_cast<const uint4*>(a.z + (size_t)row * a.ldz + k0));
+        const uint4 wv = *reinterpret_cast<const uint4*>(a.nw + (k0 & 127));
+        o = normgate8<PRO>(v, zv, wv, a.nw32, k0, a.eps);
+    }
+    rows_store(a.xq + (size_t)row * a.K, a.sxq + (size_t)row * (a.K >> 6), k0, o, lane);
+}
+static void launch_rows_prep_args(int pro, const RowsPrepArgs& a, int M, cudaStream_t st) {
+    const unsigned threads = (unsigned)(a.K >> 8) * 32u;
+    profile_launch("k_rows_prep", st, [&] {
+        if (pro == PRO_PLAIN) k_rows_prep<PRO_PLAIN><<<M, threads, 0, st>>>(a);
+        else if (pro == PRO_RMSNORM) k_rows_prep<PRO_RMSNORM><<<M, threads, 0, st>>>(a);
+        else if (pro == PRO_NORMGATE) k_rows_prep<PRO_NORMGATE><<<M, threads, 0, st>>>(a);
+        else k_rows_prep<PRO_NORMGATE32><<<M, threads, 0, st>>>(a);
+        return 0;
+    });
+}
+void launch_rows_prep_plain(const __half* x, int ldx, int M, int K, __half* xq, float* sxq, cudaStream_t st) {
+    RowsPrepArgs p{x, ldx, nullptr, nullptr, nullptr, 0, 0.f, K, xq, sxq};
+    launch_rows_prep_args(PRO_PLAIN, p, M, st);
+}
+
+// ================================================================================ shared compute
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+
+// One slice (4 groups of 64 inputs) of a 16-row tile against 8*RG staged rows.
+// xs: the slice's activations of staged row 0 (paired order), rows xstride halves apart; sxs: group sums of staged
+// row 0 for the slice's 4 groups, rows sxstride floats apart.  acc[q]: (row A, col 2t), (A, 2t+1), (B, 2t), (B, 2t+1)
+// of row group q.  The order of operations per column is that of compute_slice_x().
+template <int RG>
+__device__ __forceinline__ void compute_rows(const SliceRegs& rg, const __half* xs, int xstride, const float* sxs, int sxstride,
+                                             int r, int t, float accS[RG][4], float accB[RG][4]) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const uint4 wv = rg.w[g];
+        uint32_t a0[4], b0[4], a1[4], b1[4];
+        dequant8(wv.x, a0); dequant8(wv.z, b0); dequant8(wv.y, a1); dequant8(wv.w, b1);
+        const uint4 sv = rg.sc[g >> 1];
+        const uint32_t sa_ba = (g & 1) ? sv.z : sv.x, sb_bb = (g & 1) ? sv.w : sv.y;
+        const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&sa_ba));
+        const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&sb_bb));
+#pragma unroll
+        for (int q = 0; q < RG; ++q) {
+            const __half* xp = xs + (size_t)(q * 8 + r) * xstride + 64 * g + 16 * t;
+            const uint4 X0 = *reinterpret_cast<const uint4*>(xp), X1 = *reinterpret_cast<const uint4*>(xp + 8);
+            const float sx0 = sxs[(q * 8 + 2 * t) * sxstride + g], sx1 = sxs[(q * 8 + 2 * t + 1) * sxstride + g];
+            float c[4];
+            mma_f16_z(c, a0[0], b0[0], a0[1], b0[1], X0.x, X0.y);
+            mma_f16(c, a0[2], b0[2], a0[3], b0[3], X0.z, X0.w);
+            mma_f16(c, a1[0], b1[0], a1[1], b1[1], X1.x, X1.y);
+            mma_f16(c, a1[2], b1[2], a1[3], b1[3], X1.z, X1.w);
+            accS[q][0] = fmaf(fa.x, c[0], accS[q][0]); accS[q][1] = fmaf(fa.x, c[1], accS[q][1]);
+            accS[q][2] = fmaf(fb.x, c[2], accS[q][2]); accS[q][3] = fmaf(fb.x, c[3], accS[q][3]);
+            accB[q][0] = fmaf(fa.y, sx0, accB[q][0]); accB[q][1] = fmaf(fa.y, sx1, accB[q][1]);
+            accB[q][2] = fmaf(fb.y, sx0, accB[q][2]); accB[q][3] = fmaf(fb.y, sx1, accB[q][3]);
+        }
+    }
+}
+// slice value = scale part + bias part, added to the running total (which starts from 0, as reduce_tiles() does)
+template <int RG>
+__device__ __forceinline__ void add_slice(float tot[RG][4], const float accS[RG][4], const float accB[RG][4]) {
+#pragma unroll
+    for (int q = 0; q < RG; ++q)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tot[q][i] = __fadd_rn(tot[q][i], __fadd_rn(accS[q][i], accB[q][i]));
+}
+
+// ================================================================================ dense projection
+struct RowsDenseArgs {
+    Q4R q; int N, K, M;
+    const __half* xq; const float* sxq;  // prepared rows
+    __half* y; int ldy;
+};
+constexpr int RD_XS = 256 + 8;           // halves per staged row of one slice (16 bytes of skew: conflict-free B loads)
+// grid (ceil(tiles / 8), ceil(M / (8*RG))), 256 threads
+template <int EPI, int RG>
+__global__ void __launch_bounds__(256, RG == 1 ? 2 : 1) k_gemv_rows(RowsDenseArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int NR = 8 * RG;
+    __half* xs = reinterpret_cast<__half*>(smem);                               // [2][NR][RD_XS]
+    float* sxs = reinterpret_cast<float*>(smem + (size_t)2 * NR * RD_XS * 2);    // [2][NR][4]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, t = lane & 3;
+    const int slices = a.K >> 8, G64 = a.K >> 6, ntiles = a.N >> 4;
+    const int tile = blockIdx.x * 8 + warp;
+    const bool active = tile < ntiles;
+    const int row0 = blockIdx.y * NR, nrows = min(NR, a.M - row0);
+    const uint4* wt = a.q.wr + (size_t)tile * q4r_w_uint4(a.K);
+    const uint4* stl = a.q.sr + (size_t)tile * q4r_s_uint4(a.K);
+    auto stage = [&](int s, int b) {
+        __half* xb = xs + (size_t)b * NR * RD_XS;
+        for (int i = tid; i < NR * 32; i += 256) {
+            const int row = i >> 5, c = i & 31;
+            __half* dst = xb + (size_t)row * RD_XS + c * 8;
+            if (row < nrows) cp_async16(dst, a.xq + (size_t)(row0 + row) * a.K + s * 256 + c * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        if (tid < NR) {
+            float* dst = sxs + (size_t)(b * NR + tid) * 4;
+            if (tid < nrows) cp_async16(dst, a.sxq + (size_t)(row0 + tid) * G64 + s * 4);
+            else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        cp_async_commit();
+    };
+    SliceRegs cur, n1, n2;                                    // this slice and the next two (weights stream two slices ahead)
+    if (active) { load_slice(cur, wt, stl, 0, lane); if (slices > 1) load_slice(n1, wt, stl, 1, lane); }
+    stage(0, 0);
+    float tot[RG][4];
+#pragma unroll
+    for (int q = 0; q < RG; ++q) { tot[q][0] = 0.f; tot[q][1] = 0.f; tot[q][2] = 0.f; tot[q][3] = 0.f; }
+#pragma unroll 1
+    for (int s = 0; s < slices; ++s) {
+        const int b = s & 1;
+        if (active && s + 2 < slices) load_slice(n2, wt, stl, s + 2, lane);
+        if (s + 1 < slices) { stage(s + 1, b ^ 1); cp_async_wait<1>(); }
+        else cp_async_wait<0>();
+        __syncthreads();
+        if (active) {
+            float accS[RG][4], accB[RG][4];
+#pragma unroll
+            for (int q = 0; q < RG; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) { accS[q][i] = 0.f; accB[q][i] = 0.f; }
+            compute_rows<RG>(cur, xs + (size_t)b * NR * RD_XS, RD_XS, sxs + (size_t)b * NR * 4, 4, r, t, accS, accB);
+            add_slice<RG>(tot, accS, accB);
+        }
+        __syncthreads();                       // the buffer may be refilled by the next iteration's stage()
+        cur = n1; n1 = n2;
+    }
+    if (!active) return;
+#pragma unroll
+    for (int q = 0; q < RG; ++q)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int xrow = q * 8 + 2 * t + (i & 1), wrow = tile * 16 + r + 8 * (i >> 1);
+            if (xrow < nrows) {
+                const size_t idx = (size_t)(row0 + xrow) * a.ldy + wrow;
+                __half val = f2h(tot[q][i]);
+                if (EPI == EPI_RESID) val = hadd_rn(a.y[idx], val);
+                a.y[idx] = val;
+            }
+        }
+}
+template <int EPI, int RG>
+static void launch_gemv_rows_t(const RowsDenseArgs& a, cudaStream_t st) {
+    const size_t smem = (size_t)2 * 8 * RG * RD_XS * 2 + (size_t)2 * 8 * RG * 4 * 4;
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_gemv_rows<EPI, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); configured = true; }
+    const dim3 grid((unsigned)(((a.N >> 4) + 7) / 8), (unsigned)((a.M + 8 * RG - 1) / (8 * RG)));
+    profile_launch(EPI == EPI_RESID ? "k_gemv_rows_outproj" : "k_gemv_rows_inproj", st, [&] { k_gemv_rows<EPI, RG><<<grid, 256, smem, st>>>(a); return 0; });
+}
+// dense projection of M > 8 rows: prologue rows, then the tile kernel.  Returns false when the shape is not covered.
+bool launch_dense_rows(int pro, int epi, const DenseArgs& a, cudaStream_t st) {
+    if (!a.xq || !a.sxq || a.K % 256 || a.K > 4096 || a.N % 16 || (epi != EPI_STORE && epi != EPI_RESID)) return false;
+    RowsPrepArgs p{a.x, a.ldx, a.nw, a.nw32, a.z, a.ldz, a.eps, a.K, a.xq, a.sxq};
+    launch_rows_prep_args(pro, p, a.M, st);
+    RowsDenseArgs d{a.q, a.N, a.K, a.M, a.xq, a.sxq, a.y, a.ldy};
+    // 32 rows per CTA (weights dequantised once per 32 rows) when that still fills the device, else 8
+    const long ctas4 = (long)(((a.N >> 4) + 7) / 8) * ((a.M + 31) / 32);
+    const bool rg4 = ctas4 >= sm_count();
+    if (epi == EPI_RESID) { if (rg4) launch_gemv_rows_t<EPI_RESID, 4>(d, st); else launch_gemv_rows_t<EPI_RESID, 1>(d, st); }
+    else { if (rg4) launch_gemv_rows_t<EPI_STORE, 4>(d, st); else launch_gemv_rows_t<EPI_STORE, 1>(d, st); }
+    return true;
+}
+
+// ================================================================================ experts
+// A work item is (expert slot, block of 8 rows, group of 16 tiles); items are numbered slot-major, tile group fastest, so
+// neighbouring CTAs read neighbouring weights and the same rows.  Slot n_active is the shared expert (all rows).
+constexpr int XR_CONS = 16;                  // consumer warps = tiles per item
+constexpr int XR_THREADS = (XR_CONS + 1) * 32;
+struct XrStage {                             // one ring stage in shared memory
+    __half* xs;                              // [8][K + 8]
+    float* sxs;                              // [8][K/64 + 4]
+    float* craw;                             // down: [8][K/8] chunk sums as written by the gate/up kernel
+    int* info;                               // [0..7] destination rows (-1: none), [8] expert, [9] shared, [10] tile group
+};
+template <bool DOWN>
+__host__ __device__ inline size_t xr_stage_bytes(int K) {
+    size_t b = (size_t)8 * (K + 8) * 2 + (size_t)8 * (K / 64 + 4) * 4 + 16 * 4;
+    if (DOWN) b += (size_t)8 * (K / 8) * 4;
+    return (b + 15) & ~(size_t)15;
+}
+template <bool DOWN>
+__device__ __forceinline__ XrStage xr_carve(unsigned char* base, int K) {
+    XrStage s;
+    s.xs = reinterpret_cast<__half*>(base); base += (size_t)8 * (K + 8) * 2;
+    s.sxs = reinterpret_cast<float*>(base); base += (size_t)8 * (K / 64 + 4) * 4;
+    s.craw = reinterpret_cast<float*>(base); if (DOWN) base += (size_t)8 * (K / 8) * 4;
+    s.info = reinterpret_cast<int*>(base);
+    return s;
+}
+// grid: one CTA per multiprocessor; dynamic shared memory: nstages stages
+template <bool DOWN>
+__global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int nstages) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int s_base[260];                                  // first (slot, block) index of every slot; [n_active + 1] = total
+    __shared__ __align__(8) uint64_t s_full[8], s_empty[8], s_raw[8];
+    __shared__ int s_sig;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, t = lane & 3;
+    const int K = DOWN ? a.I : a.H;
+    const int slices = K >> 8, G64 = K >> 6, SXS = G64 + 4, XS = K + 8;
+    const int ntiles = DOWN ? a.H / 16 : a.I / 8;
+    const int NTG = (ntiles + XR_CONS - 1) / XR_CONS;
+    const int npair = a.M * a.topk;
+    const int n_active = *a.lists.n_active;
+    const int nshared = a.M_shared >= 0 ? a.M_shared : a.M;
+    const size_t stage_bytes = xr_stage_bytes<DOWN>(K);
+    // ---- (slot, block) prefix: warp 0 scans the slot counts in chunks of 32
+    if (warp == 0) {
+        int run = 0;
+        for (int j0 = 0; j0 <= n_active; j0 += 32) {
+            const int j = j0 + lane;
+            int nb = 0;
+            if (j < n_active) nb = (a.lists.slot_cnt[j] + 7) >> 3;
+            else if (j == n_active) nb = (nshared + 7) >> 3;
+            int inc = nb;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) { const int o = __shfl_up_sync(0xffffffffu, inc, d); if (lane >= d) inc += o; }
+            if (j <= n_active) s_base[j] = run + inc - nb;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) s_base[n_active + 1] = run;
+    }
+    if (tid == 0) {
+        for (int i = 0; i < nstages; ++i) { mbar_init(&s_full[i], DOWN ? 1 : 8); mbar_init(&s_empty[i], XR_CONS); mbar_init(&s_raw[i], 8); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const int total = s_base[n_active + 1] * NTG;
+    // (slot, block) index -> slot: the last j with s_base[j] <= sb
+    auto slot_of = [&](int sb) {
+        int lo = 0, hi = n_active;
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (s_base[mid] <= sb) lo = mid; else hi = mid - 1; }
+        return lo;
+    };
+    bool failed = false;
+    if (warp == XR_CONS) {
+        // ------------------------------------------------------------ producer
+        int k = 0;
+        for (int item = blockIdx.x; item < total; item += gridDim.x, ++k) {
+            const int stg = k % nstages, use = k / nstages;
+            const XrStage S = xr_carve<DOWN>(smem + (size_t)stg * stage_bytes, K);
+            if (use > 0 && !mbar_wait_bounded(&s_empty[stg], (uint32_t)((use - 1) & 1))) failed = true;
+            const int sb = item / NTG, tg = item - sb * NTG;
+            const int j = slot_of(sb), blk = sb - s_base[j];
+            const bool shared = (j == n_active);
+            const int cnt = shared ? nshared : a.lists.slot_cnt[j];
+            if (lane < 8) {
+                const int ridx = blk * 8 + lane;
+                int dst = -1, srow = 0;
+                if (ridx < cnt) {
+                    if (shared) { dst = npair + ridx; srow = DOWN ? dst : a.shared_row0 + ridx; }
+                    else { const int pr = a.lists.pairs[a.lists.slot_off[j] + ridx]; dst = pr; srow = DOWN ? pr : pr / a.topk; }
+                }
+                S.info[lane] = dst;
+                if (lane == 0) { S.info[8] = shared ? 0 : a.lists.slot_expert[j]; S.info[9] = shared ? 1 : 0; S.info[10] = tg; }
+                uint64_t* bar = DOWN ? &s_raw[stg] : &s_full[stg];
+                if (dst >= 0) {
+                    const __half* xsrc = (DOWN ? a.hbuf : a.xq) + (size_t)srow * K;
+                    if (DOWN) {
+                        mbar_expect_tx(bar, (uint32_t)(K * 2 + (K / 8) * 4));
+                        bulk_g2s(S.xs + (size_t)lane * XS, xsrc, (uint32_t)K * 2, bar);
+                        bulk_g2s(S.craw + (size_t)lane * (K / 8), a.csum + (size_t)srow * (K / 8), (uint32_t)(K / 8) * 4, bar);
+                    } else {
+                        mbar_expect_tx(bar, (uint32_t)(K * 2 + G64 * 4));
+                        bulk_g2s(S.xs + (size_t)lane * XS, xsrc, (uint32_t)K * 2, bar);
+                        bulk_g2s(S.sxs + (size_t)lane * SXS, a.sxq + (size_t)srow * G64, (uint32_t)G64 * 4, bar);
+                    }
+                } else {
+                    mbar_arrive(bar);
+                }
+            }
+            if (DOWN) {
+                // group sums from the chunk sums: eight chunk sums combined in the butterfly order of rows_store()
+                if (!mbar_wait_bounded(&s_raw[stg], (uint32_t)(use & 1))) failed = true;
+                for (int i = lane; i < 8 * G64; i += 32) {
+                    const int row = i / G64, g = i - row * G64;
+                    const float* c = S.craw + (size_t)row * (K / 8) + g * 8;
+                    const float4 lo = *reinterpret_cast<const float4*>(c), hi = *reinterpret_cast<const float4*>(c + 4);
+                    const float e = __fadd_rn(__fadd_rn(lo.x, hi.x), __fadd_rn(lo.z, hi.z));       // (s0 + s4) + (s2 + s6)
+                    const float o = __fadd_rn(__fadd_rn(lo.y, hi.y), __fadd_rn(lo.w, hi.w));       // (s1 + s5) + (s3 + s7)
+                    S.sxs[(size_t)row * SXS + g] = __fadd_rn(e, o);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_full[stg]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ consumers: warp = one tile of the item's group
+        const Q4R& qr = DOWN ? a.down : a.gu;
+        const Q4R& qs = DOWN ? a.sh_down : a.sh_gu;
+        const size_t wstep = q4r_w_uint4(K), sstep = q4r_s_uint4(K);
+        auto tile_ptrs = [&](int item, const uint4*& wt, const uint4*& stl, bool& valid) {
+            const int sb = item / NTG, tg = item - sb * NTG;
+            const int j = slot_of(sb);
+            const bool shared = (j == n_active);
+            const int tile = tg * XR_CONS + warp;
+            valid = tile < ntiles;
+            const Q4R& q = shared ? qs : qr;
+            const size_t T = (size_t)(shared ? 0 : a.lists.slot_expert[j]) * ntiles + (valid ? tile : 0);
+            wt = q.wr + T * wstep; stl = q.sr + T * sstep;
+        };
+        SliceRegs cur, nxt;
+        const uint4 *wt = nullptr, *stl = nullptr, *wt_n = nullptr, *stl_n = nullptr;
+        bool valid = false, valid_n = false;
+        if ((int)blockIdx.x < total) { tile_ptrs(blockIdx.x, wt, stl, valid); if (valid) load_slice(cur, wt, stl, 0, lane); }
+        int k = 0;
+        for (int item = blockIdx.x; item < total; item += gridDim.x, ++k) {
+            const int stg = k % nstages, use = k / nstages;
+            const XrStage S = xr_carve<DOWN>(smem + (size_t)stg * stage_bytes, K);
+            const int item_n = item + gridDim.x;
+            if (item_n < total) tile_ptrs(item_n, wt_n, stl_n, valid_n); else valid_n = false;
+            if (!mbar_wait_bounded(&s_full[stg], (uint32_t)(use & 1))) failed = true;
+            float tot[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 1
+            for (int s = 0; s < slices; ++s) {
+                if (s + 1 < slices) { if (valid) load_slice(nxt, wt, stl, s + 1, lane); }
+                else if (valid_n) load_slice(nxt, wt_n, stl_n, 0, lane);
+                if (valid) {
+                    float accS[1][4] = {{0.f, 0.f, 0.f, 0.f}}, accB[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+                    compute_rows<1>(cur, S.xs + s * 256, XS, S.sxs + s * 4, SXS, r, t, accS, accB);
+                    add_slice<1>(tot, accS, accB);
+                }
+                cur = nxt;
+            }
+            if (valid) {
+                const int tile = S.info[10] * XR_CONS + warp;
+                if (DOWN) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int dst = S.info[2 * t + (i & 1)];
+                        if (dst >= 0) {
+                            __half* rowp = a.dbuf + (size_t)dst * a.H;
+                            if (a.ep_pairs_per_rank > 0 && dst < npair) {       // routed pair in expert-parallel mode: the owner's buffer
+                                const int own = dst / a.ep_pairs_per_rank;
+                                rowp = a.peer_dbuf[own] + (size_t)(dst - own * a.ep_pairs_per_rank) * a.H;
+                            }
+                            rowp[tile * 16 + r + 8 * (i >> 1)] = f2h(tot[0][i]);
+                        }
+                    }
+                } else {
+                    // SwiGLU of (gate row r, up row r) per column; the 8 outputs of a column (lanes with the same t) form one
+                    // 8-chunk of the down projection's input: stored in the paired order with its chunk sum
+#pragma unroll
+                    for (int jc = 0; jc < 2; ++jc) {
+                        const __half hv = swiglu_h(f2h(tot[0][jc]), f2h(tot[0][2 + jc]));
+                        const unsigned hb = __half_as_ushort(hv);
+                        unsigned v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] = __shfl_sync(0xffffffffu, hb, i * 4 + t);
+                        const int dst = S.info[2 * t + jc];
+                        if (r == 0 && dst >= 0) {
+                            const uint4 nat = make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+                            const uint4 prd = make_uint4(v[0] | (v[4] << 16), v[1] | (v[5] << 16), v[2] | (v[6] << 16), v[3] | (v[7] << 16));
+                            *reinterpret_cast<uint4*>(a.hbuf + (size_t)dst * a.I + tile * 8) = prd;
+                            a.csum[(size_t)dst * (a.I / 8) + tile] = sum8_f32(nat);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[stg]);
+            wt = wt_n; stl = stl_n; valid = valid_n;
+        }
+    }
+    if (failed && a.err && lane == 0) atomicOr(a.err, 1u);
+    if (DOWN && a.ep_sig.world > 0) {
+        // expert-parallel: every CTA makes its peer stores visible system-wide and draws a ticket; the last one raises this
+        // rank's combine flag at every peer
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned ticket = atomicAdd(a.ep_sig.ticket, 1u);
+            s_sig = (ticket == gridDim.x - 1) ? 1 : 0;
+            if (s_sig) *a.ep_sig.ticket = 0u;
+        }
+        __syncthreads();
+        if (s_sig && tid < a.ep_sig.world)
+            st_release_sys(a.ep_sig.flags[tid] + 8 + a.ep_sig.rank, ep_seq(a.ep_sig.ctr, a.ep_sig.layer, 1));
+    }
+}
+template <bool DOWN>
+static bool launch_expert_rows_t(const ExpertArgs& a, cudaStream_t st) {
+    const int K = DOWN ? a.I : a.H;
+    if (K % 256 || K > 4096 || !a.csum || (!DOWN && (!a.xq || !a.sxq))) return false;
+    const size_t sb = xr_stage_bytes<DOWN>(K);
+    int nstages = (int)((size_t)(190 * 1024) / sb);
+    if (nstages > 8) nstages = 8;
+    if (nstages < 2) return false;
+    const size_t smem = sb * nstages;
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(k_expert_rows<DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
+    const int grid = sm_count();
+    profile_launch(DOWN ? "k_expert_rows_down" : "k_expert_rows_gateup", st, [&] { k_expert_rows<DOWN><<<grid, XR_THREADS, smem, st>>>(a, nstages); return 0; });
+    return true;
+}
+bool launch_expert_rows_gateup(const ExpertArgs& a, cudaStream_t st) { return launch_expert_rows_t<false>(a, st); }
+bool launch_expert_rows_down(const ExpertArgs& a, cudaStream_t st) { return launch_expert_rows_t<true>(a, st); }
+
+// ================================================================================ combine
+// grid (M), 256 threads:
+// out/resid[m] (+)= sum_k fp16(d[m*topk + k] * score[m,k]) (ascending k) + sigmoid(sgl[m]) * shared[m]
+// (swift/Sources/QwispCore/SeedlessFusedVerify.swift:462-484, SeedlessMetalForward.swift:1024-1028)
+__global__ void __launch_bounds__(256) k_moe_combine(const __half* dbuf, const __half* shared_rows, const __half* scores, const __half* sgl,
+                                                     int H, int topk, __half* resid, __half* out) {
+    const int m = blockIdx.x;
+    for (int n = threadIdx.x; n < H; n += blockDim.x) {
+        __half acc = f2h(0.0f);
+        for (int k = 0; k < topk; ++k)
+            acc = hadd_rn(acc, hmul_rn(__ldcg(dbuf + (size_t)(m * topk + k) * H + n), scores[m * topk + k]));
+        const __half res = hadd_rn(acc, hmul_rn(sigmoid_h(sgl[m]), __ldcg(shared_rows + (size_t)m * H + n)));
+        if (resid) resid[(size_t)m * H + n] = hadd_rn(resid[(size_t)m * H + n], res);
+        else out[(size_t)m * H + n] = res;
+    }
+}
+void launch_moe_combine(const __half* dbuf, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,
+                        __half* resid, __half* out, cudaStream_t st) {
+    profile_launch("k_moe_combine", st, [&] { k_moe_combine<<<M, 256, 0, st>>>(dbuf, shared_rows, scores, sgl, H, topk, resid, out); return 0; });
+}
+
+}  // namespace sl

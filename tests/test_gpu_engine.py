@@ -65,7 +65,7 @@ def test_mini_logits_within_tolerance(mini_engine, mini_oracle):
     sg.close()
 
 
-@pytest.mark.parametrize("plan", [[1], [2], [9], [17], [9, 3]])
+@pytest.mark.parametrize("plan", [[1], [2], [9], [17], [9, 3], [41]])
 def test_rows_equal_sequential(tiny_engine, plan):
     """verify_forward_rows_bitexact: an M-row step is bit-identical to M single-row steps,
     including the caches it leaves (checked through the tokens of two further steps)."""
@@ -82,6 +82,40 @@ def test_rows_equal_sequential(tiny_engine, plan):
     ta, tb = a.step_argmax(toks[pos:pos + 3]), b.step_argmax(toks[pos:pos + 3])
     assert np.array_equal(ta, tb)
     a.close(); b.close()
+
+
+def test_many_row_kernels_equal_pass_kernels():
+    """Calls with more than 8 rows run the many-row kernels (weights dequantised once per block of rows, experts
+    without CTA-wide barriers); SL_FLAG_PASS_KERNELS walks the same rows in passes of 8 with the one-to-eight-row
+    kernels.  Both must give the same bits: logits of a 37-row call, the state it leaves, and 12 lanes batched."""
+    import qwisp_b200 as Q
+    V = MINI["vocab"]
+    ea, eb = gpu_engine(MINI), gpu_engine(MINI, flags=Q._lib.SL_FLAG_PASS_KERNELS)
+    try:
+        toks = prompt(V, 37 + 19, "manyrows")
+        a, b = ea.stream(128), eb.stream(128)
+        la, lb = a.step_logits(toks[:37]), b.step_logits(toks[:37])
+        assert np.array_equal(la.view(np.uint16), lb.view(np.uint16))
+        la, lb = a.step_logits(toks[37:]), b.step_logits(toks[37:])
+        assert np.array_equal(la.view(np.uint16), lb.view(np.uint16))
+        assert np.array_equal(a.state_save(), b.state_save())
+        # 12 lanes with different histories, 3 batched steps
+        lanes_a, lanes_b, cur_a, cur_b = [], [], [], []
+        for i in range(12):
+            p = prompt(V, 2 + (i * 5) % 11, f"manyrows.lane{i}")
+            sa, sb = ea.stream(64), eb.stream(64)
+            cur_a.append(int(sa.step_argmax(p)[-1])); cur_b.append(int(sb.step_argmax(p)[-1]))
+            lanes_a.append(sa); lanes_b.append(sb)
+        assert cur_a == cur_b
+        for _ in range(3):
+            cur_a = [int(t) for t in ea.batch_step_argmax(lanes_a, cur_a)]
+            cur_b = [int(t) for t in eb.batch_step_argmax(lanes_b, cur_b)]
+            assert cur_a == cur_b
+        for sa, sb in zip(lanes_a, lanes_b):
+            assert np.array_equal(sa.state_save(), sb.state_save())
+        assert not ea.gpu_fault() and not eb.gpu_fault()
+    finally:
+        ea.close(); eb.close()
 
 
 @pytest.mark.parametrize("K", [2, 3, 8])

@@ -448,7 +448,7 @@ def test_sampler_distribution_matches_softmax(mini_engine):
         assert (full == 0).all()
 
 
-@pytest.mark.parametrize("M,K,N", [(32, 2048, 256), (70, 2048, 4096), (5, 512, 128), (64, 4096, 2048)])
+@pytest.mark.parametrize("M,K,N", [(32, 2048, 256), (70, 2048, 4096), (5, 512, 128), (64, 4096, 2048), (300, 1024, 208), (257, 256, 16)])
 def test_tensor_core_gemm_matches_gemv_and_oracle(M, K, N):
     """The tcgen05/TMEM GEMM for many rows against the GEMV form on the same device buffers (fp16
     rounding apart) and against the CPU oracle's qmm4 (tolerance of BASELINE.json)."""
@@ -478,7 +478,7 @@ def test_tensor_core_gemm_matches_gemv_and_oracle(M, K, N):
     rep_g = f16_report(g2, g1)
     print(f"tc gemm M={M} K={K} N={N}: vs oracle {rep_o}  vs gemv {rep_g}")
     assert np.isfinite(g2.astype(np.float32)).all()
-    assert rep_o["max_abs"] <= TOL and rep_g["max_abs"] <= 4e-3
+    assert rep_o["max_abs"] <= TOL and rep_g["max_abs"] <= 1e-2      # one fp16 rounding per dequantised weight: ~1e-3 of the row norm
 
 
 def test_sampler_matches_golden():
