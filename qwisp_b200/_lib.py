@@ -20,6 +20,7 @@ class SeedlessError(RuntimeError):
 
 
 SL_FLAG_NO_GRAPH, SL_FLAG_NO_PDL, SL_FLAG_STEP_KERNEL, SL_FLAG_SPLIT_EXPERTS, SL_FLAG_ROUTE_IN_ROUTER, SL_FLAG_L2_PREFETCH = 1, 2, 4, 8, 16, 32
+SL_FLAG_PASS_KERNELS = 64
 
 
 class SlConfig(C.Structure):

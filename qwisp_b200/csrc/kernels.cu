@@ -1122,58 +1122,6 @@ static void launch_expert_d(const ExpertArgs& a, int nslots, cudaStream_t st, bo
 void launch_expert_gateup(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { launch_expert_d<false>(a, nslots, st, pdl); }
 void launch_expert_down(const ExpertArgs& a, int nslots, cudaStream_t st, bool pdl) { launch_expert_d<true>(a, nslots, st, pdl); }
 
-// ---- expert-parallel helpers ----
-// One CTA: pairs (row, k) whose expert lies in [e0, e1) grouped by expert, in the format the expert
-// kernels read.  Within an expert the pairs keep ascending pair order (deterministic).
-__global__ void __launch_bounds__(256) k_build_lists(const int* inds, int npairs, int e0, int e1, MoeLists lists) {
-    __shared__ int s_cnt[256], s_off[256];
-    const int tid = threadIdx.x;
-    s_cnt[tid] = 0; s_off[tid] = 0;
-    __syncthreads();
-    for (int i = tid; i < npairs; i += 256) { int ex = inds[i]; if (ex >= e0 && ex < e1) atomicAdd(&s_cnt[ex], 1); }
-    __syncthreads();
-    if (tid == 0) {
-        int slot = 0, off = 0;
-        for (int ex = e0; ex < e1; ++ex)
-            if (s_cnt[ex] > 0) {
-                lists.slot_expert[slot] = ex; lists.slot_off[slot] = off; lists.slot_cnt[slot] = s_cnt[ex];
-                s_off[ex] = off; off += s_cnt[ex]; ++slot;
-            }
-        *lists.n_active = slot;
-    }
-    __syncthreads();
-    // one thread per expert walks the pairs in order: no atomics, so the order inside a slot is fixed
-    if (tid >= e0 && tid < e1 && s_cnt[tid] > 0) {
-        int pos = s_off[tid];
-        for (int i = 0; i < npairs; ++i) if (inds[i] == tid) lists.pairs[pos++] = i;
-    }
-}
-void launch_build_lists(const int* inds, int npairs, int e0, int e1, MoeLists lists, cudaStream_t st) {
-    ProfScope ps("k_build_lists", 0.0, st);
-    k_build_lists<<<1, 256, 0, st>>>(inds, npairs, e0, e1, lists);
-    COUNT_LAUNCH();
-}
-// grid (M), 256 threads: the combine the down kernel otherwise does in its last CTAs
-// (SeedlessFusedVerify.swift:462-484, SeedlessMetalForward.swift:1024-1028)
-__global__ void __launch_bounds__(256) k_moe_combine(const __half* dbuf, int pair0, int shared0, const __half* scores, const __half* sgl,
-                                                     int H, int topk, __half* resid, __half* out) {
-    const int m = blockIdx.x;
-    for (int n = threadIdx.x; n < H; n += blockDim.x) {
-        __half acc = f2h(0.0f);
-        for (int k = 0; k < topk; ++k)
-            acc = hadd_rn(acc, hmul_rn(__ldcg(dbuf + (size_t)(pair0 + m * topk + k) * H + n), scores[m * topk + k]));
-        __half res = hadd_rn(acc, hmul_rn(sigmoid_h(sgl[m]), __ldcg(dbuf + (size_t)(shared0 + m) * H + n)));
-        if (resid) resid[(size_t)m * H + n] = hadd_rn(resid[(size_t)m * H + n], res);
-        else out[(size_t)m * H + n] = res;
-    }
-}
-void launch_moe_combine(const __half* dbuf, int pair0, int shared0, const __half* scores, const __half* sgl, int M, int H, int topk,
-                        __half* resid, __half* out, cudaStream_t st) {
-    ProfScope ps("k_moe_combine", 0.0, st);
-    k_moe_combine<<<M, 256, 0, st>>>(dbuf, pair0, shared0, scores, sgl, H, topk, resid, out);
-    COUNT_LAUNCH();
-}
-
 // ============================================================================================
 // Gated-delta-net core: causal conv1d + SiLU, q/k l2-style norm + scale, beta / decay, the
 // recurrent state update and readout, for all rows of a segment in sequence.

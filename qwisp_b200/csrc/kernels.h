@@ -195,11 +195,7 @@ void launch_expert_down(const ExpertArgs& a, int nslots, cudaStream_t st, bool p
 // batch-1 decode: gate/up and down in ONE launch (a per-slot barrier between the phases); false if the shapes do not fit it
 bool launch_expert_fused(const ExpertArgs& a, cudaStream_t st, bool pdl);
 bool expert_fused_applicable(const ExpertArgs& a);      // the shape test launch_expert_fused applies
-// expert-parallel helpers: group the (row, k) pairs of `npairs/topk` rows whose expert lies in [e0, e1)
-void launch_build_lists(const int* inds, int npairs, int e0, int e1, MoeLists lists, cudaStream_t st);
-// out/resid[m] (+)= sum_k fp16(d[pair0 + m*topk + k] * score[m,k]) (ascending k) + sigmoid(sgl[m]) * d[shared0 + m]
-void launch_moe_combine(const __half* dbuf, int pair0, int shared0, const __half* scores, const __half* sgl, int M, int H, int topk,
-                        __half* resid, __half* out, cudaStream_t st);
+// expert-parallel exchange (ep_exchange.cu)
 void launch_ep_lists(const EpPeers& P, int npairs, int e0, int e1, const MoeLists& lists, int layer, unsigned* err, cudaStream_t st);
 void launch_ep_combine(const EpPeers& P, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,
                        __half* resid, __half* out, int layer, unsigned* err, cudaStream_t st);
