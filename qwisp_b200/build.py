@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libseedless_b200.so")
-SOURCES = ["synth.cu", "kernels.cu", "step_persistent.cu", "ep_exchange.cu", "rows_kernels.cu", "sampler.cu", "gemm_tc.cu", "engine.cu"]
+SOURCES = ["synth.cu", "kernels.cu", "step_persistent.cu", "ep_exchange.cu", "rows_kernels.cu", "attn_prefill.cu", "sampler.cu", "gemm_tc.cu", "engine.cu"]
 HEADERS = ["common.cuh", "gemv.cuh", "mixer_math.cuh", "route.cuh", "kernels.h", os.path.join("..", "..", "include", "seedless_b200.h")]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -64,6 +64,7 @@ struct sl_engine {
     __half *hbuf = nullptr, *dbuf = nullptr, *normed = nullptr, *qrot = nullptr, *opx = nullptr, *opy = nullptr;
     // many-row kernels: prepared rows of a dense projection / of the experts' input, their group sums, chunk sums of the SwiGLU rows
     __half *xq = nullptr, *xq_p = nullptr; float *sxq = nullptr, *sx_p = nullptr, *csum = nullptr;
+    __half *gdn_qk = nullptr, *gdn_vc = nullptr; float2* gdn_gb = nullptr;    // between k_gdn_prep and k_gdn_scan
     __half* logits = nullptr; int logits_rows = 0;
     int* inds = nullptr; MoeLists lists{};
     float *part_o = nullptr, *part_ml = nullptr, *pval = nullptr;
@@ -293,6 +294,9 @@ int32_t build_runtime(sl_engine* e) {
         if ((rc = dalloc(e, &e->xq_p, (size_t)R * H))) return rc;
         if ((rc = dalloc(e, &e->sx_p, (size_t)R * (H / 64)))) return rc;
         if ((rc = dalloc(e, &e->csum, prow * (size_t)(e->I / 8)))) return rc;
+        if ((rc = dalloc(e, &e->gdn_qk, (size_t)R * 2 * e->keyDim))) return rc;
+        if ((rc = dalloc(e, &e->gdn_vc, (size_t)R * e->valDim))) return rc;
+        if ((rc = dalloc(e, &e->gdn_gb, (size_t)R * c.gdn_v_heads))) return rc;
     }
     if ((rc = dalloc(e, &e->opx, (size_t)R * H))) return rc;
     if ((rc = dalloc(e, &e->opy, (size_t)R * H))) return rc;
@@ -603,7 +607,10 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
     if (!L.is_attn) {
         GdnArgs g{}; g.inproj = e->inproj; g.ld = e->gdn_in; g.conv_w = L.conv_w; g.A_log = L.A_log; g.dt_bias = L.dt_bias;
         g.Hk = c.gdn_k_heads; g.Hv = c.gdn_v_heads; g.eps = c.rms_eps; g.tab = e->tab; g.gdn_index = L.type_index; g.segs = e->segs; g.y = e->mix;
-        launch_gdn_core(g, nsegs, st, e->use_pdl);
+        g.row_seg = e->row_seg; g.qk = e->gdn_qk; g.vc = e->gdn_vc; g.gb = e->gdn_gb;
+        // segments of many rows: the state-independent part for all rows side by side, then the bare recurrence (same bits)
+        if (e->use_rows && M >= 16 && M >= 2 * nsegs) launch_gdn_rows(g, M, nsegs, st);
+        else launch_gdn_core(g, nsegs, st, e->use_pdl);
         o.x = e->mix; o.ldx = e->valDim; o.nw = L.gdn_norm; o.nw32 = L.gdn_norm32; o.z = e->inproj + e->convDim; o.ldz = e->gdn_in;
         launch_dense(L.gdn_norm32 ? PRO_NORMGATE32 : PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, o, st, e->use_pdl);
     } else {
@@ -615,7 +622,9 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
         // several rows of one stream need every row's K/V in the arena before any of them attends
         const bool self_prep = (M == nsegs) && (row_pos_override == nullptr || M == 1);
         if (!self_prep) launch_attn_prep(a, st);
-        launch_attn_fused(a, self_prep, e->att_counters, st, e->use_pdl && self_prep);
+        // prefill mode, one stream's chunk: the keys are walked once for 64 rows at a time on the tensor cores
+        if (!(e->hybrid && !self_prep && M >= 32 && launch_attn_prefill(a, nsegs, st)))
+            launch_attn_fused(a, self_prep, e->att_counters, st, e->use_pdl && self_prep);
         o.x = e->mix; o.ldx = e->attn_out;
         launch_dense(PRO_PLAIN, resid ? EPI_RESID : EPI_STORE, o, st, e->use_pdl);
     }

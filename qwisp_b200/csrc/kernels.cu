@@ -520,7 +520,7 @@ void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H
 // (SeedlessMetalForward.swift:378-434): per block accum = sum of x_i * byte_i (i ascending), the lane adds
 // scale * accum + (sum of x_i) * bias, lanes are summed by the butterfly.
 template <bool MULTI, bool Q8>
-__global__ void __launch_bounds__(256) k_moe_router(RouterArgs a) {
+__global__ void __launch_bounds__(256, MULTI ? 2 : 1) k_moe_router(RouterArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __half* ps = reinterpret_cast<__half*>(smem);            // [8][H]
     float* sm8 = reinterpret_cast<float*>(ps + 8 * a.H);
@@ -1222,6 +1222,133 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
         if (tid < 16) hist_out[(size_t)j * convDim + ch_v] = f2h(xval(idx, ch_v));
     }
 }
+// ---- segments of many rows (prompt chunks, verify rows): the same arithmetic in two kernels ----
+// k_gdn_prep   everything that does not depend on the state, for all rows side by side: conv + SiLU of every channel, the
+//              q/k norms and scales, decay and beta, the conv history the call leaves.  grid (Hk + Hv, M), 128 threads:
+//              CTAs [0, Hk) own a key head's q and k channels, CTAs [Hk, Hk + Hv) a value head's v channels and gates.
+// k_gdn_scan   the recurrence alone, rows of a segment in sequence, the next rows' operands requested four rows ahead.
+//              Same grid and state ownership as k_gdn_core.
+// Every value is formed by the same functions in the same order as in k_gdn_core, so the outputs and the state are
+// identical bit for bit; the split only removes the per-row latency chain (and the 16-fold recomputation of q / k).
+__global__ void __launch_bounds__(128) k_gdn_prep(GdnArgs a) {
+    __shared__ float red_s[8];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m = blockIdx.y;
+    const SegDesc seg = a.segs[a.row_seg[m]];
+    const int tt = m - seg.row0;
+    const int keyDim = a.Hk * GDN_DK, valDim = a.Hv * GDN_DV, convDim = 2 * keyDim + valDim;
+    const int side = a.tab.parity[seg.slot];
+    const __half* hist_in = a.tab.conv_hist + (size_t)seg.slot * a.tab.hist_stride_stream + (size_t)side * a.tab.hist_stride_side +
+                            (size_t)a.gdn_index * a.tab.hist_stride_layer;
+    __half* hist_out = a.tab.conv_hist + (size_t)seg.slot * a.tab.hist_stride_stream + (size_t)(side ^ 1) * a.tab.hist_stride_side +
+                       (size_t)a.gdn_index * a.tab.hist_stride_layer;
+    auto xval = [&](int idx, int ch) -> float {               // row idx of [hist(3) | rows of the segment]
+        if (idx < CONV_K - 1) return h2f(hist_in[(size_t)idx * convDim + ch]);
+        return h2f(a.inproj[(size_t)(seg.row0 + idx - (CONV_K - 1)) * a.ld + ch]);
+    };
+    auto conv = [&](int ch) -> float {
+        const float4 w = *reinterpret_cast<const float4*>(a.conv_w + (size_t)ch * 4);
+        return gdn_conv_silu(xval(tt + 0, ch), xval(tt + 1, ch), xval(tt + 2, ch), xval(tt + 3, ch), w);
+    };
+    const bool last = (tt == seg.nrows - 1);
+    if ((int)blockIdx.x < a.Hk) {
+        const int hk = blockIdx.x, ch_q = hk * GDN_DK + tid, ch_k = keyDim + hk * GDN_DK + tid;
+        const float qc = conv(ch_q), kc = conv(ch_k);
+        const float sq = warp_sum(qc * qc), sk = warp_sum(kc * kc);
+        if (lane == 0) { red_s[warp] = sq; red_s[4 + warp] = sk; }
+        __syncthreads();
+        const float iq = gdn_head_inv(red_s[0], red_s[1], red_s[2], red_s[3], a.eps);
+        const float ik = gdn_head_inv(red_s[4], red_s[5], red_s[6], red_s[7], a.eps);
+        a.qk[(size_t)m * 2 * keyDim + hk * GDN_DK + tid] = f2h(gdn_scale_q(qc, iq));              // exact: the value is an fp16 product
+        a.qk[(size_t)m * 2 * keyDim + keyDim + hk * GDN_DK + tid] = f2h(gdn_scale_k(kc, ik));
+        if (last)
+            for (int j = 0; j < CONV_K - 1; ++j) {
+                hist_out[(size_t)j * convDim + ch_q] = f2h(xval(seg.nrows + j, ch_q));
+                hist_out[(size_t)j * convDim + ch_k] = f2h(xval(seg.nrows + j, ch_k));
+            }
+    } else {
+        const int hv = blockIdx.x - a.Hk, ch_v = 2 * keyDim + hv * GDN_DV + tid;
+        a.vc[(size_t)m * valDim + hv * GDN_DV + tid] = f2h(conv(ch_v));                            // exact: conv + SiLU is rounded to fp16
+        if (tid == 0) {
+            const __half bh = a.inproj[(size_t)m * a.ld + convDim + valDim + hv];
+            const __half ah = a.inproj[(size_t)m * a.ld + convDim + valDim + a.Hv + hv];
+            float g, beta;
+            gdn_gate(bh, ah, a.A_log[hv], a.dt_bias[hv], g, beta);
+            a.gb[(size_t)m * a.Hv + hv] = make_float2(g, beta);
+        }
+        if (last)
+            for (int j = 0; j < CONV_K - 1; ++j) hist_out[(size_t)j * convDim + ch_v] = f2h(xval(seg.nrows + j, ch_v));
+    }
+}
+struct GdnRowOps { uint2 k, q, v; float2 gb; };     // 4 halves of k and q (this lane's dk), 4 halves of v (this warp's rows), (decay, beta)
+__global__ void __launch_bounds__(128) k_gdn_scan(GdnArgs a) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int dvt = blockIdx.x, hv = blockIdx.y;
+    const SegDesc seg = a.segs[blockIdx.z];
+    const int hk = hv / (a.Hv / a.Hk);
+    const int keyDim = a.Hk * GDN_DK, valDim = a.Hv * GDN_DV;
+    const int side = a.tab.parity[seg.slot];
+    const float* S_in = a.tab.gdn_state + (size_t)seg.slot * a.tab.state_stride_stream + (size_t)side * a.tab.state_stride_side +
+                        (size_t)a.gdn_index * a.tab.state_stride_layer + ((size_t)hv * GDN_DV + dvt * 16) * GDN_DK;
+    float* S_out = a.tab.gdn_state + (size_t)seg.slot * a.tab.state_stride_stream + (size_t)(side ^ 1) * a.tab.state_stride_side +
+                   (size_t)a.gdn_index * a.tab.state_stride_layer + ((size_t)hv * GDN_DV + dvt * 16) * GDN_DK;
+    float4 S[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) S[i] = *reinterpret_cast<const float4*>(S_in + (size_t)(warp * 4 + i) * GDN_DK + lane * 4);
+    auto load = [&](GdnRowOps& o, int tt) {
+        const size_t row = (size_t)(seg.row0 + tt);
+        o.q = __ldcg(reinterpret_cast<const uint2*>(a.qk + row * 2 * keyDim + hk * GDN_DK + lane * 4));
+        o.k = __ldcg(reinterpret_cast<const uint2*>(a.qk + row * 2 * keyDim + keyDim + hk * GDN_DK + lane * 4));
+        o.v = __ldcg(reinterpret_cast<const uint2*>(a.vc + row * valDim + hv * GDN_DV + dvt * 16 + warp * 4));
+        o.gb = __ldcg(a.gb + row * a.Hv + hv);
+    };
+    auto h4 = [](uint2 u) -> float4 {
+        const __half2 lo = *reinterpret_cast<const __half2*>(&u.x), hi = *reinterpret_cast<const __half2*>(&u.y);
+        const float2 a2 = __half22float2(lo), b2 = __half22float2(hi);
+        return make_float4(a2.x, a2.y, b2.x, b2.y);
+    };
+    constexpr int D = 4;                                     // rows in flight
+    GdnRowOps buf[D];
+#pragma unroll
+    for (int u = 0; u < D; ++u) if (u < seg.nrows) load(buf[u], u);
+    for (int t0 = 0; t0 < seg.nrows; t0 += D) {
+#pragma unroll
+        for (int u = 0; u < D; ++u) {
+            const int tt = t0 + u;
+            if (tt < seg.nrows) {
+                const GdnRowOps o = buf[u];
+                if (tt + D < seg.nrows) load(buf[u], tt + D);
+                const float4 kq = h4(o.k), qq = h4(o.q), vv = h4(o.v);
+                const float vs[4] = {vv.x, vv.y, vv.z, vv.w};
+                __half outh[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float4 s = S[i];
+                    outh[i] = f2h(gdn_row_step(s, o.gb.x, kq, qq, vs[i], o.gb.y));
+                    S[i] = s;
+                }
+                if (lane == 0) {
+                    uint2 pk;
+                    pk.x = (unsigned)__half_as_ushort(outh[0]) | ((unsigned)__half_as_ushort(outh[1]) << 16);
+                    pk.y = (unsigned)__half_as_ushort(outh[2]) | ((unsigned)__half_as_ushort(outh[3]) << 16);
+                    *reinterpret_cast<uint2*>(a.y + (size_t)(seg.row0 + tt) * valDim + hv * GDN_DV + dvt * 16 + warp * 4) = pk;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(S_out + (size_t)(warp * 4 + i) * GDN_DK + lane * 4) = S[i];
+}
+void launch_gdn_rows(const GdnArgs& a, int M, int nsegs, cudaStream_t st) {
+    {
+        ProfScope ps("k_gdn_prep", (double)M * (2 * a.Hk * GDN_DK + a.Hv * GDN_DV) * 4, st);
+        k_gdn_prep<<<dim3((unsigned)(a.Hk + a.Hv), (unsigned)M), 128, 0, st>>>(a);
+        COUNT_LAUNCH();
+    }
+    ProfScope ps("k_gdn_scan", (double)nsegs * a.Hv * GDN_DV * GDN_DK * 8, st);
+    k_gdn_scan<<<dim3(8, (unsigned)a.Hv, (unsigned)nsegs), 128, 0, st>>>(a);
+    COUNT_LAUNCH();
+}
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl) {
     dim3 grid(8, a.Hv, nsegs);
     ProfScope ps("k_gdn_core", (double)nsegs * a.Hv * GDN_DV * GDN_DK * 8, st);
@@ -1240,17 +1367,6 @@ void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl) {
 // (prep: SeedlessFusedVerify.swift:1183-1360; attention: SeedlessMetalForward.swift:4922-4989;
 //  output gate: SeedlessMetalForward.swift:1012-1022)
 // ============================================================================================
-__device__ __forceinline__ int row_position(const AttnArgs& a, int m) {
-    if (a.row_pos_override) return a.row_pos_override[m];
-    const SegDesc seg = a.segs[a.row_seg[m]];
-    return a.tab.kv_len[seg.slot] + a.row_off[m];
-}
-__device__ __forceinline__ __half* kv_ptr(const AttnArgs& a, int slot, int pos, int which, int kvh) {
-    int page = a.tab.page_table[(size_t)slot * a.tab.max_pages + pos / a.page_size];
-    size_t page_elems = (size_t)a.n_attn_layers * 2 * a.KV * a.page_size * ATT_D;
-    return a.kv_pool + (size_t)page * page_elems +
-           ((((size_t)a.attn_index * 2 + which) * a.KV + kvh) * a.page_size + (pos % a.page_size)) * ATT_D;
-}
 // grid (NH + 2*KV, M), 32 threads: one warp per (row, head); lane owns dims 8*lane..8*lane+7
 __global__ void __launch_bounds__(32) k_attn_prep(AttnArgs a) {
     const int m = blockIdx.y, hidx = blockIdx.x, lane = threadIdx.x;

@@ -108,6 +108,11 @@ struct GdnArgs {
     StreamTable tab; int gdn_index;      // which GDN layer (index among GDN layers)
     const SegDesc* segs;
     __half* y;                           // [M][Hv*128]
+    // two-kernel form for segments of many rows: row -> segment, and the scratch between the kernels
+    const int* row_seg = nullptr;
+    __half* qk = nullptr;                // [M][2*Hk*128] normed, scaled q | k
+    __half* vc = nullptr;                // [M][Hv*128] conv + SiLU of v
+    float2* gb = nullptr;                // [M][Hv] (decay, beta)
 };
 
 struct AttnArgs {
@@ -125,6 +130,21 @@ struct AttnArgs {
     __half* gated;                       // [M][NH*256]
     int M;
 };
+
+#ifdef __CUDACC__
+// position of row m; address of (stream slot, position, K=0 / V=1, kv head) in the paged arena
+__device__ __forceinline__ int row_position(const AttnArgs& a, int m) {
+    if (a.row_pos_override) return a.row_pos_override[m];
+    const SegDesc seg = a.segs[a.row_seg[m]];
+    return a.tab.kv_len[seg.slot] + a.row_off[m];
+}
+__device__ __forceinline__ __half* kv_ptr(const AttnArgs& a, int slot, int pos, int which, int kvh) {
+    int page = a.tab.page_table[(size_t)slot * a.tab.max_pages + pos / a.page_size];
+    size_t page_elems = (size_t)a.n_attn_layers * 2 * a.KV * a.page_size * ATT_D;
+    return a.kv_pool + (size_t)page * page_elems +
+           ((((size_t)a.attn_index * 2 + which) * a.KV + kvh) * a.page_size + (pos % a.page_size)) * ATT_D;
+}
+#endif
 
 struct StepEndArgs {
     StreamTable tab; const SegDesc* segs; int nsegs;
@@ -201,6 +221,9 @@ void launch_ep_combine(const EpPeers& P, const __half* shared_rows, const __half
                        __half* resid, __half* out, int layer, unsigned* err, cudaStream_t st);
 void launch_ep_step_end(unsigned* ctr, cudaStream_t st);
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl);
+// prefill-mode attention of one stream's chunk on the tensor cores (after launch_attn_prep); false: call not covered
+bool launch_attn_prefill(const AttnArgs& a, int nsegs, cudaStream_t st);
+void launch_gdn_rows(const GdnArgs& a, int M, int nsegs, cudaStream_t st);   // the same result by k_gdn_prep + k_gdn_scan (needs the scratch fields)
 void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
 // q/k prep (when every row is its stream's only row) + split-KV decode + merge in one launch; counters: M*KV zeros
 void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStream_t st, bool pdl);
