@@ -506,6 +506,19 @@ void pf_q4(PfList& pf, int i, const Q4R& q, size_t max_bytes = (size_t)48 << 20)
     if (i + 1 < 6 && gb) { pf.p[i + 1] = q.sr; pf.bytes[i + 1] = (unsigned)gb; }
 }
 
+// Router of an M-row call.  Many rows: the rows are normed once (k_final_norm), then the many-row router (logits kernel +
+// routing / pair-list kernel, same bits); otherwise the one-kernel router.
+void enqueue_router(sl_engine* e, const RouterArgs& ra, int M, bool pdl) {
+    cudaStream_t st = e->stream;
+    if (M > 8 && e->use_rows && !ra.no_route && e->E <= 256 && ra.norm_w && ra.ldh == e->H) {
+        launch_final_norm(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, st);
+        RouterArgs rb = ra; rb.h = ra.p; rb.ldh = e->H; rb.norm_w = nullptr;
+        if (launch_router_rows(rb, st)) return;
+        // not covered: the one-kernel router norms the rows again from the original input
+    }
+    launch_router(ra, st, pdl);
+}
+
 // Expert-parallel MoE block of a decode step.  Every rank runs the same number M of rows (its own streams);
 // rank r owns experts [ep_e0, ep_e1).  Per layer (kernels of ep_exchange.cu, no collective):
 //   router on the local rows, its last CTA storing the normed rows and routing indices into every rank's gather
@@ -523,7 +536,7 @@ int32_t enqueue_moe_ep(sl_engine* e, const LayerW& L, RouterArgs ra, int M, __ha
     ra.inds = e->inds + (size_t)r * M * topk;
     for (int d = 0; d < R; ++d) { ra.epd.pbuf[d] = P.pbuf[d]; ra.epd.ibuf[d] = P.ibuf[d]; ra.epd.sig.flags[d] = P.flags[d]; }
     ra.epd.sig.ctr = P.ctr; ra.epd.sig.world = R; ra.epd.sig.rank = r; ra.epd.sig.layer = layer;
-    launch_router(ra, st, false);                      // its last CTA sends the rows and indices to every rank
+    enqueue_router(e, ra, M, false);                   // its last CTA sends the rows and indices to every rank
     launch_ep_lists(P, T * topk, e->ep_e0, e->ep_e1, e->lists, layer, e->err_flag, st);
     ExpertArgs ea{}; ea.gu = L.r_gu; ea.down = L.r_down; ea.sh_gu = L.r_sh_gu; ea.sh_down = L.r_sh_down;
     ea.lists = e->lists; ea.p = P.pbuf[r]; ea.hbuf = e->hbuf; ea.dbuf = e->dbuf; ea.M = T; ea.H = H; ea.I = e->I; ea.topk = topk;
@@ -570,7 +583,7 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     // batch-1 decode: the router stops at the logits and the fused expert kernel's CTAs route the row themselves
     ra.no_route = (fused && e->use_route_in_experts) ? 1 : 0;
     ea.route_here = ra.no_route;
-    launch_router(ra, st, e->use_pdl);
+    enqueue_router(e, ra, M, e->use_pdl);
     if (fused && launch_expert_fused(ea, st, e->use_pdl)) return;                      // one launch for gate/up + down
     if (M > 8 && e->E <= 256 && e->use_rows) {
         // many rows: the normed rows are prepared once, the experts run without CTA-wide barriers, the combine is its own kernel

@@ -21,6 +21,7 @@
 //   k_moe_combine    weighted sum of a row's top-k expert rows in ascending k + shared expert + residual.
 #include "kernels.h"
 #include "gemv.cuh"
+#include "route.cuh"
 
 namespace sl {
 
@@ -470,6 +471,171 @@ static bool launch_expert_rows_t(const ExpertArgs& a, cudaStream_t st) {
 }
 bool launch_expert_rows_gateup(const ExpertArgs& a, cudaStream_t st) { return launch_expert_rows_t<false>(a, st); }
 bool launch_expert_rows_down(const ExpertArgs& a, cudaStream_t st) { return launch_expert_rows_t<true>(a, st); }
+
+// ================================================================================ router for many rows
+// k_router_rows   logits of all rows: a CTA keeps 8 router rows (or the shared gate) in registers and walks the row
+//                 groups of 8, whose normed rows arrive in shared memory by cp.async two groups ahead of their use.
+//                 The dot product is the one of k_moe_router (lane l owns 8 consecutive inputs of every 256-wide block,
+//                 sequential f32 accumulate, butterfly over the lanes), so the logits are the same bits.
+// k_route_rows    one warp per row: top-k + gates (route_row_warp); the last CTA groups the (row, k) pairs by expert with
+//                 a parallel scan (or, expert-parallel, sends rows and indices to every rank).
+// Input rows are already normed (k_final_norm), so no CTA repeats the norm.
+template <bool Q8>
+__global__ void __launch_bounds__(256, 2) k_router_rows(RouterArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];                   // [2][8][H] halves
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nblk = a.H >> 8;
+    const bool tail = (blockIdx.x == gridDim.x - 1);
+    const int e = blockIdx.x * 8 + warp;
+    const bool wvalid = tail ? (warp == 0) : (e < a.E);
+    uint4 wreg[16]; uint2 qreg[16]; __half2 sbreg[16];
+    if constexpr (Q8) {
+        const uint8_t* qrow = tail ? a.sg_q8 : (a.router_q8 + (size_t)e * a.H);
+        const __half* srow = tail ? a.sg_qs : (a.router_qs + (size_t)e * (a.H >> 6));
+        const __half* brow = tail ? a.sg_qb : (a.router_qb + (size_t)e * (a.H >> 6));
+#pragma unroll
+        for (int kb = 0; kb < 16; ++kb) {
+            const bool ok = wvalid && kb < nblk;
+            qreg[kb] = ok ? *reinterpret_cast<const uint2*>(qrow + kb * 256 + lane * 8) : make_uint2(0, 0);
+            sbreg[kb] = ok ? __halves2half2(srow[kb * 4 + (lane >> 3)], brow[kb * 4 + (lane >> 3)]) : __halves2half2(f2h(0.f), f2h(0.f));
+        }
+    } else {
+        const __half* wrow = tail ? a.shared_gate : (a.router + (size_t)e * a.H);
+#pragma unroll
+        for (int kb = 0; kb < 16; ++kb)
+            wreg[kb] = (wvalid && kb < nblk) ? *reinterpret_cast<const uint4*>(wrow + kb * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
+    }
+    const int ngroups = (a.M + 7) >> 3;
+    auto stage = [&](int rg, int b) {
+        __half* dst = reinterpret_cast<__half*>(smem) + (size_t)b * 8 * a.H;
+        const int mr = min(8, a.M - rg * 8);
+        for (int i = tid; i < mr * (a.H >> 3); i += 256) cp_async16(dst + (size_t)i * 8, a.h + (size_t)rg * 8 * a.ldh + (size_t)(i / (a.H >> 3)) * a.ldh + (size_t)(i % (a.H >> 3)) * 8);
+        cp_async_commit();
+    };
+    int it = 0;
+    if ((int)blockIdx.y < ngroups) stage(blockIdx.y, 0);
+    for (int rg = blockIdx.y; rg < ngroups; rg += gridDim.y, ++it) {
+        const int b = it & 1;
+        if (rg + (int)gridDim.y < ngroups) { stage(rg + gridDim.y, b ^ 1); cp_async_wait<1>(); } else cp_async_wait<0>();
+        __syncthreads();
+        const __half* ps = reinterpret_cast<const __half*>(smem) + (size_t)b * 8 * a.H;
+        const int m0 = rg * 8, mr = min(8, a.M - m0);
+        if (wvalid) {
+            for (int c = 0; c < mr; ++c) {
+                const __half* xrow = ps + (size_t)c * a.H;
+                float acc = 0.f;
+#pragma unroll
+                for (int kb = 0; kb < 16; ++kb) {
+                    if (kb < nblk) {
+                        const uint4 xv = *reinterpret_cast<const uint4*>(xrow + kb * 256 + lane * 8);
+                        const __half* xh = reinterpret_cast<const __half*>(&xv);
+                        if constexpr (Q8) {
+                            float sum = 0.f, accum = 0.f;
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float xf = h2f(xh[i]);
+                                const unsigned q = ((i < 4 ? qreg[kb].x : qreg[kb].y) >> (8 * (i & 3))) & 0xffu;
+                                sum = __fadd_rn(sum, xf);
+                                accum = fmaf(xf, (float)q, accum);
+                            }
+                            const float2 sb = __half22float2(sbreg[kb]);
+                            acc = __fadd_rn(acc, __fadd_rn(__fmul_rn(sb.x, accum), __fmul_rn(sum, sb.y)));
+                        } else {
+                            const __half* wh = reinterpret_cast<const __half*>(&wreg[kb]);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) acc = fmaf(h2f(xh[i]), h2f(wh[i]), acc);
+                        }
+                    }
+                }
+                const float d = warp_sum(acc);
+                if (lane == 0) { if (tail) a.sgl[m0 + c] = f2h(d); else a.logits[(size_t)(m0 + c) * a.E + e] = f2h(d); }
+            }
+        }
+        __syncthreads();                       // the buffer is refilled by the next iteration's stage()
+    }
+}
+// grid (ceil(M / 8)), 256 threads
+__global__ void __launch_bounds__(256) k_route_rows(RouterArgs a) {
+    __shared__ float s_route[8][512 + 32];
+    __shared__ int s_cnt[256], s_off[256], s_slot[256], s_cur[256], s_wsum[8], s_wact[8];
+    __shared__ int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m = blockIdx.x * 8 + warp;
+    if (m < a.M) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, s_route[warp], lane);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) { const unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid == 0) *a.counter = 0u;
+    if (a.epd.sig.world > 0) {
+        // expert-parallel: send the rank's normed rows and routing indices into every rank's gather buffers over peer
+        // memory, then raise this rank's dispatch flag there; the pair lists are built from the gathered indices
+        const EpSignal& sg = a.epd.sig;
+        const int nv = a.M * a.H / 8, ni = a.M * a.topk;
+        for (int d = 0; d < sg.world; ++d) {
+            uint4* dst = reinterpret_cast<uint4*>(a.epd.pbuf[d] + (size_t)sg.rank * a.M * a.H);
+            const uint4* src = reinterpret_cast<const uint4*>(a.p);
+            for (int i = tid; i < nv; i += 256) dst[i] = __ldcg(src + i);
+            int* di = a.epd.ibuf[d] + (size_t)sg.rank * ni;
+            for (int i = tid; i < ni; i += 256) di[i] = __ldcg(a.inds + i);
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid < sg.world) st_release_sys(sg.flags[tid] + sg.rank, ep_seq(sg.ctr, sg.layer, 0));
+        return;
+    }
+    // ---- pairs grouped by expert: counts, then slot numbers and offsets by a block scan (thread = expert)
+    s_cnt[tid] = 0; s_cur[tid] = 0;
+    __syncthreads();
+    const int npairs = a.M * a.topk;
+    for (int i = tid; i < npairs; i += 256) atomicAdd(&s_cnt[__ldcg(a.inds + i)], 1);
+    __syncthreads();
+    const int cnt = (tid < a.E) ? s_cnt[tid] : 0, act = cnt > 0 ? 1 : 0;
+    int isum = cnt, iact = act;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int o1 = __shfl_up_sync(0xffffffffu, isum, d), o2 = __shfl_up_sync(0xffffffffu, iact, d);
+        if (lane >= d) { isum += o1; iact += o2; }
+    }
+    if (lane == 31) { s_wsum[warp] = isum; s_wact[warp] = iact; }
+    __syncthreads();
+    int bsum = 0, bact = 0;
+    for (int w = 0; w < warp; ++w) { bsum += s_wsum[w]; bact += s_wact[w]; }
+    const int off = bsum + isum - cnt, slot = bact + iact - act;
+    s_off[tid] = off; s_slot[tid] = slot;
+    if (act) { a.lists.slot_expert[slot] = tid; a.lists.slot_off[slot] = off; a.lists.slot_cnt[slot] = cnt; }
+    if (tid == 255) *a.lists.n_active = slot + act;
+    __syncthreads();
+    for (int i = tid; i < npairs; i += 256) {
+        const int ex = __ldcg(a.inds + i);
+        const int pos = atomicAdd(&s_cur[ex], 1);
+        a.lists.pairs[s_off[ex] + pos] = i;
+    }
+}
+// rows already normed in a.h (ldh); E <= 256.  Returns false when the shape is not covered.
+bool launch_router_rows(const RouterArgs& a, cudaStream_t st) {
+    if (a.E > 256 || a.H % 256 || a.H > 4096 || a.norm_w) return false;
+    const size_t smem = (size_t)2 * 8 * a.H * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(k_router_rows<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(k_router_rows<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        configured = true;
+    }
+    const int ngroups = (a.M + 7) / 8;
+    const int gx = (a.E + 7) / 8 + 1;
+    int gy = (2 * sm_count() + gx - 1) / gx; if (gy > ngroups) gy = ngroups; if (gy < 1) gy = 1;
+    const dim3 grid((unsigned)gx, (unsigned)gy);
+    const bool q8 = a.router_q8 != nullptr;
+    profile_launch("k_router_rows", st, [&] {
+        if (q8) k_router_rows<true><<<grid, 256, smem, st>>>(a); else k_router_rows<false><<<grid, 256, smem, st>>>(a);
+        return 0;
+    });
+    profile_launch("k_route_rows", st, [&] { k_route_rows<<<ngroups, 256, 0, st>>>(a); return 0; });
+    return true;
+}
 
 // ================================================================================ combine
 // grid (M), 256 threads:
