@@ -270,6 +270,67 @@ def measure_prefill(Q, torch, layers, n_tokens=PREFILL_TOKENS, chunk=1024, reps=
             "kernel_shares": shares, "gpu_fault": fault}
 
 
+CFG5_STREAMS, CFG5_DECODE, CFG5_BUDGET, CFG5_PREFIX = 64, 256, 4096, 1024
+WORKLOAD_CFG5 = ("cfg5 as BASELINE.json states it, one GPU: 64 requests submitted at once to the continuous-batching scheduler "
+                 "(64 slots, 4096-token budget per round, head-of-line admission on the KV page gate), 256 greedy tokens each; "
+                 "even-numbered requests = one common seeded 1024-token prefix + a seeded tail of 128..1024 tokens, odd-numbered "
+                 "requests = seeded random prompts of 128..2048 tokens; prompt chunks of 1024 tokens in prefill mode; the "
+                 "shared-prefix store (RAM, 2 GiB) captures the state at the exact shared boundary and later requests restore "
+                 "it; the conversation store is off")
+
+
+def measure_cfg5(Q, torch, layers):
+    """The whole cfg5 job through ContinuousScheduler + LaneBatchSlots on one GPU, wall clock around run_to_completion
+    (host tokens in, host tokens out).  Decode throughput = tokens emitted by batched decode steps / the time spent in
+    them (each step ends with a synchronisation); end-to-end = all emitted tokens / wall clock."""
+    import numpy as np
+    rng = np.random.RandomState(5)
+    lens = [int(rng.randint(128, 2049)) for _ in range(CFG5_STREAMS)]
+    seq_cap = 2048 + CFG5_DECODE + 2
+    pages = CFG5_STREAMS * (-(-seq_cap // 64) + 1)
+    cfg = Q.config(n_layers=layers, max_rows=1024, max_streams=CFG5_STREAMS + 1, kv_page_size=64, kv_pages=pages)
+    eng = Q.Engine.synthetic(cfg, seed=0, norm_jitter=0.0, conv_std=0.02)
+    common = [int(t) for t in Q.ops.synth_tokens(0, "bench.cfg5.common", CFG5_PREFIX, cfg.vocab)]
+    prompts = []
+    for i in range(CFG5_STREAMS):
+        if i % 2 == 0:
+            tail = 128 + (lens[i] - 128) * (1024 - 128) // (2048 - 128)
+            prompts.append(common + [int(t) for t in Q.ops.synth_tokens(0, f"bench.cfg5.tail.{i}", tail, cfg.vocab)])
+        else:
+            prompts.append([int(t) for t in Q.ops.synth_tokens(0, f"bench.cfg5.prompt.{i}", lens[i], cfg.vocab)])
+    shared = Q.PrefixRAMStore(budget=2 << 30)
+    slots = Q.LaneBatchSlots(eng, CFG5_STREAMS, chunk=1024, default_seq_budget=seq_cap, shared_store=shared, hybrid=True, min_shared=1024)
+    step_time = [0.0, 0, 0]
+    inner_step = slots.step
+
+    def timed_step(last):
+        t0 = time.perf_counter()
+        out = inner_step(last)
+        step_time[0] += time.perf_counter() - t0
+        step_time[1] += sum(t is not None for t in out)
+        step_time[2] += 1
+        return out
+    slots.step = timed_step
+    sched = Q.ContinuousScheduler(slots, CFG5_BUDGET)
+    reqs = [sched.submit(Q.Request(prompt=p, max_tokens=CFG5_DECODE)) for p in prompts]
+    launches0 = eng.launch_count()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rounds = sched.run_to_completion()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    emitted = sum(len(r.out) for r in reqs)
+    fault = eng.gpu_fault()
+    out = {"metric": "cfg5_tok_per_s", "e2e_tok_s": emitted / wall, "decode_tok_s": step_time[1] / step_time[0] if step_time[0] > 0 else None,
+           "wall_s": wall, "decode_s": step_time[0], "decode_steps": step_time[2], "emitted_tokens": emitted, "rounds": rounds,
+           "prompt_tokens": sum(len(p) for p in prompts), "prefilled_tokens": slots.prefilled_tokens, "restored_tokens": slots.restored_tokens,
+           "prefix_captures": slots.captures, "prefix_restores": slots.restore_hits, "max_running": sched.max_running,
+           "gpu_launches": int(eng.launch_count() - launches0), "all_finished": all(r.finished and len(r.out) == CFG5_DECODE for r in reqs),
+           "gpu_fault": fault, "workload": WORKLOAD_CFG5}
+    eng.close()
+    return out
+
+
 def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
     """64 streams dealt to the ranks in blocks; every decode step is one sl_batch_step_argmax per rank
     (expert-parallel when world > 1).  Returns (aggregate tok/s by device events, by wall clock,
@@ -432,6 +493,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-batch64", action="store_true", help="skip the 64-stream measurement on the one-GPU line")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill-mode measurement on the one-GPU line")
+    ap.add_argument("--no-cfg5", action="store_true", help="skip the continuous-batching job (scheduler + prefix store) on the one-GPU line")
     ap.add_argument("--step-kernel", action="store_true", help="batch-1 arm: decode with the one-kernel step instead of the kernel-per-phase assembly")
     ap.add_argument("--timeline", action="store_true", help="with --step-kernel: add the per-phase timeline of one step (median over CTAs, microseconds) to the line")
     ap.add_argument("--layers", type=int, default=40, help="debug only: fewer layers (the reported line then says so)")
@@ -610,6 +672,10 @@ def main():
     if not args.no_prefill and args.layers == 40:
         torch.cuda.empty_cache()
         prefill = measure_prefill(Q, torch, args.layers)
+    cfg5 = None
+    if not args.no_cfg5 and args.layers == 40:
+        torch.cuda.empty_cache()
+        cfg5 = measure_cfg5(Q, torch, args.layers)
     if rank == 0:
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
@@ -626,7 +692,7 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4},
             "gpu_launches": int((launches_per_step or 0) * K),
-            "roofline": roofline, "cpu_baseline": cpu, "batch64_1gpu": batch64, "prefill": prefill,
+            "roofline": roofline, "cpu_baseline": cpu, "batch64_1gpu": batch64, "prefill": prefill, "cfg5_1gpu": cfg5,
         }
         print(json.dumps(line), flush=True)
 

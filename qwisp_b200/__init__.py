@@ -6,8 +6,9 @@ libseedless_b200.so (include/seedless_b200.h).  All arithmetic runs in hand-writ
 kernels; there is no CPU path and importing the library without it built fails loudly.
 """
 from ._lib import SeedlessError, config, lib, synth_spec  # noqa: F401
-from .engine import Engine, Stream, SpecBackend, LaneBatchSlots  # noqa: F401
+from .engine import Engine, Stream, SpecBackend, LaneBatchSlots, LaneAdmitPlan, admit_plan  # noqa: F401
 from . import ops  # noqa: F401
 from . import checkpoint  # noqa: F401
 from . import scheduler  # noqa: F401
+from .scheduler import ContinuousScheduler, Request  # noqa: F401
 from .prefix import PrefixRAMStore, PrefixDiskStore  # noqa: F401

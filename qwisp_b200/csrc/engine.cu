@@ -622,7 +622,7 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
         g.Hk = c.gdn_k_heads; g.Hv = c.gdn_v_heads; g.eps = c.rms_eps; g.tab = e->tab; g.gdn_index = L.type_index; g.segs = e->segs; g.y = e->mix;
         g.row_seg = e->row_seg; g.qk = e->gdn_qk; g.vc = e->gdn_vc; g.gb = e->gdn_gb;
         // segments of many rows: the state-independent part for all rows side by side, then the bare recurrence (same bits)
-        if (e->use_rows && M >= 16 && M >= 2 * nsegs) launch_gdn_rows(g, M, nsegs, st);
+        if (e->use_rows && M >= 16) launch_gdn_rows(g, M, nsegs, st);
         else launch_gdn_core(g, nsegs, st, e->use_pdl);
         o.x = e->mix; o.ldx = e->valDim; o.nw = L.gdn_norm; o.nw32 = L.gdn_norm32; o.z = e->inproj + e->convDim; o.ldz = e->gdn_in;
         launch_dense(L.gdn_norm32 ? PRO_NORMGATE32 : PRO_NORMGATE, resid ? EPI_RESID : EPI_STORE, o, st, e->use_pdl);

@@ -84,6 +84,33 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
     const uint32_t tmem_base = s_tmem;
     const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);   // f32 accumulate, f16 x f16, K-major both
     bool failed = false;
+    // Operands of a K group travel global -> registers -> shared memory.  All of a group's loads are issued together, and
+    // the next group's loads are issued before this group's MMAs, so one round trip to L2 is in flight per group instead
+    // of one per load.
+    constexpr int NB = NT * 8 / 128;                                       // 16-byte activation pieces per thread and group
+    const int r = lane >> 2, t = lane & 3;
+    uint4 wv[2], sv[2], xv[NB];
+    bool tvalid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) tvalid[h] = ((row0 >> 4) + warp + 4 * h) < ntiles;   // (the last CTA of a matrix whose rows are not a multiple of 128)
+    auto load_group = [&](int g) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int T = (row0 >> 4) + warp + 4 * h;
+            if (tvalid[h]) {
+                wv[h] = ldg_nc_u4(a.q.wr + ((size_t)T * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
+                sv[h] = ldg_nc_u4(a.q.sr + ((size_t)T * GP + (g >> 1)) * 8 + r);
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < NB; ++h) {
+            // piece idx: token = 8 * (idx / 64) + idx % 8, chunk = (idx / 8) % 8 -- the 8 lanes of a quarter warp store 8
+            // neighbouring 16-byte slots (no bank conflict) and read 4 x 64 contiguous bytes per token row
+            const int idx = tid + 128 * h, n = ((idx >> 6) << 3) + (idx & 7), c = (idx >> 3) & 7;
+            xv[h] = (n < nt) ? __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + n) * a.ldx + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    load_group(0);
     for (int g = 0; g < G; ++g) {
         const int s = g & 1, use = g >> 1;
         unsigned char* sA = smem + (size_t)s * STAGE;
@@ -95,18 +122,14 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int tl = warp + 4 * h;                                   // tile inside the CTA
-            const int T = (row0 >> 4) + tl;
-            const int r = lane >> 2, t = lane & 3;
             unsigned char* pa = sA + (size_t)(2 * t) * (TC_ROWS * 16) + (size_t)(tl * 16 + r) * 16;
             uint4 o[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-            if (T < ntiles) {                                              // (the last CTA of a matrix whose rows are not a multiple of 128)
-                const uint4 wv = ldg_nc_u4(a.q.wr + ((size_t)T * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
-                const uint4 sv = ldg_nc_u4(a.q.sr + ((size_t)T * GP + (g >> 1)) * 8 + r);
-                const uint32_t sa = (g & 1) ? sv.z : sv.x, sb = (g & 1) ? sv.w : sv.y;         // (scale, bias) of rows A_r and B_r
+            if (tvalid[h]) {
+                const uint32_t sa = (g & 1) ? sv[h].z : sv[h].x, sb = (g & 1) ? sv[h].w : sv[h].y;         // (scale, bias) of rows A_r and B_r
                 const __half2 hA = *reinterpret_cast<const __half2*>(&sa), hB = *reinterpret_cast<const __half2*>(&sb);
                 const __half2 sA2 = __half2half2(__low2half(hA)), bA2 = __half2half2(__high2half(hA));
                 const __half2 sB2 = __half2half2(__low2half(hB)), bB2 = __half2half2(__high2half(hB));
-                const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+                const uint32_t words[4] = {wv[h].x, wv[h].y, wv[h].z, wv[h].w};
 #pragma unroll
                 for (int wi = 0; wi < 4; ++wi) {
                     uint32_t d[4];
@@ -126,16 +149,16 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
             *reinterpret_cast<uint4*>(pa + TC_ROWS * 16 + 8 * 16) = o[3];
         }
         // ---- B stage: NT tokens x 8 chunks of 8 activations ----
-#pragma unroll 4
-        for (int h = 0; h < NT * 8 / 128; ++h) {
-            const int idx = tid + 128 * h, n = idx >> 3, c = idx & 7;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (n < nt) v = __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + n) * a.ldx + g * 64 + c * 8));
+#pragma unroll
+        for (int h = 0; h < NB; ++h) {
+            const int idx = tid + 128 * h, n = ((idx >> 6) << 3) + (idx & 7), c = (idx >> 3) & 7;
+            const uint4 v = xv[h];
             uint4 o;
             o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
             o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
             *reinterpret_cast<uint4*>(sB + (size_t)c * (NT * 16) + (size_t)n * 16) = o;
         }
+        if (g + 1 < G) load_group(g + 1);                                  // in flight across the barrier and the MMAs
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();

@@ -1226,7 +1226,8 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
 // k_gdn_prep   everything that does not depend on the state, for all rows side by side: conv + SiLU of every channel, the
 //              q/k norms and scales, decay and beta, the conv history the call leaves.  grid (Hk + Hv, M), 128 threads:
 //              CTAs [0, Hk) own a key head's q and k channels, CTAs [Hk, Hk + Hv) a value head's v channels and gates.
-// k_gdn_scan   the recurrence alone, rows of a segment in sequence, the next rows' operands requested four rows ahead.
+// k_gdn_scan   the recurrence alone, rows of a segment in sequence, the operands of 32 rows at a time staged in shared
+//              memory by cp.async one chunk ahead.
 //              Same grid and state ownership as k_gdn_core.
 // Every value is formed by the same functions in the same order as in k_gdn_core, so the outputs and the state are
 // identical bit for bit; the split only removes the per-row latency chain (and the 16-fold recomputation of q / k).
@@ -1280,8 +1281,18 @@ __global__ void __launch_bounds__(128) k_gdn_prep(GdnArgs a) {
             for (int j = 0; j < CONV_K - 1; ++j) hist_out[(size_t)j * convDim + ch_v] = f2h(xval(seg.nrows + j, ch_v));
     }
 }
-struct GdnRowOps { uint2 k, q, v; float2 gb; };     // 4 halves of k and q (this lane's dk), 4 halves of v (this warp's rows), (decay, beta)
+constexpr int GS_CH = 32;                                    // rows per staged chunk
+__device__ __forceinline__ void gs_cp16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void gs_cp8(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
 __global__ void __launch_bounds__(128) k_gdn_scan(GdnArgs a) {
+    // operands of 32 rows at a time, two buffers: q | k of the key head, the 16 v values of this CTA's state rows, (decay, beta)
+    __shared__ __align__(16) __half qk_s[2][GS_CH][2 * GDN_DK];
+    __shared__ __align__(16) __half v_s[2][GS_CH][16];
+    __shared__ __align__(8) float2 gb_s[2][GS_CH];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int dvt = blockIdx.x, hv = blockIdx.y;
     const SegDesc seg = a.segs[blockIdx.z];
@@ -1295,46 +1306,54 @@ __global__ void __launch_bounds__(128) k_gdn_scan(GdnArgs a) {
     float4 S[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) S[i] = *reinterpret_cast<const float4*>(S_in + (size_t)(warp * 4 + i) * GDN_DK + lane * 4);
-    auto load = [&](GdnRowOps& o, int tt) {
-        const size_t row = (size_t)(seg.row0 + tt);
-        o.q = __ldcg(reinterpret_cast<const uint2*>(a.qk + row * 2 * keyDim + hk * GDN_DK + lane * 4));
-        o.k = __ldcg(reinterpret_cast<const uint2*>(a.qk + row * 2 * keyDim + keyDim + hk * GDN_DK + lane * 4));
-        o.v = __ldcg(reinterpret_cast<const uint2*>(a.vc + row * valDim + hv * GDN_DV + dvt * 16 + warp * 4));
-        o.gb = __ldcg(a.gb + row * a.Hv + hv);
+    auto stage = [&](int c, int b) {
+        const int t0 = c * GS_CH, n = min(GS_CH, seg.nrows - t0);
+        for (int i = tid; i < n * 32; i += 128) {                                    // q, k: 16 + 16 pieces of 16 bytes per row
+            const int r = i >> 5, p = i & 31;
+            const size_t row = (size_t)(seg.row0 + t0 + r);
+            gs_cp16(&qk_s[b][r][p * 8], a.qk + row * 2 * keyDim + (p < 16 ? 0 : keyDim) + hk * GDN_DK + (p & 15) * 8);
+        }
+        for (int i = tid; i < n * 2; i += 128) {
+            const int r = i >> 1, p = i & 1;
+            gs_cp16(&v_s[b][r][p * 8], a.vc + (size_t)(seg.row0 + t0 + r) * valDim + hv * GDN_DV + dvt * 16 + p * 8);
+        }
+        for (int i = tid; i < n; i += 128) gs_cp8(&gb_s[b][i], a.gb + (size_t)(seg.row0 + t0 + i) * a.Hv + hv);
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
     auto h4 = [](uint2 u) -> float4 {
         const __half2 lo = *reinterpret_cast<const __half2*>(&u.x), hi = *reinterpret_cast<const __half2*>(&u.y);
         const float2 a2 = __half22float2(lo), b2 = __half22float2(hi);
         return make_float4(a2.x, a2.y, b2.x, b2.y);
     };
-    constexpr int D = 4;                                     // rows in flight
-    GdnRowOps buf[D];
+    const int nchunks = (seg.nrows + GS_CH - 1) / GS_CH;
+    stage(0, 0);
+    for (int c = 0; c < nchunks; ++c) {
+        const int b = c & 1;
+        if (c + 1 < nchunks) { stage(c + 1, b ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const int t0 = c * GS_CH, n = min(GS_CH, seg.nrows - t0);
+        for (int r = 0; r < n; ++r) {
+            const float4 qq = h4(*reinterpret_cast<const uint2*>(&qk_s[b][r][lane * 4]));
+            const float4 kq = h4(*reinterpret_cast<const uint2*>(&qk_s[b][r][GDN_DK + lane * 4]));
+            const float4 vv = h4(*reinterpret_cast<const uint2*>(&v_s[b][r][warp * 4]));
+            const float2 gb = gb_s[b][r];
+            const float vs[4] = {vv.x, vv.y, vv.z, vv.w};
+            __half outh[4];
 #pragma unroll
-    for (int u = 0; u < D; ++u) if (u < seg.nrows) load(buf[u], u);
-    for (int t0 = 0; t0 < seg.nrows; t0 += D) {
-#pragma unroll
-        for (int u = 0; u < D; ++u) {
-            const int tt = t0 + u;
-            if (tt < seg.nrows) {
-                const GdnRowOps o = buf[u];
-                if (tt + D < seg.nrows) load(buf[u], tt + D);
-                const float4 kq = h4(o.k), qq = h4(o.q), vv = h4(o.v);
-                const float vs[4] = {vv.x, vv.y, vv.z, vv.w};
-                __half outh[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float4 s = S[i];
-                    outh[i] = f2h(gdn_row_step(s, o.gb.x, kq, qq, vs[i], o.gb.y));
-                    S[i] = s;
-                }
-                if (lane == 0) {
-                    uint2 pk;
-                    pk.x = (unsigned)__half_as_ushort(outh[0]) | ((unsigned)__half_as_ushort(outh[1]) << 16);
-                    pk.y = (unsigned)__half_as_ushort(outh[2]) | ((unsigned)__half_as_ushort(outh[3]) << 16);
-                    *reinterpret_cast<uint2*>(a.y + (size_t)(seg.row0 + tt) * valDim + hv * GDN_DV + dvt * 16 + warp * 4) = pk;
-                }
+            for (int i = 0; i < 4; ++i) {
+                float4 s = S[i];
+                outh[i] = f2h(gdn_row_step(s, gb.x, kq, qq, vs[i], gb.y));
+                S[i] = s;
+            }
+            if (lane == 0) {
+                uint2 pk;
+                pk.x = (unsigned)__half_as_ushort(outh[0]) | ((unsigned)__half_as_ushort(outh[1]) << 16);
+                pk.y = (unsigned)__half_as_ushort(outh[2]) | ((unsigned)__half_as_ushort(outh[3]) << 16);
+                *reinterpret_cast<uint2*>(a.y + (size_t)(seg.row0 + t0 + r) * valDim + hv * GDN_DV + dvt * 16 + warp * 4) = pk;
             }
         }
+        __syncthreads();                       // the buffer is refilled by the next iteration's stage()
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(S_out + (size_t)(warp * 4 + i) * GDN_DK + lane * 4) = S[i];

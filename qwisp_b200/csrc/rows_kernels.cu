@@ -98,6 +98,18 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
 }
+// Wait of the expert kernel's ring, bounded in TIME (~50 ms): the first wait of a CTA that runs out raises the CTA's
+// abort word, and every later wait of that CTA gives up at once, so a stall costs one timeout per CTA, not one per item.
+constexpr long long XR_TIMEOUT = 100000000ll;                 // cycles
+__device__ __forceinline__ bool xr_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        for (int i = 0; i < 64; ++i) if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_word) return false;
+        if (clock64() - t0 > XR_TIMEOUT) { *abort_word = 1; return false; }
+    }
+}
 
 // One slice (4 groups of 64 inputs) of a 16-row tile against 8*RG staged rows.
 // xs: the slice's activations of staged row 0 (paired order), rows xstride halves apart; sxs: group sums of staged
@@ -270,7 +282,7 @@ __global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_base[260];                                  // first (slot, block) index of every slot; [n_active + 1] = total
     __shared__ __align__(8) uint64_t s_full[8], s_empty[8], s_raw[8];
-    __shared__ int s_sig;
+    __shared__ int s_sig; __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, t = lane & 3;
     const int K = DOWN ? a.I : a.H;
     const int slices = K >> 8, G64 = K >> 6, SXS = G64 + 4, XS = K + 8;
@@ -297,6 +309,7 @@ __global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int
         if (lane == 0) s_base[n_active + 1] = run;
     }
     if (tid == 0) {
+        s_abort = 0;
         for (int i = 0; i < nstages; ++i) { mbar_init(&s_full[i], DOWN ? 1 : 8); mbar_init(&s_empty[i], XR_CONS); mbar_init(&s_raw[i], 8); }
         mbar_fence_init();
     }
@@ -309,13 +322,14 @@ __global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int
         return lo;
     };
     bool failed = false;
+    unsigned fail_code = 0;          // which wait ran out: 16 producer/empty, 32 producer/chunk sums, 64 consumer/full
     if (warp == XR_CONS) {
         // ------------------------------------------------------------ producer
         int k = 0;
         for (int item = blockIdx.x; item < total; item += gridDim.x, ++k) {
             const int stg = k % nstages, use = k / nstages;
             const XrStage S = xr_carve<DOWN>(smem + (size_t)stg * stage_bytes, K);
-            if (use > 0 && !mbar_wait_bounded(&s_empty[stg], (uint32_t)((use - 1) & 1))) failed = true;
+            if (use > 0 && !xr_wait(&s_empty[stg], (uint32_t)((use - 1) & 1), &s_abort)) { failed = true; fail_code |= 16u; break; }
             const int sb = item / NTG, tg = item - sb * NTG;
             const int j = slot_of(sb), blk = sb - s_base[j];
             const bool shared = (j == n_active);
@@ -347,7 +361,7 @@ __global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int
             }
             if (DOWN) {
                 // group sums from the chunk sums: eight chunk sums combined in the butterfly order of rows_store()
-                if (!mbar_wait_bounded(&s_raw[stg], (uint32_t)(use & 1))) failed = true;
+                if (!xr_wait(&s_raw[stg], (uint32_t)(use & 1), &s_abort)) { failed = true; fail_code |= 32u; break; }
                 for (int i = lane; i < 8 * G64; i += 32) {
                     const int row = i / G64, g = i - row * G64;
                     const float* c = S.craw + (size_t)row * (K / 8) + g * 8;
@@ -385,7 +399,7 @@ __global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int
             const XrStage S = xr_carve<DOWN>(smem + (size_t)stg * stage_bytes, K);
             const int item_n = item + gridDim.x;
             if (item_n < total) tile_ptrs(item_n, wt_n, stl_n, valid_n); else valid_n = false;
-            if (!mbar_wait_bounded(&s_full[stg], (uint32_t)(use & 1))) failed = true;
+            if (!xr_wait(&s_full[stg], (uint32_t)(use & 1), &s_abort)) { failed = true; fail_code |= 64u; break; }
             float tot[1][4] = {{0.f, 0.f, 0.f, 0.f}};
 #pragma unroll 1
             for (int s = 0; s < slices; ++s) {
@@ -438,7 +452,12 @@ __global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int
             wt = wt_n; stl = stl_n; valid = valid_n;
         }
     }
-    if (failed && a.err && lane == 0) atomicOr(a.err, 1u);
+    if (failed && a.err && lane == 0) atomicOr(a.err, fail_code | (DOWN ? 8u : 4u));
+    __syncthreads();
+    if (s_abort) {                             // bulk copies this CTA started may still be landing in its shared memory: outlast them
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000ll) { }
+    }
     if (DOWN && a.ep_sig.world > 0) {
         // expert-parallel: every CTA makes its peer stores visible system-wide and draws a ticket; the last one raises this
         // rank's combine flag at every peer

@@ -349,60 +349,128 @@ class SpecBackend:
         return self.stream.engine.gpu_fault()
 
 
-class LaneBatchSlots:
-    """BatchSlots over engine streams: resumable chunked prefill + batched greedy step."""
+class LaneAdmitPlan:
+    """Where a new request starts and what it leaves behind (LaneServe.swift:98-131)."""
 
-    def __init__(self, engine, slot_count, chunk=None, default_seq_budget=4096, prefix_store=None):
+    def __init__(self, restore_len=0, capture_at=None, save_at_end=False):
+        self.restore_len, self.capture_at, self.save_at_end = restore_len, capture_at, save_at_end
+
+    def __eq__(self, o):
+        return (self.restore_len, self.capture_at, self.save_at_end) == (o.restore_len, o.capture_at, o.save_at_end)
+
+    def __repr__(self):
+        return f"LaneAdmitPlan(restore_len={self.restore_len}, capture_at={self.capture_at}, save_at_end={self.save_at_end})"
+
+
+def admit_plan(prompt_len, hit_len, lcp, min_shared):
+    """hit_len: longest whole-entry store hit over prompt[:-1]; lcp: longest PARTIAL key match (two prompts sharing
+    >= min_shared tokens define a recurring prefix).  The state is captured at the exact recurrence boundary only when
+    that beats the restore point by more than a blob copy is worth (256 tokens of prefill) and leaves >= 1 token; the
+    prompt-end state is saved unless the restore already covers everything but the last token
+    (LaneServe.swift:117-131)."""
+    capture = min(lcp, prompt_len - 1)
+    if capture < min_shared or capture < hit_len + 256:
+        capture = None
+    save_at_end = prompt_len >= min_shared and hit_len < prompt_len - 1
+    return LaneAdmitPlan(hit_len, capture, save_at_end)
+
+
+class LaneBatchSlots:
+    """BatchSlots over engine streams: resumable chunked prefill + batched greedy step (LaneServe.swift:331-485).
+
+    hybrid: prompt chunks run in prefill mode (sl_forward_hybrid) and the first token is the arg-max of the lm_head on
+    the last normed row, as the reference's lane prefill does; otherwise the strict forward.
+    shared_store / prefix_store: optional PrefixRAMStore pair.  A new request restores the longest stored state whose
+    tokens are a whole prefix of its prompt minus the last token, prefills only the rest, captures the state at the
+    exact boundary where its prompt stops agreeing with a stored key (shared_store) and saves the prompt-end state
+    (prefix_store, the reference's conversation store)."""
+
+    def __init__(self, engine, slot_count, chunk=None, default_seq_budget=4096, prefix_store=None, shared_store=None,
+                 hybrid=False, min_shared=1024):
         self.engine = engine
         self.slot_count = slot_count
         self.chunk = chunk or engine.cfg.max_rows
         self.default_seq_budget = default_seq_budget
-        # optional PrefixRAMStore: a new request starts from the longest stored state whose tokens are a
-        # prefix of its prompt (all but the last token, which must run to give the first output), and the
-        # state at the end of its prompt is stored for later requests (LaneServe.swift:362-425)
         self.prefix_store = prefix_store
+        self.shared_store = shared_store
+        self.hybrid = hybrid
+        self.min_shared = min_shared
         self.restored_tokens = 0
+        self.restore_hits = 0
+        self.captures = 0
+        self.prefilled_tokens = 0
         self._streams = [None] * slot_count
         self._resume = [0] * slot_count
+        self._plan = [None] * slot_count
 
     def can_admit(self, prompt_len, seq_budget):
         need = -(-max(seq_budget, prompt_len + 1) // self.engine.cfg.kv_page_size)
         used = sum(-(-s.max_seq_len // self.engine.cfg.kv_page_size) for s in self._streams if s is not None)
         return used + need <= self.engine.cfg.kv_pages
 
+    def _stores(self):
+        return [s for s in (self.shared_store, self.prefix_store) if s is not None and s.budget > 0]
+
+    def _open(self, prompt, slot, seq_budget):
+        self._streams[slot] = self.engine.stream(seq_budget or self.default_seq_budget)
+        self._resume[slot] = 0
+        self._plan[slot] = None
+        plan = LaneAdmitPlan()
+        stores = self._stores()
+        if stores:
+            matchable = prompt[:-1]
+            hits = [h for h in (s.best_match(matchable) for s in stores) if h is not None]
+            hit = max(hits, key=lambda h: len(h[0])) if hits else None
+            lcp = max(s.max_common_prefix(prompt) for s in stores)
+            plan = admit_plan(len(prompt), len(hit[0]) if hit else 0, lcp, self.min_shared)
+            if plan.restore_len > 0:
+                if self._streams[slot].state_restore(hit[1]):
+                    self._resume[slot] = plan.restore_len        # restored tokens are not charged to the budget
+                    self.restored_tokens += plan.restore_len
+                    self.restore_hits += 1
+                else:                                            # unusable blob: start cold on a fresh stream
+                    self._streams[slot].close()
+                    self._streams[slot] = self.engine.stream(seq_budget or self.default_seq_budget)
+                    plan.restore_len = 0
+        self._plan[slot] = plan
+
     def admit_step(self, prompt, slot, token_budget, seq_budget=0):
         """-> ("prefilling", consumed) | ("done", first_token, consumed) | ("failed",)"""
         try:
             if self._streams[slot] is None:
-                self._streams[slot] = self.engine.stream(seq_budget or self.default_seq_budget)
-                self._resume[slot] = 0
-                hit = self.prefix_store.best_match(prompt[:-1]) if self.prefix_store is not None else None
-                if hit is not None:
-                    if self._streams[slot].state_restore(hit[1]):
-                        self._resume[slot] = len(hit[0])         # restored tokens are not charged to the budget
-                        self.restored_tokens += len(hit[0])
-                    else:                                        # unusable blob: start cold on a fresh stream
-                        self._streams[slot].close()
-                        self._streams[slot] = self.engine.stream(seq_budget or self.default_seq_budget)
-            st = self._streams[slot]
+                self._open(prompt, slot, seq_budget)
+            st, plan = self._streams[slot], self._plan[slot]
             pos = self._resume[slot]
             consumed = 0
             first = True
             while pos < len(prompt):
-                n = min(self.chunk, len(prompt) - pos)
+                end = min(pos + self.chunk, len(prompt))
+                if plan.capture_at is not None and pos < plan.capture_at:
+                    end = min(end, plan.capture_at)              # one chunk is split at the exact boundary
+                n = end - pos
                 if not first and consumed + n > token_budget:
                     break                                        # forward progress: at least one whole chunk per call
-                last = (pos + n == len(prompt))
-                if last:
-                    tok = int(st.step_argmax(prompt[pos:pos + n])[-1])
+                last = (end == len(prompt))
+                tok = None
+                if self.hybrid:
+                    normed = st.forward_hybrid(prompt[pos:end], want_hidden=last)
+                    if last:
+                        from . import ops
+                        tok = int(ops.lm_head(self.engine, normed[-1:], want_logits=False)[1][0])
+                elif last:
+                    tok = int(st.step_argmax(prompt[pos:end])[-1])
                 else:
-                    st.forward(prompt[pos:pos + n], want_hidden=False)
-                pos += n
+                    st.forward(prompt[pos:end], want_hidden=False)
+                pos = end
                 consumed += n
+                self.prefilled_tokens += n
                 first = False
+                if plan.capture_at is not None and pos == plan.capture_at and self.shared_store is not None:
+                    self.shared_store.save(prompt[:pos], st.state_save())
+                    self.captures += 1
                 if last:
                     self._resume[slot] = pos
-                    if self.prefix_store is not None:
+                    if plan.save_at_end and self.prefix_store is not None and self.prefix_store.budget > 0:
                         self.prefix_store.save(prompt, st.state_save())
                     return ("done", tok, consumed)
             self._resume[slot] = pos
@@ -429,3 +497,4 @@ class LaneBatchSlots:
             self._streams[slot].close()
             self._streams[slot] = None
         self._resume[slot] = 0
+        self._plan[slot] = None

@@ -45,6 +45,18 @@ class PrefixRAMStore:
         self.entries.insert(0, e)
         return e
 
+    def max_common_prefix(self, content):
+        """Longest common token prefix between `content` and ANY stored key (a partial match, unlike best_match):
+        evidence that a prefix recurs (PrefixPersist.swift:239-251).  Does not touch the MRU order."""
+        best = 0
+        for k, _ in self.entries:
+            n = min(len(k), len(content))
+            i = 0
+            while i < n and k[i] == int(content[i]):
+                i += 1
+            best = max(best, i)
+        return best
+
     def remove_all(self):
         self.entries = []
 

@@ -20,9 +20,9 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("gloo")                   # host channel for the NCCL id only
-    B, S, PROMPT = 4, 6, 12
+    B, S, PROMPT = int(os.environ.get("EP_ROWS_PER_RANK", "4")), 6, 12
     geo = dict(hidden=2048, n_layers=4, attn_every=2, vocab=1024, n_experts=16, top_k=8, moe_inter=512,
-               max_rows=max(32, world * B), max_streams=2 * B + 2, kv_page_size=32, kv_pages=64)
+               max_rows=max(32, world * B), max_streams=2 * B + 2, kv_page_size=32, kv_pages=4 * B + 16)
     cfg = Q.config(**geo)
     ep = Q.Engine.synthetic(cfg, seed=3, norm_jitter=0.1, conv_std=0.5)
     ref = Q.Engine.synthetic(cfg, seed=3, norm_jitter=0.1, conv_std=0.5)

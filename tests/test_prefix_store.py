@@ -29,6 +29,78 @@ def test_store_longest_prefix_supersede_and_lru():
     assert st.entries == []
 
 
+def test_max_common_prefix_is_a_partial_match():
+    st = PrefixRAMStore(budget=1000)
+    st.save([1, 2, 3, 4], b"a")
+    st.save([9, 8, 7], b"b")
+    order = [k for k, _ in st.entries]
+    assert st.max_common_prefix([1, 2, 3, 9, 9]) == 3
+    assert st.max_common_prefix([1, 2, 3, 4, 5, 6]) == 4
+    assert st.max_common_prefix([9, 1]) == 1 and st.max_common_prefix([5]) == 0 and st.max_common_prefix([]) == 0
+    assert [k for k, _ in st.entries] == order                 # no MRU side effect
+    assert PrefixRAMStore(0).max_common_prefix([1, 2]) == 0
+
+
+def test_admit_plan_boundaries():
+    """The reference's own self-check of the admission plan (LaneServe.swift:133-156), case by case."""
+    from qwisp_b200.engine import LaneAdmitPlan, admit_plan
+    p = lambda n, hit, lcp: admit_plan(n, hit, lcp, 1024)
+    assert p(9000, 0, 0) == LaneAdmitPlan(0, None, True)                   # cold first request
+    assert p(12000, 0, 9000) == LaneAdmitPlan(0, 9000, True)               # second same-prefix request: capture at the exact boundary
+    assert p(12000, 9000, 9000) == LaneAdmitPlan(9000, None, True)         # third: warm restore, no re-capture
+    assert p(4000, 0, 900) == LaneAdmitPlan(0, None, True)                 # shared prefix below min_shared
+    assert p(12000, 8900, 9000) == LaneAdmitPlan(8900, None, True)         # capture not worth a blob copy
+    assert p(9000, 0, 9000) == LaneAdmitPlan(0, 8999, True)                # lcp clamps to prompt_len - 1
+    assert p(800, 0, 0) == LaneAdmitPlan(0, None, False)                   # short prompt: not cached
+    assert p(9000, 8999, 8999) == LaneAdmitPlan(8999, None, False)         # restore covers everything but the last token
+
+
+@pytest.mark.gpu
+def test_shared_prefix_is_captured_at_the_exact_boundary_and_reused():
+    """Three prompts that share their first 300 tokens: the first is served cold and leaves its prompt-end state; the
+    second sees the partial match, splits a chunk at token 300 and captures the state there; the third restores
+    those 300 tokens and prefills only its tail.  Tokens of all three equal cold lone streams (prefill mode)."""
+    import qwisp_b200 as Q
+    from conftest import SEED, TINY, gpu_engine
+    from oracle import oracle as O
+    eng = gpu_engine(TINY, max_rows=32, max_streams=8, kv_pages=64)
+    try:
+        shared, conv = Q.PrefixRAMStore(budget=64 << 20), Q.PrefixRAMStore(budget=64 << 20)
+        slots = Q.LaneBatchSlots(eng, 3, chunk=16, default_seq_budget=128, prefix_store=conv, shared_store=shared, hybrid=True, min_shared=32)
+        # (a capture must beat the restore point by 256 tokens, so the common part is 300 tokens long)
+        common = [int(t) for t in O.synth_tokens(SEED, "shared.common", 300, TINY["vocab"])]
+        tails = [[int(t) for t in O.synth_tokens(SEED, f"shared.tail{i}", 9 + 4 * i, TINY["vocab"])] for i in range(3)]
+        prompts = [common + t for t in tails]
+        eng2 = gpu_engine(TINY, max_rows=32, max_streams=8, kv_pages=64)
+        firsts = []
+        for i, pr in enumerate(prompts):
+            r = slots.admit_step(pr, i, 1 << 20, 400)
+            assert r[0] == "done"
+            firsts.append(r[1])
+        assert slots.captures == 1 and slots.restore_hits == 1 and slots.restored_tokens == 300
+        assert [len(k) for k, _ in shared.entries] == [300]
+        got = [[f] for f in firsts]
+        cur = list(firsts)
+        for _ in range(3):
+            cur = slots.step(cur)
+            for i in range(3):
+                got[i].append(cur[i])
+        for i, pr in enumerate(prompts):
+            lone = eng2.stream(400)
+            pos, normed = 0, None
+            while pos < len(pr):
+                n = min(16, len(pr) - pos)
+                normed = lone.forward_hybrid(pr[pos:pos + n]); pos += n
+            want = [int(Q.ops.lm_head(eng2, normed[-1:], want_logits=False)[1][0])]
+            for _ in range(3):
+                want.append(int(lone.step_argmax([want[-1]])[0]))
+            lone.close()
+            assert got[i] == want, i
+        eng2.close()
+    finally:
+        eng.close()
+
+
 @pytest.mark.gpu
 def test_admission_restores_the_longest_stored_prefix():
     """A second request that extends a served prompt starts from the stored state: only the suffix is
@@ -39,7 +111,7 @@ def test_admission_restores_the_longest_stored_prefix():
     eng = gpu_engine(TINY, max_rows=32, max_streams=8, kv_pages=64)
     try:
         store = Q.PrefixRAMStore(budget=64 << 20)
-        slots = Q.LaneBatchSlots(eng, 2, chunk=8, default_seq_budget=64, prefix_store=store)
+        slots = Q.LaneBatchSlots(eng, 2, chunk=8, default_seq_budget=64, prefix_store=store, min_shared=8)
         base = [int(t) for t in O.synth_tokens(SEED, "prefix.base", 20, TINY["vocab"])]
         ext = base + [int(t) for t in O.synth_tokens(SEED, "prefix.ext", 7, TINY["vocab"])]
         r1 = slots.admit_step(base, 0, 1 << 20, 64)
