@@ -275,8 +275,9 @@ WORKLOAD_CFG5 = ("cfg5 as BASELINE.json states it, one GPU: 64 requests submitte
                  "(64 slots, 4096-token budget per round, head-of-line admission on the KV page gate), 256 greedy tokens each; "
                  "even-numbered requests = one common seeded 1024-token prefix + a seeded tail of 128..1024 tokens, odd-numbered "
                  "requests = seeded random prompts of 128..2048 tokens; prompt chunks of 1024 tokens in prefill mode; the "
-                 "shared-prefix store (RAM, 2 GiB) captures the state at the exact shared boundary and later requests restore "
-                 "it; the conversation store is off")
+                 "conversation store (RAM, 1 GiB) keeps prompt-end states, whose keys are the evidence that a prefix recurs; the "
+                 "shared-prefix store (RAM, 2 GiB) then captures the state at the exact shared boundary and later requests "
+                 "restore it (host blobs, as in the reference)")
 
 
 def measure_cfg5(Q, torch, layers):
@@ -298,8 +299,9 @@ def measure_cfg5(Q, torch, layers):
             prompts.append(common + [int(t) for t in Q.ops.synth_tokens(0, f"bench.cfg5.tail.{i}", tail, cfg.vocab)])
         else:
             prompts.append([int(t) for t in Q.ops.synth_tokens(0, f"bench.cfg5.prompt.{i}", lens[i], cfg.vocab)])
-    shared = Q.PrefixRAMStore(budget=2 << 30)
-    slots = Q.LaneBatchSlots(eng, CFG5_STREAMS, chunk=1024, default_seq_budget=seq_cap, shared_store=shared, hybrid=True, min_shared=1024)
+    shared, conv = Q.PrefixRAMStore(budget=2 << 30), Q.PrefixRAMStore(budget=1 << 30)
+    slots = Q.LaneBatchSlots(eng, CFG5_STREAMS, chunk=1024, default_seq_budget=seq_cap, shared_store=shared, prefix_store=conv,
+                             hybrid=True, min_shared=1024)
     step_time = [0.0, 0, 0]
     inner_step = slots.step
 
@@ -337,6 +339,7 @@ def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
     ms per step, launches per step, tokens of this rank)."""
     import numpy as np
     from qwisp_b200 import ep as EP
+    t_begin = time.time()
     mine = EP.streams_of_rank(rank, world, BATCH_STREAMS)
     B = len(mine)
     max_prompt = 256
@@ -364,10 +367,13 @@ def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
             dist.barrier()
         torch.cuda.synchronize()
 
+    trace = (lambda msg: print(f"[bench rank {rank}] {msg} t={time.time() - t_begin:.1f}s", file=sys.stderr, flush=True)) if os.environ.get("SEEDLESS_BENCH_TRACE") else (lambda msg: None)
+    trace("prompts done")
     warm_toks = []
     for _ in range(W):
         last = [int(v) for v in eng.batch_step_argmax(streams, last)]
         warm_toks.append(list(last))
+        trace("warm-up step done")
     n0 = eng.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -382,6 +388,7 @@ def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
     barrier()
     wall = time.time() - t0
     ms = ev0.elapsed_time(ev1)
+    trace("timed steps done")
     launches = (eng.launch_count() - n0) / K
     if dist is not None:
         t = torch.tensor([ms, wall * 1e3], device="cuda")
@@ -399,6 +406,7 @@ def measure_batch64(Q, torch, dist, rank, world, layers, K, W):
     ptot = sum(v[1] for v in prep.values()) or 1.0
     kernel_shares = {k: {"launches_per_step": v[0] / nprof, "ms_per_step": v[1] / nprof, "share": v[1] / ptot} for k, v in prep.items()}
     fault = eng.gpu_fault()
+    trace("profile pass done")
     for st in streams:
         st.close()
     # The batched (expert-parallel when world > 1) token streams against plain single-stream decoding of the same

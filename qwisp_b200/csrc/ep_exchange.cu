@@ -30,31 +30,42 @@ __device__ __forceinline__ bool ep_wait_flag(const unsigned* flag, unsigned seq)
 }
 
 // One CTA: wait for every rank's dispatch flag, then group the pairs (row, k) whose expert lies in [e0, e1) by
-// expert, in the format the expert kernels read; within an expert the pairs keep ascending pair order.
+// expert, in the format the expert kernels read.
 // dynamic shared memory: npairs ints
 __global__ void __launch_bounds__(256) k_ep_lists(EpPeers P, int npairs, int e0, int e1, MoeLists lists, int layer, unsigned* err) {
     extern __shared__ int s_inds[];
-    __shared__ int s_cnt[256], s_off[256];
+    __shared__ int s_cnt[256], s_off[256], s_cur[256];
     const int tid = threadIdx.x;
     if (tid < P.world) { if (!ep_wait_flag(P.flags[P.rank] + tid, ep_seq(P.ctr, layer, 0))) atomicOr(err, 128u); }
-    s_cnt[tid] = 0; s_off[tid] = 0;
+    s_cnt[tid] = 0; s_off[tid] = 0; s_cur[tid] = 0;
     __syncthreads();
     const int* inds = P.ibuf[P.rank];
     for (int i = tid; i < npairs; i += 256) { const int ex = __ldcg(inds + i); s_inds[i] = ex; if (ex >= e0 && ex < e1) atomicAdd(&s_cnt[ex], 1); }
     __syncthreads();
-    if (tid == 0) {
-        int slot = 0, off = 0;
-        for (int ex = e0; ex < e1; ++ex)
-            if (s_cnt[ex] > 0) {
-                lists.slot_expert[slot] = ex; lists.slot_off[slot] = off; lists.slot_cnt[slot] = s_cnt[ex];
-                s_off[ex] = off; off += s_cnt[ex]; ++slot;
-            }
-        *lists.n_active = slot;
+    {   // slot numbers and offsets of the local experts by a block scan (thread = expert)
+        __shared__ int s_wsum[8], s_wact[8];
+        const int warp = tid >> 5, lane = tid & 31;
+        const int cnt = (tid >= e0 && tid < e1) ? s_cnt[tid] : 0, act = cnt > 0 ? 1 : 0;
+        int isum = cnt, iact = act;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o1 = __shfl_up_sync(0xffffffffu, isum, d), o2 = __shfl_up_sync(0xffffffffu, iact, d);
+            if (lane >= d) { isum += o1; iact += o2; }
+        }
+        if (lane == 31) { s_wsum[warp] = isum; s_wact[warp] = iact; }
+        __syncthreads();
+        int bsum = 0, bact = 0;
+        for (int w = 0; w < warp; ++w) { bsum += s_wsum[w]; bact += s_wact[w]; }
+        const int off = bsum + isum - cnt, slot = bact + iact - act;
+        s_off[tid] = off;
+        if (act) { lists.slot_expert[slot] = tid; lists.slot_off[slot] = off; lists.slot_cnt[slot] = cnt; }
+        if (tid == 255) *lists.n_active = slot + act;
     }
     __syncthreads();
-    if (tid >= e0 && tid < e1 && s_cnt[tid] > 0) {           // one thread per expert walks the pairs (shared memory) in order
-        int pos = s_off[tid];
-        for (int i = 0; i < npairs; ++i) if (s_inds[i] == tid) lists.pairs[pos++] = i;
+    // (the order of the pairs inside a slot is whatever the atomics give: it only decides which MMA column a row takes)
+    for (int i = tid; i < npairs; i += 256) {
+        const int ex = s_inds[i];
+        if (ex >= e0 && ex < e1) lists.pairs[s_off[ex] + atomicAdd(&s_cur[ex], 1)] = i;
     }
 }
 void launch_ep_lists(const EpPeers& P, int npairs, int e0, int e1, const MoeLists& lists, int layer, unsigned* err, cudaStream_t st) {

@@ -581,6 +581,31 @@ __global__ void __launch_bounds__(256) k_route_rows(RouterArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m = blockIdx.x * 8 + warp;
     if (m < a.M) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, s_route[warp], lane);
+    if (a.epd.sig.world > 0) {
+        // expert-parallel: every CTA sends its own rows (normed rows + routing indices) into every rank's gather buffers over
+        // peer memory; the CTA that finishes last raises this rank's dispatch flag at every rank.  The pair lists are built
+        // from the gathered indices by k_ep_lists.
+        const EpSignal& sg = a.epd.sig;
+        __syncwarp();
+        if (m < a.M) {
+            const uint4* src = reinterpret_cast<const uint4*>(a.p + (size_t)m * a.H);
+            for (int d = 0; d < sg.world; ++d) {
+                uint4* dst = reinterpret_cast<uint4*>(a.epd.pbuf[d] + ((size_t)sg.rank * a.M + m) * a.H);
+                for (int i = lane; i < a.H / 8; i += 32) dst[i] = __ldcg(src + i);
+                int* di = a.epd.ibuf[d] + ((size_t)sg.rank * a.M + m) * a.topk;
+                if (lane < a.topk) di[lane] = a.inds[m * a.topk + lane];
+            }
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) { const unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence_system();
+        if (tid == 0) *a.counter = 0u;
+        if (tid < sg.world) st_release_sys(sg.flags[tid] + sg.rank, ep_seq(sg.ctr, sg.layer, 0));
+        return;
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) { const unsigned ticket = atomicAdd(a.counter, 1u); s_last = (ticket == gridDim.x - 1) ? 1 : 0; }
@@ -588,23 +613,6 @@ __global__ void __launch_bounds__(256) k_route_rows(RouterArgs a) {
     if (!s_last) return;
     __threadfence();
     if (tid == 0) *a.counter = 0u;
-    if (a.epd.sig.world > 0) {
-        // expert-parallel: send the rank's normed rows and routing indices into every rank's gather buffers over peer
-        // memory, then raise this rank's dispatch flag there; the pair lists are built from the gathered indices
-        const EpSignal& sg = a.epd.sig;
-        const int nv = a.M * a.H / 8, ni = a.M * a.topk;
-        for (int d = 0; d < sg.world; ++d) {
-            uint4* dst = reinterpret_cast<uint4*>(a.epd.pbuf[d] + (size_t)sg.rank * a.M * a.H);
-            const uint4* src = reinterpret_cast<const uint4*>(a.p);
-            for (int i = tid; i < nv; i += 256) dst[i] = __ldcg(src + i);
-            int* di = a.epd.ibuf[d] + (size_t)sg.rank * ni;
-            for (int i = tid; i < ni; i += 256) di[i] = __ldcg(a.inds + i);
-        }
-        __threadfence_system();
-        __syncthreads();
-        if (tid < sg.world) st_release_sys(sg.flags[tid] + sg.rank, ep_seq(sg.ctr, sg.layer, 0));
-        return;
-    }
     // ---- pairs grouped by expert: counts, then slot numbers and offsets by a block scan (thread = expert)
     s_cnt[tid] = 0; s_cur[tid] = 0;
     __syncthreads();
