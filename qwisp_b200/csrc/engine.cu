@@ -585,6 +585,15 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     ea.route_here = ra.no_route;
     enqueue_router(e, ra, M, e->use_pdl);
     if (fused && launch_expert_fused(ea, st, e->use_pdl)) return;                      // one launch for gate/up + down
+    if (e->hybrid && M >= 64 && e->E <= 256 && e->use_rows) {
+        // prefill mode: grouped GEMMs on the tensor cores, then the combine kernel
+        ea.tile_counter = nullptr;
+        if (launch_expert_tc_gateup(ea, st) && launch_expert_tc_down(ea, st)) {
+            launch_moe_combine(e->dbuf, e->dbuf + (size_t)M * e->topk * e->H, e->scores, e->sgl, M, e->H, e->topk, resid, plain_out, st);
+            return;
+        }
+        ea.tile_counter = e->tile_counters;
+    }
     if (M > 8 && e->E <= 256 && e->use_rows) {
         // many rows: the normed rows are prepared once, the experts run without CTA-wide barriers, the combine is its own kernel
         launch_rows_prep_plain(e->p, e->H, M, e->H, e->xq_p, e->sx_p, st);

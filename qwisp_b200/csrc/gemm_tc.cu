@@ -54,6 +54,64 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- pieces of a K group shared by the dense and the grouped-expert kernels ----
+// fragment registers of one 16-row tile (wv: nibbles of rows A_r / B_r, sv: their scales and biases for the pair of
+// groups) -> fp16 weights in the A stage
+__device__ __forceinline__ void tc_dequant_A(unsigned char* sA, int tl, int r, int t, int g, uint4 wv, uint4 sv, bool valid) {
+    unsigned char* pa = sA + (size_t)(2 * t) * (TC_ROWS * 16) + (size_t)(tl * 16 + r) * 16;
+    uint4 o[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (valid) {
+        const uint32_t sa = (g & 1) ? sv.z : sv.x, sb = (g & 1) ? sv.w : sv.y;         // (scale, bias) of rows A_r and B_r
+        const __half2 hA = *reinterpret_cast<const __half2*>(&sa), hB = *reinterpret_cast<const __half2*>(&sb);
+        const __half2 sA2 = __half2half2(__low2half(hA)), bA2 = __half2half2(__high2half(hA));
+        const __half2 sB2 = __half2half2(__low2half(hB)), bB2 = __half2half2(__high2half(hB));
+        const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            uint32_t d[4];
+            dequant8(words[wi], d);
+            const __half2 sc = (wi < 2) ? sA2 : sB2, bi = (wi < 2) ? bA2 : bB2;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o[wi]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 wq = __hfma2(*reinterpret_cast<const __half2*>(&d[j]), sc, bi);
+                ow[j] = *reinterpret_cast<const uint32_t*>(&wq);
+            }
+        }
+    }
+    *reinterpret_cast<uint4*>(pa) = o[0];
+    *reinterpret_cast<uint4*>(pa + TC_ROWS * 16) = o[1];
+    *reinterpret_cast<uint4*>(pa + 8 * 16) = o[2];
+    *reinterpret_cast<uint4*>(pa + TC_ROWS * 16 + 8 * 16) = o[3];
+}
+// piece idx of the B stage: token = 8 * (idx / 64) + idx % 8, chunk = (idx / 8) % 8 -- the 8 lanes of a quarter warp store 8
+// neighbouring 16-byte slots (no bank conflict) and read 4 x 64 contiguous bytes per token row
+__device__ __forceinline__ void tc_piece(int idx, int& n, int& c) { n = ((idx >> 6) << 3) + (idx & 7); c = (idx >> 3) & 7; }
+template <int NT>
+__device__ __forceinline__ void tc_store_B(unsigned char* sB, int tid, const uint4* xv) {
+#pragma unroll
+    for (int h = 0; h < NT * 8 / 128; ++h) {
+        int n, c; tc_piece(tid + 128 * h, n, c);
+        const uint4 v = xv[h];
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
+        o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
+        *reinterpret_cast<uint4*>(sB + (size_t)c * (NT * 16) + (size_t)n * 16) = o;
+    }
+}
+// one thread: four MMAs of K = 16 (two 16-byte chunks each) accumulating into the NT columns, then the commit
+template <int NT>
+__device__ __forceinline__ void tc_issue(unsigned char* sA, unsigned char* sB, uint32_t tmem_base, uint32_t idesc, bool first, uint64_t* bar) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const uint64_t da = umma_desc_kmajor(sA + (size_t)ks * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128);
+        const uint64_t db = umma_desc_kmajor(sB + (size_t)ks * 2 * (NT * 16), NT * 16, 128);
+        umma_f16(tmem_base, da, db, idesc, (!first || ks > 0) ? 1u : 0u);
+    }
+    umma_commit(bar);
+}
+
 struct GemmTcArgs {
     Q4R q; int N, K, M;
     const __half* x; int ldx;
@@ -104,9 +162,7 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
         }
 #pragma unroll
         for (int h = 0; h < NB; ++h) {
-            // piece idx: token = 8 * (idx / 64) + idx % 8, chunk = (idx / 8) % 8 -- the 8 lanes of a quarter warp store 8
-            // neighbouring 16-byte slots (no bank conflict) and read 4 x 64 contiguous bytes per token row
-            const int idx = tid + 128 * h, n = ((idx >> 6) << 3) + (idx & 7), c = (idx >> 3) & 7;
+            int n, c; tc_piece(tid + 128 * h, n, c);
             xv[h] = (n < nt) ? __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + n) * a.ldx + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
         }
     };
@@ -120,59 +176,14 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // ---- A stage: two fragment registers per thread (tiles warp and warp+4 of the CTA's 8), dequantised to fp16 weights ----
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int tl = warp + 4 * h;                                   // tile inside the CTA
-            unsigned char* pa = sA + (size_t)(2 * t) * (TC_ROWS * 16) + (size_t)(tl * 16 + r) * 16;
-            uint4 o[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-            if (tvalid[h]) {
-                const uint32_t sa = (g & 1) ? sv[h].z : sv[h].x, sb = (g & 1) ? sv[h].w : sv[h].y;         // (scale, bias) of rows A_r and B_r
-                const __half2 hA = *reinterpret_cast<const __half2*>(&sa), hB = *reinterpret_cast<const __half2*>(&sb);
-                const __half2 sA2 = __half2half2(__low2half(hA)), bA2 = __half2half2(__high2half(hA));
-                const __half2 sB2 = __half2half2(__low2half(hB)), bB2 = __half2half2(__high2half(hB));
-                const uint32_t words[4] = {wv[h].x, wv[h].y, wv[h].z, wv[h].w};
-#pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    uint32_t d[4];
-                    dequant8(words[wi], d);
-                    const __half2 sc = (wi < 2) ? sA2 : sB2, bi = (wi < 2) ? bA2 : bB2;
-                    uint32_t* ow = reinterpret_cast<uint32_t*>(&o[wi]);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const __half2 wq = __hfma2(*reinterpret_cast<const __half2*>(&d[j]), sc, bi);
-                        ow[j] = *reinterpret_cast<const uint32_t*>(&wq);
-                    }
-                }
-            }
-            *reinterpret_cast<uint4*>(pa) = o[0];
-            *reinterpret_cast<uint4*>(pa + TC_ROWS * 16) = o[1];
-            *reinterpret_cast<uint4*>(pa + 8 * 16) = o[2];
-            *reinterpret_cast<uint4*>(pa + TC_ROWS * 16 + 8 * 16) = o[3];
-        }
+        for (int h = 0; h < 2; ++h) tc_dequant_A(sA, warp + 4 * h, r, t, g, wv[h], sv[h], tvalid[h]);
         // ---- B stage: NT tokens x 8 chunks of 8 activations ----
-#pragma unroll
-        for (int h = 0; h < NB; ++h) {
-            const int idx = tid + 128 * h, n = ((idx >> 6) << 3) + (idx & 7), c = (idx >> 3) & 7;
-            const uint4 v = xv[h];
-            uint4 o;
-            o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
-            o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
-            *reinterpret_cast<uint4*>(sB + (size_t)c * (NT * 16) + (size_t)n * 16) = o;
-        }
+        tc_store_B<NT>(sB, tid, xv);
         if (g + 1 < G) load_group(g + 1);                                  // in flight across the barrier and the MMAs
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        // ---- four MMAs of K = 16 (two 16-byte chunks each) accumulating into the NT columns ----
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                const uint64_t da = umma_desc_kmajor(sA + (size_t)ks * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128);
-                const uint64_t db = umma_desc_kmajor(sB + (size_t)ks * 2 * (NT * 16), NT * 16, 128);
-                umma_f16(tmem_base, da, db, idesc, (g > 0 || ks > 0) ? 1u : 0u);
-            }
-            umma_commit(&s_bar[s]);
-        }
+        if (tid == 0) tc_issue<NT>(sA, sB, tmem_base, idesc, g == 0, &s_bar[s]);
     }
     // the last commit covers every MMA issued before it
     if (!mbar_wait_bounded(&s_bar[(G - 1) & 1], (uint32_t)(((G - 1) >> 1) & 1))) failed = true;
@@ -223,5 +234,164 @@ int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, 
     // the token tile is a scheduling choice only: a token's column never interacts with another's
     return M <= 64 ? launch_gemm_tc_t<64>(a, st) : launch_gemm_tc_t<256>(a, st);
 }
+
+// ================================================================================ grouped experts (prefill mode)
+// Routed + shared experts of a prompt chunk on the same tensor-core pipeline: a work item is (expert slot, block of up to 64
+// of its rows, 128 weight rows = 8 tiles); the block's rows are gathered through the pair lists into the B stage, the
+// expert's weights are dequantised once per 64 rows.  Items are numbered slot-major, weight-row group fastest; persistent
+// CTAs walk them.  gate/up: the epilogue applies SwiGLU to (gate row r, up row r) of a paired tile -- they sit 8
+// accumulator lanes apart -- and stores the SwiGLU rows in natural order; down: the pair's output row.
+// Prefill-mode numerics (dequantised fp16 weights, one f32 accumulator per output over the whole K); a token's column
+// never interacts with another's, so the result does not depend on which rows share a block.
+constexpr int XT_NT = 64;
+template <bool DOWN>
+__global__ void __launch_bounds__(128) k_expert_umma(ExpertArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];              // 2 stages x [A 16 KB][B 8 KB]
+    constexpr int NT = XT_NT, A_BYTES = 8 * TC_ROWS * 16, B_BYTES = 8 * NT * 16, STAGE = A_BYTES + B_BYTES, NB = NT * 8 / 128;
+    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_base[260];
+    __shared__ int s_srow[NT], s_dst[NT];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, t = lane & 3;
+    const int K = DOWN ? a.I : a.H, G = K >> 6, GP = G >> 1;
+    const int ntiles = DOWN ? a.H / 16 : a.I / 8;                       // tiles of 16 weight rows per expert
+    const int NRT = (ntiles + 7) / 8;                                   // groups of 128 weight rows
+    const int npair = a.M * a.topk;
+    const int n_active = *a.lists.n_active;
+    const int nshared = a.M_shared >= 0 ? a.M_shared : a.M;
+    if (warp == 0) {                                                    // (slot, block) prefix, as in k_expert_rows
+        int run = 0;
+        for (int j0 = 0; j0 <= n_active; j0 += 32) {
+            const int j = j0 + lane;
+            int nb = 0;
+            if (j < n_active) nb = (a.lists.slot_cnt[j] + NT - 1) / NT;
+            else if (j == n_active) nb = (nshared + NT - 1) / NT;
+            int inc = nb;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) { const int o = __shfl_up_sync(0xffffffffu, inc, d); if (lane >= d) inc += o; }
+            if (j <= n_active) s_base[j] = run + inc - nb;
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (lane == 0) s_base[n_active + 1] = run;
+    }
+    if (tid == 0) { mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1); mbar_fence_init(); }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"((uint32_t)NT) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = s_tmem;
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+    const int total = s_base[n_active + 1] * NRT;
+    int commits[2] = {0, 0};                                             // commits made so far on each stage's barrier (same in every thread)
+    bool failed = false;
+    for (int item = blockIdx.x; item < total && !failed; item += gridDim.x) {
+        const int sb = item / NRT, rt = item - sb * NRT;
+        int lo = 0, hi = n_active;
+        while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (s_base[mid] <= sb) lo = mid; else hi = mid - 1; }
+        const int j = lo, blk = sb - s_base[j];
+        const bool shared = (j == n_active);
+        const int cnt = shared ? nshared : a.lists.slot_cnt[j];
+        const int e = shared ? 0 : a.lists.slot_expert[j];
+        const Q4R& q = DOWN ? (shared ? a.sh_down : a.down) : (shared ? a.sh_gu : a.gu);
+        if (tid < NT) {
+            const int ridx = blk * NT + tid;
+            int dst = -1, srow = -1;
+            if (ridx < cnt) {
+                if (shared) { dst = npair + ridx; srow = DOWN ? dst : a.shared_row0 + ridx; }
+                else { const int pr = a.lists.pairs[a.lists.slot_off[j] + ridx]; dst = pr; srow = DOWN ? pr : pr / a.topk; }
+            }
+            s_srow[tid] = srow; s_dst[tid] = dst;
+        }
+        __syncthreads();
+        const __half* xbase = DOWN ? a.hbuf : a.p;
+        uint4 wv[2], sv[2], xv[NB];
+        bool tvalid[2];
+        size_t Tt[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) { const int tile = rt * 8 + warp + 4 * h; tvalid[h] = tile < ntiles; Tt[h] = (size_t)e * ntiles + (tvalid[h] ? tile : 0); }
+        auto load_group = [&](int g) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (tvalid[h]) {
+                    wv[h] = ldg_nc_u4(q.wr + (Tt[h] * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
+                    sv[h] = ldg_nc_u4(q.sr + (Tt[h] * GP + (g >> 1)) * 8 + r);
+                }
+#pragma unroll
+            for (int h = 0; h < NB; ++h) {
+                int n, c; tc_piece(tid + 128 * h, n, c);
+                const int srow = s_srow[n];
+                xv[h] = (srow >= 0) ? __ldcg(reinterpret_cast<const uint4*>(xbase + (size_t)srow * K + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
+            }
+        };
+        load_group(0);
+        for (int g = 0; g < G; ++g) {
+            const int s = g & 1;
+            unsigned char* sA = smem + (size_t)s * STAGE;
+            unsigned char* sB = sA + A_BYTES;
+            // the MMAs that read this stage two groups ago (in this item) must be done before it is overwritten
+            if (g >= 2 && !mbar_wait_bounded(&s_bar[s], (uint32_t)((commits[s] - 1) & 1))) failed = true;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int h = 0; h < 2; ++h) tc_dequant_A(sA, warp + 4 * h, r, t, g, wv[h], sv[h], tvalid[h]);
+            tc_store_B<NT>(sB, tid, xv);
+            if (g + 1 < G) load_group(g + 1);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();
+            if (tid == 0) tc_issue<NT>(sA, sB, tmem_base, idesc, g == 0, &s_bar[s]);
+            commits[s] += 1;
+        }
+        {   // the last commit covers every MMA of the item
+            const int s = (G - 1) & 1;
+            if (!mbar_wait_bounded(&s_bar[s], (uint32_t)((commits[s] - 1) & 1))) failed = true;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        failed = __syncthreads_or(failed ? 1 : 0) != 0;
+        if (!failed) {
+            const int i16 = tid & 15, tl = tid >> 4, tile = rt * 8 + tl;
+#pragma unroll
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                uint32_t dreg[32];
+                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, dreg);
+#pragma unroll
+                for (int n = 0; n < 32; ++n) {
+                    const float v = __uint_as_float(dreg[n]);
+                    const int dst = s_dst[c0 + n];
+                    if (DOWN) {
+                        if (dst >= 0 && tile < ntiles) a.dbuf[(size_t)dst * a.H + (size_t)rt * TC_ROWS + tid] = f2h(v);
+                    } else {
+                        const float other = __shfl_xor_sync(0xffffffffu, v, 8);               // the up row of this gate row
+                        if (dst >= 0 && tile < ntiles && i16 < 8) a.hbuf[(size_t)dst * a.I + tile * 8 + i16] = swiglu_h(f2h(v), f2h(other));
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();                                                 // accumulator, stages and row lists may be reused
+    }
+    if (failed && a.err && tid == 0) atomicOr(a.err, 1u);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)NT) : "memory");
+}
+template <bool DOWN>
+static bool launch_expert_tc_t(const ExpertArgs& a, cudaStream_t st) {
+    const int K = DOWN ? a.I : a.H;
+    if (K % 256 || a.ep_pairs_per_rank > 0) return false;              // (expert-parallel calls keep the row kernels)
+    constexpr size_t smem = 2 * (8 * TC_ROWS * 16 + 8 * XT_NT * 16);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(k_expert_umma<DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
+        configured = true;
+    }
+    const int grid = 4 * sm_count();                                    // 48 KB of shared memory and 64 TMEM columns per CTA: four fit a multiprocessor
+    profile_launch(DOWN ? "k_expert_umma_down" : "k_expert_umma_gateup", st, [&] { k_expert_umma<DOWN><<<grid, 128, smem, st>>>(a); return 0; });
+    return true;
+}
+bool launch_expert_tc_gateup(const ExpertArgs& a, cudaStream_t st) { return launch_expert_tc_t<false>(a, st); }
+bool launch_expert_tc_down(const ExpertArgs& a, cudaStream_t st) { return launch_expert_tc_t<true>(a, st); }
 
 }  // namespace sl

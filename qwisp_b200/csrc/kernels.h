@@ -195,6 +195,9 @@ void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pd
 // many-row forms (more than 8 rows per call); the bool launchers return false when the shape is not covered
 bool launch_dense_rows(int pro, int epi, const DenseArgs& a, cudaStream_t st);
 void launch_rows_prep_plain(const __half* x, int ldx, int M, int K, __half* xq, float* sxq, cudaStream_t st);
+// prefill mode: the experts of a prompt chunk as grouped GEMMs on the tensor cores (pair lists as built by the router); hbuf in natural order
+bool launch_expert_tc_gateup(const ExpertArgs& a, cudaStream_t st);
+bool launch_expert_tc_down(const ExpertArgs& a, cudaStream_t st);
 // router for many rows: a.h holds rows that are already normed; logits kernel + routing / pair lists kernel
 bool launch_router_rows(const RouterArgs& a, cudaStream_t st);
 bool launch_expert_rows_gateup(const ExpertArgs& a, cudaStream_t st);
