@@ -54,6 +54,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t r[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Short wait on a stage barrier: non-blocking polls (the MMAs it waits for take a few hundred nanoseconds; a blocking
+// try_wait may park the warp for longer than that), bounded like every wait.
+__device__ __forceinline__ bool tc_wait(uint64_t* b, uint32_t parity) {
+    for (int i = 0; i < (1 << 24); ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
 // ---- pieces of a K group shared by the dense and the grouped-expert kernels ----
 // fragment registers of one 16-row tile (wv: nibbles of rows A_r / B_r, sv: their scales and biases for the pair of
 // groups) -> fp16 weights in the A stage
@@ -147,46 +158,50 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
     // of one per load.
     constexpr int NB = NT * 8 / 128;                                       // 16-byte activation pieces per thread and group
     const int r = lane >> 2, t = lane & 3;
-    uint4 wv[2], sv[2], xv[NB];
+    struct Regs { uint4 wv[2], sv[2], xv[NB]; };
+    Regs ra, rb;                                                           // two register sets: a group's loads have a whole iteration to land
     bool tvalid[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) tvalid[h] = ((row0 >> 4) + warp + 4 * h) < ntiles;   // (the last CTA of a matrix whose rows are not a multiple of 128)
-    auto load_group = [&](int g) {
+    auto load_group = [&](Regs& R, int g) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int T = (row0 >> 4) + warp + 4 * h;
             if (tvalid[h]) {
-                wv[h] = ldg_nc_u4(a.q.wr + ((size_t)T * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
-                sv[h] = ldg_nc_u4(a.q.sr + ((size_t)T * GP + (g >> 1)) * 8 + r);
+                R.wv[h] = ldg_nc_u4(a.q.wr + ((size_t)T * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
+                R.sv[h] = ldg_nc_u4(a.q.sr + ((size_t)T * GP + (g >> 1)) * 8 + r);
             }
         }
 #pragma unroll
         for (int h = 0; h < NB; ++h) {
             int n, c; tc_piece(tid + 128 * h, n, c);
-            xv[h] = (n < nt) ? __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + n) * a.ldx + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
+            R.xv[h] = (n < nt) ? __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + n) * a.ldx + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
         }
     };
-    load_group(0);
-    for (int g = 0; g < G; ++g) {
+    auto process = [&](const Regs& R, int g) {
         const int s = g & 1, use = g >> 1;
         unsigned char* sA = smem + (size_t)s * STAGE;
         unsigned char* sB = sA + A_BYTES;
         // the MMAs that read this stage two groups ago must be done before it is overwritten
-        if (use > 0 && !mbar_wait_bounded(&s_bar[s], (uint32_t)((use - 1) & 1))) failed = true;
+        if (use > 0 && !tc_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) failed = true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // ---- A stage: two fragment registers per thread (tiles warp and warp+4 of the CTA's 8), dequantised to fp16 weights ----
 #pragma unroll
-        for (int h = 0; h < 2; ++h) tc_dequant_A(sA, warp + 4 * h, r, t, g, wv[h], sv[h], tvalid[h]);
-        // ---- B stage: NT tokens x 8 chunks of 8 activations ----
-        tc_store_B<NT>(sB, tid, xv);
-        if (g + 1 < G) load_group(g + 1);                                  // in flight across the barrier and the MMAs
+        for (int h = 0; h < 2; ++h) tc_dequant_A(sA, warp + 4 * h, r, t, g, R.wv[h], R.sv[h], tvalid[h]);
+        tc_store_B<NT>(sB, tid, R.xv);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
         if (tid == 0) tc_issue<NT>(sA, sB, tmem_base, idesc, g == 0, &s_bar[s]);
+    };
+    load_group(ra, 0);
+    for (int g = 0; g < G; g += 2) {                                       // G is even (K is a multiple of 256)
+        load_group(rb, g + 1);
+        process(ra, g);
+        if (g + 2 < G) load_group(ra, g + 2);
+        process(rb, g + 1);
     }
     // the last commit covers every MMA issued before it
-    if (!mbar_wait_bounded(&s_bar[(G - 1) & 1], (uint32_t)(((G - 1) >> 1) & 1))) failed = true;
+    if (!tc_wait(&s_bar[(G - 1) & 1], (uint32_t)(((G - 1) >> 1) & 1))) failed = true;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     failed = __syncthreads_or(failed ? 1 : 0) != 0;
     if (failed && a.err && tid == 0) atomicOr(a.err, 1u);
@@ -307,46 +322,52 @@ __global__ void __launch_bounds__(128) k_expert_umma(ExpertArgs a) {
         }
         __syncthreads();
         const __half* xbase = DOWN ? a.hbuf : a.p;
-        uint4 wv[2], sv[2], xv[NB];
+        struct Regs { uint4 wv[2], sv[2], xv[NB]; };
+        Regs ra, rb;
         bool tvalid[2];
         size_t Tt[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) { const int tile = rt * 8 + warp + 4 * h; tvalid[h] = tile < ntiles; Tt[h] = (size_t)e * ntiles + (tvalid[h] ? tile : 0); }
-        auto load_group = [&](int g) {
+        auto load_group = [&](Regs& R, int g) {
 #pragma unroll
             for (int h = 0; h < 2; ++h)
                 if (tvalid[h]) {
-                    wv[h] = ldg_nc_u4(q.wr + (Tt[h] * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
-                    sv[h] = ldg_nc_u4(q.sr + (Tt[h] * GP + (g >> 1)) * 8 + r);
+                    R.wv[h] = ldg_nc_u4(q.wr + (Tt[h] * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
+                    R.sv[h] = ldg_nc_u4(q.sr + (Tt[h] * GP + (g >> 1)) * 8 + r);
                 }
 #pragma unroll
             for (int h = 0; h < NB; ++h) {
                 int n, c; tc_piece(tid + 128 * h, n, c);
                 const int srow = s_srow[n];
-                xv[h] = (srow >= 0) ? __ldcg(reinterpret_cast<const uint4*>(xbase + (size_t)srow * K + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
+                R.xv[h] = (srow >= 0) ? __ldcg(reinterpret_cast<const uint4*>(xbase + (size_t)srow * K + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
             }
         };
-        load_group(0);
-        for (int g = 0; g < G; ++g) {
+        auto process = [&](const Regs& R, int g) {
             const int s = g & 1;
             unsigned char* sA = smem + (size_t)s * STAGE;
             unsigned char* sB = sA + A_BYTES;
             // the MMAs that read this stage two groups ago (in this item) must be done before it is overwritten
-            if (g >= 2 && !mbar_wait_bounded(&s_bar[s], (uint32_t)((commits[s] - 1) & 1))) failed = true;
+            if (g >= 2 && !tc_wait(&s_bar[s], (uint32_t)((commits[s] - 1) & 1))) failed = true;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int h = 0; h < 2; ++h) tc_dequant_A(sA, warp + 4 * h, r, t, g, wv[h], sv[h], tvalid[h]);
-            tc_store_B<NT>(sB, tid, xv);
-            if (g + 1 < G) load_group(g + 1);
+            for (int h = 0; h < 2; ++h) tc_dequant_A(sA, warp + 4 * h, r, t, g, R.wv[h], R.sv[h], tvalid[h]);
+            tc_store_B<NT>(sB, tid, R.xv);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncthreads();
             if (tid == 0) tc_issue<NT>(sA, sB, tmem_base, idesc, g == 0, &s_bar[s]);
             commits[s] += 1;
+        };
+        load_group(ra, 0);
+        for (int g = 0; g < G; g += 2) {
+            load_group(rb, g + 1);
+            process(ra, g);
+            if (g + 2 < G) load_group(ra, g + 2);
+            process(rb, g + 1);
         }
         {   // the last commit covers every MMA of the item
             const int s = (G - 1) & 1;
-            if (!mbar_wait_bounded(&s_bar[s], (uint32_t)((commits[s] - 1) & 1))) failed = true;
+            if (!tc_wait(&s_bar[s], (uint32_t)((commits[s] - 1) & 1))) failed = true;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         failed = __syncthreads_or(failed ? 1 : 0) != 0;
