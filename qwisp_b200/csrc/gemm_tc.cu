@@ -13,13 +13,15 @@
 // A CTA of 128 threads owns 128 weight rows (8 tiles of the fragment-major layout) and NT activation rows (64 or 256).
 // Two shared-memory stages alternate over the K groups of 64 inputs:
 //   fill   every thread dequantises two fragment registers (16 nibbles of two weight rows, scale and bias applied with
-//          one fp16x2 multiply-add per pair) into the A stage -- K-major, no swizzle, core matrices of 8 rows x 16 bytes,
-//          the 8 halves of a chunk in the pair order (0,4,1,5,2,6,3,7) the one-logic-op dequantiser produces -- and
-//          copies NT x 64 activations into the B stage in the same order, so no permutation is spent;
+//          one fp16x2 multiply-add per pair) into the A stage -- K-major rows of 128 bytes, 128-byte swizzle, the 8 halves
+//          of a 16-byte chunk in the pair order (0,4,1,5,2,6,3,7) the one-logic-op dequantiser produces -- and copies
+//          NT x 64 activations into the B stage in the same order, so no permutation is spent; operands travel global ->
+//          registers -> shared memory in two register sets, a group's loads being issued a whole iteration ahead;
 //   issue  fence.proxy.async + barrier; one thread issues four MMAs (M=128, N=NT, K=16) that accumulate into the NT
 //          TMEM columns and commits them to the stage's mbarrier; the CTA goes straight on to fill the other stage,
 //          waiting (bounded) on a stage's mbarrier only before it overwrites it.
-// Two CTAs fit a multiprocessor (96 KB of shared memory, 256 TMEM columns each), so one CTA's fill overlaps the other's MMAs.
+// Two CTAs fit a multiprocessor (97 KB of shared memory, 256 TMEM columns each), so one CTA's fill overlaps the other's MMAs.
+// (An unswizzled operand layout ran the same MMAs about five times slower.)
 #include "kernels.h"
 #include "gemv.cuh"
 
@@ -27,11 +29,18 @@ namespace sl {
 
 constexpr int TC_ROWS = 128;      // weight rows per CTA (UMMA M)
 
-__device__ __forceinline__ uint64_t umma_desc_kmajor(const void* smem_ptr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    // shared-memory matrix descriptor: start address, leading (K-chunk) and stride (8-row group)
-    // byte offsets, all without their 4 low bits; descriptor version 1; no swizzle; base offset 0
+// Operand tiles in shared memory: K-major, 128-byte swizzle.  A row holds the 64 halves of one K group (128 bytes); 8 rows
+// form a 1024-byte atom inside which the 16-byte chunk index is XORed with the row index (conflict-free for the threads
+// that fill it and for the tensor core that reads it); atoms of further rows follow at 1024-byte steps.  Tiles start on
+// 1024-byte boundaries.
+__device__ __forceinline__ unsigned char* tc_at(unsigned char* tile, int row, int chunk) {
+    return tile + ((size_t)(row >> 3) << 10) + ((row & 7) << 7) + (((chunk ^ row) & 7) << 4);
+}
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* smem_ptr) {
+    // shared-memory matrix descriptor: start address; leading byte offset 1 (unused by swizzled K-major layouts); stride
+    // byte offset 1024 (between 8-row atoms); all without their 4 low bits; descriptor version 1; layout type 2 = 128-byte swizzle
     const uint64_t addr = (uint64_t)(smem_u32(smem_ptr) >> 4) & 0x3FFFull;
-    return addr | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46);
+    return addr | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -69,7 +78,6 @@ __device__ __forceinline__ bool tc_wait(uint64_t* b, uint32_t parity) {
 // fragment registers of one 16-row tile (wv: nibbles of rows A_r / B_r, sv: their scales and biases for the pair of
 // groups) -> fp16 weights in the A stage
 __device__ __forceinline__ void tc_dequant_A(unsigned char* sA, int tl, int r, int t, int g, uint4 wv, uint4 sv, bool valid) {
-    unsigned char* pa = sA + (size_t)(2 * t) * (TC_ROWS * 16) + (size_t)(tl * 16 + r) * 16;
     uint4 o[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
     if (valid) {
         const uint32_t sa = (g & 1) ? sv.z : sv.x, sb = (g & 1) ? sv.w : sv.y;         // (scale, bias) of rows A_r and B_r
@@ -90,13 +98,14 @@ __device__ __forceinline__ void tc_dequant_A(unsigned char* sA, int tl, int r, i
             }
         }
     }
-    *reinterpret_cast<uint4*>(pa) = o[0];
-    *reinterpret_cast<uint4*>(pa + TC_ROWS * 16) = o[1];
-    *reinterpret_cast<uint4*>(pa + 8 * 16) = o[2];
-    *reinterpret_cast<uint4*>(pa + TC_ROWS * 16 + 8 * 16) = o[3];
+    const int rowA = tl * 16 + r;                                     // row A_r of the tile; B_r is 8 rows further (the next atom)
+    *reinterpret_cast<uint4*>(tc_at(sA, rowA, 2 * t)) = o[0];
+    *reinterpret_cast<uint4*>(tc_at(sA, rowA, 2 * t + 1)) = o[1];
+    *reinterpret_cast<uint4*>(tc_at(sA, rowA + 8, 2 * t)) = o[2];
+    *reinterpret_cast<uint4*>(tc_at(sA, rowA + 8, 2 * t + 1)) = o[3];
 }
-// piece idx of the B stage: token = 8 * (idx / 64) + idx % 8, chunk = (idx / 8) % 8 -- the 8 lanes of a quarter warp store 8
-// neighbouring 16-byte slots (no bank conflict) and read 4 x 64 contiguous bytes per token row
+// piece idx of the B stage: token = 8 * (idx / 64) + idx % 8, chunk = (idx / 8) % 8 -- the 8 lanes of a quarter warp store
+// into the 8 rows of one atom (distinct swizzled chunks: no bank conflict) and read 4 x 64 contiguous bytes per token row
 __device__ __forceinline__ void tc_piece(int idx, int& n, int& c) { n = ((idx >> 6) << 3) + (idx & 7); c = (idx >> 3) & 7; }
 template <int NT>
 __device__ __forceinline__ void tc_store_B(unsigned char* sB, int tid, const uint4* xv) {
@@ -107,7 +116,7 @@ __device__ __forceinline__ void tc_store_B(unsigned char* sB, int tid, const uin
         uint4 o;
         o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
         o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
-        *reinterpret_cast<uint4*>(sB + (size_t)c * (NT * 16) + (size_t)n * 16) = o;
+        *reinterpret_cast<uint4*>(tc_at(sB, n, c)) = o;
     }
 }
 // one thread: four MMAs of K = 16 (two 16-byte chunks each) accumulating into the NT columns, then the commit
@@ -116,8 +125,7 @@ __device__ __forceinline__ void tc_issue(unsigned char* sA, unsigned char* sB, u
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-        const uint64_t da = umma_desc_kmajor(sA + (size_t)ks * 2 * (TC_ROWS * 16), TC_ROWS * 16, 128);
-        const uint64_t db = umma_desc_kmajor(sB + (size_t)ks * 2 * (NT * 16), NT * 16, 128);
+        const uint64_t da = umma_desc_sw128(sA + ks * 32), db = umma_desc_sw128(sB + ks * 32);      // 16 halves further along K
         umma_f16(tmem_base, da, db, idesc, (!first || ks > 0) ? 1u : 0u);
     }
     umma_commit(bar);
@@ -133,7 +141,8 @@ struct GemmTcArgs {
 
 template <int NT>
 __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];              // 2 stages x [A: 8 chunks x 128 rows x 16 B][B: 8 chunks x NT tokens x 16 B]
+    extern __shared__ __align__(1024) unsigned char smem_raw[];         // 2 stages x [A: 128 rows x 128 B][B: NT tokens x 128 B]
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // tiles start on 1024-byte boundaries
     constexpr int A_BYTES = 8 * TC_ROWS * 16, B_BYTES = 8 * NT * 16, STAGE = A_BYTES + B_BYTES;
     __shared__ __align__(8) uint64_t s_bar[2];
     __shared__ uint32_t s_tmem;
@@ -231,7 +240,7 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
 
 template <int NT>
 static int launch_gemm_tc_t(const GemmTcArgs& a, cudaStream_t st) {
-    constexpr size_t smem = 2 * (8 * TC_ROWS * 16 + 8 * NT * 16);
+    constexpr size_t smem = 2 * (8 * TC_ROWS * 16 + 8 * NT * 16) + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(k_gemm_umma<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -261,7 +270,8 @@ int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, 
 constexpr int XT_NT = 64;
 template <bool DOWN>
 __global__ void __launch_bounds__(128) k_expert_umma(ExpertArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];              // 2 stages x [A 16 KB][B 8 KB]
+    extern __shared__ __align__(1024) unsigned char smem_raw[];         // 2 stages x [A 16 KB][B 8 KB]
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // tiles start on 1024-byte boundaries
     constexpr int NT = XT_NT, A_BYTES = 8 * TC_ROWS * 16, B_BYTES = 8 * NT * 16, STAGE = A_BYTES + B_BYTES, NB = NT * 8 / 128;
     __shared__ __align__(8) uint64_t s_bar[2];
     __shared__ uint32_t s_tmem;
@@ -402,7 +412,7 @@ template <bool DOWN>
 static bool launch_expert_tc_t(const ExpertArgs& a, cudaStream_t st) {
     const int K = DOWN ? a.I : a.H;
     if (K % 256 || a.ep_pairs_per_rank > 0) return false;              // (expert-parallel calls keep the row kernels)
-    constexpr size_t smem = 2 * (8 * TC_ROWS * 16 + 8 * XT_NT * 16);
+    constexpr size_t smem = 2 * (8 * TC_ROWS * 16 + 8 * XT_NT * 16) + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(k_expert_umma<DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
