@@ -677,7 +677,7 @@ def main():
                    "roofline": {"bound": "hbm", "achieved": bg, "peak": peak_gbs, "unit": "GB/s", "frac": bg / peak_gbs, "traffic": None,
                                 "algorithmic_bytes_per_step": bb, "note": "whole step; expert bytes are the expectation for uniform routing"}}
     prefill = None
-    if not args.no_prefill and args.layers == 40:
+    if not args.no_prefill:
         torch.cuda.empty_cache()
         prefill = measure_prefill(Q, torch, args.layers)
     cfg5 = None
