@@ -513,6 +513,7 @@ void enqueue_router(sl_engine* e, const RouterArgs& ra, int M, bool pdl) {
     if (M > 8 && e->use_rows && !ra.no_route && e->E <= 256 && ra.norm_w && ra.ldh == e->H) {
         launch_final_norm(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, st);
         RouterArgs rb = ra; rb.h = ra.p; rb.ldh = e->H; rb.norm_w = nullptr;
+        if (e->hybrid && M >= 64 && launch_router_mma(rb, st)) return;
         if (launch_router_rows(rb, st)) return;
         // not covered: the one-kernel router norms the rows again from the original input
     }

@@ -1,4 +1,4 @@
-// gemm_tc.cu -- 4-bit group-64 GEMM for many activation rows ("F2": prefill chunks) on the 5th-generation
+// gemm_tc.cu -- 4-bit group-64 GEMM for many activation rows ("F2": prompt chunks in prefill mode) on the 5th-generation
 // tensor cores: tcgen05.mma (kind::f16) issued by one thread, operands in shared memory described by matrix
 // descriptors, the accumulator in tensor memory (TMEM), read back once with tcgen05.ld.
 //
@@ -10,18 +10,16 @@
 // this is not bit-identical to the GEMV family, but every token column is independent of the others and K is walked in
 // a fixed order, so results do not depend on how many rows share a call or on how a prompt is cut into calls.
 //
-// A CTA of 128 threads owns 128 weight rows (8 tiles of the fragment-major layout) and NT activation rows (64 or 256).
-// Two shared-memory stages alternate over the K groups of 64 inputs:
-//   fill   every thread dequantises two fragment registers (16 nibbles of two weight rows, scale and bias applied with
-//          one fp16x2 multiply-add per pair) into the A stage -- K-major rows of 128 bytes, 128-byte swizzle, the 8 halves
-//          of a 16-byte chunk in the pair order (0,4,1,5,2,6,3,7) the one-logic-op dequantiser produces -- and copies
-//          NT x 64 activations into the B stage in the same order, so no permutation is spent; operands travel global ->
-//          registers -> shared memory in two register sets, a group's loads being issued a whole iteration ahead;
-//   issue  fence.proxy.async + barrier; one thread issues four MMAs (M=128, N=NT, K=16) that accumulate into the NT
-//          TMEM columns and commits them to the stage's mbarrier; the CTA goes straight on to fill the other stage,
-//          waiting (bounded) on a stage's mbarrier only before it overwrites it.
-// Two CTAs fit a multiprocessor (97 KB of shared memory, 256 TMEM columns each), so one CTA's fill overlaps the other's MMAs.
-// (An unswizzled operand layout ran the same MMAs about five times slower.)
+// A CTA of 256 threads owns 128 weight rows (8 tiles of the fragment-major layout, one per warp) and NT activation rows.
+// Four shared-memory stages rotate over the K groups of 64 inputs; per group
+//   B  the NT x 64 activations go global -> shared memory by cp.async (16-byte pieces, no registers), issued TWO groups
+//      ahead into the stage whose MMAs of four groups ago have completed;
+//   A  each warp dequantises its tile's fragment register (16 nibbles of two weight rows; scale and bias applied with one
+//      fp16x2 multiply-add per pair; halves put back in natural order) into the stage -- the register was loaded two
+//      groups ahead;
+//   then cp.async.wait_group, fence.proxy.async, barrier, and one thread issues four MMAs (M=128, N=NT, K=16) that
+//   accumulate into the NT TMEM columns and commits them to the stage's mbarrier.
+// Operand tiles are K-major with the 128-byte swizzle (an unswizzled layout ran the same MMAs several times slower).
 #include "kernels.h"
 #include "gemv.cuh"
 
@@ -75,8 +73,10 @@ __device__ __forceinline__ bool tc_wait(uint64_t* b, uint32_t parity) {
     return false;
 }
 // ---- pieces of a K group shared by the dense and the grouped-expert kernels ----
-// fragment registers of one 16-row tile (wv: nibbles of rows A_r / B_r, sv: their scales and biases for the pair of
-// groups) -> fp16 weights in the A stage
+constexpr int TC_STAGES = 4;
+constexpr int TC_THREADS = 256;
+// fragment register of one 16-row tile (wv: nibbles of rows A_r / B_r, sv: their scales and biases for the pair of groups)
+// -> fp16 weights, natural order, in the A stage
 __device__ __forceinline__ void tc_dequant_A(unsigned char* sA, int tl, int r, int t, int g, uint4 wv, uint4 sv, bool valid) {
     uint4 o[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
     if (valid) {
@@ -87,15 +87,18 @@ __device__ __forceinline__ void tc_dequant_A(unsigned char* sA, int tl, int r, i
         const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
-            uint32_t d[4];
-            dequant8(words[wi], d);
+            uint32_t d[4], w[4];
+            dequant8(words[wi], d);                                    // (q0,q4) (q1,q5) (q2,q6) (q3,q7)
             const __half2 sc = (wi < 2) ? sA2 : sB2, bi = (wi < 2) ? bA2 : bB2;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&o[wi]);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const __half2 wq = __hfma2(*reinterpret_cast<const __half2*>(&d[j]), sc, bi);
-                ow[j] = *reinterpret_cast<const uint32_t*>(&wq);
+                w[j] = *reinterpret_cast<const uint32_t*>(&wq);
             }
+            o[wi].x = __byte_perm(w[0], w[1], 0x5410);                 // (w0, w1)
+            o[wi].y = __byte_perm(w[2], w[3], 0x5410);                 // (w2, w3)
+            o[wi].z = __byte_perm(w[0], w[1], 0x7632);                 // (w4, w5)
+            o[wi].w = __byte_perm(w[2], w[3], 0x7632);                 // (w6, w7)
         }
     }
     const int rowA = tl * 16 + r;                                     // row A_r of the tile; B_r is 8 rows further (the next atom)
@@ -104,21 +107,13 @@ __device__ __forceinline__ void tc_dequant_A(unsigned char* sA, int tl, int r, i
     *reinterpret_cast<uint4*>(tc_at(sA, rowA + 8, 2 * t)) = o[2];
     *reinterpret_cast<uint4*>(tc_at(sA, rowA + 8, 2 * t + 1)) = o[3];
 }
-// piece idx of the B stage: token = 8 * (idx / 64) + idx % 8, chunk = (idx / 8) % 8 -- the 8 lanes of a quarter warp store
-// into the 8 rows of one atom (distinct swizzled chunks: no bank conflict) and read 4 x 64 contiguous bytes per token row
+// piece idx of the B stage: token = 8 * (idx / 64) + idx % 8, chunk = (idx / 8) % 8 -- the 8 lanes of a quarter warp write
+// into the 8 rows of one atom (distinct swizzled chunks) and read 4 x 64 contiguous bytes per token row
 __device__ __forceinline__ void tc_piece(int idx, int& n, int& c) { n = ((idx >> 6) << 3) + (idx & 7); c = (idx >> 3) & 7; }
-template <int NT>
-__device__ __forceinline__ void tc_store_B(unsigned char* sB, int tid, const uint4* xv) {
-#pragma unroll
-    for (int h = 0; h < NT * 8 / 128; ++h) {
-        int n, c; tc_piece(tid + 128 * h, n, c);
-        const uint4 v = xv[h];
-        uint4 o;
-        o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
-        o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
-        *reinterpret_cast<uint4*>(tc_at(sB, n, c)) = o;
-    }
+__device__ __forceinline__ void tc_cp16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void tc_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // one thread: four MMAs of K = 16 (two 16-byte chunks each) accumulating into the NT columns, then the commit
 template <int NT>
 __device__ __forceinline__ void tc_issue(unsigned char* sA, unsigned char* sB, uint32_t tmem_base, uint32_t idesc, bool first, uint64_t* bar) {
@@ -130,6 +125,68 @@ __device__ __forceinline__ void tc_issue(unsigned char* sA, unsigned char* sB, u
     }
     umma_commit(bar);
 }
+// The K loop of one output tile.  load_a(g, wv, sv): this warp's fragment register of group g; b_src(n): global address
+// of token row n's first input, or nullptr (the row stays zero).  cb: commits made on EACH stage's barrier by earlier tiles
+// of this CTA (a tile adds G/4 to every stage; G is a multiple of 4); advanced here.  Returns false if a wait ran out.
+template <int NT, class LoadA, class BSrc>
+__device__ __forceinline__ bool tc_mainloop(unsigned char* smem, uint64_t* s_bar, int& cb, uint32_t tmem_base, int G, bool tvalid,
+                                            LoadA load_a, BSrc b_src) {
+    constexpr int A_BYTES = TC_ROWS * 128, B_BYTES = NT * 128, STAGE = A_BYTES + B_BYTES, NB = NT * 8 / TC_THREADS;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, t = lane & 3;
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);   // f32 accumulate, f16 x f16, K-major both
+    bool ok = true;
+    // this thread's pieces of the B tile: source row pointer (or null) and offset inside a stage
+    const __half* bsrc[NB]; uint32_t boff[NB];
+#pragma unroll
+    for (int h = 0; h < NB; ++h) {
+        int n, c; tc_piece(tid + TC_THREADS * h, n, c);
+        const __half* p = b_src(n);
+        bsrc[h] = p ? p + c * 8 : nullptr;
+        boff[h] = (uint32_t)(tc_at(smem + A_BYTES, n, c) - smem);
+        if (!p) {
+#pragma unroll
+            for (int s = 0; s < TC_STAGES; ++s) *reinterpret_cast<uint4*>(smem + (size_t)s * STAGE + boff[h]) = make_uint4(0, 0, 0, 0);
+        }
+    }
+    auto issue_b = [&](int g) {
+        unsigned char* st = smem + (size_t)(g % TC_STAGES) * STAGE;
+#pragma unroll
+        for (int h = 0; h < NB; ++h) if (bsrc[h]) tc_cp16(st + boff[h], bsrc[h] + g * 64);
+    };
+    uint4 wv0, sv0, wv1, sv1;                                              // fragment registers of groups g and g + 1
+    if (tvalid) { load_a(0, wv0, sv0); if (G > 1) load_a(1, wv1, sv1); }
+    issue_b(0); tc_cp_commit();
+    if (G > 1) issue_b(1);
+    tc_cp_commit();
+    auto step = [&](int g, uint4& wv, uint4& sv) {
+        const int s = g % TC_STAGES;
+        unsigned char* sA = smem + (size_t)s * STAGE;
+        // B of group g + 2 goes into the stage last read by the MMAs of group g + 2 - TC_STAGES
+        if (g + 2 < G) {
+            const int s2 = (g + 2) % TC_STAGES;
+            if (g + 2 >= TC_STAGES && !tc_wait(&s_bar[s2], (uint32_t)((cb + (g + 2) / TC_STAGES - 1) & 1))) ok = false;
+            issue_b(g + 2);
+        }
+        tc_cp_commit();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tc_dequant_A(sA, warp, r, t, g, wv, sv, tvalid);                   // (this stage was waited for when its B copies were issued)
+        if (tvalid && g + 2 < G) load_a(g + 2, wv, sv);
+        asm volatile("cp.async.wait_group 2;" ::: "memory");               // B of group g has landed (groups g + 1, g + 2 may be in flight)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) tc_issue<NT>(sA, sA + A_BYTES, tmem_base, idesc, g == 0, &s_bar[s]);
+    };
+    for (int g = 0; g < G; g += 2) {                                       // G is even (K is a multiple of 256)
+        step(g, wv0, sv0);
+        step(g + 1, wv1, sv1);
+    }
+    // the last commit covers every MMA issued before it
+    cb += G / TC_STAGES;
+    if (!tc_wait(&s_bar[(G - 1) % TC_STAGES], (uint32_t)((cb - 1) & 1))) ok = false;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    return ok;
+}
 
 struct GemmTcArgs {
     Q4R q; int N, K, M;
@@ -140,18 +197,17 @@ struct GemmTcArgs {
 };
 
 template <int NT>
-__global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
-    extern __shared__ __align__(1024) unsigned char smem_raw[];         // 2 stages x [A: 128 rows x 128 B][B: NT tokens x 128 B]
+__global__ void __launch_bounds__(TC_THREADS, 1) k_gemm_umma(GemmTcArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];         // 4 stages x [A: 128 rows x 128 B][B: NT tokens x 128 B]
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // tiles start on 1024-byte boundaries
-    constexpr int A_BYTES = 8 * TC_ROWS * 16, B_BYTES = 8 * NT * 16, STAGE = A_BYTES + B_BYTES;
-    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ __align__(8) uint64_t s_bar[TC_STAGES];
     __shared__ uint32_t s_tmem;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row0 = blockIdx.x * TC_ROWS, t0 = blockIdx.y * NT;
     const int nt = min(NT, a.M - t0);
     const int G = a.K >> 6, GP = G >> 1;
     const int ntiles = a.N >> 4;
-    if (tid == 0) { mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1); mbar_fence_init(); }
+    if (tid == 0) { for (int i = 0; i < TC_STAGES; ++i) mbar_init(&s_bar[i], 1); mbar_fence_init(); }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"((uint32_t)NT) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -160,66 +216,26 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = s_tmem;
-    const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);   // f32 accumulate, f16 x f16, K-major both
-    bool failed = false;
-    // Operands of a K group travel global -> registers -> shared memory.  All of a group's loads are issued together, and
-    // the next group's loads are issued before this group's MMAs, so one round trip to L2 is in flight per group instead
-    // of one per load.
-    constexpr int NB = NT * 8 / 128;                                       // 16-byte activation pieces per thread and group
-    const int r = lane >> 2, t = lane & 3;
-    struct Regs { uint4 wv[2], sv[2], xv[NB]; };
-    Regs ra, rb;                                                           // two register sets: a group's loads have a whole iteration to land
-    bool tvalid[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) tvalid[h] = ((row0 >> 4) + warp + 4 * h) < ntiles;   // (the last CTA of a matrix whose rows are not a multiple of 128)
-    auto load_group = [&](Regs& R, int g) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int T = (row0 >> 4) + warp + 4 * h;
-            if (tvalid[h]) {
-                R.wv[h] = ldg_nc_u4(a.q.wr + ((size_t)T * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
-                R.sv[h] = ldg_nc_u4(a.q.sr + ((size_t)T * GP + (g >> 1)) * 8 + r);
-            }
-        }
-#pragma unroll
-        for (int h = 0; h < NB; ++h) {
-            int n, c; tc_piece(tid + 128 * h, n, c);
-            R.xv[h] = (n < nt) ? __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + n) * a.ldx + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
-        }
-    };
-    auto process = [&](const Regs& R, int g) {
-        const int s = g & 1, use = g >> 1;
-        unsigned char* sA = smem + (size_t)s * STAGE;
-        unsigned char* sB = sA + A_BYTES;
-        // the MMAs that read this stage two groups ago must be done before it is overwritten
-        if (use > 0 && !tc_wait(&s_bar[s], (uint32_t)((use - 1) & 1))) failed = true;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-        for (int h = 0; h < 2; ++h) tc_dequant_A(sA, warp + 4 * h, r, t, g, R.wv[h], R.sv[h], tvalid[h]);
-        tc_store_B<NT>(sB, tid, R.xv);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) tc_issue<NT>(sA, sB, tmem_base, idesc, g == 0, &s_bar[s]);
-    };
-    load_group(ra, 0);
-    for (int g = 0; g < G; g += 2) {                                       // G is even (K is a multiple of 256)
-        load_group(rb, g + 1);
-        process(ra, g);
-        if (g + 2 < G) load_group(ra, g + 2);
-        process(rb, g + 1);
-    }
-    // the last commit covers every MMA issued before it
-    if (!tc_wait(&s_bar[(G - 1) & 1], (uint32_t)(((G - 1) >> 1) & 1))) failed = true;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int T = (row0 >> 4) + warp;                                  // this warp's tile
+    const bool tvalid = T < ntiles;                                    // (the last CTA of a matrix whose rows are not a multiple of 128)
+    const int r = lane >> 2;
+    int cb = 0;
+    bool failed = !tc_mainloop<NT>(smem, s_bar, cb, tmem_base, G, tvalid,
+        [&](int g, uint4& wv, uint4& sv) {
+            wv = ldg_nc_u4(a.q.wr + ((size_t)T * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
+            sv = ldg_nc_u4(a.q.sr + ((size_t)T * GP + (g >> 1)) * 8 + r);
+        },
+        [&](int n) -> const __half* { return n < nt ? a.x + (size_t)(t0 + n) * a.ldx : nullptr; });
     failed = __syncthreads_or(failed ? 1 : 0) != 0;
     if (failed && a.err && tid == 0) atomicOr(a.err, 1u);
     if (!failed) {
-        const int row = row0 + tid;
-        for (int c0 = 0; c0 < NT; c0 += 32) {
+        // accumulator lane = weight row of the CTA; warps w and w + 4 share a lane quarter and split the token columns
+        const int row = row0 + (warp & 3) * 32 + lane;
+        const int cbeg = (warp >> 2) * (NT / 2);
+        for (int c0 = cbeg; c0 < cbeg + NT / 2; c0 += 32) {
             if (c0 >= nt) break;
             uint32_t dreg[32];
-            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, dreg);
+            tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)c0, dreg);
             if (row < a.N) {
 #pragma unroll
                 for (int n = 0; n < 32; ++n) {
@@ -240,7 +256,7 @@ __global__ void __launch_bounds__(128) k_gemm_umma(GemmTcArgs a) {
 
 template <int NT>
 static int launch_gemm_tc_t(const GemmTcArgs& a, cudaStream_t st) {
-    constexpr size_t smem = 2 * (8 * TC_ROWS * 16 + 8 * NT * 16) + 1024;
+    constexpr size_t smem = (size_t)TC_STAGES * (TC_ROWS * 128 + NT * 128) + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(k_gemm_umma<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -248,7 +264,7 @@ static int launch_gemm_tc_t(const GemmTcArgs& a, cudaStream_t st) {
         configured = true;
     }
     dim3 grid((unsigned)((a.N + TC_ROWS - 1) / TC_ROWS), (unsigned)((a.M + NT - 1) / NT));
-    k_gemm_umma<NT><<<grid, 128, smem, st>>>(a);
+    k_gemm_umma<NT><<<grid, TC_THREADS, smem, st>>>(a);
     return (int)cudaGetLastError();
 }
 
@@ -269,15 +285,15 @@ int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, 
 // never interacts with another's, so the result does not depend on which rows share a block.
 constexpr int XT_NT = 64;
 template <bool DOWN>
-__global__ void __launch_bounds__(128) k_expert_umma(ExpertArgs a) {
-    extern __shared__ __align__(1024) unsigned char smem_raw[];         // 2 stages x [A 16 KB][B 8 KB]
-    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // tiles start on 1024-byte boundaries
-    constexpr int NT = XT_NT, A_BYTES = 8 * TC_ROWS * 16, B_BYTES = 8 * NT * 16, STAGE = A_BYTES + B_BYTES, NB = NT * 8 / 128;
-    __shared__ __align__(8) uint64_t s_bar[2];
+__global__ void __launch_bounds__(TC_THREADS, 2) k_expert_umma(ExpertArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];         // 4 stages x [A 16 KB][B 8 KB]
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    constexpr int NT = XT_NT;
+    __shared__ __align__(8) uint64_t s_bar[TC_STAGES];
     __shared__ uint32_t s_tmem;
     __shared__ int s_base[260];
     __shared__ int s_srow[NT], s_dst[NT];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2, t = lane & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, r = lane >> 2;
     const int K = DOWN ? a.I : a.H, G = K >> 6, GP = G >> 1;
     const int ntiles = DOWN ? a.H / 16 : a.I / 8;                       // tiles of 16 weight rows per expert
     const int NRT = (ntiles + 7) / 8;                                   // groups of 128 weight rows
@@ -299,7 +315,7 @@ __global__ void __launch_bounds__(128) k_expert_umma(ExpertArgs a) {
         }
         if (lane == 0) s_base[n_active + 1] = run;
     }
-    if (tid == 0) { mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1); mbar_fence_init(); }
+    if (tid == 0) { for (int i = 0; i < TC_STAGES; ++i) mbar_init(&s_bar[i], 1); mbar_fence_init(); }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"((uint32_t)NT) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -308,9 +324,8 @@ __global__ void __launch_bounds__(128) k_expert_umma(ExpertArgs a) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = s_tmem;
-    const uint32_t idesc = (1u << 4) | ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
     const int total = s_base[n_active + 1] * NRT;
-    int commits[2] = {0, 0};                                             // commits made so far on each stage's barrier (same in every thread)
+    int cb = 0;                                                          // commits made so far on each stage's barrier (same in every thread)
     bool failed = false;
     for (int item = blockIdx.x; item < total && !failed; item += gridDim.x) {
         const int sb = item / NRT, rt = item - sb * NRT;
@@ -332,71 +347,31 @@ __global__ void __launch_bounds__(128) k_expert_umma(ExpertArgs a) {
         }
         __syncthreads();
         const __half* xbase = DOWN ? a.hbuf : a.p;
-        struct Regs { uint4 wv[2], sv[2], xv[NB]; };
-        Regs ra, rb;
-        bool tvalid[2];
-        size_t Tt[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) { const int tile = rt * 8 + warp + 4 * h; tvalid[h] = tile < ntiles; Tt[h] = (size_t)e * ntiles + (tvalid[h] ? tile : 0); }
-        auto load_group = [&](Regs& R, int g) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-                if (tvalid[h]) {
-                    R.wv[h] = ldg_nc_u4(q.wr + (Tt[h] * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
-                    R.sv[h] = ldg_nc_u4(q.sr + (Tt[h] * GP + (g >> 1)) * 8 + r);
-                }
-#pragma unroll
-            for (int h = 0; h < NB; ++h) {
-                int n, c; tc_piece(tid + 128 * h, n, c);
-                const int srow = s_srow[n];
-                R.xv[h] = (srow >= 0) ? __ldcg(reinterpret_cast<const uint4*>(xbase + (size_t)srow * K + g * 64 + c * 8)) : make_uint4(0, 0, 0, 0);
-            }
-        };
-        auto process = [&](const Regs& R, int g) {
-            const int s = g & 1;
-            unsigned char* sA = smem + (size_t)s * STAGE;
-            unsigned char* sB = sA + A_BYTES;
-            // the MMAs that read this stage two groups ago (in this item) must be done before it is overwritten
-            if (g >= 2 && !tc_wait(&s_bar[s], (uint32_t)((commits[s] - 1) & 1))) failed = true;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int h = 0; h < 2; ++h) tc_dequant_A(sA, warp + 4 * h, r, t, g, R.wv[h], R.sv[h], tvalid[h]);
-            tc_store_B<NT>(sB, tid, R.xv);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncthreads();
-            if (tid == 0) tc_issue<NT>(sA, sB, tmem_base, idesc, g == 0, &s_bar[s]);
-            commits[s] += 1;
-        };
-        load_group(ra, 0);
-        for (int g = 0; g < G; g += 2) {
-            load_group(rb, g + 1);
-            process(ra, g);
-            if (g + 2 < G) load_group(ra, g + 2);
-            process(rb, g + 1);
-        }
-        {   // the last commit covers every MMA of the item
-            const int s = (G - 1) & 1;
-            if (!tc_wait(&s_bar[s], (uint32_t)((commits[s] - 1) & 1))) failed = true;
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int tile = rt * 8 + warp;
+        const bool tvalid = tile < ntiles;
+        const size_t Tt = (size_t)e * ntiles + (tvalid ? tile : 0);
+        failed = !tc_mainloop<NT>(smem, s_bar, cb, tmem_base, G, tvalid,
+            [&](int g, uint4& wv, uint4& sv) {
+                wv = ldg_nc_u4(q.wr + (Tt * GP + (g >> 1)) * 64 + (g & 1) * 32 + lane);
+                sv = ldg_nc_u4(q.sr + (Tt * GP + (g >> 1)) * 8 + r);
+            },
+            [&](int n) -> const __half* { const int srow = s_srow[n]; return srow >= 0 ? xbase + (size_t)srow * K : nullptr; });
         failed = __syncthreads_or(failed ? 1 : 0) != 0;
         if (!failed) {
-            const int i16 = tid & 15, tl = tid >> 4, tile = rt * 8 + tl;
+            const int i = (warp & 3) * 32 + lane;                        // accumulator lane = weight row inside the 128
+            const int i16 = i & 15, tl = i >> 4, etile = rt * 8 + tl;
+            const int c0 = (warp >> 2) * (NT / 2);                       // warps w and w + 4 split the token columns
+            uint32_t dreg[32];
+            tmem_ld32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)c0, dreg);
 #pragma unroll
-            for (int c0 = 0; c0 < NT; c0 += 32) {
-                uint32_t dreg[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, dreg);
-#pragma unroll
-                for (int n = 0; n < 32; ++n) {
-                    const float v = __uint_as_float(dreg[n]);
-                    const int dst = s_dst[c0 + n];
-                    if (DOWN) {
-                        if (dst >= 0 && tile < ntiles) a.dbuf[(size_t)dst * a.H + (size_t)rt * TC_ROWS + tid] = f2h(v);
-                    } else {
-                        const float other = __shfl_xor_sync(0xffffffffu, v, 8);               // the up row of this gate row
-                        if (dst >= 0 && tile < ntiles && i16 < 8) a.hbuf[(size_t)dst * a.I + tile * 8 + i16] = swiglu_h(f2h(v), f2h(other));
-                    }
+            for (int n = 0; n < 32; ++n) {
+                const float v = __uint_as_float(dreg[n]);
+                const int dst = s_dst[c0 + n];
+                if (DOWN) {
+                    if (dst >= 0 && etile < ntiles) a.dbuf[(size_t)dst * a.H + (size_t)rt * TC_ROWS + i] = f2h(v);
+                } else {
+                    const float other = __shfl_xor_sync(0xffffffffu, v, 8);               // the up row of this gate row
+                    if (dst >= 0 && etile < ntiles && i16 < 8) a.hbuf[(size_t)dst * a.I + etile * 8 + i16] = swiglu_h(f2h(v), f2h(other));
                 }
             }
         }
@@ -412,14 +387,14 @@ template <bool DOWN>
 static bool launch_expert_tc_t(const ExpertArgs& a, cudaStream_t st) {
     const int K = DOWN ? a.I : a.H;
     if (K % 256 || a.ep_pairs_per_rank > 0) return false;              // (expert-parallel calls keep the row kernels)
-    constexpr size_t smem = 2 * (8 * TC_ROWS * 16 + 8 * XT_NT * 16) + 1024;
+    constexpr size_t smem = (size_t)TC_STAGES * (TC_ROWS * 128 + XT_NT * 128) + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(k_expert_umma<DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return false;
         configured = true;
     }
-    const int grid = 4 * sm_count();                                    // 48 KB of shared memory and 64 TMEM columns per CTA: four fit a multiprocessor
-    profile_launch(DOWN ? "k_expert_umma_down" : "k_expert_umma_gateup", st, [&] { k_expert_umma<DOWN><<<grid, 128, smem, st>>>(a); return 0; });
+    const int grid = 2 * sm_count();                                    // 97 KB of shared memory and 64 TMEM columns per CTA: two fit a multiprocessor
+    profile_launch(DOWN ? "k_expert_umma_down" : "k_expert_umma_gateup", st, [&] { k_expert_umma<DOWN><<<grid, TC_THREADS, smem, st>>>(a); return 0; });
     return true;
 }
 bool launch_expert_tc_gateup(const ExpertArgs& a, cudaStream_t st) { return launch_expert_tc_t<false>(a, st); }

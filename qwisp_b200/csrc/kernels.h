@@ -200,6 +200,7 @@ bool launch_expert_tc_gateup(const ExpertArgs& a, cudaStream_t st);
 bool launch_expert_tc_down(const ExpertArgs& a, cudaStream_t st);
 // router for many rows: a.h holds rows that are already normed; logits kernel + routing / pair lists kernel
 bool launch_router_rows(const RouterArgs& a, cudaStream_t st);
+bool launch_router_mma(const RouterArgs& a, cudaStream_t st);    // prefill mode, fp16 router: logits on the tensor cores
 bool launch_expert_rows_gateup(const ExpertArgs& a, cudaStream_t st);
 bool launch_expert_rows_down(const ExpertArgs& a, cudaStream_t st);
 void launch_moe_combine(const __half* dbuf, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,

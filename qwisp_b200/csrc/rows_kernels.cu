@@ -641,6 +641,87 @@ __global__ void __launch_bounds__(256) k_route_rows(RouterArgs a) {
         a.lists.pairs[s_off[ex] + pos] = i;
     }
 }
+// Prefill mode: the fp16 router logits as a small tensor-core GEMM (mma.sync m16n8k16, f32 accumulators): a CTA of 4 warps
+// computes 64 rows x 64 experts, K in chunks of 64 through two cp.async buffers (16-byte pieces swizzled by the row).
+// Not the bit pattern of the strict router (the f32 sums run in MMA order), but a row's logits depend on that row only
+// and K is walked in a fixed order, so they do not depend on how a prompt is cut into calls.  The shared-gate logit is a
+// plain warp dot (the strict order) done by the CTAs of the first expert tile.
+__device__ __forceinline__ void rt_ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ __half* rt_at(__half* base, int row, int chunk) { return base + row * 64 + ((chunk ^ (row & 7)) << 3); }   // rows of 64 halves
+__global__ void __launch_bounds__(128) k_router_mma(RouterArgs a) {
+    __shared__ __align__(128) __half As[2][64 * 64], Bs[2][64 * 64];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * 64, e0 = blockIdx.y * 64;
+    const int rows = min(64, a.M - m0), cols = min(64, a.E - e0);
+    auto stage = [&](int kc, int b) {
+        for (int i = tid; i < 64 * 8; i += 128) {
+            const int r = i >> 3, c = i & 7;
+            if (r < rows) cp_async16(rt_at(As[b], r, c), a.h + (size_t)(m0 + r) * a.ldh + kc * 64 + c * 8);
+            else *reinterpret_cast<uint4*>(rt_at(As[b], r, c)) = make_uint4(0, 0, 0, 0);
+            if (r < cols) cp_async16(rt_at(Bs[b], r, c), a.router + (size_t)(e0 + r) * a.H + kc * 64 + c * 8);
+            else *reinterpret_cast<uint4*>(rt_at(Bs[b], r, c)) = make_uint4(0, 0, 0, 0);
+        }
+        cp_async_commit();
+    };
+    float acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) { acc[n][0] = 0.f; acc[n][1] = 0.f; acc[n][2] = 0.f; acc[n][3] = 0.f; }
+    const int nk = a.H >> 6;
+    stage(0, 0);
+    for (int kc = 0; kc < nk; ++kc) {
+        const int b = kc & 1;
+        if (kc + 1 < nk) { stage(kc + 1, b ^ 1); cp_async_wait<1>(); } else cp_async_wait<0>();
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            rt_ldsm_x4(a0, a1, a2, a3, rt_at(As[b], warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b0, b1, b2, b3;
+                const int mi = lane >> 3;
+                rt_ldsm_x4(b0, b1, b2, b3, rt_at(Bs[b], (np * 2 + (mi >> 1)) * 8 + (lane & 7), ks * 2 + (mi & 1)));
+                mma_f16(acc[np * 2], a0, a1, a2, a3, b0, b1);
+                mma_f16(acc[np * 2 + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = warp * 16 + (lane >> 2) + 8 * (i >> 1), c = n * 8 + 2 * (lane & 3) + (i & 1);
+            if (r < rows && c < cols) a.logits[(size_t)(m0 + r) * a.E + e0 + c] = f2h(acc[n][i]);
+        }
+    if (blockIdx.y == 0) {                     // shared-gate logit of the CTA's rows: lane l owns 8 inputs of every 256-wide block
+        for (int r = warp; r < rows; r += 4) {
+            const __half* xrow = a.h + (size_t)(m0 + r) * a.ldh;
+            float s = 0.f;
+            for (int kb = 0; kb < (a.H >> 8); ++kb) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(xrow + kb * 256 + lane * 8);
+                const uint4 wv = *reinterpret_cast<const uint4*>(a.shared_gate + kb * 256 + lane * 8);
+                const __half* xh = reinterpret_cast<const __half*>(&xv);
+                const __half* wh = reinterpret_cast<const __half*>(&wv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s = fmaf(h2f(xh[i]), h2f(wh[i]), s);
+            }
+            s = warp_sum(s);
+            if (lane == 0) a.sgl[m0 + r] = f2h(s);
+        }
+    }
+}
+// prefill mode, fp16 router: logits on the tensor cores, then the routing / pair-list kernel.  false: not covered.
+bool launch_router_mma(const RouterArgs& a, cudaStream_t st) {
+    if (a.E > 256 || a.H % 256 || a.norm_w || a.router_q8 || a.sg_q8) return false;
+    const dim3 grid((unsigned)((a.M + 63) / 64), (unsigned)((a.E + 63) / 64));
+    profile_launch("k_router_mma", st, [&] { k_router_mma<<<grid, 128, 0, st>>>(a); return 0; });
+    profile_launch("k_route_rows", st, [&] { k_route_rows<<<(a.M + 7) / 8, 256, 0, st>>>(a); return 0; });
+    return true;
+}
+
 // rows already normed in a.h (ldh); E <= 256.  Returns false when the shape is not covered.
 bool launch_router_rows(const RouterArgs& a, cudaStream_t st) {
     if (a.E > 256 || a.H % 256 || a.H > 4096 || a.norm_w) return false;
