@@ -17,8 +17,8 @@
 //   A  each warp dequantises its tile's fragment register (16 nibbles of two weight rows; scale and bias applied with one
 //      fp16x2 multiply-add per pair; halves put back in natural order) into the stage -- the register was loaded two
 //      groups ahead;
-//   then cp.async.wait_group, fence.proxy.async, barrier, and one thread issues four MMAs (M=128, N=NT, K=16) that
-//   accumulate into the NT TMEM columns and commits them to the stage's mbarrier.
+//   two groups share one cp.async.wait_group + fence.proxy.async + barrier, after which one thread issues eight MMAs
+//   (M=128, N=NT, K=16) that accumulate into the NT TMEM columns and commits them to a stage mbarrier.
 // Operand tiles are K-major with the 128-byte swizzle (an unswizzled layout ran the same MMAs several times slower).
 #include "kernels.h"
 #include "gemv.cuh"
@@ -114,20 +114,9 @@ __device__ __forceinline__ void tc_cp16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void tc_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// one thread: four MMAs of K = 16 (two 16-byte chunks each) accumulating into the NT columns, then the commit
-template <int NT>
-__device__ __forceinline__ void tc_issue(unsigned char* sA, unsigned char* sB, uint32_t tmem_base, uint32_t idesc, bool first, uint64_t* bar) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-        const uint64_t da = umma_desc_sw128(sA + ks * 32), db = umma_desc_sw128(sB + ks * 32);      // 16 halves further along K
-        umma_f16(tmem_base, da, db, idesc, (!first || ks > 0) ? 1u : 0u);
-    }
-    umma_commit(bar);
-}
 // The K loop of one output tile.  load_a(g, wv, sv): this warp's fragment register of group g; b_src(n): global address
-// of token row n's first input, or nullptr (the row stays zero).  cb: commits made on EACH stage's barrier by earlier tiles
-// of this CTA (a tile adds G/4 to every stage; G is a multiple of 4); advanced here.  Returns false if a wait ran out.
+// of token row n's first input, or nullptr (the row stays zero).  cb: commits made on the barriers of stages 1 and 3 by
+// earlier tiles of this CTA (a tile adds G/4 to each; G is a multiple of 4); advanced here.  Returns false if a wait ran out.
 template <int NT, class LoadA, class BSrc>
 __device__ __forceinline__ bool tc_mainloop(unsigned char* smem, uint64_t* s_bar, int& cb, uint32_t tmem_base, int G, bool tvalid,
                                             LoadA load_a, BSrc b_src) {
@@ -154,35 +143,43 @@ __device__ __forceinline__ bool tc_mainloop(unsigned char* smem, uint64_t* s_bar
         for (int h = 0; h < NB; ++h) if (bsrc[h]) tc_cp16(st + boff[h], bsrc[h] + g * 64);
     };
     uint4 wv0, sv0, wv1, sv1;                                              // fragment registers of groups g and g + 1
-    if (tvalid) { load_a(0, wv0, sv0); if (G > 1) load_a(1, wv1, sv1); }
-    issue_b(0); tc_cp_commit();
-    if (G > 1) issue_b(1);
+    if (tvalid) { load_a(0, wv0, sv0); load_a(1, wv1, sv1); }
+    issue_b(0); issue_b(1);
     tc_cp_commit();
-    auto step = [&](int g, uint4& wv, uint4& sv) {
-        const int s = g % TC_STAGES;
-        unsigned char* sA = smem + (size_t)s * STAGE;
-        // B of group g + 2 goes into the stage last read by the MMAs of group g + 2 - TC_STAGES
+    // Two groups per barrier: B of the NEXT pair is requested first (its stages were last read by the MMAs of the pair
+    // before this one), then both A tiles of this pair are dequantised, then one wait + fence + barrier and eight MMAs.
+    for (int g = 0; g < G; g += 2) {                                       // G is a multiple of 4 (K is a multiple of 256)
+        const int s0 = g % TC_STAGES, s1 = s0 + 1;
+        unsigned char* sA0 = smem + (size_t)s0 * STAGE;
+        unsigned char* sA1 = smem + (size_t)s1 * STAGE;
         if (g + 2 < G) {
-            const int s2 = (g + 2) % TC_STAGES;
-            if (g + 2 >= TC_STAGES && !tc_wait(&s_bar[s2], (uint32_t)((cb + (g + 2) / TC_STAGES - 1) & 1))) ok = false;
-            issue_b(g + 2);
+            // stages (g + 2) % 4 and (g + 3) % 4 were used by groups g - 2 and g - 1: their commit is the one on stage (g + 3) % 4
+            const int s3 = (g + 3) % TC_STAGES;
+            if (g >= 2 && !tc_wait(&s_bar[s3], (uint32_t)((cb + (g + 3) / TC_STAGES - 1) & 1))) ok = false;
+            issue_b(g + 2); issue_b(g + 3);
         }
         tc_cp_commit();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        tc_dequant_A(sA, warp, r, t, g, wv, sv, tvalid);                   // (this stage was waited for when its B copies were issued)
-        if (tvalid && g + 2 < G) load_a(g + 2, wv, sv);
-        asm volatile("cp.async.wait_group 2;" ::: "memory");               // B of group g has landed (groups g + 1, g + 2 may be in flight)
+        tc_dequant_A(sA0, warp, r, t, g, wv0, sv0, tvalid);
+        tc_dequant_A(sA1, warp, r, t, g + 1, wv1, sv1, tvalid);
+        if (tvalid && g + 2 < G) { load_a(g + 2, wv0, sv0); load_a(g + 3, wv1, sv1); }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");               // B of this pair has landed (the next pair may be in flight)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-        if (tid == 0) tc_issue<NT>(sA, sA + A_BYTES, tmem_base, idesc, g == 0, &s_bar[s]);
-    };
-    for (int g = 0; g < G; g += 2) {                                       // G is even (K is a multiple of 256)
-        step(g, wv0, sv0);
-        step(g + 1, wv1, sv1);
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                unsigned char* sA = (ks < 4) ? sA0 : sA1;
+                const uint64_t da = umma_desc_sw128(sA + (ks & 3) * 32), db = umma_desc_sw128(sA + A_BYTES + (ks & 3) * 32);
+                umma_f16(tmem_base, da, db, idesc, (g > 0 || ks > 0) ? 1u : 0u);
+            }
+            umma_commit(&s_bar[s1]);                                       // one commit per pair, on the odd stage's barrier
+        }
     }
     // the last commit covers every MMA issued before it
-    cb += G / TC_STAGES;
+    cb += G / TC_STAGES;                                                   // commits so far on the barriers of stages 1 and 3
     if (!tc_wait(&s_bar[(G - 1) % TC_STAGES], (uint32_t)((cb - 1) & 1))) ok = false;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     return ok;
