@@ -134,6 +134,7 @@ def cpu_oracle_sample(max_seconds, prompt_tokens=2, min_steps=2, max_steps=16):
     runs twice on the same tokens: the first pass generates the routed experts it touches, the
     second pass is the timed one."""
     from oracle import oracle as O
+    O.set_num_threads(os.cpu_count())
     cfg = O.config()
     t0 = time.time()
     model = O.Model(cfg, 0, lazy_experts=True)
@@ -171,6 +172,7 @@ def cpu_oracle_batch_sample(n_streams, prompt_tokens, steps):
     `steps` rounds in which each stream decodes one token (the oracle has no batched step; a round is the
     streams one after another, each step using all host cores).  Returns aggregate tok/s of the rounds."""
     from oracle import oracle as O
+    O.set_num_threads(os.cpu_count())        # (a torchrun worker's OpenMP runtime starts with one thread)
     cfg = O.config()
     t0 = time.time()
     model = O.Model(cfg, 0, lazy_experts=True)

@@ -146,6 +146,12 @@ def quantize_q8(w):
     return q.reshape(N, K), scale, bias
 
 
+def set_num_threads(n):
+    """OpenMP threads of the oracle's loops; returns the count in force."""
+    lib().orc_set_num_threads.restype = C.c_int
+    return int(lib().orc_set_num_threads(C.c_int(int(n))))
+
+
 def qmm4(x, packed, s, b):
     x = np.ascontiguousarray(x, dtype=np.float16)
     M, K = x.shape

@@ -37,6 +37,9 @@
 #include <string>
 #include <vector>
 #include <algorithm>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 typedef _Float16 h16;
 
@@ -70,6 +73,16 @@ static inline float sigmoid_f(float x) {
 // order, used only by the control experiment that measures how far two correct
 // implementations of the random-weight model drift apart.
 static int g_alt_order = 0;
+// Threads of the parallel loops below (test / bench infrastructure: a host process whose OpenMP runtime was initialised
+// with OMP_NUM_THREADS=1, as torch.distributed.run's workers are, sets the count here).  Returns the count in force.
+extern "C" int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n; return 1;
+#endif
+}
 extern "C" void orc_set_alt_order(int on) { g_alt_order = on; }
 static inline float bfly_sum32(const float* v) {
     float a[32], b[32];
