@@ -510,7 +510,8 @@ void pf_q4(PfList& pf, int i, const Q4R& q, size_t max_bytes = (size_t)48 << 20)
 // routing / pair-list kernel, same bits); otherwise the one-kernel router.
 void enqueue_router(sl_engine* e, const RouterArgs& ra, int M, bool pdl) {
     cudaStream_t st = e->stream;
-    if (M > 8 && e->use_rows && !ra.no_route && e->E <= 256 && ra.norm_w && ra.ldh == e->H) {
+    // (expert-parallel calls take this path from 2 rows on: its routing kernel spreads the dispatch over CTAs and warps)
+    if ((M > 8 || (ra.epd.sig.world > 0 && M > 1)) && e->use_rows && !ra.no_route && e->E <= 256 && ra.norm_w && ra.ldh == e->H) {
         launch_final_norm(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, st);
         RouterArgs rb = ra; rb.h = ra.p; rb.ldh = e->H; rb.norm_w = nullptr;
         if (e->hybrid && M >= 64 && launch_router_mma(rb, st)) return;
