@@ -12,8 +12,8 @@
 //   k_rows_prep      the prologue (plain / RMSNorm / gated RMSNorm) of every row, written once per call: activations in the
 //                    paired order the dequantiser produces (0,4,1,5,2,6,3,7 inside every 8) + the per-group sums.
 //   k_gemv_rows      dense projection: a CTA of 8 warps = 8 tiles x (8*RG rows); the rows' slice of 256 inputs is staged in
-//                    shared memory (cp.async, two buffers) and shared by the warps; each warp's tile arrives in its own
-//                    shared-memory buffer by bulk copies, 8 slices at a time.
+//                    shared memory (cp.async, two buffers) and shared by the warps; each warp streams its tile's slices
+//                    from global memory two slices ahead.
 //   k_expert_rows    routed + shared experts grouped by expert: persistent CTAs of 16 consumer warps + 1 producer warp.
 //                    The producer gathers the rows of the next (expert, row block) into a ring of shared-memory stages with
 //                    bulk copies (mbarrier full / empty), the consumers each own one tile over the whole K -- no CTA-wide
@@ -158,13 +158,11 @@ struct RowsDenseArgs {
     Q4R q; int N, K, M;
     const __half* xq; const float* sxq;  // prepared rows
     __half* y; int ldy;
-    unsigned* err;
 };
 constexpr int RD_XS = 256 + 8;           // halves per staged row of one slice (16 bytes of skew: conflict-free B loads)
-constexpr int RW_PHASE = 8;              // slices of a tile held in a warp's weight buffer at a time
 // grid (ceil(tiles / 8), ceil(M / (8*RG))), 256 threads
 template <int EPI, int RG>
-__global__ void __launch_bounds__(256, 1) k_gemv_rows(RowsDenseArgs a) {
+__global__ void __launch_bounds__(256, RG == 1 ? 2 : 1) k_gemv_rows(RowsDenseArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int NR = 8 * RG;
     __half* xs = reinterpret_cast<__half*>(smem);                               // [2][NR][RD_XS]
@@ -191,39 +189,20 @@ __global__ void __launch_bounds__(256, 1) k_gemv_rows(RowsDenseArgs a) {
         }
         cp_async_commit();
     };
-    // The warp's tile arrives in its own shared-memory buffer by two bulk copies per phase of up to 8 slices (the units of a
-    // tile are contiguous in the fragment-major layout): every weight byte of the phase is requested at once, so the warp
-    // pays one memory round trip per phase instead of one per slice.
-    uint4* wbuf = reinterpret_cast<uint4*>(smem + (size_t)2 * NR * RD_XS * 2 + (size_t)2 * NR * 4 * 4) + (size_t)warp * (RW_PHASE * (128 + 16));
-    uint4* sbuf = wbuf + RW_PHASE * 128;
-    __shared__ __align__(8) uint64_t s_wbar[8];
-    auto fetch = [&](int phase) {
-        const int s0 = phase * RW_PHASE, n = min(RW_PHASE, slices - s0);
-        mbar_expect_tx(&s_wbar[warp], (uint32_t)n * (2048 + 256));
-        bulk_g2s(wbuf, wt + (size_t)s0 * 128, (uint32_t)n * 2048, &s_wbar[warp]);
-        bulk_g2s(sbuf, stl + (size_t)s0 * 16, (uint32_t)n * 256, &s_wbar[warp]);
-    };
-    if (lane == 0) { mbar_init(&s_wbar[warp], 1); mbar_fence_init(); if (active) fetch(0); }
-    __syncwarp();
+    SliceRegs cur, n1, n2;                                    // this slice and the next two (weights stream two slices ahead)
+    if (active) { load_slice(cur, wt, stl, 0, lane); if (slices > 1) load_slice(n1, wt, stl, 1, lane); }
     stage(0, 0);
     float tot[RG][4];
 #pragma unroll
     for (int q = 0; q < RG; ++q) { tot[q][0] = 0.f; tot[q][1] = 0.f; tot[q][2] = 0.f; tot[q][3] = 0.f; }
-    bool failed = false;
 #pragma unroll 1
     for (int s = 0; s < slices; ++s) {
-        const int b = s & 1, phase = s / RW_PHASE, ps = s - phase * RW_PHASE;
+        const int b = s & 1;
+        if (active && s + 2 < slices) load_slice(n2, wt, stl, s + 2, lane);
         if (s + 1 < slices) { stage(s + 1, b ^ 1); cp_async_wait<1>(); }
         else cp_async_wait<0>();
         __syncthreads();
         if (active) {
-            if (ps == 0 && !mbar_wait_bounded(&s_wbar[warp], (uint32_t)(phase & 1))) failed = true;
-            SliceRegs cur;
-            load_slice_smem(cur, wbuf + (size_t)ps * 128, sbuf + (size_t)ps * 16, lane);
-            if (ps == RW_PHASE - 1 && s + 1 < slices) {                  // the buffer is consumed: request the next phase into it
-                __syncwarp();
-                if (lane == 0) { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); fetch(phase + 1); }
-            }
             float accS[RG][4], accB[RG][4];
 #pragma unroll
             for (int q = 0; q < RG; ++q)
@@ -233,8 +212,8 @@ __global__ void __launch_bounds__(256, 1) k_gemv_rows(RowsDenseArgs a) {
             add_slice<RG>(tot, accS, accB);
         }
         __syncthreads();                       // the buffer may be refilled by the next iteration's stage()
+        cur = n1; n1 = n2;
     }
-    if (failed && a.err && lane == 0) atomicOr(a.err, 1u);
     if (!active) return;
 #pragma unroll
     for (int q = 0; q < RG; ++q)
@@ -251,7 +230,7 @@ __global__ void __launch_bounds__(256, 1) k_gemv_rows(RowsDenseArgs a) {
 }
 template <int EPI, int RG>
 static void launch_gemv_rows_t(const RowsDenseArgs& a, cudaStream_t st) {
-    const size_t smem = (size_t)2 * 8 * RG * RD_XS * 2 + (size_t)2 * 8 * RG * 4 * 4 + (size_t)8 * RW_PHASE * (2048 + 256);
+    const size_t smem = (size_t)2 * 8 * RG * RD_XS * 2 + (size_t)2 * 8 * RG * 4 * 4;
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_gemv_rows<EPI, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); configured = true; }
     const dim3 grid((unsigned)(((a.N >> 4) + 7) / 8), (unsigned)((a.M + 8 * RG - 1) / (8 * RG)));
@@ -262,7 +241,7 @@ bool launch_dense_rows(int pro, int epi, const DenseArgs& a, cudaStream_t st) {
     if (!a.xq || !a.sxq || a.K % 256 || a.K > 4096 || a.N % 16 || (epi != EPI_STORE && epi != EPI_RESID)) return false;
     RowsPrepArgs p{a.x, a.ldx, a.nw, a.nw32, a.z, a.ldz, a.eps, a.K, a.xq, a.sxq};
     launch_rows_prep_args(pro, p, a.M, st);
-    RowsDenseArgs d{a.q, a.N, a.K, a.M, a.xq, a.sxq, a.y, a.ldy, a.err};
+    RowsDenseArgs d{a.q, a.N, a.K, a.M, a.xq, a.sxq, a.y, a.ldy};
     // 32 rows per CTA (weights dequantised once per 32 rows) when that still fills the device, else 8
     const long ctas4 = (long)(((a.N >> 4) + 7) / 8) * ((a.M + 31) / 32);
     const bool rg4 = ctas4 >= sm_count();
@@ -436,23 +415,16 @@ __global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int
             if (valid) {
                 const int tile = S.info[10] * XR_CONS + warp;
                 if (DOWN) {
-                    // the 8 outputs of (column, row half) sit in the 8 lanes with the same t: gathered by shuffles so that
-                    // one lane stores 16 contiguous bytes of the pair's output row (local, or the pair owner's over NVLink)
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const unsigned hb = __half_as_ushort(f2h(tot[0][i]));
-                        unsigned v[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] = __shfl_sync(0xffffffffu, hb, j * 4 + t);
                         const int dst = S.info[2 * t + (i & 1)];
-                        if (r == 0 && dst >= 0) {
+                        if (dst >= 0) {
                             __half* rowp = a.dbuf + (size_t)dst * a.H;
                             if (a.ep_pairs_per_rank > 0 && dst < npair) {       // routed pair in expert-parallel mode: the owner's buffer
                                 const int own = dst / a.ep_pairs_per_rank;
                                 rowp = a.peer_dbuf[own] + (size_t)(dst - own * a.ep_pairs_per_rank) * a.H;
                             }
-                            *reinterpret_cast<uint4*>(rowp + tile * 16 + 8 * (i >> 1)) =
-                                make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+                            rowp[tile * 16 + r + 8 * (i >> 1)] = f2h(tot[0][i]);
                         }
                     }
                 } else {
