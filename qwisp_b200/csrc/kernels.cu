@@ -1339,19 +1339,19 @@ __global__ void __launch_bounds__(128) k_gdn_scan(GdnArgs a) {
             const float4 vv = h4(*reinterpret_cast<const uint2*>(&v_s[b][r][warp * 4]));
             const float2 gb = gb_s[b][r];
             const float vs[4] = {vv.x, vv.y, vv.z, vv.w};
-            __half outh[4];
+            // the warp's four rows together: their two butterfly sums share shuffles (warp_sum4), same additions as gdn_row_step()
+            const float kvz = warp_sum4(gdn_decay_dot(S[0], gb.x, kq), gdn_decay_dot(S[1], gb.x, kq), gdn_decay_dot(S[2], gb.x, kq),
+                                        gdn_decay_dot(S[3], gb.x, kq), lane);
+            float op[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float4 s = S[i];
-                outh[i] = f2h(gdn_row_step(s, gb.x, kq, qq, vs[i], gb.y));
-                S[i] = s;
+                const float kv = __shfl_sync(0xffffffffu, kvz, 8 * i);
+                const float delta = (vs[i] - kv) * gb.y;
+                op[i] = gdn_update_dot(S[i], kq, delta, qq);
             }
-            if (lane == 0) {
-                uint2 pk;
-                pk.x = (unsigned)__half_as_ushort(outh[0]) | ((unsigned)__half_as_ushort(outh[1]) << 16);
-                pk.y = (unsigned)__half_as_ushort(outh[2]) | ((unsigned)__half_as_ushort(outh[3]) << 16);
-                *reinterpret_cast<uint2*>(a.y + (size_t)(seg.row0 + t0 + r) * valDim + hv * GDN_DV + dvt * 16 + warp * 4) = pk;
-            }
+            const float oz = warp_sum4(op[0], op[1], op[2], op[3], lane);
+            if ((lane & 7) == 0)
+                a.y[(size_t)(seg.row0 + t0 + r) * valDim + hv * GDN_DV + dvt * 16 + warp * 4 + (lane >> 3)] = f2h(oz);
         }
         __syncthreads();                       // the buffer is refilled by the next iteration's stage()
     }

@@ -43,14 +43,34 @@ __device__ __forceinline__ float gdn_scale_k(float kc, float ik) {
 }
 // One state row (one dv) of one token, the row spread over a warp (lane owns dk 4*lane .. 4*lane+3):
 // S <- S*g;  kv = S.k;  delta = (v - kv)*beta;  S += k*delta;  returns o = S.q (the same value in every lane)
-__device__ __forceinline__ float gdn_row_step(float4& s, float g, float4 kq, float4 qq, float v, float beta) {
+// The two lane-local halves, shared by the one-row form below and the four-rows-at-once form of k_gdn_scan:
+__device__ __forceinline__ float gdn_decay_dot(float4& s, float g, float4 kq) {
     s.x *= g; s.y *= g; s.z *= g; s.w *= g;
-    float kv = s.x * kq.x + s.y * kq.y + s.z * kq.z + s.w * kq.w;
-    kv = warp_sum(kv);
-    float delta = (v - kv) * beta;
+    return s.x * kq.x + s.y * kq.y + s.z * kq.z + s.w * kq.w;
+}
+__device__ __forceinline__ float gdn_update_dot(float4& s, float4 kq, float delta, float4 qq) {
     s.x = fmaf(kq.x, delta, s.x); s.y = fmaf(kq.y, delta, s.y); s.z = fmaf(kq.z, delta, s.z); s.w = fmaf(kq.w, delta, s.w);
-    float o = s.x * qq.x + s.y * qq.y + s.z * qq.z + s.w * qq.w;
-    return warp_sum(o);
+    return s.x * qq.x + s.y * qq.y + s.z * qq.z + s.w * qq.w;
+}
+__device__ __forceinline__ float gdn_row_step(float4& s, float g, float4 kq, float4 qq, float v, float beta) {
+    const float kv = warp_sum(gdn_decay_dot(s, g, kq));
+    const float delta = (v - kv) * beta;
+    return warp_sum(gdn_update_dot(s, kq, delta, qq));
+}
+// Butterfly sums of FOUR values per lane at once: the additions are those of four warp_sum() calls (partners at lane
+// distance 16, 8, 4, 2, 1, in that order; an addition's operands may be swapped, which changes nothing), but the first
+// two levels hand each value to a different quarter of the warp, so 6 shuffles do the work of 20.  On return the lanes
+// 8i .. 8i+7 hold the total of value i.
+__device__ __forceinline__ float warp_sum4(float a, float b, float c, float d, int lane) {
+    const bool hi = (lane & 16) != 0;
+    const float r0 = __shfl_xor_sync(0xffffffffu, hi ? a : c, 16), r1 = __shfl_xor_sync(0xffffffffu, hi ? b : d, 16);
+    const float x = (hi ? c : a) + r0, y = (hi ? d : b) + r1;           // lanes < 16: values a, b; lanes >= 16: c, d
+    const bool b3 = (lane & 8) != 0;
+    float z = (b3 ? y : x) + __shfl_xor_sync(0xffffffffu, b3 ? x : y, 8);
+    z += __shfl_xor_sync(0xffffffffu, z, 4);
+    z += __shfl_xor_sync(0xffffffffu, z, 2);
+    z += __shfl_xor_sync(0xffffffffu, z, 1);
+    return z;
 }
 
 // ---- attention ----
