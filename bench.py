@@ -24,7 +24,12 @@ With N > 1 the workload is the batched one BASELINE.json pairs with multi-GPU: 6
 decoded with the MoE expert-parallel across the N GPUs (dispatch and combine per layer by the library's own
 kernels over NVLink peer memory, attention/GDN data-parallel), aggregate tok/s, total work fixed ("strong").
 The N=1 line carries the same 64-stream workload on one GPU as `batch64_1gpu`, so both series
-(batch 1, batch 64) have their one-GPU point.
+(batch 1, batch 64) have their one-GPU point.  It also carries
+  prefill   -- a 4096-token prompt through the prefill-mode forward in 1024-token calls (tok/s, per-kernel shares)
+  cfg5_1gpu -- BASELINE.json's continuous-batching configuration as a whole job: 64 requests through the
+               token-budget scheduler and the lane slots with the shared-prefix store, wall clock; end-to-end and
+               decode-only tok/s
+(`--no-batch64`, `--no-prefill`, `--no-cfg5` skip them).
 """
 import argparse
 import json

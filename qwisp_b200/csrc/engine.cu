@@ -508,17 +508,19 @@ void pf_q4(PfList& pf, int i, const Q4R& q, size_t max_bytes = (size_t)48 << 20)
 
 // Router of an M-row call.  Many rows: the rows are normed once (k_final_norm), then the many-row router (logits kernel +
 // routing / pair-list kernel, same bits); otherwise the one-kernel router.
-void enqueue_router(sl_engine* e, const RouterArgs& ra, int M, bool pdl) {
+// xq / sxq (optional): also leave the normed rows in the prepared form of the many-row expert kernels; returns true if it did.
+bool enqueue_router(sl_engine* e, const RouterArgs& ra, int M, bool pdl, __half* xq = nullptr, float* sxq = nullptr) {
     cudaStream_t st = e->stream;
     // (expert-parallel calls take this path from 2 rows on: its routing kernel spreads the dispatch over CTAs and warps)
     if ((M > 8 || (ra.epd.sig.world > 0 && M > 1)) && e->use_rows && !ra.no_route && e->E <= 256 && ra.norm_w && ra.ldh == e->H) {
-        launch_final_norm(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, st);
+        launch_final_norm(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, st, xq, sxq);
         RouterArgs rb = ra; rb.h = ra.p; rb.ldh = e->H; rb.norm_w = nullptr;
-        if (e->hybrid && M >= 64 && launch_router_mma(rb, st)) return;
-        if (launch_router_rows(rb, st)) return;
+        if (e->hybrid && M >= 64 && launch_router_mma(rb, st)) return xq != nullptr;
+        if (launch_router_rows(rb, st)) return xq != nullptr;
         // not covered: the one-kernel router norms the rows again from the original input
     }
     launch_router(ra, st, pdl);
+    return false;
 }
 
 // Expert-parallel MoE block of a decode step.  Every rank runs the same number M of rows (its own streams);
@@ -585,9 +587,11 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     // batch-1 decode: the router stops at the logits and the fused expert kernel's CTAs route the row themselves
     ra.no_route = (fused && e->use_route_in_experts) ? 1 : 0;
     ea.route_here = ra.no_route;
-    enqueue_router(e, ra, M, e->use_pdl);
+    const bool tc_experts = e->hybrid && M >= 64 && e->E <= 256 && e->use_rows;
+    const bool rows_experts = !tc_experts && M > 8 && e->E <= 256 && e->use_rows;
+    const bool prepared = enqueue_router(e, ra, M, e->use_pdl, rows_experts ? e->xq_p : nullptr, e->sx_p);
     if (fused && launch_expert_fused(ea, st, e->use_pdl)) return;                      // one launch for gate/up + down
-    if (e->hybrid && M >= 64 && e->E <= 256 && e->use_rows) {
+    if (tc_experts) {
         // prefill mode: grouped GEMMs on the tensor cores, then the combine kernel
         ea.tile_counter = nullptr;
         if (launch_expert_tc_gateup(ea, st) && launch_expert_tc_down(ea, st)) {
@@ -596,9 +600,10 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
         }
         ea.tile_counter = e->tile_counters;
     }
-    if (M > 8 && e->E <= 256 && e->use_rows) {
-        // many rows: the normed rows are prepared once, the experts run without CTA-wide barriers, the combine is its own kernel
-        launch_rows_prep_plain(e->p, e->H, M, e->H, e->xq_p, e->sx_p, st);
+    if (rows_experts || (tc_experts && M > 8)) {
+        // many rows: the normed rows are prepared once (by the norm kernel when it ran), the experts run without CTA-wide
+        // barriers, the combine is its own kernel
+        if (!prepared) launch_rows_prep_plain(e->p, e->H, M, e->H, e->xq_p, e->sx_p, st);
         ea.xq = e->xq_p; ea.sxq = e->sx_p; ea.csum = e->csum; ea.tile_counter = nullptr;
         if (launch_expert_rows_gateup(ea, st) && launch_expert_rows_down(ea, st)) {
             launch_moe_combine(e->dbuf, e->dbuf + (size_t)M * e->topk * e->H, e->scores, e->sgl, M, e->H, e->topk, resid, plain_out, st);

@@ -456,8 +456,10 @@ void launch_embed(const __half* embed, const int* tokens, int M, int H, int voca
 }
 
 // block-wide rmsnorm of one row of width H (multiple of 256, <= 4096) with 256 threads
+// xq_row / sx_row (optional): the normed row also in the prepared form of the many-row kernels (paired order + group sums)
 __device__ __forceinline__ void block_rmsnorm_row(const __half* src, const __half* w, float eps, int H, __half* dst, float* sm8,
-                                                  bool pre = false, uint4 pv = make_uint4(0, 0, 0, 0), uint4 pw = make_uint4(0, 0, 0, 0)) {
+                                                  bool pre = false, uint4 pv = make_uint4(0, 0, 0, 0), uint4 pw = make_uint4(0, 0, 0, 0),
+                                                  __half* xq_row = nullptr, float* sx_row = nullptr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the thread's first 8-element chunk and its weights stay in registers across the reduction,
     // so the common case (H <= 8 * blockDim) touches global memory once
@@ -492,15 +494,17 @@ __device__ __forceinline__ void block_rmsnorm_row(const __half* src, const __hal
             o = v;
         }
         *reinterpret_cast<uint4*>(dst + k) = o;
+        if (xq_row) rows_store(xq_row, sx_row, k, o, lane);     // (every thread of the warp is here: H is a multiple of 256)
     }
 }
-__global__ void k_final_norm(const __half* h, const __half* w, float eps, int H, __half* out) {
+__global__ void k_final_norm(const __half* h, const __half* w, float eps, int H, __half* out, __half* xq, float* sxq) {
     __shared__ float sm8[8];
-    block_rmsnorm_row(h + (size_t)blockIdx.x * H, w, eps, H, out + (size_t)blockIdx.x * H, sm8);
+    block_rmsnorm_row(h + (size_t)blockIdx.x * H, w, eps, H, out + (size_t)blockIdx.x * H, sm8, false, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0),
+                      xq ? xq + (size_t)blockIdx.x * H : nullptr, sxq ? sxq + (size_t)blockIdx.x * (H >> 6) : nullptr);
 }
-void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st) {
+void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st, __half* xq, float* sxq) {
     ProfScope ps("k_final_norm", (double)M * H * 4, st);
-    k_final_norm<<<M, 256, 0, st>>>(h, w, eps, H, out);
+    k_final_norm<<<M, 256, 0, st>>>(h, w, eps, H, out, xq, sxq);
     COUNT_LAUNCH();
 }
 

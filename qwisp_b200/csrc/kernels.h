@@ -234,7 +234,8 @@ void launch_attn_prep(const AttnArgs& a, cudaStream_t st);
 // q/k prep (when every row is its stream's only row) + split-KV decode + merge in one launch; counters: M*KV zeros
 void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStream_t st, bool pdl);
 void launch_step_end(const StepEndArgs& a, cudaStream_t st);
-void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st);
+// xq / sxq (optional): the normed rows also in the prepared form of the many-row kernels
+void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st, __half* xq = nullptr, float* sxq = nullptr);
 void launch_wait_probe(unsigned* err, cudaStream_t st);   // test hook: a bounded wait that runs out sets bit 2 of *err
 int64_t kernel_launch_count();
 void count_launch();

@@ -26,21 +26,6 @@
 namespace sl {
 
 // ================================================================================ prologue rows
-// lane holds the 8 prologue'd activations (row, k0 .. k0+7): paired-order store + group sum (8 lanes = one group),
-// the arithmetic of store_staged()
-__device__ __forceinline__ void rows_store(__half* xq_row, float* sx_row, int k0, uint4 v, int lane) {
-    float s = sum8_f32(v);
-    s += __shfl_xor_sync(0xffffffffu, s, 4);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    if ((lane & 7) == 0) sx_row[k0 >> 6] = s;
-    uint4 o;
-    o.x = __byte_perm(v.x, v.z, 0x5410);
-    o.y = __byte_perm(v.x, v.z, 0x7632);
-    o.z = __byte_perm(v.y, v.w, 0x5410);
-    o.w = __byte_perm(v.y, v.w, 0x7632);
-    *reinterpret_cast<uint4*>(xq_row + k0) = o;
-}
 struct RowsPrepArgs {
     const __half* x; int ldx;            // rows (plain) / residual stream (rmsnorm) / mixer output (gated norm)
     const __half* nw; const float* nw32; // norm weight
