@@ -513,8 +513,10 @@ bool enqueue_router(sl_engine* e, const RouterArgs& ra, int M, bool pdl, __half*
     cudaStream_t st = e->stream;
     // (expert-parallel calls take this path from 2 rows on: its routing kernel spreads the dispatch over CTAs and warps)
     if ((M > 8 || (ra.epd.sig.world > 0 && M > 1)) && e->use_rows && !ra.no_route && e->E <= 256 && ra.norm_w && ra.ldh == e->H) {
-        launch_final_norm(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, st, xq, sxq);
-        RouterArgs rb = ra; rb.h = ra.p; rb.ldh = e->H; rb.norm_w = nullptr;
+        const bool ep = ra.epd.sig.world > 0;
+        if (ep) launch_final_norm_ep(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, ra.epd, st);     // the rows leave for the peers here
+        else launch_final_norm(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, st, xq, sxq);
+        RouterArgs rb = ra; rb.h = ra.p; rb.ldh = e->H; rb.norm_w = nullptr; rb.ep_rows_sent = ep ? 1 : 0;
         if (e->hybrid && M >= 64 && launch_router_mma(rb, st)) return xq != nullptr;
         if (launch_router_rows(rb, st)) return xq != nullptr;
         // not covered: the one-kernel router norms the rows again from the original input

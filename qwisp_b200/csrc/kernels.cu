@@ -502,9 +502,27 @@ __global__ void k_final_norm(const __half* h, const __half* w, float eps, int H,
     block_rmsnorm_row(h + (size_t)blockIdx.x * H, w, eps, H, out + (size_t)blockIdx.x * H, sm8, false, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0),
                       xq ? xq + (size_t)blockIdx.x * H : nullptr, sxq ? sxq + (size_t)blockIdx.x * (H >> 6) : nullptr);
 }
+// expert-parallel form: every thread also stores the pieces of the normed row it has just written into every rank's gather
+// buffer over peer memory, so the rows travel while the router logits are computed; the routing kernel sends the indices
+// and raises the flags (its system-scope fence follows these stores in stream order)
+__global__ void k_final_norm_ep(const __half* h, const __half* w, float eps, int H, __half* out, EpDispatch epd, int M) {
+    __shared__ float sm8[8];
+    const int m = blockIdx.x;
+    block_rmsnorm_row(h + (size_t)m * H, w, eps, H, out + (size_t)m * H, sm8);
+    for (int k = threadIdx.x * 8; k < H; k += blockDim.x * 8) {
+        const uint4 v = *reinterpret_cast<const uint4*>(out + (size_t)m * H + k);     // written by this thread
+        for (int d = 0; d < epd.sig.world; ++d)
+            *reinterpret_cast<uint4*>(epd.pbuf[d] + ((size_t)epd.sig.rank * M + m) * H + k) = v;
+    }
+}
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st, __half* xq, float* sxq) {
     ProfScope ps("k_final_norm", (double)M * H * 4, st);
     k_final_norm<<<M, 256, 0, st>>>(h, w, eps, H, out, xq, sxq);
+    COUNT_LAUNCH();
+}
+void launch_final_norm_ep(const __half* h, const __half* w, float eps, int M, int H, __half* out, const EpDispatch& epd, cudaStream_t st) {
+    ProfScope ps("k_final_norm", (double)M * H * 4, st);
+    k_final_norm_ep<<<M, 256, 0, st>>>(h, w, eps, H, out, epd, M);
     COUNT_LAUNCH();
 }
 

@@ -56,6 +56,7 @@ struct RouterArgs {
     unsigned* group_counter;             // [ceil(M/8)] tickets of the row groups, zero between launches
     int no_route = 0;                    // 1: stop after the logits; the consumer (fused expert kernel) routes from them itself
     EpDispatch epd;                      // expert-parallel: the last CTA sends the rows and indices to every rank instead of building lists
+    int ep_rows_sent = 0;                // expert-parallel, many-row router: the norm kernel has sent the rows already; only the indices remain
     PfList pf;                           // static prefetch (every CTA)
 };
 
@@ -236,6 +237,8 @@ void launch_attn_fused(const AttnArgs& a, bool prep, unsigned* counters, cudaStr
 void launch_step_end(const StepEndArgs& a, cudaStream_t st);
 // xq / sxq (optional): the normed rows also in the prepared form of the many-row kernels
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st, __half* xq = nullptr, float* sxq = nullptr);
+// expert-parallel: the normed rows also go into every rank's gather buffer (RouterArgs::ep_rows_sent then tells the routing kernel)
+void launch_final_norm_ep(const __half* h, const __half* w, float eps, int M, int H, __half* out, const EpDispatch& epd, cudaStream_t st);
 void launch_wait_probe(unsigned* err, cudaStream_t st);   // test hook: a bounded wait that runs out sets bit 2 of *err
 int64_t kernel_launch_count();
 void count_launch();

@@ -573,9 +573,11 @@ __global__ void __launch_bounds__(256) k_route_rows(RouterArgs a) {
         if (warp == 0) route_row_warp(a.logits + (size_t)m * a.E, a.E, a.topk, a.inds + m * a.topk, a.scores + m * a.topk, s_route[0], lane);
         __syncthreads();
         for (int d = warp; d < sg.world; d += 8) {
-            const uint4* src = reinterpret_cast<const uint4*>(a.p + (size_t)m * a.H);
-            uint4* dst = reinterpret_cast<uint4*>(a.epd.pbuf[d] + ((size_t)sg.rank * a.M + m) * a.H);
-            for (int i = lane; i < a.H / 8; i += 32) dst[i] = __ldcg(src + i);
+            if (!a.ep_rows_sent) {
+                const uint4* src = reinterpret_cast<const uint4*>(a.p + (size_t)m * a.H);
+                uint4* dst = reinterpret_cast<uint4*>(a.epd.pbuf[d] + ((size_t)sg.rank * a.M + m) * a.H);
+                for (int i = lane; i < a.H / 8; i += 32) dst[i] = __ldcg(src + i);
+            }
             int* di = a.epd.ibuf[d] + ((size_t)sg.rank * a.M + m) * a.topk;
             if (lane < a.topk) di[lane] = a.inds[m * a.topk + lane];
         }

@@ -77,7 +77,7 @@ def test_budget_reserves_running_slots_and_charges_consumed_tokens():
     long1 = s.submit(Request(list(range(1, 21)), 3))        # 20 prompt tokens
     long2 = s.submit(Request(list(range(50, 70)), 3))
     s.round()
-    # round 1: nothing running, pool 9: slot 0 consumes 8 (two chunks; a third would exceed), pool 1 left:
+    # first scheduling round: nothing running, pool 9: slot 0 consumes 8 (two chunks; a third would exceed), pool 1 left:
     # slot 1 still makes progress by one whole chunk (forward-progress guarantee)
     assert fake.calls[:2] == [(0, 9, 8), (1, 1, 4)]
     s.run_to_completion()
