@@ -512,12 +512,13 @@ void pf_q4(PfList& pf, int i, const Q4R& q, size_t max_bytes = (size_t)48 << 20)
 bool enqueue_router(sl_engine* e, const RouterArgs& ra, int M, bool pdl, __half* xq = nullptr, float* sxq = nullptr) {
     cudaStream_t st = e->stream;
     // (expert-parallel calls take this path from 2 rows on: its routing kernel spreads the dispatch over CTAs and warps)
-    if ((M > 8 || (ra.epd.sig.world > 0 && M > 1)) && e->use_rows && !ra.no_route && e->E <= 256 && ra.norm_w && ra.ldh == e->H) {
+    // (prefill mode takes it for ANY row count: which kernels run must not depend on how a prompt is cut into calls)
+    if ((M > 8 || e->hybrid || (ra.epd.sig.world > 0 && M > 1)) && e->use_rows && !ra.no_route && e->E <= 256 && ra.norm_w && ra.ldh == e->H) {
         const bool ep = ra.epd.sig.world > 0;
         if (ep) launch_final_norm_ep(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, ra.epd, st);     // the rows leave for the peers here
         else launch_final_norm(ra.h, ra.norm_w, ra.eps, M, e->H, ra.p, st, xq, sxq);
         RouterArgs rb = ra; rb.h = ra.p; rb.ldh = e->H; rb.norm_w = nullptr; rb.ep_rows_sent = ep ? 1 : 0;
-        if (e->hybrid && M >= 64 && launch_router_mma(rb, st)) return xq != nullptr;
+        if (e->hybrid && launch_router_mma(rb, st)) return xq != nullptr;
         if (launch_router_rows(rb, st)) return xq != nullptr;
         // not covered: the one-kernel router norms the rows again from the original input
     }
@@ -589,7 +590,7 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     // batch-1 decode: the router stops at the logits and the fused expert kernel's CTAs route the row themselves
     ra.no_route = (fused && e->use_route_in_experts) ? 1 : 0;
     ea.route_here = ra.no_route;
-    const bool tc_experts = e->hybrid && M >= 64 && e->E <= 256 && e->use_rows;
+    const bool tc_experts = e->hybrid && e->E <= 256 && e->use_rows;      // prefill mode: for any row count (chunk-split invariance)
     const bool rows_experts = !tc_experts && M > 8 && e->E <= 256 && e->use_rows;
     const bool prepared = enqueue_router(e, ra, M, e->use_pdl, rows_experts ? e->xq_p : nullptr, e->sx_p);
     if (fused && launch_expert_fused(ea, st, e->use_pdl)) return;                      // one launch for gate/up + down
@@ -651,10 +652,12 @@ void enqueue_mixer(sl_engine* e, const LayerW& L, const __half* rows, const __ha
         a.row_pos_override = row_pos_override; a.qrot = e->qrot; a.part_o = e->part_o; a.part_ml = e->part_ml; a.nsplit = NSPLIT; a.gated = e->mix; a.M = M;
         // a row that is its stream's only row in this call can make its own q/K/V inside the attention kernel;
         // several rows of one stream need every row's K/V in the arena before any of them attends
-        const bool self_prep = (M == nsegs) && (row_pos_override == nullptr || M == 1);
+        // (prefill mode always prepares first and runs the tiled kernel, whatever the row count: chunk-split invariance)
+        const bool tiled = e->hybrid && nsegs == 1 && row_pos_override == nullptr && c.kv_page_size % 32 == 0;
+        const bool self_prep = !tiled && (M == nsegs) && (row_pos_override == nullptr || M == 1);
         if (!self_prep) launch_attn_prep(a, st);
         // prefill mode, one stream's chunk: the keys are walked once for 64 rows at a time on the tensor cores
-        if (!(e->hybrid && !self_prep && M >= 32 && launch_attn_prefill(a, nsegs, st)))
+        if (!(tiled && launch_attn_prefill(a, nsegs, st)))
             launch_attn_fused(a, self_prep, e->att_counters, st, e->use_pdl && self_prep);
         o.x = e->mix; o.ldx = e->attn_out;
         launch_dense(PRO_PLAIN, resid ? EPI_RESID : EPI_STORE, o, st, e->use_pdl);

@@ -362,7 +362,7 @@ def test_draft_tokens_out_of_range_are_refused(mini_engine):
 def test_prefill_mode_vs_oracle_and_chunk_split_invariance(mini_oracle):
     """The prefill-only forward (dense projections on the tcgen05 GEMM) on 256 rows: within tolerance of
     the oracle, deterministic, and bit-identical however the prompt is cut into calls -- 256 = 128 + 128
-    = 100 + 156 = 4 x 64 (the reference locks the same for its prefill kernel,
+    = 100 + 156 = 4 x 64 = 250 + 6 = 1 + 254 + 1 = 7 + 9 + 33 + 207 (the reference locks the same for its prefill kernel,
     SeedlessVerifyTests.swift:5811-5845).  Which family runs is a property of the entry point: the strict
     forward gives the same bits for 256 rows in one call as in 32-row calls."""
     V = MINI["vocab"]
@@ -371,7 +371,8 @@ def test_prefill_mode_vs_oracle_and_chunk_split_invariance(mini_oracle):
         toks = prompt(V, 256, "hybrid")
         ref = mini_oracle.stream(320).forward(toks)
         outs = {}
-        for name, cuts in (("256", [256]), ("128+128", [128, 128]), ("100+156", [100, 156]), ("4x64", [64] * 4)):
+        for name, cuts in (("256", [256]), ("128+128", [128, 128]), ("100+156", [100, 156]), ("4x64", [64] * 4), ("250+6", [250, 6]),
+                           ("1+254+1", [1, 254, 1]), ("7+9+33+207", [7, 9, 33, 207])):
             s = eng.stream(320)
             pos, parts = 0, []
             for m in cuts:
