@@ -586,7 +586,7 @@ void enqueue_moe(sl_engine* e, const LayerW& L, const LayerW* next, const __half
     int nslots = M * e->topk < e->E ? M * e->topk : e->E;
     ea.slot_sync = e->slot_sync;
     ea.rlogits = e->rlogits; ea.E = e->E; ea.inds_out = e->inds; ea.scores_out = e->scores;
-    const bool fused = e->use_fused_experts && expert_fused_applicable(ea);
+    const bool fused = e->use_fused_experts && !e->hybrid && expert_fused_applicable(ea);   // (prefill mode: one kernel family for any row count)
     // batch-1 decode: the router stops at the logits and the fused expert kernel's CTAs route the row themselves
     ra.no_route = (fused && e->use_route_in_experts) ? 1 : 0;
     ea.route_here = ra.no_route;
