@@ -273,7 +273,7 @@ def measure_prefill(Q, torch, layers, n_tokens=PREFILL_TOKENS, chunk=1024, reps=
     st.close(); eng.close()
     ms = sorted(times)[len(times) // 2]
     return {"metric": "prefill_tok_per_s", "value": n_tokens / (ms * 1e-3), "unit": "tok/s", "ms": ms, "tokens": n_tokens, "calls": n_tokens // chunk,
-            "mode": "prefill mode (sl_forward_hybrid): dense projections on the tcgen05 GEMM, experts and mixers on the row kernels",
+            "mode": "prefill mode (sl_forward_hybrid): dense projections and experts on tcgen05 GEMMs, router logits and attention on mma.sync tiles, GDN recurrence on the scan kernel",
             "kernel_shares": shares, "gpu_fault": fault}
 
 
