@@ -164,10 +164,11 @@ int32_t sl_stream_reset(sl_stream* s);
  * (may be NULL). */
 int32_t sl_forward(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_normed_f16);
 /* SpecBackend.forwardHybrid (TellRuntime.swift:96-99; SeedlessFusedVerify.swift:4215-4345): the
- * prefill-only forward.  Same contract and outputs as sl_forward, but the dense projections run on the
- * tcgen05 tensor-core GEMM.  As in the reference the result is NOT bit-identical to sl_forward (the f32
- * summation order inside a group of 64 inputs differs) but it is deterministic and independent of how
- * a prompt is split into calls.  Which family runs is decided by which entry point is called, never by M. */
+ * prefill-only forward.  Same contract and outputs as sl_forward, but the dense projections and the experts run
+ * as tcgen05 tensor-core GEMMs on dequantised fp16 weights, the router logits and attention on tensor-core tiles.
+ * As in the reference the result is NOT bit-identical to sl_forward (f32 summation orders differ) but it is
+ * deterministic and independent of how a prompt is split into calls, down to one-row pieces.  Which family runs
+ * is decided by which entry point is called, never by M. */
 int32_t sl_forward_hybrid(sl_stream* s, const int32_t* tokens, int32_t M, uint16_t* out_normed_f16);
 /* SpecBackend.hybridChunk (TellRuntime.swift:234-238): rows per prefill call = min(1024, max_rows). */
 int32_t sl_hybrid_chunk(sl_engine* e);
@@ -254,8 +255,8 @@ int32_t sl_op_qmm4_device(const void* x_dev, const void* wr_dev, const void* sr_
                           int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream);
 /* The same product for MANY rows on the tcgen05 tensor cores (accumulator in tensor memory): the
  * GEMM form the reference uses for batched and prefill rows (tiled qmm, SeedlessMetalForward.swift:160-185).
- * Same buffers as sl_op_qmm4_device; N % 128 == 0.  Results agree with the GEMV form within fp16
- * rounding (the f32 summation order inside a group of 64 inputs differs). */
+ * Same buffers as sl_op_qmm4_device; N % 16 == 0.  Results agree with the GEMV form within fp16
+ * rounding (every weight is dequantised to fp16 with one rounding and the whole K range accumulates in one f32 sum). */
 int32_t sl_op_qmm4_tc_device(const void* x_dev, const void* wr_dev, const void* sr_dev,
                              int32_t M, int32_t K, int32_t N, void* y_dev, void* cuda_stream);
 /* NO COUNTERPART IN THE REFERENCE.  Greedy tokens of final-normed rows x [M,K] against lm_head

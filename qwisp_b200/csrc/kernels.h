@@ -206,7 +206,7 @@ bool launch_expert_rows_gateup(const ExpertArgs& a, cudaStream_t st);
 bool launch_expert_rows_down(const ExpertArgs& a, cudaStream_t st);
 void launch_moe_combine(const __half* dbuf, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,
                         __half* resid, __half* out, cudaStream_t st);
-// many-row GEMM on tcgen05 tensor cores with the accumulator in tensor memory (N % 128 == 0, K % 256 == 0); 0 or an error code
+// many-row GEMM on tcgen05 tensor cores with the accumulator in tensor memory (N % 16 == 0, K % 256 == 0); 0 or an error code
 int launch_gemm_tc(const Q4R& q, int N, int K, int M, const __half* x, int ldx, __half* y, int ldy, bool add_to_y, unsigned* err, cudaStream_t st);
 // speculative-sampling rows on fp16 logits [M][V]: categorical draw, draw without the draft token, accept flag
 void launch_sample_rows(const __half* logits, const float* adj /*[V] added to every row, or nullptr*/, const int* draft, int* samp_full, int* samp_resid, int* accept, int M, int V,
