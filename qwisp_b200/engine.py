@@ -160,6 +160,11 @@ class Engine:
         assert uid.size == 128
         self._check(lib().sl_ep_init(self._h, int(rank), int(world), _ptr(uid), int(rows_per_rank)), "sl_ep_init")
 
+    def lm_head_argmax(self, normed_rows):
+        """arg-max token of the lm_head on already normed rows [M, hidden] (the first token after a prefill-mode prompt)."""
+        from . import ops
+        return ops.lm_head(self, normed_rows, want_logits=False)[1]
+
     def batch_step_argmax(self, streams, tokens):
         B = len(streams)
         arr = (C.c_void_p * B)(*[s._h for s in streams])
@@ -455,8 +460,7 @@ class LaneBatchSlots:
                 if self.hybrid:
                     normed = st.forward_hybrid(prompt[pos:end], want_hidden=last)
                     if last:
-                        from . import ops
-                        tok = int(ops.lm_head(self.engine, normed[-1:], want_logits=False)[1][0])
+                        tok = int(self.engine.lm_head_argmax(normed[-1:])[0])
                 elif last:
                     tok = int(st.step_argmax(prompt[pos:end])[-1])
                 else:
