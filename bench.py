@@ -29,7 +29,8 @@ The N=1 line carries the same 64-stream workload on one GPU as `batch64_1gpu`, s
   cfg5_1gpu -- BASELINE.json's continuous-batching configuration as a whole job: 64 requests through the
                token-budget scheduler and the lane slots with the shared-prefix store, wall clock; end-to-end and
                decode-only tok/s
-(`--no-batch64`, `--no-prefill`, `--no-cfg5` skip them).
+(`--no-batch64`, `--no-prefill`, `--no-cfg5` skip them).  SEEDLESS_BENCH_TRACE=1 prints the stages of the batched
+measurement with their times to stderr.
 """
 import argparse
 import json
