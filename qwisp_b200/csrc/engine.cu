@@ -373,7 +373,6 @@ int32_t build_runtime(sl_engine* e) {
     e->use_route_in_experts = !(c.flags & SL_FLAG_ROUTE_IN_ROUTER);
     e->use_fused_experts = !(c.flags & SL_FLAG_SPLIT_EXPERTS);
     e->use_rows = !(c.flags & SL_FLAG_PASS_KERNELS);
-    set_launch_pdl(!(c.flags & SL_FLAG_NO_PDL));      // (process-wide: the launch helper of the many-row and exchange kernels)
     e->use_prefetch = (c.flags & SL_FLAG_L2_PREFETCH) != 0;
     e->use_pdl = !(c.flags & SL_FLAG_NO_PDL);
     e->use_graph = !(c.flags & SL_FLAG_NO_GRAPH);

@@ -36,8 +36,6 @@ __global__ void __launch_bounds__(256) k_ep_lists(EpPeers P, int npairs, int e0,
     extern __shared__ int s_inds[];
     __shared__ int s_cnt[256], s_off[256], s_cur[256];
     const int tid = threadIdx.x;
-    pdl_wait();
-    pdl_launch_dependents();
     if (tid < P.world) { if (!ep_wait_flag(P.flags[P.rank] + tid, ep_seq(P.ctr, layer, 0))) atomicOr(err, 128u); }
     s_cnt[tid] = 0; s_off[tid] = 0; s_cur[tid] = 0;
     __syncthreads();
@@ -71,7 +69,7 @@ __global__ void __launch_bounds__(256) k_ep_lists(EpPeers P, int npairs, int e0,
     }
 }
 void launch_ep_lists(const EpPeers& P, int npairs, int e0, int e1, const MoeLists& lists, int layer, unsigned* err, cudaStream_t st) {
-    profile_launch("k_ep_lists", st, [&] { launch_k(k_ep_lists, dim3(1), dim3(256), (size_t)npairs * sizeof(int), st, P, npairs, e0, e1, lists, layer, err); return 0; });
+    profile_launch("k_ep_lists", st, [&] { k_ep_lists<<<1, 256, (size_t)npairs * sizeof(int), st>>>(P, npairs, e0, e1, lists, layer, err); return 0; });
 }
 
 // grid (M), 256 threads: wait for every rank's combine flag, then
@@ -80,8 +78,6 @@ void launch_ep_lists(const EpPeers& P, int npairs, int e0, int e1, const MoeList
 __global__ void __launch_bounds__(256) k_ep_combine(EpPeers P, const __half* shared_rows, const __half* scores, const __half* sgl,
                                                     int H, int topk, __half* resid, __half* out, int layer, unsigned* err) {
     const int m = blockIdx.x;
-    pdl_wait();
-    pdl_launch_dependents();
     if ((int)threadIdx.x < P.world) { if (!ep_wait_flag(P.flags[P.rank] + 8 + threadIdx.x, ep_seq(P.ctr, layer, 1))) atomicOr(err, 256u); }
     __syncthreads();
     const __half* dbuf = P.dbuf[P.rank];
@@ -96,7 +92,7 @@ __global__ void __launch_bounds__(256) k_ep_combine(EpPeers P, const __half* sha
 }
 void launch_ep_combine(const EpPeers& P, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,
                        __half* resid, __half* out, int layer, unsigned* err, cudaStream_t st) {
-    profile_launch("k_ep_combine", st, [&] { launch_k(k_ep_combine, dim3((unsigned)M), dim3(256), 0, st, P, shared_rows, scores, sgl, H, topk, resid, out, layer, err); return 0; });
+    profile_launch("k_ep_combine", st, [&] { k_ep_combine<<<M, 256, 0, st>>>(P, shared_rows, scores, sgl, H, topk, resid, out, layer, err); return 0; });
 }
 
 __global__ void k_ep_step_end(unsigned* ctr) { *ctr += 1u; }

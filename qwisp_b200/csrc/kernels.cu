@@ -27,10 +27,6 @@ int sm_count() {
     return cached[dev];
 }
 
-static bool g_launch_pdl = true;
-bool launch_pdl_enabled() { return g_launch_pdl; }
-void set_launch_pdl(bool on) { g_launch_pdl = on; }
-
 static std::atomic<int64_t> g_launches{0};
 int64_t kernel_launch_count() { return g_launches.load(); }
 #define COUNT_LAUNCH() g_launches.fetch_add(1, std::memory_order_relaxed)
@@ -503,8 +499,6 @@ __device__ __forceinline__ void block_rmsnorm_row(const __half* src, const __hal
 }
 __global__ void k_final_norm(const __half* h, const __half* w, float eps, int H, __half* out, __half* xq, float* sxq) {
     __shared__ float sm8[8];
-    pdl_wait();
-    pdl_launch_dependents();
     block_rmsnorm_row(h + (size_t)blockIdx.x * H, w, eps, H, out + (size_t)blockIdx.x * H, sm8, false, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0),
                       xq ? xq + (size_t)blockIdx.x * H : nullptr, sxq ? sxq + (size_t)blockIdx.x * (H >> 6) : nullptr);
 }
@@ -514,8 +508,6 @@ __global__ void k_final_norm(const __half* h, const __half* w, float eps, int H,
 __global__ void k_final_norm_ep(const __half* h, const __half* w, float eps, int H, __half* out, EpDispatch epd, int M) {
     __shared__ float sm8[8];
     const int m = blockIdx.x;
-    pdl_wait();
-    pdl_launch_dependents();
     block_rmsnorm_row(h + (size_t)m * H, w, eps, H, out + (size_t)m * H, sm8);
     for (int k = threadIdx.x * 8; k < H; k += blockDim.x * 8) {
         const uint4 v = *reinterpret_cast<const uint4*>(out + (size_t)m * H + k);     // written by this thread
@@ -525,12 +517,12 @@ __global__ void k_final_norm_ep(const __half* h, const __half* w, float eps, int
 }
 void launch_final_norm(const __half* h, const __half* w, float eps, int M, int H, __half* out, cudaStream_t st, __half* xq, float* sxq) {
     ProfScope ps("k_final_norm", (double)M * H * 4, st);
-    launch_k(k_final_norm, dim3((unsigned)M), dim3(256), 0, st, h, w, eps, H, out, xq, sxq);
+    k_final_norm<<<M, 256, 0, st>>>(h, w, eps, H, out, xq, sxq);
     COUNT_LAUNCH();
 }
 void launch_final_norm_ep(const __half* h, const __half* w, float eps, int M, int H, __half* out, const EpDispatch& epd, cudaStream_t st) {
     ProfScope ps("k_final_norm", (double)M * H * 4, st);
-    launch_k(k_final_norm_ep, dim3((unsigned)M), dim3(256), 0, st, h, w, eps, H, out, epd, M);
+    k_final_norm_ep<<<M, 256, 0, st>>>(h, w, eps, H, out, epd, M);
     COUNT_LAUNCH();
 }
 
@@ -1263,8 +1255,6 @@ __global__ void __launch_bounds__(128) k_gdn_core(GdnArgs a) {
 // identical bit for bit; the split only removes the per-row latency chain (and the 16-fold recomputation of q / k).
 __global__ void __launch_bounds__(128) k_gdn_prep(GdnArgs a) {
     __shared__ float red_s[8];
-    pdl_wait();
-    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m = blockIdx.y;
     const SegDesc seg = a.segs[a.row_seg[m]];
@@ -1338,8 +1328,6 @@ __global__ void __launch_bounds__(128) k_gdn_scan(GdnArgs a) {
     float4 S[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) S[i] = *reinterpret_cast<const float4*>(S_in + (size_t)(warp * 4 + i) * GDN_DK + lane * 4);
-    pdl_wait();                                // (the state above was written a whole step ago)
-    pdl_launch_dependents();
     auto stage = [&](int c, int b) {
         const int t0 = c * GS_CH, n = min(GS_CH, seg.nrows - t0);
         for (int i = tid; i < n * 32; i += 128) {                                    // q, k: 16 + 16 pieces of 16 bytes per row
@@ -1395,11 +1383,11 @@ __global__ void __launch_bounds__(128) k_gdn_scan(GdnArgs a) {
 void launch_gdn_rows(const GdnArgs& a, int M, int nsegs, cudaStream_t st) {
     {
         ProfScope ps("k_gdn_prep", (double)M * (2 * a.Hk * GDN_DK + a.Hv * GDN_DV) * 4, st);
-        launch_k(k_gdn_prep, dim3((unsigned)(a.Hk + a.Hv), (unsigned)M), dim3(128), 0, st, a);
+        k_gdn_prep<<<dim3((unsigned)(a.Hk + a.Hv), (unsigned)M), 128, 0, st>>>(a);
         COUNT_LAUNCH();
     }
     ProfScope ps("k_gdn_scan", (double)nsegs * a.Hv * GDN_DV * GDN_DK * 8, st);
-    launch_k(k_gdn_scan, dim3(8, (unsigned)a.Hv, (unsigned)nsegs), dim3(128), 0, st, a);
+    k_gdn_scan<<<dim3(8, (unsigned)a.Hv, (unsigned)nsegs), 128, 0, st>>>(a);
     COUNT_LAUNCH();
 }
 void launch_gdn_core(const GdnArgs& a, int nsegs, cudaStream_t st, bool pdl) {

@@ -192,28 +192,6 @@ struct PStepArgs {
 bool ps_plan(PsGeom& g, int n_sm);           // fills the derived fields; false if the step kernel cannot run this geometry here
 int launch_step_persistent(const PStepArgs& a, cudaStream_t st);   // cooperative launch; returns a cudaError_t
 
-
-// Launch with the programmatic-dependent-launch attribute (when the process-wide switch is on): the kernel's CTAs may be
-// scheduled while the kernel before it in the stream is still finishing, and they begin with pdl_wait(), ahead of which
-// they read nothing a kernel of the same step writes (weights, last step's state).  With the switch off, or when the
-// kernel before did not release its dependents early, this is an ordinary launch.
-bool launch_pdl_enabled();
-void set_launch_pdl(bool on);
-#ifdef __CUDACC__
-template <class... KArgs, class... Args>
-inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    if (launch_pdl_enabled()) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
-    }
-    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
-}
-#endif
-
 void launch_dense(int pro, int epi, const DenseArgs& a, cudaStream_t st, bool pdl);
 // many-row forms (more than 8 rows per call); the bool launchers return false when the shape is not covered
 bool launch_dense_rows(int pro, int epi, const DenseArgs& a, cudaStream_t st);

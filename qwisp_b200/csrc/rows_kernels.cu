@@ -39,8 +39,6 @@ __global__ void __launch_bounds__(512) k_rows_prep(RowsPrepArgs a) {
     __shared__ float part[16];
     const int row = blockIdx.x, ch = threadIdx.x >> 5, lane = threadIdx.x & 31, chunks = a.K >> 8;
     const int k0 = (ch << 8) + lane * 8;
-    pdl_wait();
-    pdl_launch_dependents();
     const uint4 v = __ldcg(reinterpret_cast<const uint4*>(a.x + (size_t)row * a.ldx + k0));
     uint4 o;
     if (PRO == PRO_PLAIN) {
@@ -63,11 +61,10 @@ __global__ void __launch_bounds__(512) k_rows_prep(RowsPrepArgs a) {
 static void launch_rows_prep_args(int pro, const RowsPrepArgs& a, int M, cudaStream_t st) {
     const unsigned threads = (unsigned)(a.K >> 8) * 32u;
     profile_launch("k_rows_prep", st, [&] {
-        const dim3 g((unsigned)M), b(threads);
-        if (pro == PRO_PLAIN) launch_k(k_rows_prep<PRO_PLAIN>, g, b, 0, st, a);
-        else if (pro == PRO_RMSNORM) launch_k(k_rows_prep<PRO_RMSNORM>, g, b, 0, st, a);
-        else if (pro == PRO_NORMGATE) launch_k(k_rows_prep<PRO_NORMGATE>, g, b, 0, st, a);
-        else launch_k(k_rows_prep<PRO_NORMGATE32>, g, b, 0, st, a);
+        if (pro == PRO_PLAIN) k_rows_prep<PRO_PLAIN><<<M, threads, 0, st>>>(a);
+        else if (pro == PRO_RMSNORM) k_rows_prep<PRO_RMSNORM><<<M, threads, 0, st>>>(a);
+        else if (pro == PRO_NORMGATE) k_rows_prep<PRO_NORMGATE><<<M, threads, 0, st>>>(a);
+        else k_rows_prep<PRO_NORMGATE32><<<M, threads, 0, st>>>(a);
         return 0;
     });
 }
@@ -179,8 +176,6 @@ __global__ void __launch_bounds__(256, RG == 1 ? 2 : 1) k_gemv_rows(RowsDenseArg
     };
     SliceRegs cur, n1, n2;                                    // this slice and the next two (weights stream two slices ahead)
     if (active) { load_slice(cur, wt, stl, 0, lane); if (slices > 1) load_slice(n1, wt, stl, 1, lane); }
-    pdl_wait();                                // (weights do not depend on the kernel before: requested ahead of the wait)
-    pdl_launch_dependents();
     stage(0, 0);
     float tot[RG][4];
 #pragma unroll
@@ -224,7 +219,7 @@ static void launch_gemv_rows_t(const RowsDenseArgs& a, cudaStream_t st) {
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_gemv_rows<EPI, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); configured = true; }
     const dim3 grid((unsigned)(((a.N >> 4) + 7) / 8), (unsigned)((a.M + 8 * RG - 1) / (8 * RG)));
-    profile_launch(EPI == EPI_RESID ? "k_gemv_rows_outproj" : "k_gemv_rows_inproj", st, [&] { launch_k(k_gemv_rows<EPI, RG>, grid, dim3(256), smem, st, a); return 0; });
+    profile_launch(EPI == EPI_RESID ? "k_gemv_rows_outproj" : "k_gemv_rows_inproj", st, [&] { k_gemv_rows<EPI, RG><<<grid, 256, smem, st>>>(a); return 0; });
 }
 // dense projection of M > 8 rows: prologue rows, then the tile kernel.  Returns false when the shape is not covered.
 bool launch_dense_rows(int pro, int epi, const DenseArgs& a, cudaStream_t st) {
@@ -279,8 +274,6 @@ __global__ void __launch_bounds__(XR_THREADS, 1) k_expert_rows(ExpertArgs a, int
     const int ntiles = DOWN ? a.H / 16 : a.I / 8;
     const int NTG = (ntiles + XR_CONS - 1) / XR_CONS;
     const int npair = a.M * a.topk;
-    pdl_wait();
-    pdl_launch_dependents();
     const int n_active = *a.lists.n_active;
     const int nshared = a.M_shared >= 0 ? a.M_shared : a.M;
     const size_t stage_bytes = xr_stage_bytes<DOWN>(K);
@@ -477,7 +470,7 @@ static bool launch_expert_rows_t(const ExpertArgs& a, cudaStream_t st) {
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(k_expert_rows<DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); configured = true; }
     const int grid = sm_count();
-    profile_launch(DOWN ? "k_expert_rows_down" : "k_expert_rows_gateup", st, [&] { launch_k(k_expert_rows<DOWN>, dim3((unsigned)grid), dim3(XR_THREADS), smem, st, a, nstages); return 0; });
+    profile_launch(DOWN ? "k_expert_rows_down" : "k_expert_rows_gateup", st, [&] { k_expert_rows<DOWN><<<grid, XR_THREADS, smem, st>>>(a, nstages); return 0; });
     return true;
 }
 bool launch_expert_rows_gateup(const ExpertArgs& a, cudaStream_t st) { return launch_expert_rows_t<false>(a, st); }
@@ -516,8 +509,6 @@ __global__ void __launch_bounds__(256, 2) k_router_rows(RouterArgs a) {
         for (int kb = 0; kb < 16; ++kb)
             wreg[kb] = (wvalid && kb < nblk) ? *reinterpret_cast<const uint4*>(wrow + kb * 256 + lane * 8) : make_uint4(0, 0, 0, 0);
     }
-    pdl_wait();                                // (the router rows above are weights: requested ahead of the wait)
-    pdl_launch_dependents();
     const int ngroups = (a.M + 7) >> 3;
     auto stage = [&](int rg, int b) {
         __half* dst = reinterpret_cast<__half*>(smem) + (size_t)b * 8 * a.H;
@@ -573,8 +564,6 @@ __global__ void __launch_bounds__(256) k_route_rows(RouterArgs a) {
     __shared__ int s_cnt[256], s_off[256], s_slot[256], s_cur[256], s_wsum[8], s_wact[8];
     __shared__ int s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    pdl_wait();
-    pdl_launch_dependents();
     if (a.epd.sig.world > 0) {
         // expert-parallel (grid = M, one row per CTA): warp 0 routes the row, then warp w stores the normed row and its
         // routing indices into rank w's gather buffers over peer memory; the CTA that finishes last raises this rank's
@@ -716,7 +705,7 @@ bool launch_router_mma(const RouterArgs& a, cudaStream_t st) {
     if (a.E > 256 || a.H % 256 || a.norm_w || a.router_q8 || a.sg_q8) return false;
     const dim3 grid((unsigned)((a.M + 63) / 64), (unsigned)((a.E + 63) / 64));
     profile_launch("k_router_mma", st, [&] { k_router_mma<<<grid, 128, 0, st>>>(a); return 0; });
-    profile_launch("k_route_rows", st, [&] { launch_k(k_route_rows, dim3((unsigned)(a.epd.sig.world > 0 ? a.M : (a.M + 7) / 8)), dim3(256), 0, st, a); return 0; });
+    profile_launch("k_route_rows", st, [&] { k_route_rows<<<a.epd.sig.world > 0 ? a.M : (a.M + 7) / 8, 256, 0, st>>>(a); return 0; });
     return true;
 }
 
@@ -736,11 +725,11 @@ bool launch_router_rows(const RouterArgs& a, cudaStream_t st) {
     const dim3 grid((unsigned)gx, (unsigned)gy);
     const bool q8 = a.router_q8 != nullptr;
     profile_launch("k_router_rows", st, [&] {
-        if (q8) launch_k(k_router_rows<true>, grid, dim3(256), smem, st, a); else launch_k(k_router_rows<false>, grid, dim3(256), smem, st, a);
+        if (q8) k_router_rows<true><<<grid, 256, smem, st>>>(a); else k_router_rows<false><<<grid, 256, smem, st>>>(a);
         return 0;
     });
     const int route_grid = a.epd.sig.world > 0 ? a.M : ngroups;
-    profile_launch("k_route_rows", st, [&] { launch_k(k_route_rows, dim3((unsigned)route_grid), dim3(256), 0, st, a); return 0; });
+    profile_launch("k_route_rows", st, [&] { k_route_rows<<<route_grid, 256, 0, st>>>(a); return 0; });
     return true;
 }
 
@@ -751,8 +740,6 @@ bool launch_router_rows(const RouterArgs& a, cudaStream_t st) {
 __global__ void __launch_bounds__(256) k_moe_combine(const __half* dbuf, const __half* shared_rows, const __half* scores, const __half* sgl,
                                                      int H, int topk, __half* resid, __half* out) {
     const int m = blockIdx.x;
-    pdl_wait();
-    pdl_launch_dependents();
     for (int n = threadIdx.x; n < H; n += blockDim.x) {
         __half acc = f2h(0.0f);
         for (int k = 0; k < topk; ++k)
@@ -764,7 +751,7 @@ __global__ void __launch_bounds__(256) k_moe_combine(const __half* dbuf, const _
 }
 void launch_moe_combine(const __half* dbuf, const __half* shared_rows, const __half* scores, const __half* sgl, int M, int H, int topk,
                         __half* resid, __half* out, cudaStream_t st) {
-    profile_launch("k_moe_combine", st, [&] { launch_k(k_moe_combine, dim3((unsigned)M), dim3(256), 0, st, dbuf, shared_rows, scores, sgl, H, topk, resid, out); return 0; });
+    profile_launch("k_moe_combine", st, [&] { k_moe_combine<<<M, 256, 0, st>>>(dbuf, shared_rows, scores, sgl, H, topk, resid, out); return 0; });
 }
 
 }  // namespace sl
